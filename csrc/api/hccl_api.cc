@@ -1,0 +1,340 @@
+// Operator entry points: parameter checks, tag, OpParam fill, then ExecOp.
+//
+// Per-operator behaviour follows the reference entry files: count == 0 returns
+// success without touching the device (all_reduce.cc:41); pointer, count, data
+// type and reduce-op checks happen before anything else (all_reduce.cc:111-137);
+// the V operators read their host uint64 arrays at entry (all_to_all_v.cc:121-128)
+// and AlltoAll / AlltoAllVC are lowered to the AlltoAllV form
+// (all_to_all_v.cc:62-73, :424-448); BatchSendRecv copies its item list
+// (batch_send_recv.cc:99-110).
+#include <cstring>
+#include "../core/log.h"
+#include "../ops/op_common.h"
+#include "../ops/param_check.h"
+#include "hccl/hccl.h"
+
+using namespace hccl;
+
+namespace {
+
+CommImpl* C(HcclComm comm) { return static_cast<CommImpl*>(comm); }
+
+HcclResult Finish(CommImpl* c, OpParam& p)
+{
+    HcclResult r = ExecOp(c, p);
+    if (!p.algName.empty()) c->ctx.Put("last_alg", std::vector<uint8_t>(p.algName.begin(), p.algName.end()));
+    return r;
+}
+
+void Fill(OpParam& p, HcclCMDType op, CommImpl* c, const void* send, void* recv, uint64_t count, HcclDataType dt, HcclReduceOp rop,
+          uint32_t root, hcclStream_t stream)
+{
+    p.op = op;
+    p.tag = std::string(CmdName(op)) + "_" + c->name;
+    p.send = send;
+    p.recv = recv;
+    p.count = count;
+    p.dtype = dt;
+    p.recvType = dt;
+    p.redOp = rop;
+    p.root = root;
+    p.stream = (cudaStream_t)stream;
+}
+
+void ReadU64(const void* hostArray, uint32_t n, std::vector<uint64_t>* out)
+{
+    const uint64_t* a = static_cast<const uint64_t*>(hostArray);
+    out->assign(a, a + n);
+}
+
+}  // namespace
+
+extern "C" {
+
+HcclResult HcclAllReduce(void* sendBuf, void* recvBuf, uint64_t count, HcclDataType dataType, HcclReduceOp op, HcclComm comm,
+                         hcclStream_t stream)
+{
+    CHK_PTR_NULL(comm);
+    if (count == 0) return HCCL_SUCCESS;
+    CHK_PTR_NULL(sendBuf);
+    CHK_PTR_NULL(recvBuf);
+    CHK_RET(CheckCount("HcclAllReduce", count));
+    CHK_RET(CheckDataType("HcclAllReduce", dataType, true, false));
+    CHK_RET(CheckReduceOp("HcclAllReduce", dataType, op));
+    OpParam p;
+    Fill(p, HCCL_CMD_ALLREDUCE, C(comm), sendBuf, recvBuf, count, dataType, op, 0, stream);
+    return Finish(C(comm), p);
+}
+
+HcclResult HcclBroadcast(void* buf, uint64_t count, HcclDataType dataType, uint32_t root, HcclComm comm, hcclStream_t stream)
+{
+    CHK_PTR_NULL(comm);
+    if (count == 0) return HCCL_SUCCESS;
+    CHK_PTR_NULL(buf);
+    CHK_RET(CheckCount("HcclBroadcast", count));
+    CHK_RET(CheckDataType("HcclBroadcast", dataType, false, false));
+    CHK_RET(CheckRank("HcclBroadcast", "root", root, (uint32_t)C(comm)->nRanks));
+    OpParam p;
+    Fill(p, HCCL_CMD_BROADCAST, C(comm), buf, buf, count, dataType, HCCL_REDUCE_RESERVED, root, stream);
+    return Finish(C(comm), p);
+}
+
+HcclResult HcclReduceScatter(void* sendBuf, void* recvBuf, uint64_t recvCount, HcclDataType dataType, HcclReduceOp op, HcclComm comm,
+                             hcclStream_t stream)
+{
+    CHK_PTR_NULL(comm);
+    if (recvCount == 0) return HCCL_SUCCESS;
+    CHK_PTR_NULL(sendBuf);
+    CHK_PTR_NULL(recvBuf);
+    CHK_RET(CheckCount("HcclReduceScatter", recvCount * (uint64_t)C(comm)->nRanks));
+    CHK_RET(CheckDataType("HcclReduceScatter", dataType, true, true));
+    CHK_RET(CheckReduceOp("HcclReduceScatter", dataType, op));
+    OpParam p;
+    Fill(p, HCCL_CMD_REDUCE_SCATTER, C(comm), sendBuf, recvBuf, recvCount, dataType, op, 0, stream);
+    return Finish(C(comm), p);
+}
+
+HcclResult HcclReduceScatterV(void* sendBuf, const void* sendCounts, const void* sendDispls, void* recvBuf, uint64_t recvCount,
+                              HcclDataType dataType, HcclReduceOp op, HcclComm comm, hcclStream_t stream)
+{
+    CHK_PTR_NULL(comm);
+    CHK_PTR_NULL(sendCounts);
+    CHK_PTR_NULL(sendDispls);
+    CommImpl* c = C(comm);
+    CHK_RET(CheckDataType("HcclReduceScatterV", dataType, true, false));
+    CHK_RET(CheckReduceOp("HcclReduceScatterV", dataType, op));
+    OpParam p;
+    Fill(p, HCCL_CMD_REDUCE_SCATTER_V, c, sendBuf, recvBuf, recvCount, dataType, op, 0, stream);
+    ReadU64(sendCounts, (uint32_t)c->nRanks, &p.sendCounts);
+    ReadU64(sendDispls, (uint32_t)c->nRanks, &p.sdispls);
+    uint64_t total = 0;
+    for (int q = 0; q < c->nRanks; ++q) {
+        CHK_RET(CheckCount("HcclReduceScatterV", p.sendCounts[(size_t)q]));
+        CHK_RET(CheckCount("HcclReduceScatterV", p.sdispls[(size_t)q] + p.sendCounts[(size_t)q]));
+        total += p.sendCounts[(size_t)q];
+    }
+    if (p.sendCounts[(size_t)c->rank] != recvCount) {
+        ReportInputError("EI0003", "HcclReduceScatterV", "recvCount", std::to_string(recvCount), "sendCounts[rank]");
+        return HCCL_E_PARA;
+    }
+    if (total == 0) return HCCL_SUCCESS;
+    CHK_PTR_NULL(sendBuf);
+    if (recvCount) CHK_PTR_NULL(recvBuf);
+    return Finish(c, p);
+}
+
+HcclResult HcclScatter(void* sendBuf, void* recvBuf, uint64_t recvCount, HcclDataType dataType, uint32_t root, HcclComm comm,
+                       hcclStream_t stream)
+{
+    CHK_PTR_NULL(comm);
+    if (recvCount == 0) return HCCL_SUCCESS;
+    CommImpl* c = C(comm);
+    CHK_PTR_NULL(recvBuf);
+    CHK_RET(CheckRank("HcclScatter", "root", root, (uint32_t)c->nRanks));
+    if ((uint32_t)c->rank == root) CHK_PTR_NULL(sendBuf);
+    CHK_RET(CheckCount("HcclScatter", recvCount * (uint64_t)c->nRanks));
+    CHK_RET(CheckDataType("HcclScatter", dataType, false, false));
+    OpParam p;
+    // only the root's send buffer is read; the other ranks pass anything
+    Fill(p, HCCL_CMD_SCATTER, c, (uint32_t)c->rank == root ? sendBuf : nullptr, recvBuf, recvCount, dataType, HCCL_REDUCE_RESERVED, root, stream);
+    return Finish(c, p);
+}
+
+HcclResult HcclAllGather(void* sendBuf, void* recvBuf, uint64_t sendCount, HcclDataType dataType, HcclComm comm, hcclStream_t stream)
+{
+    CHK_PTR_NULL(comm);
+    if (sendCount == 0) return HCCL_SUCCESS;
+    CHK_PTR_NULL(sendBuf);
+    CHK_PTR_NULL(recvBuf);
+    CHK_RET(CheckCount("HcclAllGather", sendCount * (uint64_t)C(comm)->nRanks));
+    CHK_RET(CheckDataType("HcclAllGather", dataType, false, false));
+    OpParam p;
+    Fill(p, HCCL_CMD_ALLGATHER, C(comm), sendBuf, recvBuf, sendCount, dataType, HCCL_REDUCE_RESERVED, 0, stream);
+    return Finish(C(comm), p);
+}
+
+HcclResult HcclAllGatherV(void* sendBuf, uint64_t sendCount, void* recvBuf, const void* recvCounts, const void* recvDispls,
+                          HcclDataType dataType, HcclComm comm, hcclStream_t stream)
+{
+    CHK_PTR_NULL(comm);
+    CHK_PTR_NULL(recvCounts);
+    CHK_PTR_NULL(recvDispls);
+    CommImpl* c = C(comm);
+    CHK_RET(CheckDataType("HcclAllGatherV", dataType, false, false));
+    OpParam p;
+    Fill(p, HCCL_CMD_ALLGATHER_V, c, sendBuf, recvBuf, sendCount, dataType, HCCL_REDUCE_RESERVED, 0, stream);
+    ReadU64(recvCounts, (uint32_t)c->nRanks, &p.recvCounts);
+    ReadU64(recvDispls, (uint32_t)c->nRanks, &p.rdispls);
+    uint64_t total = 0;
+    for (int q = 0; q < c->nRanks; ++q) {
+        CHK_RET(CheckCount("HcclAllGatherV", p.recvCounts[(size_t)q]));
+        CHK_RET(CheckCount("HcclAllGatherV", p.rdispls[(size_t)q] + p.recvCounts[(size_t)q]));
+        total += p.recvCounts[(size_t)q];
+    }
+    if (p.recvCounts[(size_t)c->rank] != sendCount) {
+        ReportInputError("EI0003", "HcclAllGatherV", "sendCount", std::to_string(sendCount), "recvCounts[rank]");
+        return HCCL_E_PARA;
+    }
+    if (total == 0) return HCCL_SUCCESS;
+    CHK_PTR_NULL(recvBuf);
+    if (sendCount) CHK_PTR_NULL(sendBuf);
+    return Finish(c, p);
+}
+
+static HcclResult P2pOne(const char* name, HcclSendRecvType type, void* buf, uint64_t count, HcclDataType dataType, uint32_t peer,
+                         HcclComm comm, hcclStream_t stream)
+{
+    CHK_PTR_NULL(comm);
+    CommImpl* c = C(comm);
+    CHK_RET(CheckRank(name, type == HCCL_SEND ? "destRank" : "srcRank", peer, (uint32_t)c->nRanks));
+    CHK_RET(CheckCount(name, count));
+    CHK_RET(CheckDataType(name, dataType, false, false));
+    if (count) CHK_PTR_NULL(buf);
+    OpParam p;
+    Fill(p, type == HCCL_SEND ? HCCL_CMD_SEND : HCCL_CMD_RECEIVE, c, buf, buf, count, dataType, HCCL_REDUCE_RESERVED, peer, stream);
+    HcclSendRecvItem it;
+    it.sendRecvType = type; it.buf = buf; it.count = count; it.dataType = dataType; it.remoteRank = peer;
+    p.items.push_back(it);
+    return Finish(c, p);
+}
+
+HcclResult HcclSend(void* sendBuf, uint64_t count, HcclDataType dataType, uint32_t destRank, HcclComm comm, hcclStream_t stream)
+{
+    return P2pOne("HcclSend", HCCL_SEND, sendBuf, count, dataType, destRank, comm, stream);
+}
+HcclResult HcclRecv(void* recvBuf, uint64_t count, HcclDataType dataType, uint32_t srcRank, HcclComm comm, hcclStream_t stream)
+{
+    return P2pOne("HcclRecv", HCCL_RECV, recvBuf, count, dataType, srcRank, comm, stream);
+}
+
+HcclResult HcclBatchSendRecv(HcclSendRecvItem* items, uint32_t itemNum, HcclComm comm, hcclStream_t stream)
+{
+    CHK_PTR_NULL(comm);
+    CommImpl* c = C(comm);
+    if (itemNum != 0) CHK_PTR_NULL(items);
+    OpParam p;
+    Fill(p, HCCL_CMD_BATCH_SEND_RECV, c, nullptr, nullptr, 0, HCCL_DATA_TYPE_INT8, HCCL_REDUCE_RESERVED, 0, stream);
+    for (uint32_t i = 0; i < itemNum; ++i) {
+        const HcclSendRecvItem& it = items[i];
+        if (it.sendRecvType != HCCL_SEND && it.sendRecvType != HCCL_RECV) { ReportInputError("EI0003", "HcclBatchSendRecv", "sendRecvType", std::to_string((int)it.sendRecvType), "HCCL_SEND or HCCL_RECV"); return HCCL_E_PARA; }
+        CHK_RET(CheckRank("HcclBatchSendRecv", "remoteRank", it.remoteRank, (uint32_t)c->nRanks));
+        CHK_RET(CheckCount("HcclBatchSendRecv", it.count));
+        CHK_RET(CheckDataType("HcclBatchSendRecv", it.dataType, false, false));
+        if (it.count) CHK_PTR_NULL(it.buf);
+        p.items.push_back(it);
+    }
+    // an empty batch is legal for emulated and host ranks, where every rank must take part in the launch
+    if (itemNum == 0 && !c->emulated() && !c->hostComm) return HCCL_SUCCESS;
+    return Finish(c, p);
+}
+
+HcclResult HcclAlltoAllV(const void* sendBuf, const void* sendCounts, const void* sdispls, HcclDataType sendType, const void* recvBuf,
+                         const void* recvCounts, const void* rdispls, HcclDataType recvType, HcclComm comm, hcclStream_t stream)
+{
+    CHK_PTR_NULL(comm);
+    CHK_PTR_NULL(sendCounts); CHK_PTR_NULL(sdispls); CHK_PTR_NULL(recvCounts); CHK_PTR_NULL(rdispls);
+    CommImpl* c = C(comm);
+    CHK_RET(CheckDataType("HcclAlltoAllV", sendType, false, false));
+    CHK_RET(CheckDataType("HcclAlltoAllV", recvType, false, false));
+    if (DataTypeSize(sendType) != DataTypeSize(recvType)) { ReportInputError("EI0003", "HcclAlltoAllV", "recvType", DataTypeName(recvType), "a type of the same size as sendType"); return HCCL_E_PARA; }
+    OpParam p;
+    Fill(p, HCCL_CMD_ALLTOALLV, c, sendBuf, const_cast<void*>(recvBuf), 0, sendType, HCCL_REDUCE_RESERVED, 0, stream);
+    p.recvType = recvType;
+    const uint32_t n = (uint32_t)c->nRanks;
+    ReadU64(sendCounts, n, &p.sendCounts); ReadU64(sdispls, n, &p.sdispls); ReadU64(recvCounts, n, &p.recvCounts); ReadU64(rdispls, n, &p.rdispls);
+    uint64_t maxCount = 0, sendTotal = 0, recvTotal = 0;
+    for (uint32_t q = 0; q < n; ++q) {
+        maxCount = std::max(maxCount, std::max(p.sendCounts[q], p.recvCounts[q]));
+        sendTotal += p.sendCounts[q];
+        recvTotal += p.recvCounts[q];
+    }
+    CHK_RET(CheckCount("HcclAlltoAllV", maxCount));
+    p.count = maxCount;
+    if (sendTotal) CHK_PTR_NULL(sendBuf);
+    if (recvTotal) CHK_PTR_NULL(recvBuf);
+    return Finish(c, p);
+}
+
+HcclResult HcclAlltoAll(const void* sendBuf, uint64_t sendCount, HcclDataType sendType, const void* recvBuf, uint64_t recvCount,
+                        HcclDataType recvType, HcclComm comm, hcclStream_t stream)
+{
+    CHK_PTR_NULL(comm);
+    CommImpl* c = C(comm);
+    if (sendCount == 0 && recvCount == 0) return HCCL_SUCCESS;
+    CHK_PTR_NULL(sendBuf);
+    CHK_PTR_NULL(recvBuf);
+    CHK_RET(CheckDataType("HcclAlltoAll", sendType, false, false));
+    CHK_RET(CheckDataType("HcclAlltoAll", recvType, false, false));
+    if (sendCount != recvCount || DataTypeSize(sendType) != DataTypeSize(recvType)) {
+        ReportInputError("EI0003", "HcclAlltoAll", "recvCount", std::to_string(recvCount), "sendCount, with types of equal size");
+        return HCCL_E_PARA;
+    }
+    CHK_RET(CheckCount("HcclAlltoAll", sendCount * (uint64_t)c->nRanks));
+    OpParam p;
+    Fill(p, HCCL_CMD_ALLTOALL, c, sendBuf, const_cast<void*>(recvBuf), sendCount, sendType, HCCL_REDUCE_RESERVED, 0, stream);
+    p.recvType = recvType;
+    for (int q = 0; q < c->nRanks; ++q) {
+        p.sendCounts.push_back(sendCount); p.sdispls.push_back(sendCount * (uint64_t)q);
+        p.recvCounts.push_back(recvCount); p.rdispls.push_back(recvCount * (uint64_t)q);
+    }
+    p.globalMaxBytes = sendCount * DataTypeSize(sendType);
+    return Finish(c, p);
+}
+
+HcclResult HcclAlltoAllVC(const void* sendBuf, const void* sendCountMatrix, HcclDataType sendType, const void* recvBuf, HcclDataType recvType,
+                          HcclComm comm, hcclStream_t stream)
+{
+    CHK_PTR_NULL(comm);
+    CHK_PTR_NULL(sendCountMatrix);
+    CommImpl* c = C(comm);
+    CHK_RET(CheckDataType("HcclAlltoAllVC", sendType, false, false));
+    CHK_RET(CheckDataType("HcclAlltoAllVC", recvType, false, false));
+    if (DataTypeSize(sendType) != DataTypeSize(recvType)) return HCCL_E_PARA;
+    const uint32_t n = (uint32_t)c->nRanks, me = (uint32_t)c->rank;
+    const uint64_t* m = static_cast<const uint64_t*>(sendCountMatrix);
+    OpParam p;
+    Fill(p, HCCL_CMD_ALLTOALLVC, c, sendBuf, const_cast<void*>(recvBuf), 0, sendType, HCCL_REDUCE_RESERVED, 0, stream);
+    p.recvType = recvType;
+    // row `me` = what this rank sends; column `me` = what it receives; displacements are the running sums
+    uint64_t sd = 0, rd = 0, maxCount = 0, total = 0;
+    for (uint32_t q = 0; q < n; ++q) {
+        const uint64_t s = m[(size_t)me * n + q], r = m[(size_t)q * n + me];
+        p.sendCounts.push_back(s); p.sdispls.push_back(sd); sd += s;
+        p.recvCounts.push_back(r); p.rdispls.push_back(rd); rd += r;
+    }
+    for (size_t i = 0; i < (size_t)n * n; ++i) { maxCount = std::max(maxCount, m[i]); total += m[i]; }
+    CHK_RET(CheckCount("HcclAlltoAllVC", maxCount));
+    if (total == 0) return HCCL_SUCCESS;
+    if (sd) CHK_PTR_NULL(sendBuf);
+    if (rd) CHK_PTR_NULL(recvBuf);
+    p.count = maxCount;
+    p.globalMaxBytes = maxCount * DataTypeSize(sendType);
+    return Finish(c, p);
+}
+
+HcclResult HcclReduce(void* sendBuf, void* recvBuf, uint64_t count, HcclDataType dataType, HcclReduceOp op, uint32_t root, HcclComm comm,
+                      hcclStream_t stream)
+{
+    CHK_PTR_NULL(comm);
+    if (count == 0) return HCCL_SUCCESS;
+    CommImpl* c = C(comm);
+    CHK_PTR_NULL(sendBuf);
+    CHK_RET(CheckRank("HcclReduce", "root", root, (uint32_t)c->nRanks));
+    if ((uint32_t)c->rank == root) CHK_PTR_NULL(recvBuf);
+    CHK_RET(CheckCount("HcclReduce", count));
+    CHK_RET(CheckDataType("HcclReduce", dataType, true, false));
+    CHK_RET(CheckReduceOp("HcclReduce", dataType, op));
+    OpParam p;
+    Fill(p, HCCL_CMD_REDUCE, c, sendBuf, (uint32_t)c->rank == root ? recvBuf : nullptr, count, dataType, op, root, stream);
+    return Finish(c, p);
+}
+
+HcclResult HcclBarrier(HcclComm comm, hcclStream_t stream)
+{
+    CHK_PTR_NULL(comm);
+    OpParam p;
+    Fill(p, HCCL_CMD_BARRIER, C(comm), nullptr, nullptr, 0, HCCL_DATA_TYPE_INT8, HCCL_REDUCE_RESERVED, 0, stream);
+    return Finish(C(comm), p);
+}
+
+}  // extern "C"

@@ -1,0 +1,350 @@
+#include "config.h"
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <sstream>
+#include "log.h"
+
+namespace hccl {
+namespace {
+std::string Lower(std::string s)
+{
+    std::transform(s.begin(), s.end(), s.begin(), [](unsigned char c) { return (char)tolower(c); });
+    return s;
+}
+std::string Trim(const std::string& s)
+{
+    size_t b = s.find_first_not_of(" \t\r\n");
+    if (b == std::string::npos) return "";
+    size_t e = s.find_last_not_of(" \t\r\n");
+    return s.substr(b, e - b + 1);
+}
+std::vector<std::string> Split(const std::string& s, char sep)
+{
+    std::vector<std::string> out;
+    std::string cur;
+    std::istringstream is(s);
+    while (std::getline(is, cur, sep)) out.push_back(Trim(cur));
+    return out;
+}
+bool ParseU32(const std::string& s, uint32_t* v)
+{
+    if (s.empty() || s.size() > 10) return false;
+    for (char c : s)
+        if (c < '0' || c > '9') return false;
+    unsigned long long x = strtoull(s.c_str(), nullptr, 10);
+    if (x > 0xFFFFFFFFull) return false;
+    *v = (uint32_t)x;
+    return true;
+}
+bool ParseBool(const std::string& s, bool* v)
+{
+    std::string l = Lower(s);
+    if (l == "1" || l == "true" || l == "on") { *v = true; return true; }
+    if (l == "0" || l == "false" || l == "off") { *v = false; return true; }
+    return false;
+}
+struct OpName { const char* name; std::vector<HcclCMDType> ops; };
+const std::vector<OpName>& OpNames()
+{
+    static const std::vector<OpName> k = {
+        {"allgather", {HCCL_CMD_ALLGATHER, HCCL_CMD_ALLGATHER_V}},
+        {"reducescatter", {HCCL_CMD_REDUCE_SCATTER, HCCL_CMD_REDUCE_SCATTER_V}},
+        {"allreduce", {HCCL_CMD_ALLREDUCE}},
+        {"broadcast", {HCCL_CMD_BROADCAST}},
+        {"reduce", {HCCL_CMD_REDUCE}},
+        {"scatter", {HCCL_CMD_SCATTER}},
+        {"alltoall", {HCCL_CMD_ALLTOALL, HCCL_CMD_ALLTOALLV, HCCL_CMD_ALLTOALLVC}},
+        {"barrier", {HCCL_CMD_BARRIER}},
+    };
+    return k;
+}
+bool ParseLevels(const std::string& text, AlgoLevelConfig* out, std::string* err)
+{
+    for (const std::string& item : Split(text, ';')) {
+        if (item.empty()) continue;
+        size_t c = item.find(':');
+        if (c == std::string::npos) { *err = "missing ':' in '" + item + "'"; return false; }
+        std::string lv = Lower(Trim(item.substr(0, c)));
+        std::string alg = Trim(item.substr(c + 1));
+        int idx = -1;
+        if (lv == "level0") idx = 0; else if (lv == "level1") idx = 1; else if (lv == "level2") idx = 2;
+        if (idx < 0) { *err = "unknown level '" + lv + "'"; return false; }
+        AlgoType t;
+        if (!ParseAlgoType(alg, &t)) { *err = "unknown algorithm '" + alg + "'"; return false; }
+        if (out->level[idx] != AlgoType::DEFAULT) { *err = "level given twice: '" + lv + "'"; return false; }
+        out->level[idx] = t;
+        out->specified = true;
+    }
+    return true;
+}
+}  // namespace
+
+const char* AlgoTypeName(AlgoType t)
+{
+    switch (t) {
+        case AlgoType::DEFAULT: return "default";
+        case AlgoType::NA: return "NA";
+        case AlgoType::RING: return "ring";
+        case AlgoType::HD_R: return "H-D_R";
+        case AlgoType::NHR: return "NHR";
+        case AlgoType::NHR_V1: return "NHR_V1";
+        case AlgoType::NB: return "NB";
+        case AlgoType::AHC: return "AHC";
+        case AlgoType::PIPELINE: return "pipeline";
+        case AlgoType::PAIRWISE: return "pairwise";
+        case AlgoType::MESH: return "fullmesh";
+        case AlgoType::ONESHOT: return "oneshot";
+        case AlgoType::TWOSHOT: return "twoshot";
+        case AlgoType::NVLS: return "nvls";
+        case AlgoType::LL: return "ll";
+    }
+    return "?";
+}
+
+bool ParseAlgoType(const std::string& s, AlgoType* out)
+{
+    std::string l = Lower(Trim(s));
+    static const std::map<std::string, AlgoType> k = {
+        {"na", AlgoType::NA}, {"null", AlgoType::NA}, {"ring", AlgoType::RING}, {"h-d_r", AlgoType::HD_R},
+        {"hd", AlgoType::HD_R}, {"rhd", AlgoType::HD_R}, {"nhr", AlgoType::NHR}, {"nhr_v1", AlgoType::NHR_V1},
+        {"nb", AlgoType::NB}, {"ahc", AlgoType::AHC}, {"pipeline", AlgoType::PIPELINE},
+        {"pairwise", AlgoType::PAIRWISE}, {"fullmesh", AlgoType::MESH}, {"mesh", AlgoType::MESH},
+        {"oneshot", AlgoType::ONESHOT}, {"twoshot", AlgoType::TWOSHOT}, {"nvls", AlgoType::NVLS},
+        {"ll", AlgoType::LL},
+    };
+    auto it = k.find(l);
+    if (it == k.end()) return false;
+    *out = it->second;
+    return true;
+}
+
+const AlgoLevelConfig& AlgoConfig::For(HcclCMDType op) const
+{
+    auto it = perOp.find(op);
+    return it == perOp.end() ? global : it->second;
+}
+
+bool ParseHcclAlgo(const std::string& value, AlgoConfig* out, std::string* err)
+{
+    *out = AlgoConfig();
+    std::string v = Trim(value);
+    if (v.empty()) return true;
+    if (v.find('=') == std::string::npos) return ParseLevels(v, &out->global, err);
+    for (const std::string& part : Split(v, '/')) {
+        if (part.empty()) continue;
+        size_t eq = part.find('=');
+        if (eq == std::string::npos) { *err = "global and per-operator forms cannot be mixed: '" + part + "'"; return false; }
+        std::string op = Lower(Trim(part.substr(0, eq)));
+        const OpName* found = nullptr;
+        for (auto& n : OpNames()) if (op == n.name) found = &n;
+        if (!found) { *err = "unknown operator '" + op + "'"; return false; }
+        AlgoLevelConfig lc;
+        if (!ParseLevels(part.substr(eq + 1), &lc, err)) return false;
+        for (HcclCMDType t : found->ops) {
+            if (out->perOp.count(t)) { *err = "operator configured twice: '" + op + "'"; return false; }
+            out->perOp[t] = lc;
+        }
+    }
+    return true;
+}
+
+EnvConfig ParseEnvConfig(const EnvGetter& get)
+{
+    EnvConfig c;
+    auto val = [&](const char* name, std::string* out) {
+        const char* v = get(name);
+        if (!v || !*v) return false;
+        *out = Trim(v);
+        return !out->empty();
+    };
+    std::string s, err;
+    if (val("HCCL_ALGO", &s)) {
+        if (!ParseHcclAlgo(s, &c.algo, &err)) { c.errors.push_back("HCCL_ALGO: " + err); c.algo = AlgoConfig(); }
+    }
+    if (val("HCCL_OP_EXPANSION_MODE", &s)) {
+        std::string l = Lower(s);
+        const std::string sfx = "_cachedisable";
+        if (l.size() > sfx.size() && l.compare(l.size() - sfx.size(), sfx.size(), sfx) == 0) {
+            c.planCacheEnable = false;
+            l = l.substr(0, l.size() - sfx.size());
+        }
+        // HCCL's engine names map onto this library's engines: the SM-driven
+        // engines (AIV) are the P2P kernels, the switch/co-processor reduce
+        // engines (CCU_*) are NVLS, HOST is the host-thread backend.
+        if (l == "auto" ) c.expansionMode = HCCL_ENGINE_AUTO;
+        else if (l == "p2p" || l == "aiv" || l == "ai_cpu" || l == "aicpu_ts" || l == "aicpu") c.expansionMode = HCCL_ENGINE_P2P;
+        else if (l == "nvls" || l == "ccu_ms" || l == "ccu_sched") c.expansionMode = HCCL_ENGINE_NVLS;
+        else if (l == "host" || l == "hostcpu" || l == "host_ts") c.expansionMode = HCCL_ENGINE_HOSTCPU;
+        else c.errors.push_back("HCCL_OP_EXPANSION_MODE: unsupported value '" + s + "'");
+    }
+    if (val("HCCL_DETERMINISTIC", &s)) {
+        std::string l = Lower(s);
+        if (l == "false" || l == "0") c.deterministic = Deterministic::OFF;
+        else if (l == "true" || l == "1") c.deterministic = Deterministic::ON;
+        else if (l == "strict" || l == "2") c.deterministic = Deterministic::STRICT;
+        else c.errors.push_back("HCCL_DETERMINISTIC: expected false|true|strict, got '" + s + "'");
+    }
+    if (val("HCCL_EXEC_TIMEOUT", &s)) {
+        uint32_t t;
+        // Reference range: 0..2147483647 s, 0 = never time out (HCCL_EXEC_TIMEOUT.md).
+        // "Never" is not offered on a shared GPU: 0 keeps the default.
+        if (ParseU32(s, &t) && t <= 2147483647u) c.execTimeoutS = t;
+        else c.errors.push_back("HCCL_EXEC_TIMEOUT: expected an integer number of seconds, got '" + s + "'");
+    }
+    if (val("HCCL_OP_RETRY_ENABLE", &s)) {
+        for (const std::string& kv : Split(s, ',')) {
+            auto p = Split(kv, ':');
+            bool on;
+            if (p.size() != 2 || !ParseBool(p[1], &on)) { c.errors.push_back("HCCL_OP_RETRY_ENABLE: bad item '" + kv + "'"); continue; }
+            std::string k = Lower(p[0]);
+            if (k == "l0") { /* intra-box retry is implied by L1 here */ }
+            else if (k == "l1") c.retryL1 = on;
+            else if (k == "l2") c.retryL2 = on;
+            else c.errors.push_back("HCCL_OP_RETRY_ENABLE: unknown level '" + p[0] + "'");
+        }
+    }
+    if (val("HCCL_OP_RETRY_PARAMS", &s)) {
+        for (const std::string& kv : Split(s, ',')) {
+            auto p = Split(kv, ':');
+            uint32_t v;
+            if (p.size() != 2 || !ParseU32(p[1], &v)) { c.errors.push_back("HCCL_OP_RETRY_PARAMS: bad item '" + kv + "'"); continue; }
+            std::string k = Lower(p[0]);
+            if (k == "maxcnt") c.retryMaxCnt = v;
+            else if (k == "holdtime") c.retryHoldMs = v;
+            else if (k == "intervaltime") c.retryIntervalMs = v;
+            else c.errors.push_back("HCCL_OP_RETRY_PARAMS: unknown key '" + p[0] + "'");
+        }
+    }
+    if (val("HCCL_DFS_CONFIG", &s)) {
+        for (const std::string& kv : Split(s, ',')) {
+            auto p = Split(kv, ':');
+            if (p.size() != 2) { c.errors.push_back("HCCL_DFS_CONFIG: bad item '" + kv + "'"); continue; }
+            std::string k = Lower(p[0]);
+            bool on;
+            uint32_t v;
+            if (k == "connection_fault_detection_time") {
+                if (ParseU32(p[1], &v)) c.dfs.connectionFaultDetectionTimeS = v;
+                else c.errors.push_back("HCCL_DFS_CONFIG: bad time '" + p[1] + "'");
+            } else if (!ParseBool(p[1], &on)) {
+                c.errors.push_back("HCCL_DFS_CONFIG: expected on|off in '" + kv + "'");
+            } else if (k == "stuck_detection") c.dfs.stuckDetection = on;
+            else if (k == "cluster_heartbeat") c.dfs.clusterHeartbeat = on;
+            else if (k == "inconsistent_check") c.dfs.inconsistentCheck = on;
+            else if (k == "task_exception") c.dfs.taskException = on;
+            else c.errors.push_back("HCCL_DFS_CONFIG: unknown key '" + p[0] + "'");
+        }
+    }
+    if (val("HCCL_DEBUG_CONFIG", &s)) {
+        // "ALG,TASK,RESOURCE" enables the listed modules; a leading '^' enables all but the listed.
+        bool invert = !s.empty() && s[0] == '^';
+        uint32_t m = 0;
+        for (const std::string& name : Split(invert ? s.substr(1) : s, ',')) {
+            std::string l = Lower(name);
+            if (l == "alg") m |= LOG_MOD_ALG;
+            else if (l == "task") m |= LOG_MOD_TASK;
+            else if (l == "resource") m |= LOG_MOD_RESOURCE;
+            else if (!l.empty()) c.errors.push_back("HCCL_DEBUG_CONFIG: unknown module '" + name + "'");
+        }
+        c.debugConfigMask = invert ? (~m & (LOG_MOD_ALG | LOG_MOD_TASK | LOG_MOD_RESOURCE)) : m;
+    }
+    bool b;
+    if (val("HCCL_ENTRY_LOG_ENABLE", &s)) { if (ParseBool(s, &b)) c.entryLog = b; else c.errors.push_back("HCCL_ENTRY_LOG_ENABLE: expected 0|1"); }
+    if (val("HCCL_DIAGNOSE_ENABLE", &s)) { if (ParseBool(s, &b)) c.diagnose = b; else c.errors.push_back("HCCL_DIAGNOSE_ENABLE: expected 0|1"); }
+    uint32_t u;
+    if (val("HCCL_BUFFSIZE", &s)) {
+        // MiB, minimum 1 (HCCL_BUFFSIZE.md:7-9)
+        if (ParseU32(s, &u) && u >= 1) c.bufferSizeMiB = u; else c.errors.push_back("HCCL_BUFFSIZE: expected an integer >= 1 (MiB)");
+    }
+    val("HCCL_IF_IP", &c.ifIp);
+    if (val("HCCL_IF_BASE_PORT", &s)) { if (ParseU32(s, &u) && u >= 1024 && u <= 65520) c.ifBasePort = u; else c.errors.push_back("HCCL_IF_BASE_PORT: expected 1024..65520"); }
+    if (val("HCCL_CONNECT_TIMEOUT", &s)) { if (ParseU32(s, &u) && u >= 1 && u <= 7200) c.connectTimeoutS = u; else c.errors.push_back("HCCL_CONNECT_TIMEOUT: expected 1..7200 s"); }
+    val("HCCL_ALG_TUNER_PLUGIN", &c.tunerPlugin);
+    val("HCCL_ALGO_PLUGIN_PATH", &c.algoPlugin);
+    if (val("HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO", &s)) {
+        for (const std::string& f : Split(s, ',')) {
+            char* end = nullptr;
+            double d = strtod(f.c_str(), &end);
+            if (f.empty() || *end != 0 || d < 0) { c.errors.push_back("HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO: bad ratio '" + f + "'"); c.splitRatio.clear(); break; }
+            c.splitRatio.push_back(d);
+        }
+    }
+    if (val("HCCL_NVLS_ENABLE", &s)) { if (ParseBool(s, &b)) c.nvlsEnable = b ? 1 : 0; else c.errors.push_back("HCCL_NVLS_ENABLE: expected 0|1"); }
+    if (val("HCCL_MAX_BLOCKS", &s)) { if (ParseU32(s, &u) && u >= 1 && u <= 128) c.maxBlocks = u; else c.errors.push_back("HCCL_MAX_BLOCKS: expected 1..128"); }
+    if (val("HCCL_B200_EMULATE", &s)) { if (ParseBool(s, &b)) c.emulate = b; }
+    if (val("HCCL_B200_FORCE_IPC", &s)) { if (ParseBool(s, &b)) c.forceIpc = b; }
+    return c;
+}
+
+namespace {
+std::mutex g_mu;
+EnvConfig* g_cfg = nullptr;
+}  // namespace
+
+const EnvConfig& GetEnvConfig()
+{
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_cfg) {
+        g_cfg = new EnvConfig(ParseEnvConfig([](const char* n) { return (const char*)getenv(n); }));
+        for (auto& e : g_cfg->errors) HCCL_WARNING("environment: %s (ignored)", e.c_str());
+        SetModuleLogMask(g_cfg->debugConfigMask);
+        if (g_cfg->entryLog) SetEntryLogEnabled(true);
+    }
+    return *g_cfg;
+}
+
+void ReloadEnvConfig()
+{
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        delete g_cfg;
+        g_cfg = nullptr;
+    }
+    GetEnvConfig();
+}
+
+HcclResult MergeConfig(const EnvConfig& env, const HcclCommConfig* cfg, EffectiveConfig* out)
+{
+    out->bufferBytes = (uint64_t)(env.bufferSizeMiB ? env.bufferSizeMiB : kDefaultBufferMiB) << 20;
+    out->deterministic = env.deterministic;
+    out->engine = env.expansionMode;
+    out->execTimeoutNs = (uint64_t)(env.execTimeoutS ? env.execTimeoutS : kDefaultExecTimeoutS) * 1000000000ull;
+    out->maxBlocks = env.maxBlocks;
+    out->nvlsEnable = env.nvlsEnable;
+    out->planCacheEnable = env.planCacheEnable;
+    out->commName.clear();
+    if (!cfg) return HCCL_SUCCESS;
+    if (cfg->magicWord != HCCL_COMM_CONFIG_MAGIC || cfg->size < 16 + 8 + HCCL_COMM_CONFIG_NAME_MAX) {
+        HCCL_ERROR("HcclCommConfig was not initialised with HcclCommConfigInit (magic 0x%x size %u)", cfg->magicWord, cfg->size);
+        return HCCL_E_PARA;
+    }
+    if (cfg->version > HCCL_COMM_CONFIG_VERSION) {
+        HCCL_ERROR("HcclCommConfig version %u is newer than this library (%u)", cfg->version, HCCL_COMM_CONFIG_VERSION);
+        return HCCL_E_NOT_SUPPORT;
+    }
+    if (cfg->hcclBufferSize) out->bufferBytes = (uint64_t)cfg->hcclBufferSize << 20;
+    if (cfg->hcclDeterministic != HCCL_COMM_CONFIG_UNSET) {
+        if (cfg->hcclDeterministic > 2) return HCCL_E_PARA;
+        out->deterministic = (Deterministic)cfg->hcclDeterministic;
+    }
+    size_t n = strnlen(cfg->hcclCommName, HCCL_COMM_CONFIG_NAME_MAX);
+    if (n == HCCL_COMM_CONFIG_NAME_MAX) { HCCL_ERROR("communicator name is not terminated (max %d chars)", HCCL_COMM_CONFIG_NAME_MAX - 1); return HCCL_E_PARA; }
+    out->commName.assign(cfg->hcclCommName, n);
+    if (cfg->hcclOpExpansionMode) {
+        if (cfg->hcclOpExpansionMode >= HCCL_ENGINE_MAX) return HCCL_E_PARA;
+        out->engine = (HcclCommEngine)cfg->hcclOpExpansionMode;
+    }
+    if (cfg->hcclExecTimeoutMs) out->execTimeoutNs = (uint64_t)cfg->hcclExecTimeoutMs * 1000000ull;
+    if (cfg->hcclMaxBlocks) out->maxBlocks = cfg->hcclMaxBlocks;
+    if (cfg->hcclNvlsEnable == 1) out->nvlsEnable = 0; else if (cfg->hcclNvlsEnable == 2) out->nvlsEnable = 1;
+    return HCCL_SUCCESS;
+}
+
+TimeoutChain DeriveTimeouts(uint64_t execNs)
+{
+    const uint64_t s = 1000000000ull;
+    return TimeoutChain{execNs, execNs + 20 * s, execNs + 30 * s, execNs + 50 * s};
+}
+
+}  // namespace hccl

@@ -1,0 +1,204 @@
+// Device-side view of a communicator and the cross-GPU synchronisation
+// primitives every kernel of this library uses.
+//
+// Role in HCCL terms: this is the counterpart of AivCommBase
+// (op_common/algorithm/template/aiv/aiv_communication_base_v2.h): the peer
+// buffer table (:223-251), the Record/WaitFlag flag protocol (:475-534) and the
+// per-launch tag (:261-278).  Differences that matter on a shared NVSwitch box:
+//   * flag values are 64-bit epochs that only grow, so no flag is ever cleared
+//     and there is no first-op "clear all flags" barrier;
+//   * the epoch lives in device memory, one word per block row, and is advanced
+//     by the kernel itself - a captured CUDA graph can be replayed;
+//   * every wait is bounded: after `timeoutNs` it records what it was waiting
+//     for in a host-visible status block, raises a communicator-wide abort word
+//     and returns, and later waits return at once.  No trap, no endless spin.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "dev_types.h"
+
+namespace hccl {
+
+__device__ __forceinline__ uint64_t* FlagPtr(const DevComm& c, int ownerRank, int block, int slot, int fromRank)
+{
+    return reinterpret_cast<uint64_t*>(c.slab[ownerRank] + kSlabFlagsOff) +
+           ((size_t)(block * kFlagSlots + slot) * kMaxDevRanks + fromRank) * kFlagStride;
+}
+__device__ __forceinline__ char* StagePtr(const DevComm& c, int ownerRank) { return c.slab[ownerRank] + kSlabDataOff; }
+__device__ __forceinline__ char* StageMcPtr(const DevComm& c) { return c.slabMc ? c.slabMc + kSlabDataOff : nullptr; }
+
+__device__ __forceinline__ void StReleaseSys(uint64_t* p, uint64_t v)
+{
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t LdAcquireSys(const uint64_t* p)
+{
+    uint64_t v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint64_t LdRelaxedSys(const uint64_t* p)
+{
+    uint64_t v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t LdVolatileU32(const uint32_t* p)
+{
+    uint32_t v;
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint64_t GlobalTimerNs()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __noinline__ void ReportWaitFailure(const DevComm& c, uint32_t kernelId, int block, int slot, int peer,
+                                               uint64_t expected, uint64_t seen, uint32_t err)
+{
+    if (atomicCAS(c.abortWord, 0u, err) == 0u) {
+        DevStatus* s = c.status;
+        s->kernelId = kernelId;
+        s->block = (uint32_t)block;
+        s->slot = (uint32_t)slot;
+        s->peer = (uint32_t)peer;
+        s->rank = (uint32_t)c.rank;
+        s->expected = expected;
+        s->seen = seen;
+        __threadfence_system();
+        s->error = err;
+        __threadfence_system();
+    }
+}
+
+// Spin until *flag >= want.  Returns false when the budget ran out or the
+// communicator is already aborted.  One thread calls this for one flag.
+__device__ __forceinline__ bool WaitFlagGE(const DevComm& c, const uint64_t* flag, uint64_t want, uint32_t kernelId,
+                                           int block, int slot, int peer)
+{
+    uint64_t v = LdAcquireSys(flag);
+    if (v >= want) return true;
+    if (LdVolatileU32(c.abortWord) != 0u) return false;
+    const uint64_t t0 = GlobalTimerNs();
+    uint32_t spins = 0;
+    for (;;) {
+        v = LdAcquireSys(flag);
+        if (v >= want) return true;
+        if ((++spins & 0x3FFu) == 0u) {
+            if (LdVolatileU32(c.abortWord) != 0u) return false;
+            if (GlobalTimerNs() - t0 > c.timeoutNs) {
+                ReportWaitFailure(c, kernelId, block, slot, peer, want, v, DEV_ERR_TIMEOUT);
+                return false;
+            }
+        }
+    }
+}
+
+// Epoch handling.  A kernel that performs S cross-rank sync points per block
+// reads its row's epoch at entry and publishes epoch+S at exit; sync point k
+// (0-based) uses the flag value epoch+k+1.
+__device__ __forceinline__ uint64_t LoadEpoch(const DevComm& c, int block)
+{
+    return *reinterpret_cast<volatile uint64_t*>(c.epochs + block);
+}
+// Call after the last use of the epoch by every thread of the block.
+__device__ __forceinline__ void StoreEpoch(const DevComm& c, int block, uint64_t next)
+{
+    __syncthreads();
+    if (threadIdx.x == 0) *reinterpret_cast<volatile uint64_t*>(c.epochs + block) = next;
+}
+
+// LL (flag-in-data) ops keep their own counter row so that the slot parity
+// alternates op by op whatever other kernels ran in between.
+__device__ __forceinline__ uint64_t LoadLLEpoch(const DevComm& c, int block)
+{
+    return *reinterpret_cast<volatile uint64_t*>(c.epochs + kMaxBlocks + block);
+}
+__device__ __forceinline__ void StoreLLEpoch(const DevComm& c, int block, uint64_t next)
+{
+    __syncthreads();
+    if (threadIdx.x == 0) *reinterpret_cast<volatile uint64_t*>(c.epochs + kMaxBlocks + block) = next;
+}
+
+// Barrier among the blocks with index `block` of all ranks, on flag slot `slot`.
+// Everything the calling block wrote before the barrier (local or peer memory)
+// is visible to every participating block after it.  All threads of the block
+// must call it.  Returns false on timeout / abort (data is then meaningless but
+// the kernel can run to its end without waiting again).
+__device__ __forceinline__ bool RankBarrier(const DevComm& c, int block, int slot, uint64_t value, uint32_t kernelId)
+{
+    __shared__ int s_ok;
+    __syncthreads();
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < c.nRanks) {
+        const int peer = threadIdx.x;
+        __threadfence_system();
+        StReleaseSys(FlagPtr(c, peer, block, slot, c.rank), value);
+        if (!WaitFlagGE(c, FlagPtr(c, c.rank, block, slot, peer), value, kernelId, block, slot, peer)) s_ok = 0;
+    }
+    __syncthreads();
+    return s_ok != 0;
+}
+
+// One-directional signal / wait pair (producer -> consumer), same visibility
+// guarantees as the barrier.  Call SignalPeer from ONE thread after a
+// __syncthreads() that follows the data writes.
+__device__ __forceinline__ void SignalPeer(const DevComm& c, int peer, int block, int slot, uint64_t value)
+{
+    __threadfence_system();
+    StReleaseSys(FlagPtr(c, peer, block, slot, c.rank), value);
+}
+__device__ __forceinline__ bool WaitPeer(const DevComm& c, int peer, int block, int slot, uint64_t value,
+                                         uint32_t kernelId)
+{
+    return WaitFlagGE(c, FlagPtr(c, c.rank, block, slot, peer), value, kernelId, block, slot, peer);
+}
+
+// Stuck-detection counters (reference: stuck_detect_counter_helper.h; AIV
+// EmitStuckCounter aiv_communication_base_v2.h:368-378).  Block 0 bumps `head`
+// at entry and `tail` at exit; a host watchdog compares them.
+// The running values live in device memory (no read crosses PCIe); each bump is
+// mirrored to the host-mapped status block with one posted write.
+__device__ __forceinline__ void OpHead(const DevComm& c, int block)
+{
+    if (block == 0 && threadIdx.x == 0) {
+        volatile uint64_t* h = c.epochs + 2 * kMaxBlocks;
+        const uint64_t v = *h + 1;
+        *h = v;
+        c.status->head = v;
+    }
+}
+__device__ __forceinline__ void OpTail(const DevComm& c, int block)
+{
+    if (block == 0 && threadIdx.x == 0) {
+        volatile uint64_t* t = c.epochs + 2 * kMaxBlocks + 1;
+        const uint64_t v = *t + 1;
+        *t = v;
+        c.status->tail = v;
+    }
+}
+
+// Kernel entry wrappers: `Body` is a struct with `using Args = ...` and
+// `static __device__ void Run(const DevComm&, const Args&, int block, int nBlocks)`.
+// The `Emu` form runs R ranks inside one cooperative grid (rank = blockIdx / nb),
+// used when fewer GPUs than ranks are available: blocks of different ranks wait
+// on one another, so they must be co-resident, which only a single cooperative
+// launch guarantees.
+template <class Body>
+__global__ void __launch_bounds__(Body::kThreads) CollKernel(DevComm c, typename Body::Args a)
+{
+    Body::Run(c, a, (int)blockIdx.x, (int)gridDim.x);
+}
+template <class Body>
+__global__ void __launch_bounds__(Body::kThreads)
+    CollKernelEmu(const DevComm* cs, const typename Body::Args* as, int blocksPerRank)
+{
+    const int r = (int)blockIdx.x / blocksPerRank;
+    Body::Run(cs[r], as[r], (int)blockIdx.x % blocksPerRank, blocksPerRank);
+}
+
+}  // namespace hccl

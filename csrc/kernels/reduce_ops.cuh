@@ -1,0 +1,151 @@
+// Element types, 16-byte vector pack/unpack and the four reduction operators.
+//
+// Reductions accumulate 16-bit floats in fp32 (the cast is fused into the
+// kernel that moves the data).  Supported reduce dtypes follow the reference
+// rule set (op_common.cc:4330-4335, :4394-4396): int8/16/32/64, uint64,
+// fp16/bf16/fp32/fp64; unsigned 8/16/32-bit, int128 and 8-bit floats are
+// copy-only, except fp8 e4m3/e5m2 which ReduceScatter accepts (the analogue of
+// the hif8 ReduceScatter kernel, aiv_reduce_scatter_mesh_1d_hif8.h).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace hccl {
+
+enum RedOp : int { RED_SUM = 0, RED_PROD = 1, RED_MAX = 2, RED_MIN = 3 };
+
+template <class A>
+__device__ __forceinline__ A ApplyOp(A a, A b, int op)
+{
+    switch (op) {
+        case RED_SUM: return a + b;
+        case RED_PROD: return a * b;
+        case RED_MAX: return a > b ? a : b;
+        default: return a < b ? a : b;
+    }
+}
+
+// Traits: T = storage type, Acc = accumulation type, N = elements per 16 bytes.
+template <class T>
+struct ElemTraits {
+    using Acc = T;
+    static constexpr int N = 16 / (int)sizeof(T);
+    __device__ static __forceinline__ Acc Load(T v) { return v; }
+    __device__ static __forceinline__ T Store(Acc v) { return v; }
+};
+template <>
+struct ElemTraits<__half> {
+    using Acc = float;
+    static constexpr int N = 8;
+    __device__ static __forceinline__ float Load(__half v) { return __half2float(v); }
+    __device__ static __forceinline__ __half Store(float v) { return __float2half_rn(v); }
+};
+template <>
+struct ElemTraits<__nv_bfloat16> {
+    using Acc = float;
+    static constexpr int N = 8;
+    __device__ static __forceinline__ float Load(__nv_bfloat16 v) { return __bfloat162float(v); }
+    __device__ static __forceinline__ __nv_bfloat16 Store(float v) { return __float2bfloat16_rn(v); }
+};
+template <>
+struct ElemTraits<__nv_fp8_e4m3> {
+    using Acc = float;
+    static constexpr int N = 16;
+    __device__ static __forceinline__ float Load(__nv_fp8_e4m3 v) { return float(v); }
+    __device__ static __forceinline__ __nv_fp8_e4m3 Store(float v) { return __nv_fp8_e4m3(v); }
+};
+template <>
+struct ElemTraits<__nv_fp8_e5m2> {
+    using Acc = float;
+    static constexpr int N = 16;
+    __device__ static __forceinline__ float Load(__nv_fp8_e5m2 v) { return float(v); }
+    __device__ static __forceinline__ __nv_fp8_e5m2 Store(float v) { return __nv_fp8_e5m2(v); }
+};
+
+template <class T>
+struct AccVec {
+    typename ElemTraits<T>::Acc v[ElemTraits<T>::N];
+};
+
+template <class T>
+__device__ __forceinline__ void Unpack(const uint4& raw, AccVec<T>& a)
+{
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < ElemTraits<T>::N; ++i) a.v[i] = ElemTraits<T>::Load(e[i]);
+}
+template <class T>
+__device__ __forceinline__ void Accumulate(const uint4& raw, AccVec<T>& a, int op)
+{
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < ElemTraits<T>::N; ++i) a.v[i] = ApplyOp(a.v[i], ElemTraits<T>::Load(e[i]), op);
+}
+template <class T>
+__device__ __forceinline__ uint4 Pack(const AccVec<T>& a)
+{
+    uint4 raw;
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < ElemTraits<T>::N; ++i) e[i] = ElemTraits<T>::Store(a.v[i]);
+    return raw;
+}
+
+__device__ __forceinline__ uint4 LdVec(const void* p)
+{
+    return *reinterpret_cast<const uint4*>(p);
+}
+__device__ __forceinline__ void StVec(void* p, const uint4& v) { *reinterpret_cast<uint4*>(p) = v; }
+
+// Bulk byte copy by one block; handles any alignment.  All threads call it.
+__device__ __forceinline__ void BlockCopyBytes(char* dst, const char* src, size_t n)
+{
+    if (n == 0 || dst == src) return;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    if ((((uintptr_t)dst | (uintptr_t)src) & 15u) == 0) {
+        const size_t nv = n >> 4;
+        const uint4* s = reinterpret_cast<const uint4*>(src);
+        uint4* d = reinterpret_cast<uint4*>(dst);
+        size_t i = tid;
+        for (; i + 3 * (size_t)nt < nv; i += 4 * (size_t)nt) {
+            uint4 a = s[i], b = s[i + nt], c = s[i + 2 * (size_t)nt], e = s[i + 3 * (size_t)nt];
+            d[i] = a; d[i + nt] = b; d[i + 2 * (size_t)nt] = c; d[i + 3 * (size_t)nt] = e;
+        }
+        for (; i < nv; i += nt) d[i] = s[i];
+        for (size_t b = (nv << 4) + tid; b < n; b += nt) dst[b] = src[b];
+    } else if ((((uintptr_t)dst ^ (uintptr_t)src) & 15u) == 0) {
+        // same misalignment: scalar head up to the 16-byte boundary, vector body, scalar tail
+        size_t head = (16 - ((uintptr_t)src & 15u)) & 15u;
+        if (head > n) head = n;
+        for (size_t b = tid; b < head; b += nt) dst[b] = src[b];
+        const size_t nv = (n - head) >> 4;
+        const uint4* s = reinterpret_cast<const uint4*>(src + head);
+        uint4* d = reinterpret_cast<uint4*>(dst + head);
+        for (size_t i = tid; i < nv; i += nt) d[i] = s[i];
+        for (size_t b = head + (nv << 4) + tid; b < n; b += nt) dst[b] = src[b];
+    } else if ((((uintptr_t)dst | (uintptr_t)src | n) & 3u) == 0) {
+        const uint32_t* s = reinterpret_cast<const uint32_t*>(src);
+        uint32_t* d = reinterpret_cast<uint32_t*>(dst);
+        for (size_t i = tid; i < (n >> 2); i += nt) d[i] = s[i];
+    } else {
+        for (size_t b = tid; b < n; b += nt) dst[b] = src[b];
+    }
+}
+
+// Contiguous share of [0, n) for part `idx` of `parts`; shares are multiples of
+// `gran` except the last.
+__device__ __host__ __forceinline__ void Share(size_t n, int parts, int idx, size_t gran, size_t* begin, size_t* end)
+{
+    size_t units = (n + gran - 1) / gran;
+    size_t per = (units + parts - 1) / parts;
+    size_t b = per * idx * gran, e = per * (idx + 1) * gran;
+    if (b > n) b = n;
+    if (e > n) e = n;
+    *begin = b;
+    *end = e;
+}
+
+}  // namespace hccl

@@ -1,0 +1,515 @@
+// Operator orchestration: parameter model -> selection -> sole executor (chunk
+// loop over the staging slab) -> kernel launch.
+//
+// Reference flow (src/ops/op_common/op_common.cc): Selector() :184 (status gate,
+// topology cache, cost model / cost table, tuner) -> HcclExecOp() :1259
+// (resource context by algTag, first-call consistency check :1898-1936, engine
+// dispatch, profiling report :1440), with the single-rank shortcut
+// SingleRankProc :4458 and the fast paths that skip selection for a repeated
+// call signature (op_common.cc:432, :677).  The chunk loop bound follows
+// ins_v2_all_reduce_sole_executor.cc:240-266: bytes per loop =
+// floor(region / scratchMultiple / 128) * 128, last loop takes the remainder.
+#include "op_common.h"
+#include <algorithm>
+#include <chrono>
+#include <cstring>
+#include <sstream>
+#include "../core/log.h"
+#include "../core/plan_cache.h"
+#include "../cpu/host_comm.h"
+#include "../kernels/dev_types.h"
+#include "param_check.h"
+#include "profiling.h"
+
+namespace hccl {
+
+namespace {
+
+bool Aligned16(const void* p) { return (((uintptr_t)p) & 15u) == 0; }
+uint64_t AlignDown(uint64_t v, uint64_t a) { return v / a * a; }
+uint64_t AlignUp(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+int BlocksFor(const CommImpl* c, uint64_t bytesPerRank, DevAlg alg)
+{
+    const int maxB = c->MaxBlocks();
+    if (alg == DALG_AR_LL || alg == DALG_AG_LL) {
+        int nb = (int)std::min<uint64_t>((bytesPerRank + 8191) / 8192, 8);   // 512 threads x 8 B x 2 lines per block pass
+        return std::max(1, std::min(nb, maxB));
+    }
+    // one block per 128 KiB of traffic, at least 1, at most the configured ceiling
+    uint64_t nb = (bytesPerRank + (128u << 10) - 1) / (128u << 10);
+    return (int)std::max<uint64_t>(1, std::min<uint64_t>(nb, (uint64_t)maxB));
+}
+
+struct RegInfo {
+    bool reg = false;
+    const char* peer[kMaxDevRanks] = {nullptr};
+    const char* mc = nullptr;
+};
+RegInfo Reg(const CommImpl* c, const void* p, uint64_t bytes)
+{
+    RegInfo r;
+    if (p != nullptr && bytes > 0) r.reg = c->Lookup(p, bytes, r.peer, &r.mc);
+    return r;
+}
+
+// First call of each operator type: all ranks compare what they were called with (reference inconsistent_check.h:
+// op type, data type, count, root, buffer size), so a mismatched call fails with a message instead of hanging.
+struct ConsistencyRecord { uint32_t op, dtype, redOp, root; uint64_t count, bufferBytes; };
+HcclResult FirstCallCheck(CommImpl* c, const OpParam& p)
+{
+    if (!c->bs || c->firstOpChecked[p.op] || !GetEnvConfig().dfs.inconsistentCheck) return HCCL_SUCCESS;
+    c->firstOpChecked[p.op] = true;
+    const bool countMustMatch = p.op != HCCL_CMD_ALLTOALLV && p.op != HCCL_CMD_SEND && p.op != HCCL_CMD_RECEIVE &&
+                                p.op != HCCL_CMD_BATCH_SEND_RECV && p.op != HCCL_CMD_ALLGATHER_V && p.op != HCCL_CMD_REDUCE_SCATTER_V;
+    if (p.op == HCCL_CMD_SEND || p.op == HCCL_CMD_RECEIVE || p.op == HCCL_CMD_BATCH_SEND_RECV) return HCCL_SUCCESS;  // not collective
+    ConsistencyRecord mine = {(uint32_t)p.op, (uint32_t)p.dtype, (uint32_t)p.redOp, p.root, countMustMatch ? p.count : 0, c->cfg.bufferBytes};
+    std::vector<ConsistencyRecord> all((size_t)c->nRanks);
+    CHK_RET(c->bs->AllGather(&mine, all.data(), sizeof(mine)));
+    for (int r = 0; r < c->nRanks; ++r) {
+        if (memcmp(&all[(size_t)r], &mine, sizeof(mine)) != 0) {
+            HCCL_ERROR("comm %s: rank %d and rank %d called %s with different parameters (dtype %u/%u, op %u/%u, root %u/%u, count %llu/%llu, buffer %llu/%llu)",
+                       c->name.c_str(), c->rank, r, CmdName(p.op), mine.dtype, all[(size_t)r].dtype, mine.redOp, all[(size_t)r].redOp, mine.root,
+                       all[(size_t)r].root, (unsigned long long)mine.count, (unsigned long long)all[(size_t)r].count,
+                       (unsigned long long)mine.bufferBytes, (unsigned long long)all[(size_t)r].bufferBytes);
+            return HCCL_E_PARA;
+        }
+    }
+    return HCCL_SUCCESS;
+}
+
+HcclResult LocalCopy(void* dst, const void* src, uint64_t bytes, cudaStream_t s)
+{
+    if (bytes == 0 || dst == src) return HCCL_SUCCESS;
+    CHK_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, s));
+    return HCCL_SUCCESS;
+}
+
+// Single-rank communicator: every collective degenerates to a local copy (reference SingleRankProc op_common.cc:4458).
+HcclResult SingleRank(CommImpl*, const OpParam& p)
+{
+    const uint64_t es = DataTypeSize(p.dtype);
+    switch (p.op) {
+        case HCCL_CMD_ALLREDUCE: case HCCL_CMD_REDUCE: case HCCL_CMD_ALLGATHER: case HCCL_CMD_REDUCE_SCATTER:
+        case HCCL_CMD_SCATTER: case HCCL_CMD_ALLTOALL:
+            return LocalCopy(p.recv, p.send, p.count * es, p.stream);
+        case HCCL_CMD_ALLGATHER_V:
+            return LocalCopy((char*)p.recv + p.rdispls[0] * es, p.send, p.count * es, p.stream);
+        case HCCL_CMD_REDUCE_SCATTER_V:
+            return LocalCopy(p.recv, (const char*)p.send + p.sdispls[0] * es, p.count * es, p.stream);
+        case HCCL_CMD_ALLTOALLV: case HCCL_CMD_ALLTOALLVC:
+            return LocalCopy((char*)p.recv + p.rdispls[0] * DataTypeSize(p.recvType), (const char*)p.send + p.sdispls[0] * es, p.sendCounts[0] * es, p.stream);
+        default: return HCCL_SUCCESS;  // broadcast, barrier
+    }
+}
+
+struct Exec {
+    CommImpl* c;
+    const OpParam& p;
+    const AlgEntry* alg;
+    DevAlg dalg;
+    uint64_t es;
+    int P, me;
+    LaunchTarget tgt;
+    const StageLayout& L;
+    Exec(CommImpl* comm, const OpParam& param, const AlgEntry* a)
+        : c(comm), p(param), alg(a), dalg((DevAlg)a->devAlg), es(DataTypeSize(param.dtype)), P(comm->nRanks), me(comm->rank),
+          tgt(comm->Target(param.stream)), L(comm->layout()) {}
+
+    void FillStageIn(CollArgs& a) const { for (int q = 0; q < P; ++q) a.src[q] = c->StageBase(q) + L.inOff; a.srcMc = c->StageMcBase() ? c->StageMcBase() + L.inOff : nullptr; }
+    void FillXch(CollArgs& a) const { for (int q = 0; q < P; ++q) a.xch[q] = c->StageBase(q) + L.xchOff; }
+    HcclResult Launch(const CollArgs& a, uint64_t trafficBytes) const { return LaunchCollective(tgt, dalg, p.dtype, a, BlocksFor(c, trafficBytes, dalg)); }
+    uint64_t LoopBytes(uint64_t region, uint64_t multiple) const { return AlignDown(region / multiple, 128); }
+
+    // ---- AllReduce / Reduce --------------------------------------------------
+    HcclResult AllReduceLike() const
+    {
+        const uint64_t total = p.count * es;
+        const bool isReduce = p.op == HCCL_CMD_REDUCE;
+        const bool ll = dalg == DALG_AR_LL;
+        RegInfo in = Reg(c, p.send, total), out = Reg(c, p.recv, total);
+        const bool inDirect = in.reg && Aligned16(p.send);
+        const bool nvlsAlg = dalg == DALG_AR_NVLS;
+        // NVLS needs a multicast alias for its source; a registered buffer without one is staged
+        const bool useInDirect = inDirect && (!nvlsAlg || in.mc != nullptr) && !ll;
+        const bool outAligned = Aligned16(p.recv);
+        const bool pushOut = (dalg == DALG_AR_TWOSHOT || nvlsAlg) && out.reg && outAligned && (!nvlsAlg || out.mc != nullptr) && !isReduce;
+        uint64_t chunk = total;
+        if (!ll) {
+            uint64_t limit = ~0ull;
+            if (!useInDirect) limit = std::min(limit, LoopBytes(L.inBytes, 1));
+            const bool needXch = (dalg == DALG_AR_TWOSHOT && !pushOut) || (nvlsAlg && !pushOut) || dalg == DALG_REDUCE_TWOSHOT;
+            if (needXch) limit = std::min(limit, LoopBytes(L.xchBytes, 1));
+            if (limit == 0) return HCCL_E_MEMORY;
+            chunk = std::min(total, limit);
+        }
+        for (uint64_t off = 0; off < total; off += chunk) {
+            const uint64_t n = std::min(chunk, total - off);
+            CollArgs a;
+            memset(&a, 0, sizeof(a));
+            a.in = (const char*)p.send + off;
+            a.out = (char*)p.recv + off;
+            a.bytes = n;
+            a.op = (int)p.redOp;
+            a.root = (int)p.root;
+            if (useInDirect) { for (int q = 0; q < P; ++q) a.src[q] = in.peer[q] + off; a.srcMc = in.mc ? in.mc + off : nullptr; }
+            else { FillStageIn(a); a.mode |= MODE_STAGE_IN; }
+            FillXch(a);
+            if (pushOut) {
+                a.mode |= MODE_PUSH;
+                for (int q = 0; q < P; ++q) a.dst[q] = const_cast<char*>(out.peer[q]) + off;
+                a.dstMc = out.mc ? const_cast<char*>(out.mc) + off : nullptr;
+            } else if (nvlsAlg) {
+                a.mode |= MODE_STAGE_OUT;
+                for (int q = 0; q < P; ++q) a.dst[q] = a.xch[q];
+                a.dstMc = c->StageMcBase() + L.xchOff;
+            } else if (!outAligned) {
+                a.mode |= MODE_STAGE_OUT;
+            }
+            if (dalg == DALG_REDUCE_ONESHOT) a.mode |= MODE_PUSH;   // one-shot flavour of ReduceBody
+            CHK_RET(Launch(a, dalg == DALG_AR_ONESHOT || dalg == DALG_REDUCE_ONESHOT ? n : n / (uint64_t)P * 2 + 1));
+        }
+        return HCCL_SUCCESS;
+    }
+
+    // ---- ReduceScatter(V) ----------------------------------------------------
+    HcclResult ReduceScatterLike() const
+    {
+        const bool v = p.op == HCCL_CMD_REDUCE_SCATTER_V;
+        uint64_t cntB[kMaxDevRanks], dspB[kMaxDevRanks], maxCnt = 0, inSpan = 0;
+        for (int q = 0; q < P; ++q) {
+            cntB[q] = (v ? p.sendCounts[(size_t)q] : p.count) * es;
+            dspB[q] = (v ? p.sdispls[(size_t)q] : p.count * (uint64_t)q) * es;
+            maxCnt = std::max(maxCnt, cntB[q]);
+            inSpan = std::max(inSpan, dspB[q] + cntB[q]);
+        }
+        RegInfo in = Reg(c, p.send, inSpan);
+        bool inDirect = in.reg && Aligned16(p.send);
+        for (int q = 0; q < P && inDirect; ++q) inDirect = (dspB[q] & 15u) == 0;
+        if (dalg == DALG_RS_NVLS && in.mc == nullptr) inDirect = false;
+        uint64_t chunk = maxCnt;
+        if (!inDirect) {
+            const uint64_t limit = AlignDown(L.inBytes / (uint64_t)P, 128);
+            if (limit == 0) return HCCL_E_MEMORY;
+            chunk = std::min<uint64_t>(std::max<uint64_t>(maxCnt, 1), limit);
+        }
+        if (maxCnt == 0) chunk = 1;
+        for (uint64_t off = 0; off < std::max<uint64_t>(maxCnt, 1); off += chunk) {
+            CollArgs a;
+            memset(&a, 0, sizeof(a));
+            a.in = (const char*)p.send;
+            a.out = (char*)p.recv + off;
+            a.op = (int)p.redOp;
+            uint64_t sum = 0;
+            for (int q = 0; q < P; ++q) {
+                a.cnt[q] = cntB[q] > off ? std::min(chunk, cntB[q] - off) : 0;
+                a.dsp2[q] = dspB[q] + off;
+                a.dsp[q] = inDirect ? dspB[q] + off : (uint64_t)q * AlignUp(chunk, 16);
+                sum += a.cnt[q];
+            }
+            a.bytes = sum;
+            if (inDirect) { for (int q = 0; q < P; ++q) a.src[q] = in.peer[q]; a.srcMc = in.mc; }
+            else { FillStageIn(a); a.mode |= MODE_STAGE_IN; }
+            CHK_RET(Launch(a, a.cnt[me] * (uint64_t)(P > 1 ? 1 : 1) + 1));
+            if (maxCnt == 0) break;
+        }
+        return HCCL_SUCCESS;
+    }
+
+    // ---- AllGather(V) ----------------------------------------------------------
+    HcclResult AllGatherLike() const
+    {
+        const bool v = p.op == HCCL_CMD_ALLGATHER_V;
+        uint64_t cntB[kMaxDevRanks], dspB[kMaxDevRanks], maxCnt = 0;
+        for (int q = 0; q < P; ++q) {
+            cntB[q] = (v ? p.recvCounts[(size_t)q] : p.count) * es;
+            dspB[q] = (v ? p.rdispls[(size_t)q] : p.count * (uint64_t)q) * es;
+            maxCnt = std::max(maxCnt, cntB[q]);
+        }
+        const uint64_t myBytes = p.count * es;
+        RegInfo in = Reg(c, p.send, myBytes);
+        const bool ll = dalg == DALG_AG_LL;
+        // a peer pulls block q from rank q's input, so "registered" has to hold on every rank: by contract HcclMemAlloc
+        // buffers are allocated collectively, and a rank that passes one here passes the same one everywhere
+        const bool inDirect = in.reg && !ll;
+        const bool inPlace = (const char*)p.send == (char*)p.recv + dspB[me];
+        uint64_t chunk = std::max<uint64_t>(maxCnt, 1);
+        if (!inDirect && !ll) {
+            const uint64_t limit = LoopBytes(L.inBytes, 1);
+            if (limit == 0) return HCCL_E_MEMORY;
+            chunk = std::min(chunk, limit);
+        }
+        for (uint64_t off = 0; off < std::max<uint64_t>(maxCnt, 1); off += chunk) {
+            CollArgs a;
+            memset(&a, 0, sizeof(a));
+            a.in = (const char*)p.send + off;
+            a.out = (char*)p.recv;
+            for (int q = 0; q < P; ++q) {
+                a.cnt[q] = cntB[q] > off ? std::min(chunk, cntB[q] - off) : 0;
+                a.dsp[q] = dspB[q] + off;
+            }
+            a.bytes = a.cnt[me];
+            if (inPlace) a.mode |= MODE_INPLACE;
+            if (inDirect) { for (int q = 0; q < P; ++q) a.src[q] = in.peer[q] + off; }
+            else if (!ll) { FillStageIn(a); a.mode |= MODE_STAGE_IN; }
+            uint64_t traffic = 0;
+            for (int q = 0; q < P; ++q) traffic += a.cnt[q];
+            CHK_RET(Launch(a, ll ? a.cnt[me] : traffic));
+            if (maxCnt == 0) break;
+        }
+        return HCCL_SUCCESS;
+    }
+
+    // ---- Broadcast ---------------------------------------------------------------
+    HcclResult Broadcast() const
+    {
+        const uint64_t total = p.count * es;
+        RegInfo in = Reg(c, p.send, total);
+        const bool nvlsAlg = dalg == DALG_BCAST_NVLS;
+        const bool inDirect = in.reg && !nvlsAlg;
+        uint64_t limit = ~0ull;
+        if (!inDirect && !nvlsAlg) limit = std::min(limit, LoopBytes(L.inBytes, 1));
+        if (dalg == DALG_BCAST_TWOSHOT || nvlsAlg) limit = std::min(limit, LoopBytes(L.xchBytes, 1));
+        if (limit == 0) return HCCL_E_MEMORY;
+        const uint64_t chunk = std::min(total, limit);
+        for (uint64_t off = 0; off < total; off += chunk) {
+            const uint64_t n = std::min(chunk, total - off);
+            CollArgs a;
+            memset(&a, 0, sizeof(a));
+            a.in = (const char*)p.send + off;
+            a.out = (char*)p.send + off;
+            a.bytes = n;
+            a.root = (int)p.root;
+            if (inDirect) { for (int q = 0; q < P; ++q) a.src[q] = in.peer[q] + off; }
+            else if (!nvlsAlg) { FillStageIn(a); a.mode |= MODE_STAGE_IN; }
+            FillXch(a);
+            if (nvlsAlg) a.dstMc = c->StageMcBase() + L.xchOff;
+            if (dalg == DALG_BCAST_ONESHOT) a.mode |= MODE_PUSH;
+            CHK_RET(Launch(a, n));
+        }
+        return HCCL_SUCCESS;
+    }
+
+    // ---- Scatter -----------------------------------------------------------------
+    HcclResult Scatter() const
+    {
+        const uint64_t per = p.count * es;      // bytes every rank receives
+        // only the root's buffer matters and the other ranks cannot see whether the root registered it, so the root
+        // always publishes the blocks through its slab (a local copy at HBM speed)
+        RegInfo in;
+        const bool inDirect = false;
+        uint64_t chunk = std::max<uint64_t>(per, 1);
+        if (!inDirect) {
+            const uint64_t limit = AlignDown(L.inBytes / (uint64_t)P, 128);
+            if (limit == 0) return HCCL_E_MEMORY;
+            chunk = std::min(chunk, limit);
+        }
+        for (uint64_t off = 0; off < std::max<uint64_t>(per, 1); off += chunk) {
+            const uint64_t n = per == 0 ? 0 : std::min(chunk, per - off);
+            CollArgs a;
+            memset(&a, 0, sizeof(a));
+            a.in = (const char*)p.send;
+            a.out = (char*)p.recv + off;
+            a.bytes = n;
+            a.root = (int)p.root;
+            for (int q = 0; q < P; ++q) {
+                a.dsp2[q] = per * (uint64_t)q + off;
+                a.dsp[q] = inDirect ? a.dsp2[q] : (uint64_t)q * AlignUp(chunk, 16);
+            }
+            if (inDirect) { for (int q = 0; q < P; ++q) a.src[q] = in.peer[q]; }
+            else { FillStageIn(a); a.mode |= MODE_STAGE_IN; }
+            CHK_RET(Launch(a, n));
+            if (per == 0) break;
+        }
+        return HCCL_SUCCESS;
+    }
+
+    // ---- AlltoAll / V / VC -----------------------------------------------------
+    HcclResult AlltoAllLike() const
+    {
+        const uint64_t res = DataTypeSize(p.recvType);
+        uint64_t sendB[kMaxDevRanks], sdspB[kMaxDevRanks], recvB[kMaxDevRanks], rdspB[kMaxDevRanks];
+        uint64_t span = 0, staged = 0;
+        for (int q = 0; q < P; ++q) {
+            sendB[q] = p.sendCounts[(size_t)q] * es;
+            sdspB[q] = p.sdispls[(size_t)q] * es;
+            recvB[q] = p.recvCounts[(size_t)q] * res;
+            rdspB[q] = p.rdispls[(size_t)q] * res;
+            span = std::max(span, sdspB[q] + sendB[q]);
+            staged += AlignUp(sendB[q], 16);
+        }
+        RegInfo in = Reg(c, p.send, span);
+        const bool inDirect = in.reg;
+        // Chunking needs a loop count all ranks agree on.  It is known for the uniform op and for VC (every rank holds
+        // the whole matrix, globalMaxBytes); for AlltoAllV it is not, so an unregistered AlltoAllV must fit the slab.
+        uint64_t perPeerLimit = ~0ull;
+        if (!inDirect) {
+            perPeerLimit = AlignDown(L.inBytes / (uint64_t)P, 128);
+            if (perPeerLimit == 0) return HCCL_E_MEMORY;
+            if (p.op == HCCL_CMD_ALLTOALLV && staged > L.inBytes) {
+                HCCL_ERROR("AlltoAllV: %llu bytes to send do not fit the %llu-byte staging region; allocate the send buffer with HcclMemAlloc or raise HCCL_BUFFSIZE",
+                           (unsigned long long)staged, (unsigned long long)L.inBytes);
+                return HCCL_E_MEMORY;
+            }
+        }
+        uint64_t loops = 1, chunk = ~0ull;
+        if (!inDirect && p.op != HCCL_CMD_ALLTOALLV && p.globalMaxBytes > perPeerLimit) {
+            chunk = perPeerLimit;
+            loops = (p.globalMaxBytes + chunk - 1) / chunk;
+        }
+        for (uint64_t i = 0; i < loops; ++i) {
+            const uint64_t off = loops == 1 ? 0 : i * chunk;
+            CollArgs a;
+            memset(&a, 0, sizeof(a));
+            a.in = (const char*)p.send;
+            a.out = (char*)p.recv;
+            uint64_t traffic = 0;
+            for (int q = 0; q < P; ++q) {
+                a.cnt2[q] = sendB[q] > off ? std::min(chunk, sendB[q] - off) : 0;
+                a.dsp2[q] = sdspB[q] + off;
+                a.cnt[q] = recvB[q] > off ? std::min(chunk, recvB[q] - off) : 0;
+                a.dsp[q] = rdspB[q] + off;
+                traffic += a.cnt[q];
+            }
+            a.bytes = traffic;
+            FillXch(a);
+            if (inDirect) { for (int q = 0; q < P; ++q) a.src[q] = in.peer[q]; }
+            else { FillStageIn(a); a.mode |= MODE_STAGE_IN; }
+            CHK_RET(Launch(a, traffic));
+        }
+        return HCCL_SUCCESS;
+    }
+
+    // ---- Send / Recv / BatchSendRecv -----------------------------------------
+    HcclResult PointToPoint() const
+    {
+        // two items towards the same peer in the same direction share one sequence counter: they go in separate launches
+        std::vector<HcclSendRecvItem> rest(p.items);
+        while (!rest.empty() || p.items.empty()) {
+            P2pArgs a;
+            memset(&a, 0, sizeof(a));
+            a.halfBytes = L.mailboxHalf;
+            a.mailboxOff = L.mailboxOff;
+            a.seq = c->p2pSeq();
+            bool used[2][kMaxDevRanks] = {{false}};
+            std::vector<HcclSendRecvItem> later;
+            for (const HcclSendRecvItem& it : rest) {
+                const int dir = it.sendRecvType == HCCL_SEND ? 0 : 1;
+                if (used[dir][it.remoteRank] || a.nItems == kMaxP2pItems) { later.push_back(it); continue; }
+                used[dir][it.remoteRank] = true;
+                P2pItem& d = a.items[a.nItems++];
+                d.buf = (char*)it.buf;
+                d.bytes = it.count * DataTypeSize(it.dataType);
+                d.peer = (int)it.remoteRank;
+                d.isSend = dir == 0;
+            }
+            CHK_RET(LaunchP2p(tgt, a, std::max(1, a.nItems)));
+            rest.swap(later);
+            if (p.items.empty()) break;
+        }
+        return HCCL_SUCCESS;
+    }
+
+    HcclResult Run() const
+    {
+        switch (p.op) {
+            case HCCL_CMD_ALLREDUCE: case HCCL_CMD_REDUCE: return AllReduceLike();
+            case HCCL_CMD_REDUCE_SCATTER: case HCCL_CMD_REDUCE_SCATTER_V: return ReduceScatterLike();
+            case HCCL_CMD_ALLGATHER: case HCCL_CMD_ALLGATHER_V: return AllGatherLike();
+            case HCCL_CMD_BROADCAST: return Broadcast();
+            case HCCL_CMD_SCATTER: return Scatter();
+            case HCCL_CMD_ALLTOALL: case HCCL_CMD_ALLTOALLV: case HCCL_CMD_ALLTOALLVC: return AlltoAllLike();
+            case HCCL_CMD_SEND: case HCCL_CMD_RECEIVE: case HCCL_CMD_BATCH_SEND_RECV: return PointToPoint();
+            case HCCL_CMD_BARRIER: {
+                CollArgs a;
+                memset(&a, 0, sizeof(a));
+                return LaunchCollective(tgt, DALG_BARRIER, HCCL_DATA_TYPE_INT8, a, 1);
+            }
+            default: return HCCL_E_NOT_SUPPORT;
+        }
+    }
+};
+
+OpDesc Describe(CommImpl* c, const OpParam& p)
+{
+    OpDesc d;
+    d.op = p.op;
+    d.dtype = p.dtype;
+    d.redOp = p.redOp;
+    d.root = p.root;
+    d.nRanks = (uint32_t)c->nRanks;
+    d.det = c->cfg.deterministic;
+    d.engine = c->cfg.engine;
+    d.isMc2 = p.isMc2;
+    const uint64_t es = DataTypeSize(p.dtype);
+    const uint64_t P = (uint64_t)c->nRanks;
+    const char* peers[kMaxDevRanks];
+    uint64_t inBytes = 0, outBytes = 0;
+    switch (p.op) {
+        case HCCL_CMD_ALLREDUCE: case HCCL_CMD_REDUCE: case HCCL_CMD_BROADCAST: d.bytes = p.count * es; inBytes = outBytes = d.bytes; break;
+        case HCCL_CMD_ALLGATHER: d.bytes = p.count * es * P; inBytes = p.count * es; outBytes = d.bytes; break;
+        case HCCL_CMD_REDUCE_SCATTER: case HCCL_CMD_SCATTER: d.bytes = p.count * es * P; inBytes = d.bytes; outBytes = p.count * es; break;
+        case HCCL_CMD_ALLGATHER_V: for (uint64_t v : p.recvCounts) d.bytes += v * es; inBytes = p.count * es; outBytes = d.bytes; break;
+        case HCCL_CMD_REDUCE_SCATTER_V: for (uint64_t v : p.sendCounts) d.bytes += v * es; inBytes = d.bytes; outBytes = p.count * es; break;
+        case HCCL_CMD_ALLTOALL: case HCCL_CMD_ALLTOALLV: case HCCL_CMD_ALLTOALLVC:
+            for (uint64_t v : p.sendCounts) d.bytes += v * es;
+            inBytes = outBytes = d.bytes;
+            break;
+        case HCCL_CMD_SEND: case HCCL_CMD_RECEIVE: d.bytes = p.count * es; break;
+        case HCCL_CMD_BATCH_SEND_RECV: for (auto& it : p.items) d.bytes += it.count * DataTypeSize(it.dataType); break;
+        default: break;
+    }
+    d.inRegistered = p.send && inBytes && c->Lookup(p.send, inBytes, peers, nullptr);
+    d.outRegistered = p.recv && outBytes && c->Lookup(p.recv, outBytes, peers, nullptr);
+    d.aligned16 = Aligned16(p.send) && Aligned16(p.recv);
+    d.inPlace = p.send == p.recv;
+    return d;
+}
+
+}  // namespace
+
+HcclResult ExecOp(CommImpl* c, OpParam& p)
+{
+    CHK_PTR_NULL(c);
+    CHK_RET(c->CheckReady());
+    std::lock_guard<std::mutex> lk(c->opMu);
+    const auto t0 = std::chrono::steady_clock::now();
+    HcclResult asyncErr;
+    c->PollAsyncError(&asyncErr);
+    if (asyncErr != HCCL_SUCCESS) return asyncErr;
+    ++c->opCount;
+    if (EntryLogEnabled() || GetEnvConfig().diagnose) {
+        std::ostringstream os;
+        os << "Entry-Hccl" << CmdName(p.op) << ": tag[" << p.tag << "] sendBuf[" << p.send << "] recvBuf[" << p.recv << "] count[" << p.count
+           << "] dataType[" << DataTypeName(p.dtype) << "] op[" << ReduceOpName(p.redOp) << "] root[" << p.root << "] rank[" << c->rank << "/"
+           << c->nRanks << "] stream[" << (void*)p.stream << "] comm[" << c->name << "] seq[" << c->opCount << "]";
+        HCCL_RUN_INFO("%s", os.str().c_str());
+        if (GetEnvConfig().diagnose) DiagnoseRecord(os.str());
+    }
+    if (c->hostComm) return HostExecOp(c, p);       // host engine communicators run the algorithm templates on host threads
+    if (c->nRanks == 1) return SingleRank(c, p);
+    CHK_RET(FirstCallCheck(c, p));
+    OpDesc d = Describe(c, p);
+    PlanKey key = {(uint32_t)p.op, (uint32_t)p.dtype, (uint32_t)p.redOp, p.root, d.bytes, d.Flags(), (uint32_t)c->generation};
+    Plan plan;
+    const AlgEntry* alg = nullptr;
+    const bool cacheable = c->cfg.planCacheEnable;
+    if (cacheable && c->plans->Find(key, &plan)) {
+        alg = &AlgRegistry::Instance().All()[(size_t)plan.algIndex];
+    } else {
+        Selection sel;
+        CHK_RET(SelectAlgorithm(*c->selector, *c->topo, GetEnvConfig(), d, c->name, (HcclComm)c, c->cfg.bufferBytes, &sel));
+        alg = sel.alg;
+        plan.algIndex = sel.algIndex;
+        plan.devAlg = alg->devAlg;
+        if (cacheable) c->plans->Insert(key, plan);
+    }
+    p.algName = alg->name;
+    ProfilingScope prof(c, p, alg->name.c_str(), d.bytes);
+    HcclResult r = Exec(c, p, alg).Run();
+    if (r != HCCL_SUCCESS) HCCL_ERROR("comm %s rank %d: %s with algorithm %s failed: %s", c->name.c_str(), c->rank, CmdName(p.op), alg->name.c_str(), ResultString(r));
+    prof.SetHostUs(std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count());
+    return r;
+}
+
+}  // namespace hccl

@@ -1,0 +1,36 @@
+// Operator parameter model and the single execution entry used by every
+// operator (role of OpParam, alg_param.h:758-861, and HcclExecOp,
+// op_common.cc:1259).  Counts are in elements; V arrays are copied from the
+// caller's host arrays at entry so the call can return before the kernel runs.
+#pragma once
+#include <cstdint>
+#include <string>
+#include <vector>
+#include <cuda_runtime.h>
+#include "../core/comm.h"
+#include "../select/selector.h"
+#include "hccl/hccl_types.h"
+
+namespace hccl {
+
+struct OpParam {
+    HcclCMDType op = HCCL_CMD_INVALID;
+    std::string tag;
+    const void* send = nullptr;
+    void* recv = nullptr;
+    uint64_t count = 0;
+    HcclDataType dtype = HCCL_DATA_TYPE_RESERVED;
+    HcclDataType recvType = HCCL_DATA_TYPE_RESERVED;
+    HcclReduceOp redOp = HCCL_REDUCE_RESERVED;
+    uint32_t root = 0;
+    std::vector<uint64_t> sendCounts, sdispls, recvCounts, rdispls;   // per rank, in elements
+    uint64_t globalMaxBytes = 0;     // largest single pair transfer over ALL ranks when it is known (AlltoAll, AlltoAllVC)
+    std::vector<HcclSendRecvItem> items;
+    cudaStream_t stream = nullptr;
+    bool isMc2 = false;
+    std::string algName;             // filled by ExecOp: the algorithm that ran
+};
+
+HcclResult ExecOp(CommImpl* comm, OpParam& p);
+
+}  // namespace hccl

@@ -1,0 +1,328 @@
+// Registration of the device-engine algorithms with their attributes and cost
+// coefficients.  One entry per (engine, op, strategy, template); the executor is
+// "sole" for all of them because one NVSwitch box is a single level-0 mesh
+// (reference equivalents: AivAllReduceSoleMeshOneShot / AivAllReduceSoleMeshTwoShot
+// ins_v2_all_reduce_sole_executor.cc:459,481, CcuMSAllReduceSoleMesh :548, and
+// the Sole/Mesh entries of the other operators listed with REGISTER_EXEC_V2).
+#include "selector.h"
+#include "../kernels/dev_types.h"
+#include "../kernels/launch.h"
+
+namespace hccl {
+namespace {
+
+constexpr uint64_t Bit(HcclDataType t) { return 1ull << (int)t; }
+constexpr uint64_t kReduceTypes = Bit(HCCL_DATA_TYPE_INT8) | Bit(HCCL_DATA_TYPE_INT16) | Bit(HCCL_DATA_TYPE_INT32) |
+                                  Bit(HCCL_DATA_TYPE_INT64) | Bit(HCCL_DATA_TYPE_UINT64) | Bit(HCCL_DATA_TYPE_FP16) |
+                                  Bit(HCCL_DATA_TYPE_BFP16) | Bit(HCCL_DATA_TYPE_FP32) | Bit(HCCL_DATA_TYPE_FP64);
+constexpr uint64_t kNvlsTypes = Bit(HCCL_DATA_TYPE_FP16) | Bit(HCCL_DATA_TYPE_BFP16) | Bit(HCCL_DATA_TYPE_FP32);
+constexpr uint64_t kFp8Types = Bit(HCCL_DATA_TYPE_FP8E4M3) | Bit(HCCL_DATA_TYPE_FP8E5M2);
+constexpr uint32_t kMeshShapes = (1u << (int)Level0Shape::MESH_1D) | (1u << (int)Level0Shape::SINGLE);
+
+double UsPerByte(double gbs) { return 1.0 / (gbs * 1e3); }
+
+// Common pieces of the coefficient sets.
+struct M {
+    const LinkModel& lm;
+    double p;
+    bool stageIn, stageOut;
+    M(const TopoInfo& t, const OpDesc& o) : lm(GlobalLinkModel()), p((double)t.nRanks), stageIn(!o.inRegistered || !o.aligned16), stageOut(!o.aligned16) {}
+    double link() const { return UsPerByte(lm.p2pGBs); }
+    double nvls() const { return UsPerByte(lm.nvlsGBs); }
+    double copy() const { return UsPerByte(lm.localCopyGBs); }
+};
+
+AlgEntry Base(const char* name, HcclCMDType op, HcclCommEngine eng, const char* templ, int devAlg, AlgoType family)
+{
+    AlgEntry e;
+    e.name = name;
+    e.op = op;
+    e.engine = eng;
+    e.executor = "sole";
+    e.templates = {templ};
+    e.devAlg = devAlg;
+    e.family = family;
+    e.attrs.level0Shapes = kMeshShapes;
+    e.attrs.maxRankSize = kMaxDevRanks;
+    e.attrs.needsDeviceP2p = true;
+    return e;
+}
+
+void RegisterAll()
+{
+    AlgRegistry& R = AlgRegistry::Instance();
+    // ---------------- AllReduce
+    {
+        AlgEntry e = Base("P2pAllReduceSoleMeshLL", HCCL_CMD_ALLREDUCE, HCCL_ENGINE_P2P, "MeshLL", DALG_AR_LL, AlgoType::LL);
+        e.attrs.dtypeMask = kReduceTypes;
+        e.attrs.maxBytes = kLLMaxPayload;
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            // every rank writes 2x the payload to each peer; latency-bound: modelled without a utilisation curve
+            c.B = 2.0 * (m.p - 1) * m.link() + 2.0 * m.p * m.copy();
+            c.C = m.lm.launchUs + m.lm.llHopUs;
+            c.net = NetType::LOCAL;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+    }
+    {
+        AlgEntry e = Base("P2pAllReduceSoleMeshOneShot", HCCL_CMD_ALLREDUCE, HCCL_ENGINE_P2P, "MeshOneShot", DALG_AR_ONESHOT, AlgoType::ONESHOT);
+        e.attrs.dtypeMask = kReduceTypes;
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = (m.p - 1) * m.link();
+            c.ratio = 1.0;
+            c.B = m.stageIn ? m.copy() : 0;
+            c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+    }
+    {
+        AlgEntry e = Base("P2pAllReduceSoleMeshTwoShot", HCCL_CMD_ALLREDUCE, HCCL_ENGINE_P2P, "MeshTwoShot", DALG_AR_TWOSHOT, AlgoType::TWOSHOT);
+        e.attrs.dtypeMask = kReduceTypes;
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = 2.0 * (m.p - 1) / m.p * m.link();
+            c.ratio = 1.0 / m.p;
+            c.B = (m.stageIn ? m.copy() : 0) + (m.stageOut ? m.copy() : 0) + m.copy() / m.p;
+            c.C = m.lm.launchUs + 3 * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+    }
+    {
+        AlgEntry e = Base("NvlsAllReduceSoleMesh", HCCL_CMD_ALLREDUCE, HCCL_ENGINE_NVLS, "Mesh", DALG_AR_NVLS, AlgoType::NVLS);
+        e.attrs.dtypeMask = kNvlsTypes;
+        e.attrs.supportProd = false;
+        e.attrs.supportMaxMin = false;
+        e.attrs.needsNvls = true;
+        // the switch's reduction order is not specified: excluded under deterministic / strict
+        e.attrs.orderPreserved = false;
+        e.attrs.deterministic = false;
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = (1.0 + 1.0 / m.p) * m.nvls();
+            c.ratio = 1.0 / m.p;
+            c.net = NetType::NVLS_SWITCH;
+            c.B = (m.stageIn ? m.copy() : 0) + ((!o.outRegistered || !o.aligned16) ? m.copy() : 0);
+            c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+    }
+    // ---------------- ReduceScatter (+V)
+    for (HcclCMDType op : {HCCL_CMD_REDUCE_SCATTER, HCCL_CMD_REDUCE_SCATTER_V}) {
+        const bool v = op == HCCL_CMD_REDUCE_SCATTER_V;
+        {
+            AlgEntry e = Base(v ? "P2pReduceScatterVSoleMesh" : "P2pReduceScatterSoleMesh", op, HCCL_ENGINE_P2P, "Mesh", DALG_RS_PULL, AlgoType::MESH);
+            e.attrs.dtypeMask = kReduceTypes | (v ? 0 : kFp8Types);
+            e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+                M m(t, o);
+                CostCoeff c;
+                c.A = (m.p - 1) / m.p * m.link();
+                c.ratio = 1.0 / m.p;
+                c.B = m.stageIn ? m.copy() : 0;
+                c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
+                return std::vector<CostCoeff>{c};
+            };
+            R.Register(e);
+        }
+        {
+            AlgEntry e = Base(v ? "NvlsReduceScatterVSoleMesh" : "NvlsReduceScatterSoleMesh", op, HCCL_ENGINE_NVLS, "Mesh", DALG_RS_NVLS, AlgoType::NVLS);
+            e.attrs.dtypeMask = kNvlsTypes;
+            e.attrs.supportProd = false;
+            e.attrs.supportMaxMin = false;
+            e.attrs.needsNvls = true;
+            e.attrs.orderPreserved = false;
+            e.attrs.deterministic = false;
+            e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+                M m(t, o);
+                CostCoeff c;
+                c.A = 1.0 / m.p * m.nvls() * 1.0;   // each rank receives its reduced share once; peers feed the switch in parallel
+                c.ratio = 1.0 / m.p;
+                c.net = NetType::NVLS_SWITCH;
+                c.B = m.stageIn ? m.copy() : 0;
+                c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
+                // the switch still has to pull (p-1)/p of the input out of every GPU
+                CostCoeff f;
+                f.D = 0;
+                c.D = (m.p - 1) / m.p * m.nvls() * (double)o.bytes;
+                return std::vector<CostCoeff>{c};
+            };
+            R.Register(e);
+        }
+    }
+    // ---------------- AllGather (+V)
+    for (HcclCMDType op : {HCCL_CMD_ALLGATHER, HCCL_CMD_ALLGATHER_V}) {
+        const bool v = op == HCCL_CMD_ALLGATHER_V;
+        {
+            AlgEntry e = Base(v ? "P2pAllGatherVSoleMesh" : "P2pAllGatherSoleMesh", op, HCCL_ENGINE_P2P, "Mesh", DALG_AG_PULL, AlgoType::MESH);
+            e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+                M m(t, o);
+                CostCoeff c;
+                c.A = (m.p - 1) / m.p * m.link();
+                c.ratio = 1.0 / m.p;
+                c.B = (m.stageIn ? m.copy() / m.p : 0) + m.copy() / m.p;
+                c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
+                return std::vector<CostCoeff>{c};
+            };
+            R.Register(e);
+        }
+        if (!v) {
+            AlgEntry e = Base("P2pAllGatherSoleMeshLL", op, HCCL_ENGINE_P2P, "MeshLL", DALG_AG_LL, AlgoType::LL);
+            e.attrs.opCustomCheck = [](const OpDesc& o, const TopoInfo& t, std::string* why) {
+                if (o.bytes / t.nRanks > kLLMaxPayload) { *why = "op: per-rank block exceeds the LL slot"; return false; }
+                return true;
+            };
+            e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+                M m(t, o);
+                CostCoeff c;
+                c.B = 2.0 * (m.p - 1) / m.p * m.link() + 2.0 * m.copy();
+                c.C = m.lm.launchUs + m.lm.llHopUs;
+                c.net = NetType::LOCAL;
+                return std::vector<CostCoeff>{c};
+            };
+            R.Register(e);
+        }
+    }
+    // ---------------- Broadcast
+    {
+        AlgEntry e = Base("P2pBroadcastSoleMeshOneShot", HCCL_CMD_BROADCAST, HCCL_ENGINE_P2P, "MeshOneShot", DALG_BCAST_ONESHOT, AlgoType::ONESHOT);
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = (m.p - 1) * m.link();    // the root's egress carries the message p-1 times
+            c.B = m.stageIn ? m.copy() : 0;
+            c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+    }
+    {
+        AlgEntry e = Base("P2pBroadcastSoleMeshTwoShot", HCCL_CMD_BROADCAST, HCCL_ENGINE_P2P, "MeshTwoShot", DALG_BCAST_TWOSHOT, AlgoType::TWOSHOT);
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = 2.0 * (m.p - 1) / m.p * m.link();
+            c.ratio = 1.0 / m.p;
+            c.B = (m.stageIn ? m.copy() : 0) + m.copy() / m.p;
+            c.C = m.lm.launchUs + 3 * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+    }
+    {
+        AlgEntry e = Base("NvlsBroadcastSoleMesh", HCCL_CMD_BROADCAST, HCCL_ENGINE_NVLS, "Mesh", DALG_BCAST_NVLS, AlgoType::NVLS);
+        e.attrs.needsNvls = true;
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = m.nvls();
+            c.net = NetType::NVLS_SWITCH;
+            c.B = m.copy();
+            c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+    }
+    // ---------------- Reduce
+    {
+        AlgEntry e = Base("P2pReduceSoleMeshOneShot", HCCL_CMD_REDUCE, HCCL_ENGINE_P2P, "MeshOneShot", DALG_REDUCE_ONESHOT, AlgoType::ONESHOT);
+        e.attrs.dtypeMask = kReduceTypes;
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = (m.p - 1) * m.link();
+            c.B = m.stageIn ? m.copy() : 0;
+            c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+    }
+    {
+        AlgEntry e = Base("P2pReduceSoleMeshTwoShot", HCCL_CMD_REDUCE, HCCL_ENGINE_P2P, "MeshTwoShot", DALG_REDUCE_TWOSHOT, AlgoType::TWOSHOT);
+        e.attrs.dtypeMask = kReduceTypes;
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = 2.0 * (m.p - 1) / m.p * m.link();
+            c.ratio = 1.0 / m.p;
+            c.B = m.stageIn ? m.copy() : 0;
+            c.C = m.lm.launchUs + 3 * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+    }
+    // ---------------- Scatter
+    {
+        AlgEntry e = Base("P2pScatterSoleMesh", HCCL_CMD_SCATTER, HCCL_ENGINE_P2P, "Mesh", DALG_SCATTER_PULL, AlgoType::MESH);
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = (m.p - 1) / m.p * m.link();
+            c.ratio = 1.0 / m.p;
+            c.B = m.stageIn ? m.copy() : 0;
+            c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+    }
+    // ---------------- AlltoAll family
+    for (HcclCMDType op : {HCCL_CMD_ALLTOALL, HCCL_CMD_ALLTOALLV, HCCL_CMD_ALLTOALLVC}) {
+        const char* name = op == HCCL_CMD_ALLTOALL ? "P2pAlltoAllSoleMesh" : (op == HCCL_CMD_ALLTOALLV ? "P2pAlltoAllVSoleMesh" : "P2pAlltoAllVCSoleMesh");
+        AlgEntry e = Base(name, op, HCCL_ENGINE_P2P, "Mesh", DALG_A2A_PULL, AlgoType::MESH);
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = (m.p - 1) / m.p * m.link();
+            c.ratio = 1.0 / m.p;
+            c.B = (m.stageIn ? m.copy() : 0) + m.copy() / m.p;
+            c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+    }
+    // ---------------- point to point and barrier
+    for (HcclCMDType op : {HCCL_CMD_SEND, HCCL_CMD_RECEIVE, HCCL_CMD_BATCH_SEND_RECV}) {
+        const char* name = op == HCCL_CMD_SEND ? "P2pSendSoleMesh" : (op == HCCL_CMD_RECEIVE ? "P2pRecvSoleMesh" : "P2pBatchSendRecvSoleMesh");
+        AlgEntry e = Base(name, op, HCCL_ENGINE_P2P, "Mailbox", DALG_P2P_MAILBOX, AlgoType::MESH);
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = m.link();
+            c.B = m.copy();
+            c.C = m.lm.launchUs + m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+    }
+    {
+        AlgEntry e = Base("P2pBarrierSoleMesh", HCCL_CMD_BARRIER, HCCL_ENGINE_P2P, "Mesh", DALG_BARRIER, AlgoType::MESH);
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.C = m.lm.launchUs + m.lm.barrierUs;
+            c.net = NetType::LOCAL;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+    }
+}
+
+}  // namespace
+
+void RegisterDeviceAlgorithms()
+{
+    static bool done = false;
+    if (done) return;
+    done = true;
+    RegisterAll();
+}
+
+}  // namespace hccl

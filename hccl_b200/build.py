@@ -1,0 +1,95 @@
+"""Builds the native library ``hccl_b200/lib/libhccl_b200.so`` in-tree.
+
+Every ``.cu`` file is compiled by nvcc for sm_100a only
+(``-gencode arch=compute_100a,code=sm_100a -lineinfo``), every ``.cc`` file by
+g++; objects are cached under ``build/obj`` and rebuilt when the source or any
+header is newer.  Usage: ``python -m hccl_b200.build [--force] [--verbose]``.
+"""
+from __future__ import annotations
+
+import concurrent.futures
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+CSRC = ROOT / "csrc"
+OBJ = ROOT / "build" / "obj"
+LIB_DIR = ROOT / "hccl_b200" / "lib"
+LIB = LIB_DIR / "libhccl_b200.so"
+CUDA_HOME = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+NVCC = str(CUDA_HOME / "bin" / "nvcc")
+
+NVCC_FLAGS = [
+    "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+    "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default", "--expt-relaxed-constexpr",
+    f"-I{CSRC / 'include'}", f"-I{CSRC}",
+]
+CXX_FLAGS = [
+    "-std=c++17", "-O2", "-g", "-fPIC", "-Wall", "-Wno-unused-function", "-pthread",
+    f"-I{CSRC / 'include'}", f"-I{CSRC}", f"-I{CUDA_HOME / 'include'}",
+]
+
+
+def _sources():
+    cu = sorted(CSRC.rglob("*.cu"))
+    cc = sorted(CSRC.rglob("*.cc"))
+    return cu, cc
+
+
+def _newest_header() -> float:
+    t = 0.0
+    for pat in ("*.h", "*.cuh", "*.hpp"):
+        for h in CSRC.rglob(pat):
+            t = max(t, h.stat().st_mtime)
+    return t
+
+
+def _compile(src: Path, verbose: bool, extra_flags=()):
+    rel = src.relative_to(CSRC)
+    obj = OBJ / (str(rel).replace("/", "__") + ".o")
+    if src.suffix == ".cu":
+        cmd = [NVCC, *NVCC_FLAGS, *extra_flags, "-c", str(src), "-o", str(obj)]
+    else:
+        cmd = ["g++", *CXX_FLAGS, "-c", str(src), "-o", str(obj)]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"compiling {rel} failed:\n{r.stdout}\n{r.stderr}")
+    if verbose and r.stderr.strip():
+        print(r.stderr)
+    return obj
+
+
+def build(force: bool = False, verbose: bool = False, ptxas_verbose: bool = False) -> Path:
+    OBJ.mkdir(parents=True, exist_ok=True)
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    cu, cc = _sources()
+    hdr_time = _newest_header()
+    todo, objs = [], []
+    for src in cu + cc:
+        rel = src.relative_to(CSRC)
+        obj = OBJ / (str(rel).replace("/", "__") + ".o")
+        objs.append(obj)
+        if force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_time):
+            todo.append(src)
+    extra = ("-Xptxas", "-v") if ptxas_verbose else ()
+    if todo:
+        workers = min(len(todo), max(1, (os.cpu_count() or 4)))
+        with concurrent.futures.ThreadPoolExecutor(workers) as ex:
+            list(ex.map(lambda s: _compile(s, verbose or ptxas_verbose, extra), todo))
+    if todo or not LIB.exists():
+        cmd = [NVCC, "-shared", "-o", str(LIB), *map(str, objs), "-Xcompiler", "-pthread", "-ldl", "-lrt"]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"linking failed:\n{r.stdout}\n{r.stderr}")
+    return LIB
+
+
+if __name__ == "__main__":
+    lib = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, ptxas_verbose="--ptxas" in sys.argv)
+    print(lib)

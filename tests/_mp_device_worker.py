@@ -1,0 +1,137 @@
+"""One rank of a multi-process device test: python _mp_device_worker.py <rank> <world> <rendezvous-file> <scenario>."""
+import os
+import sys
+import time
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+import torch
+
+import hccl_b200 as hb
+from hccl_b200 import Communicator, ReduceOp
+
+
+def rendezvous(rank, path):
+    if rank == 0:
+        info = Communicator.get_root_info()
+        tmp = path + ".tmp"
+        with open(tmp, "wb") as f:
+            f.write(info)
+        os.replace(tmp, path)
+        return info
+    t0 = time.time()
+    while not os.path.exists(path):
+        if time.time() - t0 > 60:
+            raise RuntimeError("no root info")
+        time.sleep(0.05)
+    return open(path, "rb").read()
+
+
+def rnd(n, dtype, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.rand(n, device="cuda", generator=g) * 2 - 1).to(dtype)
+
+
+def scenario_collectives(comm, rank, world):
+    for registered in (False, True):
+        for dtype in (torch.float32, torch.bfloat16):
+            for n in (8, 1000, 65536, 1 << 20, (1 << 22) + 16):
+                xs = [rnd(n, dtype, 10 + r) for r in range(world)]   # every rank can build all inputs: the reference is local
+                ref = torch.stack([x.double() for x in xs]).sum(0)
+                if registered:
+                    x = comm.empty((n,), dtype); x.copy_(xs[rank])
+                    y = comm.empty((n,), dtype)
+                else:
+                    x, y = xs[rank].clone(), torch.empty(n, device="cuda", dtype=dtype)
+                comm.all_reduce(x, y)
+                torch.cuda.synchronize()
+                tol = 3e-2 if dtype == torch.bfloat16 else 1e-5
+                torch.testing.assert_close(y.double(), ref, rtol=tol, atol=tol * world)
+                alg_ar = comm.last_algorithm()
+                # all-gather / reduce-scatter
+                g = comm.empty((n * world,), dtype) if registered else torch.empty(n * world, device="cuda", dtype=dtype)
+                comm.all_gather(x, g)
+                torch.cuda.synchronize()
+                assert torch.equal(g.view(-1, n)[(rank + 1) % world], xs[(rank + 1) % world])
+                big = [rnd(n * world, dtype, 50 + r) for r in range(world)]
+                if registered:
+                    b = comm.empty((n * world,), dtype); b.copy_(big[rank])
+                else:
+                    b = big[rank]
+                o = torch.empty(n, device="cuda", dtype=dtype)
+                comm.reduce_scatter(b, o)
+                torch.cuda.synchronize()
+                refrs = torch.stack([t.double() for t in big]).sum(0)[rank * n:(rank + 1) * n]
+                torch.testing.assert_close(o.double(), refrs, rtol=tol, atol=tol * world)
+                if rank == 0:
+                    print(f"ok registered={registered} {dtype} n={n} AR={alg_ar} RS={comm.last_algorithm()}", flush=True)
+    # broadcast, all-to-all, send/recv ring, barrier
+    n = 123457
+    b = rnd(n, torch.float32, 7 if rank == 1 % world else 70 + rank)
+    comm.broadcast(b, 1 % world)
+    torch.cuda.synchronize()
+    assert torch.equal(b, rnd(n, torch.float32, 7))
+    s = rnd(n * world, torch.float32, 300 + rank)
+    r = torch.empty_like(s)
+    comm.all_to_all(s, r)
+    torch.cuda.synchronize()
+    for q in range(world):
+        assert torch.equal(r[q * n:(q + 1) * n], rnd(n * world, torch.float32, 300 + q)[rank * n:(rank + 1) * n])
+    out = torch.empty(n, device="cuda")
+    comm.batch_send_recv([("send", s[:n].contiguous(), (rank + 1) % world), ("recv", out, (rank - 1) % world)])
+    torch.cuda.synchronize()
+    assert torch.equal(out, rnd(n * world, torch.float32, 300 + (rank - 1) % world)[:n])
+    if world >= 2:
+        if rank == 0:
+            comm.send(s[:1000].contiguous(), 1)
+        elif rank == 1:
+            got = torch.empty(1000, device="cuda")
+            comm.recv(got, 0)
+            torch.cuda.synchronize()
+            assert torch.equal(got, rnd(n * world, torch.float32, 300)[:1000])
+    comm.barrier()
+    torch.cuda.synchronize()
+    assert comm.async_error() == hb.Result.SUCCESS
+
+
+def scenario_peer_exit(comm, rank, world):
+    """A rank leaves between steps; the survivors' next collective ends with an
+    error within the wait budget instead of hanging."""
+    x = torch.ones(1024, device="cuda")
+    comm.all_reduce(x)
+    torch.cuda.synchronize()
+    assert float(x[0]) == world
+    if rank == world - 1:
+        torch.cuda.synchronize()
+        os._exit(0)            # leaves with nothing in flight
+    time.sleep(1.0)
+    t0 = time.time()
+    failed = False
+    try:
+        comm.all_reduce(x)
+        torch.cuda.synchronize()
+        failed = comm.async_error() != hb.Result.SUCCESS
+    except hb.HcclError:
+        failed = True
+    assert failed, "the collective after a peer left must report an error"
+    assert time.time() - t0 < 30
+    y = torch.ones(4, device="cuda") * 3          # the context is still usable
+    assert float(y.sum()) == 12.0
+    print(f"rank {rank}: peer exit detected after {time.time() - t0:.2f}s", flush=True)
+    os._exit(0)
+
+
+def main():
+    rank, world, path, scenario = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
+    torch.cuda.set_device(rank % torch.cuda.device_count())
+    info = rendezvous(rank, path)
+    timeout_ms = 3000 if scenario == "peer_exit" else 0
+    comm = Communicator.from_root_info(info, rank, world, hb.make_config(buffer_mib=64, exec_timeout_ms=timeout_ms))
+    {"collectives": scenario_collectives, "peer_exit": scenario_peer_exit}[scenario](comm, rank, world)
+    comm.destroy()
+    print(f"rank {rank} done", flush=True)
+
+
+if __name__ == "__main__":
+    main()
