@@ -349,7 +349,7 @@ HcclResult EmuGroup::Create(int nRanks, const HcclCommConfig* cfg, std::vector<C
     std::unique_ptr<EmuGroup> g(new EmuGroup());
     g->nRanks_ = nRanks;
     g->alive_ = nRanks;
-    g->have_.assign((size_t)nRanks, false);
+    g->queues_.resize((size_t)nRanks);
     EffectiveConfig eff;
     CHK_RET(MergeConfig(GetEnvConfig(), cfg, &eff));
     // emulated ranks share one GPU: keep the per-rank slab modest unless configured
@@ -397,43 +397,49 @@ HcclResult EmuGroup::Post(int rank, const void* args, size_t argBytes, int nBloc
                           cudaStream_t stream)
 {
     std::lock_guard<std::mutex> lk(mu_);
-    if (argBytes > kArgSlotBytes) return HCCL_E_INTERNAL;
-    if (rank < 0 || rank >= nRanks_ || have_[rank]) {
-        HCCL_ERROR("emulated rank %d posted twice before the other ranks posted (call every rank once per operation)", rank);
-        return HCCL_E_PARA;
-    }
-    if (posted_ == 0) {
-        pendingKernel_ = kernel; pendingBlocks_ = nBlocks; pendingThreads_ = threads; pendingArgBytes_ = argBytes;
+    if (argBytes > kArgSlotBytes || rank < 0 || rank >= nRanks_) return HCCL_E_INTERNAL;
+    // One FIFO per rank: a rank may run ahead (an operator that needs several loops posts several launches before
+    // the next rank is called); a launch is issued whenever every rank has an entry at the head of its queue.
+    PendingPost post;
+    post.kernel = kernel; post.nBlocks = nBlocks; post.threads = threads;
+    post.args.assign((const char*)args, (const char*)args + argBytes);
+    queues_[(size_t)rank].push_back(std::move(post));
+    for (;;) {
+        for (int r = 0; r < nRanks_; ++r)
+            if (queues_[(size_t)r].empty()) return HCCL_SUCCESS;
+        const PendingPost& first = queues_[0].front();
+        for (int r = 1; r < nRanks_; ++r) {
+            const PendingPost& o = queues_[(size_t)r].front();
+            if (o.kernel != first.kernel || o.nBlocks != first.nBlocks || o.args.size() != first.args.size()) {
+                HCCL_ERROR("emulated ranks posted different operations (rank %d differs from rank 0)", r);
+                for (auto& q : queues_) q.clear();
+                return HCCL_E_PARA;
+            }
+        }
+        const size_t ab = first.args.size();
+        int nb = first.nBlocks;
+        if (nb > maxBlocksPerRank_) {
+            HCCL_ERROR("emulated launch needs %d blocks per rank, only %d fit one cooperative grid", nb, maxBlocksPerRank_);
+            for (auto& q : queues_) q.clear();
+            return HCCL_E_INTERNAL;
+        }
         // the slot is free once the launch that used it last has consumed its arguments
         if (cudaEventQuery(ringEvents_[ringHead_]) == cudaErrorNotReady) CHK_CUDA(cudaEventSynchronize(ringEvents_[ringHead_]));
-    } else if (kernel != pendingKernel_ || nBlocks != pendingBlocks_ || argBytes != pendingArgBytes_) {
-        HCCL_ERROR("emulated ranks posted different operations (rank %d differs from the first poster)", rank);
-        posted_ = 0; have_.assign((size_t)nRanks_, false);
-        return HCCL_E_PARA;
+        char* slot = hArgs_ + (size_t)ringHead_ * kArgSlotBytes * (size_t)nRanks_;
+        char* dslot = dArgs_ + (size_t)ringHead_ * kArgSlotBytes * (size_t)nRanks_;
+        for (int r = 0; r < nRanks_; ++r) memcpy(slot + (size_t)r * ab, queues_[(size_t)r].front().args.data(), ab);
+        const void* fn = first.kernel;
+        const int th = first.threads;
+        for (auto& q : queues_) q.pop_front();
+        CHK_CUDA(cudaMemcpyAsync(dslot, slot, ab * (size_t)nRanks_, cudaMemcpyHostToDevice, stream));
+        const DevComm* dc = dComms_;
+        const void* da = dslot;
+        void* kargs[3] = {(void*)&dc, (void*)&da, (void*)&nb};
+        cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3((unsigned)(nb * nRanks_)), dim3((unsigned)th), kargs, 0, stream);
+        if (e != cudaSuccess) { HCCL_ERROR("cooperative launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
+        CHK_CUDA(cudaEventRecord(ringEvents_[ringHead_], stream));
+        ringHead_ = (ringHead_ + 1) % kRing;
     }
-    char* slot = hArgs_ + (size_t)ringHead_ * kArgSlotBytes * (size_t)nRanks_;
-    memcpy(slot + (size_t)rank * argBytes, args, argBytes);
-    have_[rank] = true;
-    if (++posted_ < nRanks_) return HCCL_SUCCESS;
-    // last poster launches for everyone, on its stream
-    posted_ = 0;
-    have_.assign((size_t)nRanks_, false);
-    char* dslot = dArgs_ + (size_t)ringHead_ * kArgSlotBytes * (size_t)nRanks_;
-    CHK_CUDA(cudaMemcpyAsync(dslot, slot, argBytes * (size_t)nRanks_, cudaMemcpyHostToDevice, stream));
-    const DevComm* dc = dComms_;
-    const void* da = dslot;
-    int nb = pendingBlocks_;
-    if (nb > maxBlocksPerRank_) {
-        HCCL_ERROR("emulated launch needs %d blocks per rank, only %d fit one cooperative grid", nb, maxBlocksPerRank_);
-        return HCCL_E_INTERNAL;
-    }
-    void* kargs[3] = {(void*)&dc, (void*)&da, (void*)&nb};
-    cudaError_t e = cudaLaunchCooperativeKernel(pendingKernel_, dim3((unsigned)(nb * nRanks_)), dim3((unsigned)pendingThreads_),
-                                                kargs, 0, stream);
-    if (e != cudaSuccess) { HCCL_ERROR("cooperative launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
-    CHK_CUDA(cudaEventRecord(ringEvents_[ringHead_], stream));
-    ringHead_ = (ringHead_ + 1) % kRing;
-    return HCCL_SUCCESS;
 }
 
 HcclResult EmuGroup::MemAlloc(int rank, uint64_t size, SymSegment* seg)

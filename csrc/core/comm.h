@@ -7,6 +7,7 @@
 // Get (op_common.cc:1846-1876) and HcclGetHcclBuffer.  Here it is one C++ class.
 #pragma once
 #include <atomic>
+#include <deque>
 #include <map>
 #include <memory>
 #include <mutex>
@@ -29,6 +30,7 @@ struct TopoInfo;
 class SelectorState;
 class PlanCache;
 class HostRank;
+struct Mc2State;
 
 // Named blobs owned by the communicator (topology cache, cost model, tuner
 // context, fallback records) - the EngineCtx store of the reference.
@@ -98,6 +100,7 @@ public:
     std::unique_ptr<PlanCache> plans;
     std::unique_ptr<TopoInfo> topo;
     bool firstOpChecked[HCCL_CMD_MAX] = {false};
+    std::shared_ptr<Mc2State> mc2;  // resources of the fused matmul kernels, created on first use
     HostRank* hostComm = nullptr;  // non-null: a host-engine communicator (ranks are host threads)
 
 private:
@@ -145,12 +148,9 @@ private:
     char* dArgs_ = nullptr;
     cudaEvent_t ringEvents_[kRing] = {nullptr};
     int ringHead_ = 0;
-    // pending launch being assembled
-    int posted_ = 0;
-    std::vector<bool> have_;
-    const void* pendingKernel_ = nullptr;
-    int pendingBlocks_ = 0, pendingThreads_ = 0;
-    size_t pendingArgBytes_ = 0;
+    // launches posted by individual ranks and not yet issued
+    struct PendingPost { const void* kernel; int nBlocks, threads; std::vector<char> args; };
+    std::vector<std::deque<PendingPost>> queues_;
     std::vector<DevComm> hostComms_;
     // pending group allocation
     std::vector<SymSegment> pendingAlloc_;

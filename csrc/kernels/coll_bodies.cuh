@@ -264,7 +264,7 @@ struct ArLLBody {
         constexpr int EPL = 8 / (int)sizeof(T);  // elements per line
         OpHead(c, b);
         const int p = c.nRanks, me = c.rank;
-        const uint64_t ep = LoadLLEpoch(c, b);
+        const uint64_t ep = LoadLLEpoch(c);
         const uint32_t flag = LLFlag(ep);
         const int parity = (int)(ep & 1u);
         const size_t nLines = (a.bytes + 7) >> 3;
@@ -295,7 +295,7 @@ struct ArLLBody {
             for (int k = 0; k < EPL; ++k) rl[k] = Tr::Store(acc[k]);
             if (ok) StorePayload8(a.out, i << 3, a.bytes, outAl, r[0], r[1]);
         }
-        StoreLLEpoch(c, b, ep + 1);
+        FinishLLEpoch(c, ep, nb);
         OpTail(c, b);
     }
 };
@@ -514,7 +514,7 @@ struct AgLLBody {
     {
         OpHead(c, b);
         const int p = c.nRanks, me = c.rank;
-        const uint64_t ep = LoadLLEpoch(c, b);
+        const uint64_t ep = LoadLLEpoch(c);
         const uint32_t flag = LLFlag(ep);
         const int parity = (int)(ep & 1u);
         const size_t bytes = a.cnt[me];
@@ -542,7 +542,7 @@ struct AgLLBody {
                     StorePayload8(o, i << 3, bytes, oAl, d0, d1);
             }
         }
-        StoreLLEpoch(c, b, ep + 1);
+        FinishLLEpoch(c, ep, nb);
         OpTail(c, b);
     }
 };

@@ -56,7 +56,7 @@ __device__ __forceinline__ uint64_t GlobalTimerNs()
     return t;
 }
 
-__device__ __noinline__ void ReportWaitFailure(const DevComm& c, uint32_t kernelId, int block, int slot, int peer,
+static __device__ __noinline__ void ReportWaitFailure(const DevComm& c, uint32_t kernelId, int block, int slot, int peer,
                                                uint64_t expected, uint64_t seen, uint32_t err)
 {
     if (atomicCAS(c.abortWord, 0u, err) == 0u) {
@@ -111,16 +111,27 @@ __device__ __forceinline__ void StoreEpoch(const DevComm& c, int block, uint64_t
     if (threadIdx.x == 0) *reinterpret_cast<volatile uint64_t*>(c.epochs + block) = next;
 }
 
-// LL (flag-in-data) ops keep their own counter row so that the slot parity
-// alternates op by op whatever other kernels ran in between.
-__device__ __forceinline__ uint64_t LoadLLEpoch(const DevComm& c, int block)
+// LL (flag-in-data) ops share ONE counter per communicator: a line's flag has to be unique per op whichever block
+// wrote the line last (block rows cover different line ranges from op to op).  Every block reads the counter at
+// entry; the last block to finish advances it, which is after all blocks have read it.  Being device-resident it
+// survives CUDA-graph replay.
+__device__ __forceinline__ uint64_t LoadLLEpoch(const DevComm& c)
 {
-    return *reinterpret_cast<volatile uint64_t*>(c.epochs + kMaxBlocks + block);
+    return *reinterpret_cast<volatile uint64_t*>(c.epochs + kMaxBlocks);
 }
-__device__ __forceinline__ void StoreLLEpoch(const DevComm& c, int block, uint64_t next)
+__device__ __forceinline__ void FinishLLEpoch(const DevComm& c, uint64_t epoch, int nBlocks)
 {
     __syncthreads();
-    if (threadIdx.x == 0) *reinterpret_cast<volatile uint64_t*>(c.epochs + kMaxBlocks + block) = next;
+    if (threadIdx.x == 0) {
+        __threadfence();
+        unsigned long long* ticket = reinterpret_cast<unsigned long long*>(c.epochs + kMaxBlocks + 1);
+        const unsigned long long t = atomicAdd(ticket, 1ull);
+        if (t == (unsigned long long)(nBlocks - 1)) {
+            *reinterpret_cast<volatile uint64_t*>(ticket) = 0;
+            *reinterpret_cast<volatile uint64_t*>(c.epochs + kMaxBlocks) = epoch + 1;
+            __threadfence();
+        }
+    }
 }
 
 // Barrier among the blocks with index `block` of all ranks, on flag slot `slot`.

@@ -1,0 +1,541 @@
+// tcgen05 / TMEM GEMM pipeline shared by the MC2 (matmul + collective) kernels.
+//
+// HCCL ships only the resource half of MC2 (hccl_mc2.h; the isMc2 hooks in
+// alg_param.h:784); the fused AllGather->Matmul, Matmul->ReduceScatter and
+// Matmul->AllReduce kernels it serves live in another package.  This file is
+// the Blackwell-native kernel family for them.
+//
+// One persistent CTA per SM, 192 threads:
+//   warp 0     TMA producer: cp.async.bulk.tensor loads of A and B tiles into a
+//              4-stage shared-memory ring (128-byte swizzle), completion on
+//              "full" mbarriers
+//   warp 1     MMA issuer: one elected thread issues tcgen05.mma
+//              (cta_group::1, kind::f16, M=128, N=BN, K=16) from shared-memory
+//              descriptors into one of two TMEM accumulators;
+//              tcgen05.commit frees the stage ("empty") and publishes the tile
+//              ("tmem full")
+//   warps 2-5  epilogue: tcgen05.ld (32 lanes x 32 columns) -> registers ->
+//              bf16 -> global / peer memory, overlapped with the next tile's
+//              main loop through the second accumulator
+// Extra CTAs beyond the GEMM CTAs act as communication workers (AllGather pull,
+// ReduceScatter reduction) so that NVLink traffic overlaps the math tile by
+// tile.  Remote data is never fetched by TMA with cluster multicast: peers'
+// tiles are copied into this GPU's memory once (plain loads) and read from
+// there by TMA, or written by plain stores.
+//
+// Every wait (mbarrier, local flag, peer flag) is bounded; on expiry the CTA
+// raises the communicator's abort word, lets in-flight copies land, frees its
+// TMEM and returns.
+#pragma once
+#include <cuda_bf16.h>
+#include "dev_comm.cuh"
+#include "reduce_ops.cuh"
+#include "sm100_ptx.cuh"
+
+namespace hccl {
+namespace mc2 {
+
+using namespace sm100;
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;            // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr int kEpilogueThreads = 128;
+constexpr uint64_t kWaitLimitNs = 5ull * 1000 * 1000 * 1000;
+
+enum Mode : int { MODE_PLAIN = 0, MODE_AG = 1, MODE_RS = 2, MODE_AR = 3 };
+
+struct GemmArgs {
+    // problem: C[M, N] = A[M, K] x B[K, N]   (operand storage is described by the tensor maps)
+    int M, N, K;
+    __nv_bfloat16* out;        // PLAIN / AG: [M, ldc]; RS: [M / P, ldc] (local reduced block); AR: [M, ldc]
+    int ldc;
+    int nGemmCtas;             // CTAs [0, nGemmCtas) run the GEMM; the rest are communication workers
+    int tilesM, tilesN;
+    // ---- fused modes
+    int rank, nRanks;
+    int mPerRank;              // AG: rows per rank of the gathered A; RS: rows per rank of the output
+    // AG: peers' A shards (peer-mapped symmetric memory) and the local gathered buffer [P * mPerRank, K]
+    const __nv_bfloat16* aPeer[kMaxDevRanks];
+    __nv_bfloat16* gathered;
+    // RS / AR: exchange slots.  xchg[q] = rank q's exchange buffer mapped here; layout [srcRank][rows][N] bf16
+    __nv_bfloat16* xchg[kMaxDevRanks];
+    // device-resident control block of the communicator's MC2 state (local memory):
+    //   [0] launch epoch, [1] exit ticket, [2] abort, [16 ..) per-row-block ready counters (AG)
+    uint32_t* ctl;
+    // tile-ready flags for RS / AR: tileFlag[q] = rank q's flag array mapped here, index [srcRank][tile]
+    uint64_t* tileFlag[kMaxDevRanks];
+    int maxTiles;
+    // The exchange buffer holds two copies of the slot array; launch L uses copy (L & 1).  A rank can only reach
+    // launch L + 2 after every peer has delivered (hence started) launch L + 1, i.e. finished reading launch L, so
+    // no barrier is needed before a slot is overwritten.
+    size_t xchgParityElems;
+};
+constexpr int kCtlEpoch = 0, kCtlTicket = 1, kCtlAbort = 2, kCtlReady = 16;
+
+template <int BN>
+struct SmemLayout {
+    static constexpr int kABytes = kBM * kBK * 2;          // 16 KiB
+    static constexpr int kBBytes = BN * kBK * 2;           // 32 KiB for BN = 256
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kTileBytes = kStages * kStageBytes;
+    static constexpr int kBarrierBytes = 256;
+    static constexpr int kTotal = kTileBytes + kBarrierBytes + 1024;   // + slack for the 1024-byte alignment
+};
+
+// Flat tile index -> (m tile, n tile) in the order that suits the mode.
+template <int MODE>
+__device__ __forceinline__ void TileCoord(const GemmArgs& g, int t, int* mt, int* nt)
+{
+    if (MODE == MODE_AG) {
+        // rows grouped by source rank, own rank first, then rank+1, ... : the own shard needs no transfer and the
+        // gather workers fetch the others in exactly this order
+        const int tilesPerRank = (g.mPerRank / kBM) * g.tilesN;
+        const int step = t / tilesPerRank, rem = t % tilesPerRank;
+        const int src = (g.rank + step) % g.nRanks;
+        *mt = src * (g.mPerRank / kBM) + rem / g.tilesN;
+        *nt = rem % g.tilesN;
+    } else if (MODE == MODE_RS) {
+        // column tile major: after column tile n every rank has produced its partial of (every row block, n), so the
+        // owner can reduce column tile n while the GEMM works on n + 1.  Inside a column tile the row blocks start at
+        // rank + 1 so that at any time the ranks send to different owners.
+        const int perCol = g.tilesM;
+        const int n = t / perCol, rem = t % perCol;
+        const int rowsTiles = g.mPerRank / kBM;
+        const int step = rem / rowsTiles;
+        const int dstRank = (g.rank + 1 + step) % g.nRanks;
+        *mt = dstRank * rowsTiles + rem % rowsTiles;
+        *nt = n;
+    } else {
+        *mt = t / g.tilesN;
+        *nt = t % g.tilesN;
+    }
+}
+
+__device__ __forceinline__ bool SpinUntilGE(const volatile uint32_t* p, uint32_t want, volatile uint32_t* abortWord)
+{
+    if (*p >= want) return true;
+    const uint64_t t0 = TimerNs();
+    uint32_t spins = 0;
+    for (;;) {
+        uint32_t v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+        if (v >= want) return true;
+        if ((++spins & 0xFFu) == 0u) {
+            if (*abortWord != 0u) return false;
+            if (TimerNs() - t0 > kWaitLimitNs) { *abortWord = 1u; return false; }
+        }
+    }
+}
+
+__device__ __forceinline__ void Store32Cols(__nv_bfloat16* dst, const uint32_t (&acc)[32], int validCols)
+{
+    // 32 fp32 accumulators -> 32 bf16 = 64 bytes = 4 x 16-byte stores
+    uint32_t packed[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1]));
+        packed[i] = *reinterpret_cast<uint32_t*>(&v);
+    }
+    if (validCols >= 32) {
+        uint4* d = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) d[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+    } else {
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(packed);
+        for (int i = 0; i < validCols; ++i) dst[i] = e[i];
+    }
+}
+
+// -----------------------------------------------------------------------------
+// Communication workers.
+
+// AllGather pull: copies the peers' A shards into `gathered` row block by row block (kBM rows each), in the order
+// rank, rank+1, rank+2, ...  One thread per worker CTA drives a ring of bulk copies (peer memory -> shared memory
+// -> local memory, no multicast), kGatherStages chunks deep, so that enough bytes are in flight to cover the
+// NVLink round trip; after a row block every worker adds 1 to ready[rowBlock] and a GEMM producer waits for
+// ready[rowBlock] == nWorkers.  The own shard is copied the same way (the GEMM reads everything from `gathered`).
+constexpr int kGatherStages = 6;
+constexpr uint32_t kGatherChunk = 32 * 1024;
+__device__ __forceinline__ void GatherWorker(const DevComm& c, const GemmArgs& g, int worker, int nWorkers, uint8_t* smem, uint64_t* bars)
+{
+    volatile uint32_t* abortWord = g.ctl + kCtlAbort;
+    const uint64_t e = LoadEpoch(c, worker);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kGatherStages; ++s) MbarInit(&bars[s], 1);
+        MbarInitFence();
+    }
+    // peers have entered the kernel: their shards are final
+    const bool ok = RankBarrier(c, worker, 0, e + 1, K_MC2_AG_GEMM);
+    if (!ok && threadIdx.x == 0) *abortWord = 1u;   // the GEMM CTAs must not wait for rows that will never arrive
+    if (ok && threadIdx.x == 0) {
+        const size_t blockBytes = (size_t)g.K * 2 * kBM;
+        const int blocksPerRank = g.mPerRank / kBM;
+        const int nBlocks = g.nRanks * blocksPerRank;
+        size_t b0, b1;
+        Share(blockBytes, nWorkers, worker, 16, &b0, &b1);
+        const size_t share = b1 - b0;
+        const int chunksPerBlock = (int)((share + kGatherChunk - 1) / kGatherChunk);
+        const long total = (long)chunksPerBlock * nBlocks;
+        long issued = 0, stored = 0;
+        bool alive = true;
+        auto chunkInfo = [&](long n, const char** src, char** dst, uint32_t* bytes, int* flagIdx, bool* last) {
+            const int blk = (int)(n / chunksPerBlock), ch = (int)(n % chunksPerBlock);
+            const int step = blk / blocksPerRank, rb = blk % blocksPerRank;
+            const int srcRank = (g.rank + step) % g.nRanks;
+            const size_t off = b0 + (size_t)ch * kGatherChunk;
+            *bytes = (uint32_t)((share - (size_t)ch * kGatherChunk) < kGatherChunk ? (share - (size_t)ch * kGatherChunk) : kGatherChunk);
+            *src = reinterpret_cast<const char*>(g.aPeer[srcRank]) + (size_t)rb * blockBytes + off;
+            *dst = reinterpret_cast<char*>(g.gathered) + ((size_t)srcRank * blocksPerRank + rb) * blockBytes + off;
+            *flagIdx = srcRank * blocksPerRank + rb;
+            *last = ch == chunksPerBlock - 1;
+        };
+        while (stored < total && alive) {
+            while (issued < total && issued - stored < kGatherStages) {
+                const int slot = (int)(issued % kGatherStages);
+                // the store that used this slot last (chunk issued - stages) must have read it out
+                if (issued >= kGatherStages) BulkWaitRead((int)(stored - (issued - kGatherStages) - 1));
+                const char* src; char* dst; uint32_t bytes; int fi; bool last;
+                chunkInfo(issued, &src, &dst, &bytes, &fi, &last);
+                MbarExpectTx(&bars[slot], bytes);
+                BulkLoadG2S(smem + (size_t)slot * kGatherChunk, src, bytes, &bars[slot]);
+                ++issued;
+            }
+            const int slot = (int)(stored % kGatherStages);
+            alive = MbarWait(&bars[slot], (uint32_t)((stored / kGatherStages) & 1), abortWord, kWaitLimitNs);
+            if (!alive) break;
+            const char* src; char* dst; uint32_t bytes; int fi; bool last;
+            chunkInfo(stored, &src, &dst, &bytes, &fi, &last);
+            BulkStoreS2G(dst, smem + (size_t)slot * kGatherChunk, bytes);
+            BulkCommit();
+            ++stored;
+            if (last) {
+                BulkWaitAll();          // this worker's part of the row block is in local memory
+                __threadfence();
+                atomicAdd(g.ctl + kCtlReady + fi, 1u);
+            }
+        }
+        BulkWaitAll();
+        if (!alive) {
+            const uint64_t t0 = TimerNs();   // loads already issued still target this CTA's shared memory
+            while (TimerNs() - t0 < 200000) {}
+        }
+    }
+    // nobody may change its shard while a peer still reads it
+    RankBarrier(c, worker, 0, e + 2, K_MC2_AG_GEMM);
+    StoreEpoch(c, worker, e + 2);
+}
+
+// ReduceScatter reduction: for every tile of the local row block, waits until all ranks have delivered their
+// partial (flag value == launch epoch), sums the P partials in rank order in fp32 and writes bf16 to `out`.
+// Tiles are visited in the order they complete (column tile major).
+template <int BN>
+__device__ __forceinline__ void ReduceWorker(const DevComm& c, const GemmArgs& g, int worker, int nWorkers, uint64_t epoch)
+{
+    volatile uint32_t* abortWord = g.ctl + kCtlAbort;
+    const int rowsTiles = g.mPerRank / kBM;
+    const int nLocalTiles = rowsTiles * g.tilesN;
+    const size_t slotElems = (size_t)g.mPerRank * g.N;
+    const __nv_bfloat16* xbase = g.xchg[g.rank] + (epoch & 1u) * g.xchgParityElems;
+    for (int lt = worker; lt < nLocalTiles; lt += nWorkers) {
+        const int nt = lt / rowsTiles, mtLocal = lt % rowsTiles;
+        __shared__ int s_ok;
+        if (threadIdx.x == 0) s_ok = 1;
+        __syncthreads();
+        if (threadIdx.x < g.nRanks) {
+            const uint64_t* f = g.tileFlag[g.rank] + (size_t)threadIdx.x * g.maxTiles + (mtLocal * g.tilesN + nt);
+            if (!WaitFlagGE(c, f, epoch, K_MC2_GEMM_RS, worker, 0, threadIdx.x)) s_ok = 0;
+        }
+        __syncthreads();
+        if (!s_ok) break;
+        // tile rows [mtLocal*128, +128) x cols [nt*BN, +BN): 16-byte vectors of 8 bf16
+        const int vecPerRow = BN / 8;
+        for (int v = threadIdx.x; v < kBM * vecPerRow; v += blockDim.x) {
+            const int r = mtLocal * kBM + v / vecPerRow;
+            const int col = nt * BN + (v % vecPerRow) * 8;
+            if (r >= g.mPerRank || col >= g.N) continue;
+            float acc[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+            for (int q = 0; q < g.nRanks; ++q) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(xbase + (size_t)q * slotElems + (size_t)r * g.N + col);
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 f = __bfloat1622float2(h[k]);
+                    acc[2 * k] += f.x;
+                    acc[2 * k + 1] += f.y;
+                }
+            }
+            uint4 o;
+            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+            *reinterpret_cast<uint4*>(g.out + (size_t)r * g.ldc + col) = o;
+        }
+    }
+    (void)abortWord;
+}
+
+// -----------------------------------------------------------------------------
+template <int BN, bool A_MN, bool B_MN, int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+    GemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs g, const DevComm c)
+{
+    using L = SmemLayout<BN>;
+    extern __shared__ uint8_t smemRaw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kTileBytes);
+    uint64_t* fullBar = bars;                 // [kStages]
+    uint64_t* emptyBar = bars + kStages;      // [kStages]
+    uint64_t* tmemFull = bars + 2 * kStages;  // [2]
+    uint64_t* tmemEmpty = bars + 2 * kStages + 2;  // [2]
+    uint32_t* tmemBaseSlot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+    volatile uint32_t* abortWord = g.ctl + kCtlAbort;
+
+    const int warp = threadIdx.x / 32;
+    const int cta = (int)blockIdx.x;
+    const uint32_t launchEpoch = *reinterpret_cast<volatile uint32_t*>(g.ctl + kCtlEpoch) + 1;   // 1, 2, 3, ...
+
+    if (cta >= g.nGemmCtas) {
+        // ---- communication worker CTA
+        const int worker = cta - g.nGemmCtas, nWorkers = (int)gridDim.x - g.nGemmCtas;
+        if (MODE == MODE_AG) GatherWorker(c, g, worker, nWorkers, smem, bars);
+        if (MODE == MODE_RS) ReduceWorker<BN>(c, g, worker, nWorkers, (uint64_t)launchEpoch);
+    } else {
+        // ---- GEMM CTA
+        constexpr uint32_t kTmemCols = 2 * BN;       // two accumulators of BN fp32 columns
+        if (threadIdx.x == 0) {
+            for (int s = 0; s < kStages; ++s) { MbarInit(&fullBar[s], 1); MbarInit(&emptyBar[s], 1); }
+            for (int a = 0; a < 2; ++a) { MbarInit(&tmemFull[a], 1); MbarInit(&tmemEmpty[a], kEpilogueThreads / 32); }
+            MbarInitFence();
+            PrefetchTensorMap(&tmA);
+            PrefetchTensorMap(&tmB);
+        }
+        if (warp == 1) {
+            TmemAlloc(tmemBaseSlot, kTmemCols);
+            TmemRelinquish();
+        }
+        TcFenceBefore();
+        __syncthreads();
+        TcFenceAfter();
+        const uint32_t tmemBase = *tmemBaseSlot;
+        const int nTiles = g.tilesM * g.tilesN;
+        const int kBlocks = (g.K + kBK - 1) / kBK;
+
+        if (warp == 0) {
+            // ===== TMA producer
+            if (ElectOne()) {
+                int stage = 0;
+                uint32_t phase = 0;
+                bool ok = true;
+                for (int t = cta; t < nTiles && ok; t += g.nGemmCtas) {
+                    int mt, nt;
+                    TileCoord<MODE>(g, t, &mt, &nt);
+                    if (MODE == MODE_AG) {
+                        const int nWorkers = (int)gridDim.x - g.nGemmCtas;
+                        ok = SpinUntilGE(g.ctl + kCtlReady + mt, (uint32_t)nWorkers, abortWord);
+                        FenceProxyAsync();   // reader side of the generic -> async proxy hand-over
+                        if (!ok) break;
+                    }
+                    for (int kb = 0; kb < kBlocks; ++kb) {
+                        ok = MbarWait(&emptyBar[stage], phase ^ 1u, abortWord, kWaitLimitNs);
+                        if (!ok) break;
+                        uint8_t* sa = smem + stage * L::kStageBytes;
+                        uint8_t* sb = sa + L::kABytes;
+                        MbarExpectTx(&fullBar[stage], L::kStageBytes);
+                        if (!A_MN) {
+                            TmaLoad2D(sa, &tmA, &fullBar[stage], kb * kBK, mt * kBM);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < kBM / 64; ++j) TmaLoad2D(sa + j * (64 * kBK * 2), &tmA, &fullBar[stage], mt * kBM + j * 64, kb * kBK);
+                        }
+                        if (!B_MN) {
+                            TmaLoad2D(sb, &tmB, &fullBar[stage], kb * kBK, nt * BN);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < BN / 64; ++j) TmaLoad2D(sb + j * (64 * kBK * 2), &tmB, &fullBar[stage], nt * BN + j * 64, kb * kBK);
+                        }
+                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    }
+                }
+                if (!ok) {
+                    // let copies that were already issued land before the CTA's shared memory goes away
+                    const uint64_t t0 = TimerNs();
+                    while (TimerNs() - t0 < 200000) {}
+                }
+            }
+        } else if (warp == 1) {
+            // ===== MMA issuer
+            if (ElectOne()) {
+                constexpr uint32_t idesc = InstrDescF16(kBM, BN, true, A_MN, B_MN);
+                int stage = 0;
+                uint32_t phase = 0;
+                int acc = 0;
+                uint32_t accPhase = 0;
+                bool ok = true;
+                for (int t = cta; t < nTiles && ok; t += g.nGemmCtas) {
+                    ok = MbarWait(&tmemEmpty[acc], accPhase ^ 1u, abortWord, kWaitLimitNs);
+                    if (!ok) break;
+                    TcFenceAfter();
+                    const uint32_t tmemD = tmemBase + (uint32_t)(acc * BN);
+                    for (int kb = 0; kb < kBlocks; ++kb) {
+                        ok = MbarWait(&fullBar[stage], phase, abortWord, kWaitLimitNs);
+                        if (!ok) break;
+                        TcFenceAfter();
+                        const uint32_t sa = SmemAddr(smem + stage * L::kStageBytes);
+                        const uint32_t sb = sa + L::kABytes;
+                        const uint64_t da = A_MN ? SmemDescMnMajor(sa, 64 * kBK * 2) : SmemDescKMajor(sa);
+                        const uint64_t db = B_MN ? SmemDescMnMajor(sb, 64 * kBK * 2) : SmemDescKMajor(sb);
+#pragma unroll
+                        for (int k = 0; k < kBK / kUmmaK; ++k) {
+                            // K-major: 16 elements = 32 bytes along the row; MN-major: 16 K-rows of 128 bytes
+                            const uint64_t aStep = (uint64_t)((A_MN ? kUmmaK * 128 : kUmmaK * 2) >> 4) * k;
+                            const uint64_t bStep = (uint64_t)((B_MN ? kUmmaK * 128 : kUmmaK * 2) >> 4) * k;
+                            UmmaF16(tmemD, da + aStep, db + bStep, idesc, (kb | k) != 0 ? 1u : 0u);
+                        }
+                        UmmaCommit(&emptyBar[stage]);   // the stage is free once these MMAs have read it
+                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    }
+                    if (!ok) break;
+                    UmmaCommit(&tmemFull[acc]);
+                    if (++acc == 2) { acc = 0; accPhase ^= 1u; }
+                }
+            }
+        } else {
+            // ===== epilogue warps 2..5; a warp may only touch TMEM lanes [32 * (warp % 4), +32)
+            const int quarter = warp & 3;
+            const int lane = threadIdx.x & 31;
+            int acc = 0;
+            uint32_t accPhase = 0;
+            bool ok = true;
+            const size_t parityOff = (launchEpoch & 1u) * g.xchgParityElems;
+            for (int t = cta; t < nTiles && ok; t += g.nGemmCtas) {
+                int mt, nt;
+                TileCoord<MODE>(g, t, &mt, &nt);
+                ok = MbarWait(&tmemFull[acc], accPhase, abortWord, kWaitLimitNs);
+                if (!ok) break;
+                TcFenceAfter();
+                const int row = mt * kBM + quarter * 32 + lane;
+                const uint32_t taddr = tmemBase + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
+                __nv_bfloat16* rowPtr = nullptr;
+                bool rowValid = row < g.M;
+                if (MODE == MODE_PLAIN || MODE == MODE_AG) {
+                    rowPtr = g.out + (size_t)row * g.ldc;
+                } else if (MODE == MODE_RS) {
+                    // partial of row block `dst` goes into the owner's slot [me]
+                    const int dst = row / g.mPerRank;
+                    rowValid = rowValid && dst < g.nRanks;
+                    if (rowValid) rowPtr = g.xchg[dst] + parityOff + (size_t)g.rank * g.mPerRank * g.N + (size_t)(row - dst * g.mPerRank) * g.N;
+                } else {  // MODE_AR: own slot on every rank, written below per destination
+                    rowPtr = nullptr;
+                }
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t v[32];
+                    TmemLd32x32(taddr + (uint32_t)c0, v);
+                    TmemLdWait();
+                    const int col = nt * BN + c0;
+                    const int valid = g.N - col;
+                    if (!rowValid || valid <= 0) continue;
+                    if (MODE != MODE_AR) {
+                        Store32Cols(rowPtr + col, v, valid);
+                    } else {
+                        for (int q = 0; q < g.nRanks; ++q) {
+                            const int dst = (g.rank + q) % g.nRanks;
+                            Store32Cols(g.xchg[dst] + parityOff + (size_t)g.rank * g.M * g.N + (size_t)row * g.N + col, v, valid);
+                        }
+                    }
+                }
+                // release the accumulator to the MMA warp
+                TcFenceBefore();
+                __syncwarp();
+                if (lane == 0) MbarArrive(&tmemEmpty[acc]);
+                if (++acc == 2) { acc = 0; accPhase ^= 1u; }
+
+                if (MODE == MODE_RS || MODE == MODE_AR) {
+                    // publish the tile: all 128 epilogue threads have stored, then one thread raises the flag(s)
+                    __threadfence_system();
+                    NamedBarSync(1, kEpilogueThreads);
+                    const int tileId = MODE == MODE_RS ? ((mt % (g.mPerRank / kBM)) * g.tilesN + nt) : (mt * g.tilesN + nt);
+                    if (MODE == MODE_RS) {
+                        if (threadIdx.x == 64) {
+                            const int dst = (mt * kBM) / g.mPerRank;
+                            __threadfence_system();
+                            StReleaseSys(g.tileFlag[dst] + (size_t)g.rank * g.maxTiles + tileId, (uint64_t)launchEpoch);
+                        }
+                    } else {
+                        const int e = threadIdx.x - 64;
+                        if (e < g.nRanks) {
+                            __threadfence_system();
+                            StReleaseSys(g.tileFlag[e] + (size_t)g.rank * g.maxTiles + tileId, (uint64_t)launchEpoch);
+                        }
+                        // AllReduce: the same CTA reduces the tile once every rank's partial is here
+                        __shared__ int s_arOk;
+                        if (threadIdx.x == 64) s_arOk = 1;
+                        NamedBarSync(1, kEpilogueThreads);
+                        if (e >= 0 && e < g.nRanks) {
+                            if (!WaitFlagGE(c, g.tileFlag[g.rank] + (size_t)e * g.maxTiles + tileId, (uint64_t)launchEpoch, K_MC2_GEMM_AR, cta, 0, e))
+                                s_arOk = 0;
+                        }
+                        NamedBarSync(1, kEpilogueThreads);
+                        if (!s_arOk) { ok = false; break; }
+                        const int vecPerRow = BN / 8;
+                        const int rowsHere = min(kBM, g.M - mt * kBM);
+                        for (int v = threadIdx.x - 64; v < rowsHere * vecPerRow; v += kEpilogueThreads) {
+                            const int r = mt * kBM + v / vecPerRow;
+                            const int col = nt * BN + (v % vecPerRow) * 8;
+                            if (col >= g.N) continue;
+                            float accf[8];
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) accf[k] = 0.f;
+                            for (int q = 0; q < g.nRanks; ++q) {
+                                const uint4 raw = *reinterpret_cast<const uint4*>(g.xchg[g.rank] + parityOff + (size_t)q * g.M * g.N + (size_t)r * g.N + col);
+                                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) {
+                                    const float2 f = __bfloat1622float2(h[k]);
+                                    accf[2 * k] += f.x;
+                                    accf[2 * k + 1] += f.y;
+                                }
+                            }
+                            uint4 o;
+                            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(accf[2 * k], accf[2 * k + 1]);
+                            *reinterpret_cast<uint4*>(g.out + (size_t)r * g.ldc + col) = o;
+                        }
+                    }
+                }
+            }
+        }
+        // teardown: every role has left its loop (normally or by a bounded wait that ran out)
+        TcFenceBefore();
+        __syncthreads();
+        if (warp == 1) {
+            TcFenceAfter();
+            TmemDealloc(tmemBase, kTmemCols);
+        }
+    }
+
+    // exit ticket: the last CTA to leave advances the launch epoch and clears the AG ready counters
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const uint32_t ticket = atomicAdd(g.ctl + kCtlTicket, 1u);
+        if (ticket == gridDim.x - 1) {
+            if (MODE == MODE_AG) {
+                const int n = g.nRanks * (g.mPerRank / kBM);
+                for (int i = 0; i < n; ++i) g.ctl[kCtlReady + i] = 0;
+            }
+            g.ctl[kCtlTicket] = 0;
+            *reinterpret_cast<volatile uint32_t*>(g.ctl + kCtlEpoch) = launchEpoch;
+            __threadfence();
+        }
+    }
+}
+
+}  // namespace mc2
+}  // namespace hccl

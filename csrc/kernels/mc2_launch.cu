@@ -1,0 +1,289 @@
+// Instantiation, tensor-map encoding and launch of the MC2 kernels (sm_100a).
+#include "mc2_launch.h"
+#include <map>
+#include <mutex>
+#include "../core/comm.h"
+#include "../core/cuda_driver.h"
+#include "../core/log.h"
+#include "mc2_gemm.cuh"
+
+namespace hccl {
+
+using namespace mc2;
+
+Mc2State::~Mc2State()
+{
+    if (ctl) cudaFree(ctl);
+    if (resCtxDev) cudaFree(resCtxDev);
+    SymFree(&flags);
+    SymFree(&xchg);
+}
+
+namespace {
+
+static_assert(kGatherStages * (int)kGatherChunk <= SmemLayout<256>::kTileBytes, "gather ring must fit the GEMM tile ring");
+
+// Tensor map of a row-major bf16 matrix [rows, cols] (cols contiguous) with a box of boxCols x boxRows and the
+// 128-byte swizzle the UMMA descriptors assume.
+HcclResult MakeMap(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint32_t boxRows, uint32_t boxCols)
+{
+    const DriverApi* d = GetDriverApi();
+    if (!d) return HCCL_E_DRV;
+    if ((((uintptr_t)ptr) & 15u) != 0 || (cols * 2) % 16 != 0) {
+        HCCL_ERROR("matmul operand %p [%llu x %llu] must be 16-byte aligned with a row pitch that is a multiple of 16 bytes", ptr,
+                   (unsigned long long)rows, (unsigned long long)cols);
+        return HCCL_E_PARA;
+    }
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {boxCols, boxRows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = d->cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { HCCL_ERROR("cuTensorMapEncodeTiled failed: %s", DriverErrorString(r)); return HCCL_E_DRV; }
+    return HCCL_SUCCESS;
+}
+
+// A: logical [M, K].  transA == 0: stored [M, K] (K-major).  transA == 1: stored [K, M] (MN-major).
+HcclResult MapA(CUtensorMap* map, const void* a, uint64_t m, uint64_t k, bool mnMajor)
+{
+    return mnMajor ? MakeMap(map, a, k, m, kBK, 64) : MakeMap(map, a, m, k, kBM, kBK);
+}
+// B: logical [K, N].  transB == 1: stored [N, K] (K-major).  transB == 0: stored [K, N] (MN-major).
+HcclResult MapB(CUtensorMap* map, const void* b, uint64_t n, uint64_t k, bool mnMajor, int bn)
+{
+    return mnMajor ? MakeMap(map, b, k, n, kBK, 64) : MakeMap(map, b, n, k, (uint32_t)bn, kBK);
+}
+
+int SmCount()
+{
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    }
+    return n;
+}
+
+template <int BN, bool A_MN, bool B_MN, int MODE>
+HcclResult LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const DevComm& c, int grid, bool cooperative,
+                      cudaStream_t stream)
+{
+    auto kernel = GemmKernel<BN, A_MN, B_MN, MODE>;
+    static bool attrSet = false;
+    if (!attrSet) {
+        CHK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BN>::kTotal));
+        attrSet = true;
+    }
+    if (cooperative) {
+        void* args[4] = {(void*)&ta, (void*)&tb, (void*)&g, (void*)&c};
+        cudaError_t e = cudaLaunchCooperativeKernel((const void*)kernel, dim3((unsigned)grid), dim3(kThreads), args, SmemLayout<BN>::kTotal, stream);
+        if (e != cudaSuccess) { HCCL_ERROR("fused matmul launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
+        return HCCL_SUCCESS;
+    }
+    kernel<<<grid, kThreads, SmemLayout<BN>::kTotal, stream>>>(ta, tb, g, c);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { HCCL_ERROR("matmul launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
+    return HCCL_SUCCESS;
+}
+
+template <int BN, int MODE>
+HcclResult DispatchLayout(bool aMn, bool bMn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const DevComm& c, int grid,
+                          bool coop, cudaStream_t s)
+{
+    if (!aMn && !bMn) return LaunchGemm<BN, false, false, MODE>(ta, tb, g, c, grid, coop, s);
+    if (!aMn && bMn) return LaunchGemm<BN, false, true, MODE>(ta, tb, g, c, grid, coop, s);
+    if (MODE == MODE_PLAIN) {
+        if (aMn && !bMn) return LaunchGemm<BN, true, false, MODE_PLAIN>(ta, tb, g, c, grid, coop, s);
+        return LaunchGemm<BN, true, true, MODE_PLAIN>(ta, tb, g, c, grid, coop, s);
+    }
+    HCCL_ERROR("fused matmul kernels take A in row-major [M, K] form only");
+    return HCCL_E_NOT_SUPPORT;
+}
+
+// Control block for plain matmuls (no communicator): one per device, zeroed once.
+uint32_t* PlainCtl()
+{
+    static std::mutex mu;
+    static std::map<int, uint32_t*> perDev;
+    std::lock_guard<std::mutex> lk(mu);
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto it = perDev.find(dev);
+    if (it != perDev.end()) return it->second;
+    uint32_t* p = nullptr;
+    if (cudaMalloc(&p, kMc2CtlWords * sizeof(uint32_t)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, kMc2CtlWords * sizeof(uint32_t));
+    perDev[dev] = p;
+    return p;
+}
+
+HcclResult CheckShapes(uint64_t m, uint64_t n, uint64_t k)
+{
+    if (m == 0 || n == 0 || k == 0 || m > (1u << 30) || n > (1u << 30) || k > (1u << 30)) return HCCL_E_PARA;
+    if (n % 8 != 0 || k % 8 != 0) { HCCL_ERROR("matmul needs N and K to be multiples of 8 (got N=%llu K=%llu)", (unsigned long long)n, (unsigned long long)k); return HCCL_E_PARA; }
+    return HCCL_SUCCESS;
+}
+
+void FillPeers(CommImpl* comm, GemmArgs* g)
+{
+    Mc2State* st = comm->mc2.get();
+    for (int q = 0; q < comm->nRanks; ++q) {
+        g->xchg[q] = (__nv_bfloat16*)st->xchg.peer[q];
+        g->tileFlag[q] = (uint64_t*)st->flags.peer[q];
+    }
+    g->ctl = st->ctl;
+    g->maxTiles = kMc2MaxTiles;
+    g->xchgParityElems = st->xchgParityBytes / 2;
+    g->rank = comm->rank;
+    g->nRanks = comm->nRanks;
+}
+
+}  // namespace
+
+HcclResult Mc2EnsureState(CommImpl* comm, uint64_t parityBytes)
+{
+    if (comm->emulated() || comm->hostComm) return HCCL_E_NOT_SUPPORT;
+    if (!comm->mc2) {
+        std::shared_ptr<Mc2State> st(new Mc2State());
+        CHK_CUDA(cudaMalloc(&st->ctl, kMc2CtlWords * sizeof(uint32_t)));
+        CHK_CUDA(cudaMemset(st->ctl, 0, kMc2CtlWords * sizeof(uint32_t)));
+        CHK_RET(SymAlloc(*comm->bs, comm->device, (size_t)comm->nRanks * kMc2MaxTiles * sizeof(uint64_t), false, GetEnvConfig().forceIpc, &st->flags));
+        comm->mc2 = std::move(st);
+    }
+    Mc2State* st = comm->mc2.get();
+    if (parityBytes > st->xchgParityBytes) {
+        // all ranks call with the same shapes, so they all grow together
+        CHK_CUDA(cudaDeviceSynchronize());
+        SymFree(&st->xchg);
+        const uint64_t rounded = (parityBytes + (2u << 20) - 1) / (2u << 20) * (2u << 20);
+        CHK_RET(SymAlloc(*comm->bs, comm->device, (size_t)rounded * 2, false, GetEnvConfig().forceIpc, &st->xchg));
+        st->xchgParityBytes = rounded;
+    }
+    return HCCL_SUCCESS;
+}
+
+HcclResult Mc2Matmul(const void* a, const void* b, void* out, uint64_t m, uint64_t n, uint64_t k, int transA, int transB, cudaStream_t stream)
+{
+    CHK_PTR_NULL(a); CHK_PTR_NULL(b); CHK_PTR_NULL(out);
+    CHK_RET(CheckShapes(m, n, k));
+    const bool aMn = transA != 0, bMn = transB == 0;
+    if (aMn && m % 8 != 0) return HCCL_E_PARA;
+    const int tilesM = (int)((m + kBM - 1) / kBM);
+    // narrow column tiles when the wide ones would leave most SMs idle
+    const bool narrow = (uint64_t)tilesM * ((n + 255) / 256) < (uint64_t)SmCount() * 3 / 4;
+    const int bn = narrow ? 128 : 256;
+    CUtensorMap ta, tb;
+    CHK_RET(MapA(&ta, a, m, k, aMn));
+    CHK_RET(MapB(&tb, b, n, k, bMn, bn));
+    GemmArgs g;
+    memset(&g, 0, sizeof(g));
+    g.M = (int)m; g.N = (int)n; g.K = (int)k;
+    g.out = (__nv_bfloat16*)out;
+    g.ldc = (int)n;
+    g.tilesM = tilesM;
+    g.tilesN = (int)((n + bn - 1) / bn);
+    g.ctl = PlainCtl();
+    if (!g.ctl) return HCCL_E_MEMORY;
+    g.nRanks = 1;
+    const int grid = std::min(SmCount(), g.tilesM * g.tilesN);
+    g.nGemmCtas = grid;
+    DevComm dummy;
+    memset(&dummy, 0, sizeof(dummy));
+    if (bn == 128) return DispatchLayout<128, MODE_PLAIN>(aMn, bMn, ta, tb, g, dummy, grid, false, stream);
+    return DispatchLayout<256, MODE_PLAIN>(aMn, bMn, ta, tb, g, dummy, grid, false, stream);
+}
+
+HcclResult Mc2AllGatherMatmul(CommImpl* comm, const void* aShard, const void* b, void* out, void* gathered, uint64_t mPerRank, uint64_t n,
+                              uint64_t k, int transB, cudaStream_t stream)
+{
+    CHK_PTR_NULL(comm); CHK_PTR_NULL(aShard); CHK_PTR_NULL(b); CHK_PTR_NULL(out); CHK_PTR_NULL(gathered);
+    const uint64_t P = (uint64_t)comm->nRanks;
+    CHK_RET(CheckShapes(mPerRank * P, n, k));
+    if (mPerRank % kBM != 0) { HCCL_ERROR("AllGather->Matmul needs rows per rank to be a multiple of %d (got %llu)", kBM, (unsigned long long)mPerRank); return HCCL_E_PARA; }
+    if (P * (mPerRank / kBM) > 8 * 512) return HCCL_E_PARA;
+    const char* peers[kMaxDevRanks];
+    if (!comm->Lookup(aShard, mPerRank * k * 2, peers, nullptr)) { HCCL_ERROR("AllGather->Matmul: the activation shard must live in symmetric memory (HcclMemAlloc)"); return HCCL_E_PARA; }
+    CHK_RET(Mc2EnsureState(comm, 0));
+    const bool bMn = transB == 0;
+    CUtensorMap ta, tb;
+    CHK_RET(MapA(&ta, gathered, mPerRank * P, k, false));
+    CHK_RET(MapB(&tb, b, n, k, bMn, 256));
+    GemmArgs g;
+    memset(&g, 0, sizeof(g));
+    FillPeers(comm, &g);
+    g.M = (int)(mPerRank * P); g.N = (int)n; g.K = (int)k;
+    g.out = (__nv_bfloat16*)out;
+    g.ldc = (int)n;
+    g.tilesM = g.M / kBM;
+    g.tilesN = (int)((n + 255) / 256);
+    g.mPerRank = (int)mPerRank;
+    for (int q = 0; q < comm->nRanks; ++q) g.aPeer[q] = (const __nv_bfloat16*)peers[q];
+    g.gathered = (__nv_bfloat16*)gathered;
+    const int workers = std::min(16, std::max(2, SmCount() / 9));
+    const int grid = SmCount();
+    g.nGemmCtas = grid - workers;
+    return DispatchLayout<256, MODE_AG>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream);
+}
+
+HcclResult Mc2MatmulReduceScatter(CommImpl* comm, const void* a, const void* b, void* out, uint64_t m, uint64_t n, uint64_t k, int transB,
+                                  cudaStream_t stream)
+{
+    CHK_PTR_NULL(comm); CHK_PTR_NULL(a); CHK_PTR_NULL(b); CHK_PTR_NULL(out);
+    const uint64_t P = (uint64_t)comm->nRanks;
+    CHK_RET(CheckShapes(m, n, k));
+    if (m % (P * kBM) != 0) { HCCL_ERROR("Matmul->ReduceScatter needs M to be a multiple of %llu (got %llu)", (unsigned long long)(P * kBM), (unsigned long long)m); return HCCL_E_PARA; }
+    const uint64_t mPerRank = m / P;
+    const uint64_t tilesN = (n + 255) / 256;
+    if ((mPerRank / kBM) * tilesN > (uint64_t)kMc2MaxTiles) return HCCL_E_PARA;
+    CHK_RET(Mc2EnsureState(comm, P * mPerRank * n * 2));
+    const bool bMn = transB == 0;
+    CUtensorMap ta, tb;
+    CHK_RET(MapA(&ta, a, m, k, false));
+    CHK_RET(MapB(&tb, b, n, k, bMn, 256));
+    GemmArgs g;
+    memset(&g, 0, sizeof(g));
+    FillPeers(comm, &g);
+    g.M = (int)m; g.N = (int)n; g.K = (int)k;
+    g.out = (__nv_bfloat16*)out;
+    g.ldc = (int)n;
+    g.tilesM = (int)(m / kBM);
+    g.tilesN = (int)tilesN;
+    g.mPerRank = (int)mPerRank;
+    const int workers = std::min(16, std::max(2, SmCount() / 9));
+    const int grid = SmCount();
+    g.nGemmCtas = grid - workers;
+    return DispatchLayout<256, MODE_RS>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream);
+}
+
+HcclResult Mc2MatmulAllReduce(CommImpl* comm, const void* a, const void* b, void* out, uint64_t m, uint64_t n, uint64_t k, int transB,
+                              cudaStream_t stream)
+{
+    CHK_PTR_NULL(comm); CHK_PTR_NULL(a); CHK_PTR_NULL(b); CHK_PTR_NULL(out);
+    const uint64_t P = (uint64_t)comm->nRanks;
+    CHK_RET(CheckShapes(m, n, k));
+    if (transB == 0) { HCCL_ERROR("Matmul->AllReduce takes the weight as [N, K]"); return HCCL_E_NOT_SUPPORT; }
+    const int tilesM = (int)((m + kBM - 1) / kBM), tilesN = (int)((n + 127) / 128);
+    if ((uint64_t)tilesM * tilesN > (uint64_t)kMc2MaxTiles) return HCCL_E_PARA;
+    // every tile is reduced by the CTA that computed it, which waits for its peers: all tiles must be resident at once
+    if (tilesM * tilesN > SmCount()) { HCCL_ERROR("Matmul->AllReduce handles at most %d output tiles of 128x128 (decode shapes)", SmCount()); return HCCL_E_NOT_SUPPORT; }
+    CHK_RET(Mc2EnsureState(comm, P * m * n * 2));
+    CUtensorMap ta, tb;
+    CHK_RET(MapA(&ta, a, m, k, false));
+    CHK_RET(MapB(&tb, b, n, k, false, 128));
+    GemmArgs g;
+    memset(&g, 0, sizeof(g));
+    FillPeers(comm, &g);
+    g.M = (int)m; g.N = (int)n; g.K = (int)k;
+    g.out = (__nv_bfloat16*)out;
+    g.ldc = (int)n;
+    g.tilesM = tilesM;
+    g.tilesN = tilesN;
+    const int grid = tilesM * tilesN;
+    g.nGemmCtas = grid;
+    return LaunchGemm<128, false, false, MODE_AR>(ta, tb, g, comm->dev(), grid, true, stream);
+}
+
+}  // namespace hccl

@@ -210,7 +210,10 @@ struct Exec {
             a.bytes = sum;
             if (inDirect) { for (int q = 0; q < P; ++q) a.src[q] = in.peer[q]; a.srcMc = in.mc; }
             else { FillStageIn(a); a.mode |= MODE_STAGE_IN; }
-            CHK_RET(Launch(a, a.cnt[me] * (uint64_t)(P > 1 ? 1 : 1) + 1));
+            // the grid must be the same on every rank: size it by the largest block, which all ranks know
+            uint64_t biggest = 0;
+            for (int q = 0; q < P; ++q) biggest = std::max(biggest, a.cnt[q]);
+            CHK_RET(Launch(a, biggest + 1));
             if (maxCnt == 0) break;
         }
         return HCCL_SUCCESS;
@@ -375,7 +378,10 @@ struct Exec {
             FillXch(a);
             if (inDirect) { for (int q = 0; q < P; ++q) a.src[q] = in.peer[q]; }
             else { FillStageIn(a); a.mode |= MODE_STAGE_IN; }
-            CHK_RET(Launch(a, traffic));
+            // every rank has to launch the same grid.  The uniform op and VC know the global sizes; AlltoAllV does
+            // not (counts are private to each rank), so it always runs with a fixed grid.
+            if (p.op == HCCL_CMD_ALLTOALLV) CHK_RET(LaunchCollective(tgt, dalg, p.dtype, a, std::min(c->MaxBlocks(), 32)));
+            else CHK_RET(Launch(a, std::min(chunk, p.globalMaxBytes) * (uint64_t)P));
         }
         return HCCL_SUCCESS;
     }

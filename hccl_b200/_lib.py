@@ -124,3 +124,17 @@ _sig("HcclGetPlanCacheStats", R, c_void_p, POINTER(c_uint64), POINTER(c_uint64),
 _sig("HcclSetLinkModel", R, c_double, c_double, c_double, c_double, c_double, c_double)
 _sig("HcclGetVersion", c_char_p)
 _sig("HcclReloadEnvConfig", R)
+# MC2
+_sig("HcclKfcAllocOpArgs", R, POINTER(c_void_p))
+_sig("HcclKfcFreeOpArgs", R, c_void_p)
+_sig("HcclKfcOpArgsSetSrcDataType", R, c_void_p, c_uint8)
+_sig("HcclKfcOpArgsSetDstDataType", R, c_void_p, c_uint8)
+_sig("HcclKfcOpArgsSetReduceType", R, c_void_p, c_uint32)
+_sig("HcclKfcOpArgsSetCount", R, c_void_p, c_uint64)
+_sig("HcclKfcOpArgsSetAlgConfig", R, c_void_p, c_char_p)
+_sig("HcclKfcOpArgsSetCommEngine", R, c_void_p, c_uint8)
+_sig("HcclCreateOpResCtx", R, c_void_p, c_uint8, c_void_p, POINTER(c_void_p))
+_sig("HcclMc2Matmul", R, c_void_p, c_void_p, c_void_p, c_uint64, c_uint64, c_uint64, c_int, c_int, c_void_p)
+_sig("HcclMc2AllGatherMatmul", R, c_void_p, c_void_p, c_void_p, c_void_p, c_uint64, c_uint64, c_uint64, c_int, c_void_p, c_void_p)
+_sig("HcclMc2MatmulReduceScatter", R, c_void_p, c_void_p, c_void_p, c_uint64, c_uint64, c_uint64, c_int, c_void_p, c_void_p)
+_sig("HcclMc2MatmulAllReduce", R, c_void_p, c_void_p, c_void_p, c_uint64, c_uint64, c_uint64, c_int, c_void_p, c_void_p)

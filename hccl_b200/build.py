@@ -81,7 +81,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_verbose: bool = Fals
         with concurrent.futures.ThreadPoolExecutor(workers) as ex:
             list(ex.map(lambda s: _compile(s, verbose or ptxas_verbose, extra), todo))
     if todo or not LIB.exists():
-        cmd = [NVCC, "-shared", "-o", str(LIB), *map(str, objs), "-Xcompiler", "-pthread", "-ldl", "-lrt"]
+        cmd = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB), *map(str, objs), "-Xcompiler", "-pthread", "-ldl", "-lrt"]
         if verbose:
             print(" ".join(cmd), flush=True)
         r = subprocess.run(cmd, capture_output=True, text=True)
