@@ -1,14 +1,319 @@
-// placeholder until the host engine lands
+// Host-engine communicators: creation, operator execution (selection + sole
+// executor loop + template run) and registration of the host algorithms.
 #include "host_comm.h"
+#include <algorithm>
+#include <cstring>
+#include "../core/comm.h"
+#include "../core/json.h"
 #include "../core/log.h"
-namespace hccl {
-void RegisterHostAlgorithms() {}
-HcclResult HostWorldCreate(uint32_t, const char*, const HcclCommConfig*, CommImpl**) { return HCCL_E_NOT_SUPPORT; }
-void HostRankRelease(HostRank*) {}
-HcclResult HostExecOp(CommImpl*, OpParam&) { return HCCL_E_NOT_SUPPORT; }
-}
+#include "../core/plan_cache.h"
+#include "../ops/op_common.h"
+#include "../ops/param_check.h"
+#include "../select/selector.h"
 #include "hccl/hccl_ext.h"
-extern "C" {
-HcclResult HcclHostTraceBegin(HcclComm) { return HCCL_E_NOT_SUPPORT; }
-HcclResult HcclHostTraceVerify(HcclComm, char*, uint32_t) { return HCCL_E_NOT_SUPPORT; }
+#include "host_world.h"
+
+namespace hccl {
+
+namespace {
+
+bool ParseTopoMeta(const char* json, uint32_t nRanks, TopoMeta* out, std::string* err)
+{
+    out->clear();
+    if (!json || !*json) {
+        std::vector<uint32_t> dev(nRanks);
+        for (uint32_t i = 0; i < nRanks; ++i) dev[i] = i;
+        out->push_back({dev});
+        return true;
+    }
+    JsonValue v;
+    if (!JsonParser(json).Parse(&v, err)) return false;
+    if (v.kind != JsonValue::ARR) { *err = "topology literal must be an array of pods"; return false; }
+    uint32_t total = 0;
+    for (auto& pod : v.arr) {
+        if (pod.kind != JsonValue::ARR) { *err = "a pod must be an array of servers"; return false; }
+        std::vector<std::vector<uint32_t>> servers;
+        for (auto& srv : pod.arr) {
+            if (srv.kind != JsonValue::ARR) { *err = "a server must be an array of device ids"; return false; }
+            std::vector<uint32_t> devs;
+            for (auto& d : srv.arr) { unsigned long long x; if (!d.AsU64(&x)) { *err = "device ids must be numbers"; return false; } devs.push_back((uint32_t)x); ++total; }
+            servers.push_back(devs);
+        }
+        out->push_back(servers);
+    }
+    if (total != nRanks) { *err = "topology literal lists " + std::to_string(total) + " devices for " + std::to_string(nRanks) + " ranks"; return false; }
+    return true;
 }
+
+uint64_t InBytes(const OpParam& p, uint32_t n)
+{
+    const uint64_t es = DataTypeSize(p.dtype);
+    switch (p.op) {
+        case HCCL_CMD_REDUCE_SCATTER: case HCCL_CMD_SCATTER: return p.count * es * n;
+        case HCCL_CMD_REDUCE_SCATTER_V: { uint64_t m = 0; for (uint32_t q = 0; q < n; ++q) m = std::max(m, (p.sdispls[q] + p.sendCounts[q]) * es); return m; }
+        case HCCL_CMD_ALLTOALL: case HCCL_CMD_ALLTOALLV: case HCCL_CMD_ALLTOALLVC: { uint64_t m = 0; for (uint32_t q = 0; q < n; ++q) m = std::max(m, (p.sdispls[q] + p.sendCounts[q]) * es); return m; }
+        case HCCL_CMD_BARRIER: case HCCL_CMD_SEND: case HCCL_CMD_RECEIVE: case HCCL_CMD_BATCH_SEND_RECV: return 0;
+        default: return p.count * es;
+    }
+}
+uint64_t OutBytes(const OpParam& p, uint32_t n)
+{
+    const uint64_t es = DataTypeSize(p.dtype), res = DataTypeSize(p.recvType);
+    switch (p.op) {
+        case HCCL_CMD_ALLGATHER: return p.count * es * n;
+        case HCCL_CMD_ALLGATHER_V: { uint64_t m = 0; for (uint32_t q = 0; q < n; ++q) m = std::max(m, (p.rdispls[q] + p.recvCounts[q]) * es); return m; }
+        case HCCL_CMD_ALLTOALL: case HCCL_CMD_ALLTOALLV: case HCCL_CMD_ALLTOALLVC: { uint64_t m = 0; for (uint32_t q = 0; q < n; ++q) m = std::max(m, (p.rdispls[q] + p.recvCounts[q]) * res); return m; }
+        case HCCL_CMD_BARRIER: case HCCL_CMD_SEND: case HCCL_CMD_RECEIVE: case HCCL_CMD_BATCH_SEND_RECV: return 0;
+        default: return p.count * es;
+    }
+}
+
+HostOpDesc Desc(const OpParam& p)
+{
+    HostOpDesc d;
+    d.op = p.op; d.dtype = p.dtype; d.redOp = p.redOp; d.count = p.count; d.root = p.root;
+    d.sendCounts = p.sendCounts; d.sdispls = p.sdispls; d.recvCounts = p.recvCounts; d.rdispls = p.rdispls;
+    return d;
+}
+
+}  // namespace
+
+HcclResult HostWorldCreate(uint32_t nRanks, const char* topoJson, const HcclCommConfig* cfg, CommImpl** comms)
+{
+    if (nRanks == 0 || nRanks > 4096) return HCCL_E_PARA;
+    TopoMeta meta;
+    std::string err;
+    if (!ParseTopoMeta(topoJson, nRanks, &meta, &err)) { HCCL_ERROR("host communicator: %s", err.c_str()); return HCCL_E_PARA; }
+    EffectiveConfig eff;
+    CHK_RET(MergeConfig(GetEnvConfig(), cfg, &eff));
+    // the per-rank scratch is host memory: default 64 MiB unless configured
+    const bool sized = (cfg && cfg->hcclBufferSize) || GetEnvConfig().bufferSizeMiB;
+    const uint64_t scratch = sized ? eff.bufferBytes : (64ull << 20);
+    auto world = std::make_shared<HostWorld>(nRanks, meta, scratch, eff.execTimeoutNs);
+    for (uint32_t r = 0; r < nRanks; ++r) {
+        CommImpl* c = new CommImpl();
+        c->rank = (int)r;
+        c->nRanks = (int)nRanks;
+        c->device = -1;
+        c->cfg = eff;
+        char nm[64];
+        snprintf(nm, sizeof(nm), "hccl_host_%p", (void*)world.get());
+        c->name = eff.commName.empty() ? nm : eff.commName;
+        c->hostComm = new HostRank(world, r);
+        c->topo.reset(new TopoInfo(world->Topo(r)));
+        c->selector.reset(new SelectorState());
+        c->plans.reset(new PlanCache());
+        comms[r] = c;
+    }
+    return HCCL_SUCCESS;
+}
+
+void HostRankRelease(HostRank* r) { delete r; }
+
+HcclResult HostExecOp(CommImpl* c, OpParam& p)
+{
+    HostWorld& w = *c->hostComm->world;
+    const uint32_t rank = c->hostComm->rank, n = w.nRanks();
+    // selection (identical on every rank: same inputs)
+    OpDesc d;
+    d.op = p.op; d.dtype = p.dtype; d.redOp = p.redOp; d.root = p.root; d.nRanks = n;
+    d.det = c->cfg.deterministic;
+    d.engine = HCCL_ENGINE_HOSTCPU;
+    d.bytes = std::max(InBytes(p, n), OutBytes(p, n));
+    d.inPlace = p.send == p.recv;
+    Selection sel;
+    CHK_RET(SelectAlgorithm(*c->selector, *c->topo, GetEnvConfig(), d, c->name, (HcclComm)c, w.scratchBytes(), &sel));
+    p.algName = sel.alg->name;
+    const int alg = sel.alg->hostAlg;
+    const uint64_t es = DataTypeSize(p.dtype);
+
+    // sole-executor loop for the contiguous operators: bytes per loop = floor(scratch / multiple / 128) * 128
+    const bool chunkable = p.op == HCCL_CMD_ALLREDUCE || p.op == HCCL_CMD_BROADCAST || p.op == HCCL_CMD_REDUCE;
+    uint64_t perLoop = p.count;
+    if (chunkable && es) {
+        const uint64_t mult = HostScratchMultiple(alg, n) * 2;    // templates that keep W in scratch use half of it
+        const uint64_t maxBytes = w.scratchBytes() / mult / 128 * 128;
+        if (maxBytes == 0) return HCCL_E_MEMORY;
+        perLoop = std::min<uint64_t>(p.count, std::max<uint64_t>(1, maxBytes / es));
+    } else if (d.bytes * 2 > w.scratchBytes() && p.op != HCCL_CMD_BARRIER && p.op != HCCL_CMD_SEND && p.op != HCCL_CMD_RECEIVE &&
+               p.op != HCCL_CMD_BATCH_SEND_RECV && p.op != HCCL_CMD_ALLGATHER && p.op != HCCL_CMD_ALLGATHER_V && p.op != HCCL_CMD_ALLTOALL &&
+               p.op != HCCL_CMD_ALLTOALLV && p.op != HCCL_CMD_ALLTOALLVC && p.op != HCCL_CMD_SCATTER) {
+        HCCL_ERROR("host engine: %s of %llu bytes needs more than the %llu-byte scratch buffer (raise HCCL_BUFFSIZE)", CmdName(p.op),
+                   (unsigned long long)d.bytes, (unsigned long long)w.scratchBytes());
+        return HCCL_E_MEMORY;
+    }
+    HcclResult result = HCCL_SUCCESS;
+    for (uint64_t off = 0; off < std::max<uint64_t>(p.count, 1); off += std::max<uint64_t>(perLoop, 1)) {
+        OpParam sub = p;
+        if (chunkable) {
+            sub.count = std::min(perLoop, p.count - off);
+            sub.send = (const char*)p.send + off * es;
+            sub.recv = p.recv ? (char*)p.recv + off * es : nullptr;
+        }
+        HostOpDesc hd = Desc(sub);
+        const void* in = sub.send;
+        void* out = sub.recv;
+        if (p.op == HCCL_CMD_BROADCAST) { in = sub.recv; }
+        HcclResult r = w.Enter(rank, hd, in, out, InBytes(sub, n), OutBytes(sub, n));
+        if (r == HCCL_SUCCESS) r = RunHostAlgorithm(w, rank, alg, sub);
+        HcclResult l = w.Leave(rank);
+        if (r == HCCL_SUCCESS) r = l;
+        if (r != HCCL_SUCCESS) { result = r; break; }
+        if (!chunkable) break;
+    }
+    if (result != HCCL_SUCCESS) c->status_.store(HCCL_COMM_STATUS_ERROR);
+    return result;
+}
+
+// ------------------------------------------------------------------ registration
+namespace {
+
+constexpr uint64_t Bit(HcclDataType t) { return 1ull << (int)t; }
+constexpr uint64_t kReduceTypes = Bit(HCCL_DATA_TYPE_INT8) | Bit(HCCL_DATA_TYPE_INT16) | Bit(HCCL_DATA_TYPE_INT32) | Bit(HCCL_DATA_TYPE_INT64) |
+                                  Bit(HCCL_DATA_TYPE_UINT64) | Bit(HCCL_DATA_TYPE_FP16) | Bit(HCCL_DATA_TYPE_BFP16) | Bit(HCCL_DATA_TYPE_FP32) |
+                                  Bit(HCCL_DATA_TYPE_FP64);
+
+struct HostAlgSpec {
+    const char* name;
+    HcclCMDType op;
+    int hostAlg;
+    const char* executor;
+    std::vector<std::string> templates;
+    AlgoType family;
+    uint32_t minLevels;
+    bool reduces;
+    // cost shape: steps (latency terms) and the fraction of the message that crosses a link per rank
+    std::function<double(double p)> steps, traffic;
+    bool orderPreserved;
+};
+
+double Log2Ceil(double p) { return (double)CeilLog2((uint32_t)p); }
+
+void Reg(const HostAlgSpec& s)
+{
+    AlgEntry e;
+    e.name = s.name;
+    e.op = s.op;
+    e.engine = HCCL_ENGINE_HOSTCPU;
+    e.executor = s.executor;
+    e.templates = s.templates;
+    e.hostAlg = s.hostAlg;
+    e.family = s.family;
+    e.attrs.minLevels = s.minLevels;
+    e.attrs.maxLevels = 3;
+    // AllReduce / ReduceScatter / AllGather have hierarchical forms: their flat forms stay on one-level topologies
+    if (s.minLevels == 1 && std::string(s.executor) != "orderpreserved" &&
+        (s.op == HCCL_CMD_ALLREDUCE || s.op == HCCL_CMD_REDUCE_SCATTER || s.op == HCCL_CMD_ALLGATHER)) {
+        e.attrs.maxLevels = 1;
+        e.attrs.enforceMaxLevels = true;
+    }
+    if (s.reduces) e.attrs.dtypeMask = kReduceTypes;
+    e.attrs.orderPreserved = s.orderPreserved;
+    auto steps = s.steps, traffic = s.traffic;
+    e.costCoeff = [steps, traffic](const TopoInfo& t, const OpDesc&) {
+        const LinkModel& lm = GlobalLinkModel();
+        const double p = (double)t.nRanks;
+        CostCoeff c;
+        c.A = traffic(p) / (lm.hostMemGBs * 1e3);
+        c.C = steps(p) * lm.hostStepUs;
+        c.net = NetType::HOST_MEM;
+        c.ratio = 1.0 / p;
+        return std::vector<CostCoeff>{c};
+    };
+    AlgRegistry::Instance().Register(std::move(e));
+}
+
+}  // namespace
+
+void RegisterHostAlgorithms()
+{
+    auto P1 = [](double p) { return p - 1; };
+    auto TwoP1 = [](double p) { return 2 * (p - 1); };
+    auto L = [](double p) { return Log2Ceil(p); };
+    auto TwoL = [](double p) { return 2 * Log2Ceil(p); };
+    auto Two = [](double) { return 2.0; };
+    auto Three = [](double) { return 3.0; };
+    auto rs = [](double p) { return (p - 1) / p; };
+    auto ar = [](double p) { return 2 * (p - 1) / p; };
+    auto full = [](double p) { return p - 1; };
+    auto one = [](double) { return 1.0; };
+    // AllReduce
+    Reg({"HostAllReduceSoleMeshOneShot", HCCL_CMD_ALLREDUCE, HALG_AR_MESH_ONESHOT, "sole", {"MeshOneShot"}, AlgoType::ONESHOT, 1, true, Two, full, true});
+    Reg({"HostAllReduceSoleMeshTwoShot", HCCL_CMD_ALLREDUCE, HALG_AR_MESH_TWOSHOT, "sole", {"MeshTwoShot"}, AlgoType::MESH, 1, true, Three, ar, true});
+    Reg({"HostAllReduceSoleRing", HCCL_CMD_ALLREDUCE, HALG_AR_RING, "sole", {"Ring"}, AlgoType::RING, 1, true, TwoP1, ar, true});
+    Reg({"HostAllReduceSoleRHD", HCCL_CMD_ALLREDUCE, HALG_AR_RHD, "sole", {"RHD"}, AlgoType::HD_R, 1, true, TwoL, ar, true});
+    Reg({"HostAllReduceSoleNHR", HCCL_CMD_ALLREDUCE, HALG_AR_NHR, "sole", {"NHR"}, AlgoType::NHR, 1, true, TwoL, ar, true});
+    Reg({"HostAllReduceStrictOrderedMesh", HCCL_CMD_ALLREDUCE, HALG_AR_ORDER_PRESERVED, "orderpreserved", {"OrderPreservedGroup"}, AlgoType::AHC, 1, true, Three, full, true});
+    Reg({"HostAllReduceSequenceMeshRing", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_MESH_RING, "sequence", {"Mesh", "Ring"}, AlgoType::RING, 2, true, TwoP1, ar, true});
+    Reg({"HostAllReduceSequenceMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_MESH_NHR, "sequence", {"Mesh", "NHR"}, AlgoType::NHR, 2, true, TwoL, ar, true});
+    Reg({"HostAllReduceSequenceMeshRHD", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_MESH_RHD, "sequence", {"Mesh", "RHD"}, AlgoType::HD_R, 2, true, TwoL, ar, true});
+    Reg({"HostAllReduceSequenceMeshNHRNHR", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ3_MESH_NHR_NHR, "sequence", {"Mesh", "NHR", "NHR"}, AlgoType::NHR, 3, true, TwoL, ar, true});
+    Reg({"HostAllReduceParallelMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_PARALLEL_MESH_NHR, "parallel", {"Mesh", "NHR"}, AlgoType::PIPELINE, 2, true, TwoL, ar, true});
+    // ReduceScatter (+V)
+    Reg({"HostReduceScatterSoleMesh", HCCL_CMD_REDUCE_SCATTER, HALG_RS_MESH, "sole", {"Mesh"}, AlgoType::MESH, 1, true, Two, rs, true});
+    Reg({"HostReduceScatterSoleRing", HCCL_CMD_REDUCE_SCATTER, HALG_RS_RING, "sole", {"Ring"}, AlgoType::RING, 1, true, P1, rs, true});
+    Reg({"HostReduceScatterSoleRHD", HCCL_CMD_REDUCE_SCATTER, HALG_RS_RHD, "sole", {"RHD"}, AlgoType::HD_R, 1, true, L, rs, true});
+    Reg({"HostReduceScatterSoleNHR", HCCL_CMD_REDUCE_SCATTER, HALG_RS_NHR, "sole", {"NHR"}, AlgoType::NHR, 1, true, L, rs, true});
+    Reg({"HostReduceScatterStrictOrderedMesh", HCCL_CMD_REDUCE_SCATTER, HALG_RS_ORDER_PRESERVED, "orderpreserved", {"OrderPreservedGroup"}, AlgoType::AHC, 1, true, Three, full, true});
+    Reg({"HostReduceScatterSequenceMeshNHR", HCCL_CMD_REDUCE_SCATTER, HALG_RS_SEQ_MESH_NHR, "sequence", {"NHR", "Mesh"}, AlgoType::NHR, 2, true, L, rs, true});
+    Reg({"HostReduceScatterVSoleMesh", HCCL_CMD_REDUCE_SCATTER_V, HALG_RS_MESH, "sole", {"Mesh"}, AlgoType::MESH, 1, true, Two, rs, true});
+    // AllGather (+V)
+    Reg({"HostAllGatherSoleMesh", HCCL_CMD_ALLGATHER, HALG_AG_MESH, "sole", {"Mesh"}, AlgoType::MESH, 1, false, Two, rs, true});
+    Reg({"HostAllGatherSoleRing", HCCL_CMD_ALLGATHER, HALG_AG_RING, "sole", {"Ring"}, AlgoType::RING, 1, false, P1, rs, true});
+    Reg({"HostAllGatherSoleRHD", HCCL_CMD_ALLGATHER, HALG_AG_RHD, "sole", {"RHD"}, AlgoType::HD_R, 1, false, L, rs, true});
+    Reg({"HostAllGatherSoleNHR", HCCL_CMD_ALLGATHER, HALG_AG_NHR, "sole", {"NHR"}, AlgoType::NHR, 1, false, L, rs, true});
+    Reg({"HostAllGatherSequenceMeshNHR", HCCL_CMD_ALLGATHER, HALG_AG_SEQ_MESH_NHR, "sequence", {"Mesh", "NHR"}, AlgoType::NHR, 2, false, L, rs, true});
+    Reg({"HostAllGatherVSoleMesh", HCCL_CMD_ALLGATHER_V, HALG_AG_MESH, "sole", {"Mesh"}, AlgoType::MESH, 1, false, Two, rs, true});
+    // Broadcast / Reduce / Scatter
+    Reg({"HostBroadcastSoleMeshOneShot", HCCL_CMD_BROADCAST, HALG_BCAST_MESH_ONESHOT, "sole", {"MeshOneShot"}, AlgoType::ONESHOT, 1, false, Two, full, true});
+    Reg({"HostBroadcastSoleMeshTwoShot", HCCL_CMD_BROADCAST, HALG_BCAST_MESH_TWOSHOT, "sole", {"MeshTwoShot"}, AlgoType::MESH, 1, false, Three, ar, true});
+    Reg({"HostBroadcastSoleNHR", HCCL_CMD_BROADCAST, HALG_BCAST_NHR, "sole", {"NHR"}, AlgoType::NHR, 1, false, L, ar, true});
+    Reg({"HostReduceSoleMeshOneShot", HCCL_CMD_REDUCE, HALG_REDUCE_MESH_ONESHOT, "sole", {"MeshOneShot"}, AlgoType::ONESHOT, 1, true, Two, full, true});
+    Reg({"HostReduceSoleMeshTwoShot", HCCL_CMD_REDUCE, HALG_REDUCE_MESH_TWOSHOT, "sole", {"MeshTwoShot"}, AlgoType::MESH, 1, true, Three, ar, true});
+    Reg({"HostReduceSoleNHR", HCCL_CMD_REDUCE, HALG_REDUCE_NHR, "sole", {"NHR"}, AlgoType::NHR, 1, true, L, ar, true});
+    Reg({"HostScatterSoleMesh", HCCL_CMD_SCATTER, HALG_SCATTER_MESH, "sole", {"Mesh"}, AlgoType::MESH, 1, false, Two, rs, true});
+    Reg({"HostScatterSoleRing", HCCL_CMD_SCATTER, HALG_SCATTER_RING, "sole", {"Ring"}, AlgoType::RING, 1, false, P1, one, true});
+    // AlltoAll family
+    for (HcclCMDType op : {HCCL_CMD_ALLTOALL, HCCL_CMD_ALLTOALLV, HCCL_CMD_ALLTOALLVC}) {
+        const char* base = op == HCCL_CMD_ALLTOALL ? "HostAlltoAll" : op == HCCL_CMD_ALLTOALLV ? "HostAlltoAllV" : "HostAlltoAllVC";
+        static std::vector<std::string> keep;
+        keep.push_back(std::string(base) + "SoleMesh");
+        Reg({keep.back().c_str(), op, HALG_A2A_MESH, "sole", {"Mesh"}, AlgoType::MESH, 1, false, Two, rs, true});
+        keep.push_back(std::string(base) + "SolePairwise");
+        Reg({keep.back().c_str(), op, HALG_A2A_PAIRWISE, "sole", {"Pairwise"}, AlgoType::PAIRWISE, 1, false, P1, rs, true});
+    }
+    // point to point and barrier
+    Reg({"HostSendSoleMesh", HCCL_CMD_SEND, HALG_P2P_DIRECT, "sole", {"Direct"}, AlgoType::MESH, 1, false, one, one, true});
+    Reg({"HostRecvSoleMesh", HCCL_CMD_RECEIVE, HALG_P2P_DIRECT, "sole", {"Direct"}, AlgoType::MESH, 1, false, one, one, true});
+    Reg({"HostBatchSendRecvSoleMesh", HCCL_CMD_BATCH_SEND_RECV, HALG_P2P_DIRECT, "sole", {"Direct"}, AlgoType::MESH, 1, false, one, one, true});
+    Reg({"HostBarrierSoleMesh", HCCL_CMD_BARRIER, HALG_BARRIER_MESH, "sole", {"Mesh"}, AlgoType::MESH, 1, false, one, [](double) { return 0.0; }, true});
+    Reg({"HostBarrierSoleNHR", HCCL_CMD_BARRIER, HALG_BARRIER_NHR, "sole", {"NHR"}, AlgoType::NHR, 1, false, L, [](double) { return 0.0; }, true});
+    Reg({"HostBarrierSoleRHD", HCCL_CMD_BARRIER, HALG_BARRIER_RHD, "sole", {"RHD"}, AlgoType::HD_R, 1, false, L, [](double) { return 0.0; }, true});
+}
+
+}  // namespace hccl
+
+using namespace hccl;
+
+extern "C" {
+
+HcclResult HcclHostTraceBegin(HcclComm comm)
+{
+    CHK_PTR_NULL(comm);
+    CommImpl* c = static_cast<CommImpl*>(comm);
+    if (!c->hostComm) return HCCL_E_NOT_SUPPORT;
+    c->hostComm->world->TraceBegin();
+    return HCCL_SUCCESS;
+}
+
+HcclResult HcclHostTraceVerify(HcclComm comm, char* report, uint32_t capacity)
+{
+    CHK_PTR_NULL(comm);
+    CommImpl* c = static_cast<CommImpl*>(comm);
+    if (!c->hostComm) return HCCL_E_NOT_SUPPORT;
+    VerifyReport rep = c->hostComm->world->Verify();
+    if (report && capacity) snprintf(report, capacity, "%s", rep.Text().c_str());
+    return rep.ok ? HCCL_SUCCESS : HCCL_E_INTERNAL;
+}
+
+}  // extern "C"

@@ -1,0 +1,254 @@
+// Verifier of recorded host-engine traces.
+//
+// Same job as the reference's hccl_verifier (checker.cc:61-104): build a DAG over all ranks' tasks by
+// pairing posts with waits, then check (1) that the DAG can be executed to the end (no unmatched wait, no cycle =
+// no deadlock), (2) that every access stays inside its buffer, (3) memory conflicts: two accesses to overlapping
+// bytes of the same buffer, at least one a write, must be ordered by the DAG
+// (mem_conflict_check/check_rank_mem.h:137-199), and (4) semantics: the operator is executed symbolically - every
+// element carries the set of (source rank, source element) contributions that were reduced into it - and the final
+// outputs are compared with the operator's definition (semantics_check/*_semantics_checker.cc).
+#include <algorithm>
+#include <map>
+#include <set>
+#include <sstream>
+#include <unordered_map>
+#include "../ops/param_check.h"
+#include "host_world.h"
+
+namespace hccl {
+
+namespace {
+
+struct Node {
+    const Task* t;
+    uint32_t rank;
+    std::vector<uint32_t> succ;
+    uint32_t indeg = 0;
+};
+
+// Symbolic value of one element: which (rank, input element) pairs were folded into it.
+struct Sym {
+    std::vector<std::pair<uint32_t, uint64_t>> terms;   // sorted, unique
+    bool operator==(const Sym& o) const { return terms == o.terms; }
+};
+
+struct Range { uint32_t rank; BufKind buf; uint64_t b, e; bool write; uint32_t node; };
+
+bool Overlap(const Range& a, const Range& b) { return a.rank == b.rank && a.buf == b.buf && a.b < b.e && b.b < a.e; }
+
+}  // namespace
+
+class HostVerifier {
+public:
+    static void CheckOp(HostWorld& w, const HostWorld::OpRecord& op, VerifyReport* rep);
+};
+
+void HostVerifier::CheckOp(HostWorld& w, const HostWorld::OpRecord& op, VerifyReport* rep)
+{
+    const uint32_t n = w.nRanks();
+    const uint32_t es = std::max<uint32_t>(1, DataTypeSize(op.desc.dtype));
+    auto fail = [&](const std::string& s) { rep->ok = false; if (rep->errors.size() < 20) rep->errors.push_back(std::string(CmdName(op.desc.op)) + ": " + s); };
+
+    // ---- nodes and program-order edges (per rank and queue)
+    std::vector<Node> nodes;
+    std::vector<std::vector<uint32_t>> byRank(n);
+    for (uint32_t r = 0; r < n; ++r) {
+        std::map<uint32_t, uint32_t> lastOfQueue;
+        for (const Task& t : op.tasks[r]) {
+            const uint32_t id = (uint32_t)nodes.size();
+            nodes.push_back(Node{&t, r, {}, 0});
+            byRank[r].push_back(id);
+            auto it = lastOfQueue.find(t.queue);
+            if (it != lastOfQueue.end()) { nodes[it->second].succ.push_back(id); ++rep->edges; }
+            lastOfQueue[t.queue] = id;
+        }
+    }
+    rep->tasks += nodes.size();
+    // queues of one rank are started together and joined at the end by the executing thread; in this engine a
+    // template that uses a second queue runs it after the first, which the trace reflects through program order
+    // on the issuing thread: add the fork/join edges (first task of queue q > 0 after the last task before it).
+    for (uint32_t r = 0; r < n; ++r)
+        for (size_t i = 1; i < byRank[r].size(); ++i)
+            if (nodes[byRank[r][i]].t->queue != nodes[byRank[r][i - 1]].t->queue) { nodes[byRank[r][i - 1]].succ.push_back(byRank[r][i]); ++rep->edges; }
+
+    // ---- post -> wait edges: the k-th post from a to b on index i pairs with the k-th wait on b for (a, i)
+    std::map<std::tuple<uint32_t, uint32_t, uint32_t>, std::vector<uint32_t>> posts, waits;
+    for (uint32_t id = 0; id < nodes.size(); ++id) {
+        const Task& t = *nodes[id].t;
+        if (t.kind == TaskKind::POST) posts[{t.rank, t.peer, t.notifyIdx}].push_back(id);
+        else if (t.kind == TaskKind::WAIT) waits[{t.peer, t.rank, t.notifyIdx}].push_back(id);
+    }
+    for (auto& kv : waits) {
+        auto pit = posts.find(kv.first);
+        const size_t have = pit == posts.end() ? 0 : pit->second.size();
+        if (have < kv.second.size()) {
+            std::ostringstream os;
+            os << "rank " << std::get<1>(kv.first) << " waits " << kv.second.size() << " times for notify " << std::get<2>(kv.first) << " from rank "
+               << std::get<0>(kv.first) << " but only " << have << " posts exist (would hang)";
+            fail(os.str());
+        }
+        for (size_t k = 0; k < std::min(have, kv.second.size()); ++k) { nodes[pit->second[k]].succ.push_back(kv.second[k]); ++rep->edges; }
+    }
+    for (auto& kv : posts) {
+        auto wit = waits.find(kv.first);
+        const size_t have = wit == waits.end() ? 0 : wit->second.size();
+        if (have != kv.second.size()) {
+            std::ostringstream os;
+            os << "rank " << std::get<0>(kv.first) << " posts notify " << std::get<2>(kv.first) << " to rank " << std::get<1>(kv.first) << " " << kv.second.size()
+               << " times but it is waited for " << have << " times (a stale post would satisfy a later operator's wait)";
+            fail(os.str());
+        }
+    }
+
+    // ---- topological order (deadlock = cycle)
+    for (auto& nd : nodes) for (uint32_t s : nd.succ) ++nodes[s].indeg;
+    std::vector<uint32_t> order, ready;
+    for (uint32_t id = 0; id < nodes.size(); ++id) if (nodes[id].indeg == 0) ready.push_back(id);
+    std::vector<uint32_t> indeg(nodes.size());
+    for (uint32_t id = 0; id < nodes.size(); ++id) indeg[id] = nodes[id].indeg;
+    while (!ready.empty()) {
+        const uint32_t id = ready.back();
+        ready.pop_back();
+        order.push_back(id);
+        for (uint32_t s : nodes[id].succ) if (--indeg[s] == 0) ready.push_back(s);
+    }
+    if (order.size() != nodes.size()) { fail("the task graph has a cycle: " + std::to_string(nodes.size() - order.size()) + " tasks can never run (deadlock)"); return; }
+
+    // ---- reachability (happens-before) as bitsets, in reverse topological order
+    const size_t words = (nodes.size() + 63) / 64;
+    std::vector<uint64_t> reach(nodes.size() * words, 0);
+    for (size_t i = order.size(); i-- > 0;) {
+        const uint32_t id = order[i];
+        uint64_t* row = &reach[(size_t)id * words];
+        for (uint32_t s : nodes[id].succ) {
+            row[s / 64] |= 1ull << (s % 64);
+            const uint64_t* srow = &reach[(size_t)s * words];
+            for (size_t k = 0; k < words; ++k) row[k] |= srow[k];
+        }
+    }
+    auto before = [&](uint32_t a, uint32_t b) { return (reach[(size_t)a * words + b / 64] >> (b % 64)) & 1ull; };
+
+    // ---- bounds + access ranges
+    std::vector<Range> ranges;
+    auto bufBytes = [&](const Mem& m) -> uint64_t {
+        switch (m.buf) { case BufKind::INPUT: return op.inBytes[m.rank]; case BufKind::OUTPUT: return op.outBytes[m.rank]; default: return w.scratchBytes(); }
+    };
+    for (uint32_t id = 0; id < nodes.size(); ++id) {
+        const Task& t = *nodes[id].t;
+        if (t.kind == TaskKind::POST || t.kind == TaskKind::WAIT) continue;
+        ++rep->dataTasks;
+        if (t.dst.off + t.bytes > bufBytes(t.dst) || t.src.off + t.bytes > bufBytes(t.src)) { fail("task of rank " + std::to_string(t.rank) + " leaves its buffer"); continue; }
+        if (t.dst.buf == BufKind::INPUT) fail("task of rank " + std::to_string(t.rank) + " writes a user input buffer");
+        const bool reduces = t.kind == TaskKind::LOCAL_REDUCE || t.kind == TaskKind::READ_REDUCE || t.kind == TaskKind::WRITE_REDUCE;
+        ranges.push_back({t.dst.rank, t.dst.buf, t.dst.off, t.dst.off + t.bytes, true, id});
+        (void)reduces;
+        ranges.push_back({t.src.rank, t.src.buf, t.src.off, t.src.off + t.bytes, false, id});
+    }
+    // ---- memory conflicts: sort by (rank, buf, begin) and sweep
+    std::sort(ranges.begin(), ranges.end(), [](const Range& a, const Range& b) {
+        if (a.rank != b.rank) return a.rank < b.rank;
+        if (a.buf != b.buf) return a.buf < b.buf;
+        return a.b < b.b;
+    });
+    size_t conflicts = 0;
+    for (size_t i = 0; i < ranges.size() && conflicts < 5; ++i) {
+        for (size_t j = i + 1; j < ranges.size() && ranges[j].rank == ranges[i].rank && ranges[j].buf == ranges[i].buf && ranges[j].b < ranges[i].e; ++j) {
+            if (!ranges[i].write && !ranges[j].write) continue;
+            if (ranges[i].node == ranges[j].node) continue;
+            if (!Overlap(ranges[i], ranges[j])) continue;
+            if (before(ranges[i].node, ranges[j].node) || before(ranges[j].node, ranges[i].node)) continue;
+            std::ostringstream os;
+            const Task& a = *nodes[ranges[i].node].t;
+            const Task& b = *nodes[ranges[j].node].t;
+            os << "unordered accesses to rank " << ranges[i].rank << " buffer " << (int)ranges[i].buf << " bytes [" << std::max(ranges[i].b, ranges[j].b) << ", "
+               << std::min(ranges[i].e, ranges[j].e) << "): task of rank " << a.rank << " (" << (ranges[i].write ? "write" : "read") << ") and task of rank " << b.rank
+               << " (" << (ranges[j].write ? "write" : "read") << ")";
+            fail(os.str());
+            ++conflicts;
+        }
+    }
+
+    // ---- semantics: symbolic execution in topological order at element granularity (sparse: only touched elements)
+    std::map<std::pair<uint32_t, int>, std::unordered_map<uint64_t, Sym>> state;   // (rank, buf) -> element -> value
+    auto load = [&](const Mem& m, uint64_t elem) -> Sym {
+        auto& mp = state[{m.rank, (int)m.buf}];
+        auto it = mp.find(elem);
+        if (it != mp.end()) return it->second;
+        Sym s;
+        if (m.buf == BufKind::INPUT) s.terms = {{m.rank, elem}};
+        return s;
+    };
+    for (uint32_t id : order) {
+        const Task& t = *nodes[id].t;
+        if (t.kind == TaskKind::POST || t.kind == TaskKind::WAIT) continue;
+        if (t.bytes % es || t.dst.off % es || t.src.off % es) continue;   // metadata moves (byte granular) carry no operator semantics
+        const uint64_t ne = t.bytes / es, d0 = t.dst.off / es, s0 = t.src.off / es;
+        const bool reduces = t.kind == TaskKind::LOCAL_REDUCE || t.kind == TaskKind::READ_REDUCE || t.kind == TaskKind::WRITE_REDUCE;
+        auto& dmap = state[{t.dst.rank, (int)t.dst.buf}];
+        // a copy inside one buffer may overlap: read everything first
+        std::vector<Sym> srcVals(ne);
+        for (uint64_t i = 0; i < ne; ++i) srcVals[i] = load(t.src, s0 + i);
+        for (uint64_t i = 0; i < ne; ++i) {
+            if (!reduces) { dmap[d0 + i] = std::move(srcVals[i]); continue; }
+            const Sym cur = load(t.dst, d0 + i);
+            Sym out;
+            std::set_union(cur.terms.begin(), cur.terms.end(), srcVals[i].terms.begin(), srcVals[i].terms.end(), std::back_inserter(out.terms));
+            if (out.terms.size() != cur.terms.size() + srcVals[i].terms.size()) {
+                fail("a contribution is reduced twice into rank " + std::to_string(t.dst.rank) + " element " + std::to_string(d0 + i));
+                return;
+            }
+            dmap[d0 + i] = std::move(out);
+        }
+    }
+    // expected outputs per operator
+    const HostOpDesc& D = op.desc;
+    auto expect = [&](uint32_t rank, uint64_t outElem, const Sym& want) {
+        const Sym got = load(Mem{rank, BufKind::OUTPUT, 0}, outElem);
+        if (!(got == want)) {
+            std::ostringstream os;
+            os << "rank " << rank << " output element " << outElem << " holds " << got.terms.size() << " contributions, expected " << want.terms.size();
+            fail(os.str());
+            return false;
+        }
+        return true;
+    };
+    auto allRanksTerm = [&](uint64_t elem) { Sym s; for (uint32_t r = 0; r < n; ++r) s.terms.push_back({r, elem}); return s; };
+    bool good = true;
+    switch (D.op) {
+        case HCCL_CMD_ALLREDUCE:
+            for (uint32_t r = 0; r < n && good; ++r) for (uint64_t i = 0; i < D.count && good; ++i) good = expect(r, i, allRanksTerm(i));
+            break;
+        case HCCL_CMD_REDUCE:
+            for (uint64_t i = 0; i < D.count && good; ++i) good = expect(D.root, i, allRanksTerm(i));
+            break;
+        case HCCL_CMD_REDUCE_SCATTER:
+            for (uint32_t r = 0; r < n && good; ++r) for (uint64_t i = 0; i < D.count && good; ++i) good = expect(r, i, allRanksTerm((uint64_t)r * D.count + i));
+            break;
+        case HCCL_CMD_ALLGATHER:
+            for (uint32_t r = 0; r < n && good; ++r)
+                for (uint32_t q = 0; q < n && good; ++q)
+                    for (uint64_t i = 0; i < D.count && good; ++i) { Sym s; s.terms = {{q, i}}; good = expect(r, (uint64_t)q * D.count + i, s); }
+            break;
+        case HCCL_CMD_SCATTER:
+            for (uint32_t r = 0; r < n && good; ++r) for (uint64_t i = 0; i < D.count && good; ++i) { Sym s; s.terms = {{D.root, (uint64_t)r * D.count + i}}; good = expect(r, i, s); }
+            break;
+        case HCCL_CMD_ALLTOALL:
+            for (uint32_t r = 0; r < n && good; ++r)
+                for (uint32_t q = 0; q < n && good; ++q)
+                    for (uint64_t i = 0; i < D.count && good; ++i) { Sym s; s.terms = {{q, (uint64_t)r * D.count + i}}; good = expect(r, (uint64_t)q * D.count + i, s); }
+            break;
+        default: break;   // Broadcast is in place on OUTPUT (no INPUT identity to track); V operators and p2p are checked numerically by the tests
+    }
+}
+
+VerifyReport HostWorld::Verify()
+{
+    VerifyReport rep;
+    std::lock_guard<std::mutex> lk(traceMu_);
+    tracing_.store(false);
+    for (const OpRecord& op : ops_) HostVerifier::CheckOp(*this, op, &rep);
+    ops_.clear();
+    return rep;
+}
+
+}  // namespace hccl

@@ -67,6 +67,7 @@ struct CostCoeff {
 
 struct AlgAttrs {
     uint32_t minLevels = 1, maxLevels = 1;
+    bool enforceMaxLevels = false;           // true: not usable on a topology with more levels than maxLevels
     uint32_t level0Shapes = 0xFFFFFFFFu;     // bitmask over Level0Shape
     uint32_t maxRankSize = 0;                // 0 = unlimited
     uint32_t minRankSize = 1;

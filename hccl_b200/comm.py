@@ -52,12 +52,12 @@ class Communicator:
     def get_root_info() -> bytes:
         info = _lib.HcclRootInfo()
         _check(lib.HcclGetRootInfo(byref(info)), "HcclGetRootInfo")
-        return bytes(info.internal)
+        return ctypes.string_at(ctypes.addressof(info), ctypes.sizeof(info))
 
     @classmethod
     def from_root_info(cls, root_info: bytes, rank: int, world_size: int, config: Optional[_lib.HcclCommConfig] = None):
         info = _lib.HcclRootInfo()
-        ctypes.memmove(info.internal, root_info, len(root_info))
+        ctypes.memmove(ctypes.addressof(info), root_info, min(len(root_info), ctypes.sizeof(info)))
         h = c_void_p()
         if config is None:
             _check(lib.HcclCommInitRootInfo(world_size, byref(info), rank, byref(h)), "HcclCommInitRootInfo")

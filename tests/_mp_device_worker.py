@@ -95,6 +95,58 @@ def scenario_collectives(comm, rank, world):
     assert comm.async_error() == hb.Result.SUCCESS
 
 
+def scenario_mc2(comm, rank, world):
+    from hccl_b200.ops import mc2
+
+    torch.manual_seed(1234)      # every rank builds all operands: the reference is computed locally in fp32
+    for (m_per, n, k) in ((128, 256, 256), (256, 768, 512), (512, 1024, 1024)):
+        shards = [(torch.randn(m_per, k, device="cuda") * 0.5).bfloat16() for _ in range(world)]
+        w = (torch.randn(n, k, device="cuda") * 0.1).bfloat16()          # [N, K]
+        a = comm.empty((m_per, k), torch.bfloat16)
+        a.copy_(shards[rank])
+        for rep in range(3):
+            out, gathered = mc2.all_gather_matmul(comm, a, w)
+            torch.cuda.synchronize()
+            full = torch.cat(shards)
+            assert torch.equal(gathered, full), "gathered activations differ"
+            ref = full.float() @ w.float().t()
+            err = (out.float() - ref).abs().max().item()
+            assert err <= 2e-2 * ref.abs().max().item() + 1e-2, f"AG-matmul err {err}"
+        # matmul -> reduce-scatter: every rank has its own A [M, K] and W [N, K]
+        M = m_per * world
+        As = [(torch.randn(M, k, device="cuda") * 0.5).bfloat16() for _ in range(world)]
+        Ws = [(torch.randn(n, k, device="cuda") * 0.1).bfloat16() for _ in range(world)]
+        ref = sum(A.float() @ W.float().t() for A, W in zip(As, Ws))
+        for rep in range(3):
+            out = mc2.matmul_reduce_scatter(comm, As[rank], Ws[rank])
+            torch.cuda.synchronize()
+            mine = ref[rank * m_per:(rank + 1) * m_per]
+            err = (out.float() - mine).abs().max().item()
+            assert err <= 3e-2 * ref.abs().max().item() + 2e-2, f"matmul-RS err {err}"
+        # [K, N] weights (the backward layouts)
+        Wkn = [W.t().contiguous() for W in Ws]
+        out = mc2.matmul_reduce_scatter(comm, As[rank], Wkn[rank], weight_is_kn=True)
+        torch.cuda.synchronize()
+        err = (out.float() - ref[rank * m_per:(rank + 1) * m_per]).abs().max().item()
+        assert err <= 3e-2 * ref.abs().max().item() + 2e-2, f"matmul-RS (KN) err {err}"
+        if rank == 0:
+            print(f"mc2 ok m_per={m_per} n={n} k={k}", flush=True)
+    # matmul -> all-reduce, decode shapes
+    for M in (16, 64, 256):
+        k, n = 1024, 2048
+        As = [(torch.randn(M, k, device="cuda") * 0.5).bfloat16() for _ in range(world)]
+        Ws = [(torch.randn(n, k, device="cuda") * 0.1).bfloat16() for _ in range(world)]
+        ref = sum(A.float() @ W.float().t() for A, W in zip(As, Ws))
+        for rep in range(4):
+            out = mc2.matmul_all_reduce(comm, As[rank], Ws[rank])
+            torch.cuda.synchronize()
+            err = (out.float() - ref).abs().max().item()
+            assert err <= 3e-2 * ref.abs().max().item() + 2e-2, f"matmul-AR err {err} M={M}"
+        if rank == 0:
+            print(f"mc2 AR ok M={M}", flush=True)
+    assert comm.async_error() == hb.Result.SUCCESS
+
+
 def scenario_peer_exit(comm, rank, world):
     """A rank leaves between steps; the survivors' next collective ends with an
     error within the wait budget instead of hanging."""
@@ -128,7 +180,7 @@ def main():
     info = rendezvous(rank, path)
     timeout_ms = 3000 if scenario == "peer_exit" else 0
     comm = Communicator.from_root_info(info, rank, world, hb.make_config(buffer_mib=64, exec_timeout_ms=timeout_ms))
-    {"collectives": scenario_collectives, "peer_exit": scenario_peer_exit}[scenario](comm, rank, world)
+    {"collectives": scenario_collectives, "peer_exit": scenario_peer_exit, "mc2": scenario_mc2}[scenario](comm, rank, world)
     comm.destroy()
     print(f"rank {rank} done", flush=True)
 
