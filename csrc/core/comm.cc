@@ -445,19 +445,18 @@ HcclResult EmuGroup::Post(int rank, const void* args, size_t argBytes, int nBloc
 HcclResult EmuGroup::MemAlloc(int rank, uint64_t size, SymSegment* seg)
 {
     std::lock_guard<std::mutex> lk(mu_);
-    // Rank r's k-th allocation pairs with every other rank's k-th allocation.  The first caller of
-    // round k allocates all copies so that peer pointers are known at once.
-    if (allocPosted_ == 0) {
-        CHK_RET(SymAllocLocalGroup(nRanks_, size, &pendingAlloc_));
-        allocSize_ = size;
-        allocHave_.assign((size_t)nRanks_, false);
-    } else if (size != allocSize_ || allocHave_[(size_t)rank]) {
-        HCCL_ERROR("HcclMemAlloc: emulated ranks must each call once per allocation, with the same size");
+    // Rank r's k-th allocation pairs with every other rank's k-th allocation, whatever the interleaving of the calls.
+    // The first rank to reach round k allocates all copies, so that peer pointers are known at once.
+    if (allocNext_.empty()) allocNext_.assign((size_t)nRanks_, 0);
+    const size_t k = allocNext_[(size_t)rank]++;
+    if (k == allocRounds_.size()) {
+        allocRounds_.emplace_back();
+        CHK_RET(SymAllocLocalGroup(nRanks_, size, &allocRounds_.back()));
+    } else if (allocRounds_[k][0].size != size) {
+        HCCL_ERROR("HcclMemAlloc: emulated ranks passed different sizes for their allocation number %zu", k);
         return HCCL_E_PARA;
     }
-    allocHave_[(size_t)rank] = true;
-    *seg = pendingAlloc_[(size_t)rank];
-    if (++allocPosted_ == nRanks_) { allocPosted_ = 0; pendingAlloc_.clear(); }
+    *seg = allocRounds_[k][(size_t)rank];
     return HCCL_SUCCESS;
 }
 

@@ -31,6 +31,7 @@ class SelectorState;
 class PlanCache;
 class HostRank;
 struct Mc2State;
+struct MoeState;
 
 // Named blobs owned by the communicator (topology cache, cost model, tuner
 // context, fallback records) - the EngineCtx store of the reference.
@@ -100,6 +101,7 @@ public:
     std::unique_ptr<PlanCache> plans;
     std::unique_ptr<TopoInfo> topo;
     bool firstOpChecked[HCCL_CMD_MAX] = {false};
+    std::shared_ptr<MoeState> moe;  // scratch of the MoE dispatch / combine kernels, created on first use
     std::shared_ptr<Mc2State> mc2;  // resources of the fused matmul kernels, created on first use
     HostRank* hostComm = nullptr;  // non-null: a host-engine communicator (ranks are host threads)
 
@@ -153,10 +155,8 @@ private:
     std::vector<std::deque<PendingPost>> queues_;
     std::vector<DevComm> hostComms_;
     // pending group allocation
-    std::vector<SymSegment> pendingAlloc_;
-    int allocPosted_ = 0;
-    std::vector<bool> allocHave_;
-    uint64_t allocSize_ = 0;
+    std::vector<std::vector<SymSegment>> allocRounds_;
+    std::vector<size_t> allocNext_;
     friend class CommImpl;
     std::vector<SymSegment> slabs_;
     int maxBlocksPerRank_ = 1;

@@ -138,3 +138,10 @@ _sig("HcclMc2Matmul", R, c_void_p, c_void_p, c_void_p, c_uint64, c_uint64, c_uin
 _sig("HcclMc2AllGatherMatmul", R, c_void_p, c_void_p, c_void_p, c_void_p, c_uint64, c_uint64, c_uint64, c_int, c_void_p, c_void_p)
 _sig("HcclMc2MatmulReduceScatter", R, c_void_p, c_void_p, c_void_p, c_uint64, c_uint64, c_uint64, c_int, c_void_p, c_void_p)
 _sig("HcclMc2MatmulAllReduce", R, c_void_p, c_void_p, c_void_p, c_uint64, c_uint64, c_uint64, c_int, c_void_p, c_void_p)
+# MoE
+class HcclMoeConfig(ctypes.Structure):
+    _fields_ = [("nTokens", c_uint32), ("hidden", c_uint32), ("topk", c_uint32), ("nExperts", c_uint32), ("capacity", c_uint32)]
+
+
+_sig("HcclMoeDispatch", R, c_void_p, c_void_p, c_void_p, POINTER(HcclMoeConfig), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p)
+_sig("HcclMoeCombine", R, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(HcclMoeConfig), c_void_p, c_void_p)

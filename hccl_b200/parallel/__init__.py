@@ -1,0 +1,2 @@
+"""Parallelism helpers built on the operators: tensor / sequence parallel layers and the process-group binding."""
+from .tp_layers import ColumnParallelLinear, RowParallelLinear, TPContext  # noqa: F401
