@@ -32,6 +32,12 @@ HcclResult HcclMoeDispatch(HcclComm comm, const void* x, const int32_t* topkIdx,
 HcclResult HcclMoeCombine(HcclComm comm, const void* y, const float* topkWeight, const uint64_t* slotMap, const HcclMoeConfig* cfg, void* out,
                           hcclStream_t stream);
 
+// Local routing helper (no communicator): offsets[e] .. offsets[e + 1] is the row range of expert e when this
+// rank's nPairs (token, expert) pairs are grouped by expert; offsets has nExperts + 1 entries in device memory.
+// Ids outside [0, nExperts) are ignored.  Keeps a small device scratch buffer per GPU (allocated on first use);
+// calls on one GPU must be ordered (same stream) because they share it.
+HcclResult HcclMoeExpertOffsets(const int32_t* topkIdx, uint64_t nPairs, uint32_t nExperts, uint32_t* offsets, hcclStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -218,3 +218,42 @@ HcclResult LaunchMoeDispatch(const LaunchTarget& t, const MoeDispatchArgs& a, in
 HcclResult LaunchMoeCombine(const LaunchTarget& t, const MoeCombineArgs& a, int nBlocks) { return LaunchMoe<CombineBody>(t, a, nBlocks); }
 
 }  // namespace hccl
+
+// ------------------------------------------------------------------ expert offsets (local routing helper)
+#include <map>
+#include <mutex>
+#include "moe_route.cuh"
+#include "hccl/hccl_moe.h"
+
+namespace {
+constexpr uint32_t kOffsetsMaxExperts = 65536;
+// scratch of HcclMoeExpertOffsets: one zero-initialised buffer per device, allocated on first use
+uint32_t* OffsetsScratch()
+{
+    static std::mutex mu;
+    static std::map<int, uint32_t*> perDev;
+    std::lock_guard<std::mutex> lk(mu);
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    auto it = perDev.find(dev);
+    if (it != perDev.end()) return it->second;
+    uint32_t* p = nullptr;
+    if (cudaMalloc(&p, sizeof(uint32_t) * (kOffsetsMaxExperts + 1)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, sizeof(uint32_t) * (kOffsetsMaxExperts + 1));
+    perDev[dev] = p;
+    return p;
+}
+}  // namespace
+
+extern "C" HcclResult HcclMoeExpertOffsets(const int32_t* topkIdx, uint64_t nPairs, uint32_t nExperts, uint32_t* offsets, hcclStream_t stream)
+{
+    using namespace hccl;
+    CHK_PTR_NULL(topkIdx);
+    CHK_PTR_NULL(offsets);
+    if (nExperts == 0 || nExperts > kOffsetsMaxExperts) { HCCL_ERROR("HcclMoeExpertOffsets: 1..%u experts supported (got %u)", kOffsetsMaxExperts, nExperts); return HCCL_E_PARA; }
+    uint32_t* scratch = OffsetsScratch();
+    if (!scratch) return HCCL_E_MEMORY;
+    // calls that share the scratch are serialised by the stream they are issued on; use one stream per device
+    MoeExpertOffsetsKernel<<<MoeExpertOffsetsBlocks(nPairs), 256, 0, (cudaStream_t)stream>>>(topkIdx, nPairs, nExperts, scratch, offsets);
+    return cudaGetLastError() == cudaSuccess ? HCCL_SUCCESS : HCCL_E_RUNTIME;
+}

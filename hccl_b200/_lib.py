@@ -145,3 +145,4 @@ class HcclMoeConfig(ctypes.Structure):
 
 _sig("HcclMoeDispatch", R, c_void_p, c_void_p, c_void_p, POINTER(HcclMoeConfig), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p)
 _sig("HcclMoeCombine", R, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(HcclMoeConfig), c_void_p, c_void_p)
+_sig("HcclMoeExpertOffsets", R, c_void_p, c_uint64, c_uint32, c_void_p, c_void_p)

@@ -65,3 +65,13 @@ def dequantize(x_fp8: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     """Reference dequantisation of block-scaled rows: [rows, hidden] fp8 x [rows, hidden / 128] -> fp32."""
     rows, hidden = x_fp8.shape
     return (x_fp8.float().view(rows, hidden // 128, 128) * scales.view(rows, hidden // 128, 1)).view(rows, hidden)
+
+
+def expert_offsets(topk_idx: torch.Tensor, n_experts: int, stream=None) -> torch.Tensor:
+    """Row range of every expert when this rank's (token, expert) pairs are grouped by expert: int32 [n_experts + 1]."""
+    assert topk_idx.dtype == torch.int32 and topk_idx.is_contiguous()
+    out = torch.empty(n_experts + 1, dtype=torch.int32, device=topk_idx.device)
+    s = stream if stream is not None else torch.cuda.current_stream()
+    _check(lib.HcclMoeExpertOffsets(ctypes.c_void_p(topk_idx.data_ptr()), topk_idx.numel(), n_experts, ctypes.c_void_p(out.data_ptr()),
+                                    ctypes.c_void_p(s.cuda_stream)), "HcclMoeExpertOffsets")
+    return out

@@ -63,3 +63,18 @@ def test_dispatch_combine_emulated(p, tokens, hidden, experts, topk):
     assert comms[0].async_error() == hb.Result.SUCCESS
     for c in comms:
         c.destroy()
+
+
+@pytest.mark.parametrize("tokens,topk,experts", [(1, 1, 4), (777, 8, 256), (8192, 8, 256), (100000, 2, 4096)])
+def test_expert_offsets(tokens, topk, experts):
+    from hccl_b200.ops.moe import expert_offsets
+
+    g = torch.Generator(device="cuda").manual_seed(tokens)
+    idx = torch.randint(-1, experts, (tokens, topk), device="cuda", generator=g, dtype=torch.int32)
+    for _ in range(3):          # repeated calls: the scratch must be clean again after each
+        off = expert_offsets(idx, experts)
+        torch.cuda.synchronize()
+        valid = idx[idx >= 0].long()
+        ref = torch.zeros(experts + 1, dtype=torch.int64, device="cuda")
+        ref[1:] = torch.bincount(valid, minlength=experts).cumsum(0)
+        assert torch.equal(off.long(), ref)
