@@ -1,4 +1,5 @@
 // C entry points for communicator management.
+#include <algorithm>
 #include <cstring>
 #include <fstream>
 #include <sstream>
@@ -10,6 +11,7 @@
 #include "../cpu/host_comm.h"
 #include "../kernels/dev_types.h"
 #include "../ops/op_common.h"
+#include "../ops/param_check.h"
 #include "../ops/profiling.h"
 #include "../select/selector.h"
 #include "hccl/hccl.h"
@@ -213,6 +215,44 @@ HcclResult HcclSelectorExplain(HcclComm comm, HcclCMDType op, uint64_t count, Hc
     std::string s = (sel.alg ? "selected " + sel.alg->name + "\n" : std::string("selected none\n")) + FormatCostTable(sel);
     snprintf(text, cap, "%s", s.c_str());
     return r;
+}
+
+HcclResult HcclCalcOpResource(HcclComm comm, HcclCMDType op, uint64_t count, HcclDataType dt, HcclReduceOp rop, int registered, HcclOpResource* res)
+{
+    CHK_PTR_NULL(comm); CHK_PTR_NULL(res);
+    CommImpl* c = static_cast<CommImpl*>(comm);
+    memset(res, 0, sizeof(*res));
+    res->streams = 1;
+    OpDesc d;
+    d.op = op; d.dtype = dt; d.redOp = rop; d.nRanks = (uint32_t)c->nRanks; d.det = c->cfg.deterministic;
+    d.engine = c->hostComm ? HCCL_ENGINE_HOSTCPU : c->cfg.engine;
+    const uint64_t es = DataTypeSize(dt);
+    if (es == 0) return HCCL_E_PARA;
+    const uint64_t P = (uint64_t)c->nRanks;
+    const bool perRank = op == HCCL_CMD_ALLGATHER || op == HCCL_CMD_REDUCE_SCATTER || op == HCCL_CMD_SCATTER || op == HCCL_CMD_ALLTOALL;
+    d.bytes = count * es * (perRank ? P : 1);
+    d.inRegistered = d.outRegistered = registered != 0;
+    Selection sel;
+    CHK_RET(SelectAlgorithm(*c->selector, *c->topo, GetEnvConfig(), d, c->name, comm, c->cfg.bufferBytes, &sel));
+    snprintf(res->algName, sizeof(res->algName), "%s", sel.alg->name.c_str());
+    res->engine = (uint32_t)sel.alg->engine;
+    if (c->hostComm || c->nRanks == 1) { res->blocks = 0; res->launches = c->nRanks == 1 ? 0 : 1; return HCCL_SUCCESS; }
+    // mirror of the sole executor's loop bound: staged inputs go through the stage-in region, two-shot results through the exchange region
+    const StageLayout& L = c->layout();
+    const bool ll = sel.alg->devAlg == DALG_AR_LL || sel.alg->devAlg == DALG_AG_LL;
+    uint64_t staged = (registered || ll) ? 0 : d.bytes;
+    if (op == HCCL_CMD_ALLGATHER && !registered) staged = d.bytes / P;
+    uint64_t limit = registered ? ~0ull : (perRank && op != HCCL_CMD_ALLGATHER ? L.inBytes / P * P : L.inBytes);
+    if (sel.alg->devAlg == DALG_AR_TWOSHOT || sel.alg->devAlg == DALG_AR_NVLS || sel.alg->devAlg == DALG_BCAST_TWOSHOT || sel.alg->devAlg == DALG_REDUCE_TWOSHOT)
+        limit = std::min<uint64_t>(limit, L.xchBytes);
+    res->launches = (uint32_t)std::max<uint64_t>(1, limit == ~0ull || d.bytes == 0 ? 1 : (d.bytes + limit - 1) / limit);
+    res->scratchBytes = std::min<uint64_t>(staged, limit == ~0ull ? staged : limit);
+    const uint64_t perLaunch = d.bytes / res->launches;
+    uint64_t traffic = perLaunch;
+    if (sel.alg->devAlg == DALG_AR_TWOSHOT || sel.alg->devAlg == DALG_AR_NVLS) traffic = perLaunch / P * 2 + 1;
+    uint64_t nb = ll ? std::min<uint64_t>((perLaunch / (op == HCCL_CMD_ALLGATHER ? P : 1) + 8191) / 8192, 8) : (traffic + (128u << 10) - 1) / (128u << 10);
+    res->blocks = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(nb, (uint64_t)c->MaxBlocks()));
+    return HCCL_SUCCESS;
 }
 
 uint32_t HcclAlgRegistryCount(void)

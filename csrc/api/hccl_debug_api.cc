@@ -1,0 +1,108 @@
+// Text renderings of pure functions (step tables, HCCL_ALGO / environment parsing, cost formula) for unit tests.
+#include <cstring>
+#include <map>
+#include <sstream>
+#include "../algo/step_tables.h"
+#include "../core/config.h"
+#include "../core/log.h"
+#include "../select/selector.h"
+#include "hccl/hccl_ext.h"
+
+using namespace hccl;
+
+namespace {
+template <class V>
+std::string Join(const V& v)
+{
+    std::ostringstream os;
+    bool first = true;
+    for (auto x : v) { os << (first ? "" : ",") << x; first = false; }
+    return os.str();
+}
+}  // namespace
+
+extern "C" {
+
+HcclResult HcclDebugStepTable(const char* kind, uint32_t p, uint32_t rank, const char* arg, char* text, uint32_t cap)
+{
+    CHK_PTR_NULL(kind); CHK_PTR_NULL(text);
+    std::ostringstream os;
+    const std::string k(kind);
+    if (k == "nhr_rs" || k == "nhr_ag") {
+        for (const NhrStep& s : (k == "nhr_rs" ? NhrReduceScatterSteps(p, rank) : NhrAllGatherSteps(p, rank)))
+            os << "step " << s.step << " to " << s.sendTo << " from " << s.recvFrom << " tx [" << Join(s.txSlices) << "] rx [" << Join(s.rxSlices) << "]\n";
+    } else if (k == "rhd_rs" || k == "rhd_ag") {
+        const RhdInfo i = RhdPart1(p, rank);
+        if (!i.merged)
+            for (const RhdStep& s : (k == "rhd_rs" ? RhdReduceScatterSteps(p, i.vrank) : RhdAllGatherSteps(p, i.vrank)))
+                os << "peer " << RhdVirtualToReal(p, s.peerVirtual) << " send [" << s.sendUnitBegin << "," << s.sendUnitEnd << ") keep [" << s.keepUnitBegin << ","
+                   << s.keepUnitEnd << ")\n";
+    } else if (k == "rhd_info") {
+        const RhdInfo i = RhdPart1(p, rank);
+        os << "P " << i.P << " r " << i.r << " steps " << i.steps << " merged " << i.merged << " representative " << i.representative << " partner "
+           << i.partner << " vrank " << i.vrank << " sigma " << RhdSigma(p, rank) << "\n";
+    } else if (k == "ring_rs" || k == "ring_ag") {
+        for (const RingStep& s : (k == "ring_rs" ? RingReduceScatterSteps(p, rank) : RingAllGatherSteps(p, rank))) os << "send " << s.sendSlice << " recv " << s.recvSlice << "\n";
+    } else if (k == "pairwise") {
+        for (const PairwiseStep& s : PairwiseSteps(p, rank)) os << "to " << s.sendTo << " from " << s.recvFrom << "\n";
+    } else if (k == "fold") {
+        for (auto& pr : DeterministicFoldOrder(p)) os << pr.first << "+=" << pr.second << "\n";
+    } else if (k == "parse_algo") {
+        AlgoConfig cfg;
+        std::string err;
+        if (!ParseHcclAlgo(arg ? arg : "", &cfg, &err)) os << "error: " << err << "\n";
+        else {
+            auto dump = [&](const char* name, const AlgoLevelConfig& l) {
+                os << name << ":";
+                for (int i = 0; i < kAlgoLevels; ++i) os << " " << AlgoTypeName(l.level[i]);
+                os << "\n";
+            };
+            dump("global", cfg.global);
+            for (auto& kv : cfg.perOp) dump(("op" + std::to_string((int)kv.first)).c_str(), kv.second);
+        }
+    } else {
+        return HCCL_E_PARA;
+    }
+    snprintf(text, cap, "%s", os.str().c_str());
+    return HCCL_SUCCESS;
+}
+
+HcclResult HcclDebugParseEnv(const char* settings, char* text, uint32_t cap)
+{
+    CHK_PTR_NULL(settings); CHK_PTR_NULL(text);
+    std::map<std::string, std::string> vars;
+    std::istringstream is(settings);
+    std::string line;
+    while (std::getline(is, line)) {
+        size_t eq = line.find('=');
+        if (eq != std::string::npos) vars[line.substr(0, eq)] = line.substr(eq + 1);
+    }
+    EnvConfig c = ParseEnvConfig([&](const char* n) -> const char* {
+        auto it = vars.find(n);
+        return it == vars.end() ? nullptr : it->second.c_str();
+    });
+    EffectiveConfig eff;
+    MergeConfig(c, nullptr, &eff);
+    TimeoutChain tc = DeriveTimeouts(eff.execTimeoutNs);
+    std::ostringstream os;
+    os << "engine=" << (int)c.expansionMode << " planCache=" << c.planCacheEnable << " deterministic=" << (int)c.deterministic << " execTimeoutS=" << c.execTimeoutS
+       << " retryL1=" << c.retryL1 << " retryL2=" << c.retryL2 << " retryMaxCnt=" << c.retryMaxCnt << " stuck=" << c.dfs.stuckDetection << " heartbeat="
+       << c.dfs.clusterHeartbeat << " inconsistent=" << c.dfs.inconsistentCheck << " faultTime=" << c.dfs.connectionFaultDetectionTimeS << " debugMask="
+       << c.debugConfigMask << " entryLog=" << c.entryLog << " bufferMiB=" << c.bufferSizeMiB << " ifIp=" << c.ifIp << " basePort=" << c.ifBasePort
+       << " connectTimeoutS=" << c.connectTimeoutS << " nvls=" << c.nvlsEnable << " maxBlocks=" << c.maxBlocks << " split=" << Join(c.splitRatio)
+       << " algoSpecified=" << c.algo.global.specified << " perOp=" << c.algo.perOp.size() << "\n";
+    os << "effective bufferBytes=" << eff.bufferBytes << " execTimeoutNs=" << eff.execTimeoutNs << " waitNs=" << tc.waitNs << " fullNs=" << tc.fullNs << " kernelNs="
+       << tc.kernelNs << " hostNotifyNs=" << tc.hostNotifyNs << "\n";
+    for (auto& e : c.errors) os << "rejected: " << e << "\n";
+    snprintf(text, cap, "%s", os.str().c_str());
+    return HCCL_SUCCESS;
+}
+
+double HcclDebugEvalCost(double A, double B, double C, double D, int netType, double ratio, double bytes)
+{
+    CostCoeff c;
+    c.A = A; c.B = B; c.C = C; c.D = D; c.net = (NetType)netType; c.ratio = ratio;
+    return EvalCost({c}, CostAgg::SUM, bytes, HCCL_ENGINE_P2P);
+}
+
+}  // extern "C"

@@ -50,6 +50,30 @@ HcclResult HcclGetPlanCacheStats(HcclComm comm, uint64_t* hits, uint64_t* misses
 // Overrides entries of the link model the cost model uses (GB/s and microseconds); negative = keep.
 HcclResult HcclSetLinkModel(double p2pGBs, double nvlsGBs, double localCopyGBs, double launchUs, double barrierUs,
                             double llHopUs);
+// Resource query for graph builders (the role of HCCL's HcclCalcOpRes*GraphMode, calc_resource_graph_mode.cc:51-633:
+// scratch size, stream count, task count, core count per op before it runs): which algorithm a call would use, how
+// many thread blocks it launches, how many bytes of the communicator's staging slab it touches per loop and how many
+// loops (kernel launches) the sole executor needs.  Ops of this library never use extra streams.
+typedef struct {
+    char algName[128];
+    uint32_t engine;        // HcclCommEngine
+    uint32_t blocks;        // thread blocks per launch
+    uint32_t launches;      // kernel launches for this call (loops over the staging slab)
+    uint32_t streams;       // always 1: the caller's stream
+    uint64_t scratchBytes;  // bytes of the staging slab used per launch (0 with symmetric buffers)
+} HcclOpResource;
+HcclResult HcclCalcOpResource(HcclComm comm, HcclCMDType op, uint64_t count, HcclDataType dataType, HcclReduceOp reduceOp, int registered,
+                              HcclOpResource* res);
+
+// Unit-test access to pure functions.  Each writes a text rendering into `text`.
+//   kind "nhr_rs" / "nhr_ag" / "rhd_rs" / "rhd_ag" / "ring_rs" / "ring_ag" / "pairwise" / "fold": step table of `rank` among `p`
+//   kind "parse_algo": parses `arg` as an HCCL_ALGO value;  kind "rhd_info": pairing of `rank`
+HcclResult HcclDebugStepTable(const char* kind, uint32_t p, uint32_t rank, const char* arg, char* text, uint32_t capacity);
+// Parses the environment-style settings given as "NAME=value\nNAME=value" and renders the resulting configuration
+// (and the list of rejected variables) as text, without touching the process environment.
+HcclResult HcclDebugParseEnv(const char* settings, char* text, uint32_t capacity);
+// Evaluates the cost formula for one segment: (A / util(net, bytes * ratio) + B) * bytes + C, floored by D.
+double HcclDebugEvalCost(double A, double B, double C, double D, int netType, double ratio, double bytes);
 // Re-reads the HCCL_* environment variables (they are parsed once per process otherwise).  Existing communicators
 // keep the plans they already cached.
 HcclResult HcclReloadEnvConfig(void);

@@ -1,0 +1,318 @@
+// Two-SM variant of the MC2 matmul pipeline: a cluster of two CTAs works on one
+// 256 x 256 output tile with tcgen05.mma.cta_group::2.
+//
+// Each CTA of the pair loads its own 128 rows of A and its own 128 of the 256
+// B rows (N split), so a k-block costs 32 KiB of shared memory per CTA instead
+// of 48 KiB: a third less L2 -> SM traffic per FLOP and six pipeline stages in
+// the same shared memory.  The leader CTA (cluster rank 0) issues the MMAs;
+// they read both CTAs' shared memory and write 128 accumulator rows into each
+// CTA's TMEM.  Hand-over:
+//   full[stage]    lives in the leader; BOTH producers' TMA loads complete on
+//                  it (cp.async.bulk.tensor ... cta_group::2 with the barrier
+//                  address of cluster rank 0; no multicast anywhere)
+//   empty[stage]   one per CTA; tcgen05.commit.cta_group::2 with the commit
+//                  multicast mask 0b11 arrives on both
+//   tmemFull[acc]  one per CTA, same multicast commit
+//   tmemEmpty[acc] lives in the leader, 8 arrivals: the four epilogue warps of
+//                  each CTA (the follower arrives through the cluster window)
+// Epilogues, tile orders, worker CTAs and flag protocols are those of the
+// one-SM kernel (mc2_gemm.cuh); a CTA of the pair simply owns its 128-row half.
+#pragma once
+#include "mc2_gemm.cuh"
+
+namespace hccl {
+namespace mc2 {
+
+constexpr int kStages2 = 6;
+constexpr int kBN2 = 256;
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;     // clears the cluster-rank bit of a shared::cluster address: rank 0's copy
+
+struct SmemLayout2 {
+    static constexpr int kABytes = kBM * kBK * 2;            // 16 KiB: this CTA's 128 rows of A
+    static constexpr int kBBytes = (kBN2 / 2) * kBK * 2;     // 16 KiB: this CTA's 128 of the 256 B rows
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kTileBytes = kStages2 * kStageBytes;   // 192 KiB
+    static constexpr int kTotal = kTileBytes + 256 + 1024;
+};
+
+__device__ __forceinline__ uint32_t ClusterCtaRank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void ClusterSync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void TmaLoad2D2Sm(void* smemDst, const CUtensorMap* map, uint32_t leaderBarAddr, int x, int y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+            SmemAddr(smemDst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(leaderBarAddr), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void UmmaF16_2Sm(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmemD),
+        "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on the barrier at the same offset in both CTAs once all MMAs issued so far have completed.
+__device__ __forceinline__ void UmmaCommit2Sm(uint64_t* bar)
+{
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(SmemAddr(bar)),
+                 "h"(mask)
+                 : "memory");
+}
+__device__ __forceinline__ void MbarArriveCluster(uint32_t clusterAddr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterAddr) : "memory");
+}
+__device__ __forceinline__ void TmemAlloc2(uint32_t* smemResult, uint32_t nCols)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(smemResult)), "r"(nCols) : "memory");
+}
+__device__ __forceinline__ void TmemRelinquish2() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void TmemDealloc2(uint32_t taddr, uint32_t nCols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(nCols) : "memory");
+}
+
+// Pair tile index -> (256-row tile, 256-column tile), same orders as TileCoord but in units of 256 rows.
+template <int MODE>
+__device__ __forceinline__ void TileCoord2(const GemmArgs& g, int t, int tilesM2, int* mt2, int* nt)
+{
+    if (MODE == MODE_AG) {
+        const int rowTiles = g.mPerRank / 256;
+        const int tilesPerRank = rowTiles * g.tilesN;
+        const int step = t / tilesPerRank, rem = t % tilesPerRank;
+        const int src = (g.rank + step) % g.nRanks;
+        *mt2 = src * rowTiles + rem / g.tilesN;
+        *nt = rem % g.tilesN;
+    } else if (MODE == MODE_RS) {
+        const int rowTiles = g.mPerRank / 256;
+        const int n = t / tilesM2, rem = t % tilesM2;
+        const int step = rem / rowTiles;
+        const int dstRank = (g.rank + 1 + step) % g.nRanks;
+        *mt2 = dstRank * rowTiles + rem % rowTiles;
+        *nt = n;
+    } else {
+        // column-major walk over row tiles inside a band of 8 column tiles keeps the B tiles of a wave L2-resident
+        *mt2 = t % tilesM2;
+        *nt = t / tilesM2;
+    }
+}
+
+template <bool A_MN, bool B_MN, int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+    GemmKernel2Sm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs g, const DevComm c)
+{
+    using L = SmemLayout2;
+    extern __shared__ uint8_t smemRaw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kTileBytes);
+    uint64_t* fullBar = bars;                       // [kStages2]  (used in the leader)
+    uint64_t* emptyBar = bars + kStages2;           // [kStages2]
+    uint64_t* tmemFull = bars + 2 * kStages2;       // [2]
+    uint64_t* tmemEmpty = bars + 2 * kStages2 + 2;  // [2]       (used in the leader)
+    uint32_t* tmemBaseSlot = reinterpret_cast<uint32_t*>(bars + 2 * kStages2 + 4);
+    volatile uint32_t* abortWord = g.ctl + kCtlAbort;
+
+    const int warp = threadIdx.x / 32;
+    const int cta = (int)blockIdx.x;
+    const uint32_t crank = ClusterCtaRank();
+    const uint32_t launchEpoch = *reinterpret_cast<volatile uint32_t*>(g.ctl + kCtlEpoch) + 1;
+
+    if (cta >= g.nGemmCtas) {
+        const int worker = cta - g.nGemmCtas, nWorkers = (int)gridDim.x - g.nGemmCtas;
+        if (MODE == MODE_AG) GatherWorker(c, g, worker, nWorkers, smem, bars);
+        if (MODE == MODE_RS) ReduceWorker<kBN2>(c, g, worker, nWorkers, (uint64_t)launchEpoch);
+    } else {
+        constexpr uint32_t kTmemCols = 2 * kBN2;
+        if (threadIdx.x == 0) {
+            for (int s = 0; s < kStages2; ++s) { MbarInit(&fullBar[s], 1); MbarInit(&emptyBar[s], 1); }
+            for (int a = 0; a < 2; ++a) { MbarInit(&tmemFull[a], 1); MbarInit(&tmemEmpty[a], 2 * (kEpilogueThreads / 32)); }
+            MbarInitFence();
+            PrefetchTensorMap(&tmA);
+            PrefetchTensorMap(&tmB);
+        }
+        if (warp == 1) {
+            TmemAlloc2(tmemBaseSlot, kTmemCols);
+            TmemRelinquish2();
+        }
+        TcFenceBefore();
+        __syncthreads();
+        ClusterSync();               // the peer's barriers exist before anything arrives on them
+        TcFenceAfter();
+        const uint32_t tmemBase = *tmemBaseSlot;
+        const int pair = cta >> 1, nPairs = g.nGemmCtas >> 1;
+        const int tilesM2 = (g.M + 255) / 256;
+        const int nTiles = tilesM2 * g.tilesN;
+        const int kBlocks = (g.K + kBK - 1) / kBK;
+
+        if (warp == 0) {
+            // ===== TMA producer (both CTAs): own 128 rows of A, own 128 rows of B, completion on the LEADER's full barrier
+            if (ElectOne()) {
+                int stage = 0;
+                uint32_t phase = 0;
+                bool ok = true;
+                for (int t = pair; t < nTiles && ok; t += nPairs) {
+                    int mt2, nt;
+                    TileCoord2<MODE>(g, t, tilesM2, &mt2, &nt);
+                    const int mt = mt2 * 2 + (int)crank;           // this CTA's 128-row tile
+                    if (MODE == MODE_AG) {
+                        const int nWorkers = (int)gridDim.x - g.nGemmCtas;
+                        ok = SpinUntilGE(g.ctl + kCtlReady + mt, (uint32_t)nWorkers, abortWord);
+                        FenceProxyAsync();
+                        if (!ok) break;
+                    }
+                    for (int kb = 0; kb < kBlocks; ++kb) {
+                        ok = MbarWait(&emptyBar[stage], phase ^ 1u, abortWord, kWaitLimitNs);
+                        if (!ok) break;
+                        uint8_t* sa = smem + stage * L::kStageBytes;
+                        uint8_t* sb = sa + L::kABytes;
+                        const uint32_t leaderFull = SmemAddr(&fullBar[stage]) & kPeerBitMask;
+                        if (crank == 0) MbarExpectTx(&fullBar[stage], 2 * L::kStageBytes);
+                        if (!A_MN) {
+                            TmaLoad2D2Sm(sa, &tmA, leaderFull, kb * kBK, mt * kBM);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < kBM / 64; ++j) TmaLoad2D2Sm(sa + j * (64 * kBK * 2), &tmA, leaderFull, mt * kBM + j * 64, kb * kBK);
+                        }
+                        const int nRow = nt * kBN2 + (int)crank * (kBN2 / 2);
+                        if (!B_MN) {
+                            TmaLoad2D2Sm(sb, &tmB, leaderFull, kb * kBK, nRow);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < (kBN2 / 2) / 64; ++j) TmaLoad2D2Sm(sb + j * (64 * kBK * 2), &tmB, leaderFull, nRow + j * 64, kb * kBK);
+                        }
+                        if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+                    }
+                }
+                if (!ok) {
+                    const uint64_t t0 = TimerNs();
+                    while (TimerNs() - t0 < 200000) {}
+                }
+            }
+        } else if (warp == 1) {
+            // ===== MMA issuer: leader CTA only
+            if (crank == 0 && ElectOne()) {
+                constexpr uint32_t idesc = InstrDescF16(256, kBN2, true, A_MN, B_MN);
+                int stage = 0;
+                uint32_t phase = 0;
+                int acc = 0;
+                uint32_t accPhase = 0;
+                bool ok = true;
+                for (int t = pair; t < nTiles && ok; t += nPairs) {
+                    ok = MbarWait(&tmemEmpty[acc], accPhase ^ 1u, abortWord, kWaitLimitNs);
+                    if (!ok) break;
+                    TcFenceAfter();
+                    const uint32_t tmemD = tmemBase + (uint32_t)(acc * kBN2);
+                    for (int kb = 0; kb < kBlocks; ++kb) {
+                        ok = MbarWait(&fullBar[stage], phase, abortWord, kWaitLimitNs);
+                        if (!ok) break;
+                        TcFenceAfter();
+                        const uint32_t sa = SmemAddr(smem + stage * L::kStageBytes);
+                        const uint32_t sb = sa + L::kABytes;
+                        const uint64_t da = A_MN ? SmemDescMnMajor(sa, 64 * kBK * 2) : SmemDescKMajor(sa);
+                        const uint64_t db = B_MN ? SmemDescMnMajor(sb, 64 * kBK * 2) : SmemDescKMajor(sb);
+#pragma unroll
+                        for (int k = 0; k < kBK / kUmmaK; ++k) {
+                            const uint64_t aStep = (uint64_t)((A_MN ? kUmmaK * 128 : kUmmaK * 2) >> 4) * k;
+                            const uint64_t bStep = (uint64_t)((B_MN ? kUmmaK * 128 : kUmmaK * 2) >> 4) * k;
+                            UmmaF16_2Sm(tmemD, da + aStep, db + bStep, idesc, (kb | k) != 0 ? 1u : 0u);
+                        }
+                        UmmaCommit2Sm(&emptyBar[stage]);
+                        if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+                    }
+                    if (!ok) break;
+                    UmmaCommit2Sm(&tmemFull[acc]);
+                    if (++acc == 2) { acc = 0; accPhase ^= 1u; }
+                }
+            }
+        } else {
+            // ===== epilogue warps 2..5 of both CTAs: each CTA drains its own 128 accumulator rows
+            const int quarter = warp & 3;
+            const int lane = threadIdx.x & 31;
+            int acc = 0;
+            uint32_t accPhase = 0;
+            bool ok = true;
+            const size_t parityOff = (launchEpoch & 1u) * g.xchgParityElems;
+            for (int t = pair; t < nTiles && ok; t += nPairs) {
+                int mt2, nt;
+                TileCoord2<MODE>(g, t, tilesM2, &mt2, &nt);
+                const int mt = mt2 * 2 + (int)crank;
+                ok = MbarWait(&tmemFull[acc], accPhase, abortWord, kWaitLimitNs);
+                if (!ok) break;
+                TcFenceAfter();
+                const int row = mt * kBM + quarter * 32 + lane;
+                const uint32_t taddr = tmemBase + (uint32_t)(acc * kBN2) + ((uint32_t)(quarter * 32) << 16);
+                __nv_bfloat16* rowPtr = nullptr;
+                bool rowValid = row < g.M;
+                if (MODE == MODE_RS) {
+                    const int dst = row / g.mPerRank;
+                    rowValid = rowValid && dst < g.nRanks;
+                    if (rowValid) rowPtr = g.xchg[dst] + parityOff + (size_t)g.rank * g.mPerRank * g.N + (size_t)(row - dst * g.mPerRank) * g.N;
+                } else {
+                    rowPtr = g.out + (size_t)row * g.ldc;
+                }
+#pragma unroll 1
+                for (int c0 = 0; c0 < kBN2; c0 += 32) {
+                    uint32_t v[32];
+                    TmemLd32x32(taddr + (uint32_t)c0, v);
+                    TmemLdWait();
+                    const int col = nt * kBN2 + c0;
+                    const int valid = g.N - col;
+                    if (!rowValid || valid <= 0) continue;
+                    Store32Cols(rowPtr + col, v, valid);
+                }
+                TcFenceBefore();
+                __syncwarp();
+                if (lane == 0) MbarArriveCluster(SmemAddr(&tmemEmpty[acc]) & kPeerBitMask);     // the leader's barrier
+                if (++acc == 2) { acc = 0; accPhase ^= 1u; }
+                if (MODE == MODE_RS) {
+                    __threadfence_system();
+                    NamedBarSync(1, kEpilogueThreads);
+                    if (threadIdx.x == 64 && mt * kBM < g.M) {
+                        const int dst = (mt * kBM) / g.mPerRank;
+                        const int tileId = (mt % (g.mPerRank / kBM)) * g.tilesN + nt;
+                        __threadfence_system();
+                        StReleaseSys(g.tileFlag[dst] + (size_t)g.rank * g.maxTiles + tileId, (uint64_t)launchEpoch);
+                    }
+                }
+            }
+        }
+        // teardown: nobody leaves while its peer may still touch its shared memory, barriers or TMEM
+        TcFenceBefore();
+        __syncthreads();
+        ClusterSync();
+        if (warp == 1) {
+            TcFenceAfter();
+            TmemDealloc2(tmemBase, kTmemCols);
+        }
+    }
+
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const uint32_t ticket = atomicAdd(g.ctl + kCtlTicket, 1u);
+        if (ticket == gridDim.x - 1) {
+            if (MODE == MODE_AG) {
+                const int n = g.nRanks * (g.mPerRank / kBM);
+                for (int i = 0; i < n; ++i) g.ctl[kCtlReady + i] = 0;
+            }
+            g.ctl[kCtlTicket] = 0;
+            *reinterpret_cast<volatile uint32_t*>(g.ctl + kCtlEpoch) = launchEpoch;
+            __threadfence();
+        }
+    }
+}
+
+}  // namespace mc2
+}  // namespace hccl

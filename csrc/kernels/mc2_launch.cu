@@ -5,7 +5,7 @@
 #include "../core/comm.h"
 #include "../core/cuda_driver.h"
 #include "../core/log.h"
-#include "mc2_gemm.cuh"
+#include "mc2_gemm_2sm.cuh"
 
 namespace hccl {
 
@@ -87,6 +87,57 @@ HcclResult LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmAr
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { HCCL_ERROR("matmul launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
     return HCCL_SUCCESS;
+}
+
+template <bool A_MN, bool B_MN, int MODE>
+HcclResult LaunchGemm2Sm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const DevComm& c, int grid, bool cooperative,
+                         cudaStream_t stream)
+{
+    auto kernel = GemmKernel2Sm<A_MN, B_MN, MODE>;
+    static bool attrSet = false;
+    if (!attrSet) {
+        CHK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout2::kTotal));
+        attrSet = true;
+    }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = SmemLayout2::kTotal;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeCooperative;
+    attrs[0].val.cooperative = cooperative ? 1 : 0;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, g, c);
+    if (e != cudaSuccess) { HCCL_ERROR("two-SM matmul launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
+    return HCCL_SUCCESS;
+}
+
+template <int MODE>
+HcclResult DispatchLayout2Sm(bool aMn, bool bMn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const DevComm& c, int grid,
+                             bool coop, cudaStream_t s)
+{
+    if (!aMn && !bMn) return LaunchGemm2Sm<false, false, MODE>(ta, tb, g, c, grid, coop, s);
+    if (!aMn && bMn) return LaunchGemm2Sm<false, true, MODE>(ta, tb, g, c, grid, coop, s);
+    if (MODE == MODE_PLAIN) {
+        if (aMn && !bMn) return LaunchGemm2Sm<true, false, MODE_PLAIN>(ta, tb, g, c, grid, coop, s);
+        return LaunchGemm2Sm<true, true, MODE_PLAIN>(ta, tb, g, c, grid, coop, s);
+    }
+    HCCL_ERROR("fused matmul kernels take A in row-major [M, K] form only");
+    return HCCL_E_NOT_SUPPORT;
+}
+
+// HCCL_MC2_2SM=1 selects the two-SM (cta_group::2) kernels for tiles of 256 x 256; the one-SM kernels are the default.
+bool Use2Sm()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("HCCL_MC2_2SM");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
 }
 
 template <int BN, int MODE>
@@ -192,6 +243,14 @@ HcclResult Mc2Matmul(const void* a, const void* b, void* out, uint64_t m, uint64
     g.nGemmCtas = grid;
     DevComm dummy;
     memset(&dummy, 0, sizeof(dummy));
+    if (bn == 256 && Use2Sm() && m >= 256) {
+        // B is split between the two CTAs of a pair: each loads 128 of the 256 B rows of a tile
+        CHK_RET(MapB(&tb, b, n, k, bMn, 128));
+        const int pairsWanted = (int)((m + 255) / 256) * g.tilesN;
+        const int grid2 = std::min(SmCount() & ~1, 2 * pairsWanted);
+        g.nGemmCtas = grid2;
+        return DispatchLayout2Sm<MODE_PLAIN>(aMn, bMn, ta, tb, g, dummy, grid2, false, stream);
+    }
     if (bn == 128) return DispatchLayout<128, MODE_PLAIN>(aMn, bMn, ta, tb, g, dummy, grid, false, stream);
     return DispatchLayout<256, MODE_PLAIN>(aMn, bMn, ta, tb, g, dummy, grid, false, stream);
 }
@@ -222,9 +281,13 @@ HcclResult Mc2AllGatherMatmul(CommImpl* comm, const void* aShard, const void* b,
     g.mPerRank = (int)mPerRank;
     for (int q = 0; q < comm->nRanks; ++q) g.aPeer[q] = (const __nv_bfloat16*)peers[q];
     g.gathered = (__nv_bfloat16*)gathered;
-    const int workers = std::min(16, std::max(2, SmCount() / 9));
-    const int grid = SmCount();
+    const int workers = std::min(16, std::max(2, SmCount() / 9)) & ~1;
+    const int grid = SmCount() & ~1;
     g.nGemmCtas = grid - workers;
+    if (Use2Sm() && mPerRank % 256 == 0) {
+        CHK_RET(MapB(&tb, b, n, k, bMn, 128));
+        return DispatchLayout2Sm<MODE_AG>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream);
+    }
     return DispatchLayout<256, MODE_AG>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream);
 }
 
@@ -252,9 +315,13 @@ HcclResult Mc2MatmulReduceScatter(CommImpl* comm, const void* a, const void* b, 
     g.tilesM = (int)(m / kBM);
     g.tilesN = (int)tilesN;
     g.mPerRank = (int)mPerRank;
-    const int workers = std::min(16, std::max(2, SmCount() / 9));
-    const int grid = SmCount();
+    const int workers = std::min(16, std::max(2, SmCount() / 9)) & ~1;
+    const int grid = SmCount() & ~1;
     g.nGemmCtas = grid - workers;
+    if (Use2Sm() && mPerRank % 256 == 0) {
+        CHK_RET(MapB(&tb, b, n, k, bMn, 128));
+        return DispatchLayout2Sm<MODE_RS>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream);
+    }
     return DispatchLayout<256, MODE_RS>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream);
 }
 

@@ -146,3 +146,14 @@ class HcclMoeConfig(ctypes.Structure):
 _sig("HcclMoeDispatch", R, c_void_p, c_void_p, c_void_p, POINTER(HcclMoeConfig), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p)
 _sig("HcclMoeCombine", R, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(HcclMoeConfig), c_void_p, c_void_p)
 _sig("HcclMoeExpertOffsets", R, c_void_p, c_uint64, c_uint32, c_void_p, c_void_p)
+_sig("HcclDebugStepTable", R, c_char_p, c_uint32, c_uint32, c_char_p, c_char_p, c_uint32)
+_sig("HcclDebugParseEnv", R, c_char_p, c_char_p, c_uint32)
+_sig("HcclDebugEvalCost", c_double, c_double, c_double, c_double, c_double, c_int, c_double, c_double)
+
+
+class HcclOpResource(ctypes.Structure):
+    _fields_ = [("algName", ctypes.c_char * 128), ("engine", c_uint32), ("blocks", c_uint32), ("launches", c_uint32), ("streams", c_uint32),
+                ("scratchBytes", c_uint64)]
+
+
+_sig("HcclCalcOpResource", R, c_void_p, c_int, c_uint64, c_int, c_int, c_int, POINTER(HcclOpResource))

@@ -1,3 +1,3 @@
 """Operators on tensors: MC2 fused matmul + collective, MoE dispatch / combine and the
 torch.distributed-style functional collectives."""
-from . import mc2, moe  # noqa: F401
+from . import functional, mc2, moe  # noqa: F401

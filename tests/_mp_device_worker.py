@@ -147,6 +147,40 @@ def scenario_mc2(comm, rank, world):
     assert comm.async_error() == hb.Result.SUCCESS
 
 
+def scenario_graph(comm, rank, world):
+    """Collectives captured into a CUDA graph and replayed: the epochs live in device memory, so a replay
+    synchronises like a fresh launch."""
+    n = 1 << 16
+    x = comm.empty((n,), torch.float32)
+    y = comm.empty((n,), torch.float32)
+    small = torch.ones(64, device="cuda")
+    x.fill_(float(rank + 1))
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        comm.all_reduce(x, y)              # warm-up outside capture (first-call checks, plan cache)
+        comm.all_reduce(small)
+        torch.cuda.synchronize()
+        small.fill_(1.0)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            comm.all_reduce(x, y)          # two-shot / one-shot path on symmetric buffers
+            comm.all_reduce(small)         # LL path
+            comm.barrier()
+    want = world * (world + 1) / 2
+    acc = 1.0
+    for it in range(6):
+        y.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        acc *= world
+        assert float(y[0]) == want and float(y[-1]) == want, (it, float(y[0]))
+        assert float(small[0]) == acc, (it, float(small[0]), acc)
+    assert comm.async_error() == hb.Result.SUCCESS
+    if rank == 0:
+        print("graph replay ok", flush=True)
+
+
 def scenario_peer_exit(comm, rank, world):
     """A rank leaves between steps; the survivors' next collective ends with an
     error within the wait budget instead of hanging."""
@@ -180,7 +214,7 @@ def main():
     info = rendezvous(rank, path)
     timeout_ms = 3000 if scenario == "peer_exit" else 0
     comm = Communicator.from_root_info(info, rank, world, hb.make_config(buffer_mib=64, exec_timeout_ms=timeout_ms))
-    {"collectives": scenario_collectives, "peer_exit": scenario_peer_exit, "mc2": scenario_mc2}[scenario](comm, rank, world)
+    {"collectives": scenario_collectives, "peer_exit": scenario_peer_exit, "mc2": scenario_mc2, "graph": scenario_graph}[scenario](comm, rank, world)
     comm.destroy()
     print(f"rank {rank} done", flush=True)
 

@@ -59,3 +59,9 @@ def test_peer_exit_is_detected():
 def test_mc2_fused_multiprocess():
     codes, outs = _run(_world(), "mc2")
     assert all(c == 0 for c in codes), "\n".join(outs)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_cuda_graph_capture_and_replay():
+    codes, outs = _run(_world(), "graph")
+    assert all(c == 0 for c in codes), "\n".join(outs)

@@ -1,0 +1,258 @@
+"""Unit tier: step tables against hand-derived vectors, HCCL_ALGO grammar, environment parsing, parameter checks,
+registry / selector behaviour (cost formula, HCCL_ALGO preference, determinism filter, tuner plugin)."""
+import ctypes
+import os
+import subprocess
+import textwrap
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import hccl_b200 as hb
+from hccl_b200 import Cmd, Communicator, DataType, ReduceOp
+from hccl_b200._lib import lib
+
+
+def table(kind, p, rank, arg=None):
+    buf = ctypes.create_string_buffer(1 << 16)
+    assert lib.HcclDebugStepTable(kind.encode(), p, rank, arg.encode() if arg else None, buf, 1 << 16) == 0
+    return buf.value.decode()
+
+
+def parse_env(**kv):
+    buf = ctypes.create_string_buffer(1 << 14)
+    lib.HcclDebugParseEnv("\n".join(f"{k}={v}" for k, v in kv.items()).encode(), buf, 1 << 14)
+    return buf.value.decode()
+
+
+# ---------------------------------------------------------------- step tables
+def test_nhr_vectors():
+    # p = 5, rank 0: 3 steps; step 0 sends slices {4, 2, 0->...} per the rule nSlices = (p - 1 + 2^s) / 2^(s+1)
+    t = table("nhr_rs", 5, 0).splitlines()
+    assert t[0] == "step 0 to 4 from 1 tx [4,2] rx [0,3]"
+    assert t[1] == "step 1 to 3 from 2 tx [3] rx [0]"
+    assert t[2] == "step 2 to 1 from 4 tx [1] rx [0]"
+    t = table("nhr_ag", 5, 0).splitlines()
+    assert t[0] == "step 0 to 4 from 1 tx [0] rx [1]"
+    assert t[2] == "step 2 to 1 from 4 tx [0,3] rx [4,2]"
+    # power of two: p = 8 has 3 steps with 4, 2, 1 slices
+    t = table("nhr_rs", 8, 3).splitlines()
+    assert [len(l.split("tx [")[1].split("]")[0].split(",")) for l in t] == [4, 2, 1]
+
+
+@pytest.mark.parametrize("p", list(range(1, 18)))
+def test_nhr_reduce_scatter_delivers_every_contribution_once(p):
+    # simulate: have[r][slice] = set of contributors; after the steps rank r must hold all p contributions of slice r
+    have = [[{r} for _ in range(p)] for r in range(p)]
+    steps = [[l for l in table("nhr_rs", p, r).splitlines()] for r in range(p)]
+    n = len(steps[0]) if p > 1 else 0
+    for s in range(n):
+        moves = []
+        for r in range(p):
+            parts = steps[r][s].split()
+            to = int(parts[3])
+            tx = [int(x) for x in steps[r][s].split("tx [")[1].split("]")[0].split(",")]
+            moves.append((r, to, tx))
+        snap = [[set(x) for x in row] for row in have]
+        for r, to, tx in moves:
+            for sl in tx:
+                assert not (have[to][sl] & snap[r][sl]), "contribution delivered twice"
+                have[to][sl] |= snap[r][sl]
+    for r in range(p):
+        assert have[r][r] == set(range(p))
+
+
+def test_rhd_pairing_and_units():
+    # p = 6: P = 4, r = 2; ranks 0,1 represent 2,3; ranks 4,5 are virtual 2,3
+    assert "P 4 r 2 steps 2 merged 0 representative 1 partner 2 vrank 0 sigma 0" in table("rhd_info", 6, 0)
+    assert "merged 1 representative 0 partner 1 vrank 1 sigma 3" in table("rhd_info", 6, 3)
+    assert "merged 0 representative 0" in table("rhd_info", 6, 5) and "vrank 3 sigma 5" in table("rhd_info", 6, 5)
+    # virtual rank 0 of p = 6, step 0: dist 2, peer virtual 2 (= real 4); sends units of virtual [2, 4) = [4, 6), keeps [0, 4)
+    t = table("rhd_rs", 6, 0).splitlines()
+    assert t[0] == "peer 4 send [4,6) keep [0,4)"
+    assert t[1] == "peer 1 send [2,4) keep [0,2)"
+    t = table("rhd_ag", 6, 0).splitlines()
+    assert t[0] == "peer 1 send [0,2) keep [2,4)"
+    assert t[1] == "peer 4 send [0,4) keep [4,6)"
+    assert table("rhd_rs", 6, 2) == ""          # merged rank sits out the main phase
+
+
+def test_ring_pairwise_fold_vectors():
+    assert table("ring_rs", 4, 1).splitlines() == ["send 0 recv 3", "send 3 recv 2", "send 2 recv 1"]
+    assert table("ring_ag", 4, 1).splitlines() == ["send 1 recv 0", "send 0 recv 3", "send 3 recv 2"]
+    assert table("pairwise", 4, 1).splitlines() == ["to 2 from 0", "to 3 from 3", "to 0 from 2"]
+    # 7 slots: M = 4: 0+=4 1+=5 2+=6; then 4 -> 2: 0+=2 1+=3; then 0+=1
+    assert table("fold", 7, 0).splitlines() == ["0+=4", "1+=5", "2+=6", "0+=2", "1+=3", "0+=1"]
+    assert table("fold", 8, 0).splitlines() == ["0+=4", "1+=5", "2+=6", "3+=7", "0+=2", "1+=3", "0+=1"]
+
+
+# ---------------------------------------------------------------- grammar / environment
+def test_hccl_algo_grammar():
+    assert table("parse_algo", 0, 0, "level0:NA;level1:ring").splitlines()[0] == "global: NA ring default"
+    out = table("parse_algo", 0, 0, "allreduce=level0:NA;level1:H-D_R/alltoall=level1:pairwise")
+    assert "op2: NA H-D_R default" in out and "op10: default pairwise default" in out and "op8: default pairwise default" in out
+    assert table("parse_algo", 0, 0, "level1:bogus").startswith("error: unknown algorithm")
+    assert table("parse_algo", 0, 0, "level7:ring").startswith("error: unknown level")
+    assert table("parse_algo", 0, 0, "allreduce=level1:ring/level1:NHR").startswith("error: global and per-operator")
+    assert table("parse_algo", 0, 0, "level1:ring;level1:NHR").startswith("error: level given twice")
+    assert table("parse_algo", 0, 0, "frobnicate=level1:ring").startswith("error: unknown operator")
+
+
+def test_env_parsing_and_defaults():
+    d = parse_env()
+    assert "deterministic=0" in d and "bufferMiB=0" in d and "effective bufferBytes=268435456" in d and "execTimeoutNs=30000000000" in d
+    # timeout chain: wait = exec, full = +20 s, kernel = +30 s, host notify = +50 s
+    assert "waitNs=30000000000 fullNs=50000000000 kernelNs=60000000000 hostNotifyNs=80000000000" in d
+    e = parse_env(HCCL_DETERMINISTIC="strict", HCCL_BUFFSIZE="512", HCCL_EXEC_TIMEOUT="7", HCCL_OP_EXPANSION_MODE="AIV_CacheDisable",
+                  HCCL_OP_RETRY_ENABLE="L1:1,L2:0", HCCL_DFS_CONFIG="stuck_detection:off,connection_fault_detection_time:45",
+                  HCCL_DEBUG_CONFIG="ALG,RESOURCE", HCCL_ENTRY_LOG_ENABLE="1", HCCL_NVLS_ENABLE="0", HCCL_MAX_BLOCKS="16",
+                  HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO="0.25,0.75", HCCL_IF_IP="10.0.0.1", HCCL_IF_BASE_PORT="61000")
+    for frag in ("deterministic=2", "bufferMiB=512", "execTimeoutS=7", "engine=1 planCache=0", "retryL1=1 retryL2=0", "stuck=0", "faultTime=45",
+                 "debugMask=5", "entryLog=1", "nvls=0", "maxBlocks=16", "split=0.25,0.75", "ifIp=10.0.0.1", "basePort=61000",
+                 "effective bufferBytes=536870912 execTimeoutNs=7000000000"):
+        assert frag in e, frag
+    bad = parse_env(HCCL_DETERMINISTIC="maybe", HCCL_BUFFSIZE="0", HCCL_OP_EXPANSION_MODE="TPU", HCCL_ALGO="level9:x", HCCL_MAX_BLOCKS="4096",
+                    HCCL_DFS_CONFIG="nonsense:on", HCCL_IF_BASE_PORT="80")
+    assert bad.count("rejected:") == 7 and "deterministic=0" in bad
+
+
+def test_comm_config_overrides_environment():
+    comms = Communicator.host_sim(2, None, hb.make_config(buffer_mib=3, name="my_group", deterministic=2))
+    assert comms[0].name == "my_group"
+    for c in comms:
+        c.destroy()
+
+
+# ---------------------------------------------------------------- parameter checks through the C API
+def test_param_checks():
+    comms = Communicator.host_sim(2)
+    c = comms[0]
+    x = np.zeros(8, np.float32)
+    h = c.handle
+    null = ctypes.c_void_p(0)
+    p = ctypes.c_void_p(x.ctypes.data)
+    assert lib.HcclAllReduce(p, p, 0, 4, 0, h, null) == 0                      # count 0: success, no-op
+    assert lib.HcclAllReduce(null, p, 8, 4, 0, h, null) == int(hb.Result.E_PTR)
+    assert lib.HcclAllReduce(p, p, 8, 13, 0, h, null) == int(hb.Result.E_PARA)  # 13 is a gap, not a type
+    assert lib.HcclAllReduce(p, p, 8, 255, 0, h, null) == int(hb.Result.E_PARA)
+    assert lib.HcclAllReduce(p, p, 8, int(DataType.UINT8), 0, h, null) == int(hb.Result.E_NOT_SUPPORT)   # no reduction on uint8
+    assert lib.HcclAllReduce(p, p, 8, int(DataType.FP8E4M3), 0, h, null) == int(hb.Result.E_NOT_SUPPORT)  # fp8 only in ReduceScatter
+    assert lib.HcclAllReduce(p, p, 8, int(DataType.INT16), int(ReduceOp.PROD), h, null) == int(hb.Result.E_NOT_SUPPORT)
+    assert lib.HcclAllReduce(p, p, 8, 4, 9, h, null) == int(hb.Result.E_PARA)
+    assert lib.HcclAllReduce(p, p, 0x800000000, 4, 0, h, null) == int(hb.Result.E_PARA)                  # beyond SYS_MAX_COUNT
+    assert lib.HcclBroadcast(p, 8, 4, 2, h, null) == int(hb.Result.E_PARA)                               # root out of range
+    assert lib.HcclSend(p, 8, 4, 5, h, null) == int(hb.Result.E_PARA)
+    assert lib.HcclAllReduce(p, p, 8, 4, 0, null, null) == int(hb.Result.E_PTR)
+    for c in comms:
+        c.destroy()
+
+
+# ---------------------------------------------------------------- registry / selector
+def test_registry_names_and_counts():
+    reg = hb.registry()
+    names = [n for n, _, _ in reg]
+    assert len(names) == len(set((n, op) for n, op, _ in reg))
+    for must in ("P2pAllReduceSoleMeshLL", "P2pAllReduceSoleMeshOneShot", "P2pAllReduceSoleMeshTwoShot", "NvlsAllReduceSoleMesh",
+                 "P2pReduceScatterSoleMesh", "NvlsReduceScatterSoleMesh", "P2pAllGatherSoleMesh", "P2pBroadcastSoleMeshTwoShot", "NvlsBroadcastSoleMesh",
+                 "P2pAlltoAllVSoleMesh", "P2pBatchSendRecvSoleMesh", "P2pBarrierSoleMesh", "HostAllReduceSoleRing", "HostAllReduceSoleRHD",
+                 "HostAllReduceSoleNHR", "HostAllReduceSequenceMeshNHR", "HostAllReduceParallelMeshNHR", "HostAllReduceStrictOrderedMesh",
+                 "HostAlltoAllVSolePairwise", "HostBarrierSoleNHR"):
+        assert must in names, must
+    assert len(reg) >= 60
+
+
+def test_cost_formula():
+    # no link term: (B) * bytes + C, floored by D
+    assert lib.HcclDebugEvalCost(0.0, 1e-3, 5.0, 0.0, 0, 1.0, 1000.0) == pytest.approx(6.0)
+    assert lib.HcclDebugEvalCost(0.0, 1e-3, 5.0, 100.0, 0, 1.0, 1000.0) == pytest.approx(100.0)
+    # with a link term the utilisation curve makes small messages relatively dearer than large ones
+    small = lib.HcclDebugEvalCost(1e-6, 0, 0, 0, 1, 1.0, 65536.0) / 65536.0
+    large = lib.HcclDebugEvalCost(1e-6, 0, 0, 0, 1, 1.0, 268435456.0) / 268435456.0
+    assert small > 5 * large
+
+
+def test_selector_preference_and_determinism():
+    os.environ.pop("HCCL_ALGO", None)
+    lib.HcclReloadEnvConfig()
+    comms = Communicator.host_sim(8)
+    txt = comms[0].explain(Cmd.ALLREDUCE, 1 << 20, DataType.FP32)
+    assert txt.startswith("selected Host") and "HostAllReduceSoleRing" in txt and "P2pAllReduce" not in txt.split("\n")[0]
+    os.environ["HCCL_ALGO"] = "level0:NA;level1:ring"
+    lib.HcclReloadEnvConfig()
+    txt = comms[0].explain(Cmd.ALLREDUCE, 1 << 20, DataType.FP32)
+    assert txt.startswith("selected HostAllReduceSoleRing") and "[HCCL_ALGO]" in txt
+    # a preference nothing can honour falls back to automatic selection instead of failing
+    os.environ["HCCL_ALGO"] = "level0:NA;level1:nvls"
+    lib.HcclReloadEnvConfig()
+    assert comms[0].explain(Cmd.ALLREDUCE, 1 << 20, DataType.FP32).startswith("selected Host")
+    os.environ.pop("HCCL_ALGO")
+    lib.HcclReloadEnvConfig()
+    for c in comms:
+        c.destroy()
+
+
+TUNER_SRC = r"""
+#include "hccl/hccl_tuner_plugin.h"
+#include <stdlib.h>
+#include <string.h>
+static HcclResult Create(HcclComm, const HcclTunerCommInfo* ci, const HcclTunerTopoInfo* ti, void** ctx, uint32_t* size) {
+    if (getenv("TUNER_FAIL_CREATE")) return HCCL_E_INTERNAL;
+    uint32_t* p = (uint32_t*)malloc(8); p[0] = ti->nRanks; p[1] = 42; *ctx = p; *size = 8; (void)ci; return HCCL_SUCCESS; }
+static HcclResult Update(void* ctx, const HcclTunerCollOpInfo* op, HcclTunerAlgoCostEntry* e, uint32_t n, bool* matched) {
+    const uint32_t stride = e[0].header.size;
+    if (!ctx || ((uint32_t*)ctx)[1] != 42) return HCCL_E_INTERNAL;
+    for (uint32_t i = 0; i < n; ++i) {
+        HcclTunerAlgoCostEntry* x = (HcclTunerAlgoCostEntry*)((char*)e + (size_t)i * stride);
+        if (op->collType == HCCL_CMD_ALLREDUCE && strcmp(x->templateName, "nhr") == 0 && strcmp(x->executorName, "sole") == 0) { x->cost = 0.0f; *matched = true; }
+        if (op->collType == HCCL_CMD_ALLREDUCE && strcmp(x->templateName, "ring") == 0) { x->cost = -1.0f; *matched = true; }
+    }
+    return HCCL_SUCCESS; }
+static HcclTunerPluginOps g_ops;
+extern "C" const HcclTunerPluginOps* HcclTunerPluginOpsGet(void) {
+    HcclTunerPluginOpsInit(&g_ops); g_ops.Create = Create; g_ops.UpdateAlgoCostTable = Update;
+    if (getenv("TUNER_BAD_MAGIC")) g_ops.header.magicWord = 0x12345678u;
+    return &g_ops; }
+"""
+
+
+def test_tuner_plugin_rewrites_costs_and_bad_plugins_are_ignored(tmp_path):
+    src = tmp_path / "tuner.cc"
+    src.write_text(TUNER_SRC)
+    so = tmp_path / "libtuner.so"
+    inc = Path(__file__).resolve().parent.parent / "csrc" / "include"
+    subprocess.check_call(["g++", "-shared", "-fPIC", "-std=c++17", f"-I{inc}", str(src), "-o", str(so)])
+    try:
+        os.environ["HCCL_ALG_TUNER_PLUGIN"] = str(so)
+        lib.HcclReloadEnvConfig()
+        comms = Communicator.host_sim(8)
+        txt = comms[0].explain(Cmd.ALLREDUCE, 1 << 20, DataType.FP32)
+        assert txt.startswith("selected HostAllReduceSoleNHR"), txt           # cost 0 = preferred
+        assert "HostAllReduceSoleRing: filtered (tuner: disabled)" in txt    # cost < 0 = disabled
+        assert "[tuner]" in txt
+        for c in comms:
+            c.destroy()
+        # a plugin whose ABI header does not check out is ignored, selection still works
+        os.environ["TUNER_BAD_MAGIC"] = "1"
+        comms = Communicator.host_sim(4)
+        assert "[tuner]" not in comms[0].explain(Cmd.ALLREDUCE, 1 << 20, DataType.FP32)
+        for c in comms:
+            c.destroy()
+        os.environ.pop("TUNER_BAD_MAGIC")
+        # a plugin whose Create fails is disabled for that communicator
+        os.environ["TUNER_FAIL_CREATE"] = "1"
+        comms = Communicator.host_sim(4)
+        assert "[tuner]" not in comms[0].explain(Cmd.ALLREDUCE, 1 << 20, DataType.FP32)
+        for c in comms:
+            c.destroy()
+        # a missing file is reported and ignored
+        os.environ["HCCL_ALG_TUNER_PLUGIN"] = str(tmp_path / "nope.so")
+        lib.HcclReloadEnvConfig()
+        comms = Communicator.host_sim(2)
+        assert comms[0].explain(Cmd.ALLREDUCE, 1024, DataType.FP32).startswith("selected Host")
+        for c in comms:
+            c.destroy()
+    finally:
+        for k in ("HCCL_ALG_TUNER_PLUGIN", "TUNER_BAD_MAGIC", "TUNER_FAIL_CREATE"):
+            os.environ.pop(k, None)
+        lib.HcclReloadEnvConfig()
