@@ -72,6 +72,7 @@ struct GemmArgs {
     // launch L + 2 after every peer has delivered (hence started) launch L + 1, i.e. finished reading launch L, so
     // no barrier is needed before a slot is overwritten.
     size_t xchgParityElems;
+    int bn;                    // two-SM kernels: column tile width (multiple of 32, at most 256), chosen per problem
 };
 constexpr int kCtlEpoch = 0, kCtlTicket = 1, kCtlAbort = 2, kCtlReady = 16;
 

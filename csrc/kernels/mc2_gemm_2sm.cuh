@@ -103,9 +103,15 @@ __device__ __forceinline__ void TileCoord2(const GemmArgs& g, int t, int tilesM2
         *mt2 = dstRank * rowTiles + rem % rowTiles;
         *nt = n;
     } else {
-        // column-major walk over row tiles inside a band of 8 column tiles keeps the B tiles of a wave L2-resident
-        *mt2 = t % tilesM2;
-        *nt = t / tilesM2;
+        // grouped raster: bands of 8 row tiles, walked column by column, so that the ~74 tiles in flight touch about
+        // 8 row tiles of A and 9 column tiles of B instead of all of A
+        constexpr int kGroup = 8;
+        const int perBand = kGroup * g.tilesN;
+        const int band = t / perBand, rem = t % perBand;
+        const int first = band * kGroup;
+        const int rows = (tilesM2 - first) < kGroup ? (tilesM2 - first) : kGroup;
+        *mt2 = first + rem % rows;
+        *nt = rem / rows;
     }
 }
 
@@ -132,7 +138,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     if (cta >= g.nGemmCtas) {
         const int worker = cta - g.nGemmCtas, nWorkers = (int)gridDim.x - g.nGemmCtas;
         if (MODE == MODE_AG) GatherWorker(c, g, worker, nWorkers, smem, bars);
-        if (MODE == MODE_RS) ReduceWorker<kBN2>(c, g, worker, nWorkers, (uint64_t)launchEpoch);
+        if (MODE == MODE_RS) ReduceWorker<kBN2>(c, g, worker, nWorkers, (uint64_t)launchEpoch);   // fused modes keep 256-wide tiles
     } else {
         constexpr uint32_t kTmemCols = 2 * kBN2;
         if (threadIdx.x == 0) {
@@ -151,6 +157,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         ClusterSync();               // the peer's barriers exist before anything arrives on them
         TcFenceAfter();
         const uint32_t tmemBase = *tmemBaseSlot;
+        const int BN = g.bn;                        // column tile width of this launch (accumulators stay 256 columns apart)
         const int pair = cta >> 1, nPairs = g.nGemmCtas >> 1;
         const int tilesM2 = (g.M + 255) / 256;
         const int nTiles = tilesM2 * g.tilesN;
@@ -178,19 +185,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                         uint8_t* sa = smem + stage * L::kStageBytes;
                         uint8_t* sb = sa + L::kABytes;
                         const uint32_t leaderFull = SmemAddr(&fullBar[stage]) & kPeerBitMask;
-                        if (crank == 0) MbarExpectTx(&fullBar[stage], 2 * L::kStageBytes);
+                        if (crank == 0) MbarExpectTx(&fullBar[stage], (uint32_t)(2 * (L::kABytes + (BN / 2) * kBK * 2)));
                         if (!A_MN) {
                             TmaLoad2D2Sm(sa, &tmA, leaderFull, kb * kBK, mt * kBM);
                         } else {
 #pragma unroll
                             for (int j = 0; j < kBM / 64; ++j) TmaLoad2D2Sm(sa + j * (64 * kBK * 2), &tmA, leaderFull, mt * kBM + j * 64, kb * kBK);
                         }
-                        const int nRow = nt * kBN2 + (int)crank * (kBN2 / 2);
+                        const int nRow = nt * BN + (int)crank * (BN / 2);
                         if (!B_MN) {
                             TmaLoad2D2Sm(sb, &tmB, leaderFull, kb * kBK, nRow);
                         } else {
 #pragma unroll
-                            for (int j = 0; j < (kBN2 / 2) / 64; ++j) TmaLoad2D2Sm(sb + j * (64 * kBK * 2), &tmB, leaderFull, nRow + j * 64, kb * kBK);
+                            for (int j = 0; j < (kBN2 / 2) / 64; ++j)
+                                if (j * 64 < BN / 2) TmaLoad2D2Sm(sb + j * (64 * kBK * 2), &tmB, leaderFull, nRow + j * 64, kb * kBK);
                         }
                         if (++stage == kStages2) { stage = 0; phase ^= 1u; }
                     }
@@ -203,7 +211,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         } else if (warp == 1) {
             // ===== MMA issuer: leader CTA only
             if (crank == 0 && ElectOne()) {
-                constexpr uint32_t idesc = InstrDescF16(256, kBN2, true, A_MN, B_MN);
+                const uint32_t idesc = InstrDescF16(256, BN, true, A_MN, B_MN);
                 int stage = 0;
                 uint32_t phase = 0;
                 int acc = 0;
@@ -263,11 +271,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                     rowPtr = g.out + (size_t)row * g.ldc;
                 }
 #pragma unroll 1
-                for (int c0 = 0; c0 < kBN2; c0 += 32) {
+                for (int c0 = 0; c0 < BN; c0 += 32) {
                     uint32_t v[32];
                     TmemLd32x32(taddr + (uint32_t)c0, v);
                     TmemLdWait();
-                    const int col = nt * kBN2 + c0;
+                    const int col = nt * BN + c0;
                     const int valid = g.N - col;
                     if (!rowValid || valid <= 0) continue;
                     Store32Cols(rowPtr + col, v, valid);

@@ -129,13 +129,13 @@ HcclResult DispatchLayout2Sm(bool aMn, bool bMn, const CUtensorMap& ta, const CU
     return HCCL_E_NOT_SUPPORT;
 }
 
-// HCCL_MC2_2SM=1 selects the two-SM (cta_group::2) kernels for tiles of 256 x 256; the one-SM kernels are the default.
+// The two-SM (cta_group::2) kernels are the default for tiles of 256 x 256; HCCL_MC2_2SM=0 keeps the one-SM kernels.
 bool Use2Sm()
 {
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("HCCL_MC2_2SM");
-        v = (e && e[0] == '1') ? 1 : 0;
+        v = (e && e[0] == '0') ? 0 : 1;
     }
     return v == 1;
 }
@@ -244,9 +244,25 @@ HcclResult Mc2Matmul(const void* a, const void* b, void* out, uint64_t m, uint64
     DevComm dummy;
     memset(&dummy, 0, sizeof(dummy));
     if (bn == 256 && Use2Sm() && m >= 256) {
-        // B is split between the two CTAs of a pair: each loads 128 of the 256 B rows of a tile
-        CHK_RET(MapB(&tb, b, n, k, bMn, 128));
-        const int pairsWanted = (int)((m + 255) / 256) * g.tilesN;
+        // Column tile width: the widest tile is the most efficient one, but a last wave that is mostly empty costs a
+        // whole tile time; pick the width that minimises (waves x width).  MN-major B is loaded in 64-column boxes, so
+        // its half tile has to be a multiple of 64.
+        const int pairs = (SmCount() & ~1) / 2;
+        const int tilesM2 = (int)((m + 255) / 256);
+        int bestBn = 256;
+        double bestCost = 1e30;
+        for (int cand : {256, 224, 192, 160, 128}) {
+            if (bMn && (cand / 2) % 64 != 0) continue;
+            const int tn = (int)((n + cand - 1) / cand);
+            const int waves = (tilesM2 * tn + pairs - 1) / pairs;
+            const double cost = (double)waves * (cand + 12);      // narrower tiles amortise the fixed per-tile work less well
+            if (cost < bestCost - 1e-9) { bestCost = cost; bestBn = cand; }
+        }
+        g.bn = bestBn;
+        g.tilesN = (int)((n + bestBn - 1) / bestBn);
+        // B is split between the two CTAs of a pair: each loads half of the B rows of a tile
+        CHK_RET(MapB(&tb, b, n, k, bMn, bestBn / 2));
+        const int pairsWanted = tilesM2 * g.tilesN;
         const int grid2 = std::min(SmCount() & ~1, 2 * pairsWanted);
         g.nGemmCtas = grid2;
         return DispatchLayout2Sm<MODE_PLAIN>(aMn, bMn, ta, tb, g, dummy, grid2, false, stream);
@@ -285,6 +301,7 @@ HcclResult Mc2AllGatherMatmul(CommImpl* comm, const void* aShard, const void* b,
     const int grid = SmCount() & ~1;
     g.nGemmCtas = grid - workers;
     if (Use2Sm() && mPerRank % 256 == 0) {
+        g.bn = 256;
         CHK_RET(MapB(&tb, b, n, k, bMn, 128));
         return DispatchLayout2Sm<MODE_AG>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream);
     }
@@ -319,6 +336,7 @@ HcclResult Mc2MatmulReduceScatter(CommImpl* comm, const void* a, const void* b, 
     const int grid = SmCount() & ~1;
     g.nGemmCtas = grid - workers;
     if (Use2Sm() && mPerRank % 256 == 0) {
+        g.bn = 256;
         CHK_RET(MapB(&tb, b, n, k, bMn, 128));
         return DispatchLayout2Sm<MODE_RS>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream);
     }
