@@ -5,6 +5,7 @@
 #include <sstream>
 #include <thread>
 #include <vector>
+#include "../core/algo_plugin.h"
 #include "../core/comm.h"
 #include "../core/plan_cache.h"
 #include "../core/log.h"
@@ -23,7 +24,7 @@ using namespace hccl;
 extern "C" {
 
 const char* HcclGetVersion(void) { return "hccl_b200 0.1.0"; }
-HcclResult HcclReloadEnvConfig(void) { ReloadEnvConfig(); return HCCL_SUCCESS; }
+HcclResult HcclReloadEnvConfig(void) { ReloadEnvConfig(); AlgoPluginReload(); return HCCL_SUCCESS; }
 const char* HcclGetErrorString(HcclResult code) { return ResultString(code); }
 
 HcclResult HcclGetRootInfo(HcclRootInfo* rootInfo)

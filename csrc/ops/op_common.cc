@@ -14,6 +14,7 @@
 #include <chrono>
 #include <cstring>
 #include <sstream>
+#include "../core/algo_plugin.h"
 #include "../core/log.h"
 #include "../core/plan_cache.h"
 #include "../cpu/host_comm.h"
@@ -491,6 +492,12 @@ HcclResult ExecOp(CommImpl* c, OpParam& p)
            << c->nRanks << "] stream[" << (void*)p.stream << "] comm[" << c->name << "] seq[" << c->opCount << "]";
         HCCL_RUN_INFO("%s", os.str().c_str());
         if (GetEnvConfig().diagnose) DiagnoseRecord(os.str());
+    }
+    {
+        // an algorithm plugin may claim the call before any built-in selection (reference op_common.cc:205-207, :1275-1281)
+        HcclResult pr;
+        std::string pname;
+        if (AlgoPluginTryExecute(c, p, &pr, &pname)) { p.algName = pname; return pr; }
     }
     if (c->hostComm) return HostExecOp(c, p);       // host engine communicators run the algorithm templates on host threads
     if (c->nRanks == 1) return SingleRank(c, p);

@@ -256,3 +256,55 @@ def test_tuner_plugin_rewrites_costs_and_bad_plugins_are_ignored(tmp_path):
         for k in ("HCCL_ALG_TUNER_PLUGIN", "TUNER_BAD_MAGIC", "TUNER_FAIL_CREATE"):
             os.environ.pop(k, None)
         lib.HcclReloadEnvConfig()
+
+
+ALGO_PLUGIN_SRC = r"""
+#include "hccl/hccl_algo_plugin.h"
+#include <string.h>
+static bool Ready(void) { return true; }
+static HcclResult Select(const HcclAlgoPluginParam* p, char name[HCCL_ALGO_PLUGIN_ALG_NAME_LEN]) {
+    if (p->magic != HCCL_ALGO_PLUGIN_PARAM_MAGIC || strcmp(p->opName, "Broadcast") != 0) return HCCL_E_NOT_SUPPORT;
+    strcpy(name, "PluginBroadcastFill");
+    return HCCL_SUCCESS; }
+static HcclResult Execute(const char* name, const HcclAlgoPluginParam* p) {
+    if (strcmp(name, "PluginBroadcastFill") != 0) return HCCL_E_INTERNAL;
+    float* out = (float*)p->recvBuf;
+    for (uint64_t i = 0; i < p->count; ++i) out[i] = 1000.0f + (float)p->rankNum;   // host buffers in this test
+    return HCCL_SUCCESS; }
+static HcclAlgoPluginTable g_table = {HCCL_PLUGIN_API_VERSION, HCCL_ALGO_PLUGIN_TABLE_MAGIC, sizeof(HcclAlgoPluginTable), Ready, Select, Execute};
+extern "C" const HcclAlgoPluginTable* GetHcclAlgoPlugin(void) { return &g_table; }
+"""
+
+
+def test_algo_plugin_takes_over_claimed_operator(tmp_path):
+    import threading
+
+    src = tmp_path / "plugin.cc"
+    src.write_text(ALGO_PLUGIN_SRC)
+    so = tmp_path / "libalgo_plugin.so"
+    inc = Path(__file__).resolve().parent.parent / "csrc" / "include"
+    subprocess.check_call(["g++", "-shared", "-fPIC", "-std=c++17", f"-I{inc}", str(src), "-o", str(so)])
+    try:
+        os.environ["HCCL_ALGO_PLUGIN_PATH"] = str(so)
+        lib.HcclReloadEnvConfig()
+        comms = Communicator.host_sim(3)
+        bufs = [np.zeros(16, np.float32) for _ in range(3)]
+        outs = [np.zeros(16, np.float32) for _ in range(3)]
+        ins = [np.full(16, r + 1, np.float32) for r in range(3)]
+
+        def body(r):
+            comms[r].broadcast(bufs[r], 0)            # claimed by the plugin
+            comms[r].all_reduce(ins[r], outs[r])      # not claimed: built-in path
+
+        ts = [threading.Thread(target=body, args=(r,)) for r in range(3)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        for b, o in zip(bufs, outs):
+            assert np.all(b == 1003.0)
+            assert np.all(o == 6.0)
+        assert comms[0].last_algorithm().startswith("HostAllReduce")
+        for c in comms:
+            c.destroy()
+    finally:
+        os.environ.pop("HCCL_ALGO_PLUGIN_PATH", None)
+        lib.HcclReloadEnvConfig()
