@@ -146,11 +146,16 @@ struct ArTwoShotBody {
             BlockReduceRange<T>(srcs, p, a.xch[me] + off, extra, direct ? 1 : 0, len, a.op);
         }
         RankBarrier(c, b, 0, e + 2, K_AR_TWOSHOT);
-        for (int k = direct ? 1 : 0; k < p; ++k) {
-            const int q = (me + k) % p;
-            size_t qo, ql;
-            SliceSub(a.bytes, p, q, nb, b, &qo, &ql);
-            BlockCopyBytes(a.out + qo, a.xch[q] + qo, ql);
+        {
+            CopySeg segs[kMaxDevRanks];
+            int n = 0;
+            for (int k = direct ? 1 : 0; k < p; ++k) {
+                const int q = (me + k) % p;
+                size_t qo, ql;
+                SliceSub(a.bytes, p, q, nb, b, &qo, &ql);
+                segs[n++] = CopySeg{a.out + qo, a.xch[q] + qo, ql};
+            }
+            BlockCopyMulti(segs, n);
         }
         RankBarrier(c, b, 0, e + 3, K_AR_TWOSHOT);
         StoreEpoch(c, b, e + 3);
@@ -372,9 +377,24 @@ struct ArNvlsBody {
         size_t off, len;
         SliceSub(a.bytes, p, me, nb, b, &off, &len);
         const size_t nv = len >> 4;
-        for (size_t i = threadIdx.x; i < nv; i += blockDim.x) {
-            const uint4 v = Multimem<T>::LdReduceAdd(a.srcMc + off + (i << 4));
-            MultimemSt(a.dstMc + off + (i << 4), v);
+        {
+            // four switch reductions in flight per thread
+            size_t i = threadIdx.x;
+            const size_t st = blockDim.x;
+            for (; i + 3 * st < nv; i += 4 * st) {
+                const uint4 v0 = Multimem<T>::LdReduceAdd(a.srcMc + off + (i << 4));
+                const uint4 v1 = Multimem<T>::LdReduceAdd(a.srcMc + off + ((i + st) << 4));
+                const uint4 v2 = Multimem<T>::LdReduceAdd(a.srcMc + off + ((i + 2 * st) << 4));
+                const uint4 v3 = Multimem<T>::LdReduceAdd(a.srcMc + off + ((i + 3 * st) << 4));
+                MultimemSt(a.dstMc + off + (i << 4), v0);
+                MultimemSt(a.dstMc + off + ((i + st) << 4), v1);
+                MultimemSt(a.dstMc + off + ((i + 2 * st) << 4), v2);
+                MultimemSt(a.dstMc + off + ((i + 3 * st) << 4), v3);
+            }
+            for (; i < nv; i += st) {
+                const uint4 v = Multimem<T>::LdReduceAdd(a.srcMc + off + (i << 4));
+                MultimemSt(a.dstMc + off + (i << 4), v);
+            }
         }
         if (len & 15u) {  // only the very last sub-range of the last slice can have one
             const size_t to = off + (nv << 4);
@@ -455,7 +475,21 @@ struct RsNvlsBody {
         const size_t base = a.dsp[me] + sb;          // host guarantees 16-byte alignment of dsp
         const size_t nv = (se - sb) >> 4;
         const bool outAl = (((uintptr_t)(a.out + sb)) & 15u) == 0;
-        for (size_t i = threadIdx.x; i < nv; i += blockDim.x) {
+        size_t i0 = threadIdx.x;
+        if (outAl) {
+            const size_t st = blockDim.x;
+            for (; i0 + 3 * st < nv; i0 += 4 * st) {
+                const uint4 v0 = Multimem<T>::LdReduceAdd(a.srcMc + base + (i0 << 4));
+                const uint4 v1 = Multimem<T>::LdReduceAdd(a.srcMc + base + ((i0 + st) << 4));
+                const uint4 v2 = Multimem<T>::LdReduceAdd(a.srcMc + base + ((i0 + 2 * st) << 4));
+                const uint4 v3 = Multimem<T>::LdReduceAdd(a.srcMc + base + ((i0 + 3 * st) << 4));
+                StVec(a.out + sb + (i0 << 4), v0);
+                StVec(a.out + sb + ((i0 + st) << 4), v1);
+                StVec(a.out + sb + ((i0 + 2 * st) << 4), v2);
+                StVec(a.out + sb + ((i0 + 3 * st) << 4), v3);
+            }
+        }
+        for (size_t i = i0; i < nv; i += blockDim.x) {
             const uint4 v = Multimem<T>::LdReduceAdd(a.srcMc + base + (i << 4));
             if (outAl) {
                 StVec(a.out + sb + (i << 4), v);
@@ -492,12 +526,17 @@ struct AgBody {
         Share(a.cnt[me], nb, b, 16, &sb, &se);
         if (a.mode & MODE_STAGE_IN) BlockCopyBytes(const_cast<char*>(a.src[me]) + sb, a.in + sb, se - sb);
         RankBarrier(c, b, 0, e + 1, K_AG);
-        if (!(a.mode & MODE_INPLACE)) BlockCopyBytes(a.out + a.dsp[me] + sb, a.in + sb, se - sb);
-        for (int k = 1; k < p; ++k) {
-            const int q = (me + k) % p;
-            size_t qb, qe;
-            Share(a.cnt[q], nb, b, 16, &qb, &qe);
-            BlockCopyBytes(a.out + a.dsp[q] + qb, a.src[q] + qb, qe - qb);
+        {
+            CopySeg segs[kMaxDevRanks];
+            int n = 0;
+            for (int k = 1; k < p; ++k) {
+                const int q = (me + k) % p;
+                size_t qb, qe;
+                Share(a.cnt[q], nb, b, 16, &qb, &qe);
+                segs[n++] = CopySeg{a.out + a.dsp[q] + qb, a.src[q] + qb, qe - qb};
+            }
+            if (!(a.mode & MODE_INPLACE)) segs[n++] = CopySeg{a.out + a.dsp[me] + sb, a.in + sb, se - sb};
+            BlockCopyMulti(segs, n);
         }
         RankBarrier(c, b, 0, e + 2, K_AG);
         StoreEpoch(c, b, e + 2);
@@ -590,13 +629,16 @@ struct BcastBody {
         }
         RankBarrier(c, b, 0, e + 2, K_BCAST);
         if (me != root) {
+            CopySeg segs[kMaxDevRanks];
+            int n = 0;
             for (int k = 1; k < p; ++k) {
                 const int q = (me + k) % p;
                 size_t qo, ql;
                 SliceSub(a.bytes, p, q, nb, b, &qo, &ql);
                 // the root's own slice only exists in the root's source buffer
-                BlockCopyBytes(a.out + qo, (q == root ? a.src[root] : a.xch[q]) + qo, ql);
+                segs[n++] = CopySeg{a.out + qo, (q == root ? a.src[root] : a.xch[q]) + qo, ql};
             }
+            BlockCopyMulti(segs, n);
         }
         RankBarrier(c, b, 0, e + 3, K_BCAST);
         StoreEpoch(c, b, e + 3);
@@ -616,11 +658,26 @@ struct BcastNvlsBody {
         const uint64_t e = LoadEpoch(c, b);
         size_t off, end;
         Share(a.bytes, nb, b, 16, &off, &end);
-        // previous readers of the exchange region are done (their op ended with a barrier)
+        // MODE_PUSH: the buffer itself is symmetric memory with a multicast alias: the root stores straight into every
+        // rank's buffer.  Otherwise the message goes through the exchange region and non-roots copy it out.
+        const bool direct = (a.mode & MODE_PUSH) != 0;
+        if (direct) RankBarrier(c, b, 0, e + 1, K_BCAST_NVLS);     // every rank has reached the op: its buffer may be overwritten
         if (me == root) {
             const size_t n = end - off, nv = n >> 4;
             const bool inAl = (((uintptr_t)(a.in + off)) & 15u) == 0;
-            for (size_t i = threadIdx.x; i < nv; i += blockDim.x) {
+            size_t i = threadIdx.x;
+            const size_t st = blockDim.x;
+            if (inAl) {
+                for (; i + 3 * st < nv; i += 4 * st) {
+                    const uint4 v0 = LdVec(a.in + off + (i << 4)), v1 = LdVec(a.in + off + ((i + st) << 4));
+                    const uint4 v2 = LdVec(a.in + off + ((i + 2 * st) << 4)), v3 = LdVec(a.in + off + ((i + 3 * st) << 4));
+                    MultimemSt(a.dstMc + off + (i << 4), v0);
+                    MultimemSt(a.dstMc + off + ((i + st) << 4), v1);
+                    MultimemSt(a.dstMc + off + ((i + 2 * st) << 4), v2);
+                    MultimemSt(a.dstMc + off + ((i + 3 * st) << 4), v3);
+                }
+            }
+            for (; i < nv; i += st) {
                 uint4 v;
                 if (inAl) v = LdVec(a.in + off + (i << 4));
                 else {
@@ -629,13 +686,15 @@ struct BcastNvlsBody {
                 }
                 MultimemSt(a.dstMc + off + (i << 4), v);
             }
-            // tail (< 16 bytes): plain stores to every rank's region
+            // tail (< 16 bytes): plain stores to every rank
             for (size_t t = (nv << 4) + threadIdx.x; t < n; t += blockDim.x)
-                for (int q = 0; q < c.nRanks; ++q) a.xch[q][off + t] = a.in[off + t];
+                for (int q = 0; q < c.nRanks; ++q) (direct ? a.dst[q] : a.xch[q])[off + t] = a.in[off + t];
         }
-        RankBarrier(c, b, 0, e + 1, K_BCAST_NVLS);
-        if (me != root) BlockCopyBytes(a.out + off, a.xch[me] + off, end - off);
-        RankBarrier(c, b, 0, e + 2, K_BCAST_NVLS);
+        RankBarrier(c, b, 0, e + (direct ? 2 : 1), K_BCAST_NVLS);
+        if (!direct) {
+            if (me != root) BlockCopyBytes(a.out + off, a.xch[me] + off, end - off);
+            RankBarrier(c, b, 0, e + 2, K_BCAST_NVLS);
+        }
         StoreEpoch(c, b, e + 2);
         OpTail(c, b);
     }
@@ -682,12 +741,15 @@ struct ReduceBody {
         else BlockReduceRange<T>(srcs, p, a.xch[me] + off, nullptr, 0, len, a.op);
         RankBarrier(c, b, 0, e + 2, K_REDUCE);
         if (me == root) {
+            CopySeg segs[kMaxDevRanks];
+            int n = 0;
             for (int k = 1; k < p; ++k) {
                 const int q = (me + k) % p;
                 size_t qo, ql;
                 SliceSub(a.bytes, p, q, nb, b, &qo, &ql);
-                BlockCopyBytes(a.out + qo, a.xch[q] + qo, ql);
+                segs[n++] = CopySeg{a.out + qo, a.xch[q] + qo, ql};
             }
+            BlockCopyMulti(segs, n);
         }
         RankBarrier(c, b, 0, e + 3, K_REDUCE);
         StoreEpoch(c, b, e + 3);
@@ -754,16 +816,21 @@ struct A2aBody {
             myMeta[threadIdx.x] = a.dsp2[threadIdx.x];
         }
         RankBarrier(c, b, 0, e + 1, K_A2AV);
-        for (int k = 0; k < p; ++k) {
-            const int q = (me + k) % p;
-            size_t rb, re;
-            Share(a.cnt[q], nb, b, 16, &rb, &re);
-            if (q == me) {
-                BlockCopyBytes(a.out + a.dsp[q] + rb, a.in + a.dsp2[me] + rb, re - rb);
-            } else {
-                const uint64_t sd = reinterpret_cast<const volatile uint64_t*>(a.xch[q])[(size_t)b * kMaxDevRanks + me];
-                BlockCopyBytes(a.out + a.dsp[q] + rb, a.src[q] + sd + rb, re - rb);
+        {
+            CopySeg segs[kMaxDevRanks];
+            int n = 0;
+            for (int k = 0; k < p; ++k) {
+                const int q = (me + k) % p;
+                size_t rb, re;
+                Share(a.cnt[q], nb, b, 16, &rb, &re);
+                if (q == me) {
+                    segs[n++] = CopySeg{a.out + a.dsp[q] + rb, a.in + a.dsp2[me] + rb, re - rb};
+                } else {
+                    const uint64_t sd = reinterpret_cast<const volatile uint64_t*>(a.xch[q])[(size_t)b * kMaxDevRanks + me];
+                    segs[n++] = CopySeg{a.out + a.dsp[q] + rb, a.src[q] + sd + rb, re - rb};
+                }
             }
+            BlockCopyMulti(segs, n);
         }
         RankBarrier(c, b, 0, e + 2, K_A2AV);
         StoreEpoch(c, b, e + 2);

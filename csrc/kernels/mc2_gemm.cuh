@@ -45,6 +45,13 @@ constexpr int kThreads = 192;
 constexpr int kEpilogueThreads = 128;
 constexpr uint64_t kWaitLimitNs = 5ull * 1000 * 1000 * 1000;
 
+// Epilogue staging: each of the 4 epilogue warps transposes 32 rows x 64 columns of bf16 through shared memory so
+// that global / peer stores are 128 contiguous bytes per row instead of 16-byte pieces scattered over 32 rows (a
+// 16-byte store is a whole NVLink packet for 16 bytes of payload).  Rows are padded by 16 bytes against bank conflicts.
+constexpr int kStgRowBytes = 128 + 16;
+constexpr int kStgWarpBytes = 32 * kStgRowBytes;
+constexpr int kEpilogueStagingBytes = 4 * kStgWarpBytes;
+
 enum Mode : int { MODE_PLAIN = 0, MODE_AG = 1, MODE_RS = 2, MODE_AR = 3 };
 
 struct GemmArgs {
@@ -83,7 +90,8 @@ struct SmemLayout {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTileBytes = kStages * kStageBytes;
     static constexpr int kBarrierBytes = 256;
-    static constexpr int kTotal = kTileBytes + kBarrierBytes + 1024;   // + slack for the 1024-byte alignment
+    static constexpr int kStagingOff = kTileBytes + kBarrierBytes;
+    static constexpr int kTotal = kStagingOff + kEpilogueStagingBytes + 1024;   // + slack for the 1024-byte alignment
 };
 
 // Flat tile index -> (m tile, n tile) in the order that suits the mode.
@@ -147,6 +155,46 @@ __device__ __forceinline__ void Store32Cols(__nv_bfloat16* dst, const uint32_t (
     } else {
         const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(packed);
         for (int i = 0; i < validCols; ++i) dst[i] = e[i];
+    }
+}
+
+// Drains this warp's 32 accumulator rows x `bn` columns from TMEM and stores them as bf16 through the staging area.
+// rowPtr(r, d) returns the address of column 0 of the tile in destination d for warp row r (nullptr = skip the row);
+// validCols = columns of the tile that exist in the matrix.
+template <class RowPtrFn>
+__device__ __forceinline__ void DrainTile(uint32_t taddrLane, int bn, uint8_t* stg, int lane, int validCols, int nDst, RowPtrFn rowPtr)
+{
+    for (int c0 = 0; c0 < bn; c0 += 64) {
+        const int chunk = (bn - c0) < 64 ? (bn - c0) : 64;
+        for (int h = 0; h < chunk; h += 32) {
+            uint32_t v[32];
+            TmemLd32x32(taddrLane + (uint32_t)(c0 + h), v);
+            TmemLdWait();
+            uint4* d = reinterpret_cast<uint4*>(stg + lane * kStgRowBytes + h * 2);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
+                    w[j] = *reinterpret_cast<uint32_t*>(&b);
+                }
+                d[i] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+        __syncwarp();
+        const int piecesPerRow = chunk / 8;          // 16-byte pieces
+        for (int i = lane; i < 32 * piecesPerRow; i += 32) {
+            const int r = i / piecesPerRow, pc = i % piecesPerRow;
+            const int col = c0 + pc * 8;
+            if (col >= validCols) continue;
+            const uint4 val = *reinterpret_cast<const uint4*>(stg + r * kStgRowBytes + pc * 16);
+            for (int dd = 0; dd < nDst; ++dd) {
+                __nv_bfloat16* p = rowPtr(r, dd);
+                if (p != nullptr) *reinterpret_cast<uint4*>(p + col) = val;
+            }
+        }
+        __syncwarp();
     }
 }
 
@@ -419,36 +467,31 @@ __global__ void __launch_bounds__(kThreads, 1)
                 ok = MbarWait(&tmemFull[acc], accPhase, abortWord, kWaitLimitNs);
                 if (!ok) break;
                 TcFenceAfter();
-                const int row = mt * kBM + quarter * 32 + lane;
+                const int row0 = mt * kBM + quarter * 32;
                 const uint32_t taddr = tmemBase + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
-                __nv_bfloat16* rowPtr = nullptr;
-                bool rowValid = row < g.M;
+                uint8_t* stg = smem + L::kStagingOff + quarter * kStgWarpBytes;
+                const int validCols = g.N - nt * BN;
                 if (MODE == MODE_PLAIN || MODE == MODE_AG) {
-                    rowPtr = g.out + (size_t)row * g.ldc;
+                    __nv_bfloat16* base = g.out + (size_t)nt * BN;
+                    DrainTile(taddr, BN, stg, lane, validCols, 1, [&](int r, int) -> __nv_bfloat16* {
+                        return (row0 + r < g.M) ? base + (size_t)(row0 + r) * g.ldc : nullptr;
+                    });
                 } else if (MODE == MODE_RS) {
                     // partial of row block `dst` goes into the owner's slot [me]
-                    const int dst = row / g.mPerRank;
-                    rowValid = rowValid && dst < g.nRanks;
-                    if (rowValid) rowPtr = g.xchg[dst] + parityOff + (size_t)g.rank * g.mPerRank * g.N + (size_t)(row - dst * g.mPerRank) * g.N;
-                } else {  // MODE_AR: own slot on every rank, written below per destination
-                    rowPtr = nullptr;
-                }
-#pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32) {
-                    uint32_t v[32];
-                    TmemLd32x32(taddr + (uint32_t)c0, v);
-                    TmemLdWait();
-                    const int col = nt * BN + c0;
-                    const int valid = g.N - col;
-                    if (!rowValid || valid <= 0) continue;
-                    if (MODE != MODE_AR) {
-                        Store32Cols(rowPtr + col, v, valid);
-                    } else {
-                        for (int q = 0; q < g.nRanks; ++q) {
-                            const int dst = (g.rank + q) % g.nRanks;
-                            Store32Cols(g.xchg[dst] + parityOff + (size_t)g.rank * g.M * g.N + (size_t)row * g.N + col, v, valid);
-                        }
-                    }
+                    DrainTile(taddr, BN, stg, lane, validCols, 1, [&](int r, int) -> __nv_bfloat16* {
+                        const int row = row0 + r;
+                        const int dst = row / g.mPerRank;
+                        if (row >= g.M || dst >= g.nRanks) return nullptr;
+                        return g.xchg[dst] + parityOff + (size_t)g.rank * g.mPerRank * g.N + (size_t)(row - dst * g.mPerRank) * g.N + (size_t)nt * BN;
+                    });
+                } else {
+                    // AllReduce: this rank's slot on every rank
+                    DrainTile(taddr, BN, stg, lane, validCols, g.nRanks, [&](int r, int dd) -> __nv_bfloat16* {
+                        const int row = row0 + r;
+                        if (row >= g.M) return nullptr;
+                        const int dst = (g.rank + dd) % g.nRanks;
+                        return g.xchg[dst] + parityOff + (size_t)g.rank * g.M * g.N + (size_t)row * g.N + (size_t)nt * BN;
+                    });
                 }
                 // release the accumulator to the MMA warp
                 TcFenceBefore();

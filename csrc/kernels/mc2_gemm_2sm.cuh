@@ -32,7 +32,8 @@ struct SmemLayout2 {
     static constexpr int kBBytes = (kBN2 / 2) * kBK * 2;     // 16 KiB: this CTA's 128 of the 256 B rows
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTileBytes = kStages2 * kStageBytes;   // 192 KiB
-    static constexpr int kTotal = kTileBytes + 256 + 1024;
+    static constexpr int kStagingOff = kTileBytes + 256;
+    static constexpr int kTotal = kStagingOff + kEpilogueStagingBytes + 1024;
 };
 
 __device__ __forceinline__ uint32_t ClusterCtaRank()
@@ -259,26 +260,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 ok = MbarWait(&tmemFull[acc], accPhase, abortWord, kWaitLimitNs);
                 if (!ok) break;
                 TcFenceAfter();
-                const int row = mt * kBM + quarter * 32 + lane;
+                const int row0 = mt * kBM + quarter * 32;
                 const uint32_t taddr = tmemBase + (uint32_t)(acc * kBN2) + ((uint32_t)(quarter * 32) << 16);
-                __nv_bfloat16* rowPtr = nullptr;
-                bool rowValid = row < g.M;
+                uint8_t* stg = smem + L::kStagingOff + quarter * kStgWarpBytes;
+                const int validCols = g.N - nt * BN;
                 if (MODE == MODE_RS) {
-                    const int dst = row / g.mPerRank;
-                    rowValid = rowValid && dst < g.nRanks;
-                    if (rowValid) rowPtr = g.xchg[dst] + parityOff + (size_t)g.rank * g.mPerRank * g.N + (size_t)(row - dst * g.mPerRank) * g.N;
+                    DrainTile(taddr, BN, stg, lane, validCols, 1, [&](int r, int) -> __nv_bfloat16* {
+                        const int row = row0 + r;
+                        const int dst = row / g.mPerRank;
+                        if (row >= g.M || dst >= g.nRanks) return nullptr;
+                        return g.xchg[dst] + parityOff + (size_t)g.rank * g.mPerRank * g.N + (size_t)(row - dst * g.mPerRank) * g.N + (size_t)nt * BN;
+                    });
                 } else {
-                    rowPtr = g.out + (size_t)row * g.ldc;
-                }
-#pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32) {
-                    uint32_t v[32];
-                    TmemLd32x32(taddr + (uint32_t)c0, v);
-                    TmemLdWait();
-                    const int col = nt * BN + c0;
-                    const int valid = g.N - col;
-                    if (!rowValid || valid <= 0) continue;
-                    Store32Cols(rowPtr + col, v, valid);
+                    __nv_bfloat16* base = g.out + (size_t)nt * BN;
+                    DrainTile(taddr, BN, stg, lane, validCols, 1, [&](int r, int) -> __nv_bfloat16* {
+                        return (row0 + r < g.M) ? base + (size_t)(row0 + r) * g.ldc : nullptr;
+                    });
                 }
                 TcFenceBefore();
                 __syncwarp();

@@ -135,6 +135,56 @@ __device__ __forceinline__ void BlockCopyBytes(char* dst, const char* src, size_
     }
 }
 
+// Several copies at once (typically one per peer): the 512-byte pieces of all segments are dealt round-robin to the
+// warps of the block, so that loads from every peer are in flight together instead of peer after peer (a sequence of
+// short remote copies pays one NVLink round trip each).  Falls back to one copy after the other when a segment is not
+// 16-byte aligned.
+struct CopySeg {
+    char* dst;
+    const char* src;
+    size_t bytes;
+};
+__device__ __forceinline__ void BlockCopyMulti(const CopySeg* segs, int n)
+{
+    bool aligned = true;
+    size_t maxBytes = 0;
+    for (int q = 0; q < n; ++q) {
+        aligned = aligned && (((uintptr_t)segs[q].dst | (uintptr_t)segs[q].src) & 15u) == 0;
+        maxBytes = segs[q].bytes > maxBytes ? segs[q].bytes : maxBytes;
+    }
+    if (!aligned || n == 1) {
+        for (int q = 0; q < n; ++q) BlockCopyBytes(segs[q].dst, segs[q].src, segs[q].bytes);
+        return;
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nWarps = blockDim.x >> 5;
+    const size_t chunksPerSeg = (maxBytes + 511) >> 9;              // 512-byte pieces (32 lanes x 16 bytes)
+    const size_t slots = chunksPerSeg * (size_t)n;
+    for (size_t slot = warp; slot < slots; slot += 4 * (size_t)nWarps) {
+        uint4 v[4];
+        bool ok[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const size_t sl = slot + (size_t)u * nWarps;
+            const int q = (int)(sl % n);
+            const size_t off = ((sl / n) << 9) + ((size_t)lane << 4);
+            ok[u] = sl < slots && off + 16 <= segs[q].bytes;
+            if (ok[u]) v[u] = *reinterpret_cast<const uint4*>(segs[q].src + off);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const size_t sl = slot + (size_t)u * nWarps;
+            const int q = (int)(sl % n);
+            const size_t off = ((sl / n) << 9) + ((size_t)lane << 4);
+            if (ok[u]) *reinterpret_cast<uint4*>(segs[q].dst + off) = v[u];
+        }
+    }
+    // tails shorter than 16 bytes
+    for (int q = 0; q < n; ++q) {
+        const size_t done = segs[q].bytes & ~(size_t)15;
+        for (size_t b = done + threadIdx.x; b < segs[q].bytes; b += blockDim.x) segs[q].dst[b] = segs[q].src[b];
+    }
+}
+
 // Contiguous share of [0, n) for part `idx` of `parts`; shares are multiples of
 // `gran` except the last.
 __device__ __host__ __forceinline__ void Share(size_t n, int parts, int idx, size_t gran, size_t* begin, size_t* end)

@@ -37,8 +37,9 @@ int BlocksFor(const CommImpl* c, uint64_t bytesPerRank, DevAlg alg)
         int nb = (int)std::min<uint64_t>((bytesPerRank + 8191) / 8192, 8);   // 512 threads x 8 B x 2 lines per block pass
         return std::max(1, std::min(nb, maxB));
     }
-    // one block per 128 KiB of traffic, at least 1, at most the configured ceiling
-    uint64_t nb = (bytesPerRank + (128u << 10) - 1) / (128u << 10);
+    // one block per 32 KiB of traffic, at least 1, at most the configured ceiling: remote loads need many bytes in
+    // flight, and a block that walks a long range alone pays one NVLink round trip per pass
+    uint64_t nb = (bytesPerRank + (32u << 10) - 1) / (32u << 10);
     return (int)std::max<uint64_t>(1, std::min<uint64_t>(nb, (uint64_t)maxB));
 }
 
@@ -273,7 +274,8 @@ struct Exec {
         const bool inDirect = in.reg && !nvlsAlg;
         uint64_t limit = ~0ull;
         if (!inDirect && !nvlsAlg) limit = std::min(limit, LoopBytes(L.inBytes, 1));
-        if (dalg == DALG_BCAST_TWOSHOT || nvlsAlg) limit = std::min(limit, LoopBytes(L.xchBytes, 1));
+        const bool nvlsDirect = nvlsAlg && in.reg && in.mc != nullptr && Aligned16(p.send);
+        if (dalg == DALG_BCAST_TWOSHOT || (nvlsAlg && !nvlsDirect)) limit = std::min(limit, LoopBytes(L.xchBytes, 1));
         if (limit == 0) return HCCL_E_MEMORY;
         const uint64_t chunk = std::min(total, limit);
         for (uint64_t off = 0; off < total; off += chunk) {
@@ -287,7 +289,15 @@ struct Exec {
             if (inDirect) { for (int q = 0; q < P; ++q) a.src[q] = in.peer[q] + off; }
             else if (!nvlsAlg) { FillStageIn(a); a.mode |= MODE_STAGE_IN; }
             FillXch(a);
-            if (nvlsAlg) a.dstMc = c->StageMcBase() + L.xchOff;
+            if (nvlsAlg) {
+                if (in.reg && in.mc != nullptr && Aligned16(p.send)) {
+                    a.mode |= MODE_PUSH;      // the buffer is symmetric with a multicast alias: store straight into it
+                    a.dstMc = const_cast<char*>(in.mc) + off;
+                    for (int q = 0; q < P; ++q) a.dst[q] = const_cast<char*>(in.peer[q]) + off;
+                } else {
+                    a.dstMc = c->StageMcBase() + L.xchOff;
+                }
+            }
             if (dalg == DALG_BCAST_ONESHOT) a.mode |= MODE_PUSH;
             CHK_RET(Launch(a, n));
         }

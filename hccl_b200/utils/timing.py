@@ -36,21 +36,63 @@ def device_time_ms(fn, iters: int, warmup: int = 3, flush_l2: bool = False) -> f
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs (reading only)."""
+    """Samples SM clocks and throttle reasons while a region runs (reading only; nothing is ever set).
+
+    Reads through NVML in a thread of this process (first sample within milliseconds, so short timed regions are covered);
+    falls back to an `nvidia-smi -lms` child process when the NVML binding is missing.
+    """
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
-    def __init__(self, gpu_index: int = 0, period_ms: int = 200):
+    def __init__(self, gpu_index: int = 0, period_ms: int = 20):
         self.gpu, self.period = gpu_index, period_ms
-        self.samples = []
+        self.samples = []          # [sm_mhz, max_mhz, watts, hw_slowdown, hw_thermal, sw_thermal, sw_power_cap] ("Active"/"Not Active")
         self._proc = None
         self._thread = None
+        self._stop = threading.Event()
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            import torch
+            uuid = str(torch.cuda.get_device_properties(self.gpu).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(uuid.encode() if hasattr(uuid, "encode") else uuid)
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.gpu)
 
     def __enter__(self):
         try:
+            nv, h = self._nvml_handle()
+            mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            bits = (0x8, 0x40, 0x20, 0x4)          # hw slowdown, hw thermal slowdown, sw thermal slowdown, sw power cap
+
+            def poll():
+                while True:
+                    try:
+                        r = get_reasons(h)
+                        row = [str(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)), str(mx),
+                               str(nv.nvmlDeviceGetPowerUsage(h) / 1000.0)]
+                        row += ["Active" if r & b else "Not Active" for b in bits]
+                        self.samples.append(row)
+                    except Exception:
+                        pass
+                    if self._stop.wait(self.period / 1000.0):
+                        return
+
+            self._thread = threading.Thread(target=poll, daemon=True)
+            self._thread.start()
+            return self
+        except Exception:
+            pass
+        try:
             self._proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", f"-i={self.gpu}",
-                                           f"-lms={self.period}"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                           f"-lms={max(self.period, 100)}"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self._proc = None
             return self
@@ -66,12 +108,15 @@ class ClockSampler:
         return self
 
     def __exit__(self, *exc):
+        self._stop.set()
         if self._proc is not None:
             self._proc.terminate()          # the exact process started above
             try:
                 self._proc.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self._proc.kill()
+        elif self._thread is not None:
+            self._thread.join(timeout=2)
         return False
 
     def summary(self) -> dict:
@@ -82,7 +127,7 @@ class ClockSampler:
                 mx.append(float(s[1]))
             except ValueError:
                 continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[3:7]):
+            for name, val in zip(self.REASONS, s[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),

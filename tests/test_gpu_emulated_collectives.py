@@ -274,3 +274,47 @@ def test_unsignalled_wait_times_out_cleanly():
         cs[0].barrier()
     for c in cs:
         c.destroy()
+
+
+def test_selector_on_device_communicator_and_resource_query():
+    import ctypes
+
+    from hccl_b200 import Cmd, DataType
+    from hccl_b200._lib import HcclOpResource, lib
+
+    torch.cuda.set_device(0)
+    cs = Communicator.emulated(4, hb.make_config(buffer_mib=16))
+    small = cs[0].explain(Cmd.ALLREDUCE, 256, DataType.FP32)
+    big = cs[0].explain(Cmd.ALLREDUCE, 64 << 20, DataType.FP32)
+    assert small.startswith("selected P2pAllReduceSoleMeshLL"), small
+    assert big.startswith("selected P2pAllReduceSoleMeshTwoShot"), big
+    assert "NvlsAllReduceSoleMesh" not in big.split("\n")[0]          # no multicast on emulated ranks
+    assert "Host" not in big                                           # host algorithms never compete on a device communicator
+    r = HcclOpResource()
+    # 64 Mi floats = 256 MiB through a 16 MiB slab: several launches, scratch bounded by the slab
+    assert lib.HcclCalcOpResource(cs[0].handle, int(Cmd.ALLREDUCE), 64 << 20, int(DataType.FP32), 0, 0, ctypes.byref(r)) == 0
+    assert r.algName.decode() == "P2pAllReduceSoleMeshTwoShot" and r.launches > 1 and r.streams == 1 and 0 < r.scratchBytes <= (16 << 20)
+    assert lib.HcclCalcOpResource(cs[0].handle, int(Cmd.ALLREDUCE), 64 << 20, int(DataType.FP32), 0, 1, ctypes.byref(r)) == 0
+    assert r.scratchBytes == 0            # symmetric buffers need no staging
+    for c in cs:
+        c.destroy()
+
+
+def test_strict_determinism_repeats_bitwise():
+    torch.cuda.set_device(0)
+    p, n = 8, 300007
+    ins = [(torch.randn(n, device="cuda", generator=torch.Generator(device="cuda").manual_seed(r)) * 10.0 ** (r - 4)).float() for r in range(p)]
+    results = []
+    for rep in range(2):
+        cs = Communicator.emulated(p, hb.make_config(buffer_mib=16, deterministic=2))
+        outs = [torch.empty_like(x) for x in ins]
+        for c, x, y in zip(cs, ins, outs):
+            c.all_reduce(x, y)
+        torch.cuda.synchronize()
+        assert "Nvls" not in cs[0].last_algorithm()
+        for y in outs[1:]:
+            assert torch.equal(y, outs[0])
+        results.append(outs[0].clone())
+        for c in cs:
+            c.destroy()
+    assert torch.equal(results[0], results[1])
