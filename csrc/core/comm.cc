@@ -258,7 +258,7 @@ LaunchTarget CommImpl::Target(cudaStream_t stream) const
 
 int CommImpl::MaxBlocks() const
 {
-    int m = cfg.maxBlocks ? (int)cfg.maxBlocks : 64;
+    int m = cfg.maxBlocks ? (int)cfg.maxBlocks : 128;
     if (m > kMaxBlocks) m = kMaxBlocks;
     if (emu_) {
         int cap = emu_->maxBlocksPerRank_;

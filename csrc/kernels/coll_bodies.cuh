@@ -24,6 +24,33 @@
 
 namespace hccl {
 
+// U vectors per source in flight: the unrolled body of BlockReduceRange for p <= PMAX sources and an aligned destination.
+template <class T, int U, int PMAX>
+__device__ __forceinline__ void ReduceVecLoop(const char* const* srcs, int p, char* dst, char* const* extra, int nExtra,
+                                              size_t head, size_t nv, int op, size_t& i)
+{
+    const size_t nt = blockDim.x;
+    for (; i + (U - 1) * nt < nv; i += U * nt) {
+        uint4 raw[U][PMAX];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int q = 0; q < PMAX; ++q)
+                if (q < p) raw[u][q] = LdVec(srcs[q] + head + ((i + u * nt) << 4));
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            AccVec<T> acc;
+            Unpack<T>(raw[u][0], acc);
+#pragma unroll
+            for (int q = 1; q < PMAX; ++q)
+                if (q < p) Accumulate<T>(raw[u][q], acc, op);
+            const uint4 r = Pack<T>(acc);
+            StVec(dst + head + ((i + u * nt) << 4), r);
+            for (int x = 0; x < nExtra; ++x) StVec(extra[x] + head + ((i + u * nt) << 4), r);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Reduce `nBytes` from p equally-aligned sources into dst (and optionally the
 // same bytes into nExtra more destinations).  One block, all threads.
@@ -47,7 +74,14 @@ __device__ __forceinline__ void BlockReduceRange(const char* const* srcs, int p,
     }
     const size_t nv = (nBytes - head) >> 4;
     const bool dstAligned = (((uintptr_t)(dst + head)) & 15u) == 0;
-    for (size_t i = tid; i < nv; i += nt) {
+    size_t i = tid;
+    // bulk: eight (small groups) or sixteen loads in flight per thread; the remainder goes one vector at a time
+    if (dstAligned) {
+        if (p <= 2) ReduceVecLoop<T, 4, 2>(srcs, p, dst, extra, nExtra, head, nv, op, i);
+        else if (p <= 4) ReduceVecLoop<T, 2, 4>(srcs, p, dst, extra, nExtra, head, nv, op, i);
+        else ReduceVecLoop<T, 2, kMaxDevRanks>(srcs, p, dst, extra, nExtra, head, nv, op, i);
+    }
+    for (; i < nv; i += nt) {
         uint4 raw[kMaxDevRanks];
 #pragma unroll
         for (int q = 0; q < kMaxDevRanks; ++q)
@@ -226,6 +260,13 @@ __device__ __forceinline__ bool LLLoad(const DevComm& c, const char* line, uint3
     *d1 = bb;
     return true;
 }
+// One read of a line without waiting: {data0, flag, data1, flag}.
+__device__ __forceinline__ uint4 LLPeek(const char* line)
+{
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(line) : "memory");
+    return v;
+}
 __device__ __forceinline__ uint32_t LLFlag(uint64_t epoch) { return (uint32_t)(epoch % 0xFFFFFFFFull) + 1u; }
 
 // Loads up to 8 payload bytes [off, off+8) of `base` (clamped at `bytes`) as two words.
@@ -285,14 +326,24 @@ struct ArLLBody {
             }
         }
         for (size_t i = lb + threadIdx.x; i < le; i += blockDim.x) {
+            // first try: the lines of all peers are requested together, so one memory latency covers them; only a
+            // line that has not arrived yet is polled
+            uint4 raw[kMaxDevRanks];
+#pragma unroll
+            for (int q = 0; q < kMaxDevRanks; ++q)
+                if (q < p) raw[q] = LLPeek(LLSlot(c, me, parity, q) + (i << 4));
             typename Tr::Acc acc[EPL];
             bool ok = true;
-            for (int q = 0; q < p; ++q) {
-                uint32_t w[2];
-                ok = ok && LLLoad(c, LLSlot(c, me, parity, q) + (i << 4), flag, &w[0], &w[1], K_AR_LL, b, q);
-                const T* el = reinterpret_cast<const T*>(w);
 #pragma unroll
-                for (int k = 0; k < EPL; ++k) acc[k] = q == 0 ? Tr::Load(el[k]) : ApplyOp(acc[k], Tr::Load(el[k]), a.op);
+            for (int q = 0; q < kMaxDevRanks; ++q) {
+                if (q < p) {
+                    uint32_t w[2] = {raw[q].x, raw[q].z};
+                    if (raw[q].y != flag || raw[q].w != flag)
+                        ok = ok && LLLoad(c, LLSlot(c, me, parity, q) + (i << 4), flag, &w[0], &w[1], K_AR_LL, b, q);
+                    const T* el = reinterpret_cast<const T*>(w);
+#pragma unroll
+                    for (int k = 0; k < EPL; ++k) acc[k] = q == 0 ? Tr::Load(el[k]) : ApplyOp(acc[k], Tr::Load(el[k]), a.op);
+                }
             }
             uint32_t r[2];
             T* rl = reinterpret_cast<T*>(r);
@@ -571,14 +622,21 @@ struct AgLLBody {
             if (!(a.mode & MODE_INPLACE))
                 StorePayload8(a.out + a.dsp[me], i << 3, bytes, (((uintptr_t)(a.out + a.dsp[me])) & 7u) == 0, d0, d1);
         }
-        for (int k = 1; k < p; ++k) {
-            const int q = (me + k) % p;
-            char* o = a.out + a.dsp[q];
-            const bool oAl = (((uintptr_t)o) & 7u) == 0;
-            for (size_t i = lb + threadIdx.x; i < le; i += blockDim.x) {
-                uint32_t d0, d1;
-                if (LLLoad(c, LLSlot(c, me, parity, q) + (i << 4), flag, &d0, &d1, K_AG_LL, b, q))
-                    StorePayload8(o, i << 3, bytes, oAl, d0, d1);
+        for (size_t i = lb + threadIdx.x; i < le; i += blockDim.x) {
+            uint4 raw[kMaxDevRanks];
+#pragma unroll
+            for (int q = 0; q < kMaxDevRanks; ++q)
+                if (q < p && q != me) raw[q] = LLPeek(LLSlot(c, me, parity, q) + (i << 4));
+#pragma unroll
+            for (int q = 0; q < kMaxDevRanks; ++q) {
+                if (q < p && q != me) {
+                    uint32_t d0 = raw[q].x, d1 = raw[q].z;
+                    bool ok = true;
+                    if (raw[q].y != flag || raw[q].w != flag)
+                        ok = LLLoad(c, LLSlot(c, me, parity, q) + (i << 4), flag, &d0, &d1, K_AG_LL, b, q);
+                    char* o = a.out + a.dsp[q];
+                    if (ok) StorePayload8(o, i << 3, bytes, (((uintptr_t)o) & 7u) == 0, d0, d1);
+                }
             }
         }
         FinishLLEpoch(c, ep, nb);

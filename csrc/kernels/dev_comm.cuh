@@ -147,7 +147,8 @@ __device__ __forceinline__ bool RankBarrier(const DevComm& c, int block, int slo
     __syncthreads();
     if (threadIdx.x < c.nRanks) {
         const int peer = threadIdx.x;
-        __threadfence_system();
+        // the release store at system scope orders everything the block wrote before the __syncthreads above (release
+        // is cumulative over what the storing thread has observed), so no separate fence is needed
         StReleaseSys(FlagPtr(c, peer, block, slot, c.rank), value);
         if (!WaitFlagGE(c, FlagPtr(c, c.rank, block, slot, peer), value, kernelId, block, slot, peer)) s_ok = 0;
     }

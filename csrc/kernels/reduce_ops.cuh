@@ -110,9 +110,13 @@ __device__ __forceinline__ void BlockCopyBytes(char* dst, const char* src, size_
         const uint4* s = reinterpret_cast<const uint4*>(src);
         uint4* d = reinterpret_cast<uint4*>(dst);
         size_t i = tid;
-        for (; i + 3 * (size_t)nt < nv; i += 4 * (size_t)nt) {
-            uint4 a = s[i], b = s[i + nt], c = s[i + 2 * (size_t)nt], e = s[i + 3 * (size_t)nt];
-            d[i] = a; d[i + nt] = b; d[i + 2 * (size_t)nt] = c; d[i + 3 * (size_t)nt] = e;
+        // eight loads in flight per thread: a remote copy is bound by bytes in flight, not by issue rate
+        for (; i + 7 * (size_t)nt < nv; i += 8 * (size_t)nt) {
+            uint4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = s[i + (size_t)u * nt];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) d[i + (size_t)u * nt] = v[u];
         }
         for (; i < nv; i += nt) d[i] = s[i];
         for (size_t b = (nv << 4) + tid; b < n; b += nt) dst[b] = src[b];
@@ -157,24 +161,25 @@ __device__ __forceinline__ void BlockCopyMulti(const CopySeg* segs, int n)
         return;
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nWarps = blockDim.x >> 5;
-    const size_t chunksPerSeg = (maxBytes + 511) >> 9;              // 512-byte pieces (32 lanes x 16 bytes)
-    const size_t slots = chunksPerSeg * (size_t)n;
-    for (size_t slot = warp; slot < slots; slot += 4 * (size_t)nWarps) {
-        uint4 v[4];
-        bool ok[4];
+    const uint32_t chunksPerSeg = (uint32_t)((maxBytes + 511) >> 9);   // 512-byte pieces (32 lanes x 16 bytes)
+    const uint32_t slots = chunksPerSeg * (uint32_t)n, un = (uint32_t)n;
+    constexpr int U = 8;                                               // loads in flight per thread
+    for (uint32_t slot = warp; slot < slots; slot += U * (uint32_t)nWarps) {
+        uint4 v[U];
+        bool ok[U];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const size_t sl = slot + (size_t)u * nWarps;
-            const int q = (int)(sl % n);
-            const size_t off = ((sl / n) << 9) + ((size_t)lane << 4);
+        for (int u = 0; u < U; ++u) {
+            const uint32_t sl = slot + (uint32_t)u * nWarps;
+            const uint32_t q = sl % un;
+            const size_t off = ((size_t)(sl / un) << 9) + ((size_t)lane << 4);
             ok[u] = sl < slots && off + 16 <= segs[q].bytes;
             if (ok[u]) v[u] = *reinterpret_cast<const uint4*>(segs[q].src + off);
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const size_t sl = slot + (size_t)u * nWarps;
-            const int q = (int)(sl % n);
-            const size_t off = ((sl / n) << 9) + ((size_t)lane << 4);
+        for (int u = 0; u < U; ++u) {
+            const uint32_t sl = slot + (uint32_t)u * nWarps;
+            const uint32_t q = sl % un;
+            const size_t off = ((size_t)(sl / un) << 9) + ((size_t)lane << 4);
             if (ok[u]) *reinterpret_cast<uint4*>(segs[q].dst + off) = v[u];
         }
     }

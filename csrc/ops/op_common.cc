@@ -34,12 +34,13 @@ int BlocksFor(const CommImpl* c, uint64_t bytesPerRank, DevAlg alg)
 {
     const int maxB = c->MaxBlocks();
     if (alg == DALG_AR_LL || alg == DALG_AG_LL) {
-        int nb = (int)std::min<uint64_t>((bytesPerRank + 8191) / 8192, 8);   // 512 threads x 8 B x 2 lines per block pass
+        int nb = (int)((bytesPerRank + 4095) / 4096);   // 512 threads x 8 payload bytes: one line per thread while blocks last
         return std::max(1, std::min(nb, maxB));
     }
-    // one block per 32 KiB of traffic, at least 1, at most the configured ceiling: remote loads need many bytes in
-    // flight, and a block that walks a long range alone pays one NVLink round trip per pass
-    uint64_t nb = (bytesPerRank + (32u << 10) - 1) / (32u << 10);
+    // one block per 16 KiB of traffic, at least 1, at most the configured ceiling: remote loads need many bytes in
+    // flight (about 2.5 MB per direction to fill an NVLink 5 port), and a block that walks a long range alone pays one
+    // NVLink round trip per pass
+    uint64_t nb = (bytesPerRank + (16u << 10) - 1) / (16u << 10);
     return (int)std::max<uint64_t>(1, std::min<uint64_t>(nb, (uint64_t)maxB));
 }
 
