@@ -87,7 +87,11 @@ def main():
         w = (torch.randn(F, H, device="cuda") * 0.02).bfloat16()
         out = torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
         gathered = torch.empty(M, H, device="cuda", dtype=torch.bfloat16)
-        t_fused = timed(lambda: mc2.all_gather_matmul(comm, a_shard, w, out=out, gathered=gathered))
+        t_pull = timed(lambda: mc2.all_gather_matmul(comm, a_shard, w, out=out, gathered=gathered))
+        # push form (the default of the TP layers): the gathered buffer is symmetric, the shard a plain tensor
+        gathered_sym = comm.empty((M, H), torch.bfloat16)
+        a_plain = a_shard.clone()
+        t_fused = timed(lambda: mc2.all_gather_matmul(comm, a_plain, w, out=out, gathered=gathered_sym))
 
         def base_ag():
             dist.all_gather_into_tensor(gathered, a_shard)
@@ -98,7 +102,7 @@ def main():
         fl = 2.0 * M * F * H
         link_bytes = (world - 1) * m_per * H * 2
         roof_ms = max(fl / 1663.3e9, link_bytes / 770e6)       # measured burst GEMM peak and measured peer-copy bandwidth
-        emit({"case": "ag_matmul", "m": M, "n": F, "k": H, "n_gpus": world, "fused_ms": t_fused, "nccl_cublas_ms": t_base, "cublas_only_ms": t_mm,
+        emit({"case": "ag_matmul", "m": M, "n": F, "k": H, "n_gpus": world, "fused_ms": t_fused, "fused_pull_ms": t_pull, "nccl_cublas_ms": t_base, "cublas_only_ms": t_mm,
               "fused_tflops": fl / t_fused / 1e9, "nccl_cublas_tflops": fl / t_base / 1e9, "roofline_ms": roof_ms, "fraction_of_roofline": roof_ms / t_fused})
         # ---- Matmul -> ReduceScatter
         a = torch.randn(M, F, device="cuda").bfloat16()

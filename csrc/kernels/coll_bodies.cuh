@@ -429,18 +429,15 @@ struct ArNvlsBody {
         SliceSub(a.bytes, p, me, nb, b, &off, &len);
         const size_t nv = len >> 4;
         {
-            // four switch reductions in flight per thread
+            // eight switch reductions in flight per thread
             size_t i = threadIdx.x;
             const size_t st = blockDim.x;
-            for (; i + 3 * st < nv; i += 4 * st) {
-                const uint4 v0 = Multimem<T>::LdReduceAdd(a.srcMc + off + (i << 4));
-                const uint4 v1 = Multimem<T>::LdReduceAdd(a.srcMc + off + ((i + st) << 4));
-                const uint4 v2 = Multimem<T>::LdReduceAdd(a.srcMc + off + ((i + 2 * st) << 4));
-                const uint4 v3 = Multimem<T>::LdReduceAdd(a.srcMc + off + ((i + 3 * st) << 4));
-                MultimemSt(a.dstMc + off + (i << 4), v0);
-                MultimemSt(a.dstMc + off + ((i + st) << 4), v1);
-                MultimemSt(a.dstMc + off + ((i + 2 * st) << 4), v2);
-                MultimemSt(a.dstMc + off + ((i + 3 * st) << 4), v3);
+            for (; i + 7 * st < nv; i += 8 * st) {
+                uint4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = Multimem<T>::LdReduceAdd(a.srcMc + off + ((i + u * st) << 4));
+#pragma unroll
+                for (int u = 0; u < 8; ++u) MultimemSt(a.dstMc + off + ((i + u * st) << 4), v[u]);
             }
             for (; i < nv; i += st) {
                 const uint4 v = Multimem<T>::LdReduceAdd(a.srcMc + off + (i << 4));
@@ -529,15 +526,12 @@ struct RsNvlsBody {
         size_t i0 = threadIdx.x;
         if (outAl) {
             const size_t st = blockDim.x;
-            for (; i0 + 3 * st < nv; i0 += 4 * st) {
-                const uint4 v0 = Multimem<T>::LdReduceAdd(a.srcMc + base + (i0 << 4));
-                const uint4 v1 = Multimem<T>::LdReduceAdd(a.srcMc + base + ((i0 + st) << 4));
-                const uint4 v2 = Multimem<T>::LdReduceAdd(a.srcMc + base + ((i0 + 2 * st) << 4));
-                const uint4 v3 = Multimem<T>::LdReduceAdd(a.srcMc + base + ((i0 + 3 * st) << 4));
-                StVec(a.out + sb + (i0 << 4), v0);
-                StVec(a.out + sb + ((i0 + st) << 4), v1);
-                StVec(a.out + sb + ((i0 + 2 * st) << 4), v2);
-                StVec(a.out + sb + ((i0 + 3 * st) << 4), v3);
+            for (; i0 + 7 * st < nv; i0 += 8 * st) {
+                uint4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = Multimem<T>::LdReduceAdd(a.srcMc + base + ((i0 + u * st) << 4));
+#pragma unroll
+                for (int u = 0; u < 8; ++u) StVec(a.out + sb + ((i0 + u * st) << 4), v[u]);
             }
         }
         for (size_t i = i0; i < nv; i += blockDim.x) {
@@ -637,6 +631,85 @@ struct AgLLBody {
                     char* o = a.out + a.dsp[q];
                     if (ok) StorePayload8(o, i << 3, bytes, (((uintptr_t)o) & 7u) == 0, d0, d1);
                 }
+            }
+        }
+        FinishLLEpoch(c, ep, nb);
+        OpTail(c, b);
+    }
+};
+
+// ---------------------------------------------------------------------------
+// LL exchange: the small-message form of ReduceScatter, Broadcast and AlltoAll.  Every pair moves at most `bytes`
+// (<= kLLMaxPayload) as flag-in-data lines, so the op costs one NVLink latency and no barrier.
+//   cnt2[q] != 0 : this rank sends `bytes` from in + dsp2[q] to rank q
+//   cnt[q]  != 0 : this rank receives `bytes` from rank q; without REDUCE they land at out + dsp[q]
+// With REDUCE the contributions of all ranks (this rank's own read from in + dsp2[me]) are reduced in rank order into
+// out.  Without REDUCE the own block, when cnt[me] != 0, is copied locally.
+template <class T, bool REDUCE>
+struct LLExchangeBody {
+    using Args = CollArgs;
+    static constexpr int kThreads = 512;
+    __device__ static void Run(const DevComm& c, const Args& a, int b, int nb)
+    {
+        using Tr = ElemTraits<T>;
+        constexpr int EPL = 8 / (int)sizeof(T) > 0 ? 8 / (int)sizeof(T) : 1;
+        OpHead(c, b);
+        const int p = c.nRanks, me = c.rank;
+        const uint64_t ep = LoadLLEpoch(c);
+        const uint32_t flag = LLFlag(ep);
+        const int parity = (int)(ep & 1u);
+        const size_t bytes = a.bytes;
+        const size_t nLines = (bytes + 7) >> 3;
+        size_t lb, le;
+        Share(nLines, nb, b, 1, &lb, &le);
+        for (int k = 1; k < p; ++k) {
+            const int q = (me + k) % p;
+            if (a.cnt2[q] == 0) continue;
+            const char* src = a.in + a.dsp2[q];
+            const bool al = (((uintptr_t)src) & 7u) == 0;
+            char* slot = LLSlot(c, q, parity, me);
+            for (size_t i = lb + threadIdx.x; i < le; i += blockDim.x) {
+                uint32_t d0, d1;
+                LoadPayload8(src, i << 3, bytes, al, &d0, &d1);
+                LLStore(slot + (i << 4), d0, d1, flag);
+            }
+        }
+        const char* own = a.in + a.dsp2[me];
+        const bool ownAl = (((uintptr_t)own) & 7u) == 0;
+        for (size_t i = lb + threadIdx.x; i < le; i += blockDim.x) {
+            uint4 raw[kMaxDevRanks];
+#pragma unroll
+            for (int q = 0; q < kMaxDevRanks; ++q)
+                if (q < p && q != me && a.cnt[q] != 0) raw[q] = LLPeek(LLSlot(c, me, parity, q) + (i << 4));
+            typename Tr::Acc acc[EPL];
+            bool ok = true;
+#pragma unroll
+            for (int q = 0; q < kMaxDevRanks; ++q) {
+                if (q >= p || a.cnt[q] == 0) continue;
+                uint32_t w[2];
+                if (q == me) {
+                    LoadPayload8(own, i << 3, bytes, ownAl, &w[0], &w[1]);
+                } else {
+                    w[0] = raw[q].x;
+                    w[1] = raw[q].z;
+                    if (raw[q].y != flag || raw[q].w != flag)
+                        ok = LLLoad(c, LLSlot(c, me, parity, q) + (i << 4), flag, &w[0], &w[1], K_RS_LL, b, q) && ok;
+                }
+                if (REDUCE) {
+                    const T* el = reinterpret_cast<const T*>(w);
+#pragma unroll
+                    for (int k = 0; k < EPL; ++k) acc[k] = q == 0 ? Tr::Load(el[k]) : ApplyOp(acc[k], Tr::Load(el[k]), a.op);
+                } else if (ok) {
+                    char* o = a.out + a.dsp[q];
+                    StorePayload8(o, i << 3, bytes, (((uintptr_t)o) & 7u) == 0, w[0], w[1]);
+                }
+            }
+            if (REDUCE) {
+                uint32_t r[2] = {0u, 0u};
+                T* rl = reinterpret_cast<T*>(r);
+#pragma unroll
+                for (int k = 0; k < EPL; ++k) rl[k] = Tr::Store(acc[k]);
+                if (ok) StorePayload8(a.out, i << 3, bytes, (((uintptr_t)a.out) & 7u) == 0, r[0], r[1]);
             }
         }
         FinishLLEpoch(c, ep, nb);

@@ -46,6 +46,9 @@ HcclResult LaunchBody(const LaunchTarget& t, const typename Body::Args& a, int n
         default: break;                                                                   \
     }
 
+template <class T>
+using RsLLBody = LLExchangeBody<T, true>;
+
 }  // namespace
 
 HcclResult LaunchCollective(const LaunchTarget& t, DevAlg alg, HcclDataType dtype, const CollArgs& a, int nb)
@@ -72,6 +75,9 @@ HcclResult LaunchCollective(const LaunchTarget& t, DevAlg alg, HcclDataType dtyp
         case DALG_BCAST_NVLS: return LaunchBody<BcastNvlsBody>(t, a, nb);
         case DALG_SCATTER_PULL: return LaunchBody<ScatterBody>(t, a, nb);
         case DALG_A2A_PULL: return LaunchBody<A2aBody>(t, a, nb);
+        case DALG_RS_LL: HCCL_REDUCE_DISPATCH(RsLLBody) break;
+        case DALG_BCAST_LL:
+        case DALG_A2A_LL: return LaunchBody<LLExchangeBody<int8_t, false>>(t, a, nb);
         default: break;
     }
     HCCL_ERROR("no kernel for device algorithm %d with data type %d", (int)alg, (int)dtype);

@@ -36,6 +36,7 @@ enum DevAlg : int {
     DALG_BCAST_ONESHOT, DALG_BCAST_TWOSHOT, DALG_BCAST_NVLS,
     DALG_REDUCE_ONESHOT, DALG_REDUCE_TWOSHOT,
     DALG_SCATTER_PULL, DALG_A2A_PULL, DALG_P2P_MAILBOX, DALG_BARRIER, DALG_TEST_WAIT,
+    DALG_RS_LL, DALG_BCAST_LL, DALG_A2A_LL,
     DALG_COUNT
 };
 

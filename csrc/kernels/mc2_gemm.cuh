@@ -80,6 +80,12 @@ struct GemmArgs {
     // no barrier is needed before a slot is overwritten.
     size_t xchgParityElems;
     int bn;                    // two-SM kernels: column tile width (multiple of 32, at most 256), chosen per problem
+    // AG, push form (agPush != 0): `gathered` is symmetric memory, every rank stores its own shard into all ranks'
+    // gathered buffers and adds the bytes written to their per-row-block arrival counters; aPeer[rank] is the local shard (any memory).
+    //   gatheredPeer[q] = rank q's gathered buffer mapped here; agReady[q] = rank q's counters [P * mPerRank / 128]
+    int agPush;
+    __nv_bfloat16* gatheredPeer[kMaxDevRanks];
+    uint64_t* agReady[kMaxDevRanks];
 };
 constexpr int kCtlEpoch = 0, kCtlTicket = 1, kCtlAbort = 2, kCtlReady = 16;
 
@@ -232,7 +238,8 @@ __device__ __forceinline__ void GatherWorker(const DevComm& c, const GemmArgs& g
         bool alive = true;
         auto chunkInfo = [&](long n, const char** src, char** dst, uint32_t* bytes, int* flagIdx, bool* last) {
             const int blk = (int)(n / chunksPerBlock), ch = (int)(n % chunksPerBlock);
-            const int step = blk / blocksPerRank, rb = blk % blocksPerRank;
+            // peers first, nearest consumer order; the own shard (which the GEMM reads in place) is copied last
+            const int step = (blk / blocksPerRank + 1) % g.nRanks, rb = blk % blocksPerRank;
             const int srcRank = (g.rank + step) % g.nRanks;
             const size_t off = b0 + (size_t)ch * kGatherChunk;
             *bytes = (uint32_t)((share - (size_t)ch * kGatherChunk) < kGatherChunk ? (share - (size_t)ch * kGatherChunk) : kGatherChunk);
@@ -277,6 +284,131 @@ __device__ __forceinline__ void GatherWorker(const DevComm& c, const GemmArgs& g
     StoreEpoch(c, worker, e + 2);
 }
 
+__device__ __forceinline__ bool SpinUntilGE64(const uint64_t* p, uint64_t want, volatile uint32_t* abortWord)
+{
+    const uint64_t t0 = TimerNs();
+    uint32_t spins = 0;
+    for (;;) {
+        uint64_t v;
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+        if (v >= want) return true;
+        if ((++spins & 0xFFu) == 0u) {
+            if (*abortWord != 0u) return false;
+            if (TimerNs() - t0 > kWaitLimitNs) { *abortWord = 1u; return false; }
+        }
+    }
+}
+
+// AllGather, push form.  A read over NVLink keeps few bytes in flight per SM (every request waits a round trip), a
+// posted write does not, so the gather runs faster when every rank WRITES its shard to the others.  Every warp of a
+// worker CTA owns one contiguous range of the local shard and copies it with plain loads and stores (16 vectors in
+// flight per lane) into the gathered buffer of one destination rank after the other, nearest consumer first (rank
+// r needs the shards of r, r+1, r+2, ... in this order, so this rank serves rank, rank-1, rank-2, ...).  After each
+// destination the warp fences once and adds, for every 128-row block its range touches, the number of bytes it
+// wrote there to the destination's arrival counter of that block; the destination's GEMM producer waits until the
+// counter holds the bytes of a whole block, and the destination clears its counters when its kernel ends.  Warps
+// never wait for one another, so one warp's fence (a round trip over NVLink) overlaps the other warps' copies.  One
+// barrier at the start (every rank is inside the kernel: nobody still reads its gathered buffer from an earlier op
+// and its counters are clear); none at the end: this rank only reads its own memory.
+constexpr int kPushWarps = kThreads / 32;
+__device__ __forceinline__ void GatherPushWorker(const DevComm& c, const GemmArgs& g, int worker, int nWorkers)
+{
+    volatile uint32_t* abortWord = g.ctl + kCtlAbort;
+    const uint64_t e = LoadEpoch(c, worker);
+    const bool ok = RankBarrier(c, worker, 0, e + 1, K_MC2_AG_GEMM);
+    if (!ok && threadIdx.x == 0) *abortWord = 1u;
+    if (ok) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        const size_t blockBytes = (size_t)g.K * 2 * kBM;
+        const int blocksPerRank = g.mPerRank / kBM;
+        const size_t shardBytes = blockBytes * (size_t)blocksPerRank;
+        size_t s0, s1;
+        Share(shardBytes, nWorkers * kPushWarps, worker * kPushWarps + warp, 16, &s0, &s1);
+        const size_t nv = (s1 - s0) >> 4;
+        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(g.aPeer[g.rank]) + s0);
+        constexpr int U = 16;
+        for (int it = 0; it < g.nRanks && nv != 0; ++it) {
+            const int step = (it + 1) % g.nRanks;          // peers first; the local copy (not waited for by the GEMM) last
+            const int dstRank = (g.rank - step + g.nRanks) % g.nRanks;
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(g.gatheredPeer[dstRank]) + (size_t)g.rank * shardBytes + s0);
+            for (size_t i = lane; i < nv; i += U * 32) {
+                uint4 v[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (i + u * 32 < nv) v[u] = __ldg(src + i + u * 32);
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (i + u * 32 < nv) dst[i + u * 32] = v[u];
+            }
+            __syncwarp();
+            if (lane == 0) {
+                __threadfence_system();
+                for (size_t b = s0 / blockBytes; b * blockBytes < s1; ++b) {
+                    const size_t lo = b * blockBytes > s0 ? b * blockBytes : s0;
+                    const size_t hi = (b + 1) * blockBytes < s1 ? (b + 1) * blockBytes : s1;
+                    uint64_t* flag = g.agReady[dstRank] + (size_t)g.rank * blocksPerRank + b;
+                    asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(flag), "l"((uint64_t)(hi - lo)) : "memory");
+                }
+            }
+            __syncwarp();
+        }
+    }
+    StoreEpoch(c, worker, e + 1);
+}
+
+// One output tile of the ReduceScatter reduction: rows [mtLocal*128, +128) x cols [nt*BN, +BN), 16-byte vectors of
+// 8 bf16.  U vectors of every rank's partial are requested before any is consumed (16 loads in flight per
+// thread): the reduction is bound by bytes in flight from local memory, and a worker has to keep up with the tiles
+// of about eight GEMM CTAs.  Partials are summed in rank order in fp32.
+template <int BN, int U, int PMAX>
+__device__ __forceinline__ void ReduceTile(const GemmArgs& g, const __nv_bfloat16* xbase, size_t slotElems, int mtLocal, int nt)
+{
+    const int vecPerRow = BN / 8;
+    const int total = kBM * vecPerRow;
+    for (int v = threadIdx.x; v < total; v += U * (int)blockDim.x) {
+        int r[U], col[U];
+        bool valid[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int vv = v + u * (int)blockDim.x;
+            r[u] = mtLocal * kBM + vv / vecPerRow;
+            col[u] = nt * BN + (vv % vecPerRow) * 8;
+            valid[u] = vv < total && r[u] < g.mPerRank && col[u] < g.N;
+        }
+        uint4 raw[U][PMAX];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int q = 0; q < PMAX; ++q)
+                if (q < g.nRanks && valid[u])
+                    raw[u][q] = *reinterpret_cast<const uint4*>(xbase + (size_t)q * slotElems + (size_t)r[u] * g.N + col[u]);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (!valid[u]) continue;
+            float acc[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+#pragma unroll
+            for (int q = 0; q < PMAX; ++q) {
+                if (q < g.nRanks) {
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u][q]);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float2 f = __bfloat1622float2(h[k]);
+                        acc[2 * k] += f.x;
+                        acc[2 * k + 1] += f.y;
+                    }
+                }
+            }
+            uint4 o;
+            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+            *reinterpret_cast<uint4*>(g.out + (size_t)r[u] * g.ldc + col[u]) = o;
+        }
+    }
+}
+
 // ReduceScatter reduction: for every tile of the local row block, waits until all ranks have delivered their
 // partial (flag value == launch epoch), sums the P partials in rank order in fp32 and writes bf16 to `out`.
 // Tiles are visited in the order they complete (column tile major).
@@ -299,31 +431,9 @@ __device__ __forceinline__ void ReduceWorker(const DevComm& c, const GemmArgs& g
         }
         __syncthreads();
         if (!s_ok) break;
-        // tile rows [mtLocal*128, +128) x cols [nt*BN, +BN): 16-byte vectors of 8 bf16
-        const int vecPerRow = BN / 8;
-        for (int v = threadIdx.x; v < kBM * vecPerRow; v += blockDim.x) {
-            const int r = mtLocal * kBM + v / vecPerRow;
-            const int col = nt * BN + (v % vecPerRow) * 8;
-            if (r >= g.mPerRank || col >= g.N) continue;
-            float acc[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-            for (int q = 0; q < g.nRanks; ++q) {
-                const uint4 raw = *reinterpret_cast<const uint4*>(xbase + (size_t)q * slotElems + (size_t)r * g.N + col);
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float2 f = __bfloat1622float2(h[k]);
-                    acc[2 * k] += f.x;
-                    acc[2 * k + 1] += f.y;
-                }
-            }
-            uint4 o;
-            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
-            *reinterpret_cast<uint4*>(g.out + (size_t)r * g.ldc + col) = o;
-        }
+        if (g.nRanks <= 2) ReduceTile<BN, 8, 2>(g, xbase, slotElems, mtLocal, nt);
+        else if (g.nRanks <= 4) ReduceTile<BN, 4, 4>(g, xbase, slotElems, mtLocal, nt);
+        else ReduceTile<BN, 2, kMaxDevRanks>(g, xbase, slotElems, mtLocal, nt);
     }
     (void)abortWord;
 }
@@ -331,7 +441,8 @@ __device__ __forceinline__ void ReduceWorker(const DevComm& c, const GemmArgs& g
 // -----------------------------------------------------------------------------
 template <int BN, bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
-    GemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs g, const DevComm c)
+    GemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmAOwn,
+               const GemmArgs g, const DevComm c)
 {
     using L = SmemLayout<BN>;
     extern __shared__ uint8_t smemRaw[];
@@ -351,7 +462,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (cta >= g.nGemmCtas) {
         // ---- communication worker CTA
         const int worker = cta - g.nGemmCtas, nWorkers = (int)gridDim.x - g.nGemmCtas;
-        if (MODE == MODE_AG) GatherWorker(c, g, worker, nWorkers, smem, bars);
+        if (MODE == MODE_AG) {
+            if (g.agPush) GatherPushWorker(c, g, worker, nWorkers);
+            else GatherWorker(c, g, worker, nWorkers, smem, bars);
+        }
         if (MODE == MODE_RS) ReduceWorker<BN>(c, g, worker, nWorkers, (uint64_t)launchEpoch);
     } else {
         // ---- GEMM CTA
@@ -362,6 +476,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             MbarInitFence();
             PrefetchTensorMap(&tmA);
             PrefetchTensorMap(&tmB);
+            if (MODE == MODE_AG) PrefetchTensorMap(&tmAOwn);
         }
         if (warp == 1) {
             TmemAlloc(tmemBaseSlot, kTmemCols);
@@ -383,9 +498,16 @@ __global__ void __launch_bounds__(kThreads, 1)
                 for (int t = cta; t < nTiles && ok; t += g.nGemmCtas) {
                     int mt, nt;
                     TileCoord<MODE>(g, t, &mt, &nt);
-                    if (MODE == MODE_AG) {
+                    // AG: rows of this rank's own shard are read from the shard itself (no wait; the copy into the
+                    // gathered buffer is off the critical path), all others from the gathered buffer once they arrived
+                    const int ownFirst = g.rank * (g.mPerRank / kBM);
+                    const bool own = MODE == MODE_AG && mt >= ownFirst && mt < ownFirst + g.mPerRank / kBM;
+                    const CUtensorMap* mapA = own ? &tmAOwn : &tmA;
+                    const int rowA = (own ? mt - ownFirst : mt) * kBM;
+                    if (MODE == MODE_AG && !own) {
                         const int nWorkers = (int)gridDim.x - g.nGemmCtas;
-                        ok = SpinUntilGE(g.ctl + kCtlReady + mt, (uint32_t)nWorkers, abortWord);
+                        if (g.agPush) ok = SpinUntilGE64(g.agReady[g.rank] + mt, (uint64_t)g.K * 2 * kBM, abortWord);
+                        else ok = SpinUntilGE(g.ctl + kCtlReady + mt, (uint32_t)nWorkers, abortWord);
                         FenceProxyAsync();   // reader side of the generic -> async proxy hand-over
                         if (!ok) break;
                     }
@@ -396,7 +518,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                         uint8_t* sb = sa + L::kABytes;
                         MbarExpectTx(&fullBar[stage], L::kStageBytes);
                         if (!A_MN) {
-                            TmaLoad2D(sa, &tmA, &fullBar[stage], kb * kBK, mt * kBM);
+                            TmaLoad2D(sa, mapA, &fullBar[stage], kb * kBK, rowA);
                         } else {
 #pragma unroll
                             for (int j = 0; j < kBM / 64; ++j) TmaLoad2D(sa + j * (64 * kBK * 2), &tmA, &fullBar[stage], mt * kBM + j * 64, kb * kBK);
@@ -573,6 +695,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (MODE == MODE_AG) {
                 const int n = g.nRanks * (g.mPerRank / kBM);
                 for (int i = 0; i < n; ++i) g.ctl[kCtlReady + i] = 0;
+                if (g.agPush)
+                    for (int i = 0; i < n; ++i) g.agReady[g.rank][i] = 0;      // peers write again only after the next start barrier
             }
             g.ctl[kCtlTicket] = 0;
             *reinterpret_cast<volatile uint32_t*>(g.ctl + kCtlEpoch) = launchEpoch;

@@ -118,7 +118,8 @@ __device__ __forceinline__ void TileCoord2(const GemmArgs& g, int t, int tilesM2
 
 template <bool A_MN, bool B_MN, int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-    GemmKernel2Sm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs g, const DevComm c)
+    GemmKernel2Sm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmAOwn,
+                  const GemmArgs g, const DevComm c)
 {
     using L = SmemLayout2;
     extern __shared__ uint8_t smemRaw[];
@@ -138,7 +139,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 
     if (cta >= g.nGemmCtas) {
         const int worker = cta - g.nGemmCtas, nWorkers = (int)gridDim.x - g.nGemmCtas;
-        if (MODE == MODE_AG) GatherWorker(c, g, worker, nWorkers, smem, bars);
+        if (MODE == MODE_AG) {
+            if (g.agPush) GatherPushWorker(c, g, worker, nWorkers);
+            else GatherWorker(c, g, worker, nWorkers, smem, bars);
+        }
         if (MODE == MODE_RS) ReduceWorker<kBN2>(c, g, worker, nWorkers, (uint64_t)launchEpoch);   // fused modes keep 256-wide tiles
     } else {
         constexpr uint32_t kTmemCols = 2 * kBN2;
@@ -148,6 +152,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             MbarInitFence();
             PrefetchTensorMap(&tmA);
             PrefetchTensorMap(&tmB);
+            if (MODE == MODE_AG) PrefetchTensorMap(&tmAOwn);
         }
         if (warp == 1) {
             TmemAlloc2(tmemBaseSlot, kTmemCols);
@@ -174,9 +179,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                     int mt2, nt;
                     TileCoord2<MODE>(g, t, tilesM2, &mt2, &nt);
                     const int mt = mt2 * 2 + (int)crank;           // this CTA's 128-row tile
-                    if (MODE == MODE_AG) {
+                    const int ownFirst = g.rank * (g.mPerRank / kBM);
+                    const bool own = MODE == MODE_AG && mt >= ownFirst && mt < ownFirst + g.mPerRank / kBM;
+                    const CUtensorMap* mapA = own ? &tmAOwn : &tmA;     // own rows: read from the shard itself, no wait
+                    const int rowA = (own ? mt - ownFirst : mt) * kBM;
+                    if (MODE == MODE_AG && !own) {
                         const int nWorkers = (int)gridDim.x - g.nGemmCtas;
-                        ok = SpinUntilGE(g.ctl + kCtlReady + mt, (uint32_t)nWorkers, abortWord);
+                        if (g.agPush) ok = SpinUntilGE64(g.agReady[g.rank] + mt, (uint64_t)g.K * 2 * kBM, abortWord);
+                        else ok = SpinUntilGE(g.ctl + kCtlReady + mt, (uint32_t)nWorkers, abortWord);
                         FenceProxyAsync();
                         if (!ok) break;
                     }
@@ -188,7 +198,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                         const uint32_t leaderFull = SmemAddr(&fullBar[stage]) & kPeerBitMask;
                         if (crank == 0) MbarExpectTx(&fullBar[stage], (uint32_t)(2 * (L::kABytes + (BN / 2) * kBK * 2)));
                         if (!A_MN) {
-                            TmaLoad2D2Sm(sa, &tmA, leaderFull, kb * kBK, mt * kBM);
+                            TmaLoad2D2Sm(sa, mapA, leaderFull, kb * kBK, rowA);
                         } else {
 #pragma unroll
                             for (int j = 0; j < kBM / 64; ++j) TmaLoad2D2Sm(sa + j * (64 * kBK * 2), &tmA, leaderFull, mt * kBM + j * 64, kb * kBK);
@@ -311,6 +321,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             if (MODE == MODE_AG) {
                 const int n = g.nRanks * (g.mPerRank / kBM);
                 for (int i = 0; i < n; ++i) g.ctl[kCtlReady + i] = 0;
+                if (g.agPush)
+                    for (int i = 0; i < n; ++i) g.agReady[g.rank][i] = 0;      // peers write again only after the next start barrier
             }
             g.ctl[kCtlTicket] = 0;
             *reinterpret_cast<volatile uint32_t*>(g.ctl + kCtlEpoch) = launchEpoch;

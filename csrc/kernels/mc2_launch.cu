@@ -69,8 +69,9 @@ int SmCount()
 
 template <int BN, bool A_MN, bool B_MN, int MODE>
 HcclResult LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const DevComm& c, int grid, bool cooperative,
-                      cudaStream_t stream)
+                      cudaStream_t stream, const CUtensorMap* taOwn = nullptr)
 {
+    const CUtensorMap& ta2 = taOwn != nullptr ? *taOwn : ta;      // AG: this rank's own shard, read where it is
     auto kernel = GemmKernel<BN, A_MN, B_MN, MODE>;
     static bool attrSet = false;
     if (!attrSet) {
@@ -78,12 +79,12 @@ HcclResult LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmAr
         attrSet = true;
     }
     if (cooperative) {
-        void* args[4] = {(void*)&ta, (void*)&tb, (void*)&g, (void*)&c};
+        void* args[5] = {(void*)&ta, (void*)&tb, (void*)&ta2, (void*)&g, (void*)&c};
         cudaError_t e = cudaLaunchCooperativeKernel((const void*)kernel, dim3((unsigned)grid), dim3(kThreads), args, SmemLayout<BN>::kTotal, stream);
         if (e != cudaSuccess) { HCCL_ERROR("fused matmul launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
         return HCCL_SUCCESS;
     }
-    kernel<<<grid, kThreads, SmemLayout<BN>::kTotal, stream>>>(ta, tb, g, c);
+    kernel<<<grid, kThreads, SmemLayout<BN>::kTotal, stream>>>(ta, tb, ta2, g, c);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { HCCL_ERROR("matmul launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
     return HCCL_SUCCESS;
@@ -91,8 +92,9 @@ HcclResult LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmAr
 
 template <bool A_MN, bool B_MN, int MODE>
 HcclResult LaunchGemm2Sm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const DevComm& c, int grid, bool cooperative,
-                         cudaStream_t stream)
+                         cudaStream_t stream, const CUtensorMap* taOwn = nullptr)
 {
+    const CUtensorMap& ta2 = taOwn != nullptr ? *taOwn : ta;
     auto kernel = GemmKernel2Sm<A_MN, B_MN, MODE>;
     static bool attrSet = false;
     if (!attrSet) {
@@ -110,17 +112,17 @@ HcclResult LaunchGemm2Sm(const CUtensorMap& ta, const CUtensorMap& tb, const Gem
     attrs[0].val.cooperative = cooperative ? 1 : 0;
     cfg.attrs = attrs;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, g, c);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, ta2, g, c);
     if (e != cudaSuccess) { HCCL_ERROR("two-SM matmul launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
     return HCCL_SUCCESS;
 }
 
 template <int MODE>
 HcclResult DispatchLayout2Sm(bool aMn, bool bMn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const DevComm& c, int grid,
-                             bool coop, cudaStream_t s)
+                             bool coop, cudaStream_t s, const CUtensorMap* taOwn = nullptr)
 {
-    if (!aMn && !bMn) return LaunchGemm2Sm<false, false, MODE>(ta, tb, g, c, grid, coop, s);
-    if (!aMn && bMn) return LaunchGemm2Sm<false, true, MODE>(ta, tb, g, c, grid, coop, s);
+    if (!aMn && !bMn) return LaunchGemm2Sm<false, false, MODE>(ta, tb, g, c, grid, coop, s, taOwn);
+    if (!aMn && bMn) return LaunchGemm2Sm<false, true, MODE>(ta, tb, g, c, grid, coop, s, taOwn);
     if (MODE == MODE_PLAIN) {
         if (aMn && !bMn) return LaunchGemm2Sm<true, false, MODE_PLAIN>(ta, tb, g, c, grid, coop, s);
         return LaunchGemm2Sm<true, true, MODE_PLAIN>(ta, tb, g, c, grid, coop, s);
@@ -140,12 +142,30 @@ bool Use2Sm()
     return v == 1;
 }
 
+// CTAs of a fused launch that move data instead of computing.  The gather workers of AllGather->Matmul are bound by
+// bytes in flight per SM, so they get more SMs (about one in five) than the reduce workers of Matmul->ReduceScatter
+// (one in nine, at most 16).  HCCL_MC2_AG_WORKERS / HCCL_MC2_RS_WORKERS override the counts (even, 2 .. 64).
+int WorkerCtas(bool gather)
+{
+    static int v[2] = {-1, -1};
+    int& r = v[gather ? 1 : 0];
+    if (r < 0) {
+        r = gather ? (std::min(32, std::max(2, SmCount() / 5)) & ~1) : (std::min(16, std::max(2, SmCount() / 9)) & ~1);
+        const char* e = getenv(gather ? "HCCL_MC2_AG_WORKERS" : "HCCL_MC2_RS_WORKERS");
+        if (e != nullptr) {
+            const int n = atoi(e) & ~1;
+            if (n >= 2 && n <= 64) r = n;
+        }
+    }
+    return r;
+}
+
 template <int BN, int MODE>
 HcclResult DispatchLayout(bool aMn, bool bMn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const DevComm& c, int grid,
-                          bool coop, cudaStream_t s)
+                          bool coop, cudaStream_t s, const CUtensorMap* taOwn = nullptr)
 {
-    if (!aMn && !bMn) return LaunchGemm<BN, false, false, MODE>(ta, tb, g, c, grid, coop, s);
-    if (!aMn && bMn) return LaunchGemm<BN, false, true, MODE>(ta, tb, g, c, grid, coop, s);
+    if (!aMn && !bMn) return LaunchGemm<BN, false, false, MODE>(ta, tb, g, c, grid, coop, s, taOwn);
+    if (!aMn && bMn) return LaunchGemm<BN, false, true, MODE>(ta, tb, g, c, grid, coop, s, taOwn);
     if (MODE == MODE_PLAIN) {
         if (aMn && !bMn) return LaunchGemm<BN, true, false, MODE_PLAIN>(ta, tb, g, c, grid, coop, s);
         return LaunchGemm<BN, true, true, MODE_PLAIN>(ta, tb, g, c, grid, coop, s);
@@ -201,7 +221,7 @@ HcclResult Mc2EnsureState(CommImpl* comm, uint64_t parityBytes)
         std::shared_ptr<Mc2State> st(new Mc2State());
         CHK_CUDA(cudaMalloc(&st->ctl, kMc2CtlWords * sizeof(uint32_t)));
         CHK_CUDA(cudaMemset(st->ctl, 0, kMc2CtlWords * sizeof(uint32_t)));
-        CHK_RET(SymAlloc(*comm->bs, comm->device, (size_t)comm->nRanks * kMc2MaxTiles * sizeof(uint64_t), false, GetEnvConfig().forceIpc, &st->flags));
+        CHK_RET(SymAlloc(*comm->bs, comm->device, ((size_t)comm->nRanks * kMc2MaxTiles + kMc2AgBlocks) * sizeof(uint64_t), false, GetEnvConfig().forceIpc, &st->flags));
         comm->mc2 = std::move(st);
     }
     Mc2State* st = comm->mc2.get();
@@ -279,12 +299,21 @@ HcclResult Mc2AllGatherMatmul(CommImpl* comm, const void* aShard, const void* b,
     CHK_RET(CheckShapes(mPerRank * P, n, k));
     if (mPerRank % kBM != 0) { HCCL_ERROR("AllGather->Matmul needs rows per rank to be a multiple of %d (got %llu)", kBM, (unsigned long long)mPerRank); return HCCL_E_PARA; }
     if (P * (mPerRank / kBM) > 8 * 512) return HCCL_E_PARA;
-    const char* peers[kMaxDevRanks];
-    if (!comm->Lookup(aShard, mPerRank * k * 2, peers, nullptr)) { HCCL_ERROR("AllGather->Matmul: the activation shard must live in symmetric memory (HcclMemAlloc)"); return HCCL_E_PARA; }
+    // Push form when the gathered buffer is symmetric memory (every rank writes its shard into the others' buffers;
+    // the shard itself may live anywhere); pull form when only the shard is.  HCCL_MC2_AG_PULL=1 keeps the pull form.
+    const char* peers[kMaxDevRanks] = {nullptr};
+    const char* gathPeers[kMaxDevRanks] = {nullptr};
+    static const bool forcePull = [] { const char* e = getenv("HCCL_MC2_AG_PULL"); return e != nullptr && e[0] == '1'; }();
+    const bool push = !forcePull && comm->Lookup(gathered, P * mPerRank * k * 2, gathPeers, nullptr);
+    if (!push && !comm->Lookup(aShard, mPerRank * k * 2, peers, nullptr)) {
+        HCCL_ERROR("AllGather->Matmul: the gathered buffer or the activation shard must live in symmetric memory (HcclMemAlloc)");
+        return HCCL_E_PARA;
+    }
     CHK_RET(Mc2EnsureState(comm, 0));
     const bool bMn = transB == 0;
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, taOwn;
     CHK_RET(MapA(&ta, gathered, mPerRank * P, k, false));
+    CHK_RET(MapA(&taOwn, aShard, mPerRank, k, false));
     CHK_RET(MapB(&tb, b, n, k, bMn, 256));
     GemmArgs g;
     memset(&g, 0, sizeof(g));
@@ -297,15 +326,23 @@ HcclResult Mc2AllGatherMatmul(CommImpl* comm, const void* aShard, const void* b,
     g.mPerRank = (int)mPerRank;
     for (int q = 0; q < comm->nRanks; ++q) g.aPeer[q] = (const __nv_bfloat16*)peers[q];
     g.gathered = (__nv_bfloat16*)gathered;
-    const int workers = std::min(16, std::max(2, SmCount() / 9)) & ~1;
+    if (push) {
+        g.agPush = 1;
+        g.aPeer[comm->rank] = (const __nv_bfloat16*)aShard;
+        for (int q = 0; q < comm->nRanks; ++q) {
+            g.gatheredPeer[q] = (__nv_bfloat16*)gathPeers[q];
+            g.agReady[q] = (uint64_t*)comm->mc2->flags.peer[q] + (size_t)comm->nRanks * kMc2MaxTiles;
+        }
+    }
+    const int workers = WorkerCtas(true);
     const int grid = SmCount() & ~1;
     g.nGemmCtas = grid - workers;
     if (Use2Sm() && mPerRank % 256 == 0) {
         g.bn = 256;
         CHK_RET(MapB(&tb, b, n, k, bMn, 128));
-        return DispatchLayout2Sm<MODE_AG>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream);
+        return DispatchLayout2Sm<MODE_AG>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream, &taOwn);
     }
-    return DispatchLayout<256, MODE_AG>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream);
+    return DispatchLayout<256, MODE_AG>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream, &taOwn);
 }
 
 HcclResult Mc2MatmulReduceScatter(CommImpl* comm, const void* a, const void* b, void* out, uint64_t m, uint64_t n, uint64_t k, int transB,
@@ -332,7 +369,7 @@ HcclResult Mc2MatmulReduceScatter(CommImpl* comm, const void* a, const void* b, 
     g.tilesM = (int)(m / kBM);
     g.tilesN = (int)tilesN;
     g.mPerRank = (int)mPerRank;
-    const int workers = std::min(16, std::max(2, SmCount() / 9)) & ~1;
+    const int workers = WorkerCtas(false);
     const int grid = SmCount() & ~1;
     g.nGemmCtas = grid - workers;
     if (Use2Sm() && mPerRank % 256 == 0) {

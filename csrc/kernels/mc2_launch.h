@@ -20,6 +20,7 @@ struct Mc2State {
     ~Mc2State();
 };
 constexpr int kMc2MaxTiles = 16384;
+constexpr int kMc2AgBlocks = 8 * 512;   // arrival counters of the push-form AllGather: ranks x 128-row blocks per rank
 constexpr int kMc2CtlWords = 16 + 8 * 512;
 
 HcclResult Mc2Matmul(const void* a, const void* b, void* out, uint64_t m, uint64_t n, uint64_t k, int transA, int transB,

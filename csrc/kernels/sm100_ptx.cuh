@@ -108,6 +108,18 @@ __device__ __forceinline__ void BulkWaitRead(int pending)
 }
 // Waits until every bulk group of this thread has completed, writes included.
 __device__ __forceinline__ void BulkWaitAll() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Waits until at most `pending` of the most recent bulk groups are incomplete (their writes not yet performed).
+__device__ __forceinline__ void BulkWaitGroup(int pending)
+{
+    switch (pending) {
+        case 0: asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); break;
+        case 1: asm volatile("cp.async.bulk.wait_group 1;" ::: "memory"); break;
+        case 2: asm volatile("cp.async.bulk.wait_group 2;" ::: "memory"); break;
+        case 3: asm volatile("cp.async.bulk.wait_group 3;" ::: "memory"); break;
+        case 4: asm volatile("cp.async.bulk.wait_group 4;" ::: "memory"); break;
+        default: asm volatile("cp.async.bulk.wait_group 5;" ::: "memory"); break;
+    }
+}
 
 // Generic-proxy writes (plain stores by other threads / CTAs / GPUs) must be
 // made visible to the async proxy (TMA) with this fence, on both sides of the

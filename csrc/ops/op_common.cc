@@ -33,7 +33,7 @@ uint64_t AlignUp(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
 int BlocksFor(const CommImpl* c, uint64_t bytesPerRank, DevAlg alg)
 {
     const int maxB = c->MaxBlocks();
-    if (alg == DALG_AR_LL || alg == DALG_AG_LL) {
+    if (alg == DALG_AR_LL || alg == DALG_AG_LL || alg == DALG_RS_LL || alg == DALG_BCAST_LL || alg == DALG_A2A_LL) {
         int nb = (int)((bytesPerRank + 4095) / 4096);   // 512 threads x 8 payload bytes: one line per thread while blocks last
         return std::max(1, std::min(nb, maxB));
     }
@@ -220,6 +220,39 @@ struct Exec {
             if (maxCnt == 0) break;
         }
         return HCCL_SUCCESS;
+    }
+
+    // ---- small-message forms of ReduceScatter / Broadcast / AlltoAll: every pair moves `pair` bytes as LL lines ----
+    HcclResult LLExchange() const
+    {
+        CollArgs a;
+        memset(&a, 0, sizeof(a));
+        a.op = (int)p.redOp;
+        uint64_t pair = 0;
+        if (p.op == HCCL_CMD_REDUCE_SCATTER) {
+            pair = p.count * es;
+            a.in = (const char*)p.send;
+            a.out = (char*)p.recv;
+            for (int q = 0; q < P; ++q) { a.cnt2[q] = a.cnt[q] = pair; a.dsp2[q] = pair * (uint64_t)q; }
+            a.cnt2[me] = 0;
+        } else if (p.op == HCCL_CMD_BROADCAST) {
+            pair = p.count * es;
+            a.in = (const char*)p.send;
+            a.out = (char*)p.send;
+            a.root = (int)p.root;
+            if (me == (int)p.root) { for (int q = 0; q < P; ++q) a.cnt2[q] = q == me ? 0 : pair; }
+            else a.cnt[p.root] = pair;
+        } else {
+            pair = p.sendCounts[0] * es;
+            a.in = (const char*)p.send;
+            a.out = (char*)p.recv;
+            for (int q = 0; q < P; ++q) { a.cnt2[q] = a.cnt[q] = pair; a.dsp2[q] = a.dsp[q] = pair * (uint64_t)q; }
+            a.cnt2[me] = 0;
+        }
+        if (pair > kLLMaxPayload) return HCCL_E_INTERNAL;
+        a.bytes = pair;
+        if (pair == 0) return HCCL_SUCCESS;
+        return Launch(a, pair);
     }
 
     // ---- AllGather(V) ----------------------------------------------------------
@@ -432,11 +465,11 @@ struct Exec {
     {
         switch (p.op) {
             case HCCL_CMD_ALLREDUCE: case HCCL_CMD_REDUCE: return AllReduceLike();
-            case HCCL_CMD_REDUCE_SCATTER: case HCCL_CMD_REDUCE_SCATTER_V: return ReduceScatterLike();
+            case HCCL_CMD_REDUCE_SCATTER: case HCCL_CMD_REDUCE_SCATTER_V: return dalg == DALG_RS_LL ? LLExchange() : ReduceScatterLike();
             case HCCL_CMD_ALLGATHER: case HCCL_CMD_ALLGATHER_V: return AllGatherLike();
-            case HCCL_CMD_BROADCAST: return Broadcast();
+            case HCCL_CMD_BROADCAST: return dalg == DALG_BCAST_LL ? LLExchange() : Broadcast();
             case HCCL_CMD_SCATTER: return Scatter();
-            case HCCL_CMD_ALLTOALL: case HCCL_CMD_ALLTOALLV: case HCCL_CMD_ALLTOALLVC: return AlltoAllLike();
+            case HCCL_CMD_ALLTOALL: case HCCL_CMD_ALLTOALLV: case HCCL_CMD_ALLTOALLVC: return dalg == DALG_A2A_LL ? LLExchange() : AlltoAllLike();
             case HCCL_CMD_SEND: case HCCL_CMD_RECEIVE: case HCCL_CMD_BATCH_SEND_RECV: return PointToPoint();
             case HCCL_CMD_BARRIER: {
                 CollArgs a;

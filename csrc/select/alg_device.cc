@@ -193,6 +193,47 @@ void RegisterAll()
             R.Register(e);
         }
     }
+    // ---------------- small-message forms: flag-in-data lines, one latency, no barrier
+    {
+        AlgEntry e = Base("P2pReduceScatterSoleMeshLL", HCCL_CMD_REDUCE_SCATTER, HCCL_ENGINE_P2P, "MeshLL", DALG_RS_LL, AlgoType::LL);
+        e.attrs.dtypeMask = kReduceTypes;
+        e.attrs.maxBytes = 256 * 1024;            // whole input; a pair moves 1/p of it
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.B = 2.0 * (m.p - 1) / m.p * m.link() + 2.0 * m.copy();
+            c.C = m.lm.launchUs + m.lm.llHopUs;
+            c.net = NetType::LOCAL;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+    }
+    {
+        AlgEntry e = Base("P2pBroadcastSoleMeshLL", HCCL_CMD_BROADCAST, HCCL_ENGINE_P2P, "MeshLL", DALG_BCAST_LL, AlgoType::LL);
+        e.attrs.maxBytes = 64 * 1024;             // the root writes the message (doubled by the flags) to every peer
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.B = 2.0 * (m.p - 1) * m.link() + 2.0 * m.copy();
+            c.C = m.lm.launchUs + m.lm.llHopUs;
+            c.net = NetType::LOCAL;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+    }
+    {
+        AlgEntry e = Base("P2pAlltoAllSoleMeshLL", HCCL_CMD_ALLTOALL, HCCL_ENGINE_P2P, "MeshLL", DALG_A2A_LL, AlgoType::LL);
+        e.attrs.maxBytes = 256 * 1024;
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.B = 2.0 * (m.p - 1) / m.p * m.link() + 2.0 * m.copy();
+            c.C = m.lm.launchUs + m.lm.llHopUs;
+            c.net = NetType::LOCAL;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+    }
     // ---------------- Broadcast
     {
         AlgEntry e = Base("P2pBroadcastSoleMeshOneShot", HCCL_CMD_BROADCAST, HCCL_ENGINE_P2P, "MeshOneShot", DALG_BCAST_ONESHOT, AlgoType::ONESHOT);

@@ -181,10 +181,12 @@ class Communicator:
     def _stream(self, stream=None):
         if self.kind == "host":
             return c_void_p(0)
+        if stream is not None:
+            return c_void_p(stream.cuda_stream)
         import torch
 
-        s = stream if stream is not None else torch.cuda.current_stream()
-        return c_void_p(s.cuda_stream)
+        # the raw handle of the current stream, without building a torch.cuda.Stream object on every call
+        return c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device()))
 
     # ------------------------------------------------------------------ operators
     def all_reduce(self, send, recv=None, op: ReduceOp = ReduceOp.SUM, stream=None):

@@ -42,8 +42,12 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: 
 
 def all_gather_matmul(comm: Communicator, a_shard: torch.Tensor, weight: torch.Tensor, *, weight_is_kn: bool = False,
                       out: torch.Tensor | None = None, gathered: torch.Tensor | None = None, stream=None):
-    """``out = all_gather(a_shard, dim=0) @ W``; ``a_shard`` must be symmetric memory (``comm.empty``).
-    Returns ``(out, gathered)`` - the gathered activations are a by-product the backward pass reuses."""
+    """``out = all_gather(a_shard, dim=0) @ W``.  Returns ``(out, gathered)`` - the gathered activations are a
+    by-product the backward pass reuses.
+
+    Two forms.  Push (faster: posted writes over NVLink): pass ``gathered`` allocated with ``comm.empty``; every rank
+    stores its shard into all ranks' gathered buffers and ``a_shard`` may be any tensor.  Pull: ``a_shard`` is
+    symmetric memory and ``gathered`` a plain (or omitted) tensor; every rank reads the peers' shards."""
     m_per, k = a_shard.shape
     n = weight.shape[1] if weight_is_kn else weight.shape[0]
     p = comm.world_size

@@ -38,6 +38,10 @@ class TPContext:
             self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self._sym = {}
         self.launches = 0                 # kernels of this library launched (bench accounting)
+        # AllGather->Matmul form: "push" (every rank writes its shard into the others' symmetric gathered buffers) or
+        # "pull" (every rank reads the peers' symmetric shards)
+        import os
+        self.ag_form = os.environ.get("HCCL_TP_AG_FORM", "push")
 
     def sym_buffer(self, key, shape, dtype=torch.bfloat16):
         """A persistent symmetric buffer per call site and shape (allocated collectively on first use)."""
@@ -67,9 +71,15 @@ class _ColumnParallel(torch.autograd.Function):
             fctx.ctx, fctx.key = ctx, key
             return _mm(ctx, x_shard, weight)
         if ctx.impl == "hccl":
-            a = ctx.sym_buffer(("cp_in", key), x_shard.shape)
-            a.copy_(x_shard)
-            out, gathered = mc2.all_gather_matmul(ctx.comm, a, weight)
+            # push form: the gathered activations land in a persistent symmetric buffer of this call site (every rank
+            # writes its shard into the others' buffers); the shard itself is read where it is
+            if ctx.ag_form == "push":
+                gathered = ctx.sym_buffer(("cp_gathered", key), (x_shard.shape[0] * ctx.world, x_shard.shape[1]))
+                out, gathered = mc2.all_gather_matmul(ctx.comm, x_shard.contiguous(), weight, gathered=gathered)
+            else:
+                a = ctx.sym_buffer(("cp_in", key), x_shard.shape)
+                a.copy_(x_shard)
+                out, gathered = mc2.all_gather_matmul(ctx.comm, a, weight)
             ctx.launches += 1
         else:
             gathered = torch.empty((x_shard.shape[0] * ctx.world, x_shard.shape[1]), device=x_shard.device, dtype=x_shard.dtype)
@@ -123,9 +133,13 @@ class _RowParallel(torch.autograd.Function):
             dw = _mm(ctx, dy_shard, x, trans_a=True, trans_b=False)
             return dx, dw, None, None
         if ctx.impl == "hccl":
-            a = ctx.sym_buffer(("rp_dy", fctx.key), dy_shard.shape)
-            a.copy_(dy_shard)
-            dx, dy_full = mc2.all_gather_matmul(ctx.comm, a, weight, weight_is_kn=True)
+            if ctx.ag_form == "push":
+                dy_full = ctx.sym_buffer(("rp_dy_gathered", dy_shard.shape[1]), (dy_shard.shape[0] * ctx.world, dy_shard.shape[1]))
+                dx, dy_full = mc2.all_gather_matmul(ctx.comm, dy_shard, weight, weight_is_kn=True, gathered=dy_full)
+            else:
+                a = ctx.sym_buffer(("rp_dy", fctx.key), dy_shard.shape)
+                a.copy_(dy_shard)
+                dx, dy_full = mc2.all_gather_matmul(ctx.comm, a, weight, weight_is_kn=True)
             ctx.launches += 1
         else:
             dy_full = torch.empty((dy_shard.shape[0] * ctx.world, dy_shard.shape[1]), device=dy_shard.device, dtype=dy_shard.dtype)

@@ -100,7 +100,15 @@ DTYPE_SIZE = {
 }
 
 
+_TORCH_MAP = None
+_NUMPY_MAP = None
+
+
 def torch_dtype_map():
+    """torch dtype -> DataType (built once: operators look it up on every call)."""
+    global _TORCH_MAP
+    if _TORCH_MAP is not None:
+        return _TORCH_MAP
     import torch
 
     m = {
@@ -112,18 +120,23 @@ def torch_dtype_map():
                      ("float8_e4m3fn", DataType.FP8E4M3), ("float8_e5m2", DataType.FP8E5M2)):
         if hasattr(torch, name):
             m[getattr(torch, name)] = dt
+    _TORCH_MAP = m
     return m
 
 
 def numpy_dtype_map():
+    global _NUMPY_MAP
+    if _NUMPY_MAP is not None:
+        return _NUMPY_MAP
     import numpy as np
 
-    return {
+    _NUMPY_MAP = {
         np.dtype(np.int8): DataType.INT8, np.dtype(np.int16): DataType.INT16, np.dtype(np.int32): DataType.INT32,
         np.dtype(np.float16): DataType.FP16, np.dtype(np.float32): DataType.FP32, np.dtype(np.int64): DataType.INT64,
         np.dtype(np.uint64): DataType.UINT64, np.dtype(np.uint8): DataType.UINT8, np.dtype(np.uint16): DataType.UINT16,
         np.dtype(np.uint32): DataType.UINT32, np.dtype(np.float64): DataType.FP64,
     }
+    return _NUMPY_MAP
 
 
 class HcclError(RuntimeError):

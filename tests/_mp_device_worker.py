@@ -104,14 +104,23 @@ def scenario_mc2(comm, rank, world):
         w = (torch.randn(n, k, device="cuda") * 0.1).bfloat16()          # [N, K]
         a = comm.empty((m_per, k), torch.bfloat16)
         a.copy_(shards[rank])
-        for rep in range(3):
+        full = torch.cat(shards)
+        ref = full.float() @ w.float().t()
+        for rep in range(3):          # pull form: the shard is symmetric memory, the gathered buffer is not
             out, gathered = mc2.all_gather_matmul(comm, a, w)
             torch.cuda.synchronize()
-            full = torch.cat(shards)
             assert torch.equal(gathered, full), "gathered activations differ"
-            ref = full.float() @ w.float().t()
             err = (out.float() - ref).abs().max().item()
             assert err <= 2e-2 * ref.abs().max().item() + 1e-2, f"AG-matmul err {err}"
+        g_sym = comm.empty((m_per * world, k), torch.bfloat16)
+        for rep in range(3):          # push form: the gathered buffer is symmetric memory, the shard is a plain tensor
+            g_sym.zero_()
+            torch.cuda.synchronize()
+            out, gathered = mc2.all_gather_matmul(comm, shards[rank], w, gathered=g_sym)
+            torch.cuda.synchronize()
+            assert torch.equal(gathered, full), "gathered activations differ (push form)"
+            err = (out.float() - ref).abs().max().item()
+            assert err <= 2e-2 * ref.abs().max().item() + 1e-2, f"AG-matmul (push form) err {err}"
         # matmul -> reduce-scatter: every rank has its own A [M, K] and W [N, K]
         M = m_per * world
         As = [(torch.randn(M, k, device="cuda") * 0.5).bfloat16() for _ in range(world)]

@@ -318,3 +318,49 @@ def test_strict_determinism_repeats_bitwise():
         for c in cs:
             c.destroy()
     assert torch.equal(results[0], results[1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int8, torch.int64])
+@pytest.mark.parametrize("n", [1, 5, 1023, 4097])
+def test_small_message_ll_forms(comms, dtype, n):
+    """ReduceScatter, Broadcast and AlltoAll of small messages run as flag-in-data exchanges (no barrier); two rounds
+    back to back so that both parities of the line slots are used."""
+    p = len(comms)
+    for rnd in range(2):
+        ins = [_rand(n * p, dtype, 900 + 17 * rnd + r) for r in range(p)]
+        outs = [torch.empty(n, device="cuda", dtype=dtype) for _ in range(p)]
+        for c, x, y in zip(comms, ins, outs):
+            c.reduce_scatter(x, y)
+        es = ins[0].element_size()
+        small = n * p * es <= 256 * 1024           # the flag-in-data forms take inputs up to 256 KiB
+        if small:
+            assert comms[0].last_algorithm() == "P2pReduceScatterSoleMeshLL"
+        torch.cuda.synchronize()
+        ref = torch.stack([x.double() for x in ins]).sum(0)
+        for r, y in enumerate(outs):
+            if dtype.is_floating_point:
+                torch.testing.assert_close(y.double(), ref[r * n:(r + 1) * n], rtol=_tol(dtype), atol=_tol(dtype) * p)
+            else:
+                assert torch.equal(y.long(), ref[r * n:(r + 1) * n].long().to(dtype).long())
+
+        a2a_out = [torch.empty(n * p, device="cuda", dtype=dtype) for _ in range(p)]
+        for c, x, y in zip(comms, ins, a2a_out):
+            c.all_to_all(x, y)
+        if small:
+            assert comms[0].last_algorithm() == "P2pAlltoAllSoleMeshLL"
+        torch.cuda.synchronize()
+        for r, y in enumerate(a2a_out):
+            want = torch.cat([ins[q][r * n:(r + 1) * n] for q in range(p)])
+            assert torch.equal(y.view(torch.uint8), want.view(torch.uint8))
+
+        root = (rnd + 1) % p
+        bufs = [x[:n].clone() for x in ins]
+        want = bufs[root].clone()
+        for c, b in zip(comms, bufs):
+            c.broadcast(b, root)
+        if n * es <= 64 * 1024:
+            assert comms[0].last_algorithm() == "P2pBroadcastSoleMeshLL"
+        torch.cuda.synchronize()
+        for b in bufs:
+            assert torch.equal(b.view(torch.uint8), want.view(torch.uint8))
+    assert comms[0].async_error() == hb.Result.SUCCESS
