@@ -31,6 +31,7 @@ def parse():
     ap.add_argument("--layers", type=int, default=8)
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--tiny", action="store_true", help="small model for smoke runs (not a benchmark result)")
+    ap.add_argument("--graph", default="auto", choices=["auto", "off"], help="capture the whole step in one CUDA graph (falls back to eager)")
     return ap.parse_args()
 
 
@@ -72,7 +73,7 @@ def main():
     cfg.n_layers = args.layers if not args.tiny else cfg.n_layers
     torch.manual_seed(1234 + rank)
     model = LlamaStack(cfg, ctx)
-    opt = torch.optim.AdamW(model.parameters(), lr=1e-5, fused=True)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-5, fused=True, capturable=True)
     seq = args.seq
 
     # synthetic token ids, uniform over the vocabulary, one fresh pinned host batch per step
@@ -88,9 +89,45 @@ def main():
         opt.step()
         return loss
 
+    # The whole step (forward, backward, optimizer) as ONE CUDA graph: at 8 GPUs the kernels are short and an eager
+    # step is bound by launch gaps.  Captured after the eager warm-up (all symmetric buffers and library state exist);
+    # every flag / epoch the fused kernels use lives in device memory, so a replay runs the same protocol again.
+    graph, static_loss, graph_note, launches_per_step = None, None, "off", 0
+
+    def capture():
+        nonlocal graph, static_loss, graph_note, launches_per_step
+        try:
+            g_ = torch.cuda.CUDAGraph()
+            opt.zero_grad(set_to_none=True)
+            l0 = ctx.launches
+            with torch.cuda.graph(g_):
+                loss_ = model.loss(dev_tokens)
+                loss_.backward()
+                opt.step()
+            launches_per_step = ctx.launches - l0
+            graph, static_loss, graph_note = g_, loss_, "whole step captured"
+        except Exception as ex:                      # noqa: BLE001  (any capture failure falls back to the eager step)
+            torch.cuda.synchronize()
+            graph, graph_note = None, f"capture failed, eager step: {type(ex).__name__}: {str(ex)[:120]}"
+
+    def step_any(tokens_dev):
+        """One step on tokens already on the device (graph replay when captured)."""
+        if graph is not None:
+            dev_tokens.copy_(tokens_dev, non_blocking=True)
+            graph.replay()
+            ctx.launches += launches_per_step
+            return static_loss
+        return step_device(tokens_dev)
+
     def step_e2e(i):
-        dev_tokens.copy_(host_batches[i], non_blocking=True)          # H2D of this step's inputs from pinned memory
-        loss = step_device(dev_tokens)
+        if graph is not None:
+            dev_tokens.copy_(host_batches[i], non_blocking=True)      # H2D of this step's inputs from pinned memory
+            graph.replay()
+            ctx.launches += launches_per_step
+            loss = static_loss
+        else:
+            dev_tokens.copy_(host_batches[i], non_blocking=True)
+            loss = step_device(dev_tokens)
         loss_host.copy_(loss.detach(), non_blocking=True)             # D2H of the step's result
         torch.cuda.current_stream().synchronize()
         return float(loss_host)
@@ -105,12 +142,19 @@ def main():
     for i in range(args.warmup):
         step_device(dev_inputs[i])
     barrier()
+    if args.graph != "off":
+        capture()
+        barrier()
+        if graph is not None:
+            for i in range(min(2, args.warmup)):                       # warm the replay path as well
+                step_any(dev_inputs[i])
+            barrier()
     launches0 = ctx.launches
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(gpu_index=local) as clocks:
         ev0.record()
         for i in range(args.steps):
-            step_device(dev_inputs[args.warmup + i])
+            step_any(dev_inputs[args.warmup + i])
         ev1.record()
         barrier()
     ms = ev0.elapsed_time(ev1) / args.steps
@@ -138,7 +182,7 @@ def main():
             "config": {"model": "llama3-70b-shaped decoder stack" + (" (tiny smoke variant)" if args.tiny else ""), "layers": cfg.n_layers,
                        "hidden": cfg.hidden, "ffn": cfg.ffn, "heads": cfg.n_heads, "kv_heads": cfg.n_kv_heads, "global_batch": 1, "seq_len": seq,
                        "parallelism": f"tp{world}+sp", "optimizer": "AdamW(fused)", "loss": "mean square of final hidden states",
-                       "l2": "inputs larger than L2: >13 GB of weights stream through per step"},
+                       "l2": "inputs larger than L2: >13 GB of weights stream through per step", "cuda_graph": graph_note},
             "clocks": clocks.summary(),
             "e2e": {"value": tokens / (e2e_ms / 1000.0), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": seq * 8, "d2h_bytes_per_step": 4,
                     "last_loss": last},

@@ -361,19 +361,20 @@ __device__ __forceinline__ void GatherPushWorker(const DevComm& c, const GemmArg
 // thread): the reduction is bound by bytes in flight from local memory, and a worker has to keep up with the tiles
 // of about eight GEMM CTAs.  Partials are summed in rank order in fp32.
 template <int BN, int U, int PMAX>
-__device__ __forceinline__ void ReduceTile(const GemmArgs& g, const __nv_bfloat16* xbase, size_t slotElems, int mtLocal, int nt)
+__device__ __forceinline__ void ReduceTile(const GemmArgs& g, const __nv_bfloat16* xbase, size_t slotElems, int mtLocal, int nt,
+                                           int rowLimit, int tid, int nThreads)
 {
     const int vecPerRow = BN / 8;
     const int total = kBM * vecPerRow;
-    for (int v = threadIdx.x; v < total; v += U * (int)blockDim.x) {
+    for (int v = tid; v < total; v += U * nThreads) {
         int r[U], col[U];
         bool valid[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int vv = v + u * (int)blockDim.x;
+            const int vv = v + u * nThreads;
             r[u] = mtLocal * kBM + vv / vecPerRow;
             col[u] = nt * BN + (vv % vecPerRow) * 8;
-            valid[u] = vv < total && r[u] < g.mPerRank && col[u] < g.N;
+            valid[u] = vv < total && r[u] < rowLimit && col[u] < g.N;
         }
         uint4 raw[U][PMAX];
 #pragma unroll
@@ -431,9 +432,9 @@ __device__ __forceinline__ void ReduceWorker(const DevComm& c, const GemmArgs& g
         }
         __syncthreads();
         if (!s_ok) break;
-        if (g.nRanks <= 2) ReduceTile<BN, 8, 2>(g, xbase, slotElems, mtLocal, nt);
-        else if (g.nRanks <= 4) ReduceTile<BN, 4, 4>(g, xbase, slotElems, mtLocal, nt);
-        else ReduceTile<BN, 2, kMaxDevRanks>(g, xbase, slotElems, mtLocal, nt);
+        if (g.nRanks <= 2) ReduceTile<BN, 8, 2>(g, xbase, slotElems, mtLocal, nt, g.mPerRank, (int)threadIdx.x, (int)blockDim.x);
+        else if (g.nRanks <= 4) ReduceTile<BN, 4, 4>(g, xbase, slotElems, mtLocal, nt, g.mPerRank, (int)threadIdx.x, (int)blockDim.x);
+        else ReduceTile<BN, 2, kMaxDevRanks>(g, xbase, slotElems, mtLocal, nt, g.mPerRank, (int)threadIdx.x, (int)blockDim.x);
     }
     (void)abortWord;
 }
@@ -623,7 +624,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 
                 if (MODE == MODE_RS || MODE == MODE_AR) {
                     // publish the tile: all 128 epilogue threads have stored, then one thread raises the flag(s)
-                    __threadfence_system();
+                    // the barrier orders all epilogue threads' stores before the publishing thread, whose fence (cumulative)
+                    // then covers them: one system fence per tile instead of one per thread
                     NamedBarSync(1, kEpilogueThreads);
                     const int tileId = MODE == MODE_RS ? ((mt % (g.mPerRank / kBM)) * g.tilesN + nt) : (mt * g.tilesN + nt);
                     if (MODE == MODE_RS) {
@@ -648,30 +650,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                         }
                         NamedBarSync(1, kEpilogueThreads);
                         if (!s_arOk) { ok = false; break; }
-                        const int vecPerRow = BN / 8;
-                        const int rowsHere = min(kBM, g.M - mt * kBM);
-                        for (int v = threadIdx.x - 64; v < rowsHere * vecPerRow; v += kEpilogueThreads) {
-                            const int r = mt * kBM + v / vecPerRow;
-                            const int col = nt * BN + (v % vecPerRow) * 8;
-                            if (col >= g.N) continue;
-                            float accf[8];
-#pragma unroll
-                            for (int k = 0; k < 8; ++k) accf[k] = 0.f;
-                            for (int q = 0; q < g.nRanks; ++q) {
-                                const uint4 raw = *reinterpret_cast<const uint4*>(g.xchg[g.rank] + parityOff + (size_t)q * g.M * g.N + (size_t)r * g.N + col);
-                                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-                                for (int k = 0; k < 4; ++k) {
-                                    const float2 f = __bfloat1622float2(h[k]);
-                                    accf[2 * k] += f.x;
-                                    accf[2 * k + 1] += f.y;
-                                }
-                            }
-                            uint4 o;
-                            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-                            for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(accf[2 * k], accf[2 * k + 1]);
-                            *reinterpret_cast<uint4*>(g.out + (size_t)r * g.ldc + col) = o;
+                        {
+                            // this rank's copy of every rank's partial of the tile, summed in rank order
+                            const __nv_bfloat16* xb = g.xchg[g.rank] + parityOff;
+                            const size_t slot = (size_t)g.M * g.N;
+                            const int tid = (int)threadIdx.x - 64;
+                            if (g.nRanks <= 2) ReduceTile<BN, 8, 2>(g, xb, slot, mt, nt, g.M, tid, kEpilogueThreads);
+                            else if (g.nRanks <= 4) ReduceTile<BN, 4, 4>(g, xb, slot, mt, nt, g.M, tid, kEpilogueThreads);
+                            else ReduceTile<BN, 2, kMaxDevRanks>(g, xb, slot, mt, nt, g.M, tid, kEpilogueThreads);
                         }
                     }
                 }

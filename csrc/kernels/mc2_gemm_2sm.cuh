@@ -292,7 +292,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 if (lane == 0) MbarArriveCluster(SmemAddr(&tmemEmpty[acc]) & kPeerBitMask);     // the leader's barrier
                 if (++acc == 2) { acc = 0; accPhase ^= 1u; }
                 if (MODE == MODE_RS) {
-                    __threadfence_system();
+                    // the barrier orders all epilogue threads' stores before the publishing thread, whose fence (cumulative)
+                    // then covers them: one system fence per tile instead of one per thread
                     NamedBarSync(1, kEpilogueThreads);
                     if (threadIdx.x == 64 && mt * kBM < g.M) {
                         const int dst = (mt * kBM) / g.mPerRank;

@@ -1,4 +1,7 @@
 #include "profiling.h"
+#include "param_check.h"
+#include <nvtx3/nvToolsExt.h>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <deque>
@@ -52,8 +55,22 @@ void ProfilingClear()
     s.done.clear();
 }
 
+// NVTX range per operator (visible in Nsight Systems / Compute timelines): on with HCCL_NVTX=1.  The header-only
+// NVTX v3 does nothing until a tool injects itself, so an enabled range costs a few nanoseconds without a profiler.
+static bool NvtxEnabled()
+{
+    static const bool on = [] { const char* e = getenv("HCCL_NVTX"); return e != nullptr && e[0] == '1'; }();
+    return on;
+}
+
 ProfilingScope::ProfilingScope(CommImpl* c, const OpParam& p, const char* alg, uint64_t bytes)
 {
+    if (NvtxEnabled()) {
+        char label[160];
+        snprintf(label, sizeof(label), "Hccl%s %s %llu B", CmdName(p.op), alg, (unsigned long long)bytes);
+        nvtxRangePushA(label);
+        nvtx_ = true;
+    }
     ProfState& s = S();
     if (s.level <= 0) return;
     on_ = true;
@@ -72,6 +89,7 @@ ProfilingScope::ProfilingScope(CommImpl* c, const OpParam& p, const char* alg, u
 
 ProfilingScope::~ProfilingScope()
 {
+    if (nvtx_) nvtxRangePop();
     if (!on_) return;
     ProfState& s = S();
     rec_.hostSubmitUs = hostUs_;

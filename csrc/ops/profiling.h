@@ -6,6 +6,7 @@
 // Here: a ring of records per process, filled when HCCL_PROFILING=1 (host
 // submit time always; device time from CUDA events recorded around the op on
 // its stream when HCCL_PROFILING=2), readable through HcclProfilingDump.
+// HCCL_NVTX=1 additionally wraps every operator in an NVTX range.
 #pragma once
 #include <cstdint>
 #include <string>
@@ -37,6 +38,7 @@ public:
     void SetHostUs(double us) { hostUs_ = us; }
 private:
     bool on_ = false;
+    bool nvtx_ = false;
     ProfRecord rec_{};
     double hostUs_ = 0;
     cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;

@@ -138,6 +138,24 @@ _sig("HcclMc2Matmul", R, c_void_p, c_void_p, c_void_p, c_uint64, c_uint64, c_uin
 _sig("HcclMc2AllGatherMatmul", R, c_void_p, c_void_p, c_void_p, c_void_p, c_uint64, c_uint64, c_uint64, c_int, c_void_p, c_void_p)
 _sig("HcclMc2MatmulReduceScatter", R, c_void_p, c_void_p, c_void_p, c_uint64, c_uint64, c_uint64, c_int, c_void_p, c_void_p)
 _sig("HcclMc2MatmulAllReduce", R, c_void_p, c_void_p, c_void_p, c_uint64, c_uint64, c_uint64, c_int, c_void_p, c_void_p)
+# fused element-wise kernels of the decoder stack
+
+
+def _sig_or_none(name, restype, *argtypes):
+    """Like _sig for entry points added after the first release of the ABI: None when the loaded library predates them
+    (callers raise a clear error instead of the import failing)."""
+    try:
+        return _sig(name, restype, *argtypes)
+    except AttributeError:
+        return None
+
+
+_sig_or_none("HcclFusedAddRmsNormFwd", R, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint64, c_uint32, ctypes.c_float, c_void_p)
+_sig_or_none("HcclFusedRmsNormBwdPartials", c_uint32, c_uint64)
+_sig_or_none("HcclFusedRmsNormBwd", R, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint64, c_uint32, c_void_p)
+_sig_or_none("HcclFusedSwigluFwd", R, c_void_p, c_void_p, c_uint64, c_uint32, c_void_p)
+_sig_or_none("HcclFusedSwigluBwd", R, c_void_p, c_void_p, c_void_p, c_uint64, c_uint32, c_void_p)
+_sig_or_none("HcclFusedRope", R, c_void_p, c_uint64, c_void_p, c_uint64, c_void_p, c_void_p, c_uint64, c_uint32, c_uint32, c_int, c_void_p)
 # MoE
 class HcclMoeConfig(ctypes.Structure):
     _fields_ = [("nTokens", c_uint32), ("hidden", c_uint32), ("topk", c_uint32), ("nExperts", c_uint32), ("capacity", c_uint32)]

@@ -14,6 +14,7 @@ import math
 import torch
 import torch.nn.functional as F
 
+from ..ops import fused
 from ..parallel.tp_layers import ColumnParallelLinear, RowParallelLinear, TPContext
 
 
@@ -46,14 +47,6 @@ def rope_tables(seq, dim, theta, device):
     return f.cos(), f.sin()
 
 
-def apply_rope(x, cos, sin):
-    # x [S, H, D]; rotate pairs (first half, second half)
-    d = x.shape[-1] // 2
-    x1, x2 = x[..., :d].float(), x[..., d:].float()
-    c, s = cos[:, None, :], sin[:, None, :]
-    return torch.cat((x1 * c - x2 * s, x2 * c + x1 * s), dim=-1).to(x.dtype)
-
-
 class DecoderLayer(torch.nn.Module):
     def __init__(self, cfg: LlamaConfig, ctx: TPContext, idx: int):
         super().__init__()
@@ -64,30 +57,30 @@ class DecoderLayer(torch.nn.Module):
         dev = "cuda"
         self.attn_norm = torch.nn.Parameter(torch.ones(cfg.hidden, device=dev, dtype=torch.bfloat16))
         self.ffn_norm = torch.nn.Parameter(torch.ones(cfg.hidden, device=dev, dtype=torch.bfloat16))
-        # keys are shared between layers: the symmetric staging buffers are reused layer after layer
-        self.qkv = ColumnParallelLinear(cfg.hidden, (cfg.n_heads + 2 * cfg.n_kv_heads) * cfg.head_dim, ctx, "qkv", cfg.init_std)
+        # Column-parallel layers keep their gathered input (a persistent symmetric buffer, saved for the backward pass),
+        # so their keys are per layer; the row-parallel layers' symmetric buffers are transient and shared.
+        self.qkv = ColumnParallelLinear(cfg.hidden, (cfg.n_heads + 2 * cfg.n_kv_heads) * cfg.head_dim, ctx, f"qkv{idx}", cfg.init_std)
         self.o = RowParallelLinear(cfg.n_heads * cfg.head_dim, cfg.hidden, ctx, "o", cfg.init_std)
-        self.gate_up = ColumnParallelLinear(cfg.hidden, 2 * cfg.ffn, ctx, "gate_up", cfg.init_std)
+        self.gate_up = ColumnParallelLinear(cfg.hidden, 2 * cfg.ffn, ctx, f"gate_up{idx}", cfg.init_std)
         self.down = RowParallelLinear(cfg.ffn, cfg.hidden, ctx, "down", cfg.init_std)
 
-    def forward(self, x, cos, sin):
-        cfg = self.cfg
-        h = F.rms_norm(x, (cfg.hidden,), self.attn_norm, cfg.norm_eps)
+    def forward(self, x, delta, cos, sin):
+        """x: residual stream [S/P, hidden]; delta: the previous block's output still to be added to it (or None).
+        Returns the updated stream and this layer's pending addition, so that every residual add is fused into the
+        RMSNorm that follows it."""
+        cfg, k_ = self.cfg, self.ctx.fused_ops
+        d = cfg.head_dim
+        x, h = fused.add_rms_norm(x, delta, self.attn_norm, cfg.norm_eps, use_kernels=k_)
         qkv = self.qkv(h)                                                     # [S, (hq + 2 hkv) * D]
         s = qkv.shape[0]
-        q, k, v = qkv.split([self.hq * cfg.head_dim, self.hkv * cfg.head_dim, self.hkv * cfg.head_dim], dim=-1)
-        q = apply_rope(q.view(s, self.hq, cfg.head_dim), cos, sin)
-        k = apply_rope(k.view(s, self.hkv, cfg.head_dim), cos, sin)
-        v = v.view(s, self.hkv, cfg.head_dim)
+        q = fused.rope(qkv[:, :self.hq * d].view(s, self.hq, d), cos, sin, use_kernels=k_)
+        k = fused.rope(qkv[:, self.hq * d:(self.hq + self.hkv) * d].view(s, self.hkv, d), cos, sin, use_kernels=k_)
+        v = qkv[:, (self.hq + self.hkv) * d:].view(s, self.hkv, d)
         attn = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None], is_causal=True,
                                               enable_gqa=self.hq != self.hkv)
-        attn = attn[0].transpose(0, 1).reshape(s, self.hq * cfg.head_dim)
-        x = x + self.o(attn)
-        h = F.rms_norm(x, (cfg.hidden,), self.ffn_norm, cfg.norm_eps)
-        gu = self.gate_up(h)
-        g, u = gu.chunk(2, dim=-1)
-        x = x + self.down(F.silu(g) * u)
-        return x
+        attn = attn[0].transpose(0, 1).reshape(s, self.hq * d)
+        x, h = fused.add_rms_norm(x, self.o(attn), self.ffn_norm, cfg.norm_eps, use_kernels=k_)
+        return x, self.down(fused.swiglu(self.gate_up(h), use_kernels=k_))
 
 
 class LlamaStack(torch.nn.Module):
@@ -111,9 +104,10 @@ class LlamaStack(torch.nn.Module):
         if self._rope is None or self._rope[0].shape[0] != s:
             self._rope = rope_tables(s, self.cfg.head_dim, self.cfg.rope_theta, x.device)
         cos, sin = self._rope
+        delta = None
         for layer in self.layers:
-            x = layer(x, cos, sin)
-        return F.rms_norm(x, (self.cfg.hidden,), self.final_norm, self.cfg.norm_eps)
+            x, delta = layer(x, delta, cos, sin)
+        return fused.add_rms_norm(x, delta, self.final_norm, self.cfg.norm_eps, use_kernels=self.ctx.fused_ops)[1]
 
     def loss(self, token_ids):
         """Scalar training signal: mean square of the final hidden states of this rank's sequence shard."""

@@ -42,6 +42,9 @@ class TPContext:
         # "pull" (every rank reads the peers' symmetric shards)
         import os
         self.ag_form = os.environ.get("HCCL_TP_AG_FORM", "push")
+        # residual add + RMSNorm, SwiGLU and rotary embedding as this library's single-pass kernels (the NCCL + cuBLAS
+        # comparison arm keeps the framework's element-wise kernels); HCCL_FUSED_ELEMENTWISE=0 turns them off
+        self.fused_ops = impl == "hccl" and os.environ.get("HCCL_FUSED_ELEMENTWISE", "1") != "0"
 
     def sym_buffer(self, key, shape, dtype=torch.bfloat16):
         """A persistent symmetric buffer per call site and shape (allocated collectively on first use)."""

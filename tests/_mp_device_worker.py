@@ -217,9 +217,108 @@ def scenario_peer_exit(comm, rank, world):
     os._exit(0)
 
 
+def scenario_model(rank, world, path):
+    """Two-layer TP+SP decoder stack: loss and gradients of the fused-kernel arm against the NCCL + cuBLAS arm built
+    from the same seed, for both AllGather->Matmul forms; two steps each (persistent symmetric buffers are reused)."""
+    import torch.distributed as dist
+
+    from hccl_b200.models import LlamaConfig, LlamaStack
+    from hccl_b200.parallel import TPContext
+
+    store = dist.FileStore(path + ".store", world)
+    dist.init_process_group("nccl", rank=rank, world_size=world, store=store, device_id=torch.device("cuda", torch.cuda.current_device()))
+    comm = Communicator.from_torch_distributed(config=hb.make_config(buffer_mib=64))
+    cfg = LlamaConfig.tiny(2)
+    seq = 128 * world
+    tokens = torch.randint(0, cfg.vocab, (seq,), generator=torch.Generator().manual_seed(5), dtype=torch.int64).cuda()
+
+    def run(impl, form):
+        os.environ["HCCL_TP_AG_FORM"] = form
+        ctx = TPContext(comm=comm if impl == "hccl" else None, group=None, impl=impl)
+        torch.manual_seed(77 + rank)
+        model = LlamaStack(cfg, ctx)
+        out = []
+        for _ in range(2):
+            model.zero_grad(set_to_none=True)
+            loss = model.loss(tokens)
+            loss.backward()
+            torch.cuda.synchronize()
+            out.append((loss.item(), {n: p.grad.float().clone() for n, p in model.named_parameters() if p.grad is not None}))
+        return out
+
+    ref = run("nccl", "pull")
+    for form in ("push", "pull"):
+        got = run("hccl", form)
+        for step, ((l0, g0), (l1, g1)) in enumerate(zip(ref, got)):
+            assert abs(l0 - l1) <= 2e-2 * abs(l0) + 1e-4, f"{form} step {step}: loss {l1} vs {l0}"
+            for name in g0:
+                denom = g0[name].abs().max().item() + 1e-8
+                err = (g0[name] - g1[name]).abs().max().item() / denom
+                assert err <= 6e-2, f"{form} step {step}: grad {name} differs by {err:.3f} of its max"
+    comm.destroy()
+    dist.destroy_process_group()
+    print(f"rank {rank} model ok", flush=True)
+
+
+def scenario_torch_backend(rank, world, path):
+    """Unmodified torch.distributed calls on the "hccl" backend, compared with local references."""
+    import torch.distributed as dist
+
+    import hccl_b200.torch_backend  # noqa: F401  (registers the backend)
+
+    store = dist.FileStore(path + ".store", world)
+    dist.init_process_group("hccl", rank=rank, world_size=world, store=store)
+    assert dist.get_backend() == "hccl"
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = [torch.Generator(device="cuda").manual_seed(50 + r) for r in range(world)]
+    xs = [torch.rand(5000, device="cuda", generator=g[r]) for r in range(world)]       # every rank can rebuild all inputs
+    t = xs[rank].clone()
+    dist.all_reduce(t)
+    torch.testing.assert_close(t, torch.stack(xs).sum(0), rtol=1e-5, atol=1e-5)
+    t = xs[rank].clone()
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    assert torch.equal(t, torch.stack(xs).max(0).values)
+    b = xs[rank].clone()
+    dist.broadcast(b, src=world - 1)
+    assert torch.equal(b, xs[world - 1])
+    out = torch.empty(world * 5000, device="cuda")
+    dist.all_gather_into_tensor(out, xs[rank])
+    assert torch.equal(out, torch.cat(xs))
+    outs = [torch.empty(5000, device="cuda") for _ in range(world)]
+    dist.all_gather(outs, xs[rank])
+    assert all(torch.equal(o, x) for o, x in zip(outs, xs))
+    n = 5000 // world * world
+    rs = torch.empty(n // world, device="cuda")
+    dist.reduce_scatter_tensor(rs, xs[rank][:n].contiguous())
+    want = torch.stack([x[:n] for x in xs]).sum(0)[rank * (n // world):(rank + 1) * (n // world)]
+    torch.testing.assert_close(rs, want, rtol=1e-5, atol=1e-5)
+    a2a = torch.empty(n, device="cuda")
+    dist.all_to_all_single(a2a, xs[rank][:n].contiguous())
+    per = n // world
+    assert torch.equal(a2a, torch.cat([xs[q][rank * per:(rank + 1) * per] for q in range(world)]))
+    r = xs[rank].clone()
+    dist.reduce(r, dst=0)
+    if rank == 0:
+        torch.testing.assert_close(r, torch.stack(xs).sum(0), rtol=1e-5, atol=1e-5)
+    if rank == 0:
+        dist.send(xs[0], dst=1)
+    elif rank == 1:
+        got = torch.empty(5000, device="cuda")
+        dist.recv(got, src=0)
+        assert torch.equal(got, xs[0])
+    dist.barrier()
+    torch.cuda.synchronize()
+    dist.destroy_process_group()
+    print(f"rank {rank} torch backend ok on {dev}", flush=True)
+
+
 def main():
     rank, world, path, scenario = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
     torch.cuda.set_device(rank % torch.cuda.device_count())
+    if scenario in ("torch_backend", "model"):
+        {"torch_backend": scenario_torch_backend, "model": scenario_model}[scenario](rank, world, path)
+        print(f"rank {rank} done", flush=True)
+        return
     info = rendezvous(rank, path)
     timeout_ms = 3000 if scenario == "peer_exit" else 0
     comm = Communicator.from_root_info(info, rank, world, hb.make_config(buffer_mib=64, exec_timeout_ms=timeout_ms))

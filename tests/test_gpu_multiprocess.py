@@ -65,3 +65,15 @@ def test_mc2_fused_multiprocess():
 def test_cuda_graph_capture_and_replay():
     codes, outs = _run(_world(), "graph")
     assert all(c == 0 for c in codes), "\n".join(outs)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_torch_distributed_backend():
+    codes, outs = _run(_world(), "torch_backend")
+    assert all(c == 0 for c in codes), "\n".join(outs)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_tp_model_gradients_match_nccl_arm():
+    codes, outs = _run(_world(), "model")
+    assert all(c == 0 for c in codes), "\n".join(outs)
