@@ -181,7 +181,7 @@ def main():
             "impl": args.impl,
             "config": {"model": "llama3-70b-shaped decoder stack" + (" (tiny smoke variant)" if args.tiny else ""), "layers": cfg.n_layers,
                        "hidden": cfg.hidden, "ffn": cfg.ffn, "heads": cfg.n_heads, "kv_heads": cfg.n_kv_heads, "global_batch": 1, "seq_len": seq,
-                       "parallelism": f"tp{world}+sp", "optimizer": "AdamW(fused)", "loss": "mean square of final hidden states",
+                       "parallelism": f"tp{world}+sp", "optimizer": "AdamW(fused)", "loss": "mean product of neighbouring features of the final hidden states",
                        "l2": "inputs larger than L2: >13 GB of weights stream through per step", "cuda_graph": graph_note},
             "clocks": clocks.summary(),
             "e2e": {"value": tokens / (e2e_ms / 1000.0), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": seq * 8, "d2h_bytes_per_step": 4,

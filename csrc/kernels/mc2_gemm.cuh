@@ -86,6 +86,11 @@ struct GemmArgs {
     int agPush;
     __nv_bfloat16* gatheredPeer[kMaxDevRanks];
     uint64_t* agReady[kMaxDevRanks];
+    // RS, switch-reduce form (xchgMc != nullptr): every rank keeps its whole partial product [M, N] in its OWN exchange
+    // buffer (local stores) and the owner of a row block reduces it with multimem.ld_reduce through the multicast
+    // alias xchgMc of the exchange buffers: the partials cross NVLink inside the switch's reduction, a GPU receives
+    // only its reduced block.
+    const __nv_bfloat16* xchgMc;
 };
 constexpr int kCtlEpoch = 0, kCtlTicket = 1, kCtlAbort = 2, kCtlReady = 16;
 
@@ -410,6 +415,39 @@ __device__ __forceinline__ void ReduceTile(const GemmArgs& g, const __nv_bfloat1
     }
 }
 
+// One output tile reduced by the switch: rows [mtLocal*128, +128) x cols [nt*BN, +BN) of this rank's row block, read
+// through the multicast alias (`mcBlock` points at this rank's row block inside it) with multimem.ld_reduce (bf16 in,
+// fp32 accumulation in the switch), eight requests in flight per thread (sixteen were measured four times SLOWER:
+// the switch-reduce path throttles beyond a number of outstanding requests per SM).
+template <int BN>
+__device__ __forceinline__ void SwitchReduceTile(const GemmArgs& g, const __nv_bfloat16* mcBlock, int mtLocal, int nt)
+{
+    constexpr int U = 8;
+    const int vecPerRow = BN / 8;
+    const int total = kBM * vecPerRow;
+    for (int v = threadIdx.x; v < total; v += U * (int)blockDim.x) {
+        uint4 val[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int vv = v + u * (int)blockDim.x;
+            const int r = mtLocal * kBM + vv / vecPerRow, col = nt * BN + (vv % vecPerRow) * 8;
+            if (vv < total && r < g.mPerRank && col < g.N) {
+                const __nv_bfloat16* p = mcBlock + (size_t)r * g.N + col;
+                asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(val[u].x), "=r"(val[u].y), "=r"(val[u].z), "=r"(val[u].w)
+                             : "l"(p)
+                             : "memory");
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int vv = v + u * (int)blockDim.x;
+            const int r = mtLocal * kBM + vv / vecPerRow, col = nt * BN + (vv % vecPerRow) * 8;
+            if (vv < total && r < g.mPerRank && col < g.N) *reinterpret_cast<uint4*>(g.out + (size_t)r * g.ldc + col) = val[u];
+        }
+    }
+}
+
 // ReduceScatter reduction: for every tile of the local row block, waits until all ranks have delivered their
 // partial (flag value == launch epoch), sums the P partials in rank order in fp32 and writes bf16 to `out`.
 // Tiles are visited in the order they complete (column tile major).
@@ -432,6 +470,10 @@ __device__ __forceinline__ void ReduceWorker(const DevComm& c, const GemmArgs& g
         }
         __syncthreads();
         if (!s_ok) break;
+        if (g.xchgMc != nullptr) {
+            SwitchReduceTile<BN>(g, g.xchgMc + (epoch & 1u) * g.xchgParityElems + (size_t)g.rank * g.mPerRank * g.N, mtLocal, nt);
+            continue;
+        }
         if (g.nRanks <= 2) ReduceTile<BN, 8, 2>(g, xbase, slotElems, mtLocal, nt, g.mPerRank, (int)threadIdx.x, (int)blockDim.x);
         else if (g.nRanks <= 4) ReduceTile<BN, 4, 4>(g, xbase, slotElems, mtLocal, nt, g.mPerRank, (int)threadIdx.x, (int)blockDim.x);
         else ReduceTile<BN, 2, kMaxDevRanks>(g, xbase, slotElems, mtLocal, nt, g.mPerRank, (int)threadIdx.x, (int)blockDim.x);
@@ -605,6 +647,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                         const int row = row0 + r;
                         const int dst = row / g.mPerRank;
                         if (row >= g.M || dst >= g.nRanks) return nullptr;
+                        // switch-reduce form: the partial stays in this rank's own buffer, laid out like the product
+                        if (g.xchgMc != nullptr) return g.xchg[g.rank] + parityOff + (size_t)row * g.N + (size_t)nt * BN;
                         return g.xchg[dst] + parityOff + (size_t)g.rank * g.mPerRank * g.N + (size_t)(row - dst * g.mPerRank) * g.N + (size_t)nt * BN;
                     });
                 } else {

@@ -279,6 +279,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                         const int row = row0 + r;
                         const int dst = row / g.mPerRank;
                         if (row >= g.M || dst >= g.nRanks) return nullptr;
+                        if (g.xchgMc != nullptr) return g.xchg[g.rank] + parityOff + (size_t)row * g.N + (size_t)nt * BN;
                         return g.xchg[dst] + parityOff + (size_t)g.rank * g.mPerRank * g.N + (size_t)(row - dst * g.mPerRank) * g.N + (size_t)nt * BN;
                     });
                 } else {

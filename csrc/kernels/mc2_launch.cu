@@ -142,22 +142,61 @@ bool Use2Sm()
     return v == 1;
 }
 
-// CTAs of a fused launch that move data instead of computing.  The gather workers of AllGather->Matmul are bound by
-// bytes in flight per SM, so they get more SMs (about one in five) than the reduce workers of Matmul->ReduceScatter
-// (one in nine, at most 16).  HCCL_MC2_AG_WORKERS / HCCL_MC2_RS_WORKERS override the counts (even, 2 .. 64).
-int WorkerCtas(bool gather)
+// CTAs of a fused launch that move data instead of computing, taken from the GEMM.  HCCL_MC2_AG_WORKERS /
+// HCCL_MC2_RS_WORKERS fix the counts (even, 2 .. 64); otherwise:
+int ForcedWorkers(bool gather)
 {
-    static int v[2] = {-1, -1};
-    int& r = v[gather ? 1 : 0];
-    if (r < 0) {
-        r = gather ? (std::min(32, std::max(2, SmCount() / 5)) & ~1) : (std::min(16, std::max(2, SmCount() / 9)) & ~1);
+    static int forced[2] = {-1, -1};
+    int& f = forced[gather ? 1 : 0];
+    if (f < 0) {
+        f = 0;
         const char* e = getenv(gather ? "HCCL_MC2_AG_WORKERS" : "HCCL_MC2_RS_WORKERS");
         if (e != nullptr) {
             const int n = atoi(e) & ~1;
-            if (n >= 2 && n <= 64) r = n;
+            if (n >= 2 && n <= 64) f = n;
         }
     }
-    return r;
+    return f;
+}
+
+// Gather workers of AllGather->Matmul are bound by bytes in flight per SM, so they may take up to about one SM in
+// five.  Inside SMs/9 .. SMs/5 the count is chosen so that the GEMM loses no wave (`tiles` output tiles on
+// (SMs - workers) / ctasPerTile slots); among the counts with the fewest waves the largest wins.
+int GatherWorkerCtas(int tiles, int ctasPerTile)
+{
+    if (ForcedWorkers(true) > 0) return ForcedWorkers(true);
+    const int sms = SmCount() & ~1;
+    const int lo = std::max(2, sms / 9) & ~1, hi = std::max(2, sms / 5) & ~1;
+    int best = lo, bestWaves = 1 << 30;
+    for (int w = lo; w <= hi; w += 2) {
+        const int slots = std::max(1, (sms - w) / ctasPerTile);
+        const int waves = (tiles + slots - 1) / slots;
+        if (waves <= bestWaves) { bestWaves = waves; best = w; }
+    }
+    return best;
+}
+
+// Reduce workers of Matmul->ReduceScatter have to finish an output tile in the time the GEMM produces one for them.
+// Measured under the GEMM's memory traffic: about 11.5 us per 128 x 256 tile through the switch, about 4.5 us x (P + 1)
+// when the P partials are read from local memory; a wave of 256 x 256 GEMM tiles takes about 5 ns x K.  The count
+// minimises max(GEMM time, reduction time) inside SMs/9 .. SMs/3; ties go to the fewer workers.
+int ReduceWorkerCtas(int gemmTiles, int ctasPerTile, int localTiles128, int k, int nRanks, bool switchReduce)
+{
+    if (ForcedWorkers(false) > 0) return ForcedWorkers(false);
+    const int sms = SmCount() & ~1;
+    const int lo = std::max(2, sms / 9) & ~1, hi = std::max(2, sms / 3) & ~1;
+    const double tTile = switchReduce ? 11.5 : 4.5 * (nRanks + 1);
+    const double tWave = 5e-3 * k * (ctasPerTile == 2 ? 1.0 : 0.5);
+    int best = lo;
+    double bestCost = 1e30;
+    for (int w = lo; w <= hi; w += 2) {
+        const int slots = std::max(1, (sms - w) / ctasPerTile);
+        const double gemm = (double)((gemmTiles + slots - 1) / slots) * tWave;
+        const double reduce = (double)((localTiles128 + w - 1) / w) * tTile;
+        const double cost = std::max(gemm, reduce) + tTile;
+        if (cost < bestCost - 1e-9) { bestCost = cost; best = w; }
+    }
+    return best;
 }
 
 template <int BN, int MODE>
@@ -230,7 +269,8 @@ HcclResult Mc2EnsureState(CommImpl* comm, uint64_t parityBytes)
         CHK_CUDA(cudaDeviceSynchronize());
         SymFree(&st->xchg);
         const uint64_t rounded = (parityBytes + (2u << 20) - 1) / (2u << 20) * (2u << 20);
-        CHK_RET(SymAlloc(*comm->bs, comm->device, (size_t)rounded * 2, false, GetEnvConfig().forceIpc, &st->xchg));
+        // with a multicast alias when the communicator runs NVLS: Matmul->ReduceScatter then reduces in the switch
+        CHK_RET(SymAlloc(*comm->bs, comm->device, (size_t)rounded * 2, comm->nvls(), GetEnvConfig().forceIpc, &st->xchg));
         st->xchgParityBytes = rounded;
     }
     return HCCL_SUCCESS;
@@ -334,10 +374,11 @@ HcclResult Mc2AllGatherMatmul(CommImpl* comm, const void* aShard, const void* b,
             g.agReady[q] = (uint64_t*)comm->mc2->flags.peer[q] + (size_t)comm->nRanks * kMc2MaxTiles;
         }
     }
-    const int workers = WorkerCtas(true);
+    const bool twoSm = Use2Sm() && mPerRank % 256 == 0;
+    const int workers = twoSm ? GatherWorkerCtas((g.M / 256) * g.tilesN, 2) : GatherWorkerCtas(g.tilesM * g.tilesN, 1);
     const int grid = SmCount() & ~1;
     g.nGemmCtas = grid - workers;
-    if (Use2Sm() && mPerRank % 256 == 0) {
+    if (twoSm) {
         g.bn = 256;
         CHK_RET(MapB(&tb, b, n, k, bMn, 128));
         return DispatchLayout2Sm<MODE_AG>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream, &taOwn);
@@ -369,10 +410,18 @@ HcclResult Mc2MatmulReduceScatter(CommImpl* comm, const void* a, const void* b, 
     g.tilesM = (int)(m / kBM);
     g.tilesN = (int)tilesN;
     g.mPerRank = (int)mPerRank;
-    const int workers = WorkerCtas(false);
+    // switch-reduce form unless determinism is asked for (the switch's summation order is unspecified) or
+    // HCCL_MC2_RS_P2P=1 keeps the peer-to-peer form
+    static const bool forceP2p = [] { const char* e = getenv("HCCL_MC2_RS_P2P"); return e != nullptr && e[0] == '1'; }();
+    if (comm->mc2->xchg.mc != nullptr && !forceP2p && comm->cfg.deterministic == Deterministic::OFF)
+        g.xchgMc = (const __nv_bfloat16*)comm->mc2->xchg.mc;
+    const bool twoSm = Use2Sm() && mPerRank % 256 == 0;
+    const int localTiles = (int)(mPerRank / kBM) * g.tilesN;
+    const int workers = twoSm ? ReduceWorkerCtas((g.M / 256) * g.tilesN, 2, localTiles, g.K, g.nRanks, g.xchgMc != nullptr)
+                              : ReduceWorkerCtas(g.tilesM * g.tilesN, 1, localTiles, g.K, g.nRanks, g.xchgMc != nullptr);
     const int grid = SmCount() & ~1;
     g.nGemmCtas = grid - workers;
-    if (Use2Sm() && mPerRank % 256 == 0) {
+    if (twoSm) {
         g.bn = 256;
         CHK_RET(MapB(&tb, b, n, k, bMn, 128));
         return DispatchLayout2Sm<MODE_RS>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream);

@@ -110,5 +110,8 @@ class LlamaStack(torch.nn.Module):
         return fused.add_rms_norm(x, delta, self.final_norm, self.cfg.norm_eps, use_kernels=self.ctx.fused_ops)[1]
 
     def loss(self, token_ids):
-        """Scalar training signal: mean square of the final hidden states of this rank's sequence shard."""
-        return self.forward(token_ids).float().pow(2).mean()
+        """Scalar training signal with non-trivial gradients: the mean product of neighbouring features of the final
+        hidden states of this rank's sequence shard.  (The mean SQUARE of an RMS-normalised output is constant, so its
+        gradients would be rounding noise.)"""
+        h = self.forward(token_ids).float()
+        return (h * h.roll(1, dims=-1)).mean()

@@ -1,0 +1,59 @@
+"""CPU-side checks of the Python layers that need no GPU: backend registration, reduce-op mapping, and the PyTorch
+expressions the fused element-wise kernels fall back to (and are compared against on the GPU)."""
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from hccl_b200.ops import fused
+
+
+def test_torch_backend_is_registered_and_maps_reduce_ops():
+    import hccl_b200.torch_backend as tb
+    from hccl_b200.types import ReduceOp
+
+    assert "HCCL" in dist.Backend._plugins
+    tb.register()                                   # idempotent
+    assert tb._red(dist.ReduceOp.SUM) == ReduceOp.SUM
+    assert tb._red(dist.ReduceOp.PRODUCT) == ReduceOp.PROD
+    assert tb._red(dist.ReduceOp.MAX) == ReduceOp.MAX
+    assert tb._red(dist.ReduceOp.MIN) == ReduceOp.MIN
+    try:
+        tb._red(dist.ReduceOp.BAND)
+        raised = False
+    except NotImplementedError:
+        raised = True
+    assert raised
+
+
+def test_fused_ops_take_the_reference_path_on_cpu_tensors():
+    torch.manual_seed(0)
+    x, d, w = torch.randn(6, 32), torch.randn(6, 32), torch.rand(32) + 0.5
+    x_out, h = fused.add_rms_norm(x, d, w, 1e-5)
+    assert torch.equal(x_out, x + d)
+    torch.testing.assert_close(h, F.rms_norm(x + d, (32,), w, 1e-5))
+    x2, h2 = fused.add_rms_norm(x, None, w, 1e-5)
+    assert x2 is x
+    torch.testing.assert_close(h2, F.rms_norm(x, (32,), w, 1e-5))
+    gu = torch.randn(5, 16)
+    torch.testing.assert_close(fused.swiglu(gu), F.silu(gu[:, :8]) * gu[:, 8:])
+    q = torch.randn(7, 2, 8)
+    ang = torch.rand(7, 4)
+    out = fused.rope(q, ang.cos(), ang.sin())
+    # a rotation preserves the norm of every (i, i + d/2) pair
+    torch.testing.assert_close(out[..., :4] ** 2 + out[..., 4:] ** 2, q[..., :4] ** 2 + q[..., 4:] ** 2)
+
+
+def test_decoder_stack_runs_on_cpu_with_reference_ops():
+    """World size 1, CPU tensors: the model code path (residual stream + pending delta) against a plain restatement."""
+    from hccl_b200.models.llama import rope_tables
+
+    torch.manual_seed(1)
+    s, hdim, heads, d = 16, 32, 2, 16
+    x = torch.randn(s, hdim)
+    w = torch.ones(hdim)
+    cos, sin = rope_tables(s, d, 10000.0, x.device)
+    x1, h1 = fused.add_rms_norm(x, None, w, 1e-5, use_kernels=False)
+    x2, h2 = fused.add_rms_norm(x1, h1, w, 1e-5, use_kernels=False)
+    torch.testing.assert_close(x2, x + F.rms_norm(x, (hdim,), w, 1e-5))
+    q = fused.rope(h2.view(s, heads, d), cos, sin, use_kernels=False)
+    assert q.shape == (s, heads, d)

@@ -62,6 +62,13 @@ def test_mc2_fused_multiprocess():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_mc2_fused_multiprocess_peer_to_peer_reduce_scatter():
+    # Matmul->ReduceScatter without the switch reduction: partial tiles pushed to the owner, reduced by worker CTAs
+    codes, outs = _run(_world(), "mc2", {"HCCL_MC2_RS_P2P": "1"})
+    assert all(c == 0 for c in codes), "\n".join(outs)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
 def test_cuda_graph_capture_and_replay():
     codes, outs = _run(_world(), "graph")
     assert all(c == 0 for c in codes), "\n".join(outs)
