@@ -41,7 +41,7 @@ def main():
         # HCCL is an Ascend/CANN library: its CMake build needs the CANN toolkit (find_cann_package(hcomm ...)) and its
         # device code is AscendC for dav-c310 / dav-920r1; there is no setup.py / pyproject to install and no CUDA path.
         print(json.dumps({"impl": "reference", "unavailable": "HCCL builds only against Ascend CANN (no pip-installable package, no CUDA/sm_100 "
-                          "path); pip install of /root/reference fails: neither setup.py nor pyproject.toml"}))
+                          "path); pip install of the reference tree fails: neither setup.py nor pyproject.toml"}))
         return 0
 
     import torch

@@ -1,7 +1,7 @@
 """MC2 fused matmul + collective kernels against NCCL + cuBLAS at the same shapes.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29512 \
-        bench/mc2_bench.py --out gpurun_out/mc2_8gpu.jsonl
+        bench/mc2_bench.py --out mc2_8gpu.jsonl
 
 Shapes (tensor parallel over the N launched GPUs, bf16, weights N(0, 0.02), activations N(0, 1)):
   AllGather->Matmul      gathered activations [8192, 8192] x weight shard [8192, 28672 / 8]

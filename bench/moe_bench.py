@@ -1,7 +1,7 @@
 """MoE expert-parallel dispatch + combine against an NCCL all_to_all_single implementation of the same routing.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29515 \
-        bench/moe_bench.py --out gpurun_out/moe_8gpu.jsonl
+        bench/moe_bench.py --out moe_8gpu.jsonl
 
 Config: 8192 tokens per rank, hidden 7168, bf16 activations N(0, 1), 256 experts (32 per rank at 8 ranks), top-8
 routing from router logits N(0, 1) seeded per rank (variable per-peer counts); dispatch quantises to fp8 e4m3 with one

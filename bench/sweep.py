@@ -2,7 +2,7 @@
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29511 \
         bench/sweep.py --ops all_reduce,all_gather,reduce_scatter,broadcast,all_to_all --dtypes bf16,fp32 \
-        --min-bytes 8 --max-bytes 1073741824 --out gpurun_out/sweep_8gpu.jsonl
+        --min-bytes 8 --max-bytes 1073741824 --out sweep_8gpu.jsonl
 
 Per (op, dtype, size): 20 warm-up + 100 timed iterations (fewer above 64 MiB), device-timed with CUDA events, max over
 ranks; algBW = bytes / time, busBW = algBW * factor.  `size` is the per-rank message size as in nccl-tests: the full

@@ -167,6 +167,8 @@ HcclResult HcclGetHcclBuffer(HcclComm comm, void** buffer, uint64_t* size)
 
 HcclResult HcclMemAlloc(HcclComm comm, uint64_t size, void** p) { CHK_PTR_NULL(comm); return static_cast<CommImpl*>(comm)->MemAlloc(size, p); }
 HcclResult HcclMemFree(HcclComm comm, void* p) { CHK_PTR_NULL(comm); return static_cast<CommImpl*>(comm)->MemFree(p); }
+HcclResult HcclCommRegister(HcclComm comm, void* devPtr, uint64_t size) { CHK_PTR_NULL(comm); return static_cast<CommImpl*>(comm)->RegisterBuffer(devPtr, size); }
+HcclResult HcclCommDeregister(HcclComm comm, void* devPtr) { CHK_PTR_NULL(comm); return static_cast<CommImpl*>(comm)->DeregisterBuffer(devPtr); }
 HcclResult HcclCommSymWinGet(HcclComm comm, const void* localPtr, uint32_t peerRank, void** peerPtr)
 {
     CHK_PTR_NULL(comm); CHK_PTR_NULL(peerPtr);
@@ -211,6 +213,7 @@ HcclResult HcclSelectorExplain(HcclComm comm, HcclCMDType op, uint64_t count, Hc
     d.bytes = count * es;
     if (op == HCCL_CMD_ALLGATHER || op == HCCL_CMD_REDUCE_SCATTER || op == HCCL_CMD_SCATTER || op == HCCL_CMD_ALLTOALL) d.bytes *= (uint64_t)c->nRanks;
     d.inRegistered = d.outRegistered = registered != 0;
+    d.inMulticast = d.outMulticast = registered != 0 && c->nvls();      // "registered" here means HcclMemAlloc memory
     Selection sel;
     HcclResult r = SelectAlgorithm(*c->selector, *c->topo, GetEnvConfig(), d, c->name, comm, c->cfg.bufferBytes, &sel);
     std::string s = (sel.alg ? "selected " + sel.alg->name + "\n" : std::string("selected none\n")) + FormatCostTable(sel);
@@ -233,6 +236,7 @@ HcclResult HcclCalcOpResource(HcclComm comm, HcclCMDType op, uint64_t count, Hcc
     const bool perRank = op == HCCL_CMD_ALLGATHER || op == HCCL_CMD_REDUCE_SCATTER || op == HCCL_CMD_SCATTER || op == HCCL_CMD_ALLTOALL;
     d.bytes = count * es * (perRank ? P : 1);
     d.inRegistered = d.outRegistered = registered != 0;
+    d.inMulticast = d.outMulticast = registered != 0 && c->nvls();      // "registered" here means HcclMemAlloc memory
     Selection sel;
     CHK_RET(SelectAlgorithm(*c->selector, *c->topo, GetEnvConfig(), d, c->name, comm, c->cfg.bufferBytes, &sel));
     snprintf(res->algName, sizeof(res->algName), "%s", sel.alg->name.c_str());

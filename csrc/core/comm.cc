@@ -302,6 +302,34 @@ HcclResult CommImpl::MemFree(void* ptr)
     return HCCL_E_NOT_FOUND;
 }
 
+HcclResult CommImpl::RegisterBuffer(void* ptr, uint64_t size)
+{
+    CHK_PTR_NULL(ptr);
+    if (size == 0) return HCCL_E_PARA;
+    if (emu_ || hostComm || nRanks == 1 || bs == nullptr) return HCCL_E_NOT_SUPPORT;
+    const char* peers[HCCL_MAX_DEVICE_RANKS];
+    if (Lookup(ptr, size, peers, nullptr)) return HCCL_SUCCESS;        // already symmetric (HcclMemAlloc) or registered
+    SymSegment seg;
+    CHK_RET(SymRegisterUser(*bs, ptr, size, &seg));
+    userSegs_.push_back(seg);
+    return HCCL_SUCCESS;
+}
+
+HcclResult CommImpl::DeregisterBuffer(void* ptr)
+{
+    for (size_t i = 0; i < userSegs_.size(); ++i) {
+        if (userSegs_[i].peer[rank] == ptr && userSegs_[i].transport == SymTransport::USER_IPC) {
+            CHK_CUDA(cudaDeviceSynchronize());
+            if (bs) CHK_RET(bs->Barrier());       // no peer still reads the buffer
+            SymFree(&userSegs_[i]);
+            userSegs_.erase(userSegs_.begin() + (long)i);
+            return HCCL_SUCCESS;
+        }
+    }
+    HCCL_ERROR("HcclCommDeregister: %p was not registered on this communicator", ptr);
+    return HCCL_E_NOT_FOUND;
+}
+
 bool CommImpl::Lookup(const void* p, uint64_t bytes, const char* peerPtr[HCCL_MAX_DEVICE_RANKS], const char** mcPtr) const
 {
     for (const SymSegment& s : userSegs_) {

@@ -74,6 +74,8 @@ public:
     // symmetric user memory
     HcclResult MemAlloc(uint64_t size, void** ptr);
     HcclResult MemFree(void* ptr);
+    HcclResult RegisterBuffer(void* ptr, uint64_t size);     // collective: a buffer the caller allocated itself
+    HcclResult DeregisterBuffer(void* ptr);
     // Finds the registered segment covering [p, p+bytes); fills peer pointers. false if not registered.
     bool Lookup(const void* p, uint64_t bytes, const char* peerPtr[HCCL_MAX_DEVICE_RANKS], const char** mcPtr) const;
 

@@ -33,7 +33,7 @@ const DriverApi* GetDriverApi()
         L(cuMemCreate); L(cuMemRelease); L(cuMemAddressReserve); L(cuMemAddressFree); L(cuMemMap); L(cuMemUnmap);
         L(cuMemSetAccess); L(cuMemGetAllocationGranularity); L(cuMemExportToShareableHandle);
         L(cuMemImportFromShareableHandle); L(cuDeviceGet); L(cuDeviceGetAttribute); L(cuGetErrorString);
-        L(cuTensorMapEncodeTiled);
+        L(cuTensorMapEncodeTiled); L(cuMemGetAddressRange);
 #undef L
         // multicast entry points are optional (older drivers): their absence only disables NVLS
         bool mc = true;

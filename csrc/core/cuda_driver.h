@@ -26,6 +26,7 @@ struct DriverApi {
                                    unsigned long long);
     CUresult (*cuMulticastUnbind)(CUmemGenericAllocationHandle, CUdevice, size_t, size_t);
     CUresult (*cuMulticastGetGranularity)(size_t*, const CUmulticastObjectProp*, CUmulticastGranularity_flags);
+    CUresult (*cuMemGetAddressRange)(CUdeviceptr*, size_t*, CUdeviceptr);
     CUresult (*cuDeviceGet)(CUdevice*, int);
     CUresult (*cuDeviceGetAttribute)(int*, CUdevice_attribute, CUdevice);
     CUresult (*cuGetErrorString)(CUresult, const char**);

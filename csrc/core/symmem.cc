@@ -1,5 +1,8 @@
 #include "symmem.h"
 #include <cstring>
+#include <string>
+#include <mutex>
+#include <map>
 #include <unistd.h>
 #include "cuda_driver.h"
 #include "log.h"
@@ -192,6 +195,34 @@ HcclResult SymAlloc(Bootstrap& bs, int device, size_t size, bool wantMc, bool fo
     return HCCL_SUCCESS;
 }
 
+// A process may open an IPC handle only once at a time (two registered buffers often live in the same cudaMalloc
+// block of a caching allocator), so open mappings are shared and reference counted.
+namespace {
+struct IpcMapping { void* base; int refs; };
+std::mutex g_ipcMu;
+std::map<std::string, IpcMapping> g_ipcOpen;     // key: the 64 handle bytes
+std::string HandleKey(const cudaIpcMemHandle_t& h) { return std::string(reinterpret_cast<const char*>(&h), sizeof(h)); }
+
+cudaError_t OpenShared(const cudaIpcMemHandle_t& h, void** base)
+{
+    std::lock_guard<std::mutex> lk(g_ipcMu);
+    auto it = g_ipcOpen.find(HandleKey(h));
+    if (it != g_ipcOpen.end()) { ++it->second.refs; *base = it->second.base; return cudaSuccess; }
+    cudaError_t e = cudaIpcOpenMemHandle(base, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e == cudaSuccess) g_ipcOpen[HandleKey(h)] = IpcMapping{*base, 1};
+    return e;
+}
+void CloseShared(void* base)
+{
+    std::lock_guard<std::mutex> lk(g_ipcMu);
+    for (auto it = g_ipcOpen.begin(); it != g_ipcOpen.end(); ++it) {
+        if (it->second.base != base) continue;
+        if (--it->second.refs == 0) { cudaIpcCloseMemHandle(base); g_ipcOpen.erase(it); }
+        return;
+    }
+}
+}  // namespace
+
 HcclResult SymFree(SymSegment* seg)
 {
     if (!seg || seg->transport == SymTransport::NONE) return HCCL_SUCCESS;
@@ -217,8 +248,57 @@ HcclResult SymFree(SymSegment* seg)
         }
     } else if (seg->transport == SymTransport::LOCAL) {
         cudaFree(seg->peer[seg->rank]);
+    } else if (seg->transport == SymTransport::USER_IPC) {
+        for (int q = 0; q < seg->nRanks; ++q)
+            if (q != seg->rank && seg->ipcBase[q]) CloseShared(seg->ipcBase[q]);      // the local buffer stays the caller's
     }
     *seg = SymSegment();
+    return HCCL_SUCCESS;
+}
+
+HcclResult SymRegisterUser(Bootstrap& bs, void* ptr, size_t size, SymSegment* out)
+{
+    CHK_PTR_NULL(out); CHK_PTR_NULL(ptr);
+    *out = SymSegment();
+    const int p = bs.nRanks(), me = bs.rank();
+    if (p > HCCL_MAX_DEVICE_RANKS) return HCCL_E_NOT_SUPPORT;
+    const DriverApi* d = GetDriverApi();
+    struct Msg { cudaIpcMemHandle_t handle; uint64_t offset, size; int ok; } mine;
+    memset(&mine, 0, sizeof(mine));
+    mine.size = size;
+    CUdeviceptr base = 0;
+    size_t range = 0;
+    // an IPC handle names a whole allocation: ship the offset of the buffer inside it as well
+    if (d != nullptr && d->cuMemGetAddressRange(&base, &range, (CUdeviceptr)ptr) == CUDA_SUCCESS && (char*)ptr + size <= (char*)base + range &&
+        cudaIpcGetMemHandle(&mine.handle, (void*)base) == cudaSuccess) {
+        mine.offset = (uint64_t)((char*)ptr - (char*)base);
+        mine.ok = 1;
+    } else {
+        cudaGetLastError();
+    }
+    std::vector<Msg> all((size_t)p);
+    CHK_RET(bs.AllGather(&mine, all.data(), sizeof(mine)));
+    for (const Msg& m : all) {
+        if (!m.ok) { HCCL_ERROR("buffer registration: a rank passed memory that cannot be shared through CUDA IPC (not a cudaMalloc allocation?)"); return HCCL_E_PARA; }
+        if (m.size != size) { HCCL_ERROR("buffer registration: ranks passed different sizes (%llu vs %llu)", (unsigned long long)size, (unsigned long long)m.size); return HCCL_E_PARA; }
+    }
+    out->size = out->mappedSize = size;
+    out->rank = me;
+    out->nRanks = p;
+    out->transport = SymTransport::USER_IPC;
+    out->peer[me] = ptr;
+    bool ok = true;
+    for (int q = 0; q < p; ++q) {
+        if (q == me) continue;
+        void* mapped = nullptr;
+        cudaError_t e = OpenShared(all[(size_t)q].handle, &mapped);
+        if (e != cudaSuccess) { HCCL_ERROR("cudaIpcOpenMemHandle for rank %d failed: %s", q, cudaGetErrorString(e)); cudaGetLastError(); ok = false; continue; }
+        out->ipcBase[q] = mapped;
+        out->peer[q] = (char*)mapped + all[(size_t)q].offset;
+    }
+    bool allOk = false;
+    CHK_RET(bs.AgreeAll(ok, &allOk));
+    if (!allOk) { SymFree(out); return HCCL_E_RUNTIME; }
     return HCCL_SUCCESS;
 }
 

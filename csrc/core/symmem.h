@@ -19,7 +19,7 @@
 
 namespace hccl {
 
-enum class SymTransport : int { NONE = 0, VMM, IPC, LOCAL };
+enum class SymTransport : int { NONE = 0, VMM, IPC, LOCAL, USER_IPC };
 
 struct SymSegment {
     size_t size = 0;                 // usable bytes (as requested)
@@ -31,6 +31,7 @@ struct SymSegment {
     // bookkeeping for release
     unsigned long long localHandle = 0, mcHandle = 0;
     unsigned long long peerHandle[HCCL_MAX_DEVICE_RANKS] = {0};
+    void* ipcBase[HCCL_MAX_DEVICE_RANKS] = {nullptr};   // USER_IPC: what cudaIpcOpenMemHandle returned for each peer
     bool ContainsLocal(const void* p, size_t bytes) const
     {
         const char* b = (const char*)peer[rank];
@@ -52,6 +53,12 @@ SymCaps QuerySymCaps(int device);
 // (ccu_fallback.h; op_common.cc:2064-2083).
 HcclResult SymAlloc(Bootstrap& bs, int device, size_t size, bool wantMulticast, bool forceIpc, SymSegment* out);
 HcclResult SymFree(SymSegment* seg);
+
+// Registration of a buffer the caller allocated itself with cudaMalloc (or a framework allocator on top of it): every
+// rank passes its own buffer of `size` bytes; the peers map it through legacy CUDA IPC handles (which work for any
+// cudaMalloc allocation, whole allocations only, hence the offset exchange).  Collective.  The segment has no
+// multicast alias: operators on it run the peer-to-peer kernels without staging copies.
+HcclResult SymRegisterUser(Bootstrap& bs, void* ptr, size_t size, SymSegment* out);
 
 // Emulation: R segments on the current GPU, every "peer" pointer valid locally.
 HcclResult SymAllocLocalGroup(int nRanks, size_t size, std::vector<SymSegment>* out);

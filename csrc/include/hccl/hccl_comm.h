@@ -46,6 +46,13 @@ HcclResult HcclGetHcclBuffer(HcclComm comm, void** buffer, uint64_t* size);
 // Symmetric (zero-copy) memory: collective calls, every rank passes the same size.
 HcclResult HcclMemAlloc(HcclComm comm, uint64_t size, void** devPtr);
 HcclResult HcclMemFree(HcclComm comm, void* devPtr);
+// Registration of a buffer the caller allocated itself (cudaMalloc, or a framework allocator on top of it): collective,
+// every rank passes its own buffer of the same size and later uses the same offsets inside it.  Operators then read
+// and write it in place on the peers (peer-to-peer kernels, no staging copies; no switch reduction: for that use
+// HcclMemAlloc).  The reference's counterpart is the registration of user buffers for zero copy
+// (RegGraphModeBuffers, op_common.cc:2724).  Deregister before freeing the buffer.
+HcclResult HcclCommRegister(HcclComm comm, void* devPtr, uint64_t size);
+HcclResult HcclCommDeregister(HcclComm comm, void* devPtr);
 // Peer address of `localPtr` (inside a symmetric allocation) on `peerRank`,
 // mapped into this process; and the multicast alias (NULL when NVLS is off).
 HcclResult HcclCommSymWinGet(HcclComm comm, const void* localPtr, uint32_t peerRank, void** peerPtr);

@@ -510,8 +510,12 @@ OpDesc Describe(CommImpl* c, const OpParam& p)
         case HCCL_CMD_BATCH_SEND_RECV: for (auto& it : p.items) d.bytes += it.count * DataTypeSize(it.dataType); break;
         default: break;
     }
-    d.inRegistered = p.send && inBytes && c->Lookup(p.send, inBytes, peers, nullptr);
-    d.outRegistered = p.recv && outBytes && c->Lookup(p.recv, outBytes, peers, nullptr);
+    const char* mcIn = nullptr;
+    const char* mcOut = nullptr;
+    d.inRegistered = p.send && inBytes && c->Lookup(p.send, inBytes, peers, &mcIn);
+    d.outRegistered = p.recv && outBytes && c->Lookup(p.recv, outBytes, peers, &mcOut);
+    d.inMulticast = d.inRegistered && mcIn != nullptr;       // buffers registered with HcclCommRegister have no multicast alias
+    d.outMulticast = d.outRegistered && mcOut != nullptr;
     d.aligned16 = Aligned16(p.send) && Aligned16(p.recv);
     d.inPlace = p.send == p.recv;
     return d;

@@ -55,8 +55,8 @@ void RegisterAll()
     {
         AlgEntry e = Base("P2pAllReduceSoleMeshLL", HCCL_CMD_ALLREDUCE, HCCL_ENGINE_P2P, "MeshLL", DALG_AR_LL, AlgoType::LL);
         e.attrs.dtypeMask = kReduceTypes;
-        // every thread walks its lines peer by peer, so the op is latency-bound and stops paying off around 64 KiB
-        // (measured on 8 GPUs: 35 us up to 32 KiB, 42 us at 64 KiB, 48 us at 128 KiB against 29 us for the NVLS kernel at 512 KiB)
+        // every rank writes the whole message (doubled by the flags) to every peer, so the form stops paying off around
+        // 64 KiB, where the barrier forms catch up
         e.attrs.maxBytes = 64 * 1024;
         e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
             M m(t, o);
@@ -112,7 +112,8 @@ void RegisterAll()
             c.A = (1.0 + 1.0 / m.p) * m.nvls();
             c.ratio = 1.0 / m.p;
             c.net = NetType::NVLS_SWITCH;
-            c.B = (m.stageIn ? m.copy() : 0) + ((!o.outRegistered || !o.aligned16) ? m.copy() : 0);
+            // the switch reads and writes through multicast aliases: anything without one is staged through the slab
+            c.B = ((m.stageIn || !o.inMulticast) ? m.copy() : 0) + ((!o.outMulticast || !o.aligned16) ? m.copy() : 0);
             c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
             return std::vector<CostCoeff>{c};
         };
@@ -149,7 +150,7 @@ void RegisterAll()
                 c.A = 1.0 / m.p * m.nvls() * 1.0;   // each rank receives its reduced share once; peers feed the switch in parallel
                 c.ratio = 1.0 / m.p;
                 c.net = NetType::NVLS_SWITCH;
-                c.B = m.stageIn ? m.copy() : 0;
+                c.B = (m.stageIn || !o.inMulticast) ? m.copy() : 0;
                 c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
                 // the switch still has to pull (p-1)/p of the input out of every GPU
                 CostCoeff f;
@@ -268,7 +269,7 @@ void RegisterAll()
             CostCoeff c;
             c.A = m.nvls();
             c.net = NetType::NVLS_SWITCH;
-            c.B = m.copy();
+            c.B = o.inMulticast && o.aligned16 ? 0 : m.copy();     // stored straight into a buffer with a multicast alias
             c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
             return std::vector<CostCoeff>{c};
         };

@@ -11,7 +11,8 @@ namespace hccl {
 
 uint32_t OpDesc::Flags() const
 {
-    return (inRegistered ? 1u : 0u) | (outRegistered ? 2u : 0u) | (aligned16 ? 4u : 0u) | (inPlace ? 8u : 0u) |
+    return (inRegistered ? 1u : 0u) | (outRegistered ? 2u : 0u) | (aligned16 ? 4u : 0u) | (inPlace ? 8u : 0u) | (inMulticast ? (1u << 20) : 0u) |
+           (outMulticast ? (1u << 21) : 0u) |
            (isMc2 ? 16u : 0u) | ((uint32_t)det << 5) | ((uint32_t)engine << 8);
 }
 

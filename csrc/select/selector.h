@@ -42,6 +42,8 @@ struct OpDesc {
     uint32_t nRanks = 1;
     bool inRegistered = false;   // input lies in symmetric memory (peers can read it in place)
     bool outRegistered = false;
+    bool inMulticast = false;    // ... and has a multicast alias (switch reductions can read it in place)
+    bool outMulticast = false;
     bool aligned16 = true;       // both pointers 16-byte aligned
     bool inPlace = false;
     bool isMc2 = false;          // called on behalf of a fused matmul kernel

@@ -156,6 +156,8 @@ _sig_or_none("HcclFusedRmsNormBwd", R, c_void_p, c_void_p, c_void_p, c_void_p, c
 _sig_or_none("HcclFusedSwigluFwd", R, c_void_p, c_void_p, c_uint64, c_uint32, c_void_p)
 _sig_or_none("HcclFusedSwigluBwd", R, c_void_p, c_void_p, c_void_p, c_uint64, c_uint32, c_void_p)
 _sig_or_none("HcclFusedRope", R, c_void_p, c_uint64, c_void_p, c_uint64, c_void_p, c_void_p, c_uint64, c_uint32, c_uint32, c_int, c_void_p)
+_sig_or_none("HcclCommRegister", R, c_void_p, c_void_p, c_uint64)
+_sig_or_none("HcclCommDeregister", R, c_void_p, c_void_p)
 # MoE
 class HcclMoeConfig(ctypes.Structure):
     _fields_ = [("nTokens", c_uint32), ("hidden", c_uint32), ("topk", c_uint32), ("nExperts", c_uint32), ("capacity", c_uint32)]

@@ -162,6 +162,14 @@ class Communicator:
     def free(self, tensor) -> None:
         _check(lib.HcclMemFree(self._h, c_void_p(tensor.data_ptr())), "HcclMemFree")
 
+    def register(self, tensor) -> None:
+        """Collective: registers a tensor the caller allocated itself (same size on every rank) so that operators use it
+        in place on the peers instead of staging it.  Later calls must use the same offsets inside it on every rank."""
+        _check(lib.HcclCommRegister(self._h, c_void_p(tensor.data_ptr()), tensor.numel() * tensor.element_size()), "HcclCommRegister")
+
+    def deregister(self, tensor) -> None:
+        _check(lib.HcclCommDeregister(self._h, c_void_p(tensor.data_ptr())), "HcclCommDeregister")
+
     def peer_pointer(self, tensor, peer: int) -> int:
         p = c_void_p()
         _check(lib.HcclCommSymWinGet(self._h, c_void_p(tensor.data_ptr()), peer, byref(p)), "HcclCommSymWinGet")

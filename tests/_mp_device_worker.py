@@ -217,6 +217,36 @@ def scenario_peer_exit(comm, rank, world):
     os._exit(0)
 
 
+def scenario_register(comm, rank, world):
+    """Buffers the caller allocated itself, registered collectively: operators use them in place on the peers."""
+    n = 1 << 20
+    g = [torch.Generator(device="cuda").manual_seed(70 + r) for r in range(world)]
+    xs = [torch.rand(n, device="cuda", generator=g[r]) for r in range(world)]
+    src = torch.empty(n, device="cuda")
+    dst = torch.empty(n * world, device="cuda")
+    comm.register(src)
+    comm.register(dst)
+    for rep in range(2):
+        src.copy_(xs[rank])
+        comm.all_reduce(src, dst[:n])
+        torch.cuda.synchronize()
+        assert "Nvls" not in comm.last_algorithm(), comm.last_algorithm()      # no multicast alias: peer-to-peer kernels, zero copy
+        torch.testing.assert_close(dst[:n], torch.stack(xs).sum(0), rtol=1e-5, atol=1e-5)
+        comm.all_gather(src, dst)
+        torch.cuda.synchronize()
+        assert torch.equal(dst, torch.cat(xs))
+        per = n // world
+        comm.reduce_scatter(src, dst[:per])
+        torch.cuda.synchronize()
+        torch.testing.assert_close(dst[:per], torch.stack(xs).sum(0)[rank * per:(rank + 1) * per], rtol=1e-5, atol=1e-5)
+    comm.deregister(src)
+    comm.deregister(dst)
+    comm.all_reduce(src, dst[:n])                  # still works, staged again
+    torch.cuda.synchronize()
+    torch.testing.assert_close(dst[:n], torch.stack(xs).sum(0), rtol=1e-5, atol=1e-5)
+    assert comm.async_error() == hb.Result.SUCCESS
+
+
 def scenario_model(rank, world, path):
     """Two-layer TP+SP decoder stack: loss and gradients of the fused-kernel arm against the NCCL + cuBLAS arm built
     from the same seed, for both AllGather->Matmul forms; two steps each (persistent symmetric buffers are reused)."""
@@ -322,7 +352,8 @@ def main():
     info = rendezvous(rank, path)
     timeout_ms = 3000 if scenario == "peer_exit" else 0
     comm = Communicator.from_root_info(info, rank, world, hb.make_config(buffer_mib=64, exec_timeout_ms=timeout_ms))
-    {"collectives": scenario_collectives, "peer_exit": scenario_peer_exit, "mc2": scenario_mc2, "graph": scenario_graph}[scenario](comm, rank, world)
+    {"collectives": scenario_collectives, "peer_exit": scenario_peer_exit, "mc2": scenario_mc2, "graph": scenario_graph,
+     "register": scenario_register}[scenario](comm, rank, world)
     comm.destroy()
     print(f"rank {rank} done", flush=True)
 

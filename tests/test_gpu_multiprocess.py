@@ -84,3 +84,9 @@ def test_torch_distributed_backend():
 def test_tp_model_gradients_match_nccl_arm():
     codes, outs = _run(_world(), "model")
     assert all(c == 0 for c in codes), "\n".join(outs)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_registered_user_buffers_are_used_in_place():
+    codes, outs = _run(_world(), "register")
+    assert all(c == 0 for c in codes), "\n".join(outs)
