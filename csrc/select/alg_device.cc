@@ -4,6 +4,7 @@
 // (reference equivalents: AivAllReduceSoleMeshOneShot / AivAllReduceSoleMeshTwoShot
 // ins_v2_all_reduce_sole_executor.cc:459,481, CcuMSAllReduceSoleMesh :548, and
 // the Sole/Mesh entries of the other operators listed with REGISTER_EXEC_V2).
+#include <algorithm>
 #include "selector.h"
 #include "../kernels/dev_types.h"
 #include "../kernels/launch.h"
@@ -29,6 +30,8 @@ struct M {
     M(const TopoInfo& t, const OpDesc& o) : lm(GlobalLinkModel()), p((double)t.nRanks), stageIn(!o.inRegistered || !o.aligned16), stageOut(!o.aligned16) {}
     double link() const { return UsPerByte(lm.p2pGBs); }
     double nvls() const { return UsPerByte(lm.nvlsGBs); }
+    double nvlsReduceOut() const { return UsPerByte(lm.nvlsReduceOutGBs); }
+    double nvlsStore() const { return UsPerByte(lm.nvlsStoreGBs); }
     double copy() const { return UsPerByte(lm.localCopyGBs); }
 };
 
@@ -109,7 +112,8 @@ void RegisterAll()
         e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
             M m(t, o);
             CostCoeff c;
-            c.A = (1.0 + 1.0 / m.p) * m.nvls();
+            // every rank reduces 1/p of the message through the switch and multicasts it; its port carries the message once
+            c.A = std::max((m.nvlsReduceOut() + m.nvlsStore()) / m.p, (1.0 + 1.0 / m.p) * m.nvls());
             c.ratio = 1.0 / m.p;
             c.net = NetType::NVLS_SWITCH;
             // the switch reads and writes through multicast aliases: anything without one is staged through the slab
@@ -147,7 +151,7 @@ void RegisterAll()
             e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
                 M m(t, o);
                 CostCoeff c;
-                c.A = 1.0 / m.p * m.nvls() * 1.0;   // each rank receives its reduced share once; peers feed the switch in parallel
+                c.A = m.nvlsReduceOut() / m.p;      // each rank receives its reduced share once; peers feed the switch in parallel
                 c.ratio = 1.0 / m.p;
                 c.net = NetType::NVLS_SWITCH;
                 c.B = (m.stageIn || !o.inMulticast) ? m.copy() : 0;
@@ -267,7 +271,7 @@ void RegisterAll()
         e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
             M m(t, o);
             CostCoeff c;
-            c.A = m.nvls();
+            c.A = m.nvlsStore();
             c.net = NetType::NVLS_SWITCH;
             c.B = o.inMulticast && o.aligned16 ? 0 : m.copy();     // stored straight into a buffer with a multicast alias
             c.C = m.lm.launchUs + 2 * m.lm.barrierUs;

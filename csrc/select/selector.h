@@ -130,6 +130,8 @@ double LinkUtilisation(NetType net, double bytes, HcclCommEngine engine);
 struct LinkModel {
     double p2pGBs = 770.0;        // measured peer copy per direction per GPU
     double nvlsGBs = 900.0;       // nominal per-direction port rate, utilisation table carries the rest
+    double nvlsReduceOutGBs = 335.0;  // reduced bytes one GPU receives per second through multimem.ld_reduce (measured, 2 and 8 GPUs)
+    double nvlsStoreGBs = 515.0;      // bytes one GPU sends per second through multimem.st (measured)
     double localCopyGBs = 3200.0; // HBM read+write for a device-local copy
     double localReduceGBs = 3200.0;
     double hostMemGBs = 10.0;
