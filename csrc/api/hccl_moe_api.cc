@@ -59,7 +59,8 @@ HcclResult EnsureState(CommImpl* c, size_t nPairs)
 
 int MoeBlocks(const CommImpl* c, uint32_t nTokens)
 {
-    int nb = (int)std::min<uint32_t>(std::max<uint32_t>(nTokens / 8, 1), 64);
+    // combine is a pull over NVLink, bound by the bytes in flight: as many blocks as the flag rows allow
+    int nb = (int)std::min<uint32_t>(std::max<uint32_t>(nTokens / 8, 1), 128);
     return std::min(nb, c->MaxBlocks());
 }
 
