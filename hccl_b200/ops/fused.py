@@ -19,6 +19,14 @@ from .._lib import lib
 from ..comm import _check
 
 
+LAUNCHES = 0          # kernels of this module launched so far (benchmark accounting)
+
+
+def _count(n=1):
+    global LAUNCHES
+    LAUNCHES += n
+
+
 def _p(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
 
@@ -73,6 +81,7 @@ class _AddRmsNorm(torch.autograd.Function):
             x_out = x
         _check(lib.HcclFusedAddRmsNormFwd(_p(x), _p(delta), _p(weight), _p(x_out) if delta is not None else ctypes.c_void_p(0), _p(h), _p(rstd),
                                           rows, hidden, float(eps), _s()), "HcclFusedAddRmsNormFwd")
+        _count()
         ctx.save_for_backward(x_out, weight, rstd)
         ctx.has_delta = delta is not None
         return (x_out, h) if delta is not None else h        # without delta the input itself is the residual stream
@@ -92,6 +101,7 @@ class _AddRmsNorm(torch.autograd.Function):
         partial = torch.empty((n_part, hidden), device=x_out.device, dtype=torch.float32)
         _check(lib.HcclFusedRmsNormBwd(_p(dh), _p(x_out), _p(weight), _p(rstd), _p(extra), _p(dx), _p(partial), _p(dw), rows, hidden, _s()),
                "HcclFusedRmsNormBwd")
+        _count(2)
         return dx, (dx if ctx.has_delta else None), dw, None
 
 
@@ -103,6 +113,7 @@ class _Swiglu(torch.autograd.Function):
         rows = gate_up.numel() // gate_up.shape[-1]
         out = torch.empty(gate_up.shape[:-1] + (f,), device=gate_up.device, dtype=gate_up.dtype)
         _check(lib.HcclFusedSwigluFwd(_p(gate_up), _p(out), rows, f, _s()), "HcclFusedSwigluFwd")
+        _count()
         ctx.save_for_backward(gate_up)
         return out
 
@@ -113,6 +124,7 @@ class _Swiglu(torch.autograd.Function):
         rows = gate_up.numel() // gate_up.shape[-1]
         dgu = torch.empty_like(gate_up)
         _check(lib.HcclFusedSwigluBwd(_p(gate_up), _p(dout.contiguous()), _p(dgu), rows, f, _s()), "HcclFusedSwigluBwd")
+        _count()
         return dgu
 
 
@@ -123,6 +135,7 @@ class _Rope(torch.autograd.Function):
         assert x.stride(2) == 1 and x.stride(1) == d, "rope: heads must be packed inside a row"
         out = torch.empty((s, nh, d), device=x.device, dtype=x.dtype)
         _check(lib.HcclFusedRope(_p(x), x.stride(0), _p(out), nh * d, _p(cos), _p(sin), s, nh, d, 0, _s()), "HcclFusedRope")
+        _count()
         ctx.save_for_backward(cos, sin)
         return out
 
@@ -133,6 +146,7 @@ class _Rope(torch.autograd.Function):
         dout = dout.contiguous()
         dx = torch.empty_like(dout)
         _check(lib.HcclFusedRope(_p(dout), nh * d, _p(dx), nh * d, _p(cos), _p(sin), s, nh, d, 1, _s()), "HcclFusedRope")
+        _count()
         return dx, None, None
 
 
