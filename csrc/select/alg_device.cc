@@ -51,6 +51,14 @@ AlgEntry Base(const char* name, HcclCMDType op, HcclCommEngine eng, const char* 
     return e;
 }
 
+// Flag-in-data exchanges move one pair's block through one line slot of kLLMaxPayload payload bytes.
+bool PairFitsLLSlot(const OpDesc& o, const TopoInfo& t, std::string* why)
+{
+    const uint64_t pair = o.bytes / std::max<uint64_t>(1, t.nRanks);
+    if (pair > kLLMaxPayload) { if (why) *why = "op: a pair's block exceeds the line slot"; return false; }
+    return true;
+}
+
 void RegisterAll()
 {
     AlgRegistry& R = AlgRegistry::Instance();
@@ -202,7 +210,8 @@ void RegisterAll()
     {
         AlgEntry e = Base("P2pReduceScatterSoleMeshLL", HCCL_CMD_REDUCE_SCATTER, HCCL_ENGINE_P2P, "MeshLL", DALG_RS_LL, AlgoType::LL);
         e.attrs.dtypeMask = kReduceTypes;
-        e.attrs.maxBytes = 256 * 1024;            // whole input; a pair moves 1/p of it
+        e.attrs.maxBytes = 1024 * 1024;           // whole input; a pair moves 1/p of it (measured at 8 ranks: ahead of the switch form up to here)
+        e.attrs.opCustomCheck = PairFitsLLSlot;
         e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
             M m(t, o);
             CostCoeff c;
@@ -228,7 +237,10 @@ void RegisterAll()
     }
     {
         AlgEntry e = Base("P2pAlltoAllSoleMeshLL", HCCL_CMD_ALLTOALL, HCCL_ENGINE_P2P, "MeshLL", DALG_A2A_LL, AlgoType::LL);
-        e.attrs.maxBytes = 256 * 1024;
+        // the pull form pays two barriers and a table exchange (42 us at 8 ranks whatever the size below 16 MiB), the
+        // flag-in-data form one latency: it stays ahead as long as a pair's block fits a line slot
+        e.attrs.maxBytes = 2 * 1024 * 1024;
+        e.attrs.opCustomCheck = PairFitsLLSlot;
         e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
             M m(t, o);
             CostCoeff c;

@@ -321,7 +321,7 @@ def test_strict_determinism_repeats_bitwise():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int8, torch.int64])
-@pytest.mark.parametrize("n", [1, 5, 1023, 4097])
+@pytest.mark.parametrize("n", [1, 5, 1023, 4097, 30001])
 def test_small_message_ll_forms(comms, dtype, n):
     """ReduceScatter, Broadcast and AlltoAll of small messages run as flag-in-data exchanges (no barrier); two rounds
     back to back so that both parities of the line slots are used."""
@@ -332,8 +332,8 @@ def test_small_message_ll_forms(comms, dtype, n):
         for c, x, y in zip(comms, ins, outs):
             c.reduce_scatter(x, y)
         es = ins[0].element_size()
-        small = n * p * es <= 256 * 1024           # the flag-in-data forms take inputs up to 256 KiB
-        if small:
+        pair_ok = n * es <= 256 * 1024             # a pair's block has to fit one line slot
+        if pair_ok and n * p * es <= 1024 * 1024:
             assert comms[0].last_algorithm() == "P2pReduceScatterSoleMeshLL"
         torch.cuda.synchronize()
         ref = torch.stack([x.double() for x in ins]).sum(0)
@@ -346,7 +346,7 @@ def test_small_message_ll_forms(comms, dtype, n):
         a2a_out = [torch.empty(n * p, device="cuda", dtype=dtype) for _ in range(p)]
         for c, x, y in zip(comms, ins, a2a_out):
             c.all_to_all(x, y)
-        if small:
+        if pair_ok and n * p * es <= 2 * 1024 * 1024:
             assert comms[0].last_algorithm() == "P2pAlltoAllSoleMeshLL"
         torch.cuda.synchronize()
         for r, y in enumerate(a2a_out):
