@@ -1,3 +1,4 @@
+#include <algorithm>
 #include "step_tables.h"
 
 namespace hccl {
@@ -177,6 +178,72 @@ void SliceOf(uint64_t count, uint32_t p, uint32_t i, uint64_t* begin, uint64_t* 
     if (e > count) e = count;
     *begin = b;
     *end = e;
+}
+
+std::vector<BruckStep> BruckAllGatherSteps(uint32_t p, uint32_t me)
+{
+    std::vector<BruckStep> out;
+    for (uint32_t d = 1; d < p; d <<= 1) {
+        BruckStep s;
+        s.sendTo = (me + p - d % p) % p;
+        s.recvFrom = (me + d) % p;
+        s.nBlocks = std::min(d, p - d);
+        s.firstSendBlock = me;
+        s.firstRecvBlock = (me + d) % p;
+        out.push_back(s);
+    }
+    return out;
+}
+
+std::vector<TreeScatterStep> BinomialScatterSteps(uint32_t p, uint32_t v)
+{
+    std::vector<TreeScatterStep> out;
+    if (p <= 1) return out;
+    for (uint32_t d = 1u << (CeilLog2(p) - 1);; d >>= 1) {
+        TreeScatterStep s;
+        if (v % (2 * d) == 0 && v + d < p) {
+            s.sends = true;
+            s.peer = v + d;
+            s.firstBlock = v + d;
+            s.nBlocks = std::min(v + 2 * d, p) - (v + d);
+        } else if (v % (2 * d) == d) {
+            s.receives = true;
+            s.peer = v - d;
+            s.firstBlock = v;
+            s.nBlocks = std::min(v + d, p) - v;
+        }
+        out.push_back(s);
+        if (d == 1) break;
+    }
+    return out;
+}
+
+uint64_t BandwidthSplit(uint64_t count, double bwA, double bwB, uint64_t align)
+{
+    if (align == 0) align = 1;
+    if (bwA <= 0 || count == 0) return 0;
+    if (bwB <= 0) return count;
+    uint64_t a = (uint64_t)((double)count * (bwA / (bwA + bwB))) / align * align;
+    if (a < align) return 0;
+    if (count - a < align) return count;
+    return a;
+}
+
+std::vector<PipeSlot> PipelineSchedule(uint32_t stages, uint32_t steps)
+{
+    std::vector<PipeSlot> out;
+    if (stages == 0 || steps == 0) return out;
+    for (uint32_t t = 0; t < steps + stages - 1; ++t)
+        for (uint32_t st = stages; st-- > 0;)
+            if (t >= st && t - st < steps) out.push_back({t, st, t - st});
+    return out;
+}
+
+uint32_t PipelineStepCount(uint64_t count, uint64_t minElems, uint32_t maxSteps)
+{
+    if (minElems == 0) minElems = 1;
+    const uint64_t n = count / minElems;
+    return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(n, maxSteps));
 }
 
 }  // namespace hccl

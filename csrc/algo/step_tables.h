@@ -19,6 +19,20 @@
 //   Ring - coll_algo_intro/Ring.md: p - 1 steps, one slice to the right per step.
 //   Pairwise - coll_algo_intro/Pairwise.md: step k: send to (i + k) mod p,
 //          receive from (i - k) mod p.
+//   NB   - Nonuniform Bruck (the reference's scatter_nb.cc / AlgTemplateBase
+//          and HCCL_ALGO's "NB"): ceil(log2 p) steps for any p; AllGather step s
+//          sends the min(2^s, p - 2^s) blocks held so far, starting at the own
+//          block, to (me - 2^s) mod p and receives as many from (me + 2^s) mod p.
+//          Scatter runs a binomial tree over root-relative ranks from the widest
+//          stride down: the holder of relative blocks [v, v + 2d) hands
+//          [v + d, min(v + 2d, p)) to relative rank v + d.
+//   Data split of the Parallel / Concurrent executors - CalcParallelDataSplitRatio
+//          (template_utils.h:809-826): part A gets bwA / (bwA + bwB) of the data,
+//          cut on an alignment boundary.
+//   Pipeline schedule - docs/en/user_guide/coll_algo_intro/Pipeline.md and
+//          rfcs/0003-executor-template-refactor.md:712-747: the data is cut in
+//          at most five steps and stage k of step i runs beside stage k - 1 of
+//          step i + 1.
 //   Deterministic fold - aiv_all_reduce_mesh_1d_oneshot.h:39-72: with M the
 //          largest power of two below the live count, slot[s mod M] += slot[s]
 //          for s in [M, count), count = M, repeat.
@@ -71,6 +85,29 @@ std::vector<PairwiseStep> PairwiseSteps(uint32_t p, uint32_t me);
 
 // (dst, src) pairs: slot[dst] op= slot[src], in the order they must be applied.
 std::vector<std::pair<uint32_t, uint32_t>> DeterministicFoldOrder(uint32_t count);
+
+// Nonuniform Bruck AllGather: blocks are named by their owner's rank.
+struct BruckStep {
+    uint32_t sendTo, recvFrom;
+    uint32_t firstSendBlock, firstRecvBlock, nBlocks;    // block ranges [first, first + n) mod p
+};
+std::vector<BruckStep> BruckAllGatherSteps(uint32_t p, uint32_t me);
+// Binomial-tree scatter over relative ranks v = (rank - root) mod p.  Each step names relative ranks and blocks.
+struct TreeScatterStep {
+    bool sends = false, receives = false;
+    uint32_t peer = 0;                                   // relative rank of the partner
+    uint32_t firstBlock = 0, nBlocks = 0;                // relative blocks that move
+};
+std::vector<TreeScatterStep> BinomialScatterSteps(uint32_t p, uint32_t vrank);
+// Elements of part A when `count` elements are split in proportion bwA : bwB, rounded down to `align` elements
+// (part B takes the rest; a part below `align` elements is folded into the other).
+uint64_t BandwidthSplit(uint64_t count, double bwA, double bwB, uint64_t align);
+// Pipeline of `stages` stages over `steps` data steps: time slot t runs (stage, step = t - stage) for every stage with
+// a valid step, later stages first so that a stage frees its buffer before the previous stage refills it.
+struct PipeSlot { uint32_t time, stage, step; };
+std::vector<PipeSlot> PipelineSchedule(uint32_t stages, uint32_t steps);
+// Number of pipeline steps for a message: at most `maxSteps`, each at least `minElems` elements.
+uint32_t PipelineStepCount(uint64_t count, uint64_t minElems, uint32_t maxSteps);
 
 // Slice i of `count` elements over p ranks: sliceCount = ceil(count / p); trailing slices may be empty
 // (ins_temp_all_reduce_mesh_1D_two_shot.cc:178-201).

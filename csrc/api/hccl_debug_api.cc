@@ -5,6 +5,7 @@
 #include "../algo/step_tables.h"
 #include "../core/config.h"
 #include "../core/log.h"
+#include "../cpu/host_tree.h"
 #include "../select/selector.h"
 #include "hccl/hccl_ext.h"
 
@@ -45,6 +46,26 @@ HcclResult HcclDebugStepTable(const char* kind, uint32_t p, uint32_t rank, const
         for (const RingStep& s : (k == "ring_rs" ? RingReduceScatterSteps(p, rank) : RingAllGatherSteps(p, rank))) os << "send " << s.sendSlice << " recv " << s.recvSlice << "\n";
     } else if (k == "pairwise") {
         for (const PairwiseStep& s : PairwiseSteps(p, rank)) os << "to " << s.sendTo << " from " << s.recvFrom << "\n";
+    } else if (k == "bruck_ag") {
+        for (const BruckStep& s : BruckAllGatherSteps(p, rank))
+            os << "to " << s.sendTo << " from " << s.recvFrom << " send " << s.firstSendBlock << " recv " << s.firstRecvBlock << " n " << s.nBlocks << "\n";
+    } else if (k == "nb_scatter") {
+        for (const TreeScatterStep& s : BinomialScatterSteps(p, rank))
+            os << (s.sends ? "send" : s.receives ? "recv" : "idle") << " peer " << s.peer << " first " << s.firstBlock << " n " << s.nBlocks << "\n";
+    } else if (k == "bw_split") {
+        // arg = "count,bwA,bwB,align"
+        unsigned long long count = 0, align = 1;
+        double a = 0, b = 0;
+        if (!arg || sscanf(arg, "%llu,%lf,%lf,%llu", &count, &a, &b, &align) != 4) return HCCL_E_PARA;
+        os << BandwidthSplit(count, a, b, align) << "\n";
+    } else if (k == "pipeline") {
+        // p = stages, rank = steps
+        for (const PipeSlot& s : PipelineSchedule(p, rank)) os << "t " << s.time << " stage " << s.stage << " step " << s.step << "\n";
+    } else if (k == "parse_tree") {
+        std::unique_ptr<AlgoTreeNode> tree;
+        std::string err;
+        if (!ParseAlgoTree(arg ? arg : "", &tree, &err)) os << "error: " << err << "\n";
+        else os << AlgoTreeText(*tree) << " queues " << AlgoTreeQueues(*tree) << " levels " << AlgoTreeMinLevels(*tree) << "\n";
     } else if (k == "fold") {
         for (auto& pr : DeterministicFoldOrder(p)) os << pr.first << "+=" << pr.second << "\n";
     } else if (k == "parse_algo") {

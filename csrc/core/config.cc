@@ -99,6 +99,10 @@ const char* AlgoTypeName(AlgoType t)
         case AlgoType::TWOSHOT: return "twoshot";
         case AlgoType::NVLS: return "nvls";
         case AlgoType::LL: return "ll";
+        case AlgoType::CONCURRENT: return "concurrent";
+        case AlgoType::OMNIPIPE: return "omnipipe";
+        case AlgoType::HIER: return "hier";
+        case AlgoType::TREE: return "tree";
     }
     return "?";
 }
@@ -112,7 +116,8 @@ bool ParseAlgoType(const std::string& s, AlgoType* out)
         {"nb", AlgoType::NB}, {"ahc", AlgoType::AHC}, {"pipeline", AlgoType::PIPELINE},
         {"pairwise", AlgoType::PAIRWISE}, {"fullmesh", AlgoType::MESH}, {"mesh", AlgoType::MESH},
         {"oneshot", AlgoType::ONESHOT}, {"twoshot", AlgoType::TWOSHOT}, {"nvls", AlgoType::NVLS},
-        {"ll", AlgoType::LL},
+        {"ll", AlgoType::LL}, {"concurrent", AlgoType::CONCURRENT}, {"omnipipe", AlgoType::OMNIPIPE},
+        {"hier", AlgoType::HIER}, {"tree", AlgoType::TREE},
     };
     auto it = k.find(l);
     if (it == k.end()) return false;
@@ -262,6 +267,7 @@ EnvConfig ParseEnvConfig(const EnvGetter& get)
     if (val("HCCL_CONNECT_TIMEOUT", &s)) { if (ParseU32(s, &u) && u >= 1 && u <= 7200) c.connectTimeoutS = u; else c.errors.push_back("HCCL_CONNECT_TIMEOUT: expected 1..7200 s"); }
     val("HCCL_ALG_TUNER_PLUGIN", &c.tunerPlugin);
     val("HCCL_ALGO_PLUGIN_PATH", &c.algoPlugin);
+    val("HCCL_ALGO_TREE", &c.algoTree);
     if (val("HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO", &s)) {
         for (const std::string& f : Split(s, ',')) {
             char* end = nullptr;

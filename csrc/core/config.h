@@ -17,7 +17,8 @@ namespace hccl {
 
 // Algorithm family names accepted by HCCL_ALGO (reference grammar:
 // docs/en/user_guide/hccl_env/HCCL_ALGO.md; parser alg_parse.cc).
-enum class AlgoType : int { DEFAULT = 0, NA, RING, HD_R, NHR, NHR_V1, NB, AHC, PIPELINE, PAIRWISE, MESH, ONESHOT, TWOSHOT, NVLS, LL };
+enum class AlgoType : int { DEFAULT = 0, NA, RING, HD_R, NHR, NHR_V1, NB, AHC, PIPELINE, PAIRWISE, MESH, ONESHOT, TWOSHOT, NVLS, LL,
+                            CONCURRENT, OMNIPIPE, HIER, TREE };   // executor families beyond the reference's HCCL_ALGO names
 const char* AlgoTypeName(AlgoType t);
 bool ParseAlgoType(const std::string& s, AlgoType* out);
 
@@ -65,6 +66,7 @@ struct EnvConfig {
     std::string tunerPlugin;                          // HCCL_ALG_TUNER_PLUGIN
     std::string algoPlugin;                           // HCCL_ALGO_PLUGIN_PATH
     std::vector<double> splitRatio;                   // HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO
+    std::string algoTree;                             // HCCL_ALGO_TREE: executor tree for the tree-interpreting executor
     // B200-specific knobs
     int nvlsEnable = -1;                              // HCCL_NVLS_ENABLE: -1 auto, 0 off, 1 on
     uint32_t maxBlocks = 0;                           // HCCL_MAX_BLOCKS, 0 = auto

@@ -11,6 +11,7 @@
 #include "../ops/param_check.h"
 #include "../select/selector.h"
 #include "hccl/hccl_ext.h"
+#include "host_tree.h"
 #include "host_world.h"
 
 namespace hccl {
@@ -201,9 +202,9 @@ void Reg(const HostAlgSpec& s)
     e.family = s.family;
     e.attrs.minLevels = s.minLevels;
     e.attrs.maxLevels = 3;
-    // AllReduce / ReduceScatter / AllGather have hierarchical forms: their flat forms stay on one-level topologies
-    if (s.minLevels == 1 && std::string(s.executor) != "orderpreserved" &&
-        (s.op == HCCL_CMD_ALLREDUCE || s.op == HCCL_CMD_REDUCE_SCATTER || s.op == HCCL_CMD_ALLGATHER)) {
+    // operators with hierarchical forms: their flat forms stay on one-level topologies
+    if (s.minLevels == 1 && std::string(s.executor) != "orderpreserved" && std::string(s.executor) != "tree" &&
+        (s.op == HCCL_CMD_ALLREDUCE || s.op == HCCL_CMD_REDUCE_SCATTER || s.op == HCCL_CMD_ALLGATHER || s.op == HCCL_CMD_BROADCAST || s.op == HCCL_CMD_REDUCE)) {
         e.attrs.maxLevels = 1;
         e.attrs.enforceMaxLevels = true;
     }
@@ -220,6 +221,32 @@ void Reg(const HostAlgSpec& s)
         c.ratio = 1.0 / p;
         return std::vector<CostCoeff>{c};
     };
+    if (std::string(s.executor) == "concurrent") {
+        // two link sets side by side: the slower part decides (CostAggMode::MAX, executor_v2_base.h:130-141)
+        e.agg = CostAgg::MAX;
+        e.costCoeff = [steps, traffic](const TopoInfo& t, const OpDesc&) {
+            const LinkModel& lm = GlobalLinkModel();
+            const double p = (double)t.nRanks;
+            CostCoeff a, b;
+            a.A = traffic(p) / 3.0 / (lm.hostMemGBs * 1e3);           // mesh part: 56 / (56 + 112) of the data, three steps
+            a.C = 3.0 * lm.hostStepUs;
+            b.A = traffic(p) * 2.0 / 3.0 / (lm.hostMemGBs * 1e3);     // NHR part
+            b.C = (steps(p) + 1.0) * lm.hostStepUs;                    // + the fork / join of the second queue
+            a.net = b.net = NetType::HOST_MEM;
+            a.ratio = b.ratio = 1.0 / p;
+            return std::vector<CostCoeff>{a, b};
+        };
+    }
+    if (std::string(s.executor) == "tree") {
+        e.attrs.opCustomCheck = [](const OpDesc&, const TopoInfo&, std::string* why) {
+            std::unique_ptr<AlgoTreeNode> tree;
+            std::string err;
+            const std::string& text = GetEnvConfig().algoTree;
+            if (text.empty()) { *why = "op: HCCL_ALGO_TREE is not set"; return false; }
+            if (!ParseAlgoTree(text, &tree, &err)) { *why = "op: HCCL_ALGO_TREE: " + err; return false; }
+            return true;
+        };
+    }
     AlgRegistry::Instance().Register(std::move(e));
 }
 
@@ -281,6 +308,31 @@ void RegisterHostAlgorithms()
         Reg({keep.back().c_str(), op, HALG_A2A_MESH, "sole", {"Mesh"}, AlgoType::MESH, 1, false, Two, rs, true});
         keep.push_back(std::string(base) + "SolePairwise");
         Reg({keep.back().c_str(), op, HALG_A2A_PAIRWISE, "sole", {"Pairwise"}, AlgoType::PAIRWISE, 1, false, P1, rs, true});
+    }
+    // Concurrent, Pipeline, Nonuniform Bruck, hierarchical and tree executors (host_executors.cc).  Their step counts
+    // carry one extra step for the second queue or stage, so that automatic selection keeps the plain forms on ties.
+    auto TwoL1 = [](double p) { return 2 * Log2Ceil(p) + 1; };
+    auto L1 = [](double p) { return Log2Ceil(p) + 1; };
+    auto Four = [](double) { return 4.0; };
+    Reg({"HostAllReduceConcurrentMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, true, TwoL, ar, true});
+    Reg({"HostReduceScatterConcurrentMeshNHR", HCCL_CMD_REDUCE_SCATTER, HALG_RS_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, true, L, rs, true});
+    Reg({"HostAllGatherConcurrentMeshNHR", HCCL_CMD_ALLGATHER, HALG_AG_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, false, L, rs, true});
+    Reg({"HostAllReducePipelineMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_PIPELINE_MESH_NHR, "pipeline", {"Mesh", "NHR"}, AlgoType::OMNIPIPE, 2, true, TwoL1, ar, true});
+    Reg({"HostAllGatherPipelineMeshMesh", HCCL_CMD_ALLGATHER, HALG_AG_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, false, Four, rs, true});
+    Reg({"HostReduceScatterPipelineMeshMesh", HCCL_CMD_REDUCE_SCATTER, HALG_RS_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, true, Four, rs, true});
+    Reg({"HostBroadcastPipelineMeshMesh", HCCL_CMD_BROADCAST, HALG_BCAST_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, false, Four, ar, true});
+    Reg({"HostAllGatherSoleNB", HCCL_CMD_ALLGATHER, HALG_AG_NB, "sole", {"NB"}, AlgoType::NB, 1, false, L1, rs, true});
+    Reg({"HostBroadcastSoleNB", HCCL_CMD_BROADCAST, HALG_BCAST_NB, "sole", {"NB"}, AlgoType::NB, 1, false, L1, ar, true});
+    Reg({"HostScatterSoleNB", HCCL_CMD_SCATTER, HALG_SCATTER_NB, "sole", {"NB"}, AlgoType::NB, 1, false, L1, one, true});
+    Reg({"HostBroadcastSequenceMeshNHR", HCCL_CMD_BROADCAST, HALG_BCAST_SEQ_MESH_NHR, "sequence", {"Mesh", "NHR"}, AlgoType::NHR, 2, false, TwoL1, ar, true});
+    Reg({"HostReduceSequenceMeshNHR", HCCL_CMD_REDUCE, HALG_REDUCE_SEQ_MESH_NHR, "sequence", {"Mesh", "NHR"}, AlgoType::NHR, 2, true, TwoL1, ar, true});
+    Reg({"HostScatterSequenceMeshMesh", HCCL_CMD_SCATTER, HALG_SCATTER_SEQ_MESH_MESH, "sequence", {"Mesh", "Mesh"}, AlgoType::HIER, 2, false, Four, rs, true});
+    Reg({"HostBarrierSequenceMeshNHR", HCCL_CMD_BARRIER, HALG_BARRIER_SEQ_MESH_NHR, "sequence", {"Mesh", "NHR"}, AlgoType::HIER, 2, false, TwoL1, [](double) { return 0.0; }, true});
+    Reg({"HostAllReduceTree", HCCL_CMD_ALLREDUCE, HALG_AR_TREE, "tree", {"Tree"}, AlgoType::TREE, 1, true, TwoL1, ar, true});
+    for (HcclCMDType op : {HCCL_CMD_ALLTOALL, HCCL_CMD_ALLTOALLV, HCCL_CMD_ALLTOALLVC}) {
+        static std::vector<std::string> keepHier;
+        keepHier.push_back(std::string(op == HCCL_CMD_ALLTOALL ? "HostAlltoAll" : op == HCCL_CMD_ALLTOALLV ? "HostAlltoAllV" : "HostAlltoAllVC") + "HierMeshMesh");
+        Reg({keepHier.back().c_str(), op, HALG_A2A_HIER, "hier", {"Mesh", "Mesh"}, AlgoType::HIER, 2, false, Four, ar, true});
     }
     // point to point and barrier
     Reg({"HostSendSoleMesh", HCCL_CMD_SEND, HALG_P2P_DIRECT, "sole", {"Direct"}, AlgoType::MESH, 1, false, one, one, true});

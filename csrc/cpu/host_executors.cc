@@ -1,0 +1,653 @@
+// Executors and templates of the host engine beyond the Sole / Sequence /
+// Parallel / OrderPreserved set of host_templates.cc:
+//
+//   Concurrent - two templates on the same ranks over two disjoint link sets
+//       (the reference pairs the mesh links with the CLOS links and costs the
+//       pair with CostAggMode::MAX, executor_v2_base.h:130-141,
+//       ins_v2_all_reduce_concurrent_executor.cc): the data is split by the
+//       bandwidth ratio, part A runs the mesh template on queue 0 while part B
+//       runs NHR on queue 1.
+//   Pipeline (the reference's OmniPipe / PipeLine 2D executors,
+//       ins_v2_all_reduce_omnipipe_executor.cc, coll_algo_intro/Pipeline.md):
+//       the data is cut in at most five steps; step i's inter-server stage runs
+//       beside step i + 1's intra-server stage, each stage on its own queue.
+//   Nonuniform Bruck (HCCL_ALGO "NB", scatter_nb.cc): AllGather, Broadcast and a
+//       binomial-tree Scatter in ceil(log2 p) steps for any p.
+//   Hierarchical AlltoAll(V/VC) (all_to_all_v/.../aicpu/hier/*): intra-server
+//       stage into relays, meta table, inter-server stage.
+//   Sequence forms of Broadcast, Reduce, Scatter and Barrier on two levels.
+//   Tree executor (experimental/ops/op_common/recursive_executor/*, RFC 0003):
+//       one executor that interprets a tree of seq / par / rev nodes with
+//       template leaves, given in HCCL_ALGO_TREE.
+#include <algorithm>
+#include <cstring>
+#include <memory>
+#include <numeric>
+#include "../core/config.h"
+#include "../core/log.h"
+#include "../ops/op_common.h"
+#include "../ops/param_check.h"
+#include "host_templates.h"
+#include "host_tree.h"
+#include "host_world.h"
+
+namespace hccl {
+using namespace hosttpl;
+
+namespace {
+
+uint64_t Bytes(const OpParam& p) { return p.count * DataTypeSize(p.dtype); }
+
+// Bandwidth shares of the two link sets of a Concurrent / Parallel split.  Default: the reference's own figures for
+// its mesh links (56) and CLOS links (112) (rfcs/0003-executor-template-refactor.md:724);
+// HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO="a,b" overrides them.
+void SplitShares(double* a, double* b)
+{
+    const EnvConfig& env = GetEnvConfig();
+    *a = 56.0;
+    *b = 112.0;
+    if (env.splitRatio.size() >= 2 && env.splitRatio[0] + env.splitRatio[1] > 0) { *a = env.splitRatio[0]; *b = env.splitRatio[1]; }
+}
+
+const std::vector<uint32_t>* GroupOf(const AlgHierarchy& h, uint32_t level, uint32_t rank)
+{
+    for (auto& grp : h.infos[level])
+        if (std::find(grp.begin(), grp.end(), rank) != grp.end()) return &grp;
+    return nullptr;
+}
+uint32_t IndexIn(const std::vector<uint32_t>& grp, uint32_t rank) { return (uint32_t)(std::find(grp.begin(), grp.end(), rank) - grp.begin()); }
+
+// ---------------------------------------------------------------- Nonuniform Bruck
+void NbAllGather(Ctx& c, const Group& g, const Work& wk)
+{
+    const uint32_t p = g.size();
+    if (p == 1) return;
+    const uint32_t me = g.world(g.me);
+    for (const BruckStep& s : BruckAllGatherSteps(p, g.me)) {
+        const uint32_t to = g.world(s.sendTo), from = g.world(s.recvFrom);
+        c.x.Post(from, N_READY, c.q);      // my W may be written
+        c.x.Wait(to, N_READY, c.q);
+        for (uint32_t k = 0; k < s.nBlocks; ++k) {
+            uint64_t b, e;
+            Slice(wk, p, (s.firstSendBlock + k) % p, &b, &e);
+            c.x.Copy(wk.At(to, b), wk.At(me, b), (e - b) * wk.es, c.q);
+        }
+        c.x.Post(to, N_DATA, c.q);
+        c.x.Wait(from, N_DATA, c.q);
+    }
+}
+
+HcclResult NbScatter(HostWorld& w, HostPrims& x, const Group& all, uint32_t rank, const OpParam& p)
+{
+    const uint32_t n = all.size();
+    const uint64_t blk = Bytes(p);
+    if ((uint64_t)n * blk > w.scratchBytes()) {
+        HCCL_ERROR("host engine: tree Scatter stages %llu bytes, the scratch buffer has %llu (raise HCCL_BUFFSIZE)", (unsigned long long)(n * blk),
+                   (unsigned long long)w.scratchBytes());
+        return HCCL_E_MEMORY;
+    }
+    const uint32_t v = (rank + n - p.root) % n;
+    x.SyncGroup(all.ranks, N_READY);
+    for (const TreeScatterStep& s : BinomialScatterSteps(n, v)) {
+        const uint32_t peer = (p.root + s.peer) % n;
+        if (s.sends) {
+            for (uint32_t k = 0; k < s.nBlocks; ++k) {
+                const uint32_t rel = s.firstBlock + k, owner = (p.root + rel) % n;
+                const Mem src = rank == p.root ? In(rank, (uint64_t)owner * blk) : Scratch(rank, (uint64_t)rel * blk);
+                x.Copy(Scratch(peer, (uint64_t)rel * blk), src, blk);
+            }
+            x.Post(peer, N_DATA);
+        } else if (s.receives) {
+            x.Wait(peer, N_DATA);
+        }
+    }
+    if (rank == p.root) x.Copy(Out(rank), In(rank, (uint64_t)rank * blk), blk);
+    else x.Copy(Out(rank), Scratch(rank, (uint64_t)v * blk), blk);
+    x.SyncGroup(all.ranks, N_DONE);
+    return HCCL_SUCCESS;
+}
+
+// ---------------------------------------------------------------- Concurrent
+// AllReduce on OUTPUT (already holding the rank's input): part A mesh two-shot, part B NHR.
+void ConcurrentAllReduce(HostWorld& w, HostPrims& x, const Group& all, const Work& wk)
+{
+    double sa, sb;
+    SplitShares(&sa, &sb);
+    const uint64_t a = BandwidthSplit(wk.count, sa, sb, std::max<uint64_t>(1, 128 / wk.es));
+    const Work A{wk.buf, wk.base, a, wk.es}, B{wk.buf, wk.base + a * wk.es, wk.count - a, wk.es};
+    Ctx ca{w, x, 0, 0, 0};
+    Ctx cb{w, x, 1, 0, w.scratchBytes()};
+    if (A.count) AllReduceBy(Fam::MESH, ca, all, A);
+    if (B.count) AllReduceBy(Fam::NHR, cb, all, B);
+}
+
+// ReduceScatter: W_A / W_B are the two parts of every rank's blocks, laid out part by part in the upper half of scratch.
+void ConcurrentReduceScatter(HostWorld& w, HostPrims& x, const Group& all, uint32_t rank, const OpParam& p)
+{
+    const uint32_t n = all.size(), es = DataTypeSize(p.dtype);
+    double sa, sb;
+    SplitShares(&sa, &sb);
+    const uint64_t a = BandwidthSplit(p.count, sa, sb, std::max<uint64_t>(1, 128 / es)), b = p.count - a;
+    const uint64_t wOff = w.scratchBytes() / 2;
+    const Work A{BufKind::SCRATCH, wOff, a * n, es}, B{BufKind::SCRATCH, wOff + a * n * es, b * n, es};
+    for (uint32_t j = 0; j < n; ++j) {
+        if (a) x.Copy(A.At(rank, (uint64_t)j * a), In(rank, (uint64_t)j * p.count * es), a * es);
+        if (b) x.Copy(B.At(rank, (uint64_t)j * b), In(rank, ((uint64_t)j * p.count + a) * es), b * es, 1);
+    }
+    Ctx ca{w, x, 0, 0, 0};
+    Ctx cb{w, x, 1, 0, w.scratchBytes() / 2};
+    if (a) { MeshReduceScatter(ca, all, A); x.Copy(Out(rank), A.At(rank, (uint64_t)rank * a), a * es); }
+    if (b) { NhrReduceScatter(cb, all, B); x.Copy(Out(rank, a * es), B.At(rank, (uint64_t)rank * b), b * es, 1); }
+    x.SyncGroup(all.ranks, N_LEVEL);     // nobody reuses its scratch while a peer may still read it
+}
+
+// AllGather: part A of every block is pulled straight from the owner's INPUT over the mesh; part B is gathered by NHR
+// in scratch and copied out.
+void ConcurrentAllGather(HostWorld& w, HostPrims& x, const Group& all, uint32_t rank, const OpParam& p)
+{
+    const uint32_t n = all.size(), es = DataTypeSize(p.dtype);
+    double sa, sb;
+    SplitShares(&sa, &sb);
+    uint64_t a = BandwidthSplit(p.count, sa, sb, std::max<uint64_t>(1, 128 / es));
+    if ((p.count - a) * n * es > w.scratchBytes()) a = p.count;      // part B has to fit the staging buffer
+    const uint64_t b = p.count - a;
+    x.SyncGroup(all.ranks, N_READY);
+    for (uint32_t k = 0; k < n && a; ++k) {
+        const uint32_t j = (rank + k) % n;
+        x.Copy(Out(rank, (uint64_t)j * p.count * es), In(j), a * es);
+    }
+    if (b) {
+        const Work B{BufKind::SCRATCH, 0, b * n, es};
+        x.Copy(B.At(rank, (uint64_t)rank * b), In(rank, a * es), b * es, 1);
+        Ctx cb{w, x, 1, 0, 0};
+        NhrAllGather(cb, all, B);
+        for (uint32_t j = 0; j < n; ++j) x.Copy(Out(rank, ((uint64_t)j * p.count + a) * es), B.At(rank, (uint64_t)j * b), b * es, 1);
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+}
+
+// ---------------------------------------------------------------- two-level Sequence forms of the rooted operators
+struct TwoLevel {
+    AlgHierarchy h;
+    Group g0, g1;                 // my server, my local index across servers
+    uint32_t rootLocal = 0;       // local index of the root inside its server
+    uint32_t rootServer = 0;      // index of the root's server in level-1 order
+    uint32_t relay = 0;           // member of my server that shares the root's local index
+    bool flat = false;            // the topology has one level only
+};
+HcclResult MatchTwoLevel(HostWorld& w, uint32_t rank, uint32_t root, TwoLevel* t)
+{
+    CHK_RET(MatchTopo(w.Topo(rank), TopoMatchKind::TWO_LEVEL, &t->h));
+    t->flat = t->h.levels() < 2;
+    if (t->flat) { t->g0 = WholeGroup(w, rank); t->g1.ranks = {rank}; t->g1.me = 0; t->rootLocal = root; t->relay = root; return HCCL_SUCCESS; }
+    LevelGroup(t->h, 0, rank, &t->g0);
+    LevelGroup(t->h, 1, rank, &t->g1);
+    const std::vector<uint32_t>* rs = GroupOf(t->h, 0, root);
+    const std::vector<uint32_t>* rl = GroupOf(t->h, 1, root);
+    if (!rs || !rl) return HCCL_E_INTERNAL;
+    t->rootLocal = IndexIn(*rs, root);
+    t->rootServer = IndexIn(*rl, root);
+    t->relay = t->g0.world(t->rootLocal);
+    return HCCL_SUCCESS;
+}
+
+// Broadcast: the root feeds the members of its level-1 group (one per server) by scatter + NHR AllGather, then every
+// server spreads the data from that member by scatter + mesh AllGather.
+HcclResult SequenceBroadcast(HostWorld& w, HostPrims& x, uint32_t rank, const OpParam& p)
+{
+    TwoLevel t;
+    CHK_RET(MatchTwoLevel(w, rank, p.root, &t));
+    const uint32_t es = DataTypeSize(p.dtype);
+    const Work wk{BufKind::OUTPUT, 0, p.count, es};
+    Ctx c{w, x, 0, 0, w.scratchBytes()};
+    const Group all = WholeGroup(w, rank);
+    x.SyncGroup(all.ranks, N_READY);
+    if (!t.flat && t.g0.me == t.rootLocal) {
+        if (rank != p.root) {
+            uint64_t b, e;
+            Slice(wk, t.g1.size(), t.g1.me, &b, &e);
+            x.Copy(Out(rank, b * es), Out(p.root, b * es), (e - b) * es);
+        }
+        x.SyncGroup(t.g1.ranks, N_DATA);
+        NhrAllGather(c, t.g1, wk);
+    }
+    x.SyncGroup(t.g0.ranks, N_LEVEL);
+    if (rank != t.relay) {
+        uint64_t b, e;
+        Slice(wk, t.g0.size(), t.g0.me, &b, &e);
+        x.Copy(Out(rank, b * es), Out(t.relay, b * es), (e - b) * es);
+    }
+    x.SyncGroup(t.g0.ranks, N_AUX);
+    MeshAllGather(c, t.g0, wk);
+    return HCCL_SUCCESS;
+}
+
+// Reduce: mesh ReduceScatter inside every server, NHR ReduceScatter across servers on the slice that is left, then the
+// root collects the n pieces.
+HcclResult SequenceReduce(HostWorld& w, HostPrims& x, uint32_t rank, const OpParam& p)
+{
+    TwoLevel t;
+    CHK_RET(MatchTwoLevel(w, rank, p.root, &t));
+    const uint32_t es = DataTypeSize(p.dtype);
+    const uint64_t wOff = w.scratchBytes() / 2;
+    x.Copy(Scratch(rank, wOff), In(rank), Bytes(p));
+    const Work wk{BufKind::SCRATCH, wOff, p.count, es};
+    Ctx c{w, x, 0, 0, w.scratchBytes() / 2};
+    const Group all = WholeGroup(w, rank);
+    MeshReduceScatter(c, t.g0, wk);
+    const Work mine = SubWork(wk, t.g0.size(), t.g0.me);
+    if (!t.flat) NhrReduceScatter(c, t.g1, mine);
+    x.SyncGroup(all.ranks, N_DATA);
+    if (rank == p.root) {
+        for (uint32_t l = 0; l < t.g0.size(); ++l) {
+            const Work sl = SubWork(wk, t.g0.size(), l);
+            const std::vector<uint32_t>* col = t.flat ? nullptr : GroupOf(t.h, 1, t.g0.world(l));
+            const uint32_t servers = t.flat ? 1 : (uint32_t)col->size();
+            for (uint32_t s = 0; s < servers; ++s) {
+                const Work piece = SubWork(sl, servers, s);
+                const uint32_t holder = t.flat ? t.g0.world(l) : (*col)[s];
+                x.Copy(Out(rank, piece.base - wOff), Scratch(holder, piece.base), piece.count * es);
+            }
+        }
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+    return HCCL_SUCCESS;
+}
+
+// Scatter: the root hands every server's blocks to the member that shares its local index (level 1), which hands
+// them on inside the server (level 0).
+HcclResult SequenceScatter(HostWorld& w, HostPrims& x, uint32_t rank, const OpParam& p)
+{
+    TwoLevel t;
+    CHK_RET(MatchTwoLevel(w, rank, p.root, &t));
+    const uint64_t blk = Bytes(p);
+    if ((uint64_t)t.g0.size() * blk > w.scratchBytes()) {
+        HCCL_ERROR("host engine: hierarchical Scatter stages %llu bytes per server, the scratch buffer has %llu", (unsigned long long)(t.g0.size() * blk),
+                   (unsigned long long)w.scratchBytes());
+        return HCCL_E_MEMORY;
+    }
+    const Group all = WholeGroup(w, rank);
+    x.SyncGroup(all.ranks, N_READY);
+    if (rank == t.relay && rank != p.root)
+        for (uint32_t l = 0; l < t.g0.size(); ++l) x.Copy(Scratch(rank, (uint64_t)l * blk), In(p.root, (uint64_t)t.g0.world(l) * blk), blk);
+    x.SyncGroup(t.g0.ranks, N_DATA);
+    if (t.relay == p.root) x.Copy(Out(rank), In(p.root, (uint64_t)rank * blk), blk);
+    else x.Copy(Out(rank), Scratch(t.relay, (uint64_t)t.g0.me * blk), blk);
+    x.SyncGroup(all.ranks, N_DONE);
+    return HCCL_SUCCESS;
+}
+
+// Barrier: gather inside the server, dissemination across servers, release inside the server.
+HcclResult SequenceBarrier(HostWorld& w, HostPrims& x, uint32_t rank)
+{
+    TwoLevel t;
+    CHK_RET(MatchTwoLevel(w, rank, 0, &t));
+    x.SyncGroup(t.g0.ranks, N_READY);
+    const uint32_t S = t.g1.size();
+    for (uint32_t s = 0; s < CeilLog2(S); ++s) {
+        const uint32_t d = (1u << s) % S;
+        x.Post(t.g1.world((t.g1.me + d) % S), N_LEVEL);
+        x.Wait(t.g1.world((t.g1.me + S - d) % S), N_LEVEL);
+    }
+    x.SyncGroup(t.g0.ranks, N_DONE);
+    return HCCL_SUCCESS;
+}
+
+// ---------------------------------------------------------------- hierarchical AlltoAll / V / VC
+// Rank (s, l) = member l of server s.  Stage 1 (inside the server): member l' collects, from every server-mate, the
+// blocks bound for the ranks (*, l') and keeps them in scratch ordered by (source member, destination server); blocks for
+// itself go straight to its output.  It then publishes where each (source member, destination server) block sits.
+// Stage 2 (across servers): rank (s', l') reads that table from every (s, l') and pulls its blocks.  Every block thus
+// crosses the inter-server links once, in messages that carry a whole server's contribution.
+// Scratch layout per rank: [n send displacements][n send sizes][L x S staging offsets] (bytes, uint64), then the staging.
+HcclResult HierAlltoAll(HostWorld& w, HostPrims& x, uint32_t rank, const OpParam& p)
+{
+    AlgHierarchy h;
+    CHK_RET(MatchTopo(w.Topo(rank), TopoMatchKind::TWO_LEVEL, &h));
+    const uint32_t n = w.nRanks();
+    const Group all = WholeGroup(w, rank);
+    Group g0, g1;
+    if (h.levels() < 2) { g0 = all; g1.ranks = {rank}; g1.me = 0; }
+    else { LevelGroup(h, 0, rank, &g0); LevelGroup(h, 1, rank, &g1); }
+    const uint32_t L = g0.size(), S = g1.size();
+    const uint32_t es = DataTypeSize(p.dtype), res = DataTypeSize(p.recvType);
+    const uint64_t header = ((uint64_t)(2 * n + L * S) * 8 + 127) / 128 * 128;
+    auto table = [&](uint32_t r) { return reinterpret_cast<uint64_t*>(w.Resolve(Scratch(r, 0))); };
+    uint64_t* mine = table(rank);
+    for (uint32_t j = 0; j < n; ++j) { mine[j] = p.sdispls[j] * es; mine[n + j] = p.sendCounts[j] * es; }
+    x.SyncGroup(all.ranks, N_READY);
+    // stage 1
+    uint64_t off = header;
+    bool fits = true;
+    for (uint32_t l = 0; l < L; ++l) {
+        const uint32_t m = g0.world(l);
+        const uint64_t* tm = table(m);
+        for (uint32_t s = 0; s < S; ++s) {
+            const uint32_t d = g1.world(s);
+            const uint64_t bytes = tm[n + d];
+            mine[2 * n + l * S + s] = off;
+            if (d == rank) { x.Copy(Out(rank, p.rdispls[m] * res), In(m, tm[d]), bytes); continue; }
+            if (off + bytes > w.scratchBytes()) { fits = false; break; }
+            x.Copy(Scratch(rank, off), In(m, tm[d]), bytes);
+            off += bytes;
+        }
+    }
+    if (!fits) {
+        w.Abort("hierarchical AlltoAll: the blocks relayed by rank " + std::to_string(rank) + " exceed the scratch buffer (raise HCCL_BUFFSIZE)");
+        return HCCL_E_MEMORY;
+    }
+    x.SyncGroup(g1.ranks, N_DATA);
+    // stage 2
+    for (uint32_t k = 1; k < S; ++k) {
+        const uint32_t s = (g1.me + k) % S, relay = g1.world(s);
+        const std::vector<uint32_t>* srv = GroupOf(h, 0, relay);
+        const uint64_t* tr = table(relay);
+        for (uint32_t l = 0; l < L; ++l) {
+            const uint32_t src = (*srv)[l];
+            x.Copy(Out(rank, p.rdispls[src] * res), Scratch(relay, tr[2 * n + l * S + g1.me]), p.recvCounts[src] * res);
+        }
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+    return HCCL_SUCCESS;
+}
+
+// ---------------------------------------------------------------- Pipeline (2-D)
+constexpr uint32_t kMaxPipeSteps = 5;
+
+// AllReduce: stage 0 = mesh ReduceScatter inside the server, stage 1 = NHR AllReduce across servers on the slice that
+// is left, stage 2 = mesh AllGather inside the server; one queue per stage.
+HcclResult PipelineAllReduce(HostWorld& w, HostPrims& x, uint32_t rank, const Work& wk)
+{
+    AlgHierarchy h;
+    CHK_RET(MatchTopo(w.Topo(rank), TopoMatchKind::TWO_LEVEL, &h));
+    Ctx flat{w, x, 0, 0, w.scratchBytes()};
+    if (h.levels() < 2) { AllReduceBy(Fam::MESH, flat, WholeGroup(w, rank), wk); return HCCL_SUCCESS; }
+    Group g0, g1;
+    LevelGroup(h, 0, rank, &g0);
+    LevelGroup(h, 1, rank, &g1);
+    const uint32_t steps = PipelineStepCount(wk.count, (uint64_t)g0.size() * g1.size() * std::max<uint64_t>(1, 128 / wk.es), kMaxPipeSteps);
+    for (const PipeSlot& s : PipelineSchedule(3, steps)) {
+        const Work chunk = SubWork(wk, steps, s.step);
+        Ctx c{w, x, s.stage, 0, w.scratchBytes()};
+        if (s.stage == 0) MeshReduceScatter(c, g0, chunk);
+        else if (s.stage == 1) AllReduceBy(Fam::NHR, c, g1, SubWork(chunk, g0.size(), g0.me));
+        else MeshAllGather(c, g0, chunk);
+    }
+    return HCCL_SUCCESS;
+}
+
+// AllGather: every block is cut in steps.  Stage 0 pulls a piece of the server-mates' inputs (mesh), stage 1 pulls the
+// same piece of every other server's blocks from the rank with my local index there, once that rank's stage 0 of the
+// step is done.  Ranks are numbered server by server.
+HcclResult PipelineAllGather(HostWorld& w, HostPrims& x, uint32_t rank, const OpParam& p)
+{
+    AlgHierarchy h;
+    CHK_RET(MatchTopo(w.Topo(rank), TopoMatchKind::TWO_LEVEL, &h));
+    const Group all = WholeGroup(w, rank);
+    Group g0 = all, g1;
+    g1.ranks = {rank};
+    g1.me = 0;
+    if (h.levels() >= 2) { LevelGroup(h, 0, rank, &g0); LevelGroup(h, 1, rank, &g1); }
+    const uint32_t es = DataTypeSize(p.dtype);
+    const uint32_t steps = PipelineStepCount(p.count, std::max<uint64_t>(1, 128 / es), kMaxPipeSteps);
+    x.SyncGroup(all.ranks, N_READY);
+    for (const PipeSlot& s : PipelineSchedule(2, steps)) {
+        uint64_t b, e;
+        SliceOf(p.count, steps, s.step, &b, &e);
+        if (s.stage == 0) {
+            for (uint32_t k = 0; k < g0.size(); ++k) {
+                const uint32_t j = g0.world((g0.me + k) % g0.size());
+                x.Copy(Out(rank, ((uint64_t)j * p.count + b) * es), In(j, b * es), (e - b) * es, 0);
+            }
+        } else {
+            x.SyncGroup(g1.ranks, N_DATA, 1);
+            for (uint32_t k = 1; k < g1.size(); ++k) {
+                const uint32_t peer = g1.world((g1.me + k) % g1.size());
+                for (uint32_t j : *GroupOf(h, 0, peer)) x.Copy(Out(rank, ((uint64_t)j * p.count + b) * es), Out(peer, ((uint64_t)j * p.count + b) * es), (e - b) * es, 1);
+            }
+        }
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+    return HCCL_SUCCESS;
+}
+
+// ReduceScatter, rank (s, l): stage 0 folds, for every server s', the piece of block (s', l) over the members of my
+// server into scratch slot s'; stage 1 folds slot s of the ranks (*, l) into my output.
+HcclResult PipelineReduceScatter(HostWorld& w, HostPrims& x, uint32_t rank, const OpParam& p)
+{
+    AlgHierarchy h;
+    CHK_RET(MatchTopo(w.Topo(rank), TopoMatchKind::TWO_LEVEL, &h));
+    const Group all = WholeGroup(w, rank);
+    Group g0 = all, g1;
+    g1.ranks = {rank};
+    g1.me = 0;
+    if (h.levels() >= 2) { LevelGroup(h, 0, rank, &g0); LevelGroup(h, 1, rank, &g1); }
+    const uint32_t es = DataTypeSize(p.dtype), S = g1.size();
+    const uint64_t blk = p.count * es;
+    if ((uint64_t)S * blk > w.scratchBytes()) {
+        HCCL_ERROR("host engine: pipelined ReduceScatter stages %llu bytes, the scratch buffer has %llu", (unsigned long long)(S * blk), (unsigned long long)w.scratchBytes());
+        return HCCL_E_MEMORY;
+    }
+    const uint32_t steps = PipelineStepCount(p.count, std::max<uint64_t>(1, 128 / es), kMaxPipeSteps);
+    x.SyncGroup(all.ranks, N_READY);
+    for (const PipeSlot& s : PipelineSchedule(2, steps)) {
+        uint64_t b, e;
+        SliceOf(p.count, steps, s.step, &b, &e);
+        const uint64_t len = (e - b) * es;
+        if (s.stage == 0) {
+            for (uint32_t t = 0; t < S; ++t) {
+                const uint32_t owner = g1.world(t);                 // rank (t, l): the block my partial belongs to
+                const Mem slot = Scratch(rank, (uint64_t)t * blk + b * es);
+                x.Copy(slot, In(rank, (uint64_t)owner * blk + b * es), len, 0);
+                for (uint32_t k = 1; k < g0.size(); ++k) x.Reduce(slot, In(g0.world((g0.me + k) % g0.size()), (uint64_t)owner * blk + b * es), len, 0);
+            }
+        } else {
+            x.SyncGroup(g1.ranks, N_DATA, 1);
+            x.Copy(Out(rank, b * es), Scratch(rank, (uint64_t)g1.me * blk + b * es), len, 1);
+            for (uint32_t k = 1; k < S; ++k) x.Reduce(Out(rank, b * es), Scratch(g1.world((g1.me + k) % S), (uint64_t)g1.me * blk + b * es), len, 1);
+        }
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+    return HCCL_SUCCESS;
+}
+
+// Broadcast: stage 0 moves a step from the root to the member of every server that shares its local index, stage 1
+// spreads the step inside every server.
+HcclResult PipelineBroadcast(HostWorld& w, HostPrims& x, uint32_t rank, const OpParam& p)
+{
+    TwoLevel t;
+    CHK_RET(MatchTwoLevel(w, rank, p.root, &t));
+    const uint32_t es = DataTypeSize(p.dtype);
+    const uint32_t steps = PipelineStepCount(p.count, std::max<uint64_t>(1, 128 / es), kMaxPipeSteps);
+    const Group all = WholeGroup(w, rank);
+    x.SyncGroup(all.ranks, N_READY);
+    for (const PipeSlot& s : PipelineSchedule(2, steps)) {
+        uint64_t b, e;
+        SliceOf(p.count, steps, s.step, &b, &e);
+        if (s.stage == 0) {
+            if (rank == t.relay && rank != p.root) x.Copy(Out(rank, b * es), Out(p.root, b * es), (e - b) * es, 0);
+        } else {
+            x.SyncGroup(t.g0.ranks, N_DATA, 1);
+            if (rank != t.relay) x.Copy(Out(rank, b * es), Out(t.relay, b * es), (e - b) * es, 1);
+        }
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+    return HCCL_SUCCESS;
+}
+
+// ---------------------------------------------------------------- tree executor (AllReduce)
+struct TreeRun {
+    HostWorld& w;
+    HostPrims& x;
+    const AlgHierarchy& h;
+    uint32_t rank;
+};
+
+bool LeafFam(const std::string& leaf, Fam* f)
+{
+    if (leaf == "mesh") *f = Fam::MESH;
+    else if (leaf == "ring") *f = Fam::RING;
+    else if (leaf == "nhr" || leaf == "nb") *f = Fam::NHR;
+    else if (leaf == "rhd") *f = Fam::RHD;
+    else return false;
+    return true;
+}
+void LeafReduceScatter(const std::string& leaf, Ctx& c, const Group& g, const Work& wk)
+{
+    Fam f = Fam::MESH;
+    LeafFam(leaf, &f);
+    ReduceScatterBy(f, c, g, wk);
+}
+void LeafAllGather(const std::string& leaf, Ctx& c, const Group& g, const Work& wk)
+{
+    if (leaf == "nb") { NbAllGather(c, g, wk); return; }
+    Fam f = Fam::MESH;
+    LeafFam(leaf, &f);
+    AllGatherBy(f, c, g, wk);
+}
+// The ranks that can differ from me only in the given levels, in rank order (one level: that level's group).
+Group FlatGroup(const TreeRun& t, const std::vector<uint32_t>& levels)
+{
+    std::vector<uint32_t> set = {t.rank};
+    for (uint32_t l : levels) {
+        std::vector<uint32_t> next;
+        for (uint32_t r : set)
+            for (uint32_t m : *GroupOf(t.h, l, r)) next.push_back(m);
+        std::sort(next.begin(), next.end());
+        next.erase(std::unique(next.begin(), next.end()), next.end());
+        set.swap(next);
+    }
+    Group g;
+    g.ranks = set;
+    g.me = IndexIn(set, t.rank);
+    return g;
+}
+// Scratch bytes a subtree may use per byte of its data: every level of a seq works in a region of its own (a template
+// such as the ring writes into its neighbour's staging without asking first, so it must not share a region with the
+// level before it), and three levels of at least one rank each need at most three times the data.
+constexpr uint64_t kTreeScratchPerByte = 3;
+
+void EvalTree(const TreeRun& t, const AlgoTreeNode& n, std::vector<uint32_t> levels, const Work& wk, uint32_t queue, uint64_t scratchOff)
+{
+    if (wk.count == 0) return;
+    switch (n.kind) {
+        case AlgoTreeNode::Kind::LEAF: {
+            Ctx c{t.w, t.x, queue, scratchOff, wk.count * wk.es};
+            const Group g = FlatGroup(t, levels);
+            if (n.leaf == "nb") { NhrReduceScatter(c, g, wk); NbAllGather(c, g, wk); }
+            else { Fam f = Fam::MESH; LeafFam(n.leaf, &f); AllReduceBy(f, c, g, wk); }
+            break;
+        }
+        case AlgoTreeNode::Kind::REV:
+            std::reverse(levels.begin(), levels.end());
+            EvalTree(t, *n.kids[0], levels, wk, queue, scratchOff);
+            break;
+        case AlgoTreeNode::Kind::PAR: {
+            double sa = n.shareA, sb = n.shareB;
+            if (sa + sb <= 0) SplitShares(&sa, &sb);
+            const uint64_t a = BandwidthSplit(wk.count, sa, sb, std::max<uint64_t>(1, 128 / wk.es));
+            const Work A{wk.buf, wk.base, a, wk.es}, B{wk.buf, wk.base + a * wk.es, wk.count - a, wk.es};
+            EvalTree(t, *n.kids[0], levels, A, queue, scratchOff);
+            EvalTree(t, *n.kids[1], levels, B, queue + AlgoTreeQueues(*n.kids[0]), scratchOff + kTreeScratchPerByte * a * wk.es);
+            break;
+        }
+        case AlgoTreeNode::Kind::SEQ: {
+            const size_t lower = n.kids.size() - 1;
+            std::vector<Group> groups(lower);
+            std::vector<Work> works(lower);
+            Work cur = wk;
+            std::vector<uint64_t> offs(lower);
+            uint64_t off = scratchOff;
+            for (size_t i = 0; i < lower; ++i) {
+                groups[i] = FlatGroup(t, {levels[i]});
+                works[i] = cur;
+                offs[i] = off;
+                Ctx c{t.w, t.x, queue, off, cur.count * cur.es};
+                LeafReduceScatter(n.kids[i]->leaf, c, groups[i], cur);
+                off += cur.count * cur.es;
+                cur = SubWork(cur, groups[i].size(), groups[i].me);
+            }
+            EvalTree(t, *n.kids[lower], std::vector<uint32_t>(levels.begin() + (long)lower, levels.end()), cur, queue, off);
+            for (size_t i = lower; i-- > 0;) {
+                Ctx c{t.w, t.x, queue, offs[i], works[i].count * works[i].es};
+                LeafAllGather(n.kids[i]->leaf, c, groups[i], works[i]);
+            }
+            break;
+        }
+    }
+}
+
+HcclResult TreeAllReduce(HostWorld& w, HostPrims& x, uint32_t rank, const Work& wk)
+{
+    std::unique_ptr<AlgoTreeNode> tree;
+    std::string err;
+    if (!ParseAlgoTree(GetEnvConfig().algoTree, &tree, &err)) { HCCL_ERROR("HCCL_ALGO_TREE: %s", err.c_str()); return HCCL_E_PARA; }
+    AlgHierarchy h;
+    const TopoInfo& topo = w.Topo(rank);
+    CHK_RET(MatchTopo(topo, topo.nPods > 1 ? TopoMatchKind::THREE_LEVEL : topo.nServers > 1 ? TopoMatchKind::TWO_LEVEL : TopoMatchKind::ONE_LEVEL, &h));
+    if (AlgoTreeMinLevels(*tree) > h.levels()) {
+        HCCL_ERROR("HCCL_ALGO_TREE '%s' needs %u topology levels, this communicator has %u", AlgoTreeText(*tree).c_str(), AlgoTreeMinLevels(*tree), h.levels());
+        return HCCL_E_PARA;
+    }
+    std::vector<uint32_t> levels(h.levels());
+    std::iota(levels.begin(), levels.end(), 0u);
+    const TreeRun t{w, x, h, rank};
+    EvalTree(t, *tree, levels, wk, 0, 0);
+    return HCCL_SUCCESS;
+}
+
+}  // namespace
+
+HcclResult RunHostExecutorExt(HostWorld& w, uint32_t rank, int alg, const OpParam& p)
+{
+    HostPrims x(&w, rank);
+    const uint32_t n = w.nRanks();
+    const uint32_t es = DataTypeSize(p.dtype);
+    const Group all = WholeGroup(w, rank);
+    Ctx c{w, x, 0, 0, w.scratchBytes()};
+    HcclResult r = HCCL_SUCCESS;
+    switch (alg) {
+        case HALG_AR_CONCURRENT_MESH_NHR: case HALG_AR_PIPELINE_MESH_NHR: case HALG_AR_TREE: {
+            x.Copy(Out(rank), In(rank), Bytes(p));
+            const Work wk{BufKind::OUTPUT, 0, p.count, es};
+            if (alg == HALG_AR_CONCURRENT_MESH_NHR) ConcurrentAllReduce(w, x, all, wk);
+            else if (alg == HALG_AR_PIPELINE_MESH_NHR) r = PipelineAllReduce(w, x, rank, wk);
+            else r = TreeAllReduce(w, x, rank, wk);
+            break;
+        }
+        case HALG_RS_CONCURRENT_MESH_NHR: ConcurrentReduceScatter(w, x, all, rank, p); break;
+        case HALG_AG_CONCURRENT_MESH_NHR: ConcurrentAllGather(w, x, all, rank, p); break;
+        case HALG_AG_PIPELINE_MESH_MESH: r = PipelineAllGather(w, x, rank, p); break;
+        case HALG_RS_PIPELINE_MESH_MESH: r = PipelineReduceScatter(w, x, rank, p); break;
+        case HALG_BCAST_PIPELINE_MESH_MESH: r = PipelineBroadcast(w, x, rank, p); break;
+        case HALG_AG_NB: {
+            x.Copy(Out(rank, (uint64_t)rank * p.count * es), In(rank), p.count * es);
+            NbAllGather(c, all, Work{BufKind::OUTPUT, 0, p.count * n, es});
+            break;
+        }
+        case HALG_BCAST_NB: {
+            const Work wk{BufKind::OUTPUT, 0, p.count, es};
+            x.SyncGroup(all.ranks, N_READY);
+            if (rank != p.root) {
+                uint64_t b, e;
+                Slice(wk, n, rank, &b, &e);
+                x.Copy(Out(rank, b * es), Out(p.root, b * es), (e - b) * es);
+            }
+            x.SyncGroup(all.ranks, N_DATA);
+            NbAllGather(c, all, wk);
+            break;
+        }
+        case HALG_SCATTER_NB: r = NbScatter(w, x, all, rank, p); break;
+        case HALG_A2A_HIER: r = HierAlltoAll(w, x, rank, p); break;
+        case HALG_BCAST_SEQ_MESH_NHR: r = SequenceBroadcast(w, x, rank, p); break;
+        case HALG_REDUCE_SEQ_MESH_NHR: r = SequenceReduce(w, x, rank, p); break;
+        case HALG_SCATTER_SEQ_MESH_MESH: r = SequenceScatter(w, x, rank, p); break;
+        case HALG_BARRIER_SEQ_MESH_NHR: r = SequenceBarrier(w, x, rank); break;
+        default: return HCCL_E_NOT_SUPPORT;
+    }
+    if (r != HCCL_SUCCESS) return r;
+    if (x.failed() || w.aborted()) return HCCL_E_TIMEOUT;
+    return HCCL_SUCCESS;
+}
+
+}  // namespace hccl

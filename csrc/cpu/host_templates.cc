@@ -21,37 +21,11 @@
 #include "../core/log.h"
 #include "../ops/op_common.h"
 #include "../ops/param_check.h"
+#include "host_templates.h"
 #include "host_world.h"
 
 namespace hccl {
-namespace {
-
-enum Notify : uint32_t { N_READY = 0, N_DATA = 1, N_DONE = 2, N_ACK = 3, N_LEVEL = 4, N_P2P_DATA = 5, N_P2P_ACK = 6, N_AUX = 7 };
-
-struct Group {
-    std::vector<uint32_t> ranks;   // world ranks, in group order
-    uint32_t me;                   // my index in `ranks`
-    uint32_t size() const { return (uint32_t)ranks.size(); }
-    uint32_t world(uint32_t idx) const { return ranks[idx]; }
-};
-
-// Working-buffer descriptor: where W lives on every rank (same kind and offset everywhere) and which byte range
-// [base, base + bytes) of it the template works on; slices are cut in elements of `es` bytes.
-struct Work {
-    BufKind buf;
-    uint64_t base;      // byte offset of the region inside the buffer
-    uint64_t count;     // elements in the region
-    uint32_t es;
-    Mem At(uint32_t worldRank, uint64_t elemOff) const { return Mem{worldRank, buf, base + elemOff * es}; }
-};
-
-struct Ctx {
-    HostWorld& w;
-    HostPrims& x;
-    uint32_t q;          // queue for the recorded tasks
-    uint64_t scratchOff; // start of the scratch area this template may use (bytes)
-    uint64_t scratchLen;
-};
+namespace hosttpl {
 
 void Slice(const Work& wk, uint32_t parts, uint32_t i, uint64_t* b, uint64_t* e) { SliceOf(wk.count, parts, i, b, e); }
 
@@ -303,7 +277,6 @@ void RhdAllGather(Ctx& c, const Group& g, const Work& wk, bool skipPre)
 }
 
 // ---------------------------------------------------------------- composition helpers
-enum class Fam { MESH, RING, NHR, RHD };
 void ReduceScatterBy(Fam f, Ctx& c, const Group& g, const Work& wk)
 {
     switch (f) {
@@ -382,12 +355,14 @@ void SequenceAllReduce(Ctx& c, const AlgHierarchy& h, uint32_t rank, const Work&
 
 uint64_t Bytes(const OpParam& p) { return p.count * DataTypeSize(p.dtype); }
 
-}  // namespace
+}  // namespace hosttpl
+using namespace hosttpl;
 
 uint64_t HostScratchMultiple(int alg, uint32_t n)
 {
     switch (alg) {
         case HALG_AR_MESH_ONESHOT: case HALG_AR_ORDER_PRESERVED: case HALG_RS_ORDER_PRESERVED: return n;
+        case HALG_AR_TREE: return 3;      // one staging region per level of the tree
         default: return 1;
     }
 }
@@ -668,9 +643,11 @@ HcclResult RunHostAlgorithm(HostWorld& w, uint32_t rank, int alg, const OpParam&
             }
             break;
         }
-        default:
-            HCCL_ERROR("host algorithm %d is not implemented", alg);
-            return HCCL_E_NOT_SUPPORT;
+        default: {
+            const HcclResult r = RunHostExecutorExt(w, rank, alg, p);
+            if (r == HCCL_E_NOT_SUPPORT) HCCL_ERROR("host algorithm %d is not implemented", alg);
+            return r;
+        }
     }
     if (x.failed() || w.aborted()) return HCCL_E_TIMEOUT;
     return HCCL_SUCCESS;

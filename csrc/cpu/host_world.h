@@ -169,6 +169,13 @@ enum HostAlg : int {
     HALG_SCATTER_MESH, HALG_SCATTER_NHR, HALG_SCATTER_RING,
     HALG_A2A_MESH, HALG_A2A_PAIRWISE,
     HALG_P2P_DIRECT, HALG_BARRIER_MESH, HALG_BARRIER_NHR, HALG_BARRIER_RHD,
+    // executors of host_executors.cc
+    HALG_AR_CONCURRENT_MESH_NHR, HALG_RS_CONCURRENT_MESH_NHR, HALG_AG_CONCURRENT_MESH_NHR,
+    HALG_AR_PIPELINE_MESH_NHR, HALG_AG_PIPELINE_MESH_MESH, HALG_RS_PIPELINE_MESH_MESH, HALG_BCAST_PIPELINE_MESH_MESH,
+    HALG_AG_NB, HALG_BCAST_NB, HALG_SCATTER_NB,
+    HALG_A2A_HIER,
+    HALG_BCAST_SEQ_MESH_NHR, HALG_REDUCE_SEQ_MESH_NHR, HALG_SCATTER_SEQ_MESH_MESH, HALG_BARRIER_SEQ_MESH_NHR,
+    HALG_AR_TREE,
     HALG_COUNT
 };
 // Runs host algorithm `alg` for this rank; the world is already inside Enter().
