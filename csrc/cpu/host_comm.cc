@@ -2,7 +2,9 @@
 // executor loop + template run) and registration of the host algorithms.
 #include "host_comm.h"
 #include <algorithm>
+#include <chrono>
 #include <cstring>
+#include <thread>
 #include "../core/comm.h"
 #include "../core/json.h"
 #include "../core/log.h"
@@ -155,10 +157,24 @@ HcclResult HostExecOp(CommImpl* c, OpParam& p)
         const void* in = sub.send;
         void* out = sub.recv;
         if (p.op == HCCL_CMD_BROADCAST) { in = sub.recv; }
-        HcclResult r = w.Enter(rank, hd, in, out, InBytes(sub, n), OutBytes(sub, n));
-        if (r == HCCL_SUCCESS) r = RunHostAlgorithm(w, rank, alg, sub);
-        HcclResult l = w.Leave(rank);
-        if (r == HCCL_SUCCESS) r = l;
+        // Operator retry (HCCL_OP_RETRY_ENABLE, HCCL_OP_RETRY_PARAMS; reference HCCL_OP_RETRY_ENABLE.md:7-42): an
+        // attempt that ended in a timeout or a peer's failure is issued again from its input after every rank has
+        // reached the recovery point.  The input must still be intact, so in-place calls are not retried.
+        const EnvConfig& env = GetEnvConfig();
+        const bool inputKept = p.op != HCCL_CMD_BROADCAST && sub.send != sub.recv;
+        HcclResult r = HCCL_SUCCESS;
+        for (uint32_t attempt = 0;; ++attempt) {
+            r = w.Enter(rank, hd, in, out, InBytes(sub, n), OutBytes(sub, n));
+            if (r == HCCL_SUCCESS) r = RunHostAlgorithm(w, rank, alg, sub);
+            HcclResult l = w.Leave(rank);
+            if (r == HCCL_SUCCESS) r = l;
+            if (r == HCCL_SUCCESS || !(r == HCCL_E_TIMEOUT || r == HCCL_E_REMOTE) || !(env.retryL1 || env.retryL2) || !inputKept) break;
+            if (attempt >= env.retryMaxCnt) { r = HCCL_E_OPRETRY_FAIL; break; }
+            HCCL_WARNING("host rank %u: %s failed (%s), retry %u of %u", rank, CmdName(p.op), ResultString(r), attempt + 1, env.retryMaxCnt);
+            const uint32_t pauseMs = attempt == 0 ? env.retryHoldMs : env.retryIntervalMs;
+            if (pauseMs) std::this_thread::sleep_for(std::chrono::milliseconds(pauseMs));
+            if (w.Recover(rank) != HCCL_SUCCESS) { r = HCCL_E_OPRETRY_FAIL; break; }
+        }
         if (r != HCCL_SUCCESS) { result = r; break; }
         if (!chunkable) break;
     }
@@ -348,6 +364,24 @@ void RegisterHostAlgorithms()
 using namespace hccl;
 
 extern "C" {
+
+HcclResult HcclTestHostDropPosts(HcclComm comm, uint32_t count)
+{
+    CHK_PTR_NULL(comm);
+    CommImpl* c = static_cast<CommImpl*>(comm);
+    if (!c->hostComm) return HCCL_E_NOT_SUPPORT;
+    c->hostComm->world->DropPosts(c->hostComm->rank, count);
+    return HCCL_SUCCESS;
+}
+
+HcclResult HcclTestHostRecoveries(HcclComm comm, uint64_t* count)
+{
+    CHK_PTR_NULL(comm); CHK_PTR_NULL(count);
+    CommImpl* c = static_cast<CommImpl*>(comm);
+    if (!c->hostComm) return HCCL_E_NOT_SUPPORT;
+    *count = c->hostComm->world->recoveries();
+    return HCCL_SUCCESS;
+}
 
 HcclResult HcclHostTraceBegin(HcclComm comm)
 {

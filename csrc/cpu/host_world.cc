@@ -117,8 +117,9 @@ void HostReduceBytes(void* dst, const void* src, uint64_t bytes, HcclDataType dt
 // ------------------------------------------------------------------ HostWorld
 HostWorld::HostWorld(uint32_t nRanks, const TopoMeta& meta, uint64_t scratchBytes, uint64_t timeoutNs)
     : n_(nRanks), scratchBytes_(scratchBytes), timeoutNs_(timeoutNs), posted_((size_t)nRanks * nRanks * kNotifyIdx),
-      consumed_((size_t)nRanks * nRanks * kNotifyIdx, 0)
+      consumed_((size_t)nRanks * nRanks * kNotifyIdx, 0), dropPosts_(nRanks)
 {
+    for (auto& d : dropPosts_) d.store(0);
     topo_.resize(n_);
     for (uint32_t r = 0; r < n_; ++r) BuildTopoFromMeta(meta, r, &topo_[r]);
     for (uint32_t r = 0; r < n_; ++r) scratch_.emplace_back(new char[scratchBytes_]);
@@ -160,6 +161,29 @@ HcclResult HostWorld::BarrierAll(uint32_t rank)
         --arrived_;
         lk.unlock();
         Abort("rank " + std::to_string(rank) + " waited " + std::to_string(timeoutNs_ / 1000000) + " ms for the other ranks to call the operator");
+        return HCCL_E_TIMEOUT;
+    }
+    return HCCL_SUCCESS;
+}
+
+HcclResult HostWorld::Recover(uint32_t rank)
+{
+    std::unique_lock<std::mutex> lk(mu_);
+    const uint64_t gen = recoverGen_;
+    if (++recoverArrived_ == n_) {
+        recoverArrived_ = 0;
+        arrived_ = 0;
+        aborted_.store(false);
+        abortWhy_.clear();
+        for (auto& a : posted_) a.store(0);
+        std::fill(consumed_.begin(), consumed_.end(), 0);
+        ++recoverGen_;
+        cv_.notify_all();
+        return HCCL_SUCCESS;
+    }
+    if (!cv_.wait_for(lk, std::chrono::nanoseconds(timeoutNs_), [&] { return recoverGen_ != gen; })) {
+        --recoverArrived_;
+        HCCL_ERROR("rank %u: the other ranks did not reach the retry point within %llu ms", rank, (unsigned long long)(timeoutNs_ / 1000000));
         return HCCL_E_TIMEOUT;
     }
     return HCCL_SUCCESS;
@@ -226,6 +250,9 @@ uint64_t HostWorld::BufBytes(uint32_t rank, BufKind k) const
 
 void HostWorld::Post(uint32_t from, uint32_t to, uint32_t idx)
 {
+    uint32_t left = dropPosts_[from].load();
+    while (left > 0)
+        if (dropPosts_[from].compare_exchange_weak(left, left - 1)) return;     // lost on the way
     posted_[((size_t)to * n_ + from) * kNotifyIdx + idx].fetch_add(1, std::memory_order_release);
 }
 bool HostWorld::Wait(uint32_t me, uint32_t from, uint32_t idx)

@@ -99,6 +99,13 @@ public:
     HcclResult BarrierAll(uint32_t rank);     // host-side rendezvous with timeout (a rank that never arrives -> TIMEOUT)
     void Abort(const std::string& why);
     bool aborted() const { return aborted_.load(); }
+    // Recovery point of the operator retry: every rank calls it after a failed attempt.  When the last rank arrives
+    // the abort state, the notify counters and the rendezvous are cleared so that the operator can be issued again
+    // from its inputs.  A rank that never arrives -> HCCL_E_TIMEOUT on the others (the retry has failed).
+    HcclResult Recover(uint32_t rank);
+    // Test hook: the next `count` notifies posted by `rank` are lost on the way (a dropped message).
+    void DropPosts(uint32_t rank, uint32_t count) { dropPosts_[rank].store(count); }
+    uint64_t recoveries() const { return recoverGen_; }
 
     char* Resolve(const Mem& m) const;
     uint64_t BufBytes(uint32_t rank, BufKind k) const;
@@ -138,6 +145,9 @@ private:
     std::condition_variable cv_;
     uint32_t arrived_ = 0;
     uint64_t generation_ = 0;
+    uint32_t recoverArrived_ = 0;
+    uint64_t recoverGen_ = 0;
+    std::vector<std::atomic<uint32_t>> dropPosts_;
     std::atomic<bool> aborted_{false};
     std::string abortWhy_;
     // notify counters: [to][from][idx] posted, and per-waiter consumed counts

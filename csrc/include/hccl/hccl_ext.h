@@ -45,6 +45,10 @@ HcclResult HcclHostTraceVerify(HcclComm comm, char* report, uint32_t capacity);
 HcclResult HcclTestLaunchUnsignalledWait(HcclComm comm, hcclStream_t stream);
 // Test hook: the next bootstrap exchange on this rank fails as if its connection dropped.
 HcclResult HcclTestInjectBootstrapFailure(HcclComm comm);
+// Host-engine communicators only: the next `count` notifies this rank posts are lost (a dropped message), which makes
+// the waiting peers time out; and how many times the world went through the operator-retry recovery point.
+HcclResult HcclTestHostDropPosts(HcclComm comm, uint32_t count);
+HcclResult HcclTestHostRecoveries(HcclComm comm, uint64_t* count);
 // Plan-cache statistics.
 HcclResult HcclGetPlanCacheStats(HcclComm comm, uint64_t* hits, uint64_t* misses, uint64_t* entries);
 // Overrides entries of the link model the cost model uses (GB/s and microseconds); negative = keep.

@@ -120,6 +120,8 @@ _sig("HcclHostTraceBegin", R, c_void_p)
 _sig("HcclHostTraceVerify", R, c_void_p, c_char_p, c_uint32)
 _sig("HcclTestLaunchUnsignalledWait", R, c_void_p, c_void_p)
 _sig("HcclTestInjectBootstrapFailure", R, c_void_p)
+_sig("HcclTestHostDropPosts", R, c_void_p, ctypes.c_uint32)
+_sig("HcclTestHostRecoveries", R, c_void_p, ctypes.POINTER(ctypes.c_uint64))
 _sig("HcclGetPlanCacheStats", R, c_void_p, POINTER(c_uint64), POINTER(c_uint64), POINTER(c_uint64))
 _sig("HcclSetLinkModel", R, c_double, c_double, c_double, c_double, c_double, c_double)
 _sig("HcclGetVersion", c_char_p)
