@@ -7,17 +7,24 @@
 // and AlltoAll / AlltoAllVC are lowered to the AlltoAllV form
 // (all_to_all_v.cc:62-73, :424-448); BatchSendRecv copies its item list
 // (batch_send_recv.cc:99-110).
+#include <algorithm>
 #include <cstring>
+#include <map>
+#include <cuda_runtime.h>
 #include "../core/log.h"
 #include "../ops/op_common.h"
 #include "../ops/param_check.h"
 #include "hccl/hccl.h"
+#include "hccl/hccl_graph_mode.h"
 
 using namespace hccl;
 
 namespace {
 
 CommImpl* C(HcclComm comm) { return static_cast<CommImpl*>(comm); }
+
+// Tag of the graph node that is being issued on this thread (graph-mode twins), else null.
+thread_local const char* g_graphTag = nullptr;
 
 HcclResult Finish(CommImpl* c, OpParam& p)
 {
@@ -30,7 +37,7 @@ void Fill(OpParam& p, HcclCMDType op, CommImpl* c, const void* send, void* recv,
           uint32_t root, hcclStream_t stream)
 {
     p.op = op;
-    p.tag = std::string(CmdName(op)) + "_" + c->name;
+    p.tag = g_graphTag ? std::string(g_graphTag) : std::string(CmdName(op)) + "_" + c->name;
     p.send = send;
     p.recv = recv;
     p.count = count;
@@ -336,5 +343,141 @@ HcclResult HcclBarrier(HcclComm comm, hcclStream_t stream)
     Fill(p, HCCL_CMD_BARRIER, C(comm), nullptr, nullptr, 0, HCCL_DATA_TYPE_INT8, HCCL_REDUCE_RESERVED, 0, stream);
     return Finish(C(comm), p);
 }
+
+// ---------------------------------------------------------------- graph-mode twins (hccl_graph_mode.h)
+namespace {
+thread_local std::map<std::string, CommImpl*> g_boundComms;
+
+HcclResult ResolveGroup(const char* group, CommImpl** out)
+{
+    CHK_PTR_NULL(group);
+    auto bound = g_boundComms.find(group);
+    const std::vector<CommImpl*> all = GroupFind(group);
+    if (bound != g_boundComms.end() && std::find(all.begin(), all.end(), bound->second) != all.end()) { *out = bound->second; return HCCL_SUCCESS; }
+    if (all.empty()) { HCCL_ERROR("no communicator named '%s' in this process", group); return HCCL_E_NOT_FOUND; }
+    if (all.size() == 1) { *out = all[0]; return HCCL_SUCCESS; }
+    // several ranks of the group live in this process: take the one on the current GPU if that settles it
+    int dev = -1;
+    CommImpl* onDev = nullptr;
+    int matches = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess)
+        for (CommImpl* c : all)
+            if (!c->hostComm && !c->emulated() && c->device == dev) { onDev = c; ++matches; }
+    (void)cudaGetLastError();
+    if (matches == 1) { *out = onDev; return HCCL_SUCCESS; }
+    HCCL_ERROR("group '%s' has %zu communicators in this process: bind one to the calling thread with HcclGroupBindThread", group, all.size());
+    return HCCL_E_PARA;
+}
+
+// A node's resource pack: nothing in it is needed, but a pack that cannot be right is reported.
+HcclResult CheckResPack(const HcclResPackGraphMode* res)
+{
+    if (!res) return HCCL_SUCCESS;
+    if (res->size != sizeof(HcclResPackGraphMode)) { HCCL_ERROR("HcclResPackGraphMode.size is %u, expected %zu", res->size, sizeof(HcclResPackGraphMode)); return HCCL_E_PARA; }
+    if ((res->scratchBytes && !res->scratch) || (res->slaveStreamNum && !res->slaveStreams)) return HCCL_E_PTR;
+    return HCCL_SUCCESS;
+}
+
+struct GraphNode {
+    CommImpl* comm = nullptr;
+    HcclResult Begin(const char* group, const char* tag, const HcclResPackGraphMode* res)
+    {
+        CHK_RET(ResolveGroup(group, &comm));
+        CHK_RET(CheckResPack(res));
+        g_graphTag = (tag && *tag) ? tag : nullptr;
+        return HCCL_SUCCESS;
+    }
+    ~GraphNode() { g_graphTag = nullptr; }
+};
+}  // namespace
+
+HcclResult HcclGroupGetComm(const char* group, HcclComm* comm)
+{
+    CHK_PTR_NULL(comm);
+    CommImpl* c = nullptr;
+    CHK_RET(ResolveGroup(group, &c));
+    *comm = c;
+    return HCCL_SUCCESS;
+}
+HcclResult HcclGroupBindThread(HcclComm comm)
+{
+    CHK_PTR_NULL(comm);
+    g_boundComms[C(comm)->name] = C(comm);
+    return HCCL_SUCCESS;
+}
+HcclResult HcclGroupUnbindThread(const char* group)
+{
+    CHK_PTR_NULL(group);
+    g_boundComms.erase(group);
+    return HCCL_SUCCESS;
+}
+HcclResult HcclCalcOpResGraphMode(const char* group, HcclCMDType op, uint64_t count, HcclDataType dataType, HcclReduceOp reduceOp, HcclOpResource* res)
+{
+    CommImpl* c = nullptr;
+    CHK_RET(ResolveGroup(group, &c));
+    return HcclCalcOpResource(c, op, count, dataType, reduceOp, 0, res);
+}
+
+#define GRAPH_NODE() GraphNode node; CHK_RET(node.Begin(group, tag, res))
+HcclResult HcclAllReduceGraphMode(void* sendBuf, void* recvBuf, uint64_t count, HcclDataType dataType, HcclReduceOp op, const char* group,
+                                  const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream)
+{
+    GRAPH_NODE();
+    return HcclAllReduce(sendBuf, recvBuf, count, dataType, op, node.comm, stream);
+}
+HcclResult HcclBroadcastGraphMode(void* buf, uint64_t count, HcclDataType dataType, uint32_t root, const char* group, const char* tag,
+                                  const HcclResPackGraphMode* res, hcclStream_t stream)
+{
+    GRAPH_NODE();
+    return HcclBroadcast(buf, count, dataType, root, node.comm, stream);
+}
+HcclResult HcclReduceScatterGraphMode(void* sendBuf, void* recvBuf, uint64_t recvCount, HcclDataType dataType, HcclReduceOp op, const char* group,
+                                      const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream)
+{
+    GRAPH_NODE();
+    return HcclReduceScatter(sendBuf, recvBuf, recvCount, dataType, op, node.comm, stream);
+}
+HcclResult HcclAllGatherGraphMode(void* sendBuf, void* recvBuf, uint64_t sendCount, HcclDataType dataType, const char* group, const char* tag,
+                                  const HcclResPackGraphMode* res, hcclStream_t stream)
+{
+    GRAPH_NODE();
+    return HcclAllGather(sendBuf, recvBuf, sendCount, dataType, node.comm, stream);
+}
+HcclResult HcclReduceGraphMode(void* sendBuf, void* recvBuf, uint64_t count, HcclDataType dataType, HcclReduceOp op, uint32_t root, const char* group,
+                               const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream)
+{
+    GRAPH_NODE();
+    return HcclReduce(sendBuf, recvBuf, count, dataType, op, root, node.comm, stream);
+}
+HcclResult HcclScatterGraphMode(void* sendBuf, void* recvBuf, uint64_t recvCount, HcclDataType dataType, uint32_t root, const char* group,
+                                const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream)
+{
+    GRAPH_NODE();
+    return HcclScatter(sendBuf, recvBuf, recvCount, dataType, root, node.comm, stream);
+}
+HcclResult HcclAlltoAllGraphMode(const void* sendBuf, uint64_t sendCount, HcclDataType sendType, const void* recvBuf, uint64_t recvCount,
+                                 HcclDataType recvType, const char* group, const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream)
+{
+    GRAPH_NODE();
+    return HcclAlltoAll(sendBuf, sendCount, sendType, recvBuf, recvCount, recvType, node.comm, stream);
+}
+HcclResult HcclSendGraphMode(void* sendBuf, uint64_t count, HcclDataType dataType, uint32_t destRank, const char* group, const char* tag,
+                             const HcclResPackGraphMode* res, hcclStream_t stream)
+{
+    GRAPH_NODE();
+    return HcclSend(sendBuf, count, dataType, destRank, node.comm, stream);
+}
+HcclResult HcclRecvGraphMode(void* recvBuf, uint64_t count, HcclDataType dataType, uint32_t srcRank, const char* group, const char* tag,
+                             const HcclResPackGraphMode* res, hcclStream_t stream)
+{
+    GRAPH_NODE();
+    return HcclRecv(recvBuf, count, dataType, srcRank, node.comm, stream);
+}
+HcclResult HcclBarrierGraphMode(const char* group, const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream)
+{
+    GRAPH_NODE();
+    return HcclBarrier(node.comm, stream);
+}
+#undef GRAPH_NODE
 
 }  // extern "C"

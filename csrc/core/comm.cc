@@ -1,4 +1,5 @@
 #include "comm.h"
+#include <algorithm>
 #include <chrono>
 #include <cstring>
 #include "../kernels/dev_types.h"
@@ -112,6 +113,7 @@ HcclResult CommImpl::Init(const HcclRootInfo& root, int nR, int r, const HcclCom
     char nm[HCCL_COMM_CONFIG_NAME_MAX];
     snprintf(nm, sizeof(nm), "hccl_comm_%016llx", (unsigned long long)bs->uniqueId());
     name = cfg.commName.empty() ? nm : cfg.commName;
+    GroupRegister(this);
     const size_t slabBytes = kSlabDataOff + cfg.bufferBytes;
     const bool wantMc = cfg.nvlsEnable != 0 && nRanks > 1;
     CHK_RET(SymAlloc(*bs, device, slabBytes, wantMc, env.forceIpc, &slab_));
@@ -144,16 +146,47 @@ HcclResult CommImpl::InitEmulated(EmuGroup* group, int nR, int r, const SymSegme
     char nm[HCCL_COMM_CONFIG_NAME_MAX];
     snprintf(nm, sizeof(nm), "hccl_emu_%p", (void*)group);
     name = cfg.commName.empty() ? nm : cfg.commName;
+    GroupRegister(this);
     CHK_RET(SetupDeviceState());
     topo.reset(new TopoInfo());
     CHK_RET(DiscoverTopo(this, topo.get()));
     return HCCL_SUCCESS;
 }
 
+namespace {
+std::mutex g_groupMu;
+std::vector<CommImpl*>& Groups()
+{
+    static std::vector<CommImpl*> v;
+    return v;
+}
+}  // namespace
+void GroupRegister(CommImpl* c)
+{
+    std::lock_guard<std::mutex> lk(g_groupMu);
+    auto& v = Groups();
+    if (std::find(v.begin(), v.end(), c) == v.end()) v.push_back(c);
+}
+void GroupUnregister(CommImpl* c)
+{
+    std::lock_guard<std::mutex> lk(g_groupMu);
+    auto& v = Groups();
+    v.erase(std::remove(v.begin(), v.end(), c), v.end());
+}
+std::vector<CommImpl*> GroupFind(const std::string& name)
+{
+    std::lock_guard<std::mutex> lk(g_groupMu);
+    std::vector<CommImpl*> out;
+    for (CommImpl* c : Groups())
+        if (c->name == name) out.push_back(c);
+    return out;
+}
+
 HcclResult CommImpl::Destroy()
 {
     if (status_.load() == HCCL_COMM_STATUS_DESTROYED) return HCCL_SUCCESS;
     status_.store(HCCL_COMM_STATUS_DESTROYED);
+    GroupUnregister(this);
     watchdogStop_.store(true);
     if (watchdog_.joinable()) watchdog_.join();
     if (hStatus_ || dEpochs_) cudaDeviceSynchronize();

@@ -128,6 +128,12 @@ public:
     std::atomic<uint64_t> stuckReports{0};
 };
 
+// Process-wide registry of communicators by name, for callers that know a group only by its name (graph mode).
+void GroupRegister(CommImpl* c);
+void GroupUnregister(CommImpl* c);
+// All live communicators named `name` in this process.
+std::vector<CommImpl*> GroupFind(const std::string& name);
+
 // Ranks that share one GPU inside one process.  Collects each rank's launch and
 // issues ONE cooperative kernel when the last rank has posted.
 class EmuGroup : public EmuLauncher {

@@ -102,6 +102,7 @@ HcclResult HostWorldCreate(uint32_t nRanks, const char* topoJson, const HcclComm
         char nm[64];
         snprintf(nm, sizeof(nm), "hccl_host_%p", (void*)world.get());
         c->name = eff.commName.empty() ? nm : eff.commName;
+        GroupRegister(c);
         c->hostComm = new HostRank(world, r);
         c->topo.reset(new TopoInfo(world->Topo(r)));
         c->selector.reset(new SelectorState());

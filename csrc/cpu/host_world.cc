@@ -191,6 +191,9 @@ HcclResult HostWorld::Recover(uint32_t rank)
 
 static bool SameCall(const HostOpDesc& a, const HostOpDesc& b)
 {
+    // Send, Recv and BatchSendRecv are one family: a Send on one rank meets a Recv on another
+    auto p2p = [](HcclCMDType op) { return op == HCCL_CMD_SEND || op == HCCL_CMD_RECEIVE || op == HCCL_CMD_BATCH_SEND_RECV; };
+    if (p2p(a.op) && p2p(b.op)) return true;
     if (a.op != b.op || a.dtype != b.dtype || a.redOp != b.redOp || a.root != b.root) return false;
     switch (a.op) {
         case HCCL_CMD_ALLTOALLV: case HCCL_CMD_SEND: case HCCL_CMD_RECEIVE: case HCCL_CMD_BATCH_SEND_RECV: return true;   // per-rank counts

@@ -1,0 +1,69 @@
+// Graph-mode twins of the operators.
+//
+// A graph builder does not hold communicator handles: it knows a communication
+// group by NAME, gives every operator node a TAG, and sizes the node's resources
+// (scratch, extra streams) before the graph runs.  The reference exposes that
+// as HcclAllReduceGraphMode etc. (all_reduce.cc:58) with a ResPackGraphMode
+// (alg_param.h:928-933) and the HcclCalcOpRes*GraphMode family
+// (interface_graph_mode/calc_resource_graph_mode.cc:51-633).
+//
+// Here every operator is one stream-ordered kernel on the caller's stream that
+// works in the communicator's own staging slab, so a node needs no scratch of
+// its own and no extra streams; a resource pack is accepted and checked, and the
+// query reports what a node will use.  The calls can be captured in a CUDA graph.
+//
+// A group name resolves to the communicator of that name in this process.  When
+// several ranks of the group live in one process (threads as ranks), each thread
+// first binds its communicator with HcclGroupBindThread.
+#ifndef HCCL_B200_GRAPH_MODE_H
+#define HCCL_B200_GRAPH_MODE_H
+#include "hccl.h"
+#include "hccl_ext.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct {
+    uint32_t size;                 // sizeof(HcclResPackGraphMode), for versioning
+    void* scratch;                 // optional: unused by this library's operators
+    uint64_t scratchBytes;
+    hcclStream_t* slaveStreams;    // optional: unused, operators stay on the caller's stream
+    uint32_t slaveStreamNum;
+} HcclResPackGraphMode;
+
+// Group lookup.  HcclGroupGetComm fails with HCCL_E_NOT_FOUND for an unknown name and with HCCL_E_PARA when the name
+// is ambiguous in this process and the calling thread has bound none of the candidates.
+HcclResult HcclGroupGetComm(const char* group, HcclComm* comm);
+HcclResult HcclGroupBindThread(HcclComm comm);
+HcclResult HcclGroupUnbindThread(const char* group);
+
+// What a node of this operator will use (the role of HcclCalcOpResOffline / ...GraphMode).
+HcclResult HcclCalcOpResGraphMode(const char* group, HcclCMDType op, uint64_t count, HcclDataType dataType, HcclReduceOp reduceOp,
+                                  HcclOpResource* res);
+
+HcclResult HcclAllReduceGraphMode(void* sendBuf, void* recvBuf, uint64_t count, HcclDataType dataType, HcclReduceOp op, const char* group,
+                                  const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream);
+HcclResult HcclBroadcastGraphMode(void* buf, uint64_t count, HcclDataType dataType, uint32_t root, const char* group, const char* tag,
+                                  const HcclResPackGraphMode* res, hcclStream_t stream);
+HcclResult HcclReduceScatterGraphMode(void* sendBuf, void* recvBuf, uint64_t recvCount, HcclDataType dataType, HcclReduceOp op,
+                                      const char* group, const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream);
+HcclResult HcclAllGatherGraphMode(void* sendBuf, void* recvBuf, uint64_t sendCount, HcclDataType dataType, const char* group,
+                                  const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream);
+HcclResult HcclReduceGraphMode(void* sendBuf, void* recvBuf, uint64_t count, HcclDataType dataType, HcclReduceOp op, uint32_t root,
+                               const char* group, const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream);
+HcclResult HcclScatterGraphMode(void* sendBuf, void* recvBuf, uint64_t recvCount, HcclDataType dataType, uint32_t root, const char* group,
+                                const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream);
+HcclResult HcclAlltoAllGraphMode(const void* sendBuf, uint64_t sendCount, HcclDataType sendType, const void* recvBuf, uint64_t recvCount,
+                                 HcclDataType recvType, const char* group, const char* tag, const HcclResPackGraphMode* res,
+                                 hcclStream_t stream);
+HcclResult HcclSendGraphMode(void* sendBuf, uint64_t count, HcclDataType dataType, uint32_t destRank, const char* group, const char* tag,
+                             const HcclResPackGraphMode* res, hcclStream_t stream);
+HcclResult HcclRecvGraphMode(void* recvBuf, uint64_t count, HcclDataType dataType, uint32_t srcRank, const char* group, const char* tag,
+                             const HcclResPackGraphMode* res, hcclStream_t stream);
+HcclResult HcclBarrierGraphMode(const char* group, const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

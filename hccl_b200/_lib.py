@@ -179,3 +179,26 @@ class HcclOpResource(ctypes.Structure):
 
 
 _sig("HcclCalcOpResource", R, c_void_p, c_int, c_uint64, c_int, c_int, c_int, POINTER(HcclOpResource))
+
+
+class HcclResPackGraphMode(ctypes.Structure):
+    _fields_ = [("size", c_uint32), ("scratch", c_void_p), ("scratchBytes", c_uint64), ("slaveStreams", POINTER(c_void_p)),
+                ("slaveStreamNum", c_uint32)]
+
+
+# graph-mode twins: the group is named, not passed as a handle (hccl_graph_mode.h)
+_RP = POINTER(HcclResPackGraphMode)
+_sig("HcclGroupGetComm", R, c_char_p, POINTER(c_void_p))
+_sig("HcclGroupBindThread", R, c_void_p)
+_sig("HcclGroupUnbindThread", R, c_char_p)
+_sig("HcclCalcOpResGraphMode", R, c_char_p, c_int, c_uint64, c_int, c_int, POINTER(HcclOpResource))
+_sig("HcclAllReduceGraphMode", R, c_void_p, c_void_p, c_uint64, c_int, c_int, c_char_p, c_char_p, _RP, c_void_p)
+_sig("HcclBroadcastGraphMode", R, c_void_p, c_uint64, c_int, c_uint32, c_char_p, c_char_p, _RP, c_void_p)
+_sig("HcclReduceScatterGraphMode", R, c_void_p, c_void_p, c_uint64, c_int, c_int, c_char_p, c_char_p, _RP, c_void_p)
+_sig("HcclAllGatherGraphMode", R, c_void_p, c_void_p, c_uint64, c_int, c_char_p, c_char_p, _RP, c_void_p)
+_sig("HcclReduceGraphMode", R, c_void_p, c_void_p, c_uint64, c_int, c_int, c_uint32, c_char_p, c_char_p, _RP, c_void_p)
+_sig("HcclScatterGraphMode", R, c_void_p, c_void_p, c_uint64, c_int, c_uint32, c_char_p, c_char_p, _RP, c_void_p)
+_sig("HcclAlltoAllGraphMode", R, c_void_p, c_uint64, c_int, c_void_p, c_uint64, c_int, c_char_p, c_char_p, _RP, c_void_p)
+_sig("HcclSendGraphMode", R, c_void_p, c_uint64, c_int, c_uint32, c_char_p, c_char_p, _RP, c_void_p)
+_sig("HcclRecvGraphMode", R, c_void_p, c_uint64, c_int, c_uint32, c_char_p, c_char_p, _RP, c_void_p)
+_sig("HcclBarrierGraphMode", R, c_char_p, c_char_p, _RP, c_void_p)

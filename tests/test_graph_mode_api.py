@@ -1,0 +1,97 @@
+"""Graph-mode twins: operators addressed by group NAME and node TAG, with a
+resource pack and a resource query, run here on host-engine communicators
+(ranks as threads, each thread bound to its communicator)."""
+import ctypes
+
+import numpy as np
+import pytest
+
+import hccl_b200 as hb
+from hccl_b200 import Communicator
+from hccl_b200._lib import HcclOpResource, HcclResPackGraphMode, lib
+from hccl_b200.types import Cmd, DataType, ReduceOp, Result
+
+from test_host_engine import run_ranks
+
+
+def ptr(a):
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def test_named_group_runs_every_twin():
+    n, count = 4, 513
+    comms = Communicator.host_sim(n, None, hb.make_config(buffer_mib=8, exec_timeout_ms=20000, name="tp_group"))
+    group = b"tp_group"
+    pack = HcclResPackGraphMode(ctypes.sizeof(HcclResPackGraphMode), None, 0, None, 0)
+    ar_in = [np.random.default_rng(r).standard_normal(count).astype(np.float32) for r in range(n)]
+    ar_out = [np.zeros(count, np.float32) for _ in range(n)]
+    rs_out = [np.zeros(count, np.float32) for _ in range(n)]
+    rs_in = [np.random.default_rng(9 + r).standard_normal(count * n).astype(np.float32) for r in range(n)]
+    ag_out = [np.zeros(count * n, np.float32) for _ in range(n)]
+    bc = [np.full(count, r, np.int32) for r in range(n)]
+    red_out = np.zeros(count, np.float32)
+    sc_src = np.arange(count * n, dtype=np.int32)
+    sc_out = [np.zeros(count, np.int32) for _ in range(n)]
+    a2a_in = [np.arange(count * n, dtype=np.int64) + 10 ** 6 * r for r in range(n)]
+    a2a_out = [np.zeros(count * n, np.int64) for _ in range(n)]
+    got = [np.zeros(5, np.int32) for _ in range(n)]
+
+    def body(r, c):
+        ok = lambda code: code == 0 or (_ for _ in ()).throw(AssertionError(Result(code)))  # noqa: E731
+        ok(lib.HcclGroupBindThread(c.handle))
+        h = ctypes.c_void_p()
+        ok(lib.HcclGroupGetComm(group, ctypes.byref(h)))
+        assert h.value == c.handle.value if hasattr(c.handle, "value") else h.value == c.handle
+        ok(lib.HcclAllReduceGraphMode(ptr(ar_in[r]), ptr(ar_out[r]), count, DataType.FP32, ReduceOp.SUM, group, b"node_ar_0", ctypes.byref(pack), None))
+        ok(lib.HcclReduceScatterGraphMode(ptr(rs_in[r]), ptr(rs_out[r]), count, DataType.FP32, ReduceOp.SUM, group, b"node_rs_0", None, None))
+        ok(lib.HcclAllGatherGraphMode(ptr(rs_out[r]), ptr(ag_out[r]), count, DataType.FP32, group, None, None, None))
+        ok(lib.HcclBroadcastGraphMode(ptr(bc[r]), count, DataType.INT32, 2, group, b"node_bc", None, None))
+        ok(lib.HcclReduceGraphMode(ptr(ar_in[r]), ptr(red_out) if r == 1 else ptr(ar_out[r]), count, DataType.FP32, ReduceOp.SUM, 1, group, b"node_red", None, None))
+        ok(lib.HcclScatterGraphMode(ptr(sc_src) if r == 0 else None, ptr(sc_out[r]), count, DataType.INT32, 0, group, b"node_sc", None, None))
+        ok(lib.HcclAlltoAllGraphMode(ptr(a2a_in[r]), count, DataType.INT64, ptr(a2a_out[r]), count, DataType.INT64, group, b"node_a2a", None, None))
+        send = np.full(5, r, np.int32)
+        if r % 2 == 0:
+            ok(lib.HcclSendGraphMode(ptr(send), 5, DataType.INT32, r + 1, group, b"node_p2p", None, None))
+        else:
+            ok(lib.HcclRecvGraphMode(ptr(got[r]), 5, DataType.INT32, r - 1, group, b"node_p2p", None, None))
+        ok(lib.HcclBarrierGraphMode(group, b"node_bar", None, None))
+        ok(lib.HcclGroupUnbindThread(group))
+
+    run_ranks(comms, body)
+    ref = np.sum(np.stack(ar_in).astype(np.float64), 0)
+    np.testing.assert_allclose(red_out, ref, rtol=2e-6, atol=2e-5)
+    rs_ref = np.sum(np.stack(rs_in).astype(np.float64), 0)
+    for r in range(n):
+        np.testing.assert_allclose(rs_out[r], rs_ref[r * count:(r + 1) * count], rtol=2e-6, atol=2e-5)
+        np.testing.assert_allclose(ag_out[r], rs_ref, rtol=2e-6, atol=2e-5)
+        assert np.all(bc[r] == 2)
+        assert np.array_equal(sc_out[r], sc_src[r * count:(r + 1) * count])
+        for q in range(n):
+            assert np.array_equal(a2a_out[r][q * count:(q + 1) * count], a2a_in[q][r * count:(r + 1) * count])
+        if r % 2:
+            assert np.all(got[r] == r - 1)
+    for c in comms:
+        c.destroy()
+
+
+def test_lookup_errors_resource_query_and_bad_pack():
+    h = ctypes.c_void_p()
+    assert lib.HcclGroupGetComm(b"no_such_group", ctypes.byref(h)) == Result.E_NOT_FOUND
+    comms = Communicator.host_sim(2, None, hb.make_config(buffer_mib=8, name="pair"))
+    # two ranks of the group in one process and no binding: ambiguous
+    assert lib.HcclGroupGetComm(b"pair", ctypes.byref(h)) == Result.E_PARA
+    assert lib.HcclGroupBindThread(comms[1].handle) == 0
+    assert lib.HcclGroupGetComm(b"pair", ctypes.byref(h)) == 0
+    res = HcclOpResource()
+    assert lib.HcclCalcOpResGraphMode(b"pair", Cmd.ALLREDUCE, 1 << 20, DataType.FP32, ReduceOp.SUM, ctypes.byref(res)) == 0
+    assert res.streams == 1 and res.algName.decode().startswith("HostAllReduce")
+    bad = HcclResPackGraphMode(4, None, 0, None, 0)
+    x = np.zeros(4, np.float32)
+    assert lib.HcclAllReduceGraphMode(ptr(x), ptr(x), 4, DataType.FP32, ReduceOp.SUM, b"pair", b"t", ctypes.byref(bad), None) == Result.E_PARA
+    missing = HcclResPackGraphMode(ctypes.sizeof(HcclResPackGraphMode), None, 64, None, 0)
+    assert lib.HcclAllReduceGraphMode(ptr(x), ptr(x), 4, DataType.FP32, ReduceOp.SUM, b"pair", b"t", ctypes.byref(missing), None) == Result.E_PTR
+    assert lib.HcclGroupUnbindThread(b"pair") == 0
+    for c in comms:
+        c.destroy()
+    # a destroyed communicator leaves the registry
+    assert lib.HcclGroupGetComm(b"pair", ctypes.byref(h)) == Result.E_NOT_FOUND
