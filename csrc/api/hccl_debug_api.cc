@@ -6,6 +6,7 @@
 #include "../core/config.h"
 #include "../core/log.h"
 #include "../cpu/host_tree.h"
+#include "../select/auto_selector.h"
 #include "../select/selector.h"
 #include "hccl/hccl_ext.h"
 
@@ -66,6 +67,14 @@ HcclResult HcclDebugStepTable(const char* kind, uint32_t p, uint32_t rank, const
         std::string err;
         if (!ParseAlgoTree(arg ? arg : "", &tree, &err)) os << "error: " << err << "\n";
         else os << AlgoTreeText(*tree) << " queues " << AlgoTreeQueues(*tree) << " levels " << AlgoTreeMinLevels(*tree) << "\n";
+    } else if (k == "threshold") {
+        // p = ranks, rank = topology levels, arg = "op,bytes,host,nvls,strict"
+        ThresholdInput in;
+        int op = 0, host = 0, nvls = 0, strict = 0;
+        unsigned long long bytes = 0;
+        if (!arg || sscanf(arg, "%d,%llu,%d,%d,%d", &op, &bytes, &host, &nvls, &strict) != 5) return HCCL_E_PARA;
+        in.op = (HcclCMDType)op; in.bytes = bytes; in.nRanks = p; in.levels = rank; in.hostEngine = host; in.nvls = nvls; in.strictOrder = strict;
+        os << ThresholdSelect(in) << "\n";
     } else if (k == "fold") {
         for (auto& pr : DeterministicFoldOrder(p)) os << pr.first << "+=" << pr.second << "\n";
     } else if (k == "parse_algo") {

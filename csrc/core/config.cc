@@ -268,6 +268,12 @@ EnvConfig ParseEnvConfig(const EnvGetter& get)
     val("HCCL_ALG_TUNER_PLUGIN", &c.tunerPlugin);
     val("HCCL_ALGO_PLUGIN_PATH", &c.algoPlugin);
     val("HCCL_ALGO_TREE", &c.algoTree);
+    if (val("HCCL_SELECTOR_MODE", &s)) {
+        const std::string m = Lower(Trim(s));
+        if (m == "threshold" || m == "legacy") c.thresholdSelector = true;
+        else if (m == "cost" || m.empty()) c.thresholdSelector = false;
+        else c.errors.push_back("HCCL_SELECTOR_MODE: expected cost|threshold");
+    }
     if (val("HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO", &s)) {
         for (const std::string& f : Split(s, ',')) {
             char* end = nullptr;

@@ -66,6 +66,7 @@ struct EnvConfig {
     std::string tunerPlugin;                          // HCCL_ALG_TUNER_PLUGIN
     std::string algoPlugin;                           // HCCL_ALGO_PLUGIN_PATH
     std::vector<double> splitRatio;                   // HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO
+    bool thresholdSelector = false;                   // HCCL_SELECTOR_MODE=threshold: decision trees instead of the cost model
     std::string algoTree;                             // HCCL_ALGO_TREE: executor tree for the tree-interpreting executor
     // B200-specific knobs
     int nvlsEnable = -1;                              // HCCL_NVLS_ENABLE: -1 auto, 0 off, 1 on

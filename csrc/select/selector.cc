@@ -1,4 +1,5 @@
 #include "selector.h"
+#include "auto_selector.h"
 #include <algorithm>
 #include <chrono>
 #include <cmath>
@@ -292,7 +293,7 @@ std::string FormatCostTable(const Selection& s)
     const auto& all = AlgRegistry::Instance().All();
     for (const CostRow& r : s.table) {
         os << "  " << all[(size_t)r.algIndex].name << ": ";
-        if (r.viable) os << r.cost << " us" << (r.preferred ? " [HCCL_ALGO]" : "") << (r.tunerTouched ? " [tuner]" : "");
+        if (r.viable) os << r.cost << " us" << (r.byThreshold ? " [threshold]" : r.preferred ? " [HCCL_ALGO]" : "") << (r.tunerTouched ? " [tuner]" : "");
         else os << "filtered (" << r.reason << ")";
         if (r.algIndex == s.algIndex) os << "  <= selected";
         os << "\n";
@@ -325,6 +326,15 @@ HcclResult SelectAlgorithm(SelectorState& st, const TopoInfo& topo, const EnvCon
     bool anyPref = false;
     for (CostRow& r : out->table)
         if (r.viable && MatchesPreference(all[(size_t)r.algIndex], pref)) { r.preferred = true; anyPref = true; }
+    // Phase 2b: the threshold tree names one algorithm (HCCL_SELECTOR_MODE=threshold, and always for calls made on
+    // behalf of fused matmul kernels, as the reference does for MC2, op_common.cc:225-230).  HCCL_ALGO still wins.
+    if (!anyPref && (env.thresholdSelector || op.isMc2)) {
+        const std::string name = ThresholdSelect(ThresholdInputOf(topo, op));
+        for (CostRow& r : out->table)
+            if (r.viable && all[(size_t)r.algIndex].name == name) { r.preferred = r.byThreshold = true; anyPref = true; }
+        if (!name.empty() && !anyPref)
+            HCCL_INFO("threshold tree names %s, which cannot run this call: cost model decides", name.c_str());
+    }
     if (pref.specified && !anyPref)
         HCCL_WARNING("HCCL_ALGO names no algorithm that can run this %d-rank op (%llu bytes): automatic selection", op.nRanks, (unsigned long long)op.bytes);
     // Phase 3: tuner

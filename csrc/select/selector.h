@@ -148,6 +148,7 @@ struct CostRow {
     bool viable = false;
     bool preferred = false; // matches HCCL_ALGO
     bool tunerTouched = false;
+    bool byThreshold = false; // named by the threshold tree
     std::string reason;     // why it was filtered, empty if viable
 };
 

@@ -308,3 +308,60 @@ def test_algo_plugin_takes_over_claimed_operator(tmp_path):
     finally:
         os.environ.pop("HCCL_ALGO_PLUGIN_PATH", None)
         lib.HcclReloadEnvConfig()
+
+
+def _threshold(op, nbytes, ranks=8, levels=1, host=0, nvls=0, strict=0):
+    buf = ctypes.create_string_buffer(256)
+    assert lib.HcclDebugStepTable(b"threshold", ranks, levels, f"{int(op)},{nbytes},{host},{nvls},{strict}".encode(), buf, 256) == 0
+    return buf.value.decode().strip()
+
+
+def test_threshold_trees_cut_where_documented():
+    K, M = 1024, 1 << 20
+    # device engines: flag-in-data form, one-shot, then switch reduction or the two-shot peer form
+    assert _threshold(Cmd.ALLREDUCE, 64 * K) == "P2pAllReduceSoleMeshLL"
+    assert _threshold(Cmd.ALLREDUCE, 64 * K + 1) == "P2pAllReduceSoleMeshOneShot"
+    assert _threshold(Cmd.ALLREDUCE, 16 * M, nvls=1) == "NvlsAllReduceSoleMesh"
+    assert _threshold(Cmd.ALLREDUCE, 16 * M, nvls=1, strict=1) == "P2pAllReduceSoleMeshTwoShot"     # fixed order: no switch reduction
+    assert _threshold(Cmd.ALLREDUCE, 16 * M) == "P2pAllReduceSoleMeshTwoShot"
+    assert _threshold(Cmd.BROADCAST, 8 * M, nvls=1) == "NvlsBroadcastSoleMesh"
+    assert _threshold(Cmd.ALLTOALL, 1 * M) == "P2pAlltoAllSoleMeshLL"
+    # host engine: the reference's cut points (one-shot to 16 KiB, mesh to 512 KiB, halving-doubling for powers of two)
+    assert _threshold(Cmd.ALLREDUCE, 16 * K, host=1) == "HostAllReduceSoleMeshOneShot"
+    assert _threshold(Cmd.ALLREDUCE, 512 * K, host=1) == "HostAllReduceSoleMeshTwoShot"
+    assert _threshold(Cmd.ALLREDUCE, 4 * M, host=1) == "HostAllReduceSoleRHD"
+    assert _threshold(Cmd.ALLREDUCE, 4 * M, ranks=6, host=1) == "HostAllReduceSoleNHR"
+    assert _threshold(Cmd.ALLREDUCE, 64 * M, host=1) == "HostAllReduceSoleRing"
+    assert _threshold(Cmd.ALLREDUCE, 4 * M, levels=2, host=1) == "HostAllReduceSequenceMeshNHR"
+    assert _threshold(Cmd.ALLREDUCE, 64 * M, levels=2, host=1) == "HostAllReduceParallelMeshNHR"
+    assert _threshold(Cmd.ALLREDUCE, 4 * M, levels=3, host=1) == "HostAllReduceSequenceMeshNHRNHR"
+    assert _threshold(Cmd.ALLTOALL, 64 * M, ranks=16, host=1) == "HostAlltoAllSolePairwise"
+    assert _threshold(Cmd.ALLTOALL, 64 * M, ranks=12, host=1) == "HostAlltoAllSoleMesh"
+    assert _threshold(Cmd.ALLTOALLV, 1 * M, levels=2, host=1) == "HostAlltoAllVHierMeshMesh"
+    assert _threshold(Cmd.SCATTER, 1 * M, ranks=16, host=1) == "HostScatterSoleNB"
+
+
+def test_threshold_mode_drives_the_selection_and_hccl_algo_still_wins():
+    try:
+        os.environ["HCCL_SELECTOR_MODE"] = "threshold"
+        os.environ.pop("HCCL_ALGO", None)
+        lib.HcclReloadEnvConfig()
+        comms = Communicator.host_sim(6)
+        txt = comms[0].explain(Cmd.ALLREDUCE, 1 << 20, DataType.FP32)          # 4 MiB, six ranks: NHR
+        assert txt.startswith("selected HostAllReduceSoleNHR") and "[threshold]" in txt, txt
+        txt = comms[0].explain(Cmd.ALLREDUCE, 1024, DataType.FP32)
+        assert txt.startswith("selected HostAllReduceSoleMeshOneShot"), txt
+        os.environ["HCCL_ALGO"] = "level0:NA;level1:ring"
+        lib.HcclReloadEnvConfig()
+        txt = comms[0].explain(Cmd.ALLREDUCE, 1 << 20, DataType.FP32)
+        assert txt.startswith("selected HostAllReduceSoleRing") and "[threshold]" not in txt, txt
+        for c in comms:
+            c.destroy()
+        os.environ["HCCL_SELECTOR_MODE"] = "nonsense"
+        buf = ctypes.create_string_buffer(4096)
+        assert lib.HcclDebugParseEnv(b"HCCL_SELECTOR_MODE=nonsense", buf, 4096) == 0
+        assert "HCCL_SELECTOR_MODE" in buf.value.decode()
+    finally:
+        os.environ.pop("HCCL_SELECTOR_MODE", None)
+        os.environ.pop("HCCL_ALGO", None)
+        lib.HcclReloadEnvConfig()
