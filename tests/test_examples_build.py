@@ -1,0 +1,40 @@
+"""Every example compiles and links against the built library (nvcc
+cross-compiles for sm_100a without a GPU)."""
+import shutil
+import subprocess
+from pathlib import Path
+
+import pytest
+
+import hccl_b200  # noqa: F401  (builds the library when it is missing)
+
+ROOT = Path(__file__).resolve().parent.parent
+INC = ROOT / "csrc" / "include"
+LIBDIR = ROOT / "hccl_b200" / "lib"
+NVCC = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+
+PROGRAMS = sorted(p for p in (ROOT / "examples").rglob("*") if p.suffix in (".cc", ".cu") and "plugin" not in p.name and "tuner" not in p.name)
+PLUGINS = sorted(p for p in (ROOT / "examples").rglob("*") if p.suffix in (".cc", ".cu") and ("plugin" in p.name or "tuner" in p.name))
+
+
+@pytest.mark.skipif(not Path(NVCC).exists(), reason="nvcc not found")
+@pytest.mark.parametrize("src", PROGRAMS, ids=lambda p: p.name)
+def test_example_program_builds(src, tmp_path):
+    out = tmp_path / src.stem
+    cmd = [NVCC, "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", f"-I{INC}", str(src), f"-L{LIBDIR}", "-lhccl_b200",
+           "-Xcompiler", "-pthread", "-o", str(out)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert out.exists()
+
+
+@pytest.mark.skipif(not Path(NVCC).exists(), reason="nvcc not found")
+@pytest.mark.parametrize("src", PLUGINS, ids=lambda p: p.name)
+def test_example_plugin_builds_and_exports_its_entry(src, tmp_path):
+    out = tmp_path / f"lib{src.stem}.so"
+    cmd = [NVCC, "-shared", "-Xcompiler", "-fPIC", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", f"-I{INC}", str(src),
+           f"-L{LIBDIR}", "-lhccl_b200", "-o", str(out)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    syms = subprocess.run(["nm", "-D", "--defined-only", str(out)], capture_output=True, text=True).stdout
+    assert "GetHcclAlgoPlugin" in syms or "HcclTunerPluginOpsGet" in syms, syms[-500:]
