@@ -74,7 +74,13 @@ def main():
     cfg.n_layers = args.layers if not args.tiny else cfg.n_layers
     torch.manual_seed(1234 + rank)
     model = LlamaStack(cfg, ctx)
-    opt = torch.optim.AdamW(model.parameters(), lr=1e-5, fused=True, capturable=True)
+    if args.impl == "hccl":
+        from hccl_b200.ops import FusedAdamW
+        opt = FusedAdamW(model.parameters(), lr=1e-5)                  # this library's single-launch AdamW kernel (same update rule)
+        opt_note = "AdamW(hccl_b200 FusedAdamW kernel)"
+    else:
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-5, fused=True, capturable=True)
+        opt_note = "AdamW(torch fused)"
     seq = args.seq
 
     # synthetic token ids, uniform over the vocabulary, one fresh pinned host batch per step
@@ -182,7 +188,7 @@ def main():
             "impl": args.impl,
             "config": {"model": "llama3-70b-shaped decoder stack" + (" (tiny smoke variant)" if args.tiny else ""), "layers": cfg.n_layers,
                        "hidden": cfg.hidden, "ffn": cfg.ffn, "heads": cfg.n_heads, "kv_heads": cfg.n_kv_heads, "global_batch": 1, "seq_len": seq,
-                       "parallelism": f"tp{world}+sp", "optimizer": "AdamW(fused)", "loss": "mean product of neighbouring features of the final hidden states",
+                       "parallelism": f"tp{world}+sp", "optimizer": opt_note, "loss": "mean product of neighbouring features of the final hidden states",
                        "l2": "inputs larger than L2: >13 GB of weights stream through per step", "cuda_graph": graph_note},
             "clocks": clocks.summary(),
             "e2e": {"value": tokens / (e2e_ms / 1000.0), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": seq * 8, "d2h_bytes_per_step": 4,

@@ -97,6 +97,17 @@ HcclResult HcclDebugStepTable(const char* kind, uint32_t p, uint32_t rank, const
     return HCCL_SUCCESS;
 }
 
+HcclResult HcclDiagnoseDump(char* text, uint32_t capacity)
+{
+    CHK_PTR_NULL(text);
+    if (capacity == 0) return HCCL_E_PARA;
+    const std::string all = DiagnoseDump();
+    // keep the newest lines when the buffer is short
+    const size_t skip = all.size() + 1 > capacity ? all.size() + 1 - capacity : 0;
+    snprintf(text, capacity, "%s", all.c_str() + skip);
+    return HCCL_SUCCESS;
+}
+
 HcclResult HcclDebugParseEnv(const char* settings, char* text, uint32_t cap)
 {
     CHK_PTR_NULL(settings); CHK_PTR_NULL(text);

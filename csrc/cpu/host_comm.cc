@@ -239,8 +239,10 @@ void Reg(const HostAlgSpec& s)
         return std::vector<CostCoeff>{c};
     };
     if (std::string(s.executor) == "concurrent") {
-        // two link sets side by side: the slower part decides (CostAggMode::MAX, executor_v2_base.h:130-141)
-        e.agg = CostAgg::MAX;
+        // Two link sets side by side: the slower part decides (CostAggMode::MAX, executor_v2_base.h:130-141).  Host
+        // memory is ONE link class, so the two parts share it and their times add up; MAX is for a topology whose
+        // parts really run on separate links.
+        e.agg = CostAgg::SUM;
         e.costCoeff = [steps, traffic](const TopoInfo& t, const OpDesc&) {
             const LinkModel& lm = GlobalLinkModel();
             const double p = (double)t.nRanks;
@@ -282,25 +284,29 @@ void RegisterHostAlgorithms()
     auto full = [](double p) { return p - 1; };
     auto one = [](double) { return 1.0; };
     // AllReduce
+    // Last field: the order in which an element's contributions are folded is fixed and does not depend on the message
+    // size or on the element's position (HCCL_DETERMINISTIC=strict admits only those).  Every host algorithm is
+    // run-to-run deterministic; ring / NHR / RHD / two-shot / hierarchical forms fold in an order that depends on the
+    // slice an element falls into.
     Reg({"HostAllReduceSoleMeshOneShot", HCCL_CMD_ALLREDUCE, HALG_AR_MESH_ONESHOT, "sole", {"MeshOneShot"}, AlgoType::ONESHOT, 1, true, Two, full, true});
-    Reg({"HostAllReduceSoleMeshTwoShot", HCCL_CMD_ALLREDUCE, HALG_AR_MESH_TWOSHOT, "sole", {"MeshTwoShot"}, AlgoType::MESH, 1, true, Three, ar, true});
-    Reg({"HostAllReduceSoleRing", HCCL_CMD_ALLREDUCE, HALG_AR_RING, "sole", {"Ring"}, AlgoType::RING, 1, true, TwoP1, ar, true});
-    Reg({"HostAllReduceSoleRHD", HCCL_CMD_ALLREDUCE, HALG_AR_RHD, "sole", {"RHD"}, AlgoType::HD_R, 1, true, TwoL, ar, true});
-    Reg({"HostAllReduceSoleNHR", HCCL_CMD_ALLREDUCE, HALG_AR_NHR, "sole", {"NHR"}, AlgoType::NHR, 1, true, TwoL, ar, true});
+    Reg({"HostAllReduceSoleMeshTwoShot", HCCL_CMD_ALLREDUCE, HALG_AR_MESH_TWOSHOT, "sole", {"MeshTwoShot"}, AlgoType::MESH, 1, true, Three, ar, false});
+    Reg({"HostAllReduceSoleRing", HCCL_CMD_ALLREDUCE, HALG_AR_RING, "sole", {"Ring"}, AlgoType::RING, 1, true, TwoP1, ar, false});
+    Reg({"HostAllReduceSoleRHD", HCCL_CMD_ALLREDUCE, HALG_AR_RHD, "sole", {"RHD"}, AlgoType::HD_R, 1, true, TwoL, ar, false});
+    Reg({"HostAllReduceSoleNHR", HCCL_CMD_ALLREDUCE, HALG_AR_NHR, "sole", {"NHR"}, AlgoType::NHR, 1, true, TwoL, ar, false});
     Reg({"HostAllReduceStrictOrderedMesh", HCCL_CMD_ALLREDUCE, HALG_AR_ORDER_PRESERVED, "orderpreserved", {"OrderPreservedGroup"}, AlgoType::AHC, 1, true, Three, full, true});
-    Reg({"HostAllReduceSequenceMeshRing", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_MESH_RING, "sequence", {"Mesh", "Ring"}, AlgoType::RING, 2, true, TwoP1, ar, true});
-    Reg({"HostAllReduceSequenceMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_MESH_NHR, "sequence", {"Mesh", "NHR"}, AlgoType::NHR, 2, true, TwoL, ar, true});
-    Reg({"HostAllReduceSequenceMeshRHD", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_MESH_RHD, "sequence", {"Mesh", "RHD"}, AlgoType::HD_R, 2, true, TwoL, ar, true});
-    Reg({"HostAllReduceSequenceMeshNHRNHR", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ3_MESH_NHR_NHR, "sequence", {"Mesh", "NHR", "NHR"}, AlgoType::NHR, 3, true, TwoL, ar, true});
-    Reg({"HostAllReduceParallelMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_PARALLEL_MESH_NHR, "parallel", {"Mesh", "NHR"}, AlgoType::PIPELINE, 2, true, TwoL, ar, true});
+    Reg({"HostAllReduceSequenceMeshRing", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_MESH_RING, "sequence", {"Mesh", "Ring"}, AlgoType::RING, 2, true, TwoP1, ar, false});
+    Reg({"HostAllReduceSequenceMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_MESH_NHR, "sequence", {"Mesh", "NHR"}, AlgoType::NHR, 2, true, TwoL, ar, false});
+    Reg({"HostAllReduceSequenceMeshRHD", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_MESH_RHD, "sequence", {"Mesh", "RHD"}, AlgoType::HD_R, 2, true, TwoL, ar, false});
+    Reg({"HostAllReduceSequenceMeshNHRNHR", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ3_MESH_NHR_NHR, "sequence", {"Mesh", "NHR", "NHR"}, AlgoType::NHR, 3, true, TwoL, ar, false});
+    Reg({"HostAllReduceParallelMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_PARALLEL_MESH_NHR, "parallel", {"Mesh", "NHR"}, AlgoType::PIPELINE, 2, true, TwoL, ar, false});
     // ReduceScatter (+V)
-    Reg({"HostReduceScatterSoleMesh", HCCL_CMD_REDUCE_SCATTER, HALG_RS_MESH, "sole", {"Mesh"}, AlgoType::MESH, 1, true, Two, rs, true});
-    Reg({"HostReduceScatterSoleRing", HCCL_CMD_REDUCE_SCATTER, HALG_RS_RING, "sole", {"Ring"}, AlgoType::RING, 1, true, P1, rs, true});
-    Reg({"HostReduceScatterSoleRHD", HCCL_CMD_REDUCE_SCATTER, HALG_RS_RHD, "sole", {"RHD"}, AlgoType::HD_R, 1, true, L, rs, true});
-    Reg({"HostReduceScatterSoleNHR", HCCL_CMD_REDUCE_SCATTER, HALG_RS_NHR, "sole", {"NHR"}, AlgoType::NHR, 1, true, L, rs, true});
+    Reg({"HostReduceScatterSoleMesh", HCCL_CMD_REDUCE_SCATTER, HALG_RS_MESH, "sole", {"Mesh"}, AlgoType::MESH, 1, true, Two, rs, false});
+    Reg({"HostReduceScatterSoleRing", HCCL_CMD_REDUCE_SCATTER, HALG_RS_RING, "sole", {"Ring"}, AlgoType::RING, 1, true, P1, rs, false});
+    Reg({"HostReduceScatterSoleRHD", HCCL_CMD_REDUCE_SCATTER, HALG_RS_RHD, "sole", {"RHD"}, AlgoType::HD_R, 1, true, L, rs, false});
+    Reg({"HostReduceScatterSoleNHR", HCCL_CMD_REDUCE_SCATTER, HALG_RS_NHR, "sole", {"NHR"}, AlgoType::NHR, 1, true, L, rs, false});
     Reg({"HostReduceScatterStrictOrderedMesh", HCCL_CMD_REDUCE_SCATTER, HALG_RS_ORDER_PRESERVED, "orderpreserved", {"OrderPreservedGroup"}, AlgoType::AHC, 1, true, Three, full, true});
-    Reg({"HostReduceScatterSequenceMeshNHR", HCCL_CMD_REDUCE_SCATTER, HALG_RS_SEQ_MESH_NHR, "sequence", {"NHR", "Mesh"}, AlgoType::NHR, 2, true, L, rs, true});
-    Reg({"HostReduceScatterVSoleMesh", HCCL_CMD_REDUCE_SCATTER_V, HALG_RS_MESH, "sole", {"Mesh"}, AlgoType::MESH, 1, true, Two, rs, true});
+    Reg({"HostReduceScatterSequenceMeshNHR", HCCL_CMD_REDUCE_SCATTER, HALG_RS_SEQ_MESH_NHR, "sequence", {"NHR", "Mesh"}, AlgoType::NHR, 2, true, L, rs, false});
+    Reg({"HostReduceScatterVSoleMesh", HCCL_CMD_REDUCE_SCATTER_V, HALG_RS_MESH, "sole", {"Mesh"}, AlgoType::MESH, 1, true, Two, rs, false});
     // AllGather (+V)
     Reg({"HostAllGatherSoleMesh", HCCL_CMD_ALLGATHER, HALG_AG_MESH, "sole", {"Mesh"}, AlgoType::MESH, 1, false, Two, rs, true});
     Reg({"HostAllGatherSoleRing", HCCL_CMD_ALLGATHER, HALG_AG_RING, "sole", {"Ring"}, AlgoType::RING, 1, false, P1, rs, true});
@@ -313,8 +319,8 @@ void RegisterHostAlgorithms()
     Reg({"HostBroadcastSoleMeshTwoShot", HCCL_CMD_BROADCAST, HALG_BCAST_MESH_TWOSHOT, "sole", {"MeshTwoShot"}, AlgoType::MESH, 1, false, Three, ar, true});
     Reg({"HostBroadcastSoleNHR", HCCL_CMD_BROADCAST, HALG_BCAST_NHR, "sole", {"NHR"}, AlgoType::NHR, 1, false, L, ar, true});
     Reg({"HostReduceSoleMeshOneShot", HCCL_CMD_REDUCE, HALG_REDUCE_MESH_ONESHOT, "sole", {"MeshOneShot"}, AlgoType::ONESHOT, 1, true, Two, full, true});
-    Reg({"HostReduceSoleMeshTwoShot", HCCL_CMD_REDUCE, HALG_REDUCE_MESH_TWOSHOT, "sole", {"MeshTwoShot"}, AlgoType::MESH, 1, true, Three, ar, true});
-    Reg({"HostReduceSoleNHR", HCCL_CMD_REDUCE, HALG_REDUCE_NHR, "sole", {"NHR"}, AlgoType::NHR, 1, true, L, ar, true});
+    Reg({"HostReduceSoleMeshTwoShot", HCCL_CMD_REDUCE, HALG_REDUCE_MESH_TWOSHOT, "sole", {"MeshTwoShot"}, AlgoType::MESH, 1, true, Three, ar, false});
+    Reg({"HostReduceSoleNHR", HCCL_CMD_REDUCE, HALG_REDUCE_NHR, "sole", {"NHR"}, AlgoType::NHR, 1, true, L, ar, false});
     Reg({"HostScatterSoleMesh", HCCL_CMD_SCATTER, HALG_SCATTER_MESH, "sole", {"Mesh"}, AlgoType::MESH, 1, false, Two, rs, true});
     Reg({"HostScatterSoleRing", HCCL_CMD_SCATTER, HALG_SCATTER_RING, "sole", {"Ring"}, AlgoType::RING, 1, false, P1, one, true});
     // AlltoAll family
@@ -331,21 +337,21 @@ void RegisterHostAlgorithms()
     auto TwoL1 = [](double p) { return 2 * Log2Ceil(p) + 1; };
     auto L1 = [](double p) { return Log2Ceil(p) + 1; };
     auto Four = [](double) { return 4.0; };
-    Reg({"HostAllReduceConcurrentMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, true, TwoL, ar, true});
-    Reg({"HostReduceScatterConcurrentMeshNHR", HCCL_CMD_REDUCE_SCATTER, HALG_RS_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, true, L, rs, true});
+    Reg({"HostAllReduceConcurrentMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, true, TwoL, ar, false});
+    Reg({"HostReduceScatterConcurrentMeshNHR", HCCL_CMD_REDUCE_SCATTER, HALG_RS_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, true, L, rs, false});
     Reg({"HostAllGatherConcurrentMeshNHR", HCCL_CMD_ALLGATHER, HALG_AG_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, false, L, rs, true});
-    Reg({"HostAllReducePipelineMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_PIPELINE_MESH_NHR, "pipeline", {"Mesh", "NHR"}, AlgoType::OMNIPIPE, 2, true, TwoL1, ar, true});
+    Reg({"HostAllReducePipelineMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_PIPELINE_MESH_NHR, "pipeline", {"Mesh", "NHR"}, AlgoType::OMNIPIPE, 2, true, TwoL1, ar, false});
     Reg({"HostAllGatherPipelineMeshMesh", HCCL_CMD_ALLGATHER, HALG_AG_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, false, Four, rs, true});
-    Reg({"HostReduceScatterPipelineMeshMesh", HCCL_CMD_REDUCE_SCATTER, HALG_RS_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, true, Four, rs, true});
+    Reg({"HostReduceScatterPipelineMeshMesh", HCCL_CMD_REDUCE_SCATTER, HALG_RS_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, true, Four, rs, false});
     Reg({"HostBroadcastPipelineMeshMesh", HCCL_CMD_BROADCAST, HALG_BCAST_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, false, Four, ar, true});
     Reg({"HostAllGatherSoleNB", HCCL_CMD_ALLGATHER, HALG_AG_NB, "sole", {"NB"}, AlgoType::NB, 1, false, L1, rs, true});
     Reg({"HostBroadcastSoleNB", HCCL_CMD_BROADCAST, HALG_BCAST_NB, "sole", {"NB"}, AlgoType::NB, 1, false, L1, ar, true});
     Reg({"HostScatterSoleNB", HCCL_CMD_SCATTER, HALG_SCATTER_NB, "sole", {"NB"}, AlgoType::NB, 1, false, L1, one, true});
     Reg({"HostBroadcastSequenceMeshNHR", HCCL_CMD_BROADCAST, HALG_BCAST_SEQ_MESH_NHR, "sequence", {"Mesh", "NHR"}, AlgoType::NHR, 2, false, TwoL1, ar, true});
-    Reg({"HostReduceSequenceMeshNHR", HCCL_CMD_REDUCE, HALG_REDUCE_SEQ_MESH_NHR, "sequence", {"Mesh", "NHR"}, AlgoType::NHR, 2, true, TwoL1, ar, true});
+    Reg({"HostReduceSequenceMeshNHR", HCCL_CMD_REDUCE, HALG_REDUCE_SEQ_MESH_NHR, "sequence", {"Mesh", "NHR"}, AlgoType::NHR, 2, true, TwoL1, ar, false});
     Reg({"HostScatterSequenceMeshMesh", HCCL_CMD_SCATTER, HALG_SCATTER_SEQ_MESH_MESH, "sequence", {"Mesh", "Mesh"}, AlgoType::HIER, 2, false, Four, rs, true});
     Reg({"HostBarrierSequenceMeshNHR", HCCL_CMD_BARRIER, HALG_BARRIER_SEQ_MESH_NHR, "sequence", {"Mesh", "NHR"}, AlgoType::HIER, 2, false, TwoL1, [](double) { return 0.0; }, true});
-    Reg({"HostAllReduceTree", HCCL_CMD_ALLREDUCE, HALG_AR_TREE, "tree", {"Tree"}, AlgoType::TREE, 1, true, TwoL1, ar, true});
+    Reg({"HostAllReduceTree", HCCL_CMD_ALLREDUCE, HALG_AR_TREE, "tree", {"Tree"}, AlgoType::TREE, 1, true, TwoL1, ar, false});
     for (HcclCMDType op : {HCCL_CMD_ALLTOALL, HCCL_CMD_ALLTOALLV, HCCL_CMD_ALLTOALLVC}) {
         static std::vector<std::string> keepHier;
         keepHier.push_back(std::string(op == HCCL_CMD_ALLTOALL ? "HostAlltoAll" : op == HCCL_CMD_ALLTOALLV ? "HostAlltoAllV" : "HostAlltoAllVC") + "HierMeshMesh");

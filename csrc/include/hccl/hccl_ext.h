@@ -69,6 +69,10 @@ typedef struct {
 HcclResult HcclCalcOpResource(HcclComm comm, HcclCMDType op, uint64_t count, HcclDataType dataType, HcclReduceOp reduceOp, int registered,
                               HcclOpResource* res);
 
+// Post-mortem record of the last operator entries of this process (kept when HCCL_DIAGNOSE_ENABLE=1, 2000 lines, oldest
+// first), the counterpart of HCCL's diagnose ring.  Writes at most `capacity` bytes including the terminator.
+HcclResult HcclDiagnoseDump(char* text, uint32_t capacity);
+
 // Unit-test access to pure functions.  Each writes a text rendering into `text`.
 //   kind "nhr_rs" / "nhr_ag" / "rhd_rs" / "rhd_ag" / "ring_rs" / "ring_ag" / "pairwise" / "fold": step table of `rank` among `p`
 //   kind "parse_algo": parses `arg` as an HCCL_ALGO value;  kind "rhd_info": pairing of `rank`

@@ -181,6 +181,14 @@ class HcclOpResource(ctypes.Structure):
 _sig("HcclCalcOpResource", R, c_void_p, c_int, c_uint64, c_int, c_int, c_int, POINTER(HcclOpResource))
 
 
+if hasattr(lib, "HcclDiagnoseDump"):
+    _sig("HcclDiagnoseDump", R, ctypes.c_char_p, c_uint32)
+if hasattr(lib, "HcclFusedAdamW"):
+    _sig("HcclFusedAdamW", R, c_void_p, c_uint32, c_int, c_int, ctypes.c_float, c_void_p, ctypes.c_float, ctypes.c_float, ctypes.c_float,
+         ctypes.c_float, c_void_p, c_void_p)
+    _sig("HcclFusedAdamWLaunches", c_uint32, c_uint32)
+
+
 class HcclResPackGraphMode(ctypes.Structure):
     _fields_ = [("size", c_uint32), ("scratch", c_void_p), ("scratchBytes", c_uint64), ("slaveStreams", POINTER(c_void_p)),
                 ("slaveStreamNum", c_uint32)]

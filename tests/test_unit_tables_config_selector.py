@@ -365,3 +365,27 @@ def test_threshold_mode_drives_the_selection_and_hccl_algo_still_wins():
         os.environ.pop("HCCL_SELECTOR_MODE", None)
         os.environ.pop("HCCL_ALGO", None)
         lib.HcclReloadEnvConfig()
+
+
+def test_diagnose_ring_keeps_operator_entries():
+    try:
+        os.environ["HCCL_DIAGNOSE_ENABLE"] = "1"
+        lib.HcclReloadEnvConfig()
+        comms = Communicator.host_sim(2)
+        import threading
+        ins = [np.ones(8, np.float32) for _ in range(2)]
+        outs = [np.zeros(8, np.float32) for _ in range(2)]
+        ts = [threading.Thread(target=lambda r=r: comms[r].all_reduce(ins[r], outs[r])) for r in range(2)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        buf = ctypes.create_string_buffer(1 << 16)
+        assert lib.HcclDiagnoseDump(buf, len(buf)) == 0
+        text = buf.value.decode()
+        assert "Entry-HcclAllReduce" in text and "count[8]" in text, text[-400:]
+        small = ctypes.create_string_buffer(40)                     # a short buffer keeps the newest part
+        assert lib.HcclDiagnoseDump(small, len(small)) == 0 and len(small.value) == 39
+        for c in comms:
+            c.destroy()
+    finally:
+        os.environ.pop("HCCL_DIAGNOSE_ENABLE", None)
+        lib.HcclReloadEnvConfig()
