@@ -1,12 +1,14 @@
 """Single-pass element-wise kernels of the decoder stack against the PyTorch expressions they replace (one GPU).
 
-    python bench/fused_ops_bench.py [--rows 4096] [--hidden 8192] [--ffn 28672] [--iters 20] [--only NAME]
+    python bench/fused_ops_bench.py [--rows 4096] [--hidden 8192] [--ffn 28672] [--iters 20] [--only NAME] [--adam-params N]
 
 Shapes of the Llama-3-70B block at sequence 4096: residual add + RMSNorm on [rows, hidden], SwiGLU on
 [rows, 2 * ffn], rotary embedding on 64 heads of 128.  Forward + backward per op, CUDA events, 5 warm-up + `iters`
 timed calls; a 256 MiB buffer is rewritten between calls so that every call starts with a cold L2.  Prints one JSON row
 per op with the algorithmic bytes (each tensor read or written once), the achieved GB/s and the same for the PyTorch
 expression.  `--only NAME` runs one op a few times without the comparison (for profiling one kernel in isolation).
+The `adamw` row is the optimizer update over 24 bf16 tensors of `--adam-params` elements in total (bf16 moments, 14
+bytes per parameter) against torch.optim.AdamW(fused=True).
 """
 import argparse
 import json
@@ -44,6 +46,7 @@ def main():
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--only", default="")
+    ap.add_argument("--adam-params", type=int, default=1 << 29, help="parameters of the adamw row (default 512 Mi: 7.5 GB moved per call)")
     args = ap.parse_args()
     torch.cuda.set_device(0)
     g = torch.Generator(device="cuda").manual_seed(0)
@@ -87,6 +90,22 @@ def main():
         "swiglu": (swi, (2 * R * Fd + R * Fd) * 2 + (2 * R * Fd + R * Fd + 2 * R * Fd) * 2),
         "rope": (rope, 2 * R * NH * D * 2 * 2),
     }
+    # optimizer: the same update with this library's kernel and with PyTorch's fused multi-tensor AdamW
+    from hccl_b200.ops import FusedAdamW
+    per = max(8, args.adam_params // 24)
+    adam_state = {}
+
+    def adam(use):
+        if use not in adam_state:
+            ps = [torch.nn.Parameter(rnd(per)) for _ in range(24)]
+            for p_ in ps:
+                p_.grad = rnd(per)
+            opt = FusedAdamW(ps, lr=1e-4) if use else torch.optim.AdamW(ps, lr=1e-4, fused=True)
+            adam_state[use] = (ps, opt)
+        return adam_state[use][1].step
+
+    if not args.only or args.only == "adamw":
+        cases["adamw"] = (adam, 24 * per * 14)
     for name, (mk, nbytes) in cases.items():
         if args.only and args.only != name:
             continue

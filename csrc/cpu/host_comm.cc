@@ -4,6 +4,8 @@
 #include <algorithm>
 #include <chrono>
 #include <cstring>
+#include <map>
+#include <sstream>
 #include <thread>
 #include "../core/comm.h"
 #include "../core/json.h"
@@ -387,6 +389,80 @@ HcclResult HcclTestHostRecoveries(HcclComm comm, uint64_t* count)
     CommImpl* c = static_cast<CommImpl*>(comm);
     if (!c->hostComm) return HCCL_E_NOT_SUPPORT;
     *count = c->hostComm->world->recoveries();
+    return HCCL_SUCCESS;
+}
+
+// Verifier self-test entry: checks a trace written as text.  First line "ranks <n> op <allreduce|allgather|
+// reducescatter|reduce|scatter|alltoall> count <elements> [root <r>]" (fp32, sum); then one task per line:
+//   <rank> <queue> copy|reduce <dstRank>:<in|out|scr>:<byteOffset> <srcRank>:<in|out|scr>:<byteOffset> <bytes>
+//   <rank> <queue> post|wait <peer> <notifyIdx>
+HcclResult HcclDebugVerifyTrace(const char* script, char* report, uint32_t capacity)
+{
+    CHK_PTR_NULL(script); CHK_PTR_NULL(report);
+    std::istringstream is(script);
+    std::string word, opName;
+    uint32_t n = 0, root = 0;
+    uint64_t count = 0;
+    std::string header;
+    std::getline(is, header);
+    std::istringstream hs(header);
+    while (hs >> word) {
+        if (word == "ranks") hs >> n;
+        else if (word == "op") hs >> opName;
+        else if (word == "count") hs >> count;
+        else if (word == "root") hs >> root;
+    }
+    static const std::map<std::string, HcclCMDType> kOps = {{"allreduce", HCCL_CMD_ALLREDUCE}, {"allgather", HCCL_CMD_ALLGATHER},
+        {"reducescatter", HCCL_CMD_REDUCE_SCATTER}, {"reduce", HCCL_CMD_REDUCE}, {"scatter", HCCL_CMD_SCATTER}, {"alltoall", HCCL_CMD_ALLTOALL}};
+    auto it = kOps.find(opName);
+    if (n == 0 || n > 64 || count == 0 || it == kOps.end() || root >= n) return HCCL_E_PARA;
+    HostOpDesc d;
+    d.op = it->second; d.dtype = HCCL_DATA_TYPE_FP32; d.redOp = HCCL_REDUCE_SUM; d.count = count; d.root = root;
+    const uint64_t unit = count * 4;
+    const bool inWide = d.op == HCCL_CMD_REDUCE_SCATTER || d.op == HCCL_CMD_SCATTER || d.op == HCCL_CMD_ALLTOALL;
+    const bool outWide = d.op == HCCL_CMD_ALLGATHER || d.op == HCCL_CMD_ALLTOALL;
+    auto mem = [&](const std::string& text, Mem* m) {
+        unsigned r = 0;
+        char buf[8] = {0};
+        unsigned long long off = 0;
+        if (sscanf(text.c_str(), "%u:%3[a-z]:%llu", &r, buf, &off) != 3 || r >= n) return false;
+        const std::string b(buf);
+        m->rank = r;
+        m->off = off;
+        m->buf = b == "in" ? BufKind::INPUT : b == "out" ? BufKind::OUTPUT : BufKind::SCRATCH;
+        return b == "in" || b == "out" || b == "scr";
+    };
+    std::vector<std::vector<Task>> tasks(n);
+    std::string line;
+    while (std::getline(is, line)) {
+        std::istringstream ls(line);
+        uint32_t rank, queue;
+        std::string kind;
+        if (!(ls >> rank >> queue >> kind)) continue;      // blank line
+        if (rank >= n) return HCCL_E_PARA;
+        Task t{};
+        t.rank = rank;
+        t.queue = queue;
+        if (kind == "post" || kind == "wait") {
+            if (!(ls >> t.peer >> t.notifyIdx) || t.peer >= n || t.notifyIdx >= HostWorld::kNotifyIdx) return HCCL_E_PARA;
+            t.kind = kind == "post" ? TaskKind::POST : TaskKind::WAIT;
+        } else if (kind == "copy" || kind == "reduce") {
+            std::string dst, src;
+            if (!(ls >> dst >> src >> t.bytes) || !mem(dst, &t.dst) || !mem(src, &t.src)) return HCCL_E_PARA;
+            const bool local = t.dst.rank == rank && t.src.rank == rank, reads = t.dst.rank == rank;
+            if (kind == "copy") t.kind = local ? TaskKind::LOCAL_COPY : reads ? TaskKind::READ : TaskKind::WRITE;
+            else t.kind = local ? TaskKind::LOCAL_REDUCE : reads ? TaskKind::READ_REDUCE : TaskKind::WRITE_REDUCE;
+        } else {
+            return HCCL_E_PARA;
+        }
+        tasks[rank].push_back(t);
+    }
+    TopoMeta meta;
+    std::string err;
+    if (!ParseTopoMeta(nullptr, n, &meta, &err)) return HCCL_E_INTERNAL;
+    HostWorld world(n, meta, 1 << 20, 1000000000ull);
+    const VerifyReport rep = world.VerifyTasks(d, unit * (inWide ? n : 1), unit * (outWide ? n : 1), tasks);
+    snprintf(report, capacity, "%s", rep.Text().c_str());
     return HCCL_SUCCESS;
 }
 

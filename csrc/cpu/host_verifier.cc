@@ -241,6 +241,19 @@ void HostVerifier::CheckOp(HostWorld& w, const HostWorld::OpRecord& op, VerifyRe
     }
 }
 
+VerifyReport HostWorld::VerifyTasks(const HostOpDesc& d, uint64_t inBytes, uint64_t outBytes, const std::vector<std::vector<Task>>& tasks)
+{
+    VerifyReport rep;
+    OpRecord rec;
+    rec.desc = d;
+    rec.inBytes.assign(n_, inBytes);
+    rec.outBytes.assign(n_, outBytes);
+    rec.tasks = tasks;
+    rec.tasks.resize(n_);
+    HostVerifier::CheckOp(*this, rec, &rep);
+    return rep;
+}
+
 VerifyReport HostWorld::Verify()
 {
     VerifyReport rep;

@@ -120,6 +120,8 @@ public:
     bool tracing() const { return tracing_.load(); }
     void Append(const Task& t);
     VerifyReport Verify();      // checks the trace of the operators run since TraceBegin, then stops tracing
+    // Checks a hand-written trace of one operator (self-tests of the verifier): tasks[r] is rank r's task list.
+    VerifyReport VerifyTasks(const HostOpDesc& d, uint64_t inBytes, uint64_t outBytes, const std::vector<std::vector<Task>>& tasks);
 
     void AddRef() { refs_.fetch_add(1); }
     bool Release() { return refs_.fetch_sub(1) == 1; }

@@ -69,6 +69,10 @@ typedef struct {
 HcclResult HcclCalcOpResource(HcclComm comm, HcclCMDType op, uint64_t count, HcclDataType dataType, HcclReduceOp reduceOp, int registered,
                               HcclOpResource* res);
 
+// Self-test entry of the trace verifier: checks a trace written as text (grammar beside the definition in
+// csrc/cpu/host_comm.cc) and writes the verifier's report ("OK: ..." or "FAILED: ..." with one line per finding).
+HcclResult HcclDebugVerifyTrace(const char* script, char* report, uint32_t capacity);
+
 // Post-mortem record of the last operator entries of this process (kept when HCCL_DIAGNOSE_ENABLE=1, 2000 lines, oldest
 // first), the counterpart of HCCL's diagnose ring.  Writes at most `capacity` bytes including the terminator.
 HcclResult HcclDiagnoseDump(char* text, uint32_t capacity);

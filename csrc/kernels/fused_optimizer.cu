@@ -4,8 +4,9 @@
 // framework multi-tensor kernel that is launched hundreds of times with small chunks reaches about half of the HBM
 // copy rate.  Here the tensor table travels in the kernel's parameter space (no device table to upload, so the launch
 // can be captured in a CUDA graph as it is), a block finds its tensor by a binary search over the chunk prefix, and
-// every thread keeps sixteen 16-byte loads in flight before the first store.  Math is fp32 and follows
-// torch.optim.AdamW (decoupled weight decay, bias correction, eps added after the square root).
+// every thread keeps eight 16-byte loads in flight before the first store (32 warps per SM hide the arithmetic).
+// Math is fp32 and follows torch.optim.AdamW (decoupled weight decay, bias correction, eps added after the square
+// root); the square root and the division are the hardware approximations (two ulp).
 // The reference has no counterpart (it is a communication library).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -18,7 +19,7 @@ namespace {
 
 constexpr int kAdamThreads = 256;
 constexpr int kAdamMaxTensors = 80;                 // 80 * 40 B + 81 * 4 B + 4 B of the 4 KiB parameter space
-constexpr uint32_t kVecPerThread = 4;
+constexpr uint32_t kVecPerThread = 2;                             // 8 loads in flight per thread, 64 registers: 4 blocks per SM
 constexpr uint32_t kChunkVecs = kAdamThreads * kVecPerThread;     // 16-byte vectors of each array per block
 
 struct AdamBatch {
@@ -28,6 +29,13 @@ struct AdamBatch {
 };
 
 struct AdamScalars { float lr, beta1, beta2, eps, weightDecay; };
+
+__device__ __forceinline__ float SqrtApprox(float x)
+{
+    float r;
+    asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
 
 // step[0] += 1, step[1] = 1 - beta1^step, step[2] = sqrt(1 - beta2^step)
 __global__ void AdamStepKernel(float* step, float beta1, float beta2)
@@ -78,19 +86,20 @@ template <> struct Vec<float> {
     static __device__ __forceinline__ void Put(float* p, uint64_t i, float v) { p[i] = v; }
 };
 
-__device__ __forceinline__ void AdamElem(float& p, float g, float& m, float& v, const AdamScalars& s, float bc1, float bc2s)
+// decay = 1 - lr * weightDecay, stepSize = lr / (1 - beta1^t), rbc2s = 1 / sqrt(1 - beta2^t): computed once per thread.
+// Square root and division are the two-ulp hardware approximations; the stored values are rounded far more coarsely.
+__device__ __forceinline__ void AdamElem(float& p, float g, float& m, float& v, const AdamScalars& s, float decay, float stepSize, float rbc2s)
 {
-    p *= 1.0f - s.lr * s.weightDecay;
     m = s.beta1 * m + (1.0f - s.beta1) * g;
     v = s.beta2 * v + (1.0f - s.beta2) * g * g;
-    const float denom = sqrtf(v) / bc2s + s.eps;
-    p -= (s.lr / bc1) * (m / denom);
+    const float denom = SqrtApprox(v) * rbc2s + s.eps;
+    p = p * decay - stepSize * __fdividef(m, denom);
 }
 
 // TP: storage type of parameters and gradients, TS: storage type of the two moments.  A block owns kChunkElems
 // consecutive elements of one tensor, where an "element group" is what one 16-byte vector of the WIDER type holds.
 template <class TP, class TS>
-__global__ void __launch_bounds__(kAdamThreads) AdamWKernel(const __grid_constant__ AdamBatch b, AdamScalars s, const float* __restrict__ step,
+__global__ void __launch_bounds__(kAdamThreads, 4) AdamWKernel(const __grid_constant__ AdamBatch b, AdamScalars s, const float* __restrict__ step,
                                                             const float* __restrict__ lrDev)
 {
     // which tensor: last i with chunkStart[i] <= blockIdx.x
@@ -101,7 +110,7 @@ __global__ void __launch_bounds__(kAdamThreads) AdamWKernel(const __grid_constan
     }
     const HcclAdamTensor& t = b.t[lo];
     if (lrDev) s.lr = *lrDev;
-    const float bc1 = step[1], bc2s = step[2];
+    const float decay = 1.0f - s.lr * s.weightDecay, stepSize = s.lr / step[1], rbc2s = 1.0f / step[2];
     constexpr int G = Vec<TP>::kElems < Vec<TS>::kElems ? Vec<TP>::kElems : Vec<TS>::kElems;     // elements per thread-iteration
     constexpr uint64_t kChunkElems = (uint64_t)kChunkVecs * G;
     const uint64_t begin = (uint64_t)(blockIdx.x - b.chunkStart[lo]) * kChunkElems;
@@ -135,7 +144,7 @@ __global__ void __launch_bounds__(kAdamThreads) AdamWKernel(const __grid_constan
             Vec<TS>::Load(rm[k], fm);
             Vec<TS>::Load(rv[k], fv);
 #pragma unroll
-            for (int e = 0; e < G; ++e) AdamElem(fp[e], fg[e], fm[e], fv[e], s, bc1, bc2s);
+            for (int e = 0; e < G; ++e) AdamElem(fp[e], fg[e], fm[e], fv[e], s, decay, stepSize, rbc2s);
             reinterpret_cast<uint4*>(p + begin)[i] = Vec<TP>::Store(fp);
             reinterpret_cast<uint4*>(m + begin)[i] = Vec<TS>::Store(fm);
             reinterpret_cast<uint4*>(v + begin)[i] = Vec<TS>::Store(fv);
@@ -145,7 +154,7 @@ __global__ void __launch_bounds__(kAdamThreads) AdamWKernel(const __grid_constan
     // mixed widths, unaligned tensors and the ragged tail: element by element
     for (uint64_t i = done + threadIdx.x; i < end; i += kAdamThreads) {
         float fp = Vec<TP>::Get(p, i), fm = Vec<TS>::Get(m, i), fv = Vec<TS>::Get(v, i);
-        AdamElem(fp, Vec<TP>::Get(g, i), fm, fv, s, bc1, bc2s);
+        AdamElem(fp, Vec<TP>::Get(g, i), fm, fv, s, decay, stepSize, rbc2s);
         Vec<TP>::Put(p, i, fp);
         Vec<TS>::Put(m, i, fm);
         Vec<TS>::Put(v, i, fv);
