@@ -396,7 +396,10 @@ HcclResult SelectAlgorithm(SelectorState& st, const TopoInfo& topo, const EnvCon
             else if (r.cost == out->table[(size_t)best].cost) tie = true;
         }
         if (best >= 0) {
-            if (tie) HCCL_WARNING("cost tie for op %d at %llu bytes: first registered algorithm wins", (int)op.op, (unsigned long long)op.bytes);
+            if (tie && !st.tieWarned[op.op]) {
+                st.tieWarned[op.op] = true;
+                HCCL_WARNING("cost tie for op %d at %llu bytes: first registered algorithm wins (said once per operator)", (int)op.op, (unsigned long long)op.bytes);
+            }
             out->algIndex = out->table[(size_t)best].algIndex;
             out->alg = &all[(size_t)out->algIndex];
             out->costUs = out->table[(size_t)best].cost;

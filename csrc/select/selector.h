@@ -166,6 +166,7 @@ public:
     const HcclTunerPluginOps* tunerOps = nullptr;
     std::vector<uint8_t> tunerCtx;
     int tunerSlowCalls = 0;
+    bool tieWarned[HCCL_CMD_MAX] = {false};   // the cost-tie warning is given once per operator
     bool tunerDisabled = false;
     uint64_t selections = 0;
 };

@@ -12,7 +12,8 @@ import os
 from ctypes import POINTER, c_char_p, c_double, c_int, c_int32, c_uint8, c_uint32, c_uint64, c_void_p
 from pathlib import Path
 
-_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libhccl_b200.so"
+# HCCL_B200_LIB names another build of the library (the AddressSanitizer variant of `build.py --asan`)
+_LIB_PATH = Path(os.environ["HCCL_B200_LIB"]) if os.environ.get("HCCL_B200_LIB") else Path(__file__).resolve().parent / "lib" / "libhccl_b200.so"
 
 
 def _load() -> ctypes.CDLL:

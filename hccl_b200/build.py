@@ -3,7 +3,12 @@
 Every ``.cu`` file is compiled by nvcc for sm_100a only
 (``-gencode arch=compute_100a,code=sm_100a -lineinfo``), every ``.cc`` file by
 g++; objects are cached under ``build/obj`` and rebuilt when the source or any
-header is newer.  Usage: ``python -m hccl_b200.build [--force] [--verbose]``.
+header is newer.  Usage: ``python hccl_b200/build.py [--force] [--verbose] [--ptxas] [--asan]``.
+
+``--asan`` builds a second library, ``libhccl_b200_asan.so``, whose host code (every ``.cc`` file: API, selector,
+bootstrap, host engine, verifier) is compiled with AddressSanitizer; the CUDA objects are shared with the normal
+build.  Load it with ``HCCL_B200_LIB=<path> LD_PRELOAD=$(gcc -print-file-name=libasan.so)`` (the interpreter itself
+is not instrumented, so the runtime has to come first), ``ASAN_OPTIONS=detect_leaks=0``.
 """
 from __future__ import annotations
 
@@ -46,13 +51,18 @@ def _newest_header() -> float:
     return t
 
 
-def _compile(src: Path, verbose: bool, extra_flags=()):
+ASAN_FLAGS = ["-fsanitize=address", "-fno-omit-frame-pointer", "-O1"]
+OBJ_ASAN = ROOT / "build" / "obj_asan"
+LIB_ASAN = LIB_DIR / "libhccl_b200_asan.so"
+
+
+def _compile(src: Path, verbose: bool, extra_flags=(), obj_dir: Path = None, cxx_extra=()):
     rel = src.relative_to(CSRC)
-    obj = OBJ / (str(rel).replace("/", "__") + ".o")
+    obj = (obj_dir or OBJ) / (str(rel).replace("/", "__") + ".o")
     if src.suffix == ".cu":
         cmd = [NVCC, *NVCC_FLAGS, *extra_flags, "-c", str(src), "-o", str(obj)]
     else:
-        cmd = ["g++", *CXX_FLAGS, "-c", str(src), "-o", str(obj)]
+        cmd = ["g++", *CXX_FLAGS, *cxx_extra, "-c", str(src), "-o", str(obj)]
     if verbose:
         print(" ".join(cmd), flush=True)
     r = subprocess.run(cmd, capture_output=True, text=True)
@@ -90,6 +100,35 @@ def build(force: bool = False, verbose: bool = False, ptxas_verbose: bool = Fals
     return LIB
 
 
+def build_asan(verbose: bool = False) -> Path:
+    """The AddressSanitizer variant: instrumented host objects + the CUDA objects of the normal build."""
+    build(verbose=verbose)
+    OBJ_ASAN.mkdir(parents=True, exist_ok=True)
+    cu, cc = _sources()
+    hdr_time = _newest_header()
+    todo, objs = [], []
+    for src in cu:
+        objs.append(OBJ / (str(src.relative_to(CSRC)).replace("/", "__") + ".o"))
+    for src in cc:
+        obj = OBJ_ASAN / (str(src.relative_to(CSRC)).replace("/", "__") + ".o")
+        objs.append(obj)
+        if not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_time):
+            todo.append(src)
+    if todo:
+        with concurrent.futures.ThreadPoolExecutor(min(len(todo), max(1, (os.cpu_count() or 4)))) as ex:
+            list(ex.map(lambda s: _compile(s, verbose, (), OBJ_ASAN, ASAN_FLAGS), todo))
+    if todo or not LIB_ASAN.exists():
+        cmd = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB_ASAN), *map(str, objs), "-Xcompiler", "-pthread",
+               "-Xcompiler", "-fsanitize=address", "-ldl", "-lrt"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"linking the ASan library failed:\n{r.stdout}\n{r.stderr}")
+    return LIB_ASAN
+
+
 if __name__ == "__main__":
+    if "--asan" in sys.argv:
+        print(build_asan(verbose="--verbose" in sys.argv))
+        sys.exit(0)
     lib = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, ptxas_verbose="--ptxas" in sys.argv)
     print(lib)

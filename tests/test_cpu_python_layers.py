@@ -57,3 +57,38 @@ def test_decoder_stack_runs_on_cpu_with_reference_ops():
     torch.testing.assert_close(x2, x + F.rms_norm(x, (hdim,), w, 1e-5))
     q = fused.rope(h2.view(s, heads, d), cos, sin, use_kernels=False)
     assert q.shape == (s, heads, d)
+
+
+def test_python_wrapper_overhead_over_raw_ctypes():
+    """The Python method adds little over the raw ctypes call of the same operator (the reference budgets 10 us for its
+    wrapper: 20 warm-up calls, 100 timed, count 8).  A single-rank communicator takes the local-copy shortcut, so the
+    time is entry code only.  The bound here is loose because the CPU this runs on is shared."""
+    import ctypes
+    import time
+
+    import numpy as np
+
+    import hccl_b200 as hb
+    from hccl_b200._lib import lib
+    from hccl_b200.types import DataType, ReduceOp
+
+    comm = hb.Communicator.host_sim(1)[0]
+    x, y = np.arange(8, dtype=np.float32), np.zeros(8, np.float32)
+    px, py = x.ctypes.data_as(ctypes.c_void_p), y.ctypes.data_as(ctypes.c_void_p)
+
+    def best(fn):
+        for _ in range(20):
+            fn()
+        times = []
+        for _ in range(5):
+            t0 = time.perf_counter()
+            for _ in range(100):
+                fn()
+            times.append((time.perf_counter() - t0) / 100)
+        return min(times) * 1e6
+
+    raw = best(lambda: lib.HcclAllReduce(px, py, 8, int(DataType.FP32), int(ReduceOp.SUM), comm.handle, None))
+    wrapped = best(lambda: comm.all_reduce(x, y))
+    assert np.array_equal(y, x)
+    assert wrapped - raw < 50.0, (raw, wrapped)
+    comm.destroy()
