@@ -30,8 +30,8 @@ HcclResult HcclFusedRope(const void* in, uint64_t inStride, void* out, uint64_t 
 // AdamW (decoupled weight decay, bias correction as torch.optim.AdamW) over a list of tensors: one launch per 80
 // tensors plus one for the step counter.  `tensors` is a HOST array; it travels in the kernels' parameter space, so
 // nothing is uploaded or allocated and the call can be captured in a CUDA graph.  paramType is the storage type of
-// parameters and gradients, stateType that of the two moments: bf16/bf16 and fp32/fp32 run 16-byte vectors, bf16
-// parameters with fp32 moments run element by element.  stepState: 4 floats in device memory owned by the caller,
+// parameters and gradients, stateType that of the two moments: bf16/bf16, fp32/fp32, or bf16 parameters with fp32
+// moments; tensors whose four pointers are not 16-byte aligned run element by element.  stepState: 4 floats in device memory owned by the caller,
 // [0] = steps taken so far (start at 0; the call increments it on the device), [1..2] scratch for the bias corrections.
 // lrDev != NULL: the learning rate is read from device memory at run time (schedulers under graph replay), else `lr`.
 typedef struct {

@@ -151,7 +151,49 @@ __global__ void __launch_bounds__(kAdamThreads, 4) AdamWKernel(const __grid_cons
         }
         done = begin + nVec * G;
     }
-    // mixed widths, unaligned tensors and the ragged tail: element by element
+    if constexpr (sizeof(TP) == 2 && sizeof(TS) == 4) {
+        // bf16 parameters with fp32 moments: four elements per step, 8-byte vectors of p and g, 16-byte vectors of m and v
+        if (aligned) {
+            const uint64_t nGrp = (end - begin) / 4;
+            const uint2* pv = reinterpret_cast<const uint2*>(p + begin);
+            const uint2* gv = reinterpret_cast<const uint2*>(g + begin);
+            const uint4* mv = reinterpret_cast<const uint4*>(m + begin);
+            const uint4* vv = reinterpret_cast<const uint4*>(v + begin);
+            uint2 rp[kVecPerThread], rg[kVecPerThread];
+            uint4 rm[kVecPerThread], rv[kVecPerThread];
+#pragma unroll
+            for (uint32_t k = 0; k < kVecPerThread; ++k) {
+                const uint64_t i = threadIdx.x + (uint64_t)k * kAdamThreads;
+                if (i < nGrp) { rp[k] = pv[i]; rg[k] = __ldcs(gv + i); rm[k] = mv[i]; rv[k] = vv[i]; }
+            }
+#pragma unroll
+            for (uint32_t k = 0; k < kVecPerThread; ++k) {
+                const uint64_t i = threadIdx.x + (uint64_t)k * kAdamThreads;
+                if (i >= nGrp) continue;
+                float fp[4], fg[4], fm[4], fv[4];
+                const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&rp[k]);
+                const __nv_bfloat162* hg = reinterpret_cast<const __nv_bfloat162*>(&rg[k]);
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const float2 a = __bfloat1622float2(hp[e]), c = __bfloat1622float2(hg[e]);
+                    fp[2 * e] = a.x; fp[2 * e + 1] = a.y; fg[2 * e] = c.x; fg[2 * e + 1] = c.y;
+                }
+                Vec<float>::Load(rm[k], fm);
+                Vec<float>::Load(rv[k], fv);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) AdamElem(fp[e], fg[e], fm[e], fv[e], s, decay, stepSize, rbc2s);
+                uint2 op;
+                __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&op);
+                ho[0] = __floats2bfloat162_rn(fp[0], fp[1]);
+                ho[1] = __floats2bfloat162_rn(fp[2], fp[3]);
+                reinterpret_cast<uint2*>(p + begin)[i] = op;
+                reinterpret_cast<uint4*>(m + begin)[i] = Vec<float>::Store(fm);
+                reinterpret_cast<uint4*>(v + begin)[i] = Vec<float>::Store(fv);
+            }
+            done = begin + nGrp * 4;
+        }
+    }
+    // unaligned tensors and the ragged tail: element by element
     for (uint64_t i = done + threadIdx.x; i < end; i += kAdamThreads) {
         float fp = Vec<TP>::Get(p, i), fm = Vec<TS>::Get(m, i), fv = Vec<TS>::Get(v, i);
         AdamElem(fp, Vec<TP>::Get(g, i), fm, fv, s, decay, stepSize, rbc2s);

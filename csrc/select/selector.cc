@@ -226,7 +226,10 @@ bool TopoMatches(const AlgEntry& a, const TopoInfo& topo, std::string* why)
     const uint32_t levels = topo.nPods > 1 ? 3 : (topo.nServers > 1 ? 2 : 1);
     // an algorithm with fewer levels than the topology treats the extra levels as one flat group, which is legal;
     // more levels than the topology has is not
-    if (t.enforceMaxLevels && levels > t.maxLevels) { *why = "topo: flat algorithm on a " + std::to_string(levels) + "-level topology"; return false; }
+    // Servers of different sizes have no level-1 groups of equal local index: the hierarchical forms are out and the
+    // flat forms run across the levels as one group (the reference falls back to a flat NHR when the server sizes
+    // share no common divisor, topo_host.cc:662-684).
+    if (t.enforceMaxLevels && levels > t.maxLevels && topo.symmetric) { *why = "topo: flat algorithm on a " + std::to_string(levels) + "-level topology"; return false; }
     if (t.minLevels > levels) { *why = "topo: needs " + std::to_string(t.minLevels) + " levels, topology has " + std::to_string(levels); return false; }
     if (!(t.level0Shapes & (1u << (int)topo.level0))) { *why = "topo: level-0 shape not supported"; return false; }
     if (t.maxRankSize && topo.nRanks > t.maxRankSize) { *why = "topo: more than " + std::to_string(t.maxRankSize) + " ranks"; return false; }

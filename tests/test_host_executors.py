@@ -310,3 +310,27 @@ def test_tree_executor_is_not_selected_without_a_tree_and_rejects_too_deep_a_tre
     finally:
         os.environ.pop("HCCL_ALGO_TREE")
         lib.HcclReloadEnvConfig()
+
+
+def test_servers_of_different_sizes_fall_back_to_flat_algorithms(algo_env):
+    n = 5
+    comms = make(n, topo="[[[0,1,2],[3,4]]]", algo=None)
+    count = 777
+    ins = [np.random.default_rng(r).standard_normal(count).astype(np.float32) for r in range(n)]
+    outs = [np.zeros(count, np.float32) for _ in range(n)]
+    verified(comms, lambda r, c: c.all_reduce(ins[r], outs[r]))
+    name = comms[0].last_algorithm()
+    assert "Sole" in name or "Concurrent" in name, name
+    ref = np.sum(np.stack(ins).astype(np.float64), 0)
+    for o in outs:
+        np.testing.assert_allclose(o, ref, rtol=2e-6, atol=2e-5)
+    bufs = [np.full(count, r, np.int32) for r in range(n)]
+    verified(comms, lambda r, c: c.broadcast(bufs[r], 4))
+    assert all(np.all(b == 4) for b in bufs)
+    rs_in = [np.random.default_rng(5 + r).standard_normal(16 * n).astype(np.float32) for r in range(n)]
+    rs_out = [np.zeros(16, np.float32) for _ in range(n)]
+    verified(comms, lambda r, c: c.reduce_scatter(rs_in[r], rs_out[r]))
+    ref = np.sum(np.stack(rs_in).astype(np.float64), 0)
+    for r in range(n):
+        np.testing.assert_allclose(rs_out[r], ref[r * 16:(r + 1) * 16], rtol=2e-6, atol=2e-5)
+    destroy(comms)
