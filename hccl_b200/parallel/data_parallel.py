@@ -1,0 +1,137 @@
+"""Data-parallel gradient synchronisation on the AllReduce operator.
+
+The reference provides the collectives data parallelism consumes (AllReduce for replicated gradients, ReduceScatter +
+AllGather for sharded ones, docs/en/architecture-brief.md:16-17) and leaves the bucketing to the framework.  This is
+that thin framework side for plain PyTorch modules:
+
+* gradients are packed into flat buckets of about ``bucket_mib`` MiB, in reverse parameter order (the order in which
+  backward produces them);
+* ``overlap=True`` hooks every parameter: when the last gradient of a bucket has been accumulated, the bucket's
+  AllReduce is issued at once - on a side stream for CUDA tensors, so that it runs beside the rest of backward - and
+  buckets are always issued in index order, which keeps the ranks' call sequences identical;
+* ``finish()`` (or ``reduce()`` without hooks) waits for the side stream, divides by the world size when
+  ``average=True`` and writes the reduced values back into ``p.grad``.
+
+NVSwitch gives every GPU full bandwidth to every peer, so a bucket is sized for launch latency and overlap (tens of
+MiB), not for link count.
+"""
+from __future__ import annotations
+
+from typing import Iterable, List
+
+import torch
+
+
+class GradientBucketer:
+    def __init__(self, params: Iterable[torch.nn.Parameter], comm, bucket_mib: float = 25.0, average: bool = True, overlap: bool = False):
+        self.comm = comm
+        self.average = average
+        self.params: List[torch.nn.Parameter] = [p for p in params if p.requires_grad]
+        order = list(reversed(self.params))
+        limit = int(bucket_mib * (1 << 20))
+        self.buckets: List[List[torch.nn.Parameter]] = []
+        cur, cur_bytes, cur_key = [], 0, None
+        for p in order:
+            key = (p.dtype, p.device)
+            nbytes = p.numel() * p.element_size()
+            if cur and (key != cur_key or cur_bytes + nbytes > limit):
+                self.buckets.append(cur)
+                cur, cur_bytes = [], 0
+            cur.append(p)
+            cur_bytes += nbytes
+            cur_key = key
+        if cur:
+            self.buckets.append(cur)
+        self.flat = [torch.zeros(sum(p.numel() for p in b), dtype=b[0].dtype, device=b[0].device) for b in self.buckets]
+        self._bucket_of = {p: i for i, b in enumerate(self.buckets) for p in b}
+        self._pending = [0] * len(self.buckets)
+        self._next = 0
+        self._launched = [False] * len(self.buckets)
+        self._stream = None
+        self._hooks = []
+        if overlap:
+            for p in self.params:
+                self._hooks.append(p.register_post_accumulate_grad_hook(self._on_grad))
+        self._reset()
+
+    # ------------------------------------------------------------------ internals
+    def _reset(self):
+        self._pending = [len(b) for b in self.buckets]
+        self._launched = [False] * len(self.buckets)
+        self._next = 0
+
+    def _side_stream(self, device):
+        if device.type != "cuda":
+            return None
+        if self._stream is None:
+            self._stream = torch.cuda.Stream(device=device)
+        return self._stream
+
+    def _launch(self, i: int):
+        bucket, flat = self.buckets[i], self.flat[i]
+        side = self._side_stream(flat.device)
+        if side is not None:
+            side.wait_stream(torch.cuda.current_stream(flat.device))      # the gradients of this bucket are complete
+        ctx = torch.cuda.stream(side) if side is not None else _Null()
+        with ctx:
+            off = 0
+            for p in bucket:
+                n = p.numel()
+                if p.grad is None:
+                    flat[off:off + n].zero_()          # a parameter that took no part in this step contributes zeros
+                else:
+                    flat[off:off + n].copy_(p.grad.reshape(-1))
+                off += n
+            self.comm.all_reduce(flat, flat, stream=side) if side is not None else self.comm.all_reduce(flat, flat)
+        self._launched[i] = True
+
+    def _on_grad(self, p):
+        i = self._bucket_of[p]
+        self._pending[i] -= 1
+        # issue every bucket that is complete, in index order only
+        while self._next < len(self.buckets) and self._pending[self._next] == 0:
+            self._launch(self._next)
+            self._next += 1
+
+    # ------------------------------------------------------------------ API
+    def reduce(self):
+        """Synchronises every gradient now (no hooks needed)."""
+        for i in range(len(self.buckets)):
+            if not self._launched[i]:
+                self._launch(i)
+        self.finish()
+
+    def finish(self):
+        """Waits for the issued buckets (launching those whose parameters never produced a gradient), then writes the
+        reduced gradients back."""
+        for i in range(len(self.buckets)):
+            if not self._launched[i]:
+                self._launch(i)
+        if self._stream is not None:
+            torch.cuda.current_stream(self._stream.device).wait_stream(self._stream)
+        scale = 1.0 / self.comm.world_size if self.average else 1.0
+        for bucket, flat in zip(self.buckets, self.flat):
+            if scale != 1.0:
+                flat.mul_(scale)
+            off = 0
+            for p in bucket:
+                n = p.numel()
+                if p.grad is None:
+                    p.grad = flat[off:off + n].reshape(p.shape).clone()
+                else:
+                    p.grad.copy_(flat[off:off + n].reshape(p.shape))
+                off += n
+        self._reset()
+
+    def remove_hooks(self):
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
+
+
+class _Null:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *a):
+        return False
