@@ -92,3 +92,19 @@ def test_python_wrapper_overhead_over_raw_ctypes():
     assert np.array_equal(y, x)
     assert wrapped - raw < 50.0, (raw, wrapped)
     comm.destroy()
+
+
+def test_hccl_test_command_line_on_the_host_engine():
+    """The hccl_test-style tool prints one row per size with a passing result check."""
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    for op, extra in (("all_reduce", ["-o", "max", "-d", "int32"]), ("reduce_scatter", ["-d", "fp16"]), ("alltoall", ["-d", "int64"])):
+        r = subprocess.run([sys.executable, str(root / "bench" / "hccl_test.py"), "--op", op, "-b", "1K", "-e", "16K", "-f", "4", "-p", "3", "-n", "2", "-w", "1",
+                            "--host-sim", *extra], capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stdout + r.stderr
+        rows = [l.split() for l in r.stdout.splitlines() if l.strip() and not l.startswith("#") and not l.strip().startswith("data_size")]
+        assert [int(x[0]) for x in rows] == [1024, 4096, 16384], r.stdout
+        assert all(x[3] == "success" for x in rows), r.stdout
