@@ -95,3 +95,43 @@ def test_lookup_errors_resource_query_and_bad_pack():
         c.destroy()
     # a destroyed communicator leaves the registry
     assert lib.HcclGroupGetComm(b"pair", ctypes.byref(h)) == Result.E_NOT_FOUND
+
+
+@pytest.mark.gpu
+def test_twins_on_device_communicators():
+    """Two emulated ranks on one GPU, addressed by group name and issued on a side stream."""
+    import torch
+
+    comms = Communicator.emulated(2, hb.make_config(buffer_mib=8, name="emu_pair"))
+    group = b"emu_pair"
+    xs = [torch.full((4096,), float(r + 1), device="cuda") for r in range(2)]
+    ys = [torch.zeros(4096, device="cuda") for _ in range(2)]
+    stream = torch.cuda.Stream()
+    raw = ctypes.c_void_p(stream.cuda_stream)
+
+    def issue():
+        for r in range(2):
+            assert lib.HcclGroupBindThread(comms[r].handle) == 0
+            rc = lib.HcclAllReduceGraphMode(ctypes.c_void_p(xs[r].data_ptr()), ctypes.c_void_p(ys[r].data_ptr()), 4096, DataType.FP32, ReduceOp.SUM,
+                                            group, b"node_ar", None, raw)
+            assert rc == 0, Result(rc)
+
+    stream.wait_stream(torch.cuda.current_stream())      # the inputs were filled on the current stream
+    with torch.cuda.stream(stream):
+        issue()
+    stream.synchronize()
+    assert all(float(y[0]) == 3.0 and float(y[-1]) == 3.0 for y in ys)
+    res = HcclOpResource()
+    assert lib.HcclCalcOpResGraphMode(group, Cmd.ALLREDUCE, 4096, DataType.FP32, ReduceOp.SUM, ctypes.byref(res)) == 0
+    assert res.streams == 1 and res.launches == 1 and res.blocks >= 1
+    # a second issue of the same node reuses the cached plan
+    for r in range(2):
+        xs[r].fill_(10.0 * (r + 1))
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        issue()
+    stream.synchronize()
+    assert all(float(y[0]) == 30.0 for y in ys)
+    assert lib.HcclGroupUnbindThread(group) == 0
+    for c in comms:
+        c.destroy()
