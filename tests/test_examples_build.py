@@ -38,3 +38,12 @@ def test_example_plugin_builds_and_exports_its_entry(src, tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     syms = subprocess.run(["nm", "-D", "--defined-only", str(out)], capture_output=True, text=True).stdout
     assert "GetHcclAlgoPlugin" in syms or "HcclTunerPluginOpsGet" in syms, syms[-500:]
+
+
+def test_python_examples_and_benchmarks_compile():
+    import py_compile
+
+    scripts = sorted((ROOT / "examples").rglob("*.py")) + sorted((ROOT / "bench").glob("*.py")) + [ROOT / "bench.py"]
+    assert len(scripts) >= 10
+    for s in scripts:
+        py_compile.compile(str(s), doraise=True)
