@@ -263,7 +263,14 @@ bool OpMatches(const AlgEntry& a, const OpDesc& op, const TopoInfo& topo, std::s
     if (reduces) {
         if (op.redOp == HCCL_REDUCE_PROD && !t.supportProd) { *why = "op: PROD not supported"; return false; }
         if ((op.redOp == HCCL_REDUCE_MAX || op.redOp == HCCL_REDUCE_MIN) && !t.supportMaxMin) { *why = "op: MAX/MIN not supported"; return false; }
-        if (op.det == Deterministic::STRICT && !t.orderPreserved) { *why = "op: reduction order not fixed (HCCL_DETERMINISTIC=strict)"; return false; }
+        // The order of a reduction only shows in the result for floating-point SUM / PROD over more than two ranks
+        // (reference IsNeedStrictModeForOrderPreserved, order_preserved_common.h:104-114): integer and MAX / MIN
+        // reductions are exact in any order, and two values have one order.
+        const bool isFloat = op.dtype == HCCL_DATA_TYPE_FP16 || op.dtype == HCCL_DATA_TYPE_BFP16 || op.dtype == HCCL_DATA_TYPE_FP32 ||
+                             op.dtype == HCCL_DATA_TYPE_FP64 || op.dtype == HCCL_DATA_TYPE_FP8E4M3 || op.dtype == HCCL_DATA_TYPE_FP8E5M2 ||
+                             op.dtype == HCCL_DATA_TYPE_HIF8;
+        const bool orderShows = isFloat && (op.redOp == HCCL_REDUCE_SUM || op.redOp == HCCL_REDUCE_PROD) && op.nRanks > 2;
+        if (op.det == Deterministic::STRICT && orderShows && !t.orderPreserved) { *why = "op: reduction order not fixed (HCCL_DETERMINISTIC=strict)"; return false; }
         if (op.det == Deterministic::ON && !t.deterministic) { *why = "op: not run-to-run deterministic"; return false; }
     }
     if (op.inPlace && !t.supportInplace) { *why = "op: in-place not supported"; return false; }

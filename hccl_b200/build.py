@@ -5,7 +5,7 @@ Every ``.cu`` file is compiled by nvcc for sm_100a only
 g++; objects are cached under ``build/obj`` and rebuilt when the source or any
 header is newer.  Usage: ``python hccl_b200/build.py [--force] [--verbose] [--ptxas] [--asan]``.
 
-``--asan`` builds a second library, ``libhccl_b200_asan.so``, whose host code (every ``.cc`` file: API, selector,
+``--asan`` builds a second library, ``build/lib/libhccl_b200_asan.so``, whose host code (every ``.cc`` file: API, selector,
 bootstrap, host engine, verifier) is compiled with AddressSanitizer; the CUDA objects are shared with the normal
 build.  Load it with ``HCCL_B200_LIB=<path> LD_PRELOAD=$(gcc -print-file-name=libasan.so)`` (the interpreter itself
 is not instrumented, so the runtime has to come first), ``ASAN_OPTIONS=detect_leaks=0``.
@@ -53,7 +53,7 @@ def _newest_header() -> float:
 
 ASAN_FLAGS = ["-fsanitize=address", "-fno-omit-frame-pointer", "-O1"]
 OBJ_ASAN = ROOT / "build" / "obj_asan"
-LIB_ASAN = LIB_DIR / "libhccl_b200_asan.so"
+LIB_ASAN = ROOT / "build" / "lib" / "libhccl_b200_asan.so"      # beside the objects: a test artefact, not shipped
 
 
 def _compile(src: Path, verbose: bool, extra_flags=(), obj_dir: Path = None, cxx_extra=()):
@@ -104,6 +104,7 @@ def build_asan(verbose: bool = False) -> Path:
     """The AddressSanitizer variant: instrumented host objects + the CUDA objects of the normal build."""
     build(verbose=verbose)
     OBJ_ASAN.mkdir(parents=True, exist_ok=True)
+    LIB_ASAN.parent.mkdir(parents=True, exist_ok=True)
     cu, cc = _sources()
     hdr_time = _newest_header()
     todo, objs = [], []

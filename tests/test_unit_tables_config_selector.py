@@ -389,3 +389,26 @@ def test_diagnose_ring_keeps_operator_entries():
     finally:
         os.environ.pop("HCCL_DIAGNOSE_ENABLE", None)
         lib.HcclReloadEnvConfig()
+
+
+def test_strict_order_only_restricts_where_the_order_shows():
+    """HCCL_DETERMINISTIC=strict filters the algorithms whose fold order depends on the slicing only for floating-point
+    SUM / PROD over more than two ranks; integer sums, MAX / MIN and two-rank reductions keep every algorithm."""
+    import hccl_b200 as hb
+    from hccl_b200.types import ReduceOp
+
+    os.environ.pop("HCCL_ALGO", None)
+    lib.HcclReloadEnvConfig()
+    comms = Communicator.host_sim(4, None, hb.make_config(deterministic=2))
+    fp_sum = comms[0].explain(Cmd.ALLREDUCE, 1 << 20, DataType.FP32, ReduceOp.SUM)
+    assert "HostAllReduceSoleRing: filtered (op: reduction order not fixed" in fp_sum, fp_sum
+    assert fp_sum.startswith("selected HostAllReduceS"), fp_sum
+    for dt, rop in ((DataType.INT32, ReduceOp.SUM), (DataType.FP32, ReduceOp.MAX)):
+        txt = comms[0].explain(Cmd.ALLREDUCE, 1 << 20, dt, rop)
+        assert "reduction order not fixed" not in txt, txt
+    for c in comms:
+        c.destroy()
+    pair = Communicator.host_sim(2, None, hb.make_config(deterministic=2))
+    assert "reduction order not fixed" not in pair[0].explain(Cmd.ALLREDUCE, 1 << 20, DataType.FP32, ReduceOp.SUM)
+    for c in pair:
+        c.destroy()
