@@ -9,6 +9,7 @@
 #include "../select/auto_selector.h"
 #include "../select/selector.h"
 #include "hccl/hccl_ext.h"
+#include "ranktable.h"
 
 using namespace hccl;
 
@@ -75,6 +76,17 @@ HcclResult HcclDebugStepTable(const char* kind, uint32_t p, uint32_t rank, const
         if (!arg || sscanf(arg, "%d,%llu,%d,%d,%d", &op, &bytes, &host, &nvls, &strict) != 5) return HCCL_E_PARA;
         in.op = (HcclCMDType)op; in.bytes = bytes; in.nRanks = p; in.levels = rank; in.hostEngine = host; in.nvls = nvls; in.strictOrder = strict;
         os << ThresholdSelect(in) << "\n";
+    } else if (k == "rank_table") {
+        // arg = rank-table JSON text or a file path
+        RankTable t;
+        const HcclResult r = LoadRankTable(arg ? arg : "", &t);
+        if (r != HCCL_SUCCESS) os << "error: " << ResultString(r) << "\n";
+        else {
+            os << "ranks " << t.ranks.size() << " servers";
+            for (uint32_t n : t.serverSizes) os << " " << n;
+            os << " root " << t.rootIp << ":" << t.rootPort << " fingerprint " << t.Fingerprint() << "\n";
+            for (const RankTableEntry& e : t.ranks) os << "rank " << e.rankId << " server " << e.serverId << " device " << e.deviceId << " ip " << e.deviceIp << "\n";
+        }
     } else if (k == "fold") {
         for (auto& pr : DeterministicFoldOrder(p)) os << pr.first << "+=" << pr.second << "\n";
     } else if (k == "parse_algo") {

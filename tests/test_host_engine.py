@@ -316,3 +316,58 @@ def test_strict_order_is_batch_invariant(algo_env):
     destroy(comms)
     for r in range(n):
         assert rs_out[r].tobytes() == whole[r * m:(r + 1) * m].tobytes()
+
+
+def test_stress_mixed_operators_back_to_back(algo_env):
+    """Three hundred operators of random kind, size and root in a row on one communicator: notify counters, scratch
+    reuse and the rendezvous survive any succession, and every result is right."""
+    n = 4
+    rng = np.random.default_rng(123)
+    plan = [(rng.choice(["ar", "ag", "rs", "bc", "a2a", "red", "sc", "bar"]), int(rng.integers(1, 3000)), int(rng.integers(0, n))) for _ in range(300)]
+    for algo in (None, "level0:NA;level1:NHR"):
+        comms = make(n, algo=algo, buffer_mib=4)
+        fails = []
+
+        def body(r, c):
+            for i, (kind, count, root) in enumerate(plan):
+                base = np.arange(count, dtype=np.int64) * (r + 1) + i
+                if kind == "ar":
+                    out = np.zeros(count, np.int64)
+                    c.all_reduce(base, out)
+                    want = sum(np.arange(count, dtype=np.int64) * (q + 1) + i for q in range(n))
+                elif kind == "ag":
+                    out = np.zeros(count * n, np.int64)
+                    c.all_gather(base, out)
+                    want = np.concatenate([np.arange(count, dtype=np.int64) * (q + 1) + i for q in range(n)])
+                elif kind == "rs":
+                    src = np.arange(count * n, dtype=np.int64) * (r + 1) + i
+                    out = np.zeros(count, np.int64)
+                    c.reduce_scatter(src, out)
+                    want = sum(np.arange(count * n, dtype=np.int64) * (q + 1) + i for q in range(n))[r * count:(r + 1) * count]
+                elif kind == "bc":
+                    out = base.copy()
+                    c.broadcast(out, root)
+                    want = np.arange(count, dtype=np.int64) * (root + 1) + i
+                elif kind == "a2a":
+                    src = np.arange(count * n, dtype=np.int64) * (r + 1) + i
+                    out = np.zeros(count * n, np.int64)
+                    c.all_to_all(src, out)
+                    want = np.concatenate([(np.arange(count * n, dtype=np.int64) * (q + 1) + i)[r * count:(r + 1) * count] for q in range(n)])
+                elif kind == "red":
+                    out = np.zeros(count, np.int64)
+                    c.reduce(base, out if r == root else None, root)
+                    want = sum(np.arange(count, dtype=np.int64) * (q + 1) + i for q in range(n)) if r == root else out
+                elif kind == "sc":
+                    src = np.arange(count * n, dtype=np.int64) + i
+                    out = np.zeros(count, np.int64)
+                    c.scatter(src if r == root else None, out, root)
+                    want = src[r * count:(r + 1) * count]
+                else:
+                    c.barrier()
+                    continue
+                if not np.array_equal(out, want):
+                    fails.append((i, kind, count, root, r))
+
+        run_ranks(comms, body)
+        assert not fails, fails[:5]
+        destroy(comms)
