@@ -7,11 +7,12 @@
 #   ./build.sh -u | --ut       build, then the unit tier: step tables, config, selector, verifier self-tests, Python layers
 #   ./build.sh -s | --st       build, then the host-engine tier: every algorithm on simulated ranks with trace verification
 #   ./build.sh --gpu           build, then the device tier (needs a B200)
+#   ./build.sh --cov           coverage build of the host code, the unit and host-engine tiers against it, line coverage per file
 #   ./build.sh --pkg           build, then pack library + headers + Python package + examples into dist/hccl_b200-<version>.tar.gz
 set -euo pipefail
 cd "$(dirname "$0")"
 PY=${PYTHON:-python}
-force=""; asan=0; ut=0; st=0; gpu=0; pkg=0
+force=""; asan=0; ut=0; st=0; gpu=0; pkg=0; cov=0
 for a in "$@"; do
   case "$a" in
     --force) force="--force" ;;
@@ -20,7 +21,8 @@ for a in "$@"; do
     -s|--st) st=1 ;;
     --gpu) gpu=1 ;;
     --pkg) pkg=1 ;;
-    -h|--help) sed -n 2,12p "$0"; exit 0 ;;
+    --cov) cov=1 ;;
+    -h|--help) sed -n 2,13p "$0"; exit 0 ;;
     *) echo "unknown option $a" >&2; exit 2 ;;
   esac
 done
@@ -33,6 +35,14 @@ fi
 if [ $st -eq 1 ]; then
   $PY -m pytest -q -m "not gpu" tests/test_host_engine.py tests/test_host_executors.py tests/test_host_retry.py
   if [ $asan -eq 1 ]; then $PY -m pytest -q tests/test_asan_host_engine.py; fi
+fi
+if [ $cov -eq 1 ]; then
+  covlib=$($PY hccl_b200/build.py --cov | tail -1)
+  rm -f build/obj_cov/*.gcda
+  HCCL_B200_LIB=$covlib $PY -m pytest -q -m "not gpu" tests/test_unit_tables_config_selector.py tests/test_verifier_selftests.py \
+      tests/test_graph_mode_api.py tests/test_host_engine.py tests/test_host_executors.py tests/test_host_retry.py tests/test_rank_table.py \
+      tests/test_offline_bindings.py tests/test_context_parallel.py tests/test_data_parallel.py
+  $PY hccl_b200/build.py --cov-report
 fi
 if [ $gpu -eq 1 ]; then $PY -m pytest -q -m gpu tests; fi
 if [ $pkg -eq 1 ]; then

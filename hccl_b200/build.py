@@ -9,6 +9,8 @@ header is newer.  Usage: ``python hccl_b200/build.py [--force] [--verbose] [--pt
 bootstrap, host engine, verifier) is compiled with AddressSanitizer; the CUDA objects are shared with the normal
 build.  Load it with ``HCCL_B200_LIB=<path> LD_PRELOAD=$(gcc -print-file-name=libasan.so)`` (the interpreter itself
 is not instrumented, so the runtime has to come first), ``ASAN_OPTIONS=detect_leaks=0``.
+``--cov`` builds ``build/lib/libhccl_b200_cov.so`` with ``--coverage``; after running tests against it
+(``HCCL_B200_LIB=<path>``), ``--cov-report`` prints the line coverage of every host source.
 """
 from __future__ import annotations
 
@@ -100,36 +102,79 @@ def build(force: bool = False, verbose: bool = False, ptxas_verbose: bool = Fals
     return LIB
 
 
-def build_asan(verbose: bool = False) -> Path:
-    """The AddressSanitizer variant: instrumented host objects + the CUDA objects of the normal build."""
+def _build_variant(obj_dir: Path, lib: Path, cxx_extra, link_extra, verbose: bool) -> Path:
+    """A variant of the library whose host objects are compiled with extra flags; the CUDA objects are shared."""
     build(verbose=verbose)
-    OBJ_ASAN.mkdir(parents=True, exist_ok=True)
-    LIB_ASAN.parent.mkdir(parents=True, exist_ok=True)
+    obj_dir.mkdir(parents=True, exist_ok=True)
+    lib.parent.mkdir(parents=True, exist_ok=True)
     cu, cc = _sources()
     hdr_time = _newest_header()
     todo, objs = [], []
     for src in cu:
         objs.append(OBJ / (str(src.relative_to(CSRC)).replace("/", "__") + ".o"))
     for src in cc:
-        obj = OBJ_ASAN / (str(src.relative_to(CSRC)).replace("/", "__") + ".o")
+        obj = obj_dir / (str(src.relative_to(CSRC)).replace("/", "__") + ".o")
         objs.append(obj)
         if not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_time):
             todo.append(src)
     if todo:
         with concurrent.futures.ThreadPoolExecutor(min(len(todo), max(1, (os.cpu_count() or 4)))) as ex:
-            list(ex.map(lambda s: _compile(s, verbose, (), OBJ_ASAN, ASAN_FLAGS), todo))
-    if todo or not LIB_ASAN.exists():
-        cmd = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB_ASAN), *map(str, objs), "-Xcompiler", "-pthread",
-               "-Xcompiler", "-fsanitize=address", "-ldl", "-lrt"]
+            list(ex.map(lambda s: _compile(s, verbose, (), obj_dir, cxx_extra), todo))
+    if todo or not lib.exists():
+        cmd = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(lib), *map(str, objs), "-Xcompiler", "-pthread",
+               *link_extra, "-ldl", "-lrt"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
-            raise RuntimeError(f"linking the ASan library failed:\n{r.stdout}\n{r.stderr}")
-    return LIB_ASAN
+            raise RuntimeError(f"linking {lib.name} failed:\n{r.stdout}\n{r.stderr}")
+    return lib
+
+
+def build_asan(verbose: bool = False) -> Path:
+    """The AddressSanitizer variant: instrumented host objects + the CUDA objects of the normal build."""
+    return _build_variant(OBJ_ASAN, LIB_ASAN, ASAN_FLAGS, ["-Xcompiler", "-fsanitize=address"], verbose)
+
+
+OBJ_COV = ROOT / "build" / "obj_cov"
+LIB_COV = ROOT / "build" / "lib" / "libhccl_b200_cov.so"
+
+
+def build_cov(verbose: bool = False) -> Path:
+    """The coverage variant (gcc --coverage): run tests with HCCL_B200_LIB pointing at it, then `--cov-report`."""
+    return _build_variant(OBJ_COV, LIB_COV, ["--coverage", "-O0"], ["-Xcompiler", "--coverage"], verbose)
+
+
+def cov_report() -> str:
+    """Line coverage of the host sources from the counters the coverage build has written so far (gcov)."""
+    rows, total_lines, total_hit = [], 0, 0
+    for gcda in sorted(OBJ_COV.glob("*.gcda")):
+        r = subprocess.run(["gcov", "-n", "-o", str(OBJ_COV), str(gcda)], capture_output=True, text=True, cwd=OBJ_COV)
+        name, own = None, False
+        for line in r.stdout.splitlines():
+            if line.startswith("File '"):
+                name = line[6:-1]
+                own = name.startswith(str(CSRC)) and name.endswith(".cc")
+            elif own and line.startswith("Lines executed:"):
+                pct, of = line[len("Lines executed:"):].split("% of ")
+                n = int(of)
+                hit = round(float(pct) * n / 100.0)
+                rows.append((str(Path(name).relative_to(CSRC)), hit, n))
+                total_lines += n
+                total_hit += hit
+                own = False
+    out = [f"{100.0 * h / n:6.1f} %  {h:5d} / {n:5d}  {f}" for f, h, n in sorted(rows)]
+    out.append(f"{100.0 * total_hit / max(1, total_lines):6.1f} %  {total_hit:5d} / {total_lines:5d}  all host sources")
+    return "\n".join(out)
 
 
 if __name__ == "__main__":
     if "--asan" in sys.argv:
         print(build_asan(verbose="--verbose" in sys.argv))
+        sys.exit(0)
+    if "--cov" in sys.argv:
+        print(build_cov(verbose="--verbose" in sys.argv))
+        sys.exit(0)
+    if "--cov-report" in sys.argv:
+        print(cov_report())
         sys.exit(0)
     lib = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, ptxas_verbose="--ptxas" in sys.argv)
     print(lib)
