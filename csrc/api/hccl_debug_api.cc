@@ -3,6 +3,7 @@
 #include <map>
 #include <sstream>
 #include "../algo/step_tables.h"
+#include "../core/bootstrap.h"
 #include "../core/config.h"
 #include "../core/log.h"
 #include "../cpu/host_tree.h"
@@ -106,6 +107,49 @@ HcclResult HcclDebugStepTable(const char* kind, uint32_t p, uint32_t rank, const
         return HCCL_E_PARA;
     }
     snprintf(text, cap, "%s", os.str().c_str());
+    return HCCL_SUCCESS;
+}
+
+// ---- the bootstrap on its own (no device): connection, all-gather, barrier, agreement, failure paths
+HcclResult HcclDebugBootstrapConnect(const HcclRootInfo* info, uint32_t rank, uint32_t nRanks, uint32_t timeoutS, void** handle)
+{
+    CHK_PTR_NULL(info); CHK_PTR_NULL(handle);
+    auto* b = new Bootstrap();
+    const HcclResult r = b->Connect(*info, (int)rank, (int)nRanks, timeoutS);
+    if (r != HCCL_SUCCESS) { delete b; *handle = nullptr; return r; }
+    *handle = b;
+    return HCCL_SUCCESS;
+}
+HcclResult HcclDebugBootstrapAllGather(void* handle, const void* send, void* recv, uint64_t bytesPerRank)
+{
+    CHK_PTR_NULL(handle); CHK_PTR_NULL(send); CHK_PTR_NULL(recv);
+    return static_cast<Bootstrap*>(handle)->AllGather(send, recv, (size_t)bytesPerRank);
+}
+HcclResult HcclDebugBootstrapBarrier(void* handle)
+{
+    CHK_PTR_NULL(handle);
+    return static_cast<Bootstrap*>(handle)->Barrier();
+}
+HcclResult HcclDebugBootstrapAgree(void* handle, int ok, int* all)
+{
+    CHK_PTR_NULL(handle); CHK_PTR_NULL(all);
+    bool a = false;
+    const HcclResult r = static_cast<Bootstrap*>(handle)->AgreeAll(ok != 0, &a);
+    *all = a ? 1 : 0;
+    return r;
+}
+HcclResult HcclDebugBootstrapInjectFailure(void* handle)
+{
+    CHK_PTR_NULL(handle);
+    static_cast<Bootstrap*>(handle)->InjectFailureOnce();
+    return HCCL_SUCCESS;
+}
+HcclResult HcclDebugBootstrapClose(void* handle)
+{
+    CHK_PTR_NULL(handle);
+    Bootstrap* b = static_cast<Bootstrap*>(handle);
+    b->Close();
+    delete b;
     return HCCL_SUCCESS;
 }
 

@@ -69,6 +69,17 @@ typedef struct {
 HcclResult HcclCalcOpResource(HcclComm comm, HcclCMDType op, uint64_t count, HcclDataType dataType, HcclReduceOp reduceOp, int registered,
                               HcclOpResource* res);
 
+// The out-of-band bootstrap on its own, without a device (tests of the rendezvous and of its failure paths): connect
+// `rank` of `nRanks` to the endpoint in `info` (HcclGetRootInfo), then all-gather / barrier / agree (logical AND) over
+// the handle.  A rank that never connects makes the others' Connect return HCCL_E_TIMEOUT after timeoutS seconds; a
+// rank that closes makes the others' next call return HCCL_E_REMOTE.
+HcclResult HcclDebugBootstrapConnect(const HcclRootInfo* info, uint32_t rank, uint32_t nRanks, uint32_t timeoutS, void** handle);
+HcclResult HcclDebugBootstrapAllGather(void* handle, const void* send, void* recv, uint64_t bytesPerRank);
+HcclResult HcclDebugBootstrapBarrier(void* handle);
+HcclResult HcclDebugBootstrapAgree(void* handle, int ok, int* all);
+HcclResult HcclDebugBootstrapInjectFailure(void* handle);
+HcclResult HcclDebugBootstrapClose(void* handle);
+
 // Self-test entry of the trace verifier: checks a trace written as text (grammar beside the definition in
 // csrc/cpu/host_comm.cc) and writes the verifier's report ("OK: ..." or "FAILED: ..." with one line per finding).
 HcclResult HcclDebugVerifyTrace(const char* script, char* report, uint32_t capacity);
