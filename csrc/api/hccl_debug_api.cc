@@ -110,6 +110,42 @@ HcclResult HcclDebugStepTable(const char* kind, uint32_t p, uint32_t rank, const
     return HCCL_SUCCESS;
 }
 
+// Selection for a synthetic one-box NVSwitch topology (no device needed): what the selector would run for one call on
+// `nRanks` GPUs with or without switch reduction, on symmetric (registered != 0) or plain buffers, under a determinism
+// level (0 off, 1 on, 2 strict).  Same text as HcclSelectorExplain.
+HcclResult HcclDebugExplainDevice(uint32_t nRanks, int nvls, HcclCMDType op, uint64_t bytes, HcclDataType dt, HcclReduceOp rop, int registered,
+                                  int deterministic, char* text, uint32_t cap)
+{
+    CHK_PTR_NULL(text);
+    if (nRanks < 2 || nRanks > 8) return HCCL_E_PARA;
+    TopoInfo topo;
+    topo.nRanks = nRanks;
+    topo.rank = 0;
+    topo.serverOf.assign(nRanks, 0);
+    topo.podOf.assign(nRanks, 0);
+    topo.localOf.resize(nRanks);
+    for (uint32_t i = 0; i < nRanks; ++i) topo.localOf[i] = i;
+    topo.serverSizes = {nRanks};
+    topo.level0 = Level0Shape::MESH_1D;
+    topo.level0Link = LinkKind::NVLINK_SWITCH;
+    topo.nvls = nvls != 0;
+    topo.p2pAll = true;
+    topo.nvlinkCount = 18;
+    topo.linkGBs = GlobalLinkModel().p2pGBs;
+    topo.deviceName = "NVIDIA B200 (synthetic)";
+    OpDesc d;
+    d.op = op; d.dtype = dt; d.redOp = rop; d.nRanks = nRanks; d.bytes = bytes;
+    d.det = deterministic == 2 ? Deterministic::STRICT : deterministic == 1 ? Deterministic::ON : Deterministic::OFF;
+    d.inRegistered = d.outRegistered = registered != 0;
+    d.inMulticast = d.outMulticast = registered != 0 && nvls != 0;
+    SelectorState st;
+    Selection sel;
+    const HcclResult r = SelectAlgorithm(st, topo, GetEnvConfig(), d, "synthetic", nullptr, 256ull << 20, &sel);
+    const std::string s = (sel.alg ? "selected " + sel.alg->name + "\n" : std::string("selected none\n")) + FormatCostTable(sel);
+    snprintf(text, cap, "%s", s.c_str());
+    return r;
+}
+
 // ---- the bootstrap on its own (no device): connection, all-gather, barrier, agreement, failure paths
 HcclResult HcclDebugBootstrapConnect(const HcclRootInfo* info, uint32_t rank, uint32_t nRanks, uint32_t timeoutS, void** handle)
 {

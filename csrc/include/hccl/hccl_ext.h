@@ -69,6 +69,11 @@ typedef struct {
 HcclResult HcclCalcOpResource(HcclComm comm, HcclCMDType op, uint64_t count, HcclDataType dataType, HcclReduceOp reduceOp, int registered,
                               HcclOpResource* res);
 
+// Selection on a synthetic one-box NVSwitch topology, no device needed (regression tests of the device cost model):
+// the text of HcclSelectorExplain for `bytes` (as the selector counts them) on nRanks GPUs.  deterministic: 0, 1, 2 = strict.
+HcclResult HcclDebugExplainDevice(uint32_t nRanks, int nvls, HcclCMDType op, uint64_t bytes, HcclDataType dataType, HcclReduceOp reduceOp,
+                                  int registered, int deterministic, char* text, uint32_t capacity);
+
 // The out-of-band bootstrap on its own, without a device (tests of the rendezvous and of its failure paths): connect
 // `rank` of `nRanks` to the endpoint in `info` (HcclGetRootInfo), then all-gather / barrier / agree (logical AND) over
 // the handle.  A rank that never connects makes the others' Connect return HCCL_E_TIMEOUT after timeoutS seconds; a

@@ -412,3 +412,49 @@ def test_strict_order_only_restricts_where_the_order_shows():
     assert "reduction order not fixed" not in pair[0].explain(Cmd.ALLREDUCE, 1 << 20, DataType.FP32, ReduceOp.SUM)
     for c in pair:
         c.destroy()
+
+
+def _explain_device(n, nvls, op, nbytes, dt=DataType.BFP16, rop=0, registered=1, det=0):
+    lib.HcclDebugExplainDevice.restype = ctypes.c_int
+    lib.HcclDebugExplainDevice.argtypes = [ctypes.c_uint32, ctypes.c_int, ctypes.c_int, ctypes.c_uint64, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                           ctypes.c_int, ctypes.c_char_p, ctypes.c_uint32]
+    buf = ctypes.create_string_buffer(1 << 14)
+    rc = lib.HcclDebugExplainDevice(n, nvls, int(op), nbytes, int(dt), int(rop), registered, det, buf, len(buf))
+    assert rc == 0, rc
+    return buf.value.decode()
+
+
+def test_device_cost_model_on_a_synthetic_nvswitch_box():
+    """The device engines' selection for eight GPUs behind NVSwitch, without a device: flag-in-data forms for small
+    messages, the switch for large reductions and broadcasts, peer pulls for large gathers and exchanges; no switch
+    reduction under strict ordering or when the switch offers none."""
+    os.environ.pop("HCCL_ALGO", None)
+    os.environ.pop("HCCL_SELECTOR_MODE", None)
+    lib.HcclReloadEnvConfig()
+    K, M, G = 1 << 10, 1 << 20, 1 << 30
+    first = lambda *a, **k: _explain_device(*a, **k).splitlines()[0].replace("selected ", "")  # noqa: E731
+    assert first(8, 1, Cmd.ALLREDUCE, 1 * K) == "P2pAllReduceSoleMeshLL"
+    assert first(8, 1, Cmd.ALLREDUCE, 64 * K) == "P2pAllReduceSoleMeshLL"
+    assert first(8, 1, Cmd.ALLREDUCE, 16 * M) == "NvlsAllReduceSoleMesh"
+    assert first(8, 1, Cmd.ALLREDUCE, 1 * G) == "NvlsAllReduceSoleMesh"
+    assert first(8, 1, Cmd.ALLREDUCE, 16 * M, det=2) == "P2pAllReduceSoleMeshTwoShot"          # strict: fixed order, no switch reduction
+    assert "reduction order not fixed" in _explain_device(8, 1, Cmd.ALLREDUCE, 16 * M, det=2)
+    assert "reduction order not fixed" not in _explain_device(8, 1, Cmd.ALLREDUCE, 16 * M, dt=DataType.INT32, det=2)   # integers have no order to keep
+    assert first(8, 0, Cmd.ALLREDUCE, 16 * M) == "P2pAllReduceSoleMeshTwoShot"                 # a switch without reduction support
+    assert first(8, 1, Cmd.ALLGATHER, 1 * M) == "P2pAllGatherSoleMeshLL"
+    assert first(8, 1, Cmd.ALLGATHER, 1 * G) == "P2pAllGatherSoleMesh"
+    assert first(8, 1, Cmd.REDUCE_SCATTER, 1 * M) == "P2pReduceScatterSoleMeshLL"
+    assert first(8, 1, Cmd.REDUCE_SCATTER, 1 * G) == "NvlsReduceScatterSoleMesh"
+    assert first(8, 1, Cmd.BROADCAST, 1 * K) == "P2pBroadcastSoleMeshLL"
+    assert first(8, 1, Cmd.BROADCAST, 64 * M) == "NvlsBroadcastSoleMesh"
+    assert first(8, 1, Cmd.ALLTOALL, 1 * M) == "P2pAlltoAllSoleMeshLL"
+    assert first(8, 1, Cmd.ALLTOALL, 1 * G) == "P2pAlltoAllSoleMesh"
+    # the cost grows with the message and every viable row carries a cost
+    txt = _explain_device(8, 1, Cmd.ALLREDUCE, 16 * M)
+    costs = [float(l.split(": ")[1].split(" us")[0]) for l in txt.splitlines()[1:] if " us" in l]
+    assert len(costs) >= 3 and all(c > 0 for c in costs)
+    bigger = _explain_device(8, 1, Cmd.ALLREDUCE, 64 * M)
+    sel = lambda t: float([l for l in t.splitlines() if "<= selected" in l][0].split(": ")[1].split(" us")[0])  # noqa: E731
+    assert sel(bigger) > sel(txt)
+    # fp8 sums exist only for ReduceScatter; PROD has no switch form
+    assert "NvlsAllReduceSoleMesh: filtered" in _explain_device(8, 1, Cmd.ALLREDUCE, 16 * M, rop=int(ReduceOp.PROD), dt=DataType.FP32)
