@@ -135,3 +135,69 @@ class _Null:
 
     def __exit__(self, *a):
         return False
+
+
+class ShardedOptimizer:
+    """Sharded data parallelism on ReduceScatter + AllGather (the second DP form the reference's documents name,
+    docs/en/architecture-brief.md:16-17): every rank keeps the optimizer state of 1 / P of the parameters.
+
+    ``step()``: the gradients are packed into one flat buffer, ReduceScatter leaves every rank with the sum of its
+    shard, the inner optimizer (built by ``optimizer_factory`` over ONE flat shard parameter) updates that shard, and
+    AllGather hands every rank the updated parameters.  All parameters must share dtype and device.  The flat buffer
+    is padded to a multiple of the world size; the padding is never read back.
+    """
+
+    def __init__(self, params: Iterable[torch.nn.Parameter], comm, optimizer_factory, average: bool = True):
+        self.comm = comm
+        self.average = average
+        self.params = [p for p in params if p.requires_grad]
+        if not self.params:
+            raise ValueError("ShardedOptimizer: no trainable parameters")
+        dt, dev = self.params[0].dtype, self.params[0].device
+        if any(p.dtype != dt or p.device != dev for p in self.params):
+            raise ValueError("ShardedOptimizer: parameters must share dtype and device")
+        P = comm.world_size
+        total = sum(p.numel() for p in self.params)
+        self.shard_len = (total + P - 1) // P
+        self.flat_grad = torch.zeros(self.shard_len * P, dtype=dt, device=dev)
+        self.flat_param = torch.zeros(self.shard_len * P, dtype=dt, device=dev)
+        self._pack(self.flat_param, [p.detach() for p in self.params])
+        r = comm.rank
+        self.shard = torch.nn.Parameter(self.flat_param[r * self.shard_len:(r + 1) * self.shard_len].clone())
+        self.shard.grad = torch.zeros_like(self.shard)
+        self.optimizer = optimizer_factory([self.shard])
+
+    def _pack(self, flat, tensors):
+        off = 0
+        for t in tensors:
+            n = t.numel()
+            flat[off:off + n].copy_(t.reshape(-1))
+            off += n
+
+    @torch.no_grad()
+    def step(self):
+        off = 0
+        for p in self.params:
+            n = p.numel()
+            if p.grad is None:
+                self.flat_grad[off:off + n].zero_()
+            else:
+                self.flat_grad[off:off + n].copy_(p.grad.reshape(-1))
+            off += n
+        self.comm.reduce_scatter(self.flat_grad, self.shard.grad)
+        if self.average:
+            self.shard.grad.mul_(1.0 / self.comm.world_size)
+        self.optimizer.step()
+        self.comm.all_gather(self.shard.detach(), self.flat_param)
+        off = 0
+        for p in self.params:
+            n = p.numel()
+            p.copy_(self.flat_param[off:off + n].reshape(p.shape))
+            off += n
+
+    def zero_grad(self, set_to_none: bool = True):
+        for p in self.params:
+            if set_to_none:
+                p.grad = None
+            elif p.grad is not None:
+                p.grad.zero_()

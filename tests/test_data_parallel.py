@@ -67,3 +67,46 @@ def test_unused_parameter_contributes_zeros():
         assert torch.all(ps[r][0].grad == 1.5) and torch.all(ps[r][1].grad == 0)
     for c in comms:
         c.destroy()
+
+
+def test_sharded_optimizer_matches_replicated_training():
+    """ReduceScatter + shard update + AllGather gives the same parameters as averaging the gradients and running the
+    same optimizer on the whole model."""
+    from hccl_b200.parallel import ShardedOptimizer
+
+    n, steps = 3, 4
+    base = make_model()
+    xs = [[torch.randn(8, 16, generator=torch.Generator().manual_seed(100 * s + r)) for r in range(n)] for s in range(steps)]
+    # the replicated reference
+    ref = copy.deepcopy(base)
+    ref_opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.01)
+    for s in range(steps):
+        grads = [torch.zeros_like(p) for p in ref.parameters()]
+        for r in range(n):
+            m = copy.deepcopy(ref)
+            m(xs[s][r]).pow(2).mean().backward()
+            for g, p in zip(grads, m.parameters()):
+                g += p.grad / n
+        for p, g in zip(ref.parameters(), grads):
+            p.grad = g
+        ref_opt.step()
+    models = [copy.deepcopy(base) for _ in range(n)]
+    comms = Communicator.host_sim(n, None, hb.make_config(buffer_mib=8, exec_timeout_ms=20000))
+    shard_sizes = [None] * n
+
+    def body(r, c):
+        opt = ShardedOptimizer(models[r].parameters(), c, lambda ps: torch.optim.AdamW(ps, lr=1e-2, weight_decay=0.01))
+        shard_sizes[r] = opt.shard.numel()
+        for s in range(steps):
+            opt.zero_grad()
+            models[r](xs[s][r]).pow(2).mean().backward()
+            opt.step()
+
+    run_ranks(comms, body)
+    total = sum(p.numel() for p in base.parameters())
+    assert shard_sizes[0] == (total + n - 1) // n            # each rank holds optimizer state for a third of the model
+    for m in models:
+        for p, q in zip(m.parameters(), ref.parameters()):
+            torch.testing.assert_close(p, q, rtol=1e-4, atol=1e-5)
+    for c in comms:
+        c.destroy()
