@@ -392,6 +392,47 @@ HcclResult HcclTestHostRecoveries(HcclComm comm, uint64_t* count)
     return HCCL_SUCCESS;
 }
 
+// Topology self-test entry: the model a topology literal gives `rank`, the groups of the requested match
+// (0 one level, 1 two levels, 2 three levels), and the serialisation guards (a round trip restores the model, a
+// damaged or truncated blob is refused).
+HcclResult HcclDebugTopo(const char* topoJson, uint32_t nRanks, uint32_t rank, int matchKind, char* text, uint32_t capacity)
+{
+    CHK_PTR_NULL(text);
+    TopoMeta meta;
+    std::string err;
+    if (nRanks == 0 || rank >= nRanks || matchKind < 0 || matchKind > 2) return HCCL_E_PARA;
+    if (!ParseTopoMeta(topoJson, nRanks, &meta, &err)) { snprintf(text, capacity, "error: %s", err.c_str()); return HCCL_SUCCESS; }
+    TopoInfo t;
+    CHK_RET(BuildTopoFromMeta(meta, rank, &t));
+    std::ostringstream os;
+    os << t.Summary() << "\n";
+    os << "server " << t.serverOf[rank] << " pod " << t.podOf[rank] << " local " << t.localOf[rank] << " symmetric " << t.symmetric << " level1Nhr " << t.level1Nhr << "\n";
+    AlgHierarchy h;
+    const HcclResult mr = MatchTopo(t, (TopoMatchKind)matchKind, &h);
+    if (mr != HCCL_SUCCESS) os << "match: " << ResultString(mr) << "\n";
+    else {
+        for (uint32_t l = 0; l < h.levels(); ++l) {
+            os << "level " << l << ":";
+            for (auto& g : h.infos[l]) {
+                os << " [";
+                for (size_t i = 0; i < g.size(); ++i) os << (i ? "," : "") << g[i];
+                os << "]";
+            }
+            os << "\n";
+        }
+    }
+    std::vector<uint8_t> blob = t.Serialize();
+    TopoInfo back;
+    const bool ok = TopoInfo::Deserialize(blob, &back) && back.nRanks == t.nRanks && back.serverOf == t.serverOf && back.localOf == t.localOf && back.symmetric == t.symmetric;
+    std::vector<uint8_t> bad = blob;
+    bad[bad.size() / 2] ^= 0x5A;
+    std::vector<uint8_t> cut(blob.begin(), blob.begin() + (long)(blob.size() / 2));
+    TopoInfo junk;
+    os << "roundtrip " << ok << " damaged " << TopoInfo::Deserialize(bad, &junk) << " truncated " << TopoInfo::Deserialize(cut, &junk) << "\n";
+    snprintf(text, capacity, "%s", os.str().c_str());
+    return HCCL_SUCCESS;
+}
+
 // Verifier self-test entry: checks a trace written as text.  First line "ranks <n> op <allreduce|allgather|
 // reducescatter|reduce|scatter|alltoall> count <elements> [root <r>]" (fp32, sum); then one task per line:
 //   <rank> <queue> copy|reduce <dstRank>:<in|out|scr>:<byteOffset> <srcRank>:<in|out|scr>:<byteOffset> <bytes>

@@ -85,6 +85,11 @@ HcclResult HcclDebugBootstrapAgree(void* handle, int ok, int* all);
 HcclResult HcclDebugBootstrapInjectFailure(void* handle);
 HcclResult HcclDebugBootstrapClose(void* handle);
 
+// Self-test entry of the topology model: what the literal `topoJson` ([[[devices of a server], ...] per pod]; NULL =
+// one server) gives `rank`, the groups of a one / two / three level match (matchKind 0 / 1 / 2), and whether the
+// serialised model survives a round trip while a damaged or truncated blob is refused.
+HcclResult HcclDebugTopo(const char* topoJson, uint32_t nRanks, uint32_t rank, int matchKind, char* text, uint32_t capacity);
+
 // Self-test entry of the trace verifier: checks a trace written as text (grammar beside the definition in
 // csrc/cpu/host_comm.cc) and writes the verifier's report ("OK: ..." or "FAILED: ..." with one line per finding).
 HcclResult HcclDebugVerifyTrace(const char* script, char* report, uint32_t capacity);
