@@ -6,6 +6,7 @@
 #include "../core/bootstrap.h"
 #include "../core/config.h"
 #include "../core/log.h"
+#include "../core/plan_cache.h"
 #include "../cpu/host_tree.h"
 #include "../select/auto_selector.h"
 #include "../select/selector.h"
@@ -88,6 +89,25 @@ HcclResult HcclDebugStepTable(const char* kind, uint32_t p, uint32_t rank, const
             os << " root " << t.rootIp << ":" << t.rootPort << " fingerprint " << t.Fingerprint() << "\n";
             for (const RankTableEntry& e : t.ranks) os << "rank " << e.rankId << " server " << e.serverId << " device " << e.deviceId << " ip " << e.deviceIp << "\n";
         }
+    } else if (k == "plan_cache") {
+        // p = keys to insert (bytes = 1..p); key 1 is looked up again after every 1000 inserts, so it stays recent.
+        // Reports the size, whether key 1 / key 2 / the newest key are present, and a lookup under another generation.
+        PlanCache cache;
+        Plan plan;
+        for (uint32_t i = 1; i <= p; ++i) {
+            PlanKey key{2, 4, 0, 0, i, 0, 7};
+            plan.algIndex = (int)i;
+            cache.Insert(key, plan);
+            if (i % 1000 == 0) { PlanKey first{2, 4, 0, 0, 1, 0, 7}; cache.Find(first, &plan); }
+        }
+        Plan got;
+        const bool has1 = cache.Find(PlanKey{2, 4, 0, 0, 1, 0, 7}, &got);
+        const bool has2 = cache.Find(PlanKey{2, 4, 0, 0, 2, 0, 7}, &got);
+        const bool hasLast = cache.Find(PlanKey{2, 4, 0, 0, p, 0, 7}, &got);
+        const int lastAlg = hasLast ? got.algIndex : -1;
+        const bool otherGen = cache.Find(PlanKey{2, 4, 0, 0, p, 0, 8}, &got);
+        os << "capacity " << PlanCache::kCapacity << " size " << cache.size() << " key1 " << has1 << " key2 " << has2 << " newest " << hasLast << " alg " << lastAlg
+           << " other_generation " << otherGen << " hits " << cache.hits() << " misses " << cache.misses() << "\n";
     } else if (k == "fold") {
         for (auto& pr : DeterministicFoldOrder(p)) os << pr.first << "+=" << pr.second << "\n";
     } else if (k == "parse_algo") {

@@ -458,3 +458,24 @@ def test_device_cost_model_on_a_synthetic_nvswitch_box():
     assert sel(bigger) > sel(txt)
     # fp8 sums exist only for ReduceScatter; PROD has no switch form
     assert "NvlsAllReduceSoleMesh: filtered" in _explain_device(8, 1, Cmd.ALLREDUCE, 16 * M, rop=int(ReduceOp.PROD), dt=DataType.FP32)
+
+
+def test_plan_cache_capacity_eviction_and_generation():
+    """8192 entries; a full cache drops its least recently used fifth; a recently used entry survives; a communicator
+    generation bump (resume) makes every cached plan miss."""
+    def run(n):
+        buf = ctypes.create_string_buffer(512)
+        assert lib.HcclDebugStepTable(b"plan_cache", n, 0, None, buf, 512) == 0
+        f = buf.value.decode().split()
+        return {f[i]: int(f[i + 1]) for i in range(0, len(f), 2)}
+
+    full = run(8192)
+    assert full["capacity"] == 8192 and full["size"] == 8192 and full["key1"] == 1 and full["key2"] == 1 and full["newest"] == 1
+    assert full["alg"] == 8192 and full["other_generation"] == 0
+    over = run(8193)                                   # one insert too many: a fifth goes, the new one comes in
+    assert 8192 * 0.79 <= over["size"] <= 8192 * 0.81 + 1, over
+    assert over["key1"] == 1                           # looked up every 1000 inserts: recent
+    assert over["key2"] == 0                           # never looked up again: among the oldest
+    assert over["newest"] == 1 and over["alg"] == 8193
+    many = run(30000)
+    assert many["size"] <= 8192 and many["key1"] == 1 and many["newest"] == 1
