@@ -456,6 +456,10 @@ def test_device_cost_model_on_a_synthetic_nvswitch_box():
     bigger = _explain_device(8, 1, Cmd.ALLREDUCE, 64 * M)
     sel = lambda t: float([l for l in t.splitlines() if "<= selected" in l][0].split(": ")[1].split(" us")[0])  # noqa: E731
     assert sel(bigger) > sel(txt)
+    # plain buffers pay for the staging copy that symmetric (registered) buffers avoid
+    row = lambda t, name: float([l for l in t.splitlines() if l.strip().startswith(name + ":")][0].split(": ")[1].split(" us")[0])  # noqa: E731
+    for op, name in ((Cmd.ALLGATHER, "P2pAllGatherSoleMesh"), (Cmd.REDUCE_SCATTER, "P2pReduceScatterSoleMesh")):
+        assert row(_explain_device(8, 1, op, 1 * G, registered=1), name) < row(_explain_device(8, 1, op, 1 * G, registered=0), name)
     # fp8 sums exist only for ReduceScatter; PROD has no switch form
     assert "NvlsAllReduceSoleMesh: filtered" in _explain_device(8, 1, Cmd.ALLREDUCE, 16 * M, rop=int(ReduceOp.PROD), dt=DataType.FP32)
 
