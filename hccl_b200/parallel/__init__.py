@@ -2,3 +2,4 @@
 from .tp_layers import ColumnParallelLinear, RowParallelLinear, TPContext  # noqa: F401
 from .context_parallel import ring_attention, ulysses_attention  # noqa: F401
 from .data_parallel import GradientBucketer, ShardedOptimizer  # noqa: F401
+from .expert_parallel import moe_forward  # noqa: F401
