@@ -3,3 +3,4 @@ from .tp_layers import ColumnParallelLinear, RowParallelLinear, TPContext  # noq
 from .context_parallel import ring_attention, ulysses_attention  # noqa: F401
 from .data_parallel import GradientBucketer, ShardedOptimizer  # noqa: F401
 from .expert_parallel import moe_forward  # noqa: F401
+from .pipeline_parallel import gpipe_step  # noqa: F401
