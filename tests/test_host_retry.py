@@ -29,7 +29,7 @@ def retry_env():
     lib.HcclReloadEnvConfig()
 
 
-def make(n, enable, params=None, timeout_ms=400):
+def make(n, enable, params=None, timeout_ms=800):
     os.environ.pop("HCCL_ALGO", None)
     os.environ["HCCL_OP_RETRY_ENABLE"] = enable
     if params:
@@ -68,7 +68,7 @@ def test_dropped_notify_is_retried_and_the_result_is_right(retry_env):
 
 def test_retry_gives_up_after_max_count(retry_env):
     n = 3
-    comms = make(n, "L1:1", "MaxCnt:1,HoldTime:0,IntervalTime:0", timeout_ms=200)
+    comms = make(n, "L1:1", "MaxCnt:1,HoldTime:0,IntervalTime:0", timeout_ms=600)
     ins = [np.ones(64, np.float32) for _ in range(n)]
     outs = [np.zeros(64, np.float32) for _ in range(n)]
     assert lib.HcclTestHostDropPosts(comms[0]._h, 1000) == 0      # every attempt loses its messages
@@ -90,7 +90,7 @@ def test_retry_gives_up_after_max_count(retry_env):
 def test_without_retry_or_in_place_the_failure_is_reported(retry_env):
     n = 3
     for enable, in_place in (("L1:0", False), ("L1:1", True)):
-        comms = make(n, enable, timeout_ms=200)
+        comms = make(n, enable, timeout_ms=600)
         ins = [np.ones(64, np.float32) for _ in range(n)]
         outs = [np.zeros(64, np.float32) for _ in range(n)]
         assert lib.HcclTestHostDropPosts(comms[1]._h, 1) == 0
