@@ -27,7 +27,11 @@
 namespace hccl {
 namespace hosttpl {
 
-void Slice(const Work& wk, uint32_t parts, uint32_t i, uint64_t* b, uint64_t* e) { SliceOf(wk.count, parts, i, b, e); }
+void Slice(const Work& wk, uint32_t parts, uint32_t i, uint64_t* b, uint64_t* e)
+{
+    if (wk.vBegin) { *b = wk.vBegin[i]; *e = wk.vBegin[i] + wk.vCount[i]; return; }
+    SliceOf(wk.count, parts, i, b, e);
+}
 
 // ---------------------------------------------------------------- mesh
 // ReduceScatter over a full mesh: every member reads slice `me` from every other member's W and folds it in.
@@ -80,9 +84,12 @@ void RingReduceScatter(Ctx& c, const Group& g, const Work& wk)
     const uint32_t p = g.size();
     if (p == 1) return;
     const uint32_t me = g.world(g.me), right = g.world((g.me + 1) % p), left = g.world((g.me + p - 1) % p);
-    uint64_t b0, e0;
-    Slice(wk, p, 0, &b0, &e0);
-    const uint64_t slot = (e0 - b0) * wk.es;     // largest slice
+    uint64_t slot = 0;                           // largest slice
+    for (uint32_t i = 0; i < p; ++i) {
+        uint64_t b0, e0;
+        Slice(wk, p, i, &b0, &e0);
+        slot = std::max(slot, (e0 - b0) * wk.es);
+    }
     uint32_t step = 0;
     for (const RingStep& s : RingReduceScatterSteps(p, g.me)) {
         uint64_t sb, se, rb, re;
@@ -422,8 +429,25 @@ HcclResult RunHostAlgorithm(HostWorld& w, uint32_t rank, int alg, const OpParam&
             // work on a scratch copy of the whole input so that the user's send buffer stays intact; layout of W:
             // rank i's block at i * blockElems (V: at its displacement)
             const bool v = p.op == HCCL_CMD_REDUCE_SCATTER_V;
+            if (v && alg != HALG_RS_MESH) {
+                // variable blocks through ring / RHD / NHR: the whole input is mirrored into scratch and the templates cut
+                // it at the callers' displacements
+                uint64_t extent = 0;
+                for (uint32_t j = 0; j < n; ++j) extent = std::max(extent, p.sdispls[j] + p.sendCounts[j]);
+                const uint64_t wOff = w.scratchBytes() / 2;
+                if (extent * es > w.scratchBytes() / 2) { HCCL_ERROR("host engine: ReduceScatterV of %llu bytes needs a larger scratch buffer", (unsigned long long)(extent * es)); return HCCL_E_MEMORY; }
+                x.Copy(Scratch(rank, wOff), In(rank), extent * es);
+                Work wk{BufKind::SCRATCH, wOff, extent, es};
+                wk.vBegin = p.sdispls.data();
+                wk.vCount = p.sendCounts.data();
+                Ctx cc{w, x, 0, 0, w.scratchBytes() / 2};
+                ReduceScatterBy(alg == HALG_RS_RING ? Fam::RING : alg == HALG_RS_RHD ? Fam::RHD : Fam::NHR, cc, all, wk);
+                x.Copy(Out(rank), Scratch(rank, wOff + p.sdispls[rank] * es), p.sendCounts[rank] * es);
+                x.SyncGroup(all.ranks, N_LEVEL);
+                break;
+            }
             if (v) {
-                // variable blocks: mesh only (each member reduces its own block from every peer's INPUT)
+                // variable blocks over the mesh: each member reduces its own block from every peer's INPUT
                 x.SyncGroup(all.ranks, N_READY);
                 x.Copy(Out(rank), In(rank, p.sdispls[rank] * es), p.sendCounts[rank] * es);
                 for (uint32_t k = 1; k < n; ++k) {
@@ -472,6 +496,17 @@ HcclResult RunHostAlgorithm(HostWorld& w, uint32_t rank, int alg, const OpParam&
         // ------------------------------------------------------------ AllGather (+V)
         case HALG_AG_MESH: case HALG_AG_RING: case HALG_AG_RHD: case HALG_AG_NHR: case HALG_AG_SEQ_MESH_NHR: {
             const bool v = p.op == HCCL_CMD_ALLGATHER_V;
+            if (v && alg != HALG_AG_MESH) {
+                // variable blocks through ring / RHD / NHR, in place in the output at the callers' displacements
+                uint64_t extent = 0;
+                for (uint32_t j = 0; j < n; ++j) extent = std::max(extent, p.rdispls[j] + p.recvCounts[j]);
+                x.Copy(Out(rank, p.rdispls[rank] * es), In(rank), p.recvCounts[rank] * es);
+                Work wk{BufKind::OUTPUT, 0, extent, es};
+                wk.vBegin = p.rdispls.data();
+                wk.vCount = p.recvCounts.data();
+                AllGatherBy(alg == HALG_AG_RING ? Fam::RING : alg == HALG_AG_RHD ? Fam::RHD : Fam::NHR, c, all, wk);
+                break;
+            }
             if (v) {
                 x.Copy(Out(rank, p.rdispls[rank] * es), In(rank), p.count * es);
                 x.SyncGroup(all.ranks, N_READY);

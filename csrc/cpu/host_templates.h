@@ -31,6 +31,10 @@ struct Work {
     uint64_t base;      // byte offset of the region inside the buffer
     uint64_t count;     // elements in the region
     uint32_t es;
+    // Variable slices (the V operators): slice i of a flat group is [vBegin[i], vBegin[i] + vCount[i]) in elements
+    // instead of an equal share of `count`.  Null for the regular operators.
+    const uint64_t* vBegin = nullptr;
+    const uint64_t* vCount = nullptr;
     Mem At(uint32_t worldRank, uint64_t elemOff) const { return Mem{worldRank, buf, base + elemOff * es}; }
 };
 

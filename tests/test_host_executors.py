@@ -334,3 +334,35 @@ def test_servers_of_different_sizes_fall_back_to_flat_algorithms(algo_env):
     for r in range(n):
         np.testing.assert_allclose(rs_out[r], ref[r * 16:(r + 1) * 16], rtol=2e-6, atol=2e-5)
     destroy(comms)
+
+
+@pytest.mark.parametrize("n", [2, 3, 5, 8])
+@pytest.mark.parametrize("key,tag", [("level0:NA;level1:ring", "Ring"), ("level0:NA;level1:NHR", "NHR"), ("level0:NA;level1:H-D_R", "RHD"),
+                                     ("level0:NA;level1:fullmesh", "Mesh")])
+def test_v_operators_on_every_template(algo_env, n, key, tag):
+    """AllGatherV and ReduceScatterV with unequal, gapped and empty blocks through ring, NHR, RHD and mesh."""
+    comms = make(n, algo=key)
+    counts = [(3 * r + 1) % 5 * 7 for r in range(n)]              # some blocks are empty
+    if sum(counts) == 0:
+        counts[0] = 4
+    displs = [sum(counts[:r]) + 3 * r for r in range(n)]          # gaps between the blocks
+    total = displs[-1] + counts[-1]
+    ins = [np.full(counts[r], r + 1, np.float32) for r in range(n)]
+    outs = [np.full(total, -1, np.float32) for _ in range(n)]
+    verified(comms, lambda r, c: c.all_gather_v(ins[r], outs[r], counts, displs))
+    assert comms[0].last_algorithm() == f"HostAllGatherVSole{tag}", comms[0].last_algorithm()
+    for o in outs:
+        for r in range(n):
+            assert np.all(o[displs[r]:displs[r] + counts[r]] == r + 1)
+        gaps = np.ones(total, bool)
+        for r in range(n):
+            gaps[displs[r]:displs[r] + counts[r]] = False
+        assert np.all(o[gaps] == -1)                              # nothing written between the blocks
+    sends = [np.random.default_rng(r).integers(-20, 20, total).astype(np.int64) for r in range(n)]
+    recvs = [np.zeros(counts[r], np.int64) for r in range(n)]
+    verified(comms, lambda r, c: c.reduce_scatter_v(sends[r], recvs[r], counts, displs))
+    assert comms[0].last_algorithm() == f"HostReduceScatterVSole{tag}", comms[0].last_algorithm()
+    ref = np.sum(np.stack(sends), 0)
+    for r in range(n):
+        assert np.array_equal(recvs[r], ref[displs[r]:displs[r] + counts[r]])
+    destroy(comms)
