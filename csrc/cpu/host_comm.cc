@@ -326,9 +326,13 @@ void RegisterHostAlgorithms()
     Reg({"HostBroadcastSoleMeshOneShot", HCCL_CMD_BROADCAST, HALG_BCAST_MESH_ONESHOT, "sole", {"MeshOneShot"}, AlgoType::ONESHOT, 1, false, Two, full, true});
     Reg({"HostBroadcastSoleMeshTwoShot", HCCL_CMD_BROADCAST, HALG_BCAST_MESH_TWOSHOT, "sole", {"MeshTwoShot"}, AlgoType::MESH, 1, false, Three, ar, true});
     Reg({"HostBroadcastSoleNHR", HCCL_CMD_BROADCAST, HALG_BCAST_NHR, "sole", {"NHR"}, AlgoType::NHR, 1, false, L, ar, true});
+    Reg({"HostBroadcastSoleRing", HCCL_CMD_BROADCAST, HALG_BCAST_RING, "sole", {"Ring"}, AlgoType::RING, 1, false, P1, ar, true});
+    Reg({"HostBroadcastSoleRHD", HCCL_CMD_BROADCAST, HALG_BCAST_RHD, "sole", {"RHD"}, AlgoType::HD_R, 1, false, L, ar, true});
     Reg({"HostReduceSoleMeshOneShot", HCCL_CMD_REDUCE, HALG_REDUCE_MESH_ONESHOT, "sole", {"MeshOneShot"}, AlgoType::ONESHOT, 1, true, Two, full, true});
     Reg({"HostReduceSoleMeshTwoShot", HCCL_CMD_REDUCE, HALG_REDUCE_MESH_TWOSHOT, "sole", {"MeshTwoShot"}, AlgoType::MESH, 1, true, Three, ar, false});
     Reg({"HostReduceSoleNHR", HCCL_CMD_REDUCE, HALG_REDUCE_NHR, "sole", {"NHR"}, AlgoType::NHR, 1, true, L, ar, false});
+    Reg({"HostReduceSoleRing", HCCL_CMD_REDUCE, HALG_REDUCE_RING, "sole", {"Ring"}, AlgoType::RING, 1, true, P1, ar, false});
+    Reg({"HostReduceSoleRHD", HCCL_CMD_REDUCE, HALG_REDUCE_RHD, "sole", {"RHD"}, AlgoType::HD_R, 1, true, L, ar, false});
     Reg({"HostScatterSoleMesh", HCCL_CMD_SCATTER, HALG_SCATTER_MESH, "sole", {"Mesh"}, AlgoType::MESH, 1, false, Two, rs, true});
     Reg({"HostScatterSoleRing", HCCL_CMD_SCATTER, HALG_SCATTER_RING, "sole", {"Ring"}, AlgoType::RING, 1, false, P1, one, true});
     // AlltoAll family

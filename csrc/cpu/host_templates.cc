@@ -544,7 +544,7 @@ HcclResult RunHostAlgorithm(HostWorld& w, uint32_t rank, int alg, const OpParam&
             x.SyncGroup(all.ranks, N_DONE);
             break;
         }
-        case HALG_BCAST_MESH_TWOSHOT: case HALG_BCAST_NHR: {
+        case HALG_BCAST_MESH_TWOSHOT: case HALG_BCAST_NHR: case HALG_BCAST_RING: case HALG_BCAST_RHD: {
             // scatter from the root (member i takes slice i), then AllGather
             Work wk{BufKind::OUTPUT, 0, p.count, es};
             x.SyncGroup(all.ranks, N_READY);
@@ -554,7 +554,7 @@ HcclResult RunHostAlgorithm(HostWorld& w, uint32_t rank, int alg, const OpParam&
                 x.Copy(Out(rank, b * es), Out(p.root, b * es), (e - b) * es);
             }
             x.SyncGroup(all.ranks, N_DATA);
-            AllGatherBy(alg == HALG_BCAST_NHR ? Fam::NHR : Fam::MESH, c, all, wk);
+            AllGatherBy(alg == HALG_BCAST_NHR ? Fam::NHR : alg == HALG_BCAST_RING ? Fam::RING : alg == HALG_BCAST_RHD ? Fam::RHD : Fam::MESH, c, all, wk);
             break;
         }
         // ------------------------------------------------------------ Reduce
@@ -567,13 +567,13 @@ HcclResult RunHostAlgorithm(HostWorld& w, uint32_t rank, int alg, const OpParam&
             x.SyncGroup(all.ranks, N_DONE);
             break;
         }
-        case HALG_REDUCE_MESH_TWOSHOT: case HALG_REDUCE_NHR: {
+        case HALG_REDUCE_MESH_TWOSHOT: case HALG_REDUCE_NHR: case HALG_REDUCE_RING: case HALG_REDUCE_RHD: {
             // ReduceScatter on a scratch copy, then the root collects the slices
             const uint64_t wOff = w.scratchBytes() / 2;
             x.Copy(Scratch(rank, wOff), In(rank), Bytes(p));
             Work wk{BufKind::SCRATCH, wOff, p.count, es};
             Ctx cc{w, x, 0, 0, w.scratchBytes() / 2};
-            ReduceScatterBy(alg == HALG_REDUCE_NHR ? Fam::NHR : Fam::MESH, cc, all, wk);
+            ReduceScatterBy(alg == HALG_REDUCE_NHR ? Fam::NHR : alg == HALG_REDUCE_RING ? Fam::RING : alg == HALG_REDUCE_RHD ? Fam::RHD : Fam::MESH, cc, all, wk);
             x.SyncGroup(all.ranks, N_LEVEL);
             if (rank == p.root) {
                 for (uint32_t j = 0; j < n; ++j) {

@@ -188,6 +188,7 @@ enum HostAlg : int {
     HALG_A2A_HIER,
     HALG_BCAST_SEQ_MESH_NHR, HALG_REDUCE_SEQ_MESH_NHR, HALG_SCATTER_SEQ_MESH_MESH, HALG_BARRIER_SEQ_MESH_NHR,
     HALG_AR_TREE,
+    HALG_BCAST_RING, HALG_BCAST_RHD, HALG_REDUCE_RING, HALG_REDUCE_RHD,
     HALG_COUNT
 };
 // Runs host algorithm `alg` for this rank; the world is already inside Enter().

@@ -366,3 +366,21 @@ def test_v_operators_on_every_template(algo_env, n, key, tag):
     for r in range(n):
         assert np.array_equal(recvs[r], ref[displs[r]:displs[r] + counts[r]])
     destroy(comms)
+
+
+@pytest.mark.parametrize("n", [2, 3, 6, 8])
+@pytest.mark.parametrize("key,tag", [("level0:NA;level1:ring", "Ring"), ("level0:NA;level1:H-D_R", "RHD")])
+def test_rooted_operators_on_ring_and_halving_doubling(algo_env, n, key, tag):
+    comms = make(n, algo=key)
+    for count in (1, 77, 2050):
+        for root in (0, n - 1):
+            bufs = [np.full(count, 3 * r + 1, np.int32) for r in range(n)]
+            verified(comms, lambda r, c: c.broadcast(bufs[r], root))
+            assert comms[0].last_algorithm() == f"HostBroadcastSole{tag}", comms[0].last_algorithm()
+            assert all(np.all(b == 3 * root + 1) for b in bufs)
+            ins = [np.random.default_rng(r).standard_normal(count) for r in range(n)]
+            out = np.zeros(count)
+            verified(comms, lambda r, c: c.reduce(ins[r], out if r == root else None, root))
+            assert comms[0].last_algorithm() == f"HostReduceSole{tag}", comms[0].last_algorithm()
+            np.testing.assert_allclose(out, np.sum(np.stack(ins), 0), rtol=1e-12, atol=1e-13)
+    destroy(comms)
