@@ -425,7 +425,8 @@ HcclResult RunHostAlgorithm(HostWorld& w, uint32_t rank, int alg, const OpParam&
             break;
         }
         // ------------------------------------------------------------ ReduceScatter (+V through the slice of `me`)
-        case HALG_RS_MESH: case HALG_RS_RING: case HALG_RS_RHD: case HALG_RS_NHR: case HALG_RS_ORDER_PRESERVED: case HALG_RS_SEQ_MESH_NHR: {
+        case HALG_RS_MESH: case HALG_RS_RING: case HALG_RS_RHD: case HALG_RS_NHR: case HALG_RS_ORDER_PRESERVED: case HALG_RS_SEQ_MESH_NHR:
+        case HALG_RS_SEQ_MESH_RING: case HALG_RS_SEQ_MESH_RHD: {
             // work on a scratch copy of the whole input so that the user's send buffer stays intact; layout of W:
             // rank i's block at i * blockElems (V: at its displacement)
             const bool v = p.op == HCCL_CMD_REDUCE_SCATTER_V;
@@ -471,8 +472,9 @@ HcclResult RunHostAlgorithm(HostWorld& w, uint32_t rank, int alg, const OpParam&
                 x.SyncGroup(all.ranks, N_DONE);
                 break;
             }
-            if (alg == HALG_RS_SEQ_MESH_NHR) {
+            if (alg == HALG_RS_SEQ_MESH_NHR || alg == HALG_RS_SEQ_MESH_RING || alg == HALG_RS_SEQ_MESH_RHD) {
                 // level 1 first on whole server-sized blocks, then level 0 inside the server
+                const Fam upper = alg == HALG_RS_SEQ_MESH_RING ? Fam::RING : alg == HALG_RS_SEQ_MESH_RHD ? Fam::RHD : Fam::NHR;
                 AlgHierarchy h;
                 CHK_RET(hierarchy(TopoMatchKind::TWO_LEVEL, &h));
                 if (h.levels() == 2) {
@@ -480,7 +482,7 @@ HcclResult RunHostAlgorithm(HostWorld& w, uint32_t rank, int alg, const OpParam&
                     LevelGroup(h, 0, rank, &g0);
                     LevelGroup(h, 1, rank, &g1);
                     // ranks are numbered server by server: blocks of one server are contiguous
-                    NhrReduceScatter(cc, g1, wk);
+                    ReduceScatterBy(upper, cc, g1, wk);
                     Work mine = SubWork(wk, g1.size(), g1.me);
                     MeshReduceScatter(cc, g0, mine);
                 } else {
@@ -494,7 +496,8 @@ HcclResult RunHostAlgorithm(HostWorld& w, uint32_t rank, int alg, const OpParam&
             break;
         }
         // ------------------------------------------------------------ AllGather (+V)
-        case HALG_AG_MESH: case HALG_AG_RING: case HALG_AG_RHD: case HALG_AG_NHR: case HALG_AG_SEQ_MESH_NHR: {
+        case HALG_AG_MESH: case HALG_AG_RING: case HALG_AG_RHD: case HALG_AG_NHR: case HALG_AG_SEQ_MESH_NHR:
+        case HALG_AG_SEQ_MESH_RING: case HALG_AG_SEQ_MESH_RHD: {
             const bool v = p.op == HCCL_CMD_ALLGATHER_V;
             if (v && alg != HALG_AG_MESH) {
                 // variable blocks through ring / RHD / NHR, in place in the output at the callers' displacements
@@ -519,7 +522,8 @@ HcclResult RunHostAlgorithm(HostWorld& w, uint32_t rank, int alg, const OpParam&
             }
             x.Copy(Out(rank, (uint64_t)rank * p.count * es), In(rank), p.count * es);
             Work wk{BufKind::OUTPUT, 0, p.count * n, es};
-            if (alg == HALG_AG_SEQ_MESH_NHR) {
+            if (alg == HALG_AG_SEQ_MESH_NHR || alg == HALG_AG_SEQ_MESH_RING || alg == HALG_AG_SEQ_MESH_RHD) {
+                const Fam upper = alg == HALG_AG_SEQ_MESH_RING ? Fam::RING : alg == HALG_AG_SEQ_MESH_RHD ? Fam::RHD : Fam::NHR;
                 AlgHierarchy h;
                 CHK_RET(hierarchy(TopoMatchKind::TWO_LEVEL, &h));
                 if (h.levels() == 2) {
@@ -528,7 +532,7 @@ HcclResult RunHostAlgorithm(HostWorld& w, uint32_t rank, int alg, const OpParam&
                     LevelGroup(h, 1, rank, &g1);
                     Work mine = SubWork(wk, g1.size(), g1.me);
                     MeshAllGather(c, g0, mine);
-                    NhrAllGather(c, g1, wk);
+                    AllGatherBy(upper, c, g1, wk);
                 } else {
                     MeshAllGather(c, all, wk);
                 }
