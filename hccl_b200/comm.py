@@ -161,6 +161,11 @@ class Communicator:
 
     def free(self, tensor) -> None:
         _check(lib.HcclMemFree(self._h, c_void_p(tensor.data_ptr())), "HcclMemFree")
+        self._sym = [(p, n) for p, n in self._sym if p != tensor.data_ptr()]
+
+    def is_symmetric(self, tensor) -> bool:
+        """True when the tensor starts a block returned by :meth:`empty` that has not been freed."""
+        return any(p == tensor.data_ptr() for p, _ in self._sym)
 
     def register(self, tensor) -> None:
         """Collective: registers a tensor the caller allocated itself (same size on every rank) so that operators use it

@@ -5,6 +5,18 @@ dim 128, SwiGLU FFN 28672, RMSNorm, RoPE theta 500000, vocab 128256.  Between
 blocks the activations are sharded over the sequence; QKV and gate/up
 projections are column-parallel (AllGather->Matmul), o_proj and down_proj are
 row-parallel (Matmul->ReduceScatter).
+
+Nothing large is replicated.  The embedding table is cut along the hidden
+dimension: every rank looks all tokens up in its column slice and one AlltoAll
+turns ``[S, hidden / P]`` into the rank's sequence shard ``[S / P, hidden]``
+(1/P of the bytes a vocabulary-parallel reduce-scatter would move); the
+backward pass runs the same exchange the other way and accumulates into a
+``[vocab, hidden / P]`` gradient.  The RMSNorm weights are the only replicated
+parameters; each rank sees the gradient of its own sequence shard only, so
+``sync_replicated_grads`` sums them over the group before the optimizer step.
+The loss of a rank is its shard's share of the mean over the WHOLE sequence:
+the per-rank losses add up to the loss of the unsharded model and the
+gradients match it.
 """
 from __future__ import annotations
 
@@ -54,9 +66,8 @@ class DecoderLayer(torch.nn.Module):
         p = ctx.world
         assert cfg.n_heads % p == 0 and cfg.n_kv_heads % p == 0 and cfg.ffn % p == 0
         self.hq, self.hkv = cfg.n_heads // p, cfg.n_kv_heads // p
-        dev = "cuda"
-        self.attn_norm = torch.nn.Parameter(torch.ones(cfg.hidden, device=dev, dtype=torch.bfloat16))
-        self.ffn_norm = torch.nn.Parameter(torch.ones(cfg.hidden, device=dev, dtype=torch.bfloat16))
+        self.attn_norm = torch.nn.Parameter(torch.ones(cfg.hidden, device=ctx.device, dtype=ctx.dtype))
+        self.ffn_norm = torch.nn.Parameter(torch.ones(cfg.hidden, device=ctx.device, dtype=ctx.dtype))
         # Column-parallel layers keep their gathered input (a persistent symmetric buffer, saved for the backward pass),
         # so their keys are per layer; the row-parallel layers' symmetric buffers are transient and shared.
         self.qkv = ColumnParallelLinear(cfg.hidden, (cfg.n_heads + 2 * cfg.n_kv_heads) * cfg.head_dim, ctx, f"qkv{idx}", cfg.init_std)
@@ -83,24 +94,94 @@ class DecoderLayer(torch.nn.Module):
         return x, self.down(fused.swiglu(self.gate_up(h), use_kernels=k_))
 
 
+class _ShardedEmbedding(torch.autograd.Function):
+    """Embedding whose table is cut along the hidden dimension, producing this rank's sequence shard."""
+
+    @staticmethod
+    def forward(fctx, token_ids, table, ctx: TPContext):
+        # table [vocab, hidden / P]; token_ids [S] (the whole sequence on every rank)
+        p = ctx.world
+        s, hp = token_ids.shape[0], table.shape[1]
+        cols = F.embedding(token_ids, table)                               # [S, hidden / P]: rows grouped by destination rank
+        got = ctx.all_to_all(cols.view(p, s // p, hp), "embed_fwd")         # block q: rank q's columns of my tokens
+        fctx.save_for_backward(token_ids)
+        fctx.ctx, fctx.vocab = ctx, table.shape[0]
+        return got.permute(1, 0, 2).reshape(s // p, p * hp)
+
+    @staticmethod
+    def backward(fctx, dx):
+        (token_ids,) = fctx.saved_tensors
+        ctx, p = fctx.ctx, fctx.ctx.world
+        sp, hidden = dx.shape
+        send = dx.view(sp, p, hidden // p).permute(1, 0, 2).contiguous()   # block q: my tokens' gradient of rank q's columns
+        got = ctx.all_to_all(send, "embed_bwd").view(sp * p, hidden // p)  # every token's gradient of my columns
+        dtable = torch.ops.aten.embedding_dense_backward(got, token_ids, fctx.vocab, -1, False)
+        return None, dtable, None
+
+
 class LlamaStack(torch.nn.Module):
     """Embedding -> n decoder layers -> final norm; returns the sequence-sharded hidden states."""
 
     def __init__(self, cfg: LlamaConfig, ctx: TPContext):
         super().__init__()
         self.cfg, self.ctx = cfg, ctx
-        self.embed = torch.nn.Parameter(torch.randn(cfg.vocab, cfg.hidden, device="cuda", dtype=torch.float32).mul_(cfg.init_std).to(torch.bfloat16))
+        assert cfg.hidden % ctx.world == 0
+        self.embed = torch.nn.Parameter(torch.randn(cfg.vocab, cfg.hidden // ctx.world, device=ctx.device, dtype=torch.float32)
+                                        .mul_(cfg.init_std).to(ctx.dtype))
         self.layers = torch.nn.ModuleList(DecoderLayer(cfg, ctx, i) for i in range(cfg.n_layers))
-        self.final_norm = torch.nn.Parameter(torch.ones(cfg.hidden, device="cuda", dtype=torch.bfloat16))
+        self.final_norm = torch.nn.Parameter(torch.ones(cfg.hidden, device=ctx.device, dtype=ctx.dtype))
         self._rope = None
 
-    def forward(self, token_ids):
-        # token_ids [S] (the full sequence on every rank); each rank embeds its own sequence shard
-        s = token_ids.shape[0]
+    def replicated_parameters(self):
+        """Parameters every rank holds a full copy of (the RMSNorm weights)."""
+        out = []
+        for layer in self.layers:
+            out += [layer.attn_norm, layer.ffn_norm]
+        return out + [self.final_norm]
+
+    def sync_replicated_grads(self):
+        """Sums the gradients of the replicated parameters over the group: one flat all-reduce.  Call between
+        ``backward`` and the optimizer step; without it the copies drift apart."""
+        if self.ctx.world == 1:
+            return
+        params = [p for p in self.replicated_parameters() if p.grad is not None]
+        if not params:
+            return
+        grads = [p.grad for p in params]
+        flat = self.ctx.flat_buffer("replicated_grads", sum(g.numel() for g in grads), grads[0].dtype)
+        torch.cat([g.reshape(-1) for g in grads], out=flat)
+        self.ctx.all_reduce_(flat, "replicated_grads")
+        torch._foreach_copy_(grads, [c.view_as(g) for c, g in zip(flat.split([g.numel() for g in grads]), grads)])
+
+    @torch.no_grad()
+    def load_full(self, full: "LlamaStack"):
+        """Takes this rank's slices of an unsharded model's parameters (tests compare the two)."""
         p, r = self.ctx.world, self.ctx.rank
+        cfg = self.cfg
+        d = cfg.head_dim
+
+        def rows(w, n_per):     # [n_per * p rows] -> this rank's n_per rows
+            return w[r * n_per:(r + 1) * n_per]
+
+        self.embed.copy_(full.embed[:, r * (cfg.hidden // p):(r + 1) * (cfg.hidden // p)])
+        self.final_norm.copy_(full.final_norm)
+        for mine, ref in zip(self.layers, full.layers):
+            mine.attn_norm.copy_(ref.attn_norm)
+            mine.ffn_norm.copy_(ref.ffn_norm)
+            hq, hkv = cfg.n_heads // p, cfg.n_kv_heads // p
+            wq, wk, wv = ref.qkv.weight.split([cfg.n_heads * d, cfg.n_kv_heads * d, cfg.n_kv_heads * d])
+            mine.qkv.weight.copy_(torch.cat([rows(wq, hq * d), rows(wk, hkv * d), rows(wv, hkv * d)]))
+            wg, wu = ref.gate_up.weight.chunk(2)
+            mine.gate_up.weight.copy_(torch.cat([rows(wg, cfg.ffn // p), rows(wu, cfg.ffn // p)]))
+            mine.o.weight.copy_(ref.o.weight[:, r * hq * d:(r + 1) * hq * d])
+            mine.down.weight.copy_(ref.down.weight[:, r * (cfg.ffn // p):(r + 1) * (cfg.ffn // p)])
+
+    def forward(self, token_ids):
+        # token_ids [S] (the full sequence on every rank)
+        s = token_ids.shape[0]
+        p = self.ctx.world
         assert s % p == 0
-        shard = token_ids[r * (s // p):(r + 1) * (s // p)]
-        x = F.embedding(shard, self.embed)
+        x = F.embedding(token_ids, self.embed) if p == 1 else _ShardedEmbedding.apply(token_ids, self.embed, self.ctx)
         if self._rope is None or self._rope[0].shape[0] != s:
             self._rope = rope_tables(s, self.cfg.head_dim, self.cfg.rope_theta, x.device)
         cos, sin = self._rope
@@ -110,8 +191,9 @@ class LlamaStack(torch.nn.Module):
         return fused.add_rms_norm(x, delta, self.final_norm, self.cfg.norm_eps, use_kernels=self.ctx.fused_ops)[1]
 
     def loss(self, token_ids):
-        """Scalar training signal with non-trivial gradients: the mean product of neighbouring features of the final
-        hidden states of this rank's sequence shard.  (The mean SQUARE of an RMS-normalised output is constant, so its
-        gradients would be rounding noise.)"""
+        """Scalar training signal with non-trivial gradients: the mean, over the WHOLE sequence, of the product of
+        neighbouring features of the final hidden states; a rank returns its sequence shard's share of it, so the
+        ranks' losses add up to the unsharded model's.  (The mean SQUARE of an RMS-normalised output is constant, so
+        its gradients would be rounding noise.)"""
         h = self.forward(token_ids).float()
-        return (h * h.roll(1, dims=-1)).mean()
+        return (h * h.roll(1, dims=-1)).sum() / (token_ids.shape[0] * h.shape[-1])

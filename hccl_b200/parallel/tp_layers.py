@@ -26,10 +26,12 @@ from ..ops import mc2
 class TPContext:
     """What the layers need to know about the tensor-parallel group."""
 
-    def __init__(self, comm=None, group=None, impl: str = "hccl"):
+    def __init__(self, comm=None, group=None, impl: str = "hccl", device="cuda", dtype=torch.bfloat16, fused_ops=None):
         self.comm = comm                  # hccl_b200.Communicator (impl == "hccl")
-        self.group = group                # torch.distributed group (impl == "nccl")
+        self.group = group                # torch.distributed group (impl == "nccl"; any backend, gloo on CPU included)
         self.impl = impl
+        self.device = device              # where parameters and activations live ("cpu" only with impl == "nccl")
+        self.dtype = dtype
         if impl == "hccl":
             self.world = comm.world_size if comm is not None else 1
             self.rank = comm.rank if comm is not None else 0
@@ -45,7 +47,59 @@ class TPContext:
         self.ag_form = os.environ.get("HCCL_TP_AG_FORM", "push" if self.world <= 2 else "pull")
         # residual add + RMSNorm, SwiGLU and rotary embedding as this library's single-pass kernels (the NCCL + cuBLAS
         # comparison arm keeps the framework's element-wise kernels); HCCL_FUSED_ELEMENTWISE=0 turns them off
-        self.fused_ops = impl == "hccl" and os.environ.get("HCCL_FUSED_ELEMENTWISE", "1") != "0"
+        # ``fused_ops=True`` also gives them to the NCCL + cuBLAS arm, so that the two arms differ in the collectives
+        # and the matmul kernels only
+        if fused_ops is None:
+            fused_ops = impl == "hccl"
+        self.fused_ops = bool(fused_ops) and str(device).startswith("cuda") and os.environ.get("HCCL_FUSED_ELEMENTWISE", "1") != "0"
+
+    # ---- collectives on whole tensors, either arm (used for what is not a fused matmul: the embedding exchange and
+    # the gradients of replicated parameters)
+    def all_to_all(self, send, key):
+        """``send [P, ...]``: block q goes to rank q; returns ``[P, ...]`` whose block q came from rank q."""
+        if self.world == 1:
+            return send
+        if self.impl == "hccl":
+            buf = self.sym_buffer(("a2a_send", key), send.shape, send.dtype)
+            buf.copy_(send)
+            recv = torch.empty_like(send)
+            self.comm.all_to_all(buf, recv)
+            self.launches += 1
+            return recv
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send.contiguous(), group=self.group)
+        return recv
+
+    def all_reduce_(self, t, key):
+        """In-place sum over the group."""
+        if self.world == 1:
+            return t
+        if self.impl == "hccl":
+            self.comm.all_reduce(t)
+            self.launches += 1
+        else:
+            dist.all_reduce(t, group=self.group)
+        return t
+
+    def flat_buffer(self, key, numel, dtype):
+        """A flat scratch tensor that the all-reduce of this arm takes at full speed (symmetric memory for the library)."""
+        if self.impl == "hccl" and self.world > 1:
+            return self.sym_buffer(("flat", key), (numel,), dtype)
+        k = ("flat", key, numel, dtype)
+        buf = self._sym.get(k)
+        if buf is None:
+            buf = torch.empty(numel, device=self.device, dtype=dtype)
+            self._sym[k] = buf
+        return buf
+
+    def release(self):
+        """Frees the symmetric buffers of this context (collective: every rank calls it)."""
+        bufs, self._sym = self._sym, {}
+        if self.impl == "hccl" and self.comm is not None:
+            torch.cuda.synchronize()
+            for k in sorted(bufs, key=repr):              # same order on every rank
+                if bufs[k].is_cuda and self.comm.is_symmetric(bufs[k]):
+                    self.comm.free(bufs[k])
 
     def sym_buffer(self, key, shape, dtype=torch.bfloat16):
         """A persistent symmetric buffer per call site and shape (allocated collectively on first use)."""
@@ -55,6 +109,20 @@ class TPContext:
             buf = self.comm.empty(tuple(shape), dtype)
             self._sym[k] = buf
         return buf
+
+
+def _reduce_scatter_rows(ctx, full):
+    """Framework arm: ``[S, N] -> [S / P, N]`` summed over the group (backends without a reduce-scatter, gloo on CPU,
+    take an all-reduce and keep their rows)."""
+    rows = full.shape[0] // ctx.world
+    out = torch.empty((rows, full.shape[1]), device=full.device, dtype=full.dtype)
+    if full.is_cuda:
+        dist.reduce_scatter_tensor(out, full, group=ctx.group)
+    else:
+        full = full.clone()
+        dist.all_reduce(full, group=ctx.group)
+        out.copy_(full[ctx.rank * rows:(ctx.rank + 1) * rows])
+    return out
 
 
 def _mm(ctx, a, b, **kw):
@@ -105,9 +173,7 @@ class _ColumnParallel(torch.autograd.Function):
             dx = mc2.matmul_reduce_scatter(ctx.comm, dy, weight, weight_is_kn=True)
             ctx.launches += 1
         else:
-            full = dy @ weight
-            dx = torch.empty((full.shape[0] // ctx.world, full.shape[1]), device=dy.device, dtype=dy.dtype)
-            dist.reduce_scatter_tensor(dx, full, group=ctx.group)
+            dx = _reduce_scatter_rows(ctx, dy @ weight)
         return dx, dw, None, None
 
 
@@ -122,10 +188,7 @@ class _RowParallel(torch.autograd.Function):
         if ctx.impl == "hccl":
             ctx.launches += 1
             return mc2.matmul_reduce_scatter(ctx.comm, x.contiguous(), weight)
-        full = x @ weight.t()
-        out = torch.empty((full.shape[0] // ctx.world, full.shape[1]), device=x.device, dtype=x.dtype)
-        dist.reduce_scatter_tensor(out, full, group=ctx.group)
-        return out
+        return _reduce_scatter_rows(ctx, x @ weight.t())
 
     @staticmethod
     def backward(fctx, dy_shard):
@@ -156,11 +219,13 @@ class _RowParallel(torch.autograd.Function):
 class ColumnParallelLinear(torch.nn.Module):
     """``y[S, N/P] = all_gather(x[S/P, K]) @ W^T`` with the weight sharded over its rows (output features)."""
 
-    def __init__(self, in_features, out_features, ctx: TPContext, key, std=0.02, device="cuda", dtype=torch.bfloat16):
+    shard_dim = 0             # the full weight [out, in] is cut along this dimension
+
+    def __init__(self, in_features, out_features, ctx: TPContext, key, std=0.02):
         super().__init__()
         assert out_features % ctx.world == 0
         self.ctx, self.key = ctx, key
-        self.weight = torch.nn.Parameter(torch.randn(out_features // ctx.world, in_features, device=device, dtype=torch.float32).mul_(std).to(dtype))
+        self.weight = torch.nn.Parameter(torch.randn(out_features // ctx.world, in_features, device=ctx.device, dtype=torch.float32).mul_(std).to(ctx.dtype))
 
     def forward(self, x_shard):
         return _ColumnParallel.apply(x_shard, self.weight, self.ctx, self.key)
@@ -169,11 +234,13 @@ class ColumnParallelLinear(torch.nn.Module):
 class RowParallelLinear(torch.nn.Module):
     """``y[S/P, N] = reduce_scatter(x[S, K/P] @ W^T)`` with the weight sharded over its columns (input features)."""
 
-    def __init__(self, in_features, out_features, ctx: TPContext, key, std=0.02, device="cuda", dtype=torch.bfloat16):
+    shard_dim = 1
+
+    def __init__(self, in_features, out_features, ctx: TPContext, key, std=0.02):
         super().__init__()
         assert in_features % ctx.world == 0
         self.ctx, self.key = ctx, key
-        self.weight = torch.nn.Parameter(torch.randn(out_features, in_features // ctx.world, device=device, dtype=torch.float32).mul_(std).to(dtype))
+        self.weight = torch.nn.Parameter(torch.randn(out_features, in_features // ctx.world, device=ctx.device, dtype=torch.float32).mul_(std).to(ctx.dtype))
 
     def forward(self, x):
         return _RowParallel.apply(x, self.weight, self.ctx, self.key)

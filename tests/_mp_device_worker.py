@@ -248,8 +248,9 @@ def scenario_register(comm, rank, world):
 
 
 def scenario_model(rank, world, path):
-    """Two-layer TP+SP decoder stack: loss and gradients of the fused-kernel arm against the NCCL + cuBLAS arm built
-    from the same seed, for both AllGather->Matmul forms; two steps each (persistent symmetric buffers are reused)."""
+    """Two-layer TP+SP decoder stack: loss and gradients of the NCCL + cuBLAS arm against the same model in one piece,
+    and of the fused-kernel arm against the NCCL + cuBLAS arm, for both AllGather->Matmul forms; two steps each
+    (persistent symmetric buffers are reused)."""
     import torch.distributed as dist
 
     from hccl_b200.models import LlamaConfig, LlamaStack
@@ -262,23 +263,49 @@ def scenario_model(rank, world, path):
     seq = 128 * world
     tokens = torch.randint(0, cfg.vocab, (seq,), generator=torch.Generator().manual_seed(5), dtype=torch.int64).cuda()
 
+    # the same model in one piece (this library's matmul kernels on one GPU), built from one seed on every rank
+    one_ctx = TPContext(comm=None, impl="hccl")
+    torch.manual_seed(77)
+    one = LlamaStack(cfg, one_ctx)
+    with torch.no_grad():
+        for p_ in one.replicated_parameters():
+            p_.add_(0.1 * torch.randn_like(p_))
+    one_loss = one.loss(tokens)
+    one_loss.backward()
+    holder_src = LlamaStack(cfg, one_ctx)
+    with torch.no_grad():
+        for (n_, p_), (_, q_) in zip(holder_src.named_parameters(), one.named_parameters()):
+            p_.copy_(q_.grad)
+
     def run(impl, form):
         os.environ["HCCL_TP_AG_FORM"] = form
         ctx = TPContext(comm=comm if impl == "hccl" else None, group=None, impl=impl)
-        torch.manual_seed(77 + rank)
         model = LlamaStack(cfg, ctx)
+        model.load_full(one)
         out = []
         for _ in range(2):
             model.zero_grad(set_to_none=True)
             loss = model.loss(tokens)
             loss.backward()
+            model.sync_replicated_grads()
+            total = loss.detach().clone()
+            dist.all_reduce(total)
             torch.cuda.synchronize()
-            out.append((loss.item(), {n: p.grad.float().clone() for n, p in model.named_parameters() if p.grad is not None}))
-        return out
+            out.append((total.item(), {n: p.grad.float().clone() for n, p in model.named_parameters() if p.grad is not None}))
+        want = LlamaStack(cfg, ctx)
+        want.load_full(holder_src)                      # this rank's slices of the one-piece gradients
+        ctx.release()
+        return out, {n: p.detach().float() for n, p in want.named_parameters()}
 
-    ref = run("nccl", "pull")
+    ref, want = run("nccl", "pull")
+    # the framework arm against the model in one piece: loss and every gradient (sharded and replicated)
+    assert abs(ref[0][0] - one_loss.item()) <= 2e-2 * abs(one_loss.item()) + 1e-4, f"loss {ref[0][0]} vs one-piece {one_loss.item()}"
+    for name, g in ref[0][1].items():
+        denom = want[name].abs().max().item() + 1e-8
+        err = (g - want[name]).abs().max().item() / denom
+        assert err <= 8e-2, f"grad {name} differs from the one-piece model by {err:.3f} of its max"
     for form in ("push", "pull"):
-        got = run("hccl", form)
+        got, _ = run("hccl", form)
         for step, ((l0, g0), (l1, g1)) in enumerate(zip(ref, got)):
             assert abs(l0 - l1) <= 2e-2 * abs(l0) + 1e-4, f"{form} step {step}: loss {l1} vs {l0}"
             for name in g0:
