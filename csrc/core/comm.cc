@@ -411,6 +411,7 @@ HcclResult EmuGroup::Create(int nRanks, const HcclCommConfig* cfg, std::vector<C
     g->nRanks_ = nRanks;
     g->alive_ = nRanks;
     g->queues_.resize((size_t)nRanks);
+    g->pendingOps.resize((size_t)nRanks);
     EffectiveConfig eff;
     CHK_RET(MergeConfig(GetEnvConfig(), cfg, &eff));
     // emulated ranks share one GPU: keep the per-rank slab modest unless configured
@@ -428,6 +429,7 @@ HcclResult EmuGroup::Create(int nRanks, const HcclCommConfig* cfg, std::vector<C
         HcclResult res = c->InitEmulated(g.get(), nRanks, r, g->slabs_[r], cfg);
         if (res != HCCL_SUCCESS) { delete c; return res; }
         g->hostComms_[r] = c->dev();
+        g->members.push_back(c);
         comms->push_back(c);
     }
     CHK_CUDA(cudaMemcpy(g->dComms_, g->hostComms_.data(), sizeof(DevComm) * (size_t)nRanks, cudaMemcpyHostToDevice));

@@ -88,6 +88,7 @@ public:
     const StageLayout& layout() const { return layout_; }
     bool nvls() const { return slab_.mc != nullptr; }
     bool emulated() const { return emu_ != nullptr; }
+    EmuGroup* emuGroup() const { return emu_; }
     int MaxBlocks() const;
 
     int rank = 0, nRanks = 1, device = 0;
@@ -145,6 +146,11 @@ public:
     HcclResult MemAlloc(int rank, uint64_t size, SymSegment* seg);   // R matching calls -> one group allocation
     void Release(CommImpl* c);
     int nRanks() const { return nRanks_; }
+    // Collectives queued per rank until every rank has called (the operator layer owns the entries).
+    struct PendingOp;
+    std::mutex opMu;
+    std::vector<std::deque<std::shared_ptr<PendingOp>>> pendingOps;
+    std::vector<CommImpl*> members;
 private:
     EmuGroup() = default;
     int nRanks_ = 0;

@@ -54,6 +54,7 @@ struct Plan {
     int devAlg = -1;          // DevAlg
     int nBlocks = 1;
     uint64_t chunkBytes = 0;  // bytes per loop of the sole executor (0 = whole message)
+    uint32_t agreedFlags = 0; // buffer facts all ranks share for this call signature (what selection and execution used)
     uint64_t uses = 0;
 };
 

@@ -316,6 +316,7 @@ struct ArLLBody {
         const size_t nLines = (a.bytes + 7) >> 3;
         size_t lb, le;
         Share(nLines, nb, b, 1, &lb, &le);
+        LLCreditWait(c, ep, K_AR_LL, b);
         const bool inAl = (((uintptr_t)a.in) & 7u) == 0, outAl = (((uintptr_t)a.out) & 7u) == 0;
         for (size_t i = lb + threadIdx.x; i < le; i += blockDim.x) {
             uint32_t d0, d1;
@@ -605,6 +606,7 @@ struct AgLLBody {
         const size_t nLines = (bytes + 7) >> 3;
         size_t lb, le;
         Share(nLines, nb, b, 1, &lb, &le);
+        LLCreditWait(c, ep, K_AG_LL, b);
         const bool inAl = (((uintptr_t)a.in) & 7u) == 0;
         for (size_t i = lb + threadIdx.x; i < le; i += blockDim.x) {
             uint32_t d0, d1;
@@ -662,6 +664,7 @@ struct LLExchangeBody {
         const size_t nLines = (bytes + 7) >> 3;
         size_t lb, le;
         Share(nLines, nb, b, 1, &lb, &le);
+        LLCreditWait(c, ep, K_RS_LL, b);
         for (int k = 1; k < p; ++k) {
             const int q = (me + k) % p;
             if (a.cnt2[q] == 0) continue;
@@ -921,10 +924,20 @@ struct ScatterBody {
 //   cnt[q]  = bytes this rank receives from q      dsp[q]  = where they go in `out`
 //   cnt2[q] = bytes this rank sends to q           dsp2[q] = where they start in `in`
 // A receiver needs the SENDER's displacement towards it, which only the sender
-// knows, so every block row first publishes its rank's send displacements in a
-// small table inside its exchange region ([kMaxBlocks][kMaxDevRanks] uint64),
-// and reads the peers' tables after the first barrier.  With MODE_STAGE_IN the
-// send ranges are compacted into the slab in rank order.
+// knows, so every block row first publishes its rank's send displacements (and
+// send sizes) in a small table inside its exchange region
+// ([kMaxBlocks][2][kMaxDevRanks] uint64), and reads the peers' tables after the
+// first barrier.  With MODE_STAGE_IN the send ranges are copied into the slab.
+//
+// Staged AlltoAllV of any size (chunk != 0): a pair's data goes through a window of
+// `chunk` bytes per peer.  How many passes that takes depends on the largest
+// pair of the WHOLE matrix, which no rank knows on the host (counts are private
+// to each rank), so the kernel works it out: after the first barrier every
+// block row reads all P x P send sizes from the tables, takes the maximum and
+// loops ceil(max / chunk) times - the same number on every rank.  Pass k moves
+// bytes [k * chunk, (k + 1) * chunk) of every pair: stage, barrier, pull,
+// barrier (nobody restages while a peer still reads).  The reference paces the
+// same loop with per-peer credit flags (aiv_all_to_all_v_mesh_1D.h:184-214).
 struct A2aBody {
     using Args = CollArgs;
     static constexpr int kThreads = 512;
@@ -933,8 +946,21 @@ struct A2aBody {
         OpHead(c, b);
         const int p = c.nRanks, me = c.rank;
         const uint64_t e = LoadEpoch(c, b);
-        uint64_t* myMeta = reinterpret_cast<uint64_t*>(a.xch[me]) + (size_t)b * kMaxDevRanks;
-        if (a.mode & MODE_STAGE_IN) {
+        uint64_t* myMeta = reinterpret_cast<uint64_t*>(a.xch[me]) + (size_t)b * 2 * kMaxDevRanks;
+        const bool windowed = (a.mode & MODE_STAGE_IN) && a.chunk != 0;
+        const size_t win = (a.chunk + 15) & ~(size_t)15;
+        if (windowed) {
+            for (int q = 0; q < p; ++q) {
+                const size_t n0 = a.cnt2[q] < a.chunk ? a.cnt2[q] : a.chunk;
+                size_t sb, se;
+                Share(n0, nb, b, 16, &sb, &se);
+                BlockCopyBytes(const_cast<char*>(a.src[me]) + (size_t)q * win + sb, a.in + a.dsp2[q] + sb, se - sb);
+            }
+            if (threadIdx.x < p) {
+                myMeta[threadIdx.x] = (uint64_t)threadIdx.x * win;
+                myMeta[kMaxDevRanks + threadIdx.x] = a.cnt2[threadIdx.x];
+            }
+        } else if (a.mode & MODE_STAGE_IN) {
             size_t run = 0;
             for (int q = 0; q < p; ++q) {
                 size_t sb, se;
@@ -947,24 +973,55 @@ struct A2aBody {
             myMeta[threadIdx.x] = a.dsp2[threadIdx.x];
         }
         RankBarrier(c, b, 0, e + 1, K_A2AV);
-        {
-            CopySeg segs[kMaxDevRanks];
-            int n = 0;
-            for (int k = 0; k < p; ++k) {
-                const int q = (me + k) % p;
-                size_t rb, re;
-                Share(a.cnt[q], nb, b, 16, &rb, &re);
-                if (q == me) {
-                    segs[n++] = CopySeg{a.out + a.dsp[q] + rb, a.in + a.dsp2[me] + rb, re - rb};
-                } else {
-                    const uint64_t sd = reinterpret_cast<const volatile uint64_t*>(a.xch[q])[(size_t)b * kMaxDevRanks + me];
-                    segs[n++] = CopySeg{a.out + a.dsp[q] + rb, a.src[q] + sd + rb, re - rb};
-                }
+        uint64_t passes = 1;
+        if (windowed) {
+            __shared__ unsigned long long s_max;
+            if (threadIdx.x == 0) s_max = 0ull;
+            __syncthreads();
+            if ((int)threadIdx.x < p * p) {
+                const int q = threadIdx.x / p, r = threadIdx.x % p;
+                const uint64_t v = reinterpret_cast<const volatile uint64_t*>(a.xch[q])[(size_t)b * 2 * kMaxDevRanks + kMaxDevRanks + r];
+                atomicMax(&s_max, (unsigned long long)v);
             }
-            BlockCopyMulti(segs, n);
+            __syncthreads();
+            passes = s_max == 0 ? 1 : (s_max + a.chunk - 1) / a.chunk;
         }
-        RankBarrier(c, b, 0, e + 2, K_A2AV);
-        StoreEpoch(c, b, e + 2);
+        for (uint64_t k = 0; k < passes; ++k) {
+            const size_t base = windowed ? (size_t)k * a.chunk : 0;
+            if (k > 0) {
+                for (int q = 0; q < p; ++q) {
+                    const size_t left = a.cnt2[q] > base ? a.cnt2[q] - base : 0;
+                    const size_t n0 = left < a.chunk ? left : a.chunk;
+                    size_t sb, se;
+                    Share(n0, nb, b, 16, &sb, &se);
+                    BlockCopyBytes(const_cast<char*>(a.src[me]) + (size_t)q * win + sb, a.in + a.dsp2[q] + base + sb, se - sb);
+                }
+                RankBarrier(c, b, 0, e + 1 + 2 * k, K_A2AV);
+            }
+            {
+                CopySeg segs[kMaxDevRanks];
+                int n = 0;
+                for (int kk = 0; kk < p; ++kk) {
+                    const int q = (me + kk) % p;
+                    size_t len = a.cnt[q];
+                    if (windowed) {
+                        const size_t left = a.cnt[q] > base ? a.cnt[q] - base : 0;
+                        len = left < a.chunk ? left : a.chunk;
+                    }
+                    size_t rb, re;
+                    Share(len, nb, b, 16, &rb, &re);
+                    if (q == me) {
+                        segs[n++] = CopySeg{a.out + a.dsp[q] + base + rb, a.in + a.dsp2[me] + base + rb, re - rb};
+                    } else {
+                        const uint64_t sd = reinterpret_cast<const volatile uint64_t*>(a.xch[q])[(size_t)b * 2 * kMaxDevRanks + me];
+                        segs[n++] = CopySeg{a.out + a.dsp[q] + base + rb, a.src[q] + sd + rb, re - rb};
+                    }
+                }
+                BlockCopyMulti(segs, n);
+            }
+            RankBarrier(c, b, 0, e + 2 + 2 * k, K_A2AV);
+        }
+        StoreEpoch(c, b, e + 2 * passes);
         OpTail(c, b);
     }
 };

@@ -119,6 +119,25 @@ __device__ __forceinline__ uint64_t LoadLLEpoch(const DevComm& c)
 {
     return *reinterpret_cast<volatile uint64_t*>(c.epochs + kMaxBlocks);
 }
+// Credit of the LL forms.  Lines of op `epoch` go into the reader's slot of parity epoch & 1, which op epoch - 2 used
+// last.  In the forms where every rank waits for lines of every peer, a rank in op `epoch` knows that all peers have
+// entered epoch - 1 and so finished epoch - 2; a one-to-many form (Broadcast: the root waits for nobody, a receiver
+// only for the root) gives no such guarantee, and a writer two ops ahead of a slow reader would replace lines the
+// reader still polls for.  So every rank tells every peer when it has finished an LL op (flag slot kLLCreditSlot of
+// block row 0, value epoch + 1), and before writing the lines of op `epoch` a rank checks that each peer it writes to
+// has reported epoch - 2.  In step the check is one read of local memory per peer.
+constexpr int kLLCreditSlot = 1;
+__device__ __forceinline__ bool LLCreditWait(const DevComm& c, uint64_t epoch, uint32_t kernelId, int block)
+{
+    __shared__ int s_creditOk;
+    if (threadIdx.x == 0) s_creditOk = 1;
+    __syncthreads();
+    if (epoch >= 2 && (int)threadIdx.x < c.nRanks && (int)threadIdx.x != c.rank) {
+        if (!WaitFlagGE(c, FlagPtr(c, c.rank, 0, kLLCreditSlot, threadIdx.x), epoch - 1, kernelId, block, kLLCreditSlot, threadIdx.x)) s_creditOk = 0;
+    }
+    __syncthreads();
+    return s_creditOk != 0;
+}
 __device__ __forceinline__ void FinishLLEpoch(const DevComm& c, uint64_t epoch, int nBlocks)
 {
     __syncthreads();
@@ -130,6 +149,9 @@ __device__ __forceinline__ void FinishLLEpoch(const DevComm& c, uint64_t epoch, 
             *reinterpret_cast<volatile uint64_t*>(ticket) = 0;
             *reinterpret_cast<volatile uint64_t*>(c.epochs + kMaxBlocks) = epoch + 1;
             __threadfence();
+            // every block of this rank has read its lines of this op: the peers may reuse the slots of this parity
+            for (int q = 0; q < c.nRanks; ++q)
+                if (q != c.rank) StReleaseSys(FlagPtr(c, q, 0, kLLCreditSlot, c.rank), epoch + 1);
         }
     }
 }

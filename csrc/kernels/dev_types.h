@@ -59,7 +59,8 @@ struct DevComm {
 };
 
 constexpr size_t kEpochWords = 2 * kMaxBlocks + 8;
-constexpr size_t kA2aMetaBytes = (size_t)kMaxBlocks * kMaxDevRanks * sizeof(uint64_t);
+// AlltoAll table at the start of the exchange region: per block row, every peer's send displacement and send size
+constexpr size_t kA2aMetaBytes = (size_t)kMaxBlocks * 2 * kMaxDevRanks * sizeof(uint64_t);
 
 enum CollMode : uint32_t {
     MODE_STAGE_IN = 1u,    // copy local `in` into own slab (args.src[rank]) before the first barrier
@@ -85,6 +86,9 @@ struct CollArgs {
     int root;
     uint32_t mode;
     uint32_t pad;
+    uint64_t chunk;                      // AlltoAllV staged through the slab: bytes of one pair's staging window (0: one pass)
+    float scale;                         // reductions: factor applied to the reduced value before it is stored (1 = none)
+    int outType;                         // reductions: HcclDataType of `out` when it differs from the input type, else -1
 };
 
 struct P2pItem {

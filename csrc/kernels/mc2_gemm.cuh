@@ -80,9 +80,11 @@ struct GemmArgs {
     // no barrier is needed before a slot is overwritten.
     size_t xchgParityElems;
     int bn;                    // two-SM kernels: column tile width (multiple of 32, at most 256), chosen per problem
-    // AG, push form (agPush != 0): `gathered` is symmetric memory, every rank stores its own shard into all ranks'
+    // AG, push forms (agPush != 0): `gathered` is symmetric memory, every rank stores its own shard into all ranks'
     // gathered buffers and adds the bytes written to their per-row-block arrival counters; aPeer[rank] is the local shard (any memory).
     //   gatheredPeer[q] = rank q's gathered buffer mapped here; agReady[q] = rank q's counters [P * mPerRank / 128]
+    // kAgPushWorkers: dedicated worker CTAs copy; kAgPushCoop: no worker CTAs, the epilogue warps of every GEMM CTA
+    // copy pieces of the shard whenever they have no accumulator to drain.
     int agPush;
     __nv_bfloat16* gatheredPeer[kMaxDevRanks];
     uint64_t* agReady[kMaxDevRanks];
@@ -92,7 +94,9 @@ struct GemmArgs {
     // only its reduced block.
     const __nv_bfloat16* xchgMc;
 };
-constexpr int kCtlEpoch = 0, kCtlTicket = 1, kCtlAbort = 2, kCtlReady = 16;
+constexpr int kCtlEpoch = 0, kCtlTicket = 1, kCtlAbort = 2, kCtlPushNext = 3, kCtlPushGo = 4, kCtlReady = 16;
+// agPush values
+constexpr int kAgPull = 0, kAgPushWorkers = 1, kAgPushCoop = 2;
 
 template <int BN>
 struct SmemLayout {
@@ -361,6 +365,126 @@ __device__ __forceinline__ void GatherPushWorker(const DevComm& c, const GemmArg
     StoreEpoch(c, worker, e + 1);
 }
 
+// AllGather, cooperative push form.  The epilogue warps of a GEMM CTA are idle for most of a tile's main loop (a
+// 256 x 256 x 8192 tile takes about 45 us, draining it a few), and a posted write needs no shared memory and almost no
+// issue slots.  So instead of giving 20-28 SMs to copy workers, every CTA computes and its four epilogue warps take
+// 32 KiB pieces of the local shard from a shared counter whenever no accumulator is waiting: destinations in the
+// order rank-1, rank-2, ... (the order in which the consumers need this rank's rows), pieces in address order, the
+// copy into this rank's own gathered buffer last.  After a piece the warp fences once and adds the bytes it wrote to
+// the destination's arrival counter of every 128-row block the piece touches.  At the start of the kernel all
+// epilogue warps are idle, which front-loads the transfer: the first remote rows reach their consumer long before the
+// tiles of its own shard are done.  One warp of CTA 0 runs the start barrier (every rank is inside the kernel: nobody
+// still reads its gathered buffer from earlier work, and its arrival counters are clear) and then opens the counter.
+constexpr uint32_t kPushPieceBytes = 32 * 1024;
+
+__device__ __forceinline__ bool MbarTestWait(uint64_t* bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(SmemAddr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Run by ONE warp of CTA 0 before its tile loop.
+__device__ __forceinline__ void CoopPushOpen(const DevComm& c, const GemmArgs& g, uint32_t launchEpoch, int lane)
+{
+    const uint64_t e = LoadEpoch(c, 0);
+    bool ok = true;
+    if (lane < c.nRanks) {
+        StReleaseSys(FlagPtr(c, lane, 0, 0, c.rank), e + 1);
+        ok = WaitFlagGE(c, FlagPtr(c, c.rank, 0, 0, lane), e + 1, K_MC2_AG_GEMM, 0, 0, lane);
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (lane == 0) {
+        *reinterpret_cast<volatile uint64_t*>(c.epochs) = e + 1;
+        if (!ok) *(g.ctl + kCtlAbort) = 1u;          // the GEMM CTAs must not wait for rows that will never arrive
+        else asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(g.ctl + kCtlPushGo), "r"(launchEpoch) : "memory");
+    }
+    __syncwarp();
+}
+
+// One piece, by one whole warp.  Returns 0 when every piece has been taken, 1 after copying one, 2 while the start
+// barrier has not completed yet.
+__device__ __forceinline__ int CoopPushStep(const GemmArgs& g, uint32_t launchEpoch, int lane)
+{
+    uint32_t go = 0, u = 0;
+    if (lane == 0) asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(go) : "l"(g.ctl + kCtlPushGo) : "memory");
+    go = __shfl_sync(0xffffffffu, go, 0);
+    if (go != launchEpoch) return 2;
+    const size_t blockBytes = (size_t)g.K * 2 * kBM;
+    const int blocksPerRank = g.mPerRank / kBM;
+    const size_t shardBytes = blockBytes * (size_t)blocksPerRank;
+    const uint32_t piecesPerDst = (uint32_t)((shardBytes + kPushPieceBytes - 1) / kPushPieceBytes);
+    const uint32_t total = piecesPerDst * (uint32_t)g.nRanks;
+    if (lane == 0) u = atomicAdd(g.ctl + kCtlPushNext, 1u);
+    u = __shfl_sync(0xffffffffu, u, 0);
+    if (u >= total) return 0;
+    const int it = (int)(u / piecesPerDst);
+    const int step = (it + 1) % g.nRanks;            // peers first, nearest consumer first; the local copy last
+    const int dstRank = (g.rank - step + g.nRanks) % g.nRanks;
+    const size_t s0 = (size_t)(u % piecesPerDst) * kPushPieceBytes;
+    const size_t s1 = s0 + kPushPieceBytes < shardBytes ? s0 + kPushPieceBytes : shardBytes;
+    const size_t nv = (s1 - s0) >> 4;                // the shard is a multiple of 16 bytes (K is a multiple of 8)
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(g.aPeer[g.rank]) + s0);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(g.gatheredPeer[dstRank]) + (size_t)g.rank * shardBytes + s0);
+    constexpr int U = 16;
+    for (size_t i = lane; i < nv; i += U * 32) {
+        uint4 v[U];
+#pragma unroll
+        for (int k = 0; k < U; ++k)
+            if (i + k * 32 < nv) v[k] = __ldg(src + i + k * 32);
+#pragma unroll
+        for (int k = 0; k < U; ++k)
+            if (i + k * 32 < nv) dst[i + k * 32] = v[k];
+    }
+    __syncwarp();
+    if (lane == 0) {
+        __threadfence_system();
+        for (size_t b = s0 / blockBytes; b * blockBytes < s1; ++b) {
+            const size_t lo = b * blockBytes > s0 ? b * blockBytes : s0;
+            const size_t hi = (b + 1) * blockBytes < s1 ? (b + 1) * blockBytes : s1;
+            uint64_t* flag = g.agReady[dstRank] + (size_t)g.rank * blocksPerRank + b;
+            asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(flag), "l"((uint64_t)(hi - lo)) : "memory");
+        }
+    }
+    __syncwarp();
+    return 1;
+}
+
+// Epilogue warp, cooperative push form: copies pieces until accumulator `bar` is ready (returns true) or no piece is
+// left (returns false: the caller goes on with plain waits).
+__device__ __forceinline__ bool CoopPushWhileWaiting(const GemmArgs& g, uint32_t launchEpoch, int lane, uint64_t* bar, uint32_t parity)
+{
+    for (;;) {
+        if (MbarTestWait(bar, parity)) return true;
+        const int r = CoopPushStep(g, launchEpoch, lane);
+        if (r == 0) return false;
+        if (r == 2 && *(volatile uint32_t*)(g.ctl + kCtlAbort) != 0u) return false;     // the plain wait that follows returns at once
+    }
+}
+
+// After its last tile an epilogue warp keeps copying until the pieces run out.  Bounded: gives up when the
+// communicator aborts or the start barrier stays closed for the wait limit.
+__device__ __forceinline__ void CoopPushDrain(const GemmArgs& g, uint32_t launchEpoch, int lane)
+{
+    volatile uint32_t* abortWord = g.ctl + kCtlAbort;
+    uint64_t t0 = 0;
+    for (;;) {
+        const int r = CoopPushStep(g, launchEpoch, lane);
+        if (r == 0) return;
+        if (r == 2) {
+            const uint64_t now = TimerNs();
+            if (t0 == 0) t0 = now;
+            if (*abortWord != 0u || now - t0 > kWaitLimitNs) return;
+        }
+    }
+}
+
 // One output tile of the ReduceScatter reduction: rows [mtLocal*128, +128) x cols [nt*BN, +BN), 16-byte vectors of
 // 8 bf16.  U vectors of every rank's partial are requested before any is consumed (16 loads in flight per
 // thread): the reduction is bound by bytes in flight from local memory, and a worker has to keep up with the tiles
@@ -626,9 +750,12 @@ __global__ void __launch_bounds__(kThreads, 1)
             uint32_t accPhase = 0;
             bool ok = true;
             const size_t parityOff = (launchEpoch & 1u) * g.xchgParityElems;
+            bool pushLeft = MODE == MODE_AG && g.agPush == kAgPushCoop;
+            if (pushLeft && cta == 0 && warp == 2) CoopPushOpen(c, g, launchEpoch, lane);
             for (int t = cta; t < nTiles && ok; t += g.nGemmCtas) {
                 int mt, nt;
                 TileCoord<MODE>(g, t, &mt, &nt);
+                if (MODE == MODE_AG && pushLeft) pushLeft = CoopPushWhileWaiting(g, launchEpoch, lane, &tmemFull[acc], accPhase);
                 ok = MbarWait(&tmemFull[acc], accPhase, abortWord, kWaitLimitNs);
                 if (!ok) break;
                 TcFenceAfter();
@@ -706,6 +833,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     }
                 }
             }
+            if (MODE == MODE_AG && pushLeft) CoopPushDrain(g, launchEpoch, lane);
         }
         // teardown: every role has left its loop (normally or by a bounded wait that ran out)
         TcFenceBefore();
@@ -729,6 +857,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     for (int i = 0; i < n; ++i) g.agReady[g.rank][i] = 0;      // peers write again only after the next start barrier
             }
             g.ctl[kCtlTicket] = 0;
+            g.ctl[kCtlPushNext] = 0;
             *reinterpret_cast<volatile uint32_t*>(g.ctl + kCtlEpoch) = launchEpoch;
             __threadfence();
         }

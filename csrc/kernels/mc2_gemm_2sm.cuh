@@ -263,10 +263,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             uint32_t accPhase = 0;
             bool ok = true;
             const size_t parityOff = (launchEpoch & 1u) * g.xchgParityElems;
+            bool pushLeft = MODE == MODE_AG && g.agPush == kAgPushCoop;
+            if (pushLeft && cta == 0 && warp == 2) CoopPushOpen(c, g, launchEpoch, lane);
             for (int t = pair; t < nTiles && ok; t += nPairs) {
                 int mt2, nt;
                 TileCoord2<MODE>(g, t, tilesM2, &mt2, &nt);
                 const int mt = mt2 * 2 + (int)crank;
+                if (MODE == MODE_AG && pushLeft) pushLeft = CoopPushWhileWaiting(g, launchEpoch, lane, &tmemFull[acc], accPhase);
                 ok = MbarWait(&tmemFull[acc], accPhase, abortWord, kWaitLimitNs);
                 if (!ok) break;
                 TcFenceAfter();
@@ -304,6 +307,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                     }
                 }
             }
+            if (MODE == MODE_AG && pushLeft) CoopPushDrain(g, launchEpoch, lane);
         }
         // teardown: nobody leaves while its peer may still touch its shared memory, barriers or TMEM
         TcFenceBefore();
@@ -327,6 +331,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                     for (int i = 0; i < n; ++i) g.agReady[g.rank][i] = 0;      // peers write again only after the next start barrier
             }
             g.ctl[kCtlTicket] = 0;
+            g.ctl[kCtlPushNext] = 0;
             *reinterpret_cast<volatile uint32_t*>(g.ctl + kCtlEpoch) = launchEpoch;
             __threadfence();
         }

@@ -359,7 +359,7 @@ HcclResult Mc2AllGatherMatmul(CommImpl* comm, const void* aShard, const void* b,
     for (int q = 0; q < comm->nRanks; ++q) g.aPeer[q] = (const __nv_bfloat16*)peers[q];
     g.gathered = (__nv_bfloat16*)gathered;
     if (push) {
-        g.agPush = 1;
+        g.agPush = kAgPushWorkers;
         g.aPeer[comm->rank] = (const __nv_bfloat16*)aShard;
         for (int q = 0; q < comm->nRanks; ++q) {
             g.gatheredPeer[q] = (__nv_bfloat16*)gathPeers[q];
@@ -367,12 +367,30 @@ HcclResult Mc2AllGatherMatmul(CommImpl* comm, const void* aShard, const void* b,
         }
     }
     const bool twoSm = Use2Sm() && mPerRank % 256 == 0;
-    const int workers = twoSm ? GatherWorkerCtas((g.M / 256) * g.tilesN, 2) : GatherWorkerCtas(g.tilesM * g.tilesN, 1);
     const int grid = SmCount() & ~1;
+    // Push form without worker CTAs (the default): every CTA computes, its epilogue warps copy the shard while they
+    // wait for accumulators.  HCCL_MC2_AG_WORKERS=<n> keeps n dedicated copy CTAs instead.
+    const bool coop = push && ForcedWorkers(true) == 0;
+    int workers = 0;
+    if (coop) g.agPush = kAgPushCoop;
+    else workers = twoSm ? GatherWorkerCtas((g.M / 256) * g.tilesN, 2) : GatherWorkerCtas(g.tilesM * g.tilesN, 1);
     g.nGemmCtas = grid - workers;
     if (twoSm) {
-        g.bn = 256;
-        CHK_RET(MapB(&tb, b, n, k, bMn, 128));
+        // column tile width: fewest (waves x width), as for the plain matmul; MN-major B is loaded in 64-column boxes
+        const int pairs = g.nGemmCtas / 2;
+        const int tilesM2 = g.M / 256;
+        int bestBn = 256;
+        double bestCost = 1e30;
+        for (int cand : {256, 224, 192, 160, 128}) {
+            if (bMn && (cand / 2) % 64 != 0) continue;
+            const int tn = (int)((n + cand - 1) / cand);
+            const int waves = (tilesM2 * tn + pairs - 1) / pairs;
+            const double cost = (double)waves * (cand + 12);
+            if (cost < bestCost - 1e-9) { bestCost = cost; bestBn = cand; }
+        }
+        g.bn = bestBn;
+        g.tilesN = (int)((n + bestBn - 1) / bestBn);
+        CHK_RET(MapB(&tb, b, n, k, bMn, bestBn / 2));
         return DispatchLayout2Sm<MODE_AG>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream, &taOwn);
     }
     return DispatchLayout<256, MODE_AG>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream, &taOwn);

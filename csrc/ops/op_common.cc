@@ -109,14 +109,16 @@ HcclResult SingleRank(CommImpl*, const OpParam& p)
 struct Exec {
     CommImpl* c;
     const OpParam& p;
+    const OpDesc& d;          // buffer facts every rank agrees on: whatever a peer can observe (where it reads this rank's data,
+                              // how many launches and blocks an operator takes) is derived from these, never from local lookups alone
     const AlgEntry* alg;
     DevAlg dalg;
     uint64_t es;
     int P, me;
     LaunchTarget tgt;
     const StageLayout& L;
-    Exec(CommImpl* comm, const OpParam& param, const AlgEntry* a)
-        : c(comm), p(param), alg(a), dalg((DevAlg)a->devAlg), es(DataTypeSize(param.dtype)), P(comm->nRanks), me(comm->rank),
+    Exec(CommImpl* comm, const OpParam& param, const OpDesc& desc, const AlgEntry* a)
+        : c(comm), p(param), d(desc), alg(a), dalg((DevAlg)a->devAlg), es(DataTypeSize(param.dtype)), P(comm->nRanks), me(comm->rank),
           tgt(comm->Target(param.stream)), L(comm->layout()) {}
 
     void FillStageIn(CollArgs& a) const { for (int q = 0; q < P; ++q) a.src[q] = c->StageBase(q) + L.inOff; a.srcMc = c->StageMcBase() ? c->StageMcBase() + L.inOff : nullptr; }
@@ -131,12 +133,15 @@ struct Exec {
         const bool isReduce = p.op == HCCL_CMD_REDUCE;
         const bool ll = dalg == DALG_AR_LL;
         RegInfo in = Reg(c, p.send, total), out = Reg(c, p.recv, total);
-        const bool inDirect = in.reg && Aligned16(p.send);
+        const bool inDirect = d.inRegistered && d.aligned16 && in.reg && Aligned16(p.send);
         const bool nvlsAlg = dalg == DALG_AR_NVLS;
-        // NVLS needs a multicast alias for its source; a registered buffer without one is staged
-        const bool useInDirect = inDirect && (!nvlsAlg || in.mc != nullptr) && !ll;
+        // NVLS needs a multicast alias for its source; a registered buffer without one is staged.  One-shot in place on
+        // a registered buffer would let a rank overwrite its input with sums while its peers still read it (every rank
+        // reads the whole message of every peer between the two barriers): that case is staged as well.
+        const bool useInDirect = inDirect && (!nvlsAlg || (d.inMulticast && in.mc != nullptr)) && !ll && !(dalg == DALG_AR_ONESHOT && d.inPlace);
         const bool outAligned = Aligned16(p.recv);
-        const bool pushOut = (dalg == DALG_AR_TWOSHOT || nvlsAlg) && out.reg && outAligned && (!nvlsAlg || out.mc != nullptr) && !isReduce;
+        const bool pushOut = (dalg == DALG_AR_TWOSHOT || nvlsAlg) && d.outRegistered && d.aligned16 && out.reg && outAligned &&
+                             (!nvlsAlg || (d.outMulticast && out.mc != nullptr)) && !isReduce;
         uint64_t chunk = total;
         if (!ll) {
             uint64_t limit = ~0ull;
@@ -187,9 +192,9 @@ struct Exec {
             inSpan = std::max(inSpan, dspB[q] + cntB[q]);
         }
         RegInfo in = Reg(c, p.send, inSpan);
-        bool inDirect = in.reg && Aligned16(p.send);
+        bool inDirect = d.inRegistered && d.aligned16 && in.reg && Aligned16(p.send);
         for (int q = 0; q < P && inDirect; ++q) inDirect = (dspB[q] & 15u) == 0;
-        if (dalg == DALG_RS_NVLS && in.mc == nullptr) inDirect = false;
+        if (dalg == DALG_RS_NVLS && (!d.inMulticast || in.mc == nullptr)) inDirect = false;
         uint64_t chunk = maxCnt;
         if (!inDirect) {
             const uint64_t limit = AlignDown(L.inBytes / (uint64_t)P, 128);
@@ -268,9 +273,8 @@ struct Exec {
         const uint64_t myBytes = p.count * es;
         RegInfo in = Reg(c, p.send, myBytes);
         const bool ll = dalg == DALG_AG_LL;
-        // a peer pulls block q from rank q's input, so "registered" has to hold on every rank: by contract HcclMemAlloc
-        // buffers are allocated collectively, and a rank that passes one here passes the same one everywhere
-        const bool inDirect = in.reg && !ll;
+        // a peer pulls block q from rank q's input, so "registered" has to hold on every rank: d.inRegistered does
+        const bool inDirect = d.inRegistered && in.reg && !ll;
         const bool inPlace = (const char*)p.send == (char*)p.recv + dspB[me];
         uint64_t chunk = std::max<uint64_t>(maxCnt, 1);
         if (!inDirect && !ll) {
@@ -305,10 +309,10 @@ struct Exec {
         const uint64_t total = p.count * es;
         RegInfo in = Reg(c, p.send, total);
         const bool nvlsAlg = dalg == DALG_BCAST_NVLS;
-        const bool inDirect = in.reg && !nvlsAlg;
+        const bool inDirect = d.inRegistered && in.reg && !nvlsAlg;
         uint64_t limit = ~0ull;
         if (!inDirect && !nvlsAlg) limit = std::min(limit, LoopBytes(L.inBytes, 1));
-        const bool nvlsDirect = nvlsAlg && in.reg && in.mc != nullptr && Aligned16(p.send);
+        const bool nvlsDirect = nvlsAlg && d.inRegistered && d.inMulticast && d.aligned16 && in.reg && in.mc != nullptr && Aligned16(p.send);
         if (dalg == DALG_BCAST_TWOSHOT || (nvlsAlg && !nvlsDirect)) limit = std::min(limit, LoopBytes(L.xchBytes, 1));
         if (limit == 0) return HCCL_E_MEMORY;
         const uint64_t chunk = std::min(total, limit);
@@ -324,7 +328,7 @@ struct Exec {
             else if (!nvlsAlg) { FillStageIn(a); a.mode |= MODE_STAGE_IN; }
             FillXch(a);
             if (nvlsAlg) {
-                if (in.reg && in.mc != nullptr && Aligned16(p.send)) {
+                if (nvlsDirect) {
                     a.mode |= MODE_PUSH;      // the buffer is symmetric with a multicast alias: store straight into it
                     a.dstMc = const_cast<char*>(in.mc) + off;
                     for (int q = 0; q < P; ++q) a.dst[q] = const_cast<char*>(in.peer[q]) + off;
@@ -387,19 +391,16 @@ struct Exec {
             staged += AlignUp(sendB[q], 16);
         }
         RegInfo in = Reg(c, p.send, span);
-        const bool inDirect = in.reg;
-        // Chunking needs a loop count all ranks agree on.  It is known for the uniform op and for VC (every rank holds
-        // the whole matrix, globalMaxBytes); for AlltoAllV it is not, so an unregistered AlltoAllV must fit the slab.
+        const bool inDirect = d.inRegistered && in.reg;
+        // Chunking on the host needs a loop count all ranks agree on.  It is known for the uniform op and for VC (every
+        // rank holds the whole matrix, globalMaxBytes); AlltoAllV counts are private to each rank, so a staged AlltoAllV
+        // hands the kernel the window size and the kernel derives the number of passes from all ranks' send sizes.
         uint64_t perPeerLimit = ~0ull;
         if (!inDirect) {
             perPeerLimit = AlignDown(L.inBytes / (uint64_t)P, 128);
             if (perPeerLimit == 0) return HCCL_E_MEMORY;
-            if (p.op == HCCL_CMD_ALLTOALLV && staged > L.inBytes) {
-                HCCL_ERROR("AlltoAllV: %llu bytes to send do not fit the %llu-byte staging region; allocate the send buffer with HcclMemAlloc or raise HCCL_BUFFSIZE",
-                           (unsigned long long)staged, (unsigned long long)L.inBytes);
-                return HCCL_E_MEMORY;
-            }
         }
+        (void)staged;
         uint64_t loops = 1, chunk = ~0ull;
         if (!inDirect && p.op != HCCL_CMD_ALLTOALLV && p.globalMaxBytes > perPeerLimit) {
             chunk = perPeerLimit;
@@ -422,7 +423,7 @@ struct Exec {
             a.bytes = traffic;
             FillXch(a);
             if (inDirect) { for (int q = 0; q < P; ++q) a.src[q] = in.peer[q]; }
-            else { FillStageIn(a); a.mode |= MODE_STAGE_IN; }
+            else { FillStageIn(a); a.mode |= MODE_STAGE_IN; if (p.op == HCCL_CMD_ALLTOALLV) a.chunk = perPeerLimit; }
             // every rank has to launch the same grid.  The uniform op and VC know the global sizes; AlltoAllV does
             // not (counts are private to each rank), so it always runs with a fixed grid.
             if (p.op == HCCL_CMD_ALLTOALLV) CHK_RET(LaunchCollective(tgt, dalg, p.dtype, a, std::min(c->MaxBlocks(), 32)));
@@ -517,18 +518,143 @@ OpDesc Describe(CommImpl* c, const OpParam& p)
     d.inMulticast = d.inRegistered && mcIn != nullptr;       // buffers registered with HcclCommRegister have no multicast alias
     d.outMulticast = d.outRegistered && mcOut != nullptr;
     d.aligned16 = Aligned16(p.send) && Aligned16(p.recv);
-    d.inPlace = p.send == p.recv;
+    // in place: the output overlaps the input (AllGather / ReduceScatter on a slice of the other buffer included)
+    const char* sb = (const char*)p.send;
+    const char* rb = (const char*)p.recv;
+    d.inPlace = sb != nullptr && rb != nullptr && sb < rb + outBytes && rb < sb + inBytes;
     return d;
 }
 
+// What identifies a call on every rank alike: everything selection looks at except the facts about this rank's own
+// buffers.  AlltoAllV counts are private to a rank, so its size is left out.
+uint64_t SharedSignature(const OpParam& p, const OpDesc& d, uint64_t generation)
+{
+    const bool privateSize = p.op == HCCL_CMD_ALLTOALLV;
+    const uint64_t fields[6] = {(uint64_t)p.op, (uint64_t)p.dtype, (uint64_t)p.redOp, (uint64_t)p.root, privateSize ? 0 : d.bytes, generation};
+    return Fnv1a(fields, sizeof(fields));
+}
+
+bool IsCollective(HcclCMDType op) { return op != HCCL_CMD_SEND && op != HCCL_CMD_RECEIVE && op != HCCL_CMD_BATCH_SEND_RECV; }
+
+// Ranks may be called with buffers that differ in registration, alignment or aliasing, and both the choice of an
+// algorithm and its launch shape depend on those facts; ranks that chose differently would wait for flags that never
+// come.  So the first time a rank meets a call signature it exchanges its flag word with all ranks (reference: ranks
+// exchange their execution configuration and take the lowest common one, op_common.cc:265-276, comm_negotiation.h:
+// 41-50) and everything a peer can observe is derived from the combined word, which the plan keeps.  A rank that
+// meets the signature with the same local facts again reuses the plan without talking to anybody.
+struct ShapeRecord { uint64_t signature; uint32_t flags; uint32_t pad; };
+HcclResult AgreeOnCallShape(CommImpl* c, const OpParam& p, uint64_t signature, uint32_t localFlags, uint32_t* agreed)
+{
+    *agreed = localFlags;
+    if (!c->bs || !IsCollective(p.op) || !GetEnvConfig().callShapeAgree) return HCCL_SUCCESS;
+    ShapeRecord mine = {signature, localFlags, 0};
+    std::vector<ShapeRecord> all((size_t)c->nRanks);
+    CHK_RET(c->bs->AllGather(&mine, all.data(), sizeof(mine)));
+    for (int r = 0; r < c->nRanks; ++r) {
+        if (all[(size_t)r].signature != signature) {
+            HCCL_ERROR("comm %s: rank %d and rank %d are not in the same operation (%s here): operator, data type, reduce op, root or count differ",
+                       c->name.c_str(), c->rank, r, CmdName(p.op));
+            return HCCL_E_PARA;
+        }
+        *agreed = OpDesc::CombineFlags(*agreed, all[(size_t)r].flags);
+    }
+    if (*agreed != localFlags)
+        HCCL_RUN_INFO("comm %s rank %d: %s runs on the buffer facts all ranks share (flags %#x, local %#x)", c->name.c_str(), c->rank, CmdName(p.op),
+                      *agreed, localFlags);
+    return HCCL_SUCCESS;
+}
+
 }  // namespace
+
+// Selection (or plan reuse) and execution of a described call.  `presetAgreed` carries the combined flag word when
+// the caller already knows it (emulated ranks, whose calls are collected first).
+HcclResult ExecDescribed(CommImpl* c, OpParam& p, OpDesc d, const uint32_t* presetAgreed)
+{
+    const auto t0 = std::chrono::steady_clock::now();
+    const uint32_t localFlags = d.Flags();
+    PlanKey key = {(uint32_t)p.op, (uint32_t)p.dtype, (uint32_t)p.redOp, p.root, d.bytes, localFlags, (uint32_t)c->generation};
+    Plan plan;
+    const AlgEntry* alg = nullptr;
+    // emulated ranks never cache: a plan's combined flags depend on what the OTHER ranks passed, which the key does not see
+    const bool cacheable = c->cfg.planCacheEnable && presetAgreed == nullptr;
+    if (cacheable && c->plans->Find(key, &plan)) {
+        alg = &AlgRegistry::Instance().All()[(size_t)plan.algIndex];
+        d.ApplyFlags(plan.agreedFlags);
+    } else {
+        uint32_t agreed = localFlags;
+        if (presetAgreed != nullptr) agreed = *presetAgreed;
+        else CHK_RET(AgreeOnCallShape(c, p, SharedSignature(p, d, c->generation), localFlags, &agreed));
+        d.ApplyFlags(agreed);
+        Selection sel;
+        CHK_RET(SelectAlgorithm(*c->selector, *c->topo, GetEnvConfig(), d, c->name, (HcclComm)c, c->cfg.bufferBytes, &sel));
+        alg = sel.alg;
+        plan.algIndex = sel.algIndex;
+        plan.devAlg = alg->devAlg;
+        plan.agreedFlags = agreed;
+        if (cacheable) c->plans->Insert(key, plan);
+    }
+    p.algName = alg->name;
+    c->ctx.Put("last_alg", std::vector<uint8_t>(alg->name.begin(), alg->name.end()));
+    ProfilingScope prof(c, p, alg->name.c_str(), d.bytes);
+    HcclResult r = Exec(c, p, d, alg).Run();
+    if (r != HCCL_SUCCESS) HCCL_ERROR("comm %s rank %d: %s with algorithm %s failed: %s", c->name.c_str(), c->rank, CmdName(p.op), alg->name.c_str(), ResultString(r));
+    prof.SetHostUs(std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count());
+    return r;
+}
+
+OpDesc DescribeCall(CommImpl* c, const OpParam& p) { return Describe(c, p); }
+
+struct EmuGroup::PendingOp { OpParam p; };
+
+HcclResult EmuSubmitCollective(CommImpl* c, const OpParam& p)
+{
+    EmuGroup* g = c->emuGroup();
+    std::lock_guard<std::mutex> lk(g->opMu);
+    const int n = g->nRanks();
+    std::shared_ptr<EmuGroup::PendingOp> mine(new EmuGroup::PendingOp{p});
+    g->pendingOps[(size_t)c->rank].push_back(mine);
+    HcclResult result = HCCL_SUCCESS;
+    for (;;) {
+        for (int r = 0; r < n; ++r)
+            if (g->pendingOps[(size_t)r].empty()) return result;
+        std::vector<std::shared_ptr<EmuGroup::PendingOp>> ops;
+        for (int r = 0; r < n; ++r) { ops.push_back(g->pendingOps[(size_t)r].front()); g->pendingOps[(size_t)r].pop_front(); }
+        // the same operator everywhere (the multi-process path compares this over the bootstrap on the first call)
+        std::vector<OpDesc> descs;
+        uint32_t agreed = 0;
+        const OpParam& first = ops[0]->p;
+        for (int r = 0; r < n; ++r) {
+            const OpParam& q = ops[(size_t)r]->p;
+            const bool countMustMatch = q.op != HCCL_CMD_ALLTOALLV && q.op != HCCL_CMD_ALLGATHER_V && q.op != HCCL_CMD_REDUCE_SCATTER_V;
+            if (q.op != first.op || q.dtype != first.dtype || q.redOp != first.redOp || q.root != first.root || (countMustMatch && q.count != first.count)) {
+                HCCL_ERROR("emulated ranks 0 and %d are not in the same operation (%s vs %s, count %llu vs %llu)", r, CmdName(first.op), CmdName(q.op),
+                           (unsigned long long)first.count, (unsigned long long)q.count);
+                return HCCL_E_PARA;
+            }
+            descs.push_back(Describe(g->members[(size_t)r], q));
+            agreed = r == 0 ? descs.back().Flags() : OpDesc::CombineFlags(agreed, descs.back().Flags());
+        }
+        for (int r = 0; r < n; ++r) {
+            HcclResult e = ExecDescribed(g->members[(size_t)r], ops[(size_t)r]->p, descs[(size_t)r], &agreed);
+            if (e != HCCL_SUCCESS) result = e;
+        }
+    }
+}
 
 HcclResult ExecOp(CommImpl* c, OpParam& p)
 {
     CHK_PTR_NULL(c);
     CHK_RET(c->CheckReady());
+    // ranks emulated on one GPU are called one after the other: their collectives are queued and run together once
+    // the last rank has called, when every rank's buffer facts are known (the group's own lock serialises them)
+    if (c->emulated() && c->nRanks > 1 && !c->hostComm && IsCollective(p.op)) {
+        HcclResult emuErr;
+        c->PollAsyncError(&emuErr);
+        if (emuErr != HCCL_SUCCESS) return emuErr;
+        ++c->opCount;
+        return EmuSubmitCollective(c, p);
+    }
     std::lock_guard<std::mutex> lk(c->opMu);
-    const auto t0 = std::chrono::steady_clock::now();
     HcclResult asyncErr;
     c->PollAsyncError(&asyncErr);
     if (asyncErr != HCCL_SUCCESS) return asyncErr;
@@ -550,27 +676,7 @@ HcclResult ExecOp(CommImpl* c, OpParam& p)
     if (c->hostComm) return HostExecOp(c, p);       // host engine communicators run the algorithm templates on host threads
     if (c->nRanks == 1) return SingleRank(c, p);
     CHK_RET(FirstCallCheck(c, p));
-    OpDesc d = Describe(c, p);
-    PlanKey key = {(uint32_t)p.op, (uint32_t)p.dtype, (uint32_t)p.redOp, p.root, d.bytes, d.Flags(), (uint32_t)c->generation};
-    Plan plan;
-    const AlgEntry* alg = nullptr;
-    const bool cacheable = c->cfg.planCacheEnable;
-    if (cacheable && c->plans->Find(key, &plan)) {
-        alg = &AlgRegistry::Instance().All()[(size_t)plan.algIndex];
-    } else {
-        Selection sel;
-        CHK_RET(SelectAlgorithm(*c->selector, *c->topo, GetEnvConfig(), d, c->name, (HcclComm)c, c->cfg.bufferBytes, &sel));
-        alg = sel.alg;
-        plan.algIndex = sel.algIndex;
-        plan.devAlg = alg->devAlg;
-        if (cacheable) c->plans->Insert(key, plan);
-    }
-    p.algName = alg->name;
-    ProfilingScope prof(c, p, alg->name.c_str(), d.bytes);
-    HcclResult r = Exec(c, p, alg).Run();
-    if (r != HCCL_SUCCESS) HCCL_ERROR("comm %s rank %d: %s with algorithm %s failed: %s", c->name.c_str(), c->rank, CmdName(p.op), alg->name.c_str(), ResultString(r));
-    prof.SetHostUs(std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count());
-    return r;
+    return ExecDescribed(c, p, Describe(c, p), nullptr);
 }
 
 }  // namespace hccl

@@ -33,4 +33,12 @@ struct OpParam {
 
 HcclResult ExecOp(CommImpl* comm, OpParam& p);
 
+// The two halves of ExecOp for callers that collect the calls of several ranks first (ranks emulated on one GPU):
+// what this rank's call looks like to the selector, and selection + execution on the flag word all ranks share.
+OpDesc DescribeCall(CommImpl* comm, const OpParam& p);
+HcclResult ExecDescribed(CommImpl* comm, OpParam& p, OpDesc d, const uint32_t* presetAgreedFlags);
+// Queues a collective of an emulated rank; once every rank of the group has one queued, combines their flag words and
+// runs them all.  Returns the result of the calls it ran (success while others are still missing).
+HcclResult EmuSubmitCollective(CommImpl* comm, const OpParam& p);
+
 }  // namespace hccl

@@ -10,6 +10,26 @@
 
 namespace hccl {
 
+// Bits of Flags() that describe THIS rank's buffers; the rest is communicator-wide.
+constexpr uint32_t kCapabilityBits = 1u | 2u | 4u | (1u << 20) | (1u << 21);
+constexpr uint32_t kInPlaceBit = 8u;
+
+uint32_t OpDesc::CombineFlags(uint32_t a, uint32_t b)
+{
+    // a capability holds for the call only when every rank has it; one rank working in place makes the call in place
+    return (a & b & kCapabilityBits) | ((a | b) & kInPlaceBit) | (a & ~(kCapabilityBits | kInPlaceBit));
+}
+
+void OpDesc::ApplyFlags(uint32_t f)
+{
+    inRegistered = (f & 1u) != 0;
+    outRegistered = (f & 2u) != 0;
+    aligned16 = (f & 4u) != 0;
+    inPlace = (f & 8u) != 0;
+    inMulticast = (f & (1u << 20)) != 0;
+    outMulticast = (f & (1u << 21)) != 0;
+}
+
 uint32_t OpDesc::Flags() const
 {
     return (inRegistered ? 1u : 0u) | (outRegistered ? 2u : 0u) | (aligned16 ? 4u : 0u) | (inPlace ? 8u : 0u) | (inMulticast ? (1u << 20) : 0u) |

@@ -50,6 +50,10 @@ struct OpDesc {
     Deterministic det = Deterministic::OFF;
     HcclCommEngine engine = HCCL_ENGINE_AUTO;   // requested engine (HCCL_OP_EXPANSION_MODE / comm config)
     uint32_t Flags() const;
+    // What all ranks can rely on when their local flag words are `a` and `b` (associative, commutative): registration,
+    // multicast and alignment only if both have them, in place if either works in place.
+    static uint32_t CombineFlags(uint32_t a, uint32_t b);
+    void ApplyFlags(uint32_t flags);    // overwrites the per-buffer facts with those of a (combined) flag word
 };
 
 enum class NetType : int { LOCAL = 0, MESH_P2P = 1, NVLS_SWITCH = 2, HOST_MEM = 3 };

@@ -99,7 +99,8 @@ def scenario_mc2(comm, rank, world):
     from hccl_b200.ops import mc2
 
     torch.manual_seed(1234)      # every rank builds all operands: the reference is computed locally in fp32
-    for (m_per, n, k) in ((128, 256, 256), (256, 768, 512), (512, 1024, 1024)):
+    # the last two shapes take narrower column tiles (fewest waves x width): 160 and 224 columns at two ranks
+    for (m_per, n, k) in ((128, 256, 256), (256, 768, 512), (512, 1024, 1024), (512, 1280, 512), (2048, 7168, 256)):
         shards = [(torch.randn(m_per, k, device="cuda") * 0.5).bfloat16() for _ in range(world)]
         w = (torch.randn(n, k, device="cuda") * 0.1).bfloat16()          # [N, K]
         a = comm.empty((m_per, k), torch.bfloat16)
@@ -113,7 +114,8 @@ def scenario_mc2(comm, rank, world):
             err = (out.float() - ref).abs().max().item()
             assert err <= 2e-2 * ref.abs().max().item() + 1e-2, f"AG-matmul err {err}"
         g_sym = comm.empty((m_per * world, k), torch.bfloat16)
-        for rep in range(3):          # push form: the gathered buffer is symmetric memory, the shard is a plain tensor
+        for rep in range(3):          # push form: the gathered buffer is symmetric memory, the shard is a plain tensor;
+            # no worker CTAs (the epilogue warps copy) unless HCCL_MC2_AG_WORKERS asks for them
             g_sym.zero_()
             torch.cuda.synchronize()
             out, gathered = mc2.all_gather_matmul(comm, shards[rank], w, gathered=g_sym)
@@ -138,6 +140,16 @@ def scenario_mc2(comm, rank, world):
         torch.cuda.synchronize()
         err = (out.float() - ref[rank * m_per:(rank + 1) * m_per]).abs().max().item()
         assert err <= 3e-2 * ref.abs().max().item() + 2e-2, f"matmul-RS (KN) err {err}"
+        # the backward form of the row-parallel layer: gathered dy times a [K, N] weight
+        Wkn0 = Ws[0].t().contiguous()                        # [k, n]: A [M, k] x [k, n]
+        g_sym.zero_()
+        out, gathered = mc2.all_gather_matmul(comm, shards[rank], Wkn0, weight_is_kn=True, gathered=g_sym)
+        torch.cuda.synchronize()
+        ref = full.float() @ Wkn0.float()
+        err = (out.float() - ref).abs().max().item()
+        assert torch.equal(gathered, full) and err <= 2e-2 * ref.abs().max().item() + 1e-2, f"AG-matmul (KN, push) err {err}"
+        comm.free(g_sym)
+        comm.free(a)
         if rank == 0:
             print(f"mc2 ok m_per={m_per} n={n} k={k}", flush=True)
     # matmul -> all-reduce, decode shapes
@@ -244,6 +256,68 @@ def scenario_register(comm, rank, world):
     comm.all_reduce(src, dst[:n])                  # still works, staged again
     torch.cuda.synchronize()
     torch.testing.assert_close(dst[:n], torch.stack(xs).sum(0), rtol=1e-5, atol=1e-5)
+    assert comm.async_error() == hb.Result.SUCCESS
+
+
+def scenario_skew(comm, rank, world):
+    """Ranks out of step and buffers that differ from rank to rank.
+    * runs of small broadcasts while the receivers lag behind the root (the flag-in-data form: a root must not run
+      over lines a receiver has not read);
+    * in-place AllReduce on symmetric memory at sizes that select the one-shot form;
+    * one rank with a 4-byte aligned view, the others with 16-byte aligned tensors;
+    * AlltoAllV on ordinary buffers four times the staging window."""
+    n = 1024
+    busy = torch.empty(1 << 26, device="cuda")
+    for rep in range(3):
+        bufs = []
+        for it in range(6):
+            root = (rep + it) % world
+            b = rnd(n, torch.float32, 1000 + 10 * rep + it) if rank == root else torch.zeros(n, device="cuda")
+            if rank != root:
+                for _ in range(3):
+                    busy.add_(1.0)                   # the receivers' stream is behind the root's
+            comm.broadcast(b, root)
+            bufs.append(b)
+        torch.cuda.synchronize()
+        for it, b in enumerate(bufs):
+            assert torch.equal(b, rnd(n, torch.float32, 1000 + 10 * rep + it)), f"broadcast {rep}/{it}"
+    assert comm.async_error() == hb.Result.SUCCESS
+    for dtype in (torch.float32, torch.bfloat16):
+        for m in (8, 3000, 40000, 300000, 1 << 21):
+            xs = [rnd(m, dtype, 20 + r) for r in range(world)]
+            x = comm.empty((m,), dtype)
+            for rep in range(3):
+                x.copy_(xs[rank])
+                if rank % 2 == 1:
+                    busy.add_(1.0)
+                comm.all_reduce(x)
+                torch.cuda.synchronize()
+                tol = 3e-2 if dtype == torch.bfloat16 else 1e-5
+                torch.testing.assert_close(x.double(), torch.stack([t.double() for t in xs]).sum(0), rtol=tol, atol=tol * world)
+            if rank == 0:
+                print(f"in-place symmetric {dtype} n={m}: {comm.last_algorithm()}", flush=True)
+            comm.free(x)
+    for m in (1000, 100000, 1 << 21):
+        xs = [rnd(m + 4, torch.float32, 60 + r) for r in range(world)]
+        x = xs[rank][1:1 + m] if rank == 1 else xs[rank][:m]
+        y = torch.empty(m + 4, device="cuda")[(1 if rank == 1 else 0):][:m]
+        comm.all_reduce(x, y)
+        torch.cuda.synchronize()
+        want = torch.stack([(t[1:1 + m] if r == 1 else t[:m]).double() for r, t in enumerate(xs)]).sum(0)
+        torch.testing.assert_close(y.double(), want, rtol=1e-5, atol=1e-5)
+    unit = (64 << 20) // world          # elements of 4 bytes: 4x a pair's window of the 64 MiB slab
+    sc = [[unit // 2 + 100 * ((r + 2 * q) % 5) + 3 for q in range(world)] for r in range(world)]
+    rc = [sc[q][rank] for q in range(world)]
+    sd = [sum(sc[rank][:q]) for q in range(world)]
+    rd = [sum(rc[:q]) for q in range(world)]
+    src = rnd(sum(sc[rank]), torch.float32, 700 + rank)
+    out = torch.zeros(sum(rc), device="cuda")
+    comm.all_to_all_v(src, sc[rank], sd, out, rc, rd)
+    torch.cuda.synchronize()
+    for q in range(world):
+        peer = rnd(sum(sc[q]), torch.float32, 700 + q)
+        off = sum(sc[q][:rank])
+        assert torch.equal(out[rd[q]:rd[q] + rc[q]], peer[off:off + sc[q][rank]]), f"alltoallv block {q}->{rank}"
     assert comm.async_error() == hb.Result.SUCCESS
 
 
@@ -379,7 +453,7 @@ def main():
     info = rendezvous(rank, path)
     timeout_ms = 3000 if scenario == "peer_exit" else 0
     comm = Communicator.from_root_info(info, rank, world, hb.make_config(buffer_mib=64, exec_timeout_ms=timeout_ms))
-    {"collectives": scenario_collectives, "peer_exit": scenario_peer_exit, "mc2": scenario_mc2, "graph": scenario_graph,
+    {"collectives": scenario_collectives, "skew": scenario_skew, "peer_exit": scenario_peer_exit, "mc2": scenario_mc2, "graph": scenario_graph,
      "register": scenario_register}[scenario](comm, rank, world)
     comm.destroy()
     print(f"rank {rank} done", flush=True)

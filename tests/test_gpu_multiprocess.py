@@ -49,6 +49,13 @@ def test_collectives_multiprocess_p2p_only():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+@pytest.mark.parametrize("nvls", ["0", "1"])
+def test_ranks_out_of_step_and_buffers_that_differ_per_rank(nvls):
+    codes, outs = _run(_world(), "skew", {"HCCL_NVLS_ENABLE": nvls})
+    assert all(c == 0 for c in codes), "\n".join(outs)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
 def test_peer_exit_is_detected():
     # NVLS off and plain peer loads: a rank that dies while bound to a multicast object can fault its peers
     codes, outs = _run(min(_world(), 4), "peer_exit", {"HCCL_NVLS_ENABLE": "0", "NCCL_NVLS_ENABLE": "0"}, timeout=120)
@@ -65,6 +72,13 @@ def test_mc2_fused_multiprocess():
 def test_mc2_fused_multiprocess_peer_to_peer_reduce_scatter():
     # Matmul->ReduceScatter without the switch reduction: partial tiles pushed to the owner, reduced by worker CTAs
     codes, outs = _run(_world(), "mc2", {"HCCL_MC2_RS_P2P": "1"})
+    assert all(c == 0 for c in codes), "\n".join(outs)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_mc2_fused_multiprocess_with_copy_worker_ctas():
+    # AllGather->Matmul push form with dedicated copy CTAs instead of the epilogue warps
+    codes, outs = _run(_world(), "mc2", {"HCCL_MC2_AG_WORKERS": "16"})
     assert all(c == 0 for c in codes), "\n".join(outs)
 
 
