@@ -30,7 +30,7 @@ $PY hccl_b200/build.py $force
 if [ $asan -eq 1 ]; then $PY hccl_b200/build.py --asan; fi
 if [ $ut -eq 1 ]; then
   $PY -m pytest -q -m "not gpu" tests/test_unit_tables_config_selector.py tests/test_verifier_selftests.py tests/test_cpu_python_layers.py \
-      tests/test_graph_mode_api.py tests/test_examples_build.py tests/test_tuner_workflow.py
+      tests/test_graph_mode_api.py tests/test_examples_build.py tests/test_tuner_workflow.py tests/test_kernel_harness_cpu.py
 fi
 if [ $st -eq 1 ]; then
   $PY -m pytest -q -m "not gpu" tests/test_host_engine.py tests/test_host_executors.py tests/test_host_retry.py

@@ -10,6 +10,8 @@
 #include <algorithm>
 #include <cstring>
 #include <map>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include "../core/log.h"
 #include "../ops/op_common.h"
@@ -99,6 +101,94 @@ HcclResult HcclReduceScatter(void* sendBuf, void* recvBuf, uint64_t recvCount, H
     OpParam p;
     Fill(p, HCCL_CMD_REDUCE_SCATTER, C(comm), sendBuf, recvBuf, recvCount, dataType, op, 0, stream);
     return Finish(C(comm), p);
+}
+
+// ---- reductions fused with a cast and a scale ------------------------------------------------------------------
+namespace {
+bool IsCastType(HcclDataType t) { return t == HCCL_DATA_TYPE_FP32 || t == HCCL_DATA_TYPE_BFP16 || t == HCCL_DATA_TYPE_FP16; }
+float LoadAs(const void* p, HcclDataType t, uint64_t i)
+{
+    switch (t) {
+        case HCCL_DATA_TYPE_FP32: return static_cast<const float*>(p)[i];
+        case HCCL_DATA_TYPE_BFP16: return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+        default: return __half2float(static_cast<const __half*>(p)[i]);
+    }
+}
+void StoreAs(void* p, HcclDataType t, uint64_t i, float v)
+{
+    switch (t) {
+        case HCCL_DATA_TYPE_FP32: static_cast<float*>(p)[i] = v; break;
+        case HCCL_DATA_TYPE_BFP16: static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v); break;
+        default: static_cast<__half*>(p)[i] = __float2half_rn(v); break;
+    }
+}
+HcclResult CheckEx(const char* what, HcclDataType inType, HcclDataType outType, float scale)
+{
+    if (!IsCastType(inType) || !IsCastType(outType)) {
+        HCCL_ERROR("%s: input and output types must be fp32, bf16 or fp16 (got %s -> %s)", what, DataTypeName(inType), DataTypeName(outType));
+        return HCCL_E_NOT_SUPPORT;
+    }
+    if (!(scale == scale) || scale == 0.0f) { HCCL_ERROR("%s: scale must be a non-zero number", what); return HCCL_E_PARA; }
+    return HCCL_SUCCESS;
+}
+}  // namespace
+
+HcclResult HcclAllReduceEx(void* sendBuf, void* recvBuf, uint64_t count, HcclDataType inType, HcclDataType outType, HcclReduceOp op, float scale,
+                           HcclComm comm, hcclStream_t stream)
+{
+    CHK_PTR_NULL(comm);
+    if (count == 0) return HCCL_SUCCESS;
+    CHK_PTR_NULL(sendBuf);
+    CHK_PTR_NULL(recvBuf);
+    CHK_RET(CheckCount("HcclAllReduceEx", count));
+    CHK_RET(CheckEx("HcclAllReduceEx", inType, outType, scale));
+    CHK_RET(CheckReduceOp("HcclAllReduceEx", inType, op));
+    if (inType == outType && scale == 1.0f) return HcclAllReduce(sendBuf, recvBuf, count, inType, op, comm, stream);
+    CommImpl* c = C(comm);
+    if (c->hostComm || c->nRanks == 1) {
+        // host engine (and the single-rank shortcut): the plain operator, then cast and scale on the host / by a copy kernel
+        if (c->hostComm) {
+            std::vector<char> tmp(count * DataTypeSize(inType));
+            CHK_RET(HcclAllReduce(sendBuf, tmp.data(), count, inType, op, comm, stream));
+            for (uint64_t i = 0; i < count; ++i) StoreAs(recvBuf, outType, i, LoadAs(tmp.data(), inType, i) * scale);
+            return HCCL_SUCCESS;
+        }
+        HCCL_ERROR("HcclAllReduceEx needs more than one rank on a device communicator");
+        return HCCL_E_NOT_SUPPORT;
+    }
+    OpParam p;
+    Fill(p, HCCL_CMD_ALLREDUCE, c, sendBuf, recvBuf, count, inType, op, 0, stream);
+    p.castScale = true;
+    p.outType = outType;
+    p.scale = scale;
+    return Finish(c, p);
+}
+
+HcclResult HcclReduceScatterEx(void* sendBuf, void* recvBuf, uint64_t recvCount, HcclDataType inType, HcclDataType outType, HcclReduceOp op,
+                               float scale, HcclComm comm, hcclStream_t stream)
+{
+    CHK_PTR_NULL(comm);
+    if (recvCount == 0) return HCCL_SUCCESS;
+    CHK_PTR_NULL(sendBuf);
+    CHK_PTR_NULL(recvBuf);
+    CommImpl* c = C(comm);
+    CHK_RET(CheckCount("HcclReduceScatterEx", recvCount * (uint64_t)c->nRanks));
+    CHK_RET(CheckEx("HcclReduceScatterEx", inType, outType, scale));
+    CHK_RET(CheckReduceOp("HcclReduceScatterEx", inType, op));
+    if (inType == outType && scale == 1.0f) return HcclReduceScatter(sendBuf, recvBuf, recvCount, inType, op, comm, stream);
+    if (c->hostComm) {
+        std::vector<char> tmp(recvCount * DataTypeSize(inType));
+        CHK_RET(HcclReduceScatter(sendBuf, tmp.data(), recvCount, inType, op, comm, stream));
+        for (uint64_t i = 0; i < recvCount; ++i) StoreAs(recvBuf, outType, i, LoadAs(tmp.data(), inType, i) * scale);
+        return HCCL_SUCCESS;
+    }
+    if (c->nRanks == 1) { HCCL_ERROR("HcclReduceScatterEx needs more than one rank on a device communicator"); return HCCL_E_NOT_SUPPORT; }
+    OpParam p;
+    Fill(p, HCCL_CMD_REDUCE_SCATTER, c, sendBuf, recvBuf, recvCount, inType, op, 0, stream);
+    p.castScale = true;
+    p.outType = outType;
+    p.scale = scale;
+    return Finish(c, p);
 }
 
 HcclResult HcclReduceScatterV(void* sendBuf, const void* sendCounts, const void* sendDispls, void* recvBuf, uint64_t recvCount,

@@ -213,6 +213,7 @@ HcclResult HcclSelectorExplain(HcclComm comm, HcclCMDType op, uint64_t count, Hc
     d.bytes = count * es;
     if (op == HCCL_CMD_ALLGATHER || op == HCCL_CMD_REDUCE_SCATTER || op == HCCL_CMD_SCATTER || op == HCCL_CMD_ALLTOALL) d.bytes *= (uint64_t)c->nRanks;
     d.inRegistered = d.outRegistered = registered != 0;
+    d.stageInBytes = c->layout().inBytes;
     d.inMulticast = d.outMulticast = registered != 0 && c->nvls();      // "registered" here means HcclMemAlloc memory
     Selection sel;
     HcclResult r = SelectAlgorithm(*c->selector, *c->topo, GetEnvConfig(), d, c->name, comm, c->cfg.bufferBytes, &sel);
@@ -236,6 +237,7 @@ HcclResult HcclCalcOpResource(HcclComm comm, HcclCMDType op, uint64_t count, Hcc
     const bool perRank = op == HCCL_CMD_ALLGATHER || op == HCCL_CMD_REDUCE_SCATTER || op == HCCL_CMD_SCATTER || op == HCCL_CMD_ALLTOALL;
     d.bytes = count * es * (perRank ? P : 1);
     d.inRegistered = d.outRegistered = registered != 0;
+    d.stageInBytes = c->layout().inBytes;
     d.inMulticast = d.outMulticast = registered != 0 && c->nvls();      // "registered" here means HcclMemAlloc memory
     Selection sel;
     CHK_RET(SelectAlgorithm(*c->selector, *c->topo, GetEnvConfig(), d, c->name, comm, c->cfg.bufferBytes, &sel));

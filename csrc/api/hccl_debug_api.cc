@@ -158,6 +158,7 @@ HcclResult HcclDebugExplainDevice(uint32_t nRanks, int nvls, HcclCMDType op, uin
     d.det = deterministic == 2 ? Deterministic::STRICT : deterministic == 1 ? Deterministic::ON : Deterministic::OFF;
     d.inRegistered = d.outRegistered = registered != 0;
     d.inMulticast = d.outMulticast = registered != 0 && nvls != 0;
+    d.stageInBytes = 100ull << 20;          // the stage-in region of the default 256 MiB slab
     SelectorState st;
     Selection sel;
     const HcclResult r = SelectAlgorithm(st, topo, GetEnvConfig(), d, "synthetic", nullptr, 256ull << 20, &sel);

@@ -95,7 +95,9 @@ void Reduce16(void* dst, const void* src, uint64_t n, HcclReduceOp op)
     for (uint64_t i = 0; i < n; ++i) d[i] = S(Apply<float>(L(d[i]), L(s[i]), op));
 }
 
-void HostReduceBytes(void* dst, const void* src, uint64_t bytes, HcclDataType dt, HcclReduceOp op)
+// false: the host engine has no reduction for this data type (the caller fails the operator instead of returning
+// unreduced data)
+bool HostReduceBytes(void* dst, const void* src, uint64_t bytes, HcclDataType dt, HcclReduceOp op)
 {
     const uint64_t n = bytes / DataTypeSize(dt);
     switch (dt) {
@@ -108,8 +110,9 @@ void HostReduceBytes(void* dst, const void* src, uint64_t bytes, HcclDataType dt
         case HCCL_DATA_TYPE_FP64: ReduceTyped<double>(dst, src, n, op); break;
         case HCCL_DATA_TYPE_FP16: Reduce16<HalfToFloat, FloatToHalf>(dst, src, n, op); break;
         case HCCL_DATA_TYPE_BFP16: Reduce16<Bf16ToFloat, FloatToBf16>(dst, src, n, op); break;
-        default: break;
+        default: return false;
     }
+    return true;
 }
 
 }  // namespace
@@ -325,7 +328,10 @@ void HostPrims::Reduce(Mem dst, Mem src, uint64_t bytes, uint32_t queue)
     }
     Record(t);
     const HostOpDesc& d = w_->CurrentOp();
-    HostReduceBytes(w_->Resolve(dst), w_->Resolve(src), bytes, d.dtype, d.redOp);
+    if (!HostReduceBytes(w_->Resolve(dst), w_->Resolve(src), bytes, d.dtype, d.redOp)) {
+        failed_ = true;
+        w_->Abort(std::string("the host engine cannot reduce data type ") + DataTypeName(d.dtype));
+    }
 }
 
 void HostPrims::Post(uint32_t peer, uint32_t idx, uint32_t queue)

@@ -21,6 +21,17 @@ HcclResult HcclCommInitHostSim(uint32_t nRanks, const char* topoJson, const Hccl
 HcclResult HcclCommInitEmulated(uint32_t nRanks, const HcclCommConfig* config, HcclComm* comms);
 
 // Name of the algorithm the last operator on this communicator ran with.
+/* Reductions fused with a data type cast and a scale: out[i] = (outType)(scale * reduce_r in_r[i]), accumulated in fp32.
+ * inType and outType are each one of fp32, bf16, fp16.  Typical uses: averaging gradients (scale = 1 / ranks) without
+ * a second pass, reducing bf16 gradients into an fp32 master copy, reducing fp32 partials into a bf16 tensor.  The
+ * nearest analogue in the reference widens hif8 to float, reduces and narrows again inside one ReduceScatter kernel
+ * (aiv_reduce_scatter_mesh_1d_hif8.h).  The output needs count (AllReduce) or recvCount (ReduceScatter) elements of
+ * outType; an output that overlaps the input is only allowed when the types have the same size. */
+HcclResult HcclAllReduceEx(void* sendBuf, void* recvBuf, uint64_t count, HcclDataType inType, HcclDataType outType, HcclReduceOp op, float scale,
+                           HcclComm comm, hcclStream_t stream);
+HcclResult HcclReduceScatterEx(void* sendBuf, void* recvBuf, uint64_t recvCount, HcclDataType inType, HcclDataType outType, HcclReduceOp op,
+                               float scale, HcclComm comm, hcclStream_t stream);
+
 HcclResult HcclGetLastAlgName(HcclComm comm, char* name, uint32_t capacity);
 // Runs selection for a hypothetical call and writes the cost table as text.
 HcclResult HcclSelectorExplain(HcclComm comm, HcclCMDType op, uint64_t count, HcclDataType dataType,

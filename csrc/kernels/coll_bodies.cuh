@@ -229,11 +229,34 @@ __device__ __forceinline__ char* LLSlot(const DevComm& c, int owner, int parity,
 {
     return c.slab[owner] + kSlabLLOff + ((size_t)(parity * kMaxDevRanks + writer)) * kLLSlotBytes;
 }
+#ifdef HCCL_HOST_SHIM
+// a line is two 8-byte halves {data, flag}; each half is written and read as one atomic unit, as the 16-byte
+// volatile vector access is on the GPU
+inline void LLStore(char* line, uint32_t d0, uint32_t d1, uint32_t flag)
+{
+    __atomic_store_n(reinterpret_cast<uint64_t*>(line), (uint64_t)d0 | ((uint64_t)flag << 32), __ATOMIC_RELAXED);
+    __atomic_store_n(reinterpret_cast<uint64_t*>(line) + 1, (uint64_t)d1 | ((uint64_t)flag << 32), __ATOMIC_RELAXED);
+}
+inline uint4 LLPeek(const char* line)
+{
+    const uint64_t lo = __atomic_load_n(reinterpret_cast<const uint64_t*>(line), __ATOMIC_RELAXED);
+    const uint64_t hi = __atomic_load_n(reinterpret_cast<const uint64_t*>(line) + 1, __ATOMIC_RELAXED);
+    return make_uint4((uint32_t)lo, (uint32_t)(lo >> 32), (uint32_t)hi, (uint32_t)(hi >> 32));
+}
+#else
 __device__ __forceinline__ void LLStore(char* line, uint32_t d0, uint32_t d1, uint32_t flag)
 {
     asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(line), "r"(d0), "r"(flag), "r"(d1), "r"(flag)
                  : "memory");
 }
+// One read of a line without waiting: {data0, flag, data1, flag}.
+__device__ __forceinline__ uint4 LLPeek(const char* line)
+{
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(line) : "memory");
+    return v;
+}
+#endif
 __device__ __forceinline__ bool LLLoad(const DevComm& c, const char* line, uint32_t flag, uint32_t* d0, uint32_t* d1,
                                        uint32_t kernelId, int block, int peer)
 {
@@ -241,11 +264,10 @@ __device__ __forceinline__ bool LLLoad(const DevComm& c, const char* line, uint3
     uint64_t t0 = 0;
     uint32_t spins = 0;
     for (;;) {
-        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(a), "=r"(f0), "=r"(bb), "=r"(f1)
-                     : "l"(line)
-                     : "memory");
+        const uint4 v = LLPeek(line);
+        a = v.x; f0 = v.y; bb = v.z; f1 = v.w;
         if (f0 == flag && f1 == flag) break;
+        HCCL_SPIN_PAUSE();
         if ((++spins & 0x3FFu) == 0u) {
             if (LdVolatileU32(c.abortWord) != 0u) return false;
             const uint64_t now = GlobalTimerNs();
@@ -259,13 +281,6 @@ __device__ __forceinline__ bool LLLoad(const DevComm& c, const char* line, uint3
     *d0 = a;
     *d1 = bb;
     return true;
-}
-// One read of a line without waiting: {data0, flag, data1, flag}.
-__device__ __forceinline__ uint4 LLPeek(const char* line)
-{
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(line) : "memory");
-    return v;
 }
 __device__ __forceinline__ uint32_t LLFlag(uint64_t epoch) { return (uint32_t)(epoch % 0xFFFFFFFFull) + 1u; }
 
@@ -361,6 +376,33 @@ struct ArLLBody {
 // NVLS primitives (multimem.*): the switch reduces / replicates.
 template <class T>
 struct Multimem;  // only the specialisations below exist
+#ifdef HCCL_HOST_SHIM
+// the switch's reduction / replication as loops over the ranks' copies (plain accesses: races stay visible)
+template <class T>
+struct MultimemHost {
+    static uint4 LdReduceAdd(const void* mc)
+    {
+        size_t off = 0;
+        const hostshim::McWindow* w = hostshim::McFind(mc, &off);
+        AccVec<T> acc;
+        for (size_t r = 0; r < w->targets.size(); ++r) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(w->targets[r] + off);
+            if (r == 0) Unpack<T>(raw, acc);
+            else Accumulate<T>(raw, acc, RED_SUM);
+        }
+        return Pack<T>(acc);
+    }
+};
+template <> struct Multimem<float> : MultimemHost<float> {};
+template <> struct Multimem<__nv_bfloat16> : MultimemHost<__nv_bfloat16> {};
+template <> struct Multimem<__half> : MultimemHost<__half> {};
+inline void MultimemSt(void* mc, const uint4& v)
+{
+    size_t off = 0;
+    const hostshim::McWindow* w = hostshim::McFind(mc, &off);
+    for (char* t : w->targets) *reinterpret_cast<uint4*>(t + off) = v;
+}
+#else
 template <>
 struct Multimem<float> {
     __device__ static __forceinline__ uint4 LdReduceAdd(const void* mc)
@@ -403,6 +445,7 @@ __device__ __forceinline__ void MultimemSt(void* mc, const uint4& v)
                  "r"(v.w)
                  : "memory");
 }
+#endif
 
 // AllReduce NVLS (sum of fp32 / bf16 / fp16): each rank ld_reduces its slice
 // through the switch and multimem-stores the result to every rank.  Requires
@@ -581,8 +624,8 @@ struct AgBody {
                 Share(a.cnt[q], nb, b, 16, &qb, &qe);
                 segs[n++] = CopySeg{a.out + a.dsp[q] + qb, a.src[q] + qb, qe - qb};
             }
-            if (!(a.mode & MODE_INPLACE)) segs[n++] = CopySeg{a.out + a.dsp[me] + sb, a.in + sb, se - sb};
-            BlockCopyMulti(segs, n);
+            if (!(a.mode & MODE_INPLACE)) BlockCopyRemoteAndLocal(segs, n, CopySeg{a.out + a.dsp[me] + sb, a.in + sb, se - sb});
+            else BlockCopyMulti(segs, n);
         }
         RankBarrier(c, b, 0, e + 2, K_AG);
         StoreEpoch(c, b, e + 2);
@@ -734,11 +777,20 @@ struct BcastBody {
         OpHead(c, b);
         const int p = c.nRanks, me = c.rank, root = a.root;
         const uint64_t e = LoadEpoch(c, b);
+        // a block row stages exactly the bytes that the same block row of the peers reads after the barrier (rows only
+        // synchronise with the same row): the one-shot form reads one contiguous share per row, the two-shot form
+        // sub-range b of every slice
         if (me == root && (a.mode & MODE_STAGE_IN)) {
-            for (int s = 0; s < p; ++s) {
-                size_t off, len;
-                SliceSub(a.bytes, p, s, nb, b, &off, &len);
-                BlockCopyBytes(const_cast<char*>(a.src[root]) + off, a.in + off, len);
+            if (a.mode & MODE_PUSH) {
+                size_t off, end;
+                Share(a.bytes, nb, b, 16, &off, &end);
+                BlockCopyBytes(const_cast<char*>(a.src[root]) + off, a.in + off, end - off);
+            } else {
+                for (int s = 0; s < p; ++s) {
+                    size_t off, len;
+                    SliceSub(a.bytes, p, s, nb, b, &off, &len);
+                    BlockCopyBytes(const_cast<char*>(a.src[root]) + off, a.in + off, len);
+                }
             }
         }
         RankBarrier(c, b, 0, e + 1, K_BCAST);
@@ -795,7 +847,9 @@ struct BcastNvlsBody {
         // MODE_PUSH: the buffer itself is symmetric memory with a multicast alias: the root stores straight into every
         // rank's buffer.  Otherwise the message goes through the exchange region and non-roots copy it out.
         const bool direct = (a.mode & MODE_PUSH) != 0;
-        if (direct) RankBarrier(c, b, 0, e + 1, K_BCAST_NVLS);     // every rank has reached the op: its buffer may be overwritten
+        // every rank has reached the op: its buffer - or its exchange region, out of which it may still be copying the
+        // result of the previous operator - may be overwritten
+        RankBarrier(c, b, 0, e + 1, K_BCAST_NVLS);
         if (me == root) {
             const size_t n = end - off, nv = n >> 4;
             const bool inAl = (((uintptr_t)(a.in + off)) & 15u) == 0;
@@ -824,11 +878,8 @@ struct BcastNvlsBody {
             for (size_t t = (nv << 4) + threadIdx.x; t < n; t += blockDim.x)
                 for (int q = 0; q < c.nRanks; ++q) (direct ? a.dst[q] : a.xch[q])[off + t] = a.in[off + t];
         }
-        RankBarrier(c, b, 0, e + (direct ? 2 : 1), K_BCAST_NVLS);
-        if (!direct) {
-            if (me != root) BlockCopyBytes(a.out + off, a.xch[me] + off, end - off);
-            RankBarrier(c, b, 0, e + 2, K_BCAST_NVLS);
-        }
+        RankBarrier(c, b, 0, e + 2, K_BCAST_NVLS);
+        if (!direct && me != root) BlockCopyBytes(a.out + off, a.xch[me] + off, end - off);
         StoreEpoch(c, b, e + 2);
         OpTail(c, b);
     }
@@ -848,10 +899,17 @@ struct ReduceBody {
         const int p = c.nRanks, me = c.rank, root = a.root;
         const uint64_t e = LoadEpoch(c, b);
         if (a.mode & MODE_STAGE_IN) {
-            for (int s = 0; s < p; ++s) {
-                size_t off, len;
-                SliceSub(a.bytes, p, s, nb, b, &off, &len);
-                BlockCopyBytes(const_cast<char*>(a.src[me]) + off, a.in + off, len);
+            // staged by the partition the readers use (see BcastBody): one contiguous share per row in the one-shot form
+            if (a.mode & MODE_PUSH) {
+                size_t off, end;
+                Share(a.bytes, nb, b, 16, &off, &end);
+                BlockCopyBytes(const_cast<char*>(a.src[me]) + off, a.in + off, end - off);
+            } else {
+                for (int s = 0; s < p; ++s) {
+                    size_t off, len;
+                    SliceSub(a.bytes, p, s, nb, b, &off, &len);
+                    BlockCopyBytes(const_cast<char*>(a.src[me]) + off, a.in + off, len);
+                }
             }
         }
         RankBarrier(c, b, 0, e + 1, K_REDUCE);
@@ -949,11 +1007,15 @@ struct A2aBody {
         uint64_t* myMeta = reinterpret_cast<uint64_t*>(a.xch[me]) + (size_t)b * 2 * kMaxDevRanks;
         const bool windowed = (a.mode & MODE_STAGE_IN) && a.chunk != 0;
         const size_t win = (a.chunk + 15) & ~(size_t)15;
+        // A block row owns the same byte range [wb, we) of every window in every pass (clipped to what the pass moves):
+        // block rows only synchronise with the same row of the peers, so a row must never restage bytes that another
+        // row's reader may still be pulling.
+        size_t wb = 0, we = 0;
+        if (windowed) Share(a.chunk, nb, b, 16, &wb, &we);
         if (windowed) {
             for (int q = 0; q < p; ++q) {
                 const size_t n0 = a.cnt2[q] < a.chunk ? a.cnt2[q] : a.chunk;
-                size_t sb, se;
-                Share(n0, nb, b, 16, &sb, &se);
+                const size_t sb = wb < n0 ? wb : n0, se = we < n0 ? we : n0;
                 BlockCopyBytes(const_cast<char*>(a.src[me]) + (size_t)q * win + sb, a.in + a.dsp2[q] + sb, se - sb);
             }
             if (threadIdx.x < p) {
@@ -975,7 +1037,7 @@ struct A2aBody {
         RankBarrier(c, b, 0, e + 1, K_A2AV);
         uint64_t passes = 1;
         if (windowed) {
-            __shared__ unsigned long long s_max;
+            HCCL_SHARED(unsigned long long, s_max);
             if (threadIdx.x == 0) s_max = 0ull;
             __syncthreads();
             if ((int)threadIdx.x < p * p) {
@@ -992,14 +1054,14 @@ struct A2aBody {
                 for (int q = 0; q < p; ++q) {
                     const size_t left = a.cnt2[q] > base ? a.cnt2[q] - base : 0;
                     const size_t n0 = left < a.chunk ? left : a.chunk;
-                    size_t sb, se;
-                    Share(n0, nb, b, 16, &sb, &se);
+                    const size_t sb = wb < n0 ? wb : n0, se = we < n0 ? we : n0;
                     BlockCopyBytes(const_cast<char*>(a.src[me]) + (size_t)q * win + sb, a.in + a.dsp2[q] + base + sb, se - sb);
                 }
                 RankBarrier(c, b, 0, e + 1 + 2 * k, K_A2AV);
             }
             {
                 CopySeg segs[kMaxDevRanks];
+                CopySeg own{nullptr, nullptr, 0};
                 int n = 0;
                 for (int kk = 0; kk < p; ++kk) {
                     const int q = (me + kk) % p;
@@ -1009,15 +1071,16 @@ struct A2aBody {
                         len = left < a.chunk ? left : a.chunk;
                     }
                     size_t rb, re;
-                    Share(len, nb, b, 16, &rb, &re);
+                    if (windowed) { rb = wb < len ? wb : len; re = we < len ? we : len; }
+                    else Share(len, nb, b, 16, &rb, &re);
                     if (q == me) {
-                        segs[n++] = CopySeg{a.out + a.dsp[q] + base + rb, a.in + a.dsp2[me] + base + rb, re - rb};
+                        own = CopySeg{a.out + a.dsp[q] + base + rb, a.in + a.dsp2[me] + base + rb, re - rb};
                     } else {
                         const uint64_t sd = reinterpret_cast<const volatile uint64_t*>(a.xch[q])[(size_t)b * 2 * kMaxDevRanks + me];
                         segs[n++] = CopySeg{a.out + a.dsp[q] + base + rb, a.src[q] + sd + rb, re - rb};
                     }
                 }
-                BlockCopyMulti(segs, n);
+                BlockCopyRemoteAndLocal(segs, n, own);
             }
             RankBarrier(c, b, 0, e + 2 + 2 * k, K_A2AV);
         }
@@ -1050,7 +1113,7 @@ struct P2pBody {
     static constexpr int kThreads = 512;
     __device__ static void Run(const DevComm& c, const Args& a, int b, int)
     {
-        __shared__ int s_ok;
+        HCCL_SHARED(int, s_ok);
         OpHead(c, b);
         if (b < a.nItems) {
             const P2pItem it = a.items[b];

@@ -1,28 +1,9 @@
 // Instantiation and launch of the collective kernels (sm_100a).
 #include "coll_bodies.cuh"
-#include "launch.h"
-#include "../core/log.h"
+#include "coll_launch_common.cuh"
 
 namespace hccl {
 namespace {
-
-template <class Body>
-HcclResult LaunchBody(const LaunchTarget& t, const typename Body::Args& a, int nBlocks)
-{
-    if (nBlocks < 1) nBlocks = 1;
-    if (nBlocks > kMaxBlocks) nBlocks = kMaxBlocks;
-    if (t.emu != nullptr) {
-        return t.emu->Post(t.emuRank, &a, sizeof(a), nBlocks, Body::kThreads,
-                           reinterpret_cast<const void*>(&CollKernelEmu<Body>), t.stream);
-    }
-    CollKernel<Body><<<nBlocks, Body::kThreads, 0, t.stream>>>(*t.dev, a);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) {
-        HCCL_ERROR("kernel launch failed: %s", cudaGetErrorString(e));
-        return HCCL_E_RUNTIME;
-    }
-    return HCCL_SUCCESS;
-}
 
 // Reduce dtypes (reference rule set op_common.cc:4330-4335).
 #define HCCL_REDUCE_DISPATCH(TMPL)                                                        \
@@ -80,6 +61,7 @@ HcclResult LaunchCollective(const LaunchTarget& t, DevAlg alg, HcclDataType dtyp
         case DALG_A2A_LL: return LaunchBody<LLExchangeBody<int8_t, false>>(t, a, nb);
         default: break;
     }
+    if (alg >= DALG_AR_ONESHOT_CAST && alg < DALG_COUNT) return LaunchCollectiveExt(t, alg, dtype, dtype, a, nb);
     HCCL_ERROR("no kernel for device algorithm %d with data type %d", (int)alg, (int)dtype);
     return HCCL_E_NOT_SUPPORT;
 }

@@ -16,6 +16,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include "dev_types.h"
+#include "host_shim.h"
 
 namespace hccl {
 
@@ -27,6 +28,13 @@ __device__ __forceinline__ uint64_t* FlagPtr(const DevComm& c, int ownerRank, in
 __device__ __forceinline__ char* StagePtr(const DevComm& c, int ownerRank) { return c.slab[ownerRank] + kSlabDataOff; }
 __device__ __forceinline__ char* StageMcPtr(const DevComm& c) { return c.slabMc ? c.slabMc + kSlabDataOff : nullptr; }
 
+#ifdef HCCL_HOST_SHIM
+inline void StReleaseSys(uint64_t* p, uint64_t v) { __atomic_store_n(p, v, __ATOMIC_RELEASE); }
+inline uint64_t LdAcquireSys(const uint64_t* p) { return __atomic_load_n(p, __ATOMIC_ACQUIRE); }
+inline uint64_t LdRelaxedSys(const uint64_t* p) { return __atomic_load_n(p, __ATOMIC_RELAXED); }
+inline uint32_t LdVolatileU32(const uint32_t* p) { return __atomic_load_n(p, __ATOMIC_RELAXED); }
+inline uint64_t GlobalTimerNs() { return hostshim::NowNs(); }
+#else
 __device__ __forceinline__ void StReleaseSys(uint64_t* p, uint64_t v)
 {
     asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
@@ -55,6 +63,7 @@ __device__ __forceinline__ uint64_t GlobalTimerNs()
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
+#endif
 
 static __device__ __noinline__ void ReportWaitFailure(const DevComm& c, uint32_t kernelId, int block, int slot, int peer,
                                                uint64_t expected, uint64_t seen, uint32_t err)
@@ -87,6 +96,7 @@ __device__ __forceinline__ bool WaitFlagGE(const DevComm& c, const uint64_t* fla
     for (;;) {
         v = LdAcquireSys(flag);
         if (v >= want) return true;
+        HCCL_SPIN_PAUSE();
         if ((++spins & 0x3FFu) == 0u) {
             if (LdVolatileU32(c.abortWord) != 0u) return false;
             if (GlobalTimerNs() - t0 > c.timeoutNs) {
@@ -129,7 +139,7 @@ __device__ __forceinline__ uint64_t LoadLLEpoch(const DevComm& c)
 constexpr int kLLCreditSlot = 1;
 __device__ __forceinline__ bool LLCreditWait(const DevComm& c, uint64_t epoch, uint32_t kernelId, int block)
 {
-    __shared__ int s_creditOk;
+    HCCL_SHARED(int, s_creditOk);
     if (threadIdx.x == 0) s_creditOk = 1;
     __syncthreads();
     if (epoch >= 2 && (int)threadIdx.x < c.nRanks && (int)threadIdx.x != c.rank) {
@@ -163,7 +173,7 @@ __device__ __forceinline__ void FinishLLEpoch(const DevComm& c, uint64_t epoch, 
 // the kernel can run to its end without waiting again).
 __device__ __forceinline__ bool RankBarrier(const DevComm& c, int block, int slot, uint64_t value, uint32_t kernelId)
 {
-    __shared__ int s_ok;
+    HCCL_SHARED(int, s_ok);
     __syncthreads();
     if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();
@@ -222,6 +232,7 @@ __device__ __forceinline__ void OpTail(const DevComm& c, int block)
 // used when fewer GPUs than ranks are available: blocks of different ranks wait
 // on one another, so they must be co-resident, which only a single cooperative
 // launch guarantees.
+#ifndef HCCL_HOST_SHIM
 template <class Body>
 __global__ void __launch_bounds__(Body::kThreads) CollKernel(DevComm c, typename Body::Args a)
 {
@@ -234,5 +245,6 @@ __global__ void __launch_bounds__(Body::kThreads)
     const int r = (int)blockIdx.x / blocksPerRank;
     Body::Run(cs[r], as[r], (int)blockIdx.x % blocksPerRank, blocksPerRank);
 }
+#endif
 
 }  // namespace hccl

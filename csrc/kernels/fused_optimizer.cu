@@ -244,6 +244,15 @@ extern "C" HcclResult HcclFusedAdamW(const HcclAdamTensor* tensors, uint32_t nTe
     if (nTensors == 0) return HCCL_SUCCESS;
     CHK_PTR_NULL(tensors);
     if (!(beta1 >= 0.f && beta1 < 1.f) || !(beta2 >= 0.f && beta2 < 1.f) || !(eps >= 0.f)) return HCCL_E_PARA;
+    // everything that can be refused is checked before the step counter moves: a call that fails leaves no trace
+    const bool known = (paramType == HCCL_DATA_TYPE_BFP16 && (stateType == HCCL_DATA_TYPE_BFP16 || stateType == HCCL_DATA_TYPE_FP32)) ||
+                       (paramType == HCCL_DATA_TYPE_FP32 && stateType == HCCL_DATA_TYPE_FP32);
+    if (!known) {
+        HCCL_ERROR("HcclFusedAdamW: parameters %d with moments %d are not supported (bf16/bf16, fp32/fp32, bf16/fp32)", (int)paramType, (int)stateType);
+        return HCCL_E_NOT_SUPPORT;
+    }
+    for (uint32_t i = 0; i < nTensors; ++i)
+        if (tensors[i].numel != 0 && (!tensors[i].param || !tensors[i].grad || !tensors[i].expAvg || !tensors[i].expAvgSq)) return HCCL_E_PTR;
     cudaStream_t s = (cudaStream_t)stream;
     AdamStepKernel<<<1, 1, 0, s>>>(stepState, beta1, beta2);
     if (cudaGetLastError() != cudaSuccess) return HCCL_E_RUNTIME;

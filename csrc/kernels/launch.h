@@ -37,10 +37,18 @@ enum DevAlg : int {
     DALG_REDUCE_ONESHOT, DALG_REDUCE_TWOSHOT,
     DALG_SCATTER_PULL, DALG_A2A_PULL, DALG_P2P_MAILBOX, DALG_BARRIER, DALG_TEST_WAIT,
     DALG_RS_LL, DALG_BCAST_LL, DALG_A2A_LL,
+    // reductions fused with a cast to another floating type and a scale
+    DALG_AR_ONESHOT_CAST, DALG_AR_TWOSHOT_CAST, DALG_RS_CAST,
+    // ring and halving-doubling templates
+    DALG_RS_RING, DALG_AG_RING, DALG_AR_RHD,
+    // switch multicast AllGather, Broadcast as scatter + switch AllGather, AlltoAll through the receivers' slabs
+    DALG_AG_NVLS, DALG_BCAST_SCATTER_NVLS, DALG_A2A_PUSH,
     DALG_COUNT
 };
 
 HcclResult LaunchCollective(const LaunchTarget& t, DevAlg alg, HcclDataType dtype, const CollArgs& args, int nBlocks);
+// The algorithms of coll_bodies_ext.cuh (outType only matters for the cast forms; pass dtype otherwise).
+HcclResult LaunchCollectiveExt(const LaunchTarget& t, DevAlg alg, HcclDataType dtype, HcclDataType outType, const CollArgs& args, int nBlocks);
 HcclResult LaunchP2p(const LaunchTarget& t, const P2pArgs& args, int nBlocks);
 // Highest number of blocks per emulated rank that still fits one cooperative grid.
 int EmuMaxBlocksPerRank(int nRanks);

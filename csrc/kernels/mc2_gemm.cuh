@@ -93,6 +93,10 @@ struct GemmArgs {
     // alias xchgMc of the exchange buffers: the partials cross NVLink inside the switch's reduction, a GPU receives
     // only its reduced block.
     const __nv_bfloat16* xchgMc;
+    // plain two-SM matmul: row tiles per raster band (0 = 8) and L2 eviction policy of the operand loads
+    // (0 none, 1 evict last: the operand every wave re-reads, 2 evict first: the operand that streams through once)
+    int rasterGroup;
+    int l2HintA, l2HintB;
 };
 constexpr int kCtlEpoch = 0, kCtlTicket = 1, kCtlAbort = 2, kCtlPushNext = 3, kCtlPushGo = 4, kCtlReady = 16;
 // agPush values

@@ -54,6 +54,15 @@ __device__ __forceinline__ void TmaLoad2D2Sm(void* smemDst, const CUtensorMap* m
         "l"(reinterpret_cast<uint64_t>(map)), "r"(leaderBarAddr), "r"(x), "r"(y)
         : "memory");
 }
+// The same load with an L2 eviction policy (see L2PolicyEvictLast / L2PolicyEvictFirst).
+__device__ __forceinline__ void TmaLoad2D2SmHint(void* smemDst, const CUtensorMap* map, uint32_t leaderBarAddr, int x, int y, uint64_t policy)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(
+            SmemAddr(smemDst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(leaderBarAddr), "r"(x), "r"(y), "l"(policy)
+        : "memory");
+}
 __device__ __forceinline__ void UmmaF16_2Sm(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate)
 {
     asm volatile(
@@ -106,7 +115,7 @@ __device__ __forceinline__ void TileCoord2(const GemmArgs& g, int t, int tilesM2
     } else {
         // grouped raster: bands of 8 row tiles, walked column by column, so that the ~74 tiles in flight touch about
         // 8 row tiles of A and 9 column tiles of B instead of all of A
-        constexpr int kGroup = 8;
+        const int kGroup = g.rasterGroup > 0 ? g.rasterGroup : 8;
         const int perBand = kGroup * g.tilesN;
         const int band = t / perBand, rem = t % perBand;
         const int first = band * kGroup;
@@ -175,6 +184,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 int stage = 0;
                 uint32_t phase = 0;
                 bool ok = true;
+                const uint64_t polA = g.l2HintA == 1 ? L2PolicyEvictLast() : L2PolicyEvictFirst();
+                const uint64_t polB = g.l2HintB == 1 ? L2PolicyEvictLast() : L2PolicyEvictFirst();
                 for (int t = pair; t < nTiles && ok; t += nPairs) {
                     int mt2, nt;
                     TileCoord2<MODE>(g, t, tilesM2, &mt2, &nt);
@@ -198,18 +209,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                         const uint32_t leaderFull = SmemAddr(&fullBar[stage]) & kPeerBitMask;
                         if (crank == 0) MbarExpectTx(&fullBar[stage], (uint32_t)(2 * (L::kABytes + (BN / 2) * kBK * 2)));
                         if (!A_MN) {
-                            TmaLoad2D2Sm(sa, mapA, leaderFull, kb * kBK, rowA);
+                            if (g.l2HintA != 0) TmaLoad2D2SmHint(sa, mapA, leaderFull, kb * kBK, rowA, polA);
+                            else TmaLoad2D2Sm(sa, mapA, leaderFull, kb * kBK, rowA);
                         } else {
 #pragma unroll
-                            for (int j = 0; j < kBM / 64; ++j) TmaLoad2D2Sm(sa + j * (64 * kBK * 2), &tmA, leaderFull, mt * kBM + j * 64, kb * kBK);
+                            for (int j = 0; j < kBM / 64; ++j) {
+                                if (g.l2HintA != 0) TmaLoad2D2SmHint(sa + j * (64 * kBK * 2), &tmA, leaderFull, mt * kBM + j * 64, kb * kBK, polA);
+                                else TmaLoad2D2Sm(sa + j * (64 * kBK * 2), &tmA, leaderFull, mt * kBM + j * 64, kb * kBK);
+                            }
                         }
                         const int nRow = nt * BN + (int)crank * (BN / 2);
                         if (!B_MN) {
-                            TmaLoad2D2Sm(sb, &tmB, leaderFull, kb * kBK, nRow);
+                            if (g.l2HintB != 0) TmaLoad2D2SmHint(sb, &tmB, leaderFull, kb * kBK, nRow, polB);
+                            else TmaLoad2D2Sm(sb, &tmB, leaderFull, kb * kBK, nRow);
                         } else {
 #pragma unroll
-                            for (int j = 0; j < (kBN2 / 2) / 64; ++j)
-                                if (j * 64 < BN / 2) TmaLoad2D2Sm(sb + j * (64 * kBK * 2), &tmB, leaderFull, nRow + j * 64, kb * kBK);
+                            for (int j = 0; j < (kBN2 / 2) / 64; ++j) {
+                                if (j * 64 >= BN / 2) continue;
+                                if (g.l2HintB != 0) TmaLoad2D2SmHint(sb + j * (64 * kBK * 2), &tmB, leaderFull, nRow + j * 64, kb * kBK, polB);
+                                else TmaLoad2D2Sm(sb + j * (64 * kBK * 2), &tmB, leaderFull, nRow + j * 64, kb * kBK);
+                            }
                         }
                         if (++stage == kStages2) { stage = 0; phase ^= 1u; }
                     }

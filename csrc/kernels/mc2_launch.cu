@@ -5,7 +5,7 @@
 #include "../core/comm.h"
 #include "../core/cuda_driver.h"
 #include "../core/log.h"
-#include "mc2_gemm_2sm.cuh"
+#include "mc2_gemm_2sm_wide.cuh"
 
 namespace hccl {
 
@@ -115,6 +115,39 @@ HcclResult LaunchGemm2Sm(const CUtensorMap& ta, const CUtensorMap& tb, const Gem
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, ta2, g, c);
     if (e != cudaSuccess) { HCCL_ERROR("two-SM matmul launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
     return HCCL_SUCCESS;
+}
+
+template <bool A_MN, bool B_MN>
+HcclResult LaunchGemm2SmWide(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, int grid, cudaStream_t stream)
+{
+    auto kernel = GemmKernel2SmWide<A_MN, B_MN>;
+    static bool attrSet = false;
+    if (!attrSet) {
+        CHK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayoutWide::kTotal));
+        attrSet = true;
+    }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = SmemLayoutWide::kTotal;
+    cfg.stream = stream;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, g);
+    if (e != cudaSuccess) { HCCL_ERROR("wide two-SM matmul launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
+    return HCCL_SUCCESS;
+}
+
+// Wide tiles (two column tiles per CTA pair, see mc2_gemm_2sm_wide.cuh): HCCL_MC2_WIDE=0 never, 1 whenever the shape
+// allows, otherwise when the inner dimension is long enough to hide the unoverlapped epilogue and there are enough
+// tiles to fill the last wave.
+int WideMode()
+{
+    static int v = -2;
+    if (v == -2) {
+        const char* e = getenv("HCCL_MC2_WIDE");
+        v = e == nullptr ? -1 : (e[0] == '0' ? 0 : 1);
+    }
+    return v;
 }
 
 template <int MODE>
@@ -310,10 +343,53 @@ HcclResult Mc2Matmul(const void* a, const void* b, void* out, uint64_t m, uint64
             const double cost = (double)waves * (cand + 12);      // narrower tiles amortise the fixed per-tile work less well
             if (cost < bestCost - 1e-9) { bestCost = cost; bestBn = cand; }
         }
+        // wide tiles: the same search over (waves x width) with two column tiles per work item
+        {
+            int wideBn = 0;
+            double wideCost = 1e30;
+            for (int cand : {256, 224, 192, 160, 128}) {
+                if (bMn && (cand / 2) % 64 != 0) continue;
+                const int tn = (int)((n + cand - 1) / cand);
+                const int items = tilesM2 * ((tn + 1) / 2);
+                const int waves = (items + pairs - 1) / pairs;
+                const double cost = (double)waves * 2.0 * (cand + 12);
+                if (cost < wideCost - 1e-9) { wideCost = cost; wideBn = cand; }
+            }
+            const int wideItems = tilesM2 * (((int)((n + wideBn - 1) / wideBn) + 1) / 2);
+            const bool wideAuto = k >= 4096 && wideItems >= 4 * pairs && wideCost <= bestCost * 1.03;
+            if (WideMode() != 0 && (WideMode() == 1 || wideAuto) && n > (uint64_t)wideBn) {
+                g.bn = wideBn;
+                g.tilesN = (int)((n + wideBn - 1) / wideBn);
+                CHK_RET(MapB(&tb, b, n, k, bMn, wideBn / 2));
+                const int grid2 = std::min(SmCount() & ~1, 2 * wideItems);
+                g.nGemmCtas = grid2;
+                if (!aMn && !bMn) return LaunchGemm2SmWide<false, false>(ta, tb, g, grid2, stream);
+                if (!aMn && bMn) return LaunchGemm2SmWide<false, true>(ta, tb, g, grid2, stream);
+                if (aMn && !bMn) return LaunchGemm2SmWide<true, false>(ta, tb, g, grid2, stream);
+                return LaunchGemm2SmWide<true, true>(ta, tb, g, grid2, stream);
+            }
+        }
         g.bn = bestBn;
         g.tilesN = (int)((n + bestBn - 1) / bestBn);
         // B is split between the two CTAs of a pair: each loads half of the B rows of a tile
         CHK_RET(MapB(&tb, b, n, k, bMn, bestBn / 2));
+        // Raster and L2 policy (experimental, HCCL_MC2_L2_HINTS=1).  About `pairs` tiles are in flight: r row tiles x c
+        // column tiles, walking the columns of a band of r rows.  When one operand is small enough to live in L2 next
+        // to the stream of the other, it is loaded "evict last", the streamed one "evict first", and the band covers
+        // the whole small operand.  Measured on the decoder's matmuls it did not pay (evict-first lines of the
+        // streamed operand leave before the other row tiles of the wave have read them), so it is off by default.
+        static const bool l2Hints = [] { const char* e = getenv("HCCL_MC2_L2_HINTS"); return e != nullptr && e[0] == '1'; }();
+        if (l2Hints) {
+            const double bytesA = 2.0 * (double)m * (double)k, bytesB = 2.0 * (double)n * (double)k;
+            const double fits = 72.0 * (1 << 20);
+            if (bytesA <= fits && bytesB > 1.5 * bytesA) {
+                g.l2HintA = 1; g.l2HintB = 2;
+                g.rasterGroup = std::min(tilesM2, 32);            // all rows of A in one band: B is read once
+            } else if (bytesB <= fits && bytesA > 1.5 * bytesB) {
+                g.l2HintA = 2; g.l2HintB = 1;
+                g.rasterGroup = std::max(1, std::min(8, pairs / std::max(1, g.tilesN)));   // all columns of B in flight together
+            }
+        }
         const int pairsWanted = tilesM2 * g.tilesN;
         const int grid2 = std::min(SmCount() & ~1, 2 * pairsWanted);
         g.nGemmCtas = grid2;

@@ -190,6 +190,69 @@ __device__ __forceinline__ void BlockCopyMulti(const CopySeg* segs, int n)
     }
 }
 
+// Remote copies plus one device-local copy in the same block.  A remote load waits a round trip over NVLink, a
+// local one a fraction of that, so dealing them round-robin over the same warps would halve the remote bytes in
+// flight: the last `kLocalWarps` warps take the local segment, all the others the remote ones.
+constexpr int kLocalWarps = 2;
+__device__ __forceinline__ void BlockCopyRemoteAndLocal(const CopySeg* remote, int nRemote, const CopySeg& local)
+{
+    const int nWarps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    bool aligned = ((((uintptr_t)local.dst | (uintptr_t)local.src) & 15u) == 0) && nWarps > 2 * kLocalWarps;
+    for (int q = 0; q < nRemote; ++q) aligned = aligned && (((uintptr_t)remote[q].dst | (uintptr_t)remote[q].src) & 15u) == 0;
+    if (!aligned || nRemote == 0 || local.bytes == 0) {
+        if (nRemote > 0) BlockCopyMulti(remote, nRemote);
+        BlockCopyBytes(local.dst, local.src, local.bytes);
+        return;
+    }
+    constexpr int U = 8;
+    if (warp >= nWarps - kLocalWarps) {
+        const size_t nv = local.bytes >> 4;
+        const uint4* s = reinterpret_cast<const uint4*>(local.src);
+        uint4* d = reinterpret_cast<uint4*>(local.dst);
+        const size_t st = (size_t)kLocalWarps * 32;
+        size_t i = (size_t)(warp - (nWarps - kLocalWarps)) * 32 + lane;
+        for (; i + (U - 1) * st < nv; i += U * st) {
+            uint4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) v[u] = s[i + u * st];
+#pragma unroll
+            for (int u = 0; u < U; ++u) d[i + u * st] = v[u];
+        }
+        for (; i < nv; i += st) d[i] = s[i];
+    } else {
+        const int rw = nWarps - kLocalWarps;
+        size_t maxBytes = 0;
+        for (int q = 0; q < nRemote; ++q) maxBytes = remote[q].bytes > maxBytes ? remote[q].bytes : maxBytes;
+        const uint32_t chunksPerSeg = (uint32_t)((maxBytes + 511) >> 9);
+        const uint32_t slots = chunksPerSeg * (uint32_t)nRemote, un = (uint32_t)nRemote;
+        for (uint32_t slot = warp; slot < slots; slot += U * (uint32_t)rw) {
+            uint4 v[U];
+            bool ok[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const uint32_t sl = slot + (uint32_t)u * rw;
+                const uint32_t q = sl % un;
+                const size_t off = ((size_t)(sl / un) << 9) + ((size_t)lane << 4);
+                ok[u] = sl < slots && off + 16 <= remote[q].bytes;
+                if (ok[u]) v[u] = *reinterpret_cast<const uint4*>(remote[q].src + off);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const uint32_t sl = slot + (uint32_t)u * rw;
+                const uint32_t q = sl % un;
+                const size_t off = ((size_t)(sl / un) << 9) + ((size_t)lane << 4);
+                if (ok[u]) *reinterpret_cast<uint4*>(remote[q].dst + off) = v[u];
+            }
+        }
+    }
+    // tails shorter than 16 bytes
+    for (size_t b = (local.bytes & ~(size_t)15) + threadIdx.x; b < local.bytes; b += blockDim.x) local.dst[b] = local.src[b];
+    for (int q = 0; q < nRemote; ++q) {
+        const size_t done = remote[q].bytes & ~(size_t)15;
+        for (size_t b = done + threadIdx.x; b < remote[q].bytes; b += blockDim.x) remote[q].dst[b] = remote[q].src[b];
+    }
+}
+
 // Contiguous share of [0, n) for part `idx` of `parts`; shares are multiples of
 // `gran` except the last.
 __device__ __host__ __forceinline__ void Share(size_t n, int parts, int idx, size_t gran, size_t* begin, size_t* end)

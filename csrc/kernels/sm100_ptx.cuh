@@ -80,6 +80,21 @@ __device__ __forceinline__ void TmaLoad2D(void* smemDst, const CUtensorMap* map,
         "l"(reinterpret_cast<uint64_t>(map)), "r"(SmemAddr(bar)), "r"(x), "r"(y)
         : "memory");
 }
+// L2 eviction policies for tiled loads: an operand that every wave of tiles re-reads (and that fits the cache) is
+// loaded "evict last", the operand that streams through once "evict first", so that the stream does not push the
+// reused operand out to HBM.
+__device__ __forceinline__ uint64_t L2PolicyEvictLast()
+{
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t L2PolicyEvictFirst()
+{
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
 // Untiled bulk copies (both addresses 16-byte aligned, size a multiple of 16).
 __device__ __forceinline__ void BulkLoadG2S(void* smemDst, const void* gsrc, uint32_t bytes, uint64_t* bar)
 {

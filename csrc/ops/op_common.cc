@@ -123,7 +123,12 @@ struct Exec {
 
     void FillStageIn(CollArgs& a) const { for (int q = 0; q < P; ++q) a.src[q] = c->StageBase(q) + L.inOff; a.srcMc = c->StageMcBase() ? c->StageMcBase() + L.inOff : nullptr; }
     void FillXch(CollArgs& a) const { for (int q = 0; q < P; ++q) a.xch[q] = c->StageBase(q) + L.xchOff; }
-    HcclResult Launch(const CollArgs& a, uint64_t trafficBytes) const { return LaunchCollective(tgt, dalg, p.dtype, a, BlocksFor(c, trafficBytes, dalg)); }
+    HcclResult Launch(const CollArgs& a, uint64_t trafficBytes) const
+    {
+        if (p.castScale) return LaunchCollectiveExt(tgt, dalg, p.dtype, p.outType, a, BlocksFor(c, trafficBytes, dalg));
+        return LaunchCollective(tgt, dalg, p.dtype, a, BlocksFor(c, trafficBytes, dalg));
+    }
+    uint64_t esOut() const { return p.castScale ? DataTypeSize(p.outType) : es; }
     uint64_t LoopBytes(uint64_t region, uint64_t multiple) const { return AlignDown(region / multiple, 128); }
 
     // ---- AllReduce / Reduce --------------------------------------------------
@@ -138,7 +143,9 @@ struct Exec {
         // NVLS needs a multicast alias for its source; a registered buffer without one is staged.  One-shot in place on
         // a registered buffer would let a rank overwrite its input with sums while its peers still read it (every rank
         // reads the whole message of every peer between the two barriers): that case is staged as well.
-        const bool useInDirect = inDirect && (!nvlsAlg || (d.inMulticast && in.mc != nullptr)) && !ll && !(dalg == DALG_AR_ONESHOT && d.inPlace);
+        const bool oneShotForm = dalg == DALG_AR_ONESHOT || dalg == DALG_AR_ONESHOT_CAST;
+        const bool readsInputLate = oneShotForm || dalg == DALG_AR_RHD;      // a peer may read this rank's input after this rank wrote output
+        const bool useInDirect = inDirect && (!nvlsAlg || (d.inMulticast && in.mc != nullptr)) && !ll && !(readsInputLate && d.inPlace);
         const bool outAligned = Aligned16(p.recv);
         const bool pushOut = (dalg == DALG_AR_TWOSHOT || nvlsAlg) && d.outRegistered && d.aligned16 && out.reg && outAligned &&
                              (!nvlsAlg || (d.outMulticast && out.mc != nullptr)) && !isReduce;
@@ -146,8 +153,10 @@ struct Exec {
         if (!ll) {
             uint64_t limit = ~0ull;
             if (!useInDirect) limit = std::min(limit, LoopBytes(L.inBytes, 1));
-            const bool needXch = (dalg == DALG_AR_TWOSHOT && !pushOut) || (nvlsAlg && !pushOut) || dalg == DALG_REDUCE_TWOSHOT;
-            if (needXch) limit = std::min(limit, LoopBytes(L.xchBytes, 1));
+            const bool needXch = (dalg == DALG_AR_TWOSHOT && !pushOut) || (nvlsAlg && !pushOut) || dalg == DALG_REDUCE_TWOSHOT ||
+                                 dalg == DALG_AR_TWOSHOT_CAST || dalg == DALG_AR_RHD;
+            // the cast form keeps output elements in the exchange region: count the limit in input bytes
+            if (needXch) limit = std::min(limit, LoopBytes(L.xchBytes * es / std::max<uint64_t>(es, esOut()), 1));
             if (limit == 0) return HCCL_E_MEMORY;
             chunk = std::min(total, limit);
         }
@@ -156,10 +165,11 @@ struct Exec {
             CollArgs a;
             memset(&a, 0, sizeof(a));
             a.in = (const char*)p.send + off;
-            a.out = (char*)p.recv + off;
+            a.out = (char*)p.recv + off / es * esOut();
             a.bytes = n;
             a.op = (int)p.redOp;
             a.root = (int)p.root;
+            a.scale = p.castScale ? p.scale : 1.0f;
             if (useInDirect) { for (int q = 0; q < P; ++q) a.src[q] = in.peer[q] + off; a.srcMc = in.mc ? in.mc + off : nullptr; }
             else { FillStageIn(a); a.mode |= MODE_STAGE_IN; }
             FillXch(a);
@@ -175,7 +185,7 @@ struct Exec {
                 a.mode |= MODE_STAGE_OUT;
             }
             if (dalg == DALG_REDUCE_ONESHOT) a.mode |= MODE_PUSH;   // one-shot flavour of ReduceBody
-            CHK_RET(Launch(a, dalg == DALG_AR_ONESHOT || dalg == DALG_REDUCE_ONESHOT ? n : n / (uint64_t)P * 2 + 1));
+            CHK_RET(Launch(a, oneShotForm || dalg == DALG_REDUCE_ONESHOT ? n : n / (uint64_t)P * 2 + 1));
         }
         return HCCL_SUCCESS;
     }
@@ -201,13 +211,21 @@ struct Exec {
             if (limit == 0) return HCCL_E_MEMORY;
             chunk = std::min<uint64_t>(std::max<uint64_t>(maxCnt, 1), limit);
         }
+        if (dalg == DALG_RS_RING) {
+            // the partial sums travel through one exchange slot per step
+            const uint64_t limit = AlignDown(L.xchBytes / (uint64_t)std::max(1, P - 1), 128);
+            if (limit == 0) return HCCL_E_MEMORY;
+            chunk = std::min<uint64_t>(std::max<uint64_t>(chunk, 1), limit);
+        }
         if (maxCnt == 0) chunk = 1;
         for (uint64_t off = 0; off < std::max<uint64_t>(maxCnt, 1); off += chunk) {
             CollArgs a;
             memset(&a, 0, sizeof(a));
             a.in = (const char*)p.send;
-            a.out = (char*)p.recv + off;
+            a.out = (char*)p.recv + off / es * esOut();
             a.op = (int)p.redOp;
+            a.scale = p.castScale ? p.scale : 1.0f;
+            FillXch(a);
             uint64_t sum = 0;
             for (int q = 0; q < P; ++q) {
                 a.cnt[q] = cntB[q] > off ? std::min(chunk, cntB[q] - off) : 0;
@@ -215,7 +233,7 @@ struct Exec {
                 a.dsp[q] = inDirect ? dspB[q] + off : (uint64_t)q * AlignUp(chunk, 16);
                 sum += a.cnt[q];
             }
-            a.bytes = sum;
+            a.bytes = dalg == DALG_RS_RING ? a.cnt[me] : sum;          // the ring's slots are one block wide
             if (inDirect) { for (int q = 0; q < P; ++q) a.src[q] = in.peer[q]; a.srcMc = in.mc; }
             else { FillStageIn(a); a.mode |= MODE_STAGE_IN; }
             // the grid must be the same on every rank: size it by the largest block, which all ranks know
@@ -276,9 +294,26 @@ struct Exec {
         // a peer pulls block q from rank q's input, so "registered" has to hold on every rank: d.inRegistered does
         const bool inDirect = d.inRegistered && in.reg && !ll;
         const bool inPlace = (const char*)p.send == (char*)p.recv + dspB[me];
+        const bool nvlsAlg = dalg == DALG_AG_NVLS;
+        RegInfo out;
+        uint64_t outSpan = 0;
+        for (int q = 0; q < P; ++q) outSpan = std::max(outSpan, dspB[q] + cntB[q]);
+        if (nvlsAlg) out = Reg(c, p.recv, outSpan);
+        bool nvlsDirect = nvlsAlg && d.outRegistered && d.outMulticast && d.aligned16 && out.reg && out.mc != nullptr && Aligned16(p.recv);
+        for (int q = 0; q < P && nvlsDirect; ++q) nvlsDirect = (dspB[q] & 15u) == 0;
         uint64_t chunk = std::max<uint64_t>(maxCnt, 1);
-        if (!inDirect && !ll) {
+        if (!inDirect && !ll && !nvlsAlg) {
             const uint64_t limit = LoopBytes(L.inBytes, 1);
+            if (limit == 0) return HCCL_E_MEMORY;
+            chunk = std::min(chunk, limit);
+        }
+        if (dalg == DALG_AG_RING) {
+            const uint64_t limit = AlignDown(L.xchBytes / (uint64_t)std::max(1, P - 1), 128);
+            if (limit == 0) return HCCL_E_MEMORY;
+            chunk = std::min(chunk, limit);
+        }
+        if (nvlsAlg && !nvlsDirect) {
+            const uint64_t limit = AlignDown(L.xchBytes / (uint64_t)P, 128);      // every rank's block lands in the exchange region
             if (limit == 0) return HCCL_E_MEMORY;
             chunk = std::min(chunk, limit);
         }
@@ -290,10 +325,21 @@ struct Exec {
             for (int q = 0; q < P; ++q) {
                 a.cnt[q] = cntB[q] > off ? std::min(chunk, cntB[q] - off) : 0;
                 a.dsp[q] = dspB[q] + off;
+                a.dsp2[q] = nvlsDirect ? a.dsp[q] : (uint64_t)q * AlignUp(chunk, 16);
             }
             a.bytes = a.cnt[me];
+            FillXch(a);
             if (inPlace) a.mode |= MODE_INPLACE;
-            if (inDirect) { for (int q = 0; q < P; ++q) a.src[q] = in.peer[q] + off; }
+            if (nvlsAlg) {
+                if (nvlsDirect) {
+                    a.mode |= MODE_PUSH;
+                    a.dstMc = const_cast<char*>(out.mc);
+                    for (int q = 0; q < P; ++q) a.dst[q] = const_cast<char*>(out.peer[q]);
+                } else {
+                    a.dstMc = c->StageMcBase() + L.xchOff;
+                    for (int q = 0; q < P; ++q) a.dst[q] = a.xch[q];
+                }
+            } else if (inDirect) { for (int q = 0; q < P; ++q) a.src[q] = in.peer[q] + off; }
             else if (!ll) { FillStageIn(a); a.mode |= MODE_STAGE_IN; }
             uint64_t traffic = 0;
             for (int q = 0; q < P; ++q) traffic += a.cnt[q];
@@ -308,12 +354,13 @@ struct Exec {
     {
         const uint64_t total = p.count * es;
         RegInfo in = Reg(c, p.send, total);
+        const bool scatterNvls = dalg == DALG_BCAST_SCATTER_NVLS;      // reads the root like the pull forms, writes like the switch form
         const bool nvlsAlg = dalg == DALG_BCAST_NVLS;
         const bool inDirect = d.inRegistered && in.reg && !nvlsAlg;
         uint64_t limit = ~0ull;
         if (!inDirect && !nvlsAlg) limit = std::min(limit, LoopBytes(L.inBytes, 1));
-        const bool nvlsDirect = nvlsAlg && d.inRegistered && d.inMulticast && d.aligned16 && in.reg && in.mc != nullptr && Aligned16(p.send);
-        if (dalg == DALG_BCAST_TWOSHOT || (nvlsAlg && !nvlsDirect)) limit = std::min(limit, LoopBytes(L.xchBytes, 1));
+        const bool nvlsDirect = (nvlsAlg || scatterNvls) && d.inRegistered && d.inMulticast && d.aligned16 && in.reg && in.mc != nullptr && Aligned16(p.send);
+        if (dalg == DALG_BCAST_TWOSHOT || ((nvlsAlg || scatterNvls) && !nvlsDirect)) limit = std::min(limit, LoopBytes(L.xchBytes, 1));
         if (limit == 0) return HCCL_E_MEMORY;
         const uint64_t chunk = std::min(total, limit);
         for (uint64_t off = 0; off < total; off += chunk) {
@@ -327,13 +374,14 @@ struct Exec {
             if (inDirect) { for (int q = 0; q < P; ++q) a.src[q] = in.peer[q] + off; }
             else if (!nvlsAlg) { FillStageIn(a); a.mode |= MODE_STAGE_IN; }
             FillXch(a);
-            if (nvlsAlg) {
+            if (nvlsAlg || scatterNvls) {
                 if (nvlsDirect) {
                     a.mode |= MODE_PUSH;      // the buffer is symmetric with a multicast alias: store straight into it
                     a.dstMc = const_cast<char*>(in.mc) + off;
                     for (int q = 0; q < P; ++q) a.dst[q] = const_cast<char*>(in.peer[q]) + off;
                 } else {
                     a.dstMc = c->StageMcBase() + L.xchOff;
+                    for (int q = 0; q < P; ++q) a.dst[q] = a.xch[q];
                 }
             }
             if (dalg == DALG_BCAST_ONESHOT) a.mode |= MODE_PUSH;
@@ -401,6 +449,20 @@ struct Exec {
             if (perPeerLimit == 0) return HCCL_E_MEMORY;
         }
         (void)staged;
+        if (dalg == DALG_A2A_PUSH) {
+            // every pair's block lands in the receiver's stage-in region, two copies by parity
+            const uint64_t pair = sendB[0], slot = AlignUp(pair, 16), copyBytes = slot * (uint64_t)P;
+            if (2 * copyBytes > L.inBytes) return HCCL_E_INTERNAL;
+            CollArgs a;
+            memset(&a, 0, sizeof(a));
+            a.in = (const char*)p.send;
+            a.out = (char*)p.recv;
+            a.bytes = pair;
+            a.chunk = copyBytes;
+            for (int q = 0; q < P; ++q) { a.dsp2[q] = sdspB[q]; a.dsp[q] = rdspB[q]; }
+            FillStageIn(a);
+            return Launch(a, pair * (uint64_t)P);
+        }
         uint64_t loops = 1, chunk = ~0ull;
         if (!inDirect && p.op != HCCL_CMD_ALLTOALLV && p.globalMaxBytes > perPeerLimit) {
             chunk = perPeerLimit;
@@ -425,8 +487,9 @@ struct Exec {
             if (inDirect) { for (int q = 0; q < P; ++q) a.src[q] = in.peer[q]; }
             else { FillStageIn(a); a.mode |= MODE_STAGE_IN; if (p.op == HCCL_CMD_ALLTOALLV) a.chunk = perPeerLimit; }
             // every rank has to launch the same grid.  The uniform op and VC know the global sizes; AlltoAllV does
-            // not (counts are private to each rank), so it always runs with a fixed grid.
-            if (p.op == HCCL_CMD_ALLTOALLV) CHK_RET(LaunchCollective(tgt, dalg, p.dtype, a, std::min(c->MaxBlocks(), 32)));
+            // not (counts are private to each rank), so it always runs with the full grid: a large exchange is bound
+            // by the bytes in flight, and the extra block rows of a small one only add their own (parallel) barriers.
+            if (p.op == HCCL_CMD_ALLTOALLV) CHK_RET(LaunchCollective(tgt, dalg, p.dtype, a, c->MaxBlocks()));
             else CHK_RET(Launch(a, std::min(chunk, p.globalMaxBytes) * (uint64_t)P));
         }
         return HCCL_SUCCESS;
@@ -493,6 +556,8 @@ OpDesc Describe(CommImpl* c, const OpParam& p)
     d.det = c->cfg.deterministic;
     d.engine = c->cfg.engine;
     d.isMc2 = p.isMc2;
+    d.castScale = p.castScale;
+    d.stageInBytes = c->layout().inBytes;
     const uint64_t es = DataTypeSize(p.dtype);
     const uint64_t P = (uint64_t)c->nRanks;
     const char* peers[kMaxDevRanks];
@@ -575,9 +640,10 @@ HcclResult ExecDescribed(CommImpl* c, OpParam& p, OpDesc d, const uint32_t* pres
     PlanKey key = {(uint32_t)p.op, (uint32_t)p.dtype, (uint32_t)p.redOp, p.root, d.bytes, localFlags, (uint32_t)c->generation};
     Plan plan;
     const AlgEntry* alg = nullptr;
-    // emulated ranks never cache: a plan's combined flags depend on what the OTHER ranks passed, which the key does not see
-    const bool cacheable = c->cfg.planCacheEnable && presetAgreed == nullptr;
-    if (cacheable && c->plans->Find(key, &plan)) {
+    // a plan made for other combined flags (emulated ranks: the combination is known before every call and depends on
+    // what the OTHER ranks passed, which the key does not see) is replaced
+    const bool cacheable = c->cfg.planCacheEnable;
+    if (cacheable && c->plans->Find(key, &plan) && (presetAgreed == nullptr || plan.agreedFlags == *presetAgreed)) {
         alg = &AlgRegistry::Instance().All()[(size_t)plan.algIndex];
         d.ApplyFlags(plan.agreedFlags);
     } else {

@@ -28,6 +28,11 @@ struct OpParam {
     std::vector<HcclSendRecvItem> items;
     cudaStream_t stream = nullptr;
     bool isMc2 = false;
+    // reductions fused with a cast and a scale (HcclAllReduceEx / HcclReduceScatterEx): the output holds elements of
+    // outType, every reduced value is multiplied by scale before it is stored
+    bool castScale = false;
+    HcclDataType outType = HCCL_DATA_TYPE_RESERVED;
+    float scale = 1.0f;
     std::string algName;             // filled by ExecOp: the algorithm that ran
 };
 

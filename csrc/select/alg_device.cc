@@ -165,8 +165,6 @@ void RegisterAll()
                 c.B = (m.stageIn || !o.inMulticast) ? m.copy() : 0;
                 c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
                 // the switch still has to pull (p-1)/p of the input out of every GPU
-                CostCoeff f;
-                f.D = 0;
                 c.D = (m.p - 1) / m.p * m.nvls() * (double)o.bytes;
                 return std::vector<CostCoeff>{c};
             };
@@ -344,6 +342,151 @@ void RegisterAll()
             c.ratio = 1.0 / m.p;
             c.B = (m.stageIn ? m.copy() : 0) + m.copy() / m.p;
             c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+    }
+    // ---------------- reductions fused with a cast and a scale (only for calls that ask for one)
+    {
+        constexpr uint64_t kCastTypes = Bit(HCCL_DATA_TYPE_FP16) | Bit(HCCL_DATA_TYPE_BFP16) | Bit(HCCL_DATA_TYPE_FP32);
+        AlgEntry e = Base("P2pAllReduceSoleMeshOneShotCast", HCCL_CMD_ALLREDUCE, HCCL_ENGINE_P2P, "MeshOneShotCast", DALG_AR_ONESHOT_CAST, AlgoType::ONESHOT);
+        e.attrs.dtypeMask = kCastTypes;
+        e.attrs.castScale = true;
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = (m.p - 1) * m.link();
+            c.B = m.stageIn ? m.copy() : 0;
+            c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+        AlgEntry f = Base("P2pAllReduceSoleMeshTwoShotCast", HCCL_CMD_ALLREDUCE, HCCL_ENGINE_P2P, "MeshTwoShotCast", DALG_AR_TWOSHOT_CAST, AlgoType::TWOSHOT);
+        f.attrs.dtypeMask = kCastTypes;
+        f.attrs.castScale = true;
+        f.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = 2.0 * (m.p - 1) / m.p * m.link();
+            c.ratio = 1.0 / m.p;
+            c.B = (m.stageIn ? m.copy() : 0) + 2.0 * m.copy() / m.p;
+            c.C = m.lm.launchUs + 3 * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(f);
+        AlgEntry g = Base("P2pReduceScatterSoleMeshCast", HCCL_CMD_REDUCE_SCATTER, HCCL_ENGINE_P2P, "MeshCast", DALG_RS_CAST, AlgoType::MESH);
+        g.attrs.dtypeMask = kCastTypes;
+        g.attrs.castScale = true;
+        g.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = (m.p - 1) / m.p * m.link();
+            c.ratio = 1.0 / m.p;
+            c.B = m.stageIn ? m.copy() : 0;
+            c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(g);
+    }
+    // ---------------- ring and halving-doubling templates on the device: neighbour / partner flags between the steps.
+    // On one NVSwitch box the mesh forms move the same bytes in fewer steps, so the cost model only takes these when
+    // HCCL_ALGO names them (ring, H-D_R) or a tuner prefers them; they are the level-1 candidates of a multi-box
+    // topology.
+    {
+        AlgEntry e = Base("P2pReduceScatterSoleRing", HCCL_CMD_REDUCE_SCATTER, HCCL_ENGINE_P2P, "Ring", DALG_RS_RING, AlgoType::RING);
+        e.attrs.dtypeMask = kReduceTypes;
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = (m.p - 1) / m.p * m.link();
+            c.ratio = 1.0 / m.p;
+            c.B = (m.stageIn ? m.copy() : 0) + 2.0 * (m.p - 1) / m.p * m.copy();
+            c.C = m.lm.launchUs + 2 * m.lm.barrierUs + (m.p - 1) * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+        AlgEntry f = Base("P2pAllGatherSoleRing", HCCL_CMD_ALLGATHER, HCCL_ENGINE_P2P, "Ring", DALG_AG_RING, AlgoType::RING);
+        f.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = (m.p - 1) / m.p * m.link();
+            c.ratio = 1.0 / m.p;
+            c.B = (m.stageIn ? m.copy() / m.p : 0) + 2.0 * m.copy();
+            c.C = m.lm.launchUs + 2 * m.lm.barrierUs + (m.p - 1) * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(f);
+        AlgEntry g = Base("P2pAllReduceSoleRhd", HCCL_CMD_ALLREDUCE, HCCL_ENGINE_P2P, "Rhd", DALG_AR_RHD, AlgoType::HD_R);
+        g.attrs.dtypeMask = kReduceTypes;
+        g.attrs.powerOfTwoRanksOnly = true;
+        g.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            double steps = 0;
+            for (double q = 1; q < m.p; q *= 2) steps += 1;
+            c.A = 2.0 * (m.p - 1) / m.p * m.link();
+            c.ratio = 0.5;
+            c.B = (m.stageIn ? m.copy() : 0) + 3.0 * m.copy();
+            c.C = m.lm.launchUs + 2 * m.lm.barrierUs + 2.0 * steps * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(g);
+    }
+    // ---------------- switch multicast AllGather; Broadcast as scatter + switch AllGather
+    {
+        AlgEntry e = Base("NvlsAllGatherSoleMesh", HCCL_CMD_ALLGATHER, HCCL_ENGINE_NVLS, "Mesh", DALG_AG_NVLS, AlgoType::NVLS);
+        e.attrs.needsNvls = true;
+        e.attrs.needsAligned16 = true;
+        e.attrs.opCustomCheck = [](const OpDesc& o, const TopoInfo& t, std::string* why) {
+            if ((o.bytes / std::max<uint32_t>(1, t.nRanks)) % 16 != 0) { *why = "op: blocks are not a multiple of 16 bytes"; return false; }
+            return true;
+        };
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            // a port sends its block once and receives p - 1 blocks: bound by the same ingress as the pull form.  Priced a
+            // little above it until a measurement on the box says otherwise (HCCL_ALGO="allgather=level0:nvls" picks it)
+            c.A = std::max((m.p - 1) / m.p * m.link() * 1.03, m.nvlsStore() / m.p);
+            c.ratio = 1.0 / m.p;
+            c.B = m.copy() / m.p + (o.outMulticast ? 0 : m.copy());      // without a multicast alias the blocks are copied out of the slab
+            c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+        AlgEntry f = Base("NvlsBroadcastSoleMeshScatter", HCCL_CMD_BROADCAST, HCCL_ENGINE_NVLS, "MeshScatter", DALG_BCAST_SCATTER_NVLS, AlgoType::NVLS);
+        f.attrs.needsNvls = true;
+        f.attrs.minBytes = 1024 * 1024;
+        f.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            // the root's port carries (p - 1) / p of the message once; every port then multicasts 1 / p
+            c.A = (m.p - 1) / m.p * m.link() + std::max(m.nvlsStore() / m.p, (m.p - 1) / m.p * m.nvls()) * 0.25;
+            c.ratio = 1.0 / m.p;
+            c.net = NetType::NVLS_SWITCH;
+            c.B = (m.stageIn ? m.copy() : 0) + ((o.inMulticast && o.aligned16) ? 0 : m.copy());
+            c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(f);
+    }
+    // ---------------- AlltoAll through the receivers' slabs: posted writes, one barrier, a local copy
+    {
+        AlgEntry e = Base("P2pAlltoAllSoleMeshPush", HCCL_CMD_ALLTOALL, HCCL_ENGINE_P2P, "MeshPush", DALG_A2A_PUSH, AlgoType::MESH);
+        e.attrs.maxBytes = 64ull << 20;
+        e.attrs.opCustomCheck = [](const OpDesc& o, const TopoInfo& t, std::string* why) {
+            // both landing copies of all pairs' blocks must fit the stage-in region: about a quarter of the slab (the
+            // executor checks the exact size and the selector only offers the form well inside it)
+            const uint64_t pair = o.bytes / std::max<uint32_t>(1, t.nRanks);
+            if ((pair + 16) * t.nRanks * 2 > o.stageInBytes) { *why = "op: the blocks do not fit the landing zone twice"; return false; }
+            return true;
+        };
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = (m.p - 1) / m.p * m.link();
+            c.ratio = 1.0 / m.p;
+            c.B = 2.0 * m.copy();
+            c.C = m.lm.launchUs + m.lm.barrierUs;
             return std::vector<CostCoeff>{c};
         };
         R.Register(e);

@@ -34,7 +34,7 @@ uint32_t OpDesc::Flags() const
 {
     return (inRegistered ? 1u : 0u) | (outRegistered ? 2u : 0u) | (aligned16 ? 4u : 0u) | (inPlace ? 8u : 0u) | (inMulticast ? (1u << 20) : 0u) |
            (outMulticast ? (1u << 21) : 0u) |
-           (isMc2 ? 16u : 0u) | ((uint32_t)det << 5) | ((uint32_t)engine << 8);
+           (isMc2 ? 16u : 0u) | ((uint32_t)det << 5) | ((uint32_t)engine << 8) | (castScale ? (1u << 22) : 0u);
 }
 
 // ------------------------------------------------------------------ registry
@@ -298,6 +298,7 @@ bool OpMatches(const AlgEntry& a, const OpDesc& op, const TopoInfo& topo, std::s
     if (t.needsAligned16 && !op.aligned16) { *why = "op: buffers are not 16-byte aligned"; return false; }
     if (t.needsRegisteredOut && !op.outRegistered) { *why = "op: output is not symmetric memory"; return false; }
     if (op.isMc2 && !t.supportMc2) { *why = "op: not usable from fused matmul kernels"; return false; }
+    if (op.castScale != t.castScale) { *why = t.castScale ? "op: a cast + scale form, the call asks for neither" : "op: the call casts or scales"; return false; }
     if (t.opCustomCheck && !t.opCustomCheck(op, topo, why)) return false;
     return true;
 }

@@ -47,6 +47,8 @@ struct OpDesc {
     bool aligned16 = true;       // both pointers 16-byte aligned
     bool inPlace = false;
     bool isMc2 = false;          // called on behalf of a fused matmul kernel
+    uint64_t stageInBytes = 0;   // size of the communicator's stage-in region (forms that land data there check their fit)
+    bool castScale = false;      // the reduction casts to another type and / or scales: only the cast forms can run it
     Deterministic det = Deterministic::OFF;
     HcclCommEngine engine = HCCL_ENGINE_AUTO;   // requested engine (HCCL_OP_EXPANSION_MODE / comm config)
     uint32_t Flags() const;
@@ -90,6 +92,7 @@ struct AlgAttrs {
     bool needsRegisteredOut = false;
     uint64_t minBytes = 0, maxBytes = ~0ull;
     bool supportMc2 = true;
+    bool castScale = false;                  // a cast + scale form: used for calls that ask for it, and only for those
     std::function<bool(const OpDesc&, const TopoInfo&, std::string*)> opCustomCheck;
     std::function<bool(const TopoInfo&, std::string*)> topoCustomCheck;
 };

@@ -96,6 +96,8 @@ _sig("HcclMemFree", R, c_void_p, c_void_p)
 _sig("HcclCommSymWinGet", R, c_void_p, c_void_p, c_uint32, POINTER(c_void_p))
 _sig("HcclCommSymWinGetMulticast", R, c_void_p, c_void_p, POINTER(c_void_p))
 _sig("HcclAllReduce", R, c_void_p, c_void_p, c_uint64, c_int, c_int, c_void_p, c_void_p)
+_sig("HcclAllReduceEx", R, c_void_p, c_void_p, c_uint64, c_int, c_int, c_int, ctypes.c_float, c_void_p, c_void_p)
+_sig("HcclReduceScatterEx", R, c_void_p, c_void_p, c_uint64, c_int, c_int, c_int, ctypes.c_float, c_void_p, c_void_p)
 _sig("HcclBroadcast", R, c_void_p, c_uint64, c_int, c_uint32, c_void_p, c_void_p)
 _sig("HcclReduceScatter", R, c_void_p, c_void_p, c_uint64, c_int, c_int, c_void_p, c_void_p)
 _sig("HcclReduceScatterV", R, c_void_p, c_void_p, c_void_p, c_void_p, c_uint64, c_int, c_int, c_void_p, c_void_p)

@@ -209,6 +209,23 @@ class Communicator:
         _check(lib.HcclAllReduce(sp, rp, n, int(dt), int(op), self._h, self._stream(stream)), "HcclAllReduce")
         return recv
 
+    def all_reduce_ex(self, send, recv=None, op: ReduceOp = ReduceOp.SUM, scale: float = 1.0, stream=None):
+        """``recv = (recv.dtype)(scale * reduce(send))`` in one pass: ``recv`` may have another floating type than
+        ``send`` (fp32 / bf16 / fp16 on either side) and ``scale`` is applied to the fp32 accumulator.  ``scale = 1 /
+        world_size`` averages."""
+        recv = send if recv is None else recv
+        sp, n, dt = self._buf(send)
+        rp, _, rdt = self._buf(recv)
+        _check(lib.HcclAllReduceEx(sp, rp, n, int(dt), int(rdt), int(op), float(scale), self._h, self._stream(stream)), "HcclAllReduceEx")
+        return recv
+
+    def reduce_scatter_ex(self, send, recv, op: ReduceOp = ReduceOp.SUM, scale: float = 1.0, stream=None):
+        """ReduceScatter with the output cast to ``recv.dtype`` and scaled, in one pass."""
+        sp, _, dt = self._buf(send)
+        rp, n, rdt = self._buf(recv)
+        _check(lib.HcclReduceScatterEx(sp, rp, n, int(dt), int(rdt), int(op), float(scale), self._h, self._stream(stream)), "HcclReduceScatterEx")
+        return recv
+
     def broadcast(self, buf, root: int = 0, stream=None):
         p, n, dt = self._buf(buf)
         _check(lib.HcclBroadcast(p, n, int(dt), root, self._h, self._stream(stream)), "HcclBroadcast")

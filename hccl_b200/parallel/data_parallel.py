@@ -9,8 +9,12 @@ that thin framework side for plain PyTorch modules:
 * ``overlap=True`` hooks every parameter: when the last gradient of a bucket has been accumulated, the bucket's
   AllReduce is issued at once - on a side stream for CUDA tensors, so that it runs beside the rest of backward - and
   buckets are always issued in index order, which keeps the ranks' call sequences identical;
-* ``finish()`` (or ``reduce()`` without hooks) waits for the side stream, divides by the world size when
-  ``average=True`` and writes the reduced values back into ``p.grad``.
+* the average is part of the AllReduce (``all_reduce_ex`` with ``scale = 1 / world``: the kernel scales its fp32
+  accumulator before it stores), so no separate pass divides the bucket;
+* on a device communicator the flat buckets live in symmetric memory (``comm.empty``), which the kernels read and
+  write in place on the peers instead of staging them through the slab;
+* ``finish()`` (or ``reduce()`` without hooks) waits for the side stream and writes the reduced values back into
+  ``p.grad``.
 
 NVSwitch gives every GPU full bandwidth to every peer, so a bucket is sized for launch latency and overlap (tens of
 MiB), not for link count.
@@ -42,7 +46,16 @@ class GradientBucketer:
             cur_key = key
         if cur:
             self.buckets.append(cur)
-        self.flat = [torch.zeros(sum(p.numel() for p in b), dtype=b[0].dtype, device=b[0].device) for b in self.buckets]
+        self._float_types = (torch.float32, torch.bfloat16, torch.float16)
+        self.flat = []
+        for b in self.buckets:
+            numel = sum(p.numel() for p in b)
+            if b[0].is_cuda and getattr(comm, "kind", "") == "device" and comm.world_size > 1:
+                buf = comm.empty((numel,), b[0].dtype)          # collective: every rank builds the same buckets in the same order
+                buf.zero_()
+            else:
+                buf = torch.zeros(numel, dtype=b[0].dtype, device=b[0].device)
+            self.flat.append(buf)
         self._bucket_of = {p: i for i, b in enumerate(self.buckets) for p in b}
         self._pending = [0] * len(self.buckets)
         self._next = 0
@@ -82,7 +95,13 @@ class GradientBucketer:
                 else:
                     flat[off:off + n].copy_(p.grad.reshape(-1))
                 off += n
-            self.comm.all_reduce(flat, flat, stream=side) if side is not None else self.comm.all_reduce(flat, flat)
+            fused = self.average and flat.dtype in self._float_types and self.comm.world_size > 1
+            scale = 1.0 / self.comm.world_size if fused else 1.0
+            kw = {"stream": side} if side is not None else {}
+            if fused:
+                self.comm.all_reduce_ex(flat, flat, scale=scale, **kw)
+            else:
+                self.comm.all_reduce(flat, flat, **kw)
         self._launched[i] = True
 
     def _on_grad(self, p):
@@ -109,10 +128,9 @@ class GradientBucketer:
                 self._launch(i)
         if self._stream is not None:
             torch.cuda.current_stream(self._stream.device).wait_stream(self._stream)
-        scale = 1.0 / self.comm.world_size if self.average else 1.0
         for bucket, flat in zip(self.buckets, self.flat):
-            if scale != 1.0:
-                flat.mul_(scale)
+            if self.average and flat.dtype not in self._float_types:
+                flat.div_(self.comm.world_size, rounding_mode="floor") if not flat.dtype.is_floating_point else flat.mul_(1.0 / self.comm.world_size)
             off = 0
             for p in bucket:
                 n = p.numel()
@@ -184,9 +202,12 @@ class ShardedOptimizer:
             else:
                 self.flat_grad[off:off + n].copy_(p.grad.reshape(-1))
             off += n
-        self.comm.reduce_scatter(self.flat_grad, self.shard.grad)
-        if self.average:
-            self.shard.grad.mul_(1.0 / self.comm.world_size)
+        if self.average and self.flat_grad.dtype in (torch.float32, torch.bfloat16, torch.float16) and self.comm.world_size > 1:
+            self.comm.reduce_scatter_ex(self.flat_grad, self.shard.grad, scale=1.0 / self.comm.world_size)      # averaged in the same pass
+        else:
+            self.comm.reduce_scatter(self.flat_grad, self.shard.grad)
+            if self.average:
+                self.shard.grad.mul_(1.0 / self.comm.world_size)
         self.optimizer.step()
         self.comm.all_gather(self.shard.detach(), self.flat_param)
         off = 0

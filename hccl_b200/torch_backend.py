@@ -25,13 +25,20 @@ _REDUCE = {dist.ReduceOp.SUM: ReduceOp.SUM, dist.ReduceOp.PRODUCT: ReduceOp.PROD
            dist.ReduceOp.MIN: ReduceOp.MIN}
 
 
+def _is_avg(op) -> bool:
+    key = getattr(op, "op", op) if not isinstance(op, dist.ReduceOp.RedOpType) else op
+    return key == dist.ReduceOp.AVG
+
+
 def _red(op) -> ReduceOp:
     # torch passes either the enum value or a ReduceOp object wrapping it
     key = getattr(op, "op", op) if not isinstance(op, dist.ReduceOp.RedOpType) else op
+    if key == dist.ReduceOp.AVG:
+        return ReduceOp.SUM              # the caller scales by 1 / world inside the same kernel (all_reduce_ex)
     for k, v in _REDUCE.items():
         if key == k:
             return v
-    raise NotImplementedError(f"hccl backend: reduce op {op} is not supported (sum, prod, max, min are)")
+    raise NotImplementedError(f"hccl backend: reduce op {op} is not supported (sum, avg, prod, max, min are)")
 
 
 class _DoneWork(dist._Work):
@@ -87,8 +94,14 @@ class ProcessGroupHCCL(dist.ProcessGroup):
     # ---- collectives
     def allreduce(self, tensors, opts=None):
         op = _red(opts.reduceOp) if opts is not None else ReduceOp.SUM
+        avg = opts is not None and _is_avg(opts.reduceOp)
         for t in tensors:
-            self.comm.all_reduce(self._c(t), op=op)
+            if avg and t.dtype in (torch.float32, torch.bfloat16, torch.float16) and self._size > 1:
+                self.comm.all_reduce_ex(self._c(t), scale=1.0 / self._size)          # the average is fused into the reduction
+            else:
+                self.comm.all_reduce(self._c(t), op=op)
+                if avg:
+                    t.div_(self._size)
         return _DoneWork(tensors)
 
     def allreduce_coalesced(self, tensors, opts=None):
@@ -128,6 +141,13 @@ class ProcessGroupHCCL(dist.ProcessGroup):
 
     def _reduce_scatter_base(self, output, input, opts=None):
         op = _red(opts.reduceOp) if opts is not None else ReduceOp.SUM
+        if opts is not None and _is_avg(opts.reduceOp) and self._size > 1:
+            if input.dtype in (torch.float32, torch.bfloat16, torch.float16):
+                self.comm.reduce_scatter_ex(self._c(input), self._c(output), scale=1.0 / self._size)
+            else:
+                self.comm.reduce_scatter(self._c(input), self._c(output), op)
+                output.div_(self._size)
+            return _DoneWork(output)
         self.comm.reduce_scatter(self._c(input), self._c(output), op)
         return _DoneWork(output)
 

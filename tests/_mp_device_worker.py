@@ -321,6 +321,66 @@ def scenario_skew(comm, rank, world):
     assert comm.async_error() == hb.Result.SUCCESS
 
 
+def scenario_switch_forms(comm, rank, world):
+    """AllGather through the switch (symmetric and ordinary outputs), Broadcast as scatter + switch AllGather, and the
+    cast + scale reductions over the real transport."""
+    import os
+
+    from hccl_b200._lib import lib
+
+    os.environ["HCCL_ALGO"] = "allgather=level0:nvls"
+    lib.HcclReloadEnvConfig()
+    for n in (4096, 300000, 1 << 22):
+        xs = [rnd(n, torch.float32, 40 + r) for r in range(world)]
+        for sym in (False, True):
+            out = comm.empty((n * world,), torch.float32) if sym else torch.empty(n * world, device="cuda")
+            for rep in range(2):
+                out.zero_()
+                comm.all_gather(xs[rank], out)
+                torch.cuda.synchronize()
+                assert torch.equal(out, torch.cat(xs)), f"switch allgather n={n} sym={sym}"
+            if rank == 0:
+                print(f"allgather n={n} sym={sym}: {comm.last_algorithm()}", flush=True)
+            if sym:
+                comm.free(out)
+    os.environ.pop("HCCL_ALGO")
+    lib.HcclReloadEnvConfig()
+    for n in (1 << 19, (1 << 22) + 4):
+        for root in (0, world - 1):
+            for sym in (False, True):
+                b = comm.empty((n,), torch.float32) if sym else torch.empty(n, device="cuda")
+                b.copy_(rnd(n, torch.float32, 5) if rank == root else torch.zeros(n, device="cuda"))
+                comm.broadcast(b, root)
+                torch.cuda.synchronize()
+                assert torch.equal(b, rnd(n, torch.float32, 5)), f"broadcast n={n} root={root} sym={sym}"
+                if rank == 0:
+                    print(f"broadcast n={n} root={root} sym={sym}: {comm.last_algorithm()}", flush=True)
+                if sym:
+                    comm.free(b)
+    for n in (1000, 1 << 21):
+        xs = [rnd(n, torch.float32, 70 + r) for r in range(world)]
+        y = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+        comm.all_reduce_ex(xs[rank], y, scale=1.0 / world)
+        torch.cuda.synchronize()
+        torch.testing.assert_close(y.double(), torch.stack([t.double() for t in xs]).mean(0), rtol=1e-2, atol=1e-2)
+        g = comm.empty((n,), torch.float32)
+        g.copy_(xs[rank])
+        comm.all_reduce_ex(g, scale=1.0 / world)
+        torch.cuda.synchronize()
+        torch.testing.assert_close(g.double(), torch.stack([t.double() for t in xs]).mean(0), rtol=1e-6, atol=1e-6)
+        comm.free(g)
+    s = rnd(300000 * world, torch.float32, 300 + rank)
+    r = torch.empty_like(s)
+    for rep in range(3):
+        comm.all_to_all(s, r)
+        torch.cuda.synchronize()
+        for q in range(world):
+            assert torch.equal(r[q * 300000:(q + 1) * 300000], rnd(300000 * world, torch.float32, 300 + q)[rank * 300000:(rank + 1) * 300000])
+    if rank == 0:
+        print(f"alltoall 300000 floats per pair: {comm.last_algorithm()}", flush=True)
+    assert comm.async_error() == hb.Result.SUCCESS
+
+
 def scenario_model(rank, world, path):
     """Two-layer TP+SP decoder stack: loss and gradients of the NCCL + cuBLAS arm against the same model in one piece,
     and of the fused-kernel arm against the NCCL + cuBLAS arm, for both AllGather->Matmul forms; two steps each
@@ -453,7 +513,7 @@ def main():
     info = rendezvous(rank, path)
     timeout_ms = 3000 if scenario == "peer_exit" else 0
     comm = Communicator.from_root_info(info, rank, world, hb.make_config(buffer_mib=64, exec_timeout_ms=timeout_ms))
-    {"collectives": scenario_collectives, "skew": scenario_skew, "peer_exit": scenario_peer_exit, "mc2": scenario_mc2, "graph": scenario_graph,
+    {"collectives": scenario_collectives, "skew": scenario_skew, "switch_forms": scenario_switch_forms, "peer_exit": scenario_peer_exit, "mc2": scenario_mc2, "graph": scenario_graph,
      "register": scenario_register}[scenario](comm, rank, world)
     comm.destroy()
     print(f"rank {rank} done", flush=True)

@@ -56,6 +56,12 @@ def test_ranks_out_of_step_and_buffers_that_differ_per_rank(nvls):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_switch_allgather_scatter_broadcast_and_cast_reductions():
+    codes, outs = _run(_world(), "switch_forms")
+    assert all(c == 0 for c in codes), "\n".join(outs)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
 def test_peer_exit_is_detected():
     # NVLS off and plain peer loads: a rank that dies while bound to a multicast object can fault its peers
     codes, outs = _run(min(_world(), 4), "peer_exit", {"HCCL_NVLS_ENABLE": "0", "NCCL_NVLS_ENABLE": "0"}, timeout=120)
