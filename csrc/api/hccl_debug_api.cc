@@ -252,6 +252,16 @@ HcclResult HcclDebugParseEnv(const char* settings, char* text, uint32_t cap)
     return HCCL_SUCCESS;
 }
 
+HcclResult HcclLoadLinkModel(const char* path, char* error, uint32_t cap)
+{
+    CHK_PTR_NULL(path);
+    std::string err;
+    const bool ok = LoadLinkModelFile(path, &err);
+    if (error && cap) snprintf(error, cap, "%s", err.c_str());
+    return ok ? HCCL_SUCCESS : HCCL_E_PARA;
+}
+double HcclDebugLinkUtilisation(int netType, double bytes, uint32_t nRanks) { return LinkUtilisation((NetType)netType, bytes, HCCL_ENGINE_P2P, (int)nRanks); }
+
 double HcclDebugEvalCost(double A, double B, double C, double D, int netType, double ratio, double bytes)
 {
     CostCoeff c;

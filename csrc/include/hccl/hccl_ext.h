@@ -117,6 +117,10 @@ HcclResult HcclDebugStepTable(const char* kind, uint32_t p, uint32_t rank, const
 // (and the list of rejected variables) as text, without touching the process environment.
 HcclResult HcclDebugParseEnv(const char* settings, char* text, uint32_t capacity);
 // Evaluates the cost formula for one segment: (A / util(net, bytes * ratio) + B) * bytes + C, floored by D.
+/* Loads link parameters and per-GPU-count utilisation curves from a measurement file (see docs/algorithms.md); the
+ * library loads hccl_b200/data/link_model.json, or the file HCCL_LINK_MODEL_FILE names, by itself on first use. */
+HcclResult HcclLoadLinkModel(const char* path, char* error, uint32_t capacity);
+double HcclDebugLinkUtilisation(int netType, double bytes, uint32_t nRanks);
 double HcclDebugEvalCost(double A, double B, double C, double D, int netType, double ratio, double bytes);
 // Re-reads the HCCL_* environment variables (they are parsed once per process otherwise).  Existing communicators
 // keep the plans they already cached.

@@ -38,6 +38,7 @@ namespace mc2 {
 using namespace sm100;
 
 constexpr int kBM = 128;
+constexpr int kBN2c = 256;         // column tile width of the fused modes
 constexpr int kBK = 64;            // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kUmmaK = 16;
 constexpr int kStages = 4;
@@ -97,8 +98,12 @@ struct GemmArgs {
     // (0 none, 1 evict last: the operand every wave re-reads, 2 evict first: the operand that streams through once)
     int rasterGroup;
     int l2HintA, l2HintB;
+    // RS without worker CTAs (rsCoop != 0): rsCoop (1 .. 4) of the epilogue warps of every GEMM CTA reduce the finished
+    // tiles of this rank's row block whenever they have no accumulator to drain.  The switch-reduce path slows down
+    // beyond a number of outstanding requests per GPU, so not all four warps take part by default.
+    int rsCoop;
 };
-constexpr int kCtlEpoch = 0, kCtlTicket = 1, kCtlAbort = 2, kCtlPushNext = 3, kCtlPushGo = 4, kCtlReady = 16;
+constexpr int kCtlEpoch = 0, kCtlTicket = 1, kCtlAbort = 2, kCtlPushNext = 3, kCtlPushGo = 4, kCtlReduceNext = 5, kCtlReady = 16;
 // agPush values
 constexpr int kAgPull = 0, kAgPushWorkers = 1, kAgPushCoop = 2;
 
@@ -576,6 +581,159 @@ __device__ __forceinline__ void SwitchReduceTile(const GemmArgs& g, const __nv_b
     }
 }
 
+// ReduceScatter, cooperative form.  As with the AllGather push, the epilogue warps are idle for most of a tile's
+// main loop, so they also do the reduction and every SM computes: a warp takes the next 32-row x 256-column piece of
+// this rank's output (column tile major, the order in which partials complete), looks - without waiting - whether all
+// ranks have published that tile, and reduces it: through the switch (multimem.ld_reduce over the ranks' exchange
+// buffers) or, in the deterministic form, by summing the P partials from local memory in rank order.  A piece whose
+// partials are not there yet is kept and tried again after the next look at the accumulator barrier, so a warp
+// never blocks the GEMM and nothing can wait in a circle.
+constexpr int kReducePieceRows = 32;
+
+template <int PMAX>
+__device__ __forceinline__ void WarpLocalReducePiece(const GemmArgs& g, const __nv_bfloat16* xbase, size_t slotElems, int row0, int col0, int lane)
+{
+    constexpr int U = PMAX <= 2 ? 4 : (PMAX <= 4 ? 2 : 1);          // eight local loads in flight per lane, 32 registers
+    const int vecPerRow = kBN2c / 8;
+    const int total = kReducePieceRows * vecPerRow;
+    for (int v = lane; v < total; v += U * 32) {
+        uint4 raw[U][PMAX];
+        bool valid[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int vv = v + u * 32;
+            const int r = row0 + vv / vecPerRow, col = col0 + (vv % vecPerRow) * 8;
+            valid[u] = vv < total && r < g.mPerRank && col < g.N;
+#pragma unroll
+            for (int q = 0; q < PMAX; ++q)
+                if (q < g.nRanks && valid[u]) raw[u][q] = *reinterpret_cast<const uint4*>(xbase + (size_t)q * slotElems + (size_t)r * g.N + col);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (!valid[u]) continue;
+            const int vv = v + u * 32;
+            const int r = row0 + vv / vecPerRow, col = col0 + (vv % vecPerRow) * 8;
+            float acc[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+#pragma unroll
+            for (int q = 0; q < PMAX; ++q) {
+                if (q < g.nRanks) {
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u][q]);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float2 f = __bfloat1622float2(h[k]);
+                        acc[2 * k] += f.x;
+                        acc[2 * k + 1] += f.y;
+                    }
+                }
+            }
+            uint4 o;
+            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+            *reinterpret_cast<uint4*>(g.out + (size_t)r * g.ldc + col) = o;
+        }
+    }
+}
+
+__device__ __forceinline__ void WarpSwitchReducePiece(const GemmArgs& g, const __nv_bfloat16* mcBlock, int row0, int col0, int lane)
+{
+    constexpr int U = 8;          // more outstanding switch reductions per SM were measured slower
+    const int vecPerRow = kBN2c / 8;
+    const int total = kReducePieceRows * vecPerRow;
+    for (int v = lane; v < total; v += U * 32) {
+        uint4 val[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int vv = v + u * 32;
+            const int r = row0 + vv / vecPerRow, col = col0 + (vv % vecPerRow) * 8;
+            if (vv < total && r < g.mPerRank && col < g.N) {
+                const __nv_bfloat16* p = mcBlock + (size_t)r * g.N + col;
+                asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(val[u].x), "=r"(val[u].y), "=r"(val[u].z), "=r"(val[u].w)
+                             : "l"(p)
+                             : "memory");
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int vv = v + u * 32;
+            const int r = row0 + vv / vecPerRow, col = col0 + (vv % vecPerRow) * 8;
+            if (vv < total && r < g.mPerRank && col < g.N) *reinterpret_cast<uint4*>(g.out + (size_t)r * g.ldc + col) = val[u];
+        }
+    }
+}
+
+// One step of a warp.  *pending: a piece this warp has claimed whose partials were not all there (or -1).
+// Returns 0 when nothing is left for this warp, 1 after reducing a piece, 2 when its piece is not ready yet.
+// Not inlined: its 16 vectors in flight must not take registers from the accumulator drain of the same warps.
+static __device__ __noinline__ int CoopReduceStep(const GemmArgs& g, uint32_t launchEpoch, int lane, int* pending)
+{
+    const int rowsTiles = g.mPerRank / kBM;
+    const int piecesPerTile = kBM / kReducePieceRows;
+    const uint32_t total = (uint32_t)(rowsTiles * g.tilesN * piecesPerTile);
+    int u = *pending;
+    if (u < 0) {
+        uint32_t t = 0;
+        if (lane == 0) t = atomicAdd(g.ctl + kCtlReduceNext, 1u);
+        t = __shfl_sync(0xffffffffu, t, 0);
+        if (t >= total) return 0;
+        u = (int)t;
+    }
+    const int lt = u / piecesPerTile, piece = u % piecesPerTile;
+    const int nt = lt / rowsTiles, mtLocal = lt % rowsTiles;           // column tile major: the order in which partials complete
+    bool ready = true;
+    if (lane < g.nRanks) {
+        const uint64_t* f = g.tileFlag[g.rank] + (size_t)lane * g.maxTiles + (mtLocal * g.tilesN + nt);
+        uint64_t v;
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(f) : "memory");
+        ready = v >= (uint64_t)launchEpoch;
+    }
+    ready = __all_sync(0xffffffffu, ready);
+    if (!ready) { *pending = u; return 2; }
+    *pending = -1;
+    const int row0 = mtLocal * kBM + piece * kReducePieceRows, col0 = nt * kBN2c;
+    const size_t parityOff = (launchEpoch & 1u) * g.xchgParityElems;
+    if (g.xchgMc != nullptr) {
+        WarpSwitchReducePiece(g, g.xchgMc + parityOff + (size_t)g.rank * g.mPerRank * g.N, row0, col0, lane);
+    } else {
+        const __nv_bfloat16* xbase = g.xchg[g.rank] + parityOff;
+        const size_t slotElems = (size_t)g.mPerRank * g.N;
+        if (g.nRanks <= 2) WarpLocalReducePiece<2>(g, xbase, slotElems, row0, col0, lane);
+        else if (g.nRanks <= 4) WarpLocalReducePiece<4>(g, xbase, slotElems, row0, col0, lane);
+        else WarpLocalReducePiece<kMaxDevRanks>(g, xbase, slotElems, row0, col0, lane);
+    }
+    return 1;
+}
+
+// Reduces pieces until accumulator `bar` is ready (true) or nothing is left for this warp (false).
+__device__ __forceinline__ bool CoopReduceWhileWaiting(const GemmArgs& g, uint32_t launchEpoch, int lane, int* pending, uint64_t* bar, uint32_t parity)
+{
+    for (;;) {
+        if (MbarTestWait(bar, parity)) return true;
+        const int r = CoopReduceStep(g, launchEpoch, lane, pending);
+        if (r == 0) return false;
+        if (r == 2 && *(volatile uint32_t*)(g.ctl + kCtlAbort) != 0u) return false;
+    }
+}
+
+// After its last tile a warp reduces until the pieces run out; bounded by the wait limit per piece.
+__device__ __forceinline__ void CoopReduceDrain(const GemmArgs& g, uint32_t launchEpoch, int lane, int* pending)
+{
+    volatile uint32_t* abortWord = g.ctl + kCtlAbort;
+    uint64_t t0 = 0;
+    for (;;) {
+        const int r = CoopReduceStep(g, launchEpoch, lane, pending);
+        if (r == 0) return;
+        if (r == 1) { t0 = 0; continue; }
+        const uint64_t now = TimerNs();
+        if (t0 == 0) t0 = now;
+        if (*abortWord != 0u) return;
+        if (now - t0 > kWaitLimitNs) { *abortWord = 1u; return; }
+    }
+}
+
 // ReduceScatter reduction: for every tile of the local row block, waits until all ranks have delivered their
 // partial (flag value == launch epoch), sums the P partials in rank order in fp32 and writes bf16 to `out`.
 // Tiles are visited in the order they complete (column tile major).
@@ -755,11 +913,14 @@ __global__ void __launch_bounds__(kThreads, 1)
             bool ok = true;
             const size_t parityOff = (launchEpoch & 1u) * g.xchgParityElems;
             bool pushLeft = MODE == MODE_AG && g.agPush == kAgPushCoop;
+            bool reduceLeft = MODE == MODE_RS && (warp - 2) < g.rsCoop;      // g.rsCoop of the four epilogue warps reduce
+            int reducePending = -1;
             if (pushLeft && cta == 0 && warp == 2) CoopPushOpen(c, g, launchEpoch, lane);
             for (int t = cta; t < nTiles && ok; t += g.nGemmCtas) {
                 int mt, nt;
                 TileCoord<MODE>(g, t, &mt, &nt);
                 if (MODE == MODE_AG && pushLeft) pushLeft = CoopPushWhileWaiting(g, launchEpoch, lane, &tmemFull[acc], accPhase);
+                if (MODE == MODE_RS && reduceLeft) reduceLeft = CoopReduceWhileWaiting(g, launchEpoch, lane, &reducePending, &tmemFull[acc], accPhase);
                 ok = MbarWait(&tmemFull[acc], accPhase, abortWord, kWaitLimitNs);
                 if (!ok) break;
                 TcFenceAfter();
@@ -838,6 +999,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
             }
             if (MODE == MODE_AG && pushLeft) CoopPushDrain(g, launchEpoch, lane);
+            if (MODE == MODE_RS && reduceLeft && BN == kBN2c) CoopReduceDrain(g, launchEpoch, lane, &reducePending);
         }
         // teardown: every role has left its loop (normally or by a bounded wait that ran out)
         TcFenceBefore();
@@ -862,6 +1024,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             g.ctl[kCtlTicket] = 0;
             g.ctl[kCtlPushNext] = 0;
+            g.ctl[kCtlReduceNext] = 0;
             *reinterpret_cast<volatile uint32_t*>(g.ctl + kCtlEpoch) = launchEpoch;
             __threadfence();
         }

@@ -283,12 +283,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             bool ok = true;
             const size_t parityOff = (launchEpoch & 1u) * g.xchgParityElems;
             bool pushLeft = MODE == MODE_AG && g.agPush == kAgPushCoop;
+            bool reduceLeft = MODE == MODE_RS && (warp - 2) < g.rsCoop;      // g.rsCoop of the four epilogue warps reduce
+            int reducePending = -1;
             if (pushLeft && cta == 0 && warp == 2) CoopPushOpen(c, g, launchEpoch, lane);
             for (int t = pair; t < nTiles && ok; t += nPairs) {
                 int mt2, nt;
                 TileCoord2<MODE>(g, t, tilesM2, &mt2, &nt);
                 const int mt = mt2 * 2 + (int)crank;
                 if (MODE == MODE_AG && pushLeft) pushLeft = CoopPushWhileWaiting(g, launchEpoch, lane, &tmemFull[acc], accPhase);
+                if (MODE == MODE_RS && reduceLeft) reduceLeft = CoopReduceWhileWaiting(g, launchEpoch, lane, &reducePending, &tmemFull[acc], accPhase);
                 ok = MbarWait(&tmemFull[acc], accPhase, abortWord, kWaitLimitNs);
                 if (!ok) break;
                 TcFenceAfter();
@@ -327,6 +330,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 }
             }
             if (MODE == MODE_AG && pushLeft) CoopPushDrain(g, launchEpoch, lane);
+            if (MODE == MODE_RS && reduceLeft) CoopReduceDrain(g, launchEpoch, lane, &reducePending);
         }
         // teardown: nobody leaves while its peer may still touch its shared memory, barriers or TMEM
         TcFenceBefore();
@@ -351,6 +355,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             }
             g.ctl[kCtlTicket] = 0;
             g.ctl[kCtlPushNext] = 0;
+            g.ctl[kCtlReduceNext] = 0;
             *reinterpret_cast<volatile uint32_t*>(g.ctl + kCtlEpoch) = launchEpoch;
             __threadfence();
         }

@@ -137,15 +137,16 @@ HcclResult LaunchGemm2SmWide(const CUtensorMap& ta, const CUtensorMap& tb, const
     return HCCL_SUCCESS;
 }
 
-// Wide tiles (two column tiles per CTA pair, see mc2_gemm_2sm_wide.cuh): HCCL_MC2_WIDE=0 never, 1 whenever the shape
-// allows, otherwise when the inner dimension is long enough to hide the unoverlapped epilogue and there are enough
-// tiles to fill the last wave.
+// Wide tiles (two column tiles per CTA pair, see mc2_gemm_2sm_wide.cuh): HCCL_MC2_WIDE=1 whenever the shape allows,
+// HCCL_MC2_WIDE=auto when the inner dimension is long and there are enough tiles to fill the last wave; off otherwise.
+// Measured on the decoder's matmuls the unoverlapped epilogue (about 9 us per 256 accumulator columns) costs more
+// than the saved L2 traffic returns, so the double-buffered 256 x 256 kernel stays the default.
 int WideMode()
 {
     static int v = -2;
     if (v == -2) {
         const char* e = getenv("HCCL_MC2_WIDE");
-        v = e == nullptr ? -1 : (e[0] == '0' ? 0 : 1);
+        v = e == nullptr ? 0 : (e[0] == 'a' ? -1 : (e[0] == '1' ? 1 : 0));
     }
     return v;
 }
@@ -503,8 +504,13 @@ HcclResult Mc2MatmulReduceScatter(CommImpl* comm, const void* a, const void* b, 
         g.xchgMc = (const __nv_bfloat16*)comm->mc2->xchg.mc;
     const bool twoSm = Use2Sm() && mPerRank % 256 == 0;
     const int localTiles = (int)(mPerRank / kBM) * g.tilesN;
-    const int workers = twoSm ? ReduceWorkerCtas((g.M / 256) * g.tilesN, 2, localTiles, g.K, g.nRanks, g.xchgMc != nullptr)
-                              : ReduceWorkerCtas(g.tilesM * g.tilesN, 1, localTiles, g.K, g.nRanks, g.xchgMc != nullptr);
+    // No worker CTAs by default: every CTA computes, its epilogue warps reduce the finished tiles of this rank's row
+    // block while they wait for accumulators.  HCCL_MC2_RS_WORKERS=<n> keeps n dedicated reduction CTAs instead.
+    int workers = 0;
+    static const int rsWarps = [] { const char* e = getenv("HCCL_MC2_RS_WARPS"); const int v = e ? atoi(e) : 4; return v < 1 ? 1 : (v > 4 ? 4 : v); }();
+    if (ForcedWorkers(false) == 0) g.rsCoop = rsWarps;
+    else workers = twoSm ? ReduceWorkerCtas((g.M / 256) * g.tilesN, 2, localTiles, g.K, g.nRanks, g.xchgMc != nullptr)
+                         : ReduceWorkerCtas(g.tilesM * g.tilesN, 1, localTiles, g.K, g.nRanks, g.xchgMc != nullptr);
     const int grid = SmCount() & ~1;
     g.nGemmCtas = grid - workers;
     if (twoSm) {

@@ -47,6 +47,8 @@ struct DispatchBody {
         __shared__ uint32_t s_cnt[kMaxDevRanks * kMoeMaxExperts];   // [src][expert]
         __shared__ uint32_t s_base[kMoeMaxExperts];                 // slot base in the destination rank for (expert, src = me)
         __shared__ float s_scale[64];                               // up to 64 blocks of 128 -> hidden <= 8192
+        __shared__ uint4 s_row[8192 / 16];                          // the quantised row: hidden <= 8192 bytes of fp8
+        __shared__ uint64_t s_dst[kMoeMaxTopk];                     // (destination rank, slot) of the row's copies
         OpHead(c, b);
         const int p = c.nRanks, me = c.rank;
         const int E = a.nExperts, perRank = E / p;
@@ -104,35 +106,53 @@ struct DispatchBody {
                 if (v < vecPerRow && (threadIdx.x & 15) == 0) s_scale[v / 16] = fmaxf(amax, 1e-10f) / 448.f;
             }
             __syncthreads();
-            for (int k = 0; k < a.topk; ++k) {
-                const int pair = t * a.topk + k;
-                const int e = a.topkIdx[pair];
-                if (e < 0 || e >= E) { if (threadIdx.x == 0) a.slotMap[pair] = ~0ull; continue; }
-                const int d = e / perRank;
-                const uint32_t slot = s_base[e] + a.pos[pair];
-                if (threadIdx.x == 0) a.slotMap[pair] = ((uint64_t)d << 32) | slot;
-                if (slot >= a.capacity) continue;      // reported by the receiver's bounds check above
-                uint8_t* dstRow = a.recvX[d] + (size_t)slot * H;
-                // 16 bytes of fp8 = 16 elements = 2 input vectors per thread
-                for (int w = threadIdx.x; w < H / 16; w += blockDim.x) {
-                    const float inv = 1.f / s_scale[(w * 16) / 128];
-                    const uint4 r0 = row[2 * w], r1 = row[2 * w + 1];
-                    const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&r0);
-                    const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&r1);
-                    uint32_t outw[4];
+            // quantise the row ONCE into shared memory (16 bytes of fp8 = 16 elements = 2 input vectors per thread) ...
+            for (int w = threadIdx.x; w < H / 16; w += blockDim.x) {
+                const float inv = 1.f / s_scale[(w * 16) / 128];
+                const uint4 r0 = row[2 * w], r1 = row[2 * w + 1];
+                const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&r0);
+                const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&r1);
+                uint32_t outw[4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const __nv_bfloat162* h = j < 2 ? h0 + 2 * j : h1 + 2 * (j - 2);
-                        const float2 fa = __bfloat1622float2(h[0]), fb = __bfloat1622float2(h[1]);
-                        const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(fa.x * inv, fa.y * inv), __NV_SATFINITE, __NV_E4M3);
-                        const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(fb.x * inv, fb.y * inv), __NV_SATFINITE, __NV_E4M3);
-                        outw[j] = (uint32_t)lo | ((uint32_t)hi << 16);
-                    }
-                    reinterpret_cast<uint4*>(dstRow)[w] = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+                for (int j = 0; j < 4; ++j) {
+                    const __nv_bfloat162* h = j < 2 ? h0 + 2 * j : h1 + 2 * (j - 2);
+                    const float2 fa = __bfloat1622float2(h[0]), fb = __bfloat1622float2(h[1]);
+                    const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(fa.x * inv, fa.y * inv), __NV_SATFINITE, __NV_E4M3);
+                    const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(fb.x * inv, fb.y * inv), __NV_SATFINITE, __NV_E4M3);
+                    outw[j] = (uint32_t)lo | ((uint32_t)hi << 16);
                 }
-                float* dstScale = a.recvScale[d] + (size_t)slot * nScale;
-                for (int s = threadIdx.x; s < nScale; s += blockDim.x) dstScale[s] = s_scale[s];
-                if (threadIdx.x == 0) a.recvSrc[d][slot] = ((uint64_t)me << 32) | (uint32_t)pair;
+                s_row[w] = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+            }
+            // ... and where its topk copies go
+            if (threadIdx.x < a.topk) {
+                const int pair = t * a.topk + threadIdx.x;
+                const int e = a.topkIdx[pair];
+                uint64_t sm = ~0ull;
+                if (e >= 0 && e < E) sm = ((uint64_t)(e / perRank) << 32) | (uint64_t)(s_base[e] + a.pos[pair]);
+                a.slotMap[pair] = sm;
+                s_dst[threadIdx.x] = (sm != ~0ull && (uint32_t)sm < a.capacity) ? sm : ~0ull;      // overflow: reported by the receiver's bounds check above
+            }
+            __syncthreads();
+            // then the K copies leave as plain stores from shared memory: every thread has all K destinations' stores of
+            // its piece in flight together
+            for (int w = threadIdx.x; w < H / 16; w += blockDim.x) {
+                const uint4 q = s_row[w];
+#pragma unroll
+                for (int k = 0; k < kMoeMaxTopk; ++k) {
+                    if (k >= a.topk) break;
+                    const uint64_t sm = s_dst[k];
+                    if (sm == ~0ull) continue;
+                    reinterpret_cast<uint4*>(a.recvX[sm >> 32] + (size_t)(uint32_t)sm * H)[w] = q;
+                }
+            }
+            for (int i = threadIdx.x; i < a.topk * nScale; i += blockDim.x) {
+                const int k = i / nScale, sidx = i % nScale;
+                const uint64_t sm = s_dst[k];
+                if (sm != ~0ull) a.recvScale[sm >> 32][(size_t)(uint32_t)sm * nScale + sidx] = s_scale[sidx];
+            }
+            if (threadIdx.x < a.topk) {
+                const uint64_t sm = s_dst[threadIdx.x];
+                if (sm != ~0ull) a.recvSrc[sm >> 32][(uint32_t)sm] = ((uint64_t)me << 32) | (uint32_t)(t * a.topk + threadIdx.x);
             }
             __syncthreads();
         }
@@ -152,40 +172,60 @@ struct CombineBody {
         const uint64_t e0 = LoadEpoch(c, b);
         bool ok = RankBarrier(c, b, 0, e0 + 1, K_MOE_COMBINE);      // the peers' expert outputs are final
         const int H = a.hidden, vecPerRow = H / 8;
+        // Two pieces (16 bytes each) of a token row per thread and pass: 2 x topk remote loads are requested before the
+        // first is used (a pull over NVLink is bound by the bytes in flight, not by issue rate).
+        constexpr int U = 2;
         for (int t = b; t < a.nTokens && ok; t += nb) {
-            for (int v = threadIdx.x; v < vecPerRow; v += blockDim.x) {
-                float acc[8];
+            float w[kMoeMaxTopk];
+            const __nv_bfloat16* src[kMoeMaxTopk];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-                // all K rows are requested before the first is used: K remote loads in flight per thread
-                uint4 raw[kMoeMaxTopk];
-                float w[kMoeMaxTopk];
-#pragma unroll
-                for (int k = 0; k < kMoeMaxTopk; ++k) {
-                    if (k < a.topk) {
-                        const uint64_t sm = a.slotMap[t * a.topk + k];
+            for (int k = 0; k < kMoeMaxTopk; ++k) {
+                w[k] = 0.f;
+                src[k] = nullptr;
+                if (k < a.topk) {
+                    const uint64_t sm = a.slotMap[t * a.topk + k];
+                    if (sm != ~0ull && (uint32_t)sm < a.capacity) {
                         w[k] = a.topkWeight[t * a.topk + k];
-                        if (sm == ~0ull || (uint32_t)sm >= a.capacity) { w[k] = 0.f; raw[k] = make_uint4(0, 0, 0, 0); }
-                        else raw[k] = reinterpret_cast<const uint4*>(a.y[sm >> 32] + (size_t)(uint32_t)sm * H)[v];
+                        src[k] = a.y[sm >> 32] + (size_t)(uint32_t)sm * H;
+                    }
+                }
+            }
+            for (int v0 = threadIdx.x; v0 < vecPerRow; v0 += U * blockDim.x) {
+                uint4 raw[U][kMoeMaxTopk];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int v = v0 + u * blockDim.x;
+#pragma unroll
+                    for (int k = 0; k < kMoeMaxTopk; ++k) {
+                        raw[u][k] = make_uint4(0, 0, 0, 0);
+                        if (k < a.topk && v < vecPerRow && src[k] != nullptr) raw[u][k] = reinterpret_cast<const uint4*>(src[k])[v];
                     }
                 }
 #pragma unroll
-                for (int k = 0; k < kMoeMaxTopk; ++k) {
-                    if (k < a.topk) {
-                        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[k]);
+                for (int u = 0; u < U; ++u) {
+                    const int v = v0 + u * blockDim.x;
+                    if (v >= vecPerRow) continue;
+                    float acc[8];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float2 f = __bfloat1622float2(h[j]);
-                            acc[2 * j] += w[k] * f.x;
-                            acc[2 * j + 1] += w[k] * f.y;
+                    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+                    for (int k = 0; k < kMoeMaxTopk; ++k) {
+                        if (k < a.topk) {
+                            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u][k]);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float2 f = __bfloat1622float2(h[j]);
+                                acc[2 * j] += w[k] * f.x;
+                                acc[2 * j + 1] += w[k] * f.y;
+                            }
                         }
                     }
-                }
-                uint4 o;
-                __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+                    uint4 o;
+                    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-                reinterpret_cast<uint4*>(a.out + (size_t)t * H)[v] = o;
+                    for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+                    reinterpret_cast<uint4*>(a.out + (size_t)t * H)[v] = o;
+                }
             }
         }
         RankBarrier(c, b, 0, e0 + 2, K_MOE_COMBINE);                 // nobody overwrites its outputs while a peer still reads

@@ -130,12 +130,43 @@ __device__ __forceinline__ void BlockCopyBytes(char* dst, const char* src, size_
         uint4* d = reinterpret_cast<uint4*>(dst + head);
         for (size_t i = tid; i < nv; i += nt) d[i] = s[i];
         for (size_t b = head + (nv << 4) + tid; b < n; b += nt) dst[b] = src[b];
-    } else if ((((uintptr_t)dst | (uintptr_t)src | n) & 3u) == 0) {
-        const uint32_t* s = reinterpret_cast<const uint32_t*>(src);
-        uint32_t* d = reinterpret_cast<uint32_t*>(dst);
-        for (size_t i = tid; i < (n >> 2); i += nt) d[i] = s[i];
     } else {
-        for (size_t b = tid; b < n; b += nt) dst[b] = src[b];
+        // different misalignment: the loads (remote in the pull forms, a round trip each) stay 16-byte vectors from
+        // the source's aligned body; only the stores (local, posted) are split to what the destination's alignment
+        // allows - 4-, 2- or 1-byte pieces
+        size_t head = (16 - ((uintptr_t)src & 15u)) & 15u;
+        if (head > n) head = n;
+        for (size_t b = tid; b < head; b += nt) dst[b] = src[b];
+        const size_t nv = (n - head) >> 4;
+        const uint4* s = reinterpret_cast<const uint4*>(src + head);
+        char* d = dst + head;
+        const unsigned dal = (unsigned)((uintptr_t)d & 3u);
+        constexpr int U = 4;
+        for (size_t i = tid; i < nv; i += (size_t)U * nt) {
+            uint4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (i + (size_t)u * nt < nv) v[u] = s[i + (size_t)u * nt];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (i + (size_t)u * nt >= nv) continue;
+                char* o = d + ((i + (size_t)u * nt) << 4);
+                if (dal == 0) {
+                    const uint32_t* w = reinterpret_cast<const uint32_t*>(&v[u]);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) reinterpret_cast<uint32_t*>(o)[k] = w[k];
+                } else if (dal == 2) {
+                    const uint16_t* w = reinterpret_cast<const uint16_t*>(&v[u]);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) reinterpret_cast<uint16_t*>(o)[k] = w[k];
+                } else {
+                    const char* w = reinterpret_cast<const char*>(&v[u]);
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) o[k] = w[k];
+                }
+            }
+        }
+        for (size_t b = head + (nv << 4) + tid; b < n; b += nt) dst[b] = src[b];
     }
 }
 

@@ -5,7 +5,10 @@
 #include <cmath>
 #include <cstring>
 #include <dlfcn.h>
+#include <fstream>
+#include <mutex>
 #include <sstream>
+#include "../core/json.h"
 #include "../core/log.h"
 
 namespace hccl {
@@ -120,8 +123,48 @@ double Interp(const UtilPoint (&t)[N], double bytes)
 }
 }  // namespace
 
-double LinkUtilisation(NetType net, double bytes, HcclCommEngine)
+namespace {
+// measured curves per GPU count, loaded from a measurement file; empty = built-in curves
+struct LoadedCurves {
+    std::map<int, std::vector<UtilPoint>> p2p, nvls;
+    std::mutex mu;
+};
+LoadedCurves& Curves()
 {
+    static LoadedCurves c;
+    return c;
+}
+double InterpVec(const std::vector<UtilPoint>& t, double bytes)
+{
+    if (bytes <= t[0].bytes) return std::max(1e-4, t[0].util * bytes / t[0].bytes);
+    for (size_t i = 1; i < t.size(); ++i) {
+        if (bytes <= t[i].bytes) {
+            const double f = (std::log(bytes) - std::log(t[i - 1].bytes)) / (std::log(t[i].bytes) - std::log(t[i - 1].bytes));
+            return t[i - 1].util + f * (t[i].util - t[i - 1].util);
+        }
+    }
+    return t.back().util;
+}
+const std::vector<UtilPoint>* Nearest(const std::map<int, std::vector<UtilPoint>>& m, int nRanks)
+{
+    const std::vector<UtilPoint>* best = nullptr;
+    int bestDist = 1 << 30;
+    for (auto& kv : m) {
+        const int d = std::abs(kv.first - nRanks);
+        if (!kv.second.empty() && d < bestDist) { bestDist = d; best = &kv.second; }
+    }
+    return best;
+}
+}  // namespace
+
+double LinkUtilisation(NetType net, double bytes, HcclCommEngine, int nRanks)
+{
+    if (nRanks > 0 && (net == NetType::MESH_P2P || net == NetType::NVLS_SWITCH)) {
+        LoadedCurves& c = Curves();
+        std::lock_guard<std::mutex> lk(c.mu);
+        const std::vector<UtilPoint>* t = Nearest(net == NetType::MESH_P2P ? c.p2p : c.nvls, nRanks);
+        if (t != nullptr) return InterpVec(*t, bytes);
+    }
     switch (net) {
         case NetType::MESH_P2P: return Interp(kP2pUtil, bytes);
         case NetType::NVLS_SWITCH: return Interp(kNvlsUtil, bytes);
@@ -130,12 +173,71 @@ double LinkUtilisation(NetType net, double bytes, HcclCommEngine)
     }
 }
 
-double EvalCost(const std::vector<CostCoeff>& segs, CostAgg agg, double bytes, HcclCommEngine engine)
+bool LoadLinkModelFile(const std::string& path, std::string* err)
+{
+    std::ifstream f(path);
+    if (!f) { if (err) *err = "cannot open " + path; return false; }
+    std::stringstream ss;
+    ss << f.rdbuf();
+    JsonValue root;
+    std::string perr;
+    JsonParser parser(ss.str());
+    if (!parser.Parse(&root, &perr) || root.kind != JsonValue::OBJ) { if (err) *err = "not a JSON object: " + perr; return false; }
+    LinkModel lm = GlobalLinkModel();
+    if (const JsonValue* link = root.Get("link")) {
+        auto num = [&](const char* k, double* out) { const JsonValue* v = link->Get(k); if (v && v->kind == JsonValue::NUM && v->num > 0) *out = v->num; };
+        num("p2pGBs", &lm.p2pGBs); num("nvlsGBs", &lm.nvlsGBs); num("nvlsReduceOutGBs", &lm.nvlsReduceOutGBs); num("nvlsStoreGBs", &lm.nvlsStoreGBs);
+        num("localCopyGBs", &lm.localCopyGBs); num("localReduceGBs", &lm.localReduceGBs); num("launchUs", &lm.launchUs); num("barrierUs", &lm.barrierUs);
+        num("llHopUs", &lm.llHopUs);
+    }
+    std::map<int, std::vector<UtilPoint>> p2p, nvls;
+    if (const JsonValue* u = root.Get("utilisation")) {
+        for (const char* kind : {"p2p", "nvls"}) {
+            const JsonValue* k = u->Get(kind);
+            if (!k || k->kind != JsonValue::OBJ) continue;
+            for (auto& kv : k->obj) {
+                const int n = atoi(kv.first.c_str());
+                if (n < 2 || kv.second.kind != JsonValue::ARR) { if (err) *err = std::string("utilisation.") + kind + ": keys are GPU counts, values arrays of [bytes, utilisation]"; return false; }
+                std::vector<UtilPoint> pts;
+                for (const JsonValue& pt : kv.second.arr) {
+                    if (pt.kind != JsonValue::ARR || pt.arr.size() != 2 || pt.arr[0].num <= 0 || pt.arr[1].num <= 0 || pt.arr[1].num > 1.5 ||
+                        (!pts.empty() && pt.arr[0].num <= pts.back().bytes)) {
+                        if (err) *err = std::string("utilisation.") + kind + "." + kv.first + ": points must be [bytes, utilisation] with growing bytes and utilisation in (0, 1.5]";
+                        return false;
+                    }
+                    pts.push_back(UtilPoint{pt.arr[0].num, pt.arr[1].num});
+                }
+                if (!pts.empty()) (std::string(kind) == "p2p" ? p2p : nvls)[n] = pts;
+            }
+        }
+    }
+    GlobalLinkModel() = lm;
+    LoadedCurves& c = Curves();
+    std::lock_guard<std::mutex> lk(c.mu);
+    c.p2p = p2p;
+    c.nvls = nvls;
+    return true;
+}
+
+std::string DefaultLinkModelPath()
+{
+    if (const char* e = getenv("HCCL_LINK_MODEL_FILE")) return e;
+    Dl_info info;
+    if (dladdr((const void*)&DefaultLinkModelPath, &info) == 0 || info.dli_fname == nullptr) return "";
+    std::string lib = info.dli_fname;                       // .../hccl_b200/lib/libhccl_b200.so
+    const size_t slash = lib.rfind('/');
+    if (slash == std::string::npos) return "";
+    const std::string candidate = lib.substr(0, slash) + "/../data/link_model.json";
+    std::ifstream f(candidate);
+    return f ? candidate : "";
+}
+
+double EvalCost(const std::vector<CostCoeff>& segs, CostAgg agg, double bytes, HcclCommEngine engine, int nRanks)
 {
     std::map<int, double> groups;
     double floorSum = 0;
     for (const CostCoeff& s : segs) {
-        const double util = s.A > 0 ? LinkUtilisation(s.net, bytes * s.ratio, engine) : 1.0;
+        const double util = s.A > 0 ? LinkUtilisation(s.net, bytes * s.ratio, engine, nRanks) : 1.0;
         const double seg = (s.A / util + s.B + s.Bre) * bytes + s.C;
         double& g = groups[s.group];
         g = (agg == CostAgg::MAX) ? std::max(g, seg) : g + seg;
@@ -263,6 +365,15 @@ bool TopoMatches(const AlgEntry& a, const TopoInfo& topo, std::string* why)
 void BuildModel(SelectorState& st, const TopoInfo& topo)
 {
     EnsureAlgorithmsRegistered();
+    // link parameters and utilisation curves measured on the box, when a measurement file is there (once per process)
+    static std::once_flag linkModelOnce;
+    std::call_once(linkModelOnce, [] {
+        const std::string path = DefaultLinkModelPath();
+        if (path.empty()) return;
+        std::string err;
+        if (LoadLinkModelFile(path, &err)) HCCL_CONFIG_INFO(LOG_MOD_ALG, "link model loaded from %s", path.c_str());
+        else HCCL_WARNING("link model file %s ignored: %s", path.c_str(), err.c_str());
+    });
     const auto& all = AlgRegistry::Instance().All();
     st.modelDropReason.assign(all.size(), "");
     for (auto& v : st.modelAlgs) v.clear();
@@ -349,7 +460,7 @@ HcclResult SelectAlgorithm(SelectorState& st, const TopoInfo& topo, const EnvCon
         std::string why;
         if (!OpMatches(all[(size_t)idx], op, topo, &why)) { row.reason = why; out->table.push_back(row); continue; }
         row.viable = true;
-        row.cost = all[(size_t)idx].costCoeff ? EvalCost(all[(size_t)idx].costCoeff(topo, op), all[(size_t)idx].agg, (double)op.bytes, all[(size_t)idx].engine) : 1e9;
+        row.cost = all[(size_t)idx].costCoeff ? EvalCost(all[(size_t)idx].costCoeff(topo, op), all[(size_t)idx].agg, (double)op.bytes, all[(size_t)idx].engine, (int)topo.nRanks) : 1e9;
         out->table.push_back(row);
     }
     // Phase 2: HCCL_ALGO is a preference, not a hard filter: if any viable algorithm matches, only those compete

@@ -132,7 +132,15 @@ struct AlgNameDims { std::string engine, executor, templ; };
 bool MapAlgName(const AlgEntry& e, AlgNameDims* out);
 
 // Measured utilisation of a link class at a given per-link message size, in (0, 1].
-double LinkUtilisation(NetType net, double bytes, HcclCommEngine engine);
+// nRanks picks the curve measured at that GPU count (the nearest one measured; 0 = the built-in curve).
+double LinkUtilisation(NetType net, double bytes, HcclCommEngine engine, int nRanks = 0);
+// Replaces the link parameters and the utilisation curves with those of a measurement file (JSON, written by
+// bench/sweep.py --write-link-model): {"link": {"p2pGBs": ..}, "utilisation": {"p2p": {"2": [[bytes, util], ..], "8": ..},
+// "nvls": {..}}}.  Returns false and fills *err when the file cannot be read or parsed; the built-in values stay.
+bool LoadLinkModelFile(const std::string& path, std::string* err);
+// The file the library loads by itself on first use: HCCL_LINK_MODEL_FILE, else data/link_model.json beside the
+// Python package / the library.  Empty when none exists.
+std::string DefaultLinkModelPath();
 // Peak figures (GB/s, us) the coefficients are built from; overridable for tests and by calibration.
 struct LinkModel {
     double p2pGBs = 770.0;        // measured peer copy per direction per GPU
@@ -190,7 +198,7 @@ struct Selection {
 HcclResult SelectAlgorithm(SelectorState& st, const TopoInfo& topo, const EnvConfig& env, const OpDesc& op,
                            const std::string& commName, HcclComm commHandle, uint64_t bufferBytes, Selection* out);
 // Pure helpers (unit-tested).
-double EvalCost(const std::vector<CostCoeff>& segs, CostAgg agg, double bytes, HcclCommEngine engine);
+double EvalCost(const std::vector<CostCoeff>& segs, CostAgg agg, double bytes, HcclCommEngine engine, int nRanks = 0);
 std::vector<HcclCommEngine> EngineTiers(HcclCommEngine requested);
 std::string FormatCostTable(const Selection& s);
 HcclResult TunerInit(SelectorState& st, const EnvConfig& env, const TopoInfo& topo, const std::string& commName,

@@ -54,6 +54,39 @@ def timed_each(fn, warm, iters, group=None):
     return t.mean().item(), t.max().item()
 
 
+def graph_replay_us(fn, calls=10, replays=5, group=None):
+    """Device time of one call when `calls` of them are captured in a CUDA graph and replayed (no host launch cost
+    between them): the max over ranks of the best replay, in microseconds; None when the capture fails."""
+    try:
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(calls):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        multi = dist.is_initialized() and dist.get_world_size(group) > 1
+        best = float("inf")
+        for _ in range(replays):
+            if multi:
+                dist.barrier(group)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1) * 1000.0 / calls)
+        t = torch.tensor([best], device="cuda", dtype=torch.float64)
+        if multi:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        del g
+        return t.item()
+    except Exception:                                  # noqa: BLE001  (a library that cannot be captured just has no figure)
+        torch.cuda.synchronize()
+        return None
+
+
 def _v_counts(n, world, rank):
     """Uneven split of n elements for the AlltoAllV rows: the block this rank sends to peer q is (1 + ((rank + q) % 3) / 4)
     shares wide; the matrix is symmetric, so receive counts equal send counts."""
@@ -129,6 +162,12 @@ def collective_ladder(comm, sizes=LADDER, dtypes=("bf16", "fp32"), ops=("all_red
                     row[impl + "_busbw_gbs"] = moved / (mean * 1e-3) / 1e9 * f
                     if impl != "nccl":
                         row[impl + "_alg"] = comm.last_algorithm()
+                if nbytes <= (4 << 20):
+                    # without the host: what the device needs per call (launch-bound calls otherwise measure Python)
+                    row["hccl_sym_graph_us"] = graph_replay_us(make("hccl_sym"))
+                    row["nccl_graph_us"] = graph_replay_us(make("nccl"))
+                    if row["hccl_sym_graph_us"] and row["nccl_graph_us"]:
+                        row["sym_vs_nccl_graph"] = row["nccl_graph_us"] / row["hccl_sym_graph_us"]
                 row["sym_vs_nccl"] = row["nccl_us"] / row["hccl_sym_us"]
                 if with_plain:
                     row["plain_vs_nccl"] = row["nccl_us"] / row["hccl_us"]

@@ -47,16 +47,29 @@ def test_dispatch_combine_emulated(p, tokens, hidden, experts, topk):
         for le in range(per):
             seg = srank[off[le]:off[le + 1]]
             assert seg == sorted(seg)
-    # "experts": y = 2 * dequantised input (so the combine result is known)
+    # "experts": expert e multiplies by 1 + (e % 7) / 4, a different factor per expert of a token, so that the combine
+    # result depends on WHICH gate weight meets which expert output (a constant factor would hide a wrong pairing)
+    def factor(e):
+        return 1.0 + (e % 7) / 4.0
+
     for r in range(p):
-        n = int(res[r].offsets[-1])
-        disp[r].y[:n] = (2 * dequantize(res[r].x_fp8[:n], res[r].scales[:n])).bfloat16()
+        off = res[r].offsets.cpu().tolist()
+        n = off[-1]
+        deq = dequantize(res[r].x_fp8[:n], res[r].scales[:n])
+        for le in range(per):
+            deq[off[le]:off[le + 1]] *= factor(r * per + le)
+        disp[r].y[:n] = deq.bfloat16()
     outs = [d.combine(w) for d, w in zip(disp, ws)]
     torch.cuda.synchronize()
     for r in range(p):
-        ref = 2 * xs[r].float()                       # weights sum to 1
+        f = torch.tensor([[factor(int(e)) if e >= 0 else 0.0 for e in row] for row in idxs[r].cpu().tolist()], device="cuda")
+        ref = xs[r].float() * (ws[r].float() * f).sum(1, keepdim=True)
         err = (outs[r].float() - ref).abs().max().item()
         assert err <= 0.08 * ref.abs().max().item() + 1e-2, err
+        # the check can tell a wrong pairing: the same sum with the weights of each token rotated by one is far off
+        if topk > 1:
+            wrong = xs[r].float() * (ws[r].float().roll(1, dims=1) * f).sum(1, keepdim=True)
+            assert (wrong - ref).abs().max().item() > 0.1 * ref.abs().max().item()
     # a second round reuses all buffers
     res = [d.dispatch(x, i) for d, x, i in zip(disp, xs, idxs)]
     torch.cuda.synchronize()
