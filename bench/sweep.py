@@ -4,10 +4,13 @@
         bench/sweep.py --ops all_reduce,all_gather,reduce_scatter,broadcast,all_to_all --dtypes bf16,fp32 \
         --min-bytes 8 --max-bytes 1073741824 --out sweep_8gpu.jsonl
 
-Per (op, dtype, size): 20 warm-up + 100 timed iterations (fewer above 64 MiB), device-timed with CUDA events, max over
-ranks; algBW = bytes / time, busBW = algBW * factor.  `size` is the per-rank message size as in nccl-tests: the full
-buffer for all_reduce / broadcast, the total (all ranks) for all_gather / reduce_scatter / all_to_all.  Inputs are
-uniform[-1, 1] seeded by rank.  Rows: impl in {hccl (plain buffers), hccl_sym (symmetric memory, zero copy), nccl}.
+Per (op, dtype, size): 20 warm-up + 100 timed iterations (fewer above 64 MiB), every iteration timed on its own with
+CUDA events (max over ranks), repeated `--repeats` times: `time_us` is the median of the repeats' means, `max_us` the
+slowest single iteration of all repeats (an intermittent stall shows there, not in a footnote).  algBW = bytes / time,
+busBW = algBW * factor.  `size` is the per-rank message size as in nccl-tests: the full buffer for all_reduce /
+broadcast, the total (all ranks) for all_gather / reduce_scatter / all_to_all(_v).  Inputs are uniform[-1, 1] seeded
+by rank.  Rows: impl in {hccl (plain buffers), hccl_sym (symmetric memory, zero copy), nccl}.  `all_to_all_v` moves
+uneven blocks (4 : 5 : 6 shares, a symmetric count matrix).
 """
 from __future__ import annotations
 
@@ -22,6 +25,7 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import hccl_b200 as hb  # noqa: E402
 from hccl_b200.utils import bus_bandwidth_factor  # noqa: E402
+from hccl_b200.utils.headline import _v_counts, timed_each  # noqa: E402
 
 DTYPES = {"bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}
 
@@ -52,6 +56,7 @@ def main():
     ap.add_argument("--out", default="")
     ap.add_argument("--iters", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--repeats", type=int, default=3)
     ap.add_argument("--check", action="store_true", help="verify results against NCCL at every size")
     args = ap.parse_args()
 
@@ -83,7 +88,7 @@ def main():
                 sym_in.copy_(plain_in)
             for size in sizes:
                 n = max(1, size // es)
-                if op in ("all_gather", "reduce_scatter", "all_to_all"):
+                if op in ("all_gather", "reduce_scatter", "all_to_all", "all_to_all_v"):
                     if n < world:
                         continue
                     n = n // world * world
@@ -92,9 +97,15 @@ def main():
                 iters = args.iters if nbytes <= (64 << 20) else max(5, args.iters // 10)
                 warm = args.warmup if nbytes <= (64 << 20) else 3
 
+                sc, sd = _v_counts(n, world, rank)
+
                 def make(impl):
                     src = sym_in if impl == "hccl_sym" else plain_in
                     dst = sym_out if impl == "hccl_sym" else plain_out
+                    if op == "all_to_all_v":
+                        if impl == "nccl":
+                            return lambda: dist.all_to_all_single(plain_out[:sum(sc)], plain_in[:sum(sc)], sc, sc)
+                        return lambda: comm.all_to_all_v(src, sc, sd, dst, sc, sd)
                     if impl == "nccl":
                         if op == "all_reduce":
                             return lambda: dist.all_reduce(plain_out[:n])
@@ -115,7 +126,9 @@ def main():
                         return lambda: comm.broadcast(dst[:n], 0)
                     return lambda: comm.all_to_all(src[:n], dst[:n])
 
-                if args.check and op != "broadcast":
+                if op == "all_to_all_v":
+                    nbytes = sum(sc) * es
+                if args.check and op not in ("broadcast", "all_to_all_v"):
                     ref = torch.empty_like(plain_out[:n])
                     if op == "all_reduce":
                         ref.copy_(plain_in[:n]); dist.all_reduce(ref)
@@ -136,10 +149,16 @@ def main():
                         if not torch.allclose(got[:m].float(), ref[:m].float(), rtol=tol, atol=tol * world):
                             raise SystemExit(f"rank {rank}: {impl} {op} {dname} size {nbytes} differs from NCCL")
                 for impl in impls:
-                    ms = timed(make(impl), warm, iters)
+                    fn = make(impl)
+                    means, worst = [], 0.0
+                    for _ in range(max(1, args.repeats)):
+                        mean, mx = timed_each(fn, warm, iters)
+                        means.append(mean)
+                        worst = max(worst, mx)
+                    ms = sorted(means)[len(means) // 2]
                     alg = nbytes / (ms * 1e-3) / 1e9
-                    row = {"op": op, "dtype": dname, "bytes": nbytes, "impl": impl, "time_us": ms * 1000, "algbw_gbs": alg,
-                           "busbw_gbs": alg * bus_bandwidth_factor(op, world), "n_gpus": world,
+                    row = {"op": op, "dtype": dname, "bytes": nbytes, "impl": impl, "time_us": ms * 1000, "max_us": worst * 1000, "algbw_gbs": alg,
+                           "busbw_gbs": alg * bus_bandwidth_factor("all_to_all" if op == "all_to_all_v" else op, world), "n_gpus": world,
                            "alg": comm.last_algorithm() if impl != "nccl" else "nccl"}
                     rows.append(row)
                     if rank == 0:

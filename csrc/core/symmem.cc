@@ -32,107 +32,178 @@ namespace {
 
 size_t RoundUp(size_t v, size_t g) { return (v + g - 1) / g * g; }
 
-HcclResult AllocVmm(Bootstrap& bs, int device, size_t size, bool wantMc, SymSegment* seg, bool* mcDone)
+// Releases whatever a (possibly half-built) VMM segment holds: mappings, address ranges, imported and local handles,
+// the multicast binding.  Safe on a segment that is only partly filled in.
+void ReleaseVmm(SymSegment* seg, int device)
 {
     const DriverApi* d = GetDriverApi();
-    if (!d) return HCCL_E_DRV;
+    if (!d) return;
+    if (seg->mc) {
+        d->cuMemUnmap((CUdeviceptr)seg->mc, seg->mappedSize);
+        d->cuMemAddressFree((CUdeviceptr)seg->mc, seg->mappedSize);
+        seg->mc = nullptr;
+    }
+    if (seg->mcHandle) {
+        CUdevice dev;
+        // the binding goes before the object: an object released while memory is still bound keeps the switch's
+        // multicast group alive until the last bound allocation is freed
+        if (seg->mcBound && d->cuMulticastUnbind && d->cuDeviceGet(&dev, device) == CUDA_SUCCESS) d->cuMulticastUnbind(seg->mcHandle, dev, 0, seg->mappedSize);
+        d->cuMemRelease(seg->mcHandle);
+        seg->mcHandle = 0;
+        seg->mcBound = false;
+    }
+    for (int q = 0; q < seg->nRanks; ++q) {
+        if (seg->peer[q]) {
+            d->cuMemUnmap((CUdeviceptr)seg->peer[q], seg->mappedSize);
+            d->cuMemAddressFree((CUdeviceptr)seg->peer[q], seg->mappedSize);
+            seg->peer[q] = nullptr;
+        }
+        if (q != seg->rank && seg->peerHandle[q]) { d->cuMemRelease(seg->peerHandle[q]); seg->peerHandle[q] = 0; }
+    }
+    if (seg->localHandle) { d->cuMemRelease(seg->localHandle); seg->localHandle = 0; }
+}
+
+// VMM allocation in phases.  Every phase ends in ONE status all ranks agree on: a rank whose local step failed still
+// takes part in every exchange of the phase (descriptor passing, barrier, agreement), so the ranks never get out of
+// step on the bootstrap, and on an agreed failure every rank releases what it has acquired and returns the same
+// error.  Reserved address ranges, imported handles and descriptors are released on every path.
+HcclResult AllocVmm(Bootstrap& bs, int device, size_t size, bool wantMc, SymSegment* seg, bool* mcDone)
+{
+    *mcDone = false;
+    const DriverApi* d = GetDriverApi();
     const int p = bs.nRanks(), me = bs.rank();
-    CUdevice dev;
-    CHK_CU(d->cuDeviceGet(&dev, device));
+    bool ok = d != nullptr, all = false;
+    // ---- phase 1: create and export the local allocation
+    CUdevice dev = 0;
     CUmemAllocationProp prop;
     memset(&prop, 0, sizeof(prop));
     prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
     prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
     prop.location.id = device;
     prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
-    size_t gran = 0;
-    CHK_CU(d->cuMemGetAllocationGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED));
     CUmulticastObjectProp mprop;
     memset(&mprop, 0, sizeof(mprop));
-    if (wantMc) {
+    size_t gran = 0, msize = 0;
+    CUmemGenericAllocationHandle h = 0;
+    int fd = -1;
+    auto step = [&](CUresult r, const char* what) {
+        if (ok && r != CUDA_SUCCESS) { HCCL_ERROR("%s failed: %s", what, DriverErrorString(r)); ok = false; }
+    };
+    if (ok) step(d->cuDeviceGet(&dev, device), "cuDeviceGet");
+    if (ok) step(d->cuMemGetAllocationGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED), "cuMemGetAllocationGranularity");
+    if (ok && wantMc) {
         mprop.numDevices = (unsigned)p;
         mprop.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
         mprop.size = RoundUp(size, gran);
         size_t mg = 0;
         if (d->cuMulticastGetGranularity(&mg, &mprop, CU_MULTICAST_GRANULARITY_RECOMMENDED) == CUDA_SUCCESS && mg > gran) gran = mg;
     }
-    const size_t msize = RoundUp(size, gran);
-    mprop.size = msize;
-    CUmemGenericAllocationHandle h = 0;
-    CHK_CU(d->cuMemCreate(&h, msize, &prop, 0));
-    seg->localHandle = h;
-    seg->mappedSize = msize;
-    int fd = -1;
-    CHK_CU(d->cuMemExportToShareableHandle(&fd, h, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0));
-    for (int k = 1; k < p; ++k) CHK_RET(bs.SendFd((me + k) % p, fd));
+    if (ok) {
+        msize = RoundUp(size, gran);
+        mprop.size = msize;
+        step(d->cuMemCreate(&h, msize, &prop, 0), "cuMemCreate");
+    }
+    if (ok) {
+        seg->localHandle = h;
+        seg->mappedSize = msize;
+        step(d->cuMemExportToShareableHandle(&fd, h, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0), "cuMemExportToShareableHandle");
+    }
+    CHK_RET(bs.AgreeAll(ok, &all));
+    if (!all) {
+        if (fd >= 0) ::close(fd);
+        ReleaseVmm(seg, device);
+        return HCCL_E_DRV;
+    }
+    // ---- phase 2: pass the descriptors around, import and map every rank's allocation
+    HcclResult net = HCCL_SUCCESS;      // a bootstrap failure ends the attempt for everybody (the peers' calls fail too)
+    for (int k = 1; k < p && net == HCCL_SUCCESS; ++k) net = bs.SendFd((me + k) % p, fd);
     CUmemAccessDesc acc;
     memset(&acc, 0, sizeof(acc));
     acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
     acc.location.id = device;
     acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
-    for (int k = 0; k < p; ++k) {
+    for (int k = 0; k < p && net == HCCL_SUCCESS; ++k) {
         const int q = (me + k) % p;
         CUmemGenericAllocationHandle hq = h;
         if (q != me) {
             int pfd = -1;
-            CHK_RET(bs.RecvFd(q, &pfd));
-            CUresult r = d->cuMemImportFromShareableHandle(&hq, (void*)(uintptr_t)pfd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+            net = bs.RecvFd(q, &pfd);                      // received even after a local failure: the sender has sent it
+            if (net != HCCL_SUCCESS) break;
+            if (ok) {
+                CUresult r = d->cuMemImportFromShareableHandle(&hq, (void*)(uintptr_t)pfd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+                if (r != CUDA_SUCCESS) { HCCL_ERROR("importing rank %d's allocation failed: %s", q, DriverErrorString(r)); ok = false; }
+                else seg->peerHandle[q] = hq;
+            }
             ::close(pfd);
-            if (r != CUDA_SUCCESS) { HCCL_ERROR("importing rank %d's allocation failed: %s", q, DriverErrorString(r)); return HCCL_E_DRV; }
-            seg->peerHandle[q] = hq;
         }
+        if (!ok) continue;
         CUdeviceptr va = 0;
-        CHK_CU(d->cuMemAddressReserve(&va, msize, gran, 0, 0));
-        CHK_CU(d->cuMemMap(va, msize, 0, hq, 0));
-        CHK_CU(d->cuMemSetAccess(va, msize, &acc, 1));
-        seg->peer[q] = (void*)va;
+        step(d->cuMemAddressReserve(&va, msize, gran, 0, 0), "cuMemAddressReserve");
+        if (!ok) continue;
+        CUresult r = d->cuMemMap(va, msize, 0, hq, 0);
+        if (r != CUDA_SUCCESS) { d->cuMemAddressFree(va, msize); step(r, "cuMemMap"); continue; }
+        seg->peer[q] = (void*)va;                           // from here on ReleaseVmm unmaps and frees the range
+        step(d->cuMemSetAccess(va, msize, &acc, 1), "cuMemSetAccess");
     }
     ::close(fd);
-    CHK_RET(bs.Barrier());  // everyone has imported: exporters may drop their descriptors
-    *mcDone = false;
+    if (net != HCCL_SUCCESS) { ReleaseVmm(seg, device); return net; }
+    CHK_RET(bs.AgreeAll(ok, &all));     // also the point after which exporters may drop their descriptors: everyone has imported
+    if (!all) { ReleaseVmm(seg, device); return HCCL_E_DRV; }
     if (!wantMc) return HCCL_SUCCESS;
-    // Multicast object: created by rank 0, joined by every device, then each rank binds its own allocation.
+    // ---- phase 3: multicast object, created by rank 0, joined by every device; then each rank binds its allocation.
+    // A failure here only turns NVLS off: the peer mappings stay.
     CUmemGenericAllocationHandle mc = 0;
-    bool okLocal = true;
+    bool mcOk = true;
+    int mfd = -1;
     if (me == 0) {
         CUresult r = d->cuMulticastCreate(&mc, &mprop);
-        if (r != CUDA_SUCCESS) { HCCL_WARNING("cuMulticastCreate failed (%s): NVLS off", DriverErrorString(r)); okLocal = false; }
+        if (r != CUDA_SUCCESS) { HCCL_WARNING("cuMulticastCreate failed (%s): NVLS off", DriverErrorString(r)); mcOk = false; }
+        if (mcOk && d->cuMemExportToShareableHandle(&mfd, mc, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0) != CUDA_SUCCESS) mcOk = false;
     }
-    bool all = false;
-    CHK_RET(bs.AgreeAll(okLocal, &all));
-    if (!all) return HCCL_SUCCESS;
+    CHK_RET(bs.AgreeAll(mcOk, &all));
+    auto dropMc = [&]() {
+        if (mfd >= 0) ::close(mfd);
+        if (mc) d->cuMemRelease(mc);
+    };
+    if (!all) { dropMc(); return HCCL_SUCCESS; }
     if (me == 0) {
-        int mfd = -1;
-        CHK_CU(d->cuMemExportToShareableHandle(&mfd, mc, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0));
-        for (int q = 1; q < p; ++q) CHK_RET(bs.SendFd(q, mfd));
+        for (int q = 1; q < p && net == HCCL_SUCCESS; ++q) net = bs.SendFd(q, mfd);
         ::close(mfd);
+        mfd = -1;
     } else {
-        int mfd = -1;
-        CHK_RET(bs.RecvFd(0, &mfd));
-        CUresult r = d->cuMemImportFromShareableHandle(&mc, (void*)(uintptr_t)mfd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
-        ::close(mfd);
-        if (r != CUDA_SUCCESS) okLocal = false;
+        net = bs.RecvFd(0, &mfd);
+        if (net == HCCL_SUCCESS) {
+            if (d->cuMemImportFromShareableHandle(&mc, (void*)(uintptr_t)mfd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR) != CUDA_SUCCESS) { mc = 0; mcOk = false; }
+            ::close(mfd);
+            mfd = -1;
+        }
     }
-    if (okLocal && d->cuMulticastAddDevice(mc, dev) != CUDA_SUCCESS) okLocal = false;
-    CHK_RET(bs.AgreeAll(okLocal, &all));   // every device must be added before any bind
-    if (!all) { if (mc) d->cuMemRelease(mc); return HCCL_SUCCESS; }
+    if (net != HCCL_SUCCESS) { dropMc(); ReleaseVmm(seg, device); return net; }
+    if (mcOk && d->cuMulticastAddDevice(mc, dev) != CUDA_SUCCESS) mcOk = false;
+    CHK_RET(bs.AgreeAll(mcOk, &all));   // every device must be added before any bind
+    if (!all) { dropMc(); return HCCL_SUCCESS; }
+    seg->mcHandle = mc;
     CUresult br = d->cuMulticastBindMem(mc, 0, h, 0, msize, 0);
-    if (br != CUDA_SUCCESS) { HCCL_WARNING("cuMulticastBindMem failed (%s): NVLS off", DriverErrorString(br)); okLocal = false; }
+    if (br != CUDA_SUCCESS) { HCCL_WARNING("cuMulticastBindMem failed (%s): NVLS off", DriverErrorString(br)); mcOk = false; }
+    else seg->mcBound = true;
     CUdeviceptr mva = 0;
-    if (okLocal) {
-        if (d->cuMemAddressReserve(&mva, msize, gran, 0, 0) != CUDA_SUCCESS || d->cuMemMap(mva, msize, 0, mc, 0) != CUDA_SUCCESS ||
-            d->cuMemSetAccess(mva, msize, &acc, 1) != CUDA_SUCCESS)
-            okLocal = false;
+    if (mcOk) {
+        if (d->cuMemAddressReserve(&mva, msize, gran, 0, 0) != CUDA_SUCCESS) mcOk = false;
+        else if (d->cuMemMap(mva, msize, 0, mc, 0) != CUDA_SUCCESS) { d->cuMemAddressFree(mva, msize); mva = 0; mcOk = false; }
+        else {
+            seg->mc = (void*)mva;
+            if (d->cuMemSetAccess(mva, msize, &acc, 1) != CUDA_SUCCESS) mcOk = false;
+        }
     }
-    CHK_RET(bs.AgreeAll(okLocal, &all));
+    CHK_RET(bs.AgreeAll(mcOk, &all));
     if (!all) {
-        if (mva) { d->cuMemUnmap(mva, msize); d->cuMemAddressFree(mva, msize); }
-        d->cuMulticastUnbind(mc, dev, 0, msize);
+        // only the multicast part goes: unmap the alias, unbind, release the object
+        if (seg->mc) { d->cuMemUnmap((CUdeviceptr)seg->mc, msize); d->cuMemAddressFree((CUdeviceptr)seg->mc, msize); seg->mc = nullptr; }
+        if (seg->mcBound) { d->cuMulticastUnbind(mc, dev, 0, msize); seg->mcBound = false; }
         d->cuMemRelease(mc);
+        seg->mcHandle = 0;
         return HCCL_SUCCESS;
     }
-    seg->mc = (void*)mva;
-    seg->mcHandle = mc;
     *mcDone = true;
     return HCCL_SUCCESS;
 }
@@ -187,6 +258,7 @@ HcclResult SymAlloc(Bootstrap& bs, int device, size_t size, bool wantMc, bool fo
             return bs.Barrier();
         }
         HCCL_WARNING("VMM symmetric allocation failed on some rank (local result %s): falling back to CUDA IPC", ResultString(r));
+        ReleaseVmm(out, device);      // a rank that succeeded while a peer failed gives its mappings back
         *out = SymSegment();
         out->size = size; out->rank = bs.rank(); out->nRanks = bs.nRanks();
     }
@@ -228,18 +300,9 @@ HcclResult SymFree(SymSegment* seg)
     if (!seg || seg->transport == SymTransport::NONE) return HCCL_SUCCESS;
     const DriverApi* d = GetDriverApi();
     if (seg->transport == SymTransport::VMM && d) {
-        if (seg->mc) {
-            d->cuMemUnmap((CUdeviceptr)seg->mc, seg->mappedSize);
-            d->cuMemAddressFree((CUdeviceptr)seg->mc, seg->mappedSize);
-        }
-        if (seg->mcHandle) d->cuMemRelease(seg->mcHandle);
-        for (int q = 0; q < seg->nRanks; ++q) {
-            if (!seg->peer[q]) continue;
-            d->cuMemUnmap((CUdeviceptr)seg->peer[q], seg->mappedSize);
-            d->cuMemAddressFree((CUdeviceptr)seg->peer[q], seg->mappedSize);
-            if (q != seg->rank && seg->peerHandle[q]) d->cuMemRelease(seg->peerHandle[q]);
-        }
-        if (seg->localHandle) d->cuMemRelease(seg->localHandle);
+        int device = 0;
+        cudaGetDevice(&device);
+        ReleaseVmm(seg, device);      // unmaps the alias, unbinds the allocation from the multicast object, then releases
     } else if (seg->transport == SymTransport::IPC) {
         for (int q = 0; q < seg->nRanks; ++q) {
             if (!seg->peer[q]) continue;

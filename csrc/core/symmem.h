@@ -30,6 +30,7 @@ struct SymSegment {
     void* mc = nullptr;              // multicast alias or nullptr
     // bookkeeping for release
     unsigned long long localHandle = 0, mcHandle = 0;
+    bool mcBound = false;            // the local allocation is bound to the multicast object
     unsigned long long peerHandle[HCCL_MAX_DEVICE_RANKS] = {0};
     void* ipcBase[HCCL_MAX_DEVICE_RANKS] = {nullptr};   // USER_IPC: what cudaIpcOpenMemHandle returned for each peer
     bool ContainsLocal(const void* p, size_t bytes) const

@@ -181,7 +181,8 @@ bool LoadLinkModelFile(const std::string& path, std::string* err)
     ss << f.rdbuf();
     JsonValue root;
     std::string perr;
-    JsonParser parser(ss.str());
+    const std::string text = ss.str();          // the parser keeps a reference
+    JsonParser parser(text);
     if (!parser.Parse(&root, &perr) || root.kind != JsonValue::OBJ) { if (err) *err = "not a JSON object: " + perr; return false; }
     LinkModel lm = GlobalLinkModel();
     if (const JsonValue* link = root.Get("link")) {

@@ -483,3 +483,61 @@ def test_plan_cache_capacity_eviction_and_generation():
     assert over["newest"] == 1 and over["alg"] == 8193
     many = run(30000)
     assert many["size"] <= 8192 and many["key1"] == 1 and many["newest"] == 1
+
+
+def test_link_model_file_replaces_curves_per_gpu_count(tmp_path):
+    """The cost model's utilisation curves come from a measurement file when one is given: one curve per link class
+    and GPU count, the nearest count applies; a malformed file is refused and changes nothing."""
+    import json
+
+    lib.HcclDebugLinkUtilisation.restype = ctypes.c_double
+    lib.HcclDebugLinkUtilisation.argtypes = [ctypes.c_int, ctypes.c_double, ctypes.c_uint32]
+    lib.HcclLoadLinkModel.argtypes = [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_uint32]
+    builtin = lib.HcclDebugLinkUtilisation(1, float(1 << 20), 8)
+    good = tmp_path / "lm.json"
+    good.write_text(json.dumps({"link": {"p2pGBs": 770.0}, "utilisation": {
+        "p2p": {"2": [[65536, 0.1], [1048576, 0.5], [16777216, 0.9]], "8": [[65536, 0.05], [1048576, 0.3], [16777216, 0.8]]},
+        "nvls": {"8": [[1048576, 0.4], [16777216, 0.85]]}}}))
+    err = ctypes.create_string_buffer(256)
+    assert lib.HcclLoadLinkModel(str(good).encode(), err, 256) == 0, err.value
+    assert abs(lib.HcclDebugLinkUtilisation(1, float(1 << 20), 2) - 0.5) < 1e-9
+    assert abs(lib.HcclDebugLinkUtilisation(1, float(1 << 20), 8) - 0.3) < 1e-9
+    assert abs(lib.HcclDebugLinkUtilisation(1, float(1 << 20), 4) - 0.5) < 1e-9 or abs(lib.HcclDebugLinkUtilisation(1, float(1 << 20), 4) - 0.3) < 1e-9
+    assert abs(lib.HcclDebugLinkUtilisation(1, float(1 << 20), 3) - 0.5) < 1e-9          # nearest measured count
+    assert abs(lib.HcclDebugLinkUtilisation(2, float(1 << 24), 8) - 0.85) < 1e-9
+    mid = lib.HcclDebugLinkUtilisation(1, float(1 << 22), 8)                               # log-interpolated between the points
+    assert 0.3 < mid < 0.8
+    bad = tmp_path / "bad.json"
+    bad.write_text(json.dumps({"utilisation": {"p2p": {"8": [[1048576, 0.3], [65536, 0.05]]}}}))       # sizes must grow
+    assert lib.HcclLoadLinkModel(str(bad).encode(), err, 256) != 0 and b"growing" in err.value
+    assert abs(lib.HcclDebugLinkUtilisation(1, float(1 << 20), 8) - 0.3) < 1e-9            # the refused file changed nothing
+    assert lib.HcclLoadLinkModel(str(tmp_path / "missing.json").encode(), err, 256) != 0
+    # back to the built-in curves for the tests that follow
+    empty = tmp_path / "empty.json"
+    empty.write_text("{}")
+    assert lib.HcclLoadLinkModel(str(empty).encode(), err, 256) == 0
+    assert abs(lib.HcclDebugLinkUtilisation(1, float(1 << 20), 8) - builtin) < 1e-12
+
+
+def test_reductions_with_cast_and_scale_on_the_host_engine():
+    comms = Communicator.host_sim(4, None, hb.make_config(buffer_mib=4, exec_timeout_ms=20000))
+    n = 1000
+    ins = [np.random.default_rng(r).standard_normal(n).astype(np.float32) for r in range(4)]
+    outs16 = [np.zeros(n, dtype=np.float16) for _ in range(4)]
+    outs = [np.zeros(n // 4, dtype=np.float32) for _ in range(4)]
+
+    def body(r, c):
+        c.all_reduce_ex(ins[r], outs16[r], scale=0.25)
+        c.reduce_scatter_ex(ins[r], outs[r], scale=2.0)
+
+    from test_host_engine import run_ranks
+
+    run_ranks(comms, body)
+    mean = np.stack(ins).astype(np.float64).mean(0)
+    for r in range(4):
+        np.testing.assert_allclose(outs16[r].astype(np.float64), mean, rtol=2e-3, atol=2e-3)
+        np.testing.assert_allclose(outs[r], 2.0 * np.stack(ins).sum(0)[r * (n // 4):(r + 1) * (n // 4)], rtol=1e-5, atol=1e-5)
+    with pytest.raises(hb.HcclError):
+        comms[0].all_reduce_ex(np.zeros(4, dtype=np.int32), np.zeros(4, dtype=np.int32), scale=0.5)
+    for c in comms:
+        c.destroy()
