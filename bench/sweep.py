@@ -46,6 +46,43 @@ def timed(fn, warm, iters):
     return t.item()
 
 
+def human(b):
+    for unit, size in (("GiB", 1 << 30), ("MiB", 1 << 20), ("KiB", 1 << 10)):
+        if b >= size and b % size == 0:
+            return f"{b // size} {unit}"
+    return f"{b} B"
+
+
+def write_markdown(rows, path, command):
+    """One table per (op, dtype): time (busBW) of the symmetric-buffer and the ordinary-buffer path and of NCCL, the
+    slowest single iteration of this library's symmetric path, the algorithm that ran, and the ratios."""
+    import collections
+
+    t = collections.OrderedDict()
+    for r in rows:
+        t.setdefault((r["op"], r["dtype"], r["bytes"]), {})[r["impl"]] = r
+    world = rows[0]["n_gpus"] if rows else 0
+    with open(path, "w") as f:
+        f.write(f"# Collective sweep against NCCL, {world} x B200\n\nCommand:\n\n    {command}\n\n"
+                "Every iteration is timed on its own with CUDA events (maximum over ranks); `us` is the median over the repeats of the mean, "
+                "`max` the slowest single iteration of all repeats; busBW follows nccl-tests.  `sym` = buffers from `HcclMemAlloc` "
+                "(read and written in place on the peers), `plain` = ordinary tensors staged through the slab.\n")
+        cur = None
+        for (op, dt, b), d in t.items():
+            if (op, dt) != cur:
+                cur = (op, dt)
+                f.write(f"\n### {op}, {dt}\n\n| size | sym us (busBW GB/s) | sym max us | algorithm | plain us | NCCL us (busBW) | NCCL max us | sym / NCCL | plain / NCCL |\n"
+                        "|---|---|---|---|---|---|---|---|---|\n")
+            s_, p_, n_ = d.get("hccl_sym"), d.get("hccl"), d.get("nccl")
+            if not (s_ and n_):
+                continue
+            f.write(f"| {human(b)} | {s_['time_us']:.1f} ({s_['busbw_gbs']:.0f}) | {s_.get('max_us', 0):.1f} | {s_['alg']} | "
+                    f"{p_['time_us']:.1f} | {n_['time_us']:.1f} ({n_['busbw_gbs']:.0f}) | {n_.get('max_us', 0):.1f} | "
+                    f"{n_['time_us'] / s_['time_us']:.2f}x | {n_['time_us'] / p_['time_us']:.2f}x |\n" if p_ else
+                    f"| {human(b)} | {s_['time_us']:.1f} ({s_['busbw_gbs']:.0f}) | {s_.get('max_us', 0):.1f} | {s_['alg']} | - | "
+                    f"{n_['time_us']:.1f} ({n_['busbw_gbs']:.0f}) | {n_.get('max_us', 0):.1f} | {n_['time_us'] / s_['time_us']:.2f}x | - |\n")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ops", default="all_reduce,all_gather,reduce_scatter,broadcast,all_to_all")
@@ -57,6 +94,7 @@ def main():
     ap.add_argument("--iters", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--repeats", type=int, default=3)
+    ap.add_argument("--markdown", default="", help="also write the tables as markdown to this file")
     ap.add_argument("--check", action="store_true", help="verify results against NCCL at every size")
     args = ap.parse_args()
 
@@ -172,6 +210,8 @@ def main():
         with open(args.out, "w") as f:
             for r in rows:
                 f.write(json.dumps(r) + "\n")
+    if rank == 0 and args.markdown:
+        write_markdown(rows, args.markdown, f"python -m torch.distributed.run --nnodes=1 --nproc-per-node {world} --master-addr 127.0.0.1 " + " ".join(sys.argv))
     comm.destroy()
     dist.destroy_process_group()
 

@@ -252,11 +252,15 @@ HcclResult HcclCalcOpResource(HcclComm comm, HcclCMDType op, uint64_t count, Hcc
     uint64_t limit = registered ? ~0ull : (perRank && op != HCCL_CMD_ALLGATHER ? L.inBytes / P * P : L.inBytes);
     if (sel.alg->devAlg == DALG_AR_TWOSHOT || sel.alg->devAlg == DALG_AR_NVLS || sel.alg->devAlg == DALG_BCAST_TWOSHOT || sel.alg->devAlg == DALG_REDUCE_TWOSHOT)
         limit = std::min<uint64_t>(limit, L.xchBytes);
+    // push forms: one landing copy (half of the stage-in region) holds a launch's blocks
+    if (sel.alg->devAlg == DALG_AR_PUSH_TWOSHOT) limit = std::min<uint64_t>(L.inBytes / 2 / 128 * 128 - 16 * P, L.xchBytes);
+    if (sel.alg->devAlg == DALG_RS_PUSH) limit = L.inBytes / 2 / P / 128 * 128 * P;
     res->launches = (uint32_t)std::max<uint64_t>(1, limit == ~0ull || d.bytes == 0 ? 1 : (d.bytes + limit - 1) / limit);
     res->scratchBytes = std::min<uint64_t>(staged, limit == ~0ull ? staged : limit);
     const uint64_t perLaunch = d.bytes / res->launches;
     uint64_t traffic = perLaunch;
-    if (sel.alg->devAlg == DALG_AR_TWOSHOT || sel.alg->devAlg == DALG_AR_NVLS) traffic = perLaunch / P * 2 + 1;
+    if (sel.alg->devAlg == DALG_AR_TWOSHOT || sel.alg->devAlg == DALG_AR_NVLS || sel.alg->devAlg == DALG_AR_PUSH_TWOSHOT) traffic = perLaunch / P * 2 + 1;
+    if (sel.alg->devAlg == DALG_RS_PUSH) traffic = perLaunch / P + 1;
     uint64_t nb = ll ? std::min<uint64_t>((perLaunch / (op == HCCL_CMD_ALLGATHER ? P : 1) + 8191) / 8192, 8) : (traffic + (128u << 10) - 1) / (128u << 10);
     res->blocks = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(nb, (uint64_t)c->MaxBlocks()));
     return HCCL_SUCCESS;

@@ -1,4 +1,5 @@
 #include "config.h"
+#include <atomic>
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
@@ -307,8 +308,12 @@ const EnvConfig& GetEnvConfig()
     return *g_cfg;
 }
 
+static std::atomic<uint32_t> g_cfgVersion{0};
+uint32_t EnvConfigVersion() { return g_cfgVersion.load(std::memory_order_relaxed); }
+
 void ReloadEnvConfig()
 {
+    g_cfgVersion.fetch_add(1, std::memory_order_relaxed);
     {
         std::lock_guard<std::mutex> lk(g_mu);
         delete g_cfg;

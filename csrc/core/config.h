@@ -90,6 +90,7 @@ EnvConfig ParseEnvConfig(const EnvGetter& get);
 // Cached process-wide config (parsed on first use); ReloadEnvConfig re-reads.
 const EnvConfig& GetEnvConfig();
 void ReloadEnvConfig();
+uint32_t EnvConfigVersion();     // counts reloads: cached selections are keyed by it (HCCL_ALGO and friends may have changed)
 
 // The effective settings of one communicator after merging HcclCommConfig.
 struct EffectiveConfig {

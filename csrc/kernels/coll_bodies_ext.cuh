@@ -509,8 +509,9 @@ struct BcastScatterNvlsBody {
 // AlltoAll through the receivers' slabs.  The pull form pays a table exchange and two barriers around the
 // transfer; here a rank WRITES its block for q into q's stage-in region (posted stores, no round trip), one
 // barrier publishes everything, and every rank copies its received blocks out locally.  The landing zone holds two
-// copies by parity of the block row's epoch: to write for operator n + 2 a rank has passed the barrier of n + 1,
-// which the peer entered after finishing n, so the copy a peer still reads is never the one being written.  The
+// copies, taken in turn by the communicator's count of push operators (LoadPushSeq): to write for push operator
+// n + 2 a rank has finished n + 1, which the peer entered after finishing n, so the copy a peer still reads is never
+// the one being written.  The
 // stage-in region is the one part of a slab that no other operator writes from a remote rank (its owner stages
 // into it before a barrier), which is what makes the missing closing barrier safe.  `bytes` = one pair's block (equal
 // for all pairs); the copy of parity h starts at src[q] + h * chunk, the block from rank r inside it at r * slot.
@@ -524,7 +525,8 @@ struct A2aPushBody {
         const int p = c.nRanks, me = c.rank;
         const uint64_t e = LoadEpoch(c, b);
         const size_t slot = (a.bytes + 15) & ~(size_t)15;
-        const size_t region = (size_t)(e & 1u) * a.chunk;
+        const uint64_t seq = LoadPushSeq(c);
+        const size_t region = (size_t)(seq & 1u) * a.chunk;
         size_t sb, se;
         Share(a.bytes, nb, b, 16, &sb, &se);
         for (int k = 1; k < p; ++k) {
@@ -538,6 +540,105 @@ struct A2aPushBody {
             BlockCopyBytes(a.out + a.dsp[q] + sb, a.src[me] + region + (size_t)q * slot + sb, se - sb);
         }
         StoreEpoch(c, b, e + 1);
+        FinishPushSeq(c, seq, nb);
+        OpTail(c, b);
+    }
+};
+
+// ---------------------------------------------------------------------------------------------------------------
+// ReduceScatter and AllReduce for ORDINARY (unregistered) buffers without the stage-in pass.  The pull forms first
+// copy the whole input into the slab so that the peers can read it: a full extra pass over the message.  Here a
+// rank writes block q of its input straight into rank q's slab (posted stores over NVLink, the input is read once,
+// locally), one barrier publishes everything, and every rank reduces the p - 1 blocks that landed in its own slab
+// with its own block, which it reads in place.  Landing zone and parity rule are those of A2aPushBody (stage-in
+// region, two copies taken in turn, no closing barrier).  cnt / dsp2 as in RsBody with equal blocks of `bytes`
+// (one chunk of a larger message per launch); chunk = size of one landing copy.  Sync points: 1.
+template <class T>
+struct RsPushBody {
+    using Args = CollArgs;
+    static constexpr int kThreads = 512;
+    __device__ static void Run(const DevComm& c, const Args& a, int b, int nb)
+    {
+        OpHead(c, b);
+        const int p = c.nRanks, me = c.rank;
+        const uint64_t e = LoadEpoch(c, b);
+        const size_t slot = (a.bytes + 15) & ~(size_t)15;
+        const uint64_t seq = LoadPushSeq(c);
+        const size_t region = (size_t)(seq & 1u) * a.chunk;
+        size_t sb, se;
+        Share(a.bytes, nb, b, 16, &sb, &se);
+        // BlockReduceRange wants all sources equally aligned: the landed blocks are 16-byte aligned, so an input block
+        // that is not goes through this rank's own landing slot as well (a local copy)
+        const bool ownDirect = (((uintptr_t)(a.in + a.dsp2[me])) & 15u) == 0;
+        for (int k = ownDirect ? 1 : 0; k < p; ++k) {
+            const int q = (me + k) % p;
+            BlockCopyBytes(const_cast<char*>(a.src[q]) + region + (size_t)me * slot + sb, a.in + a.dsp2[q] + sb, se - sb);
+        }
+        RankBarrier(c, b, 0, e + 1, K_RS);
+        const char* srcs[kMaxDevRanks];
+        for (int q = 0; q < p; ++q) srcs[q] = (q == me && ownDirect) ? a.in + a.dsp2[me] + sb : a.src[me] + region + (size_t)q * slot + sb;
+        BlockReduceRange<T>(srcs, p, a.out + sb, nullptr, 0, se - sb, a.op);
+        StoreEpoch(c, b, e + 1);
+        FinishPushSeq(c, seq, nb);
+        OpTail(c, b);
+    }
+};
+
+// AllReduce for ordinary buffers, two-shot without the stage-in pass: the ReduceScatter above leaves slice `me`
+// reduced in this rank's exchange region (and in `out`), then every rank pulls the other slices from their owners.
+// bytes = the whole message of this launch, sliced over the ranks in 16-byte units; chunk = one landing copy.
+// Sync points: 3 (landing, slices ready, slices read).
+template <class T>
+struct ArPushTwoShotBody {
+    using Args = CollArgs;
+    static constexpr int kThreads = 512;
+    __device__ static void Run(const DevComm& c, const Args& a, int b, int nb)
+    {
+        OpHead(c, b);
+        const int p = c.nRanks, me = c.rank;
+        const uint64_t e = LoadEpoch(c, b);
+        size_t s0, s1;
+        Share(a.bytes, p, 0, 16, &s0, &s1);
+        const size_t slot = s1 - s0;                               // the widest slice (slices are equal except the last)
+        // the landing copies are taken in turn: a push operator without a closing barrier may have used the other one
+        // just before, and its reader may still be busy
+        const uint64_t seq = LoadPushSeq(c);
+        const size_t region = (size_t)(seq & 1u) * a.chunk;
+        const bool ownDirect = (((uintptr_t)a.in) & 15u) == 0;
+        for (int k = ownDirect ? 1 : 0; k < p; ++k) {
+            const int q = (me + k) % p;
+            size_t off, len;
+            SliceSub(a.bytes, p, q, nb, b, &off, &len);
+            size_t q0, q1;
+            Share(a.bytes, p, q, 16, &q0, &q1);
+            BlockCopyBytes(const_cast<char*>(a.src[q]) + region + (size_t)me * slot + (off - q0), a.in + off, len);
+        }
+        RankBarrier(c, b, 0, e + 1, K_AR_TWOSHOT);
+        size_t off, len, m0, m1;
+        SliceSub(a.bytes, p, me, nb, b, &off, &len);
+        Share(a.bytes, p, me, 16, &m0, &m1);
+        {
+            const char* srcs[kMaxDevRanks];
+            for (int q = 0; q < p; ++q) srcs[q] = (q == me && ownDirect) ? a.in + off : a.src[me] + region + (size_t)q * slot + (off - m0);
+            BlockReduceRange<T>(srcs, p, a.xch[me] + off, nullptr, 0, len, a.op);
+            __syncthreads();
+            BlockCopyBytes(a.out + off, a.xch[me] + off, len);
+        }
+        RankBarrier(c, b, 0, e + 2, K_AR_TWOSHOT);
+        {
+            CopySeg segs[kMaxDevRanks];
+            int n = 0;
+            for (int k = 1; k < p; ++k) {
+                const int q = (me + k) % p;
+                size_t qo, ql;
+                SliceSub(a.bytes, p, q, nb, b, &qo, &ql);
+                segs[n++] = CopySeg{a.out + qo, a.xch[q] + qo, ql};
+            }
+            BlockCopyMulti(segs, n);
+        }
+        RankBarrier(c, b, 0, e + 3, K_AR_TWOSHOT);
+        StoreEpoch(c, b, e + 3);
+        FinishPushSeq(c, seq, nb);
         OpTail(c, b);
     }
 };

@@ -50,6 +50,8 @@ HcclResult LaunchCollectiveExt(const LaunchTarget& t, DevAlg alg, HcclDataType d
         case DALG_RS_CAST: return CastIn<RsCastBody>(t, dtype, outType, a, nb);
         case DALG_RS_RING: HCCL_REDUCE_DISPATCH_EXT(RsRingBody) break;
         case DALG_AR_RHD: HCCL_REDUCE_DISPATCH_EXT(ArRhdBody) break;
+        case DALG_RS_PUSH: HCCL_REDUCE_DISPATCH_EXT(RsPushBody) break;
+        case DALG_AR_PUSH_TWOSHOT: HCCL_REDUCE_DISPATCH_EXT(ArPushTwoShotBody) break;
         case DALG_AG_RING: return LaunchBody<AgRingBody>(t, a, nb);
         case DALG_AG_NVLS: return LaunchBody<AgNvlsBody>(t, a, nb);
         case DALG_BCAST_SCATTER_NVLS: return LaunchBody<BcastScatterNvlsBody>(t, a, nb);

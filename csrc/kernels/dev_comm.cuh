@@ -166,6 +166,31 @@ __device__ __forceinline__ void FinishLLEpoch(const DevComm& c, uint64_t epoch, 
     }
 }
 
+// The push forms (blocks written into the receivers' stage-in region, no closing barrier) alternate between two
+// landing copies.  Which copy an operator uses must not depend on a block row (rows cover different byte ranges from
+// operator to operator, and their barrier epochs drift apart when operators use different grids), so the parity comes
+// from one counter per communicator that counts push operators: every block reads it at entry, the last block to
+// finish advances it.  All ranks issue the same operators in the same order, so the counters agree; being
+// device-resident they survive CUDA-graph replay.  Why two copies suffice: a rank that writes for push operator n + 2
+// has finished kernel n + 1, in which at least one of its block rows passed a barrier that the peer's row entered
+// after the peer's kernel n had ended (stream order).
+__device__ __forceinline__ uint64_t LoadPushSeq(const DevComm& c)
+{
+    return *reinterpret_cast<volatile uint64_t*>(c.epochs + kMaxBlocks + 2);
+}
+__device__ __forceinline__ void FinishPushSeq(const DevComm& c, uint64_t seq, int nBlocks)
+{
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long* ticket = reinterpret_cast<unsigned long long*>(c.epochs + kMaxBlocks + 3);
+        const unsigned long long t = atomicAdd(ticket, 1ull);
+        if (t == (unsigned long long)(nBlocks - 1)) {
+            *reinterpret_cast<volatile uint64_t*>(ticket) = 0;
+            *reinterpret_cast<volatile uint64_t*>(c.epochs + kMaxBlocks + 2) = seq + 1;
+        }
+    }
+}
+
 // Barrier among the blocks with index `block` of all ranks, on flag slot `slot`.
 // Everything the calling block wrote before the barrier (local or peer memory)
 // is visible to every participating block after it.  All threads of the block

@@ -43,6 +43,8 @@ enum DevAlg : int {
     DALG_RS_RING, DALG_AG_RING, DALG_AR_RHD,
     // switch multicast AllGather, Broadcast as scatter + switch AllGather, AlltoAll through the receivers' slabs
     DALG_AG_NVLS, DALG_BCAST_SCATTER_NVLS, DALG_A2A_PUSH,
+    // ordinary buffers without the stage-in pass: blocks pushed into the receivers' slabs
+    DALG_RS_PUSH, DALG_AR_PUSH_TWOSHOT,
     DALG_COUNT
 };
 

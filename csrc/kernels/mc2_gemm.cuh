@@ -72,6 +72,7 @@ struct GemmArgs {
     __nv_bfloat16* xchg[kMaxDevRanks];
     // device-resident control block of the communicator's MC2 state (local memory):
     //   [0] launch epoch, [1] exit ticket, [2] abort, [16 ..) per-row-block ready counters (AG)
+    uint64_t* trace;                // timeline words per CTA (kTraceWords each), filled only by builds with HCCL_MC2_TRACE
     uint32_t* ctl;
     // tile-ready flags for RS / AR: tileFlag[q] = rank q's flag array mapped here, index [srcRank][tile]
     uint64_t* tileFlag[kMaxDevRanks];
@@ -104,6 +105,19 @@ struct GemmArgs {
     int rsCoop;
 };
 constexpr int kCtlEpoch = 0, kCtlTicket = 1, kCtlAbort = 2, kCtlPushNext = 3, kCtlPushGo = 4, kCtlReduceNext = 5, kCtlReady = 16;
+
+// Timeline of a fused launch for performance work: builds with -DHCCL_MC2_TRACE (hccl_b200/build.py --trace) make
+// every role of every CTA of the two-SM kernel write where its time went; other builds compile none of it.
+// Absolute points are global-timer nanoseconds, durations are SM clock cycles.
+enum TraceWord {
+    TR_START_NS = 0, TR_GO_NS, TR_PROD_READY_CLK, TR_PROD_FIRST_REMOTE_NS, TR_PROD_EMPTY_CLK, TR_PROD_END_NS, TR_MMA_FULL_CLK, TR_MMA_TMEM_CLK,
+    TR_MMA_END_NS, TR_EPI_PUSH_CLK, TR_EPI_PIECES, TR_EPI_DRAIN_CLK, TR_EPI_FULL_CLK, TR_EPI_END_NS, TR_EPI_TAIL_PUSH_CLK, TR_TILES, kTraceWords
+};
+#ifdef HCCL_MC2_TRACE
+#define MC2_TR(...) __VA_ARGS__
+#else
+#define MC2_TR(...)
+#endif
 // agPush values
 constexpr int kAgPull = 0, kAgPushWorkers = 1, kAgPushCoop = 2;
 
@@ -184,15 +198,52 @@ __device__ __forceinline__ void Store32Cols(__nv_bfloat16* dst, const uint32_t (
 
 // Drains this warp's 32 accumulator rows x `bn` columns from TMEM and stores them as bf16 through the staging area.
 // rowPtr(r, d) returns the address of column 0 of the tile in destination d for warp row r (nullptr = skip the row);
-// validCols = columns of the tile that exist in the matrix.
-//
-// Software pipeline over chunks of 64 columns: the two tensor-memory loads of chunk i + 1 are issued BEFORE chunk i is
-// copied from the staging area to its destination, so their latency is covered by that copy (global / peer stores are
-// posted); one wait per chunk instead of one per 32 columns.  An accumulator of 256 columns leaves in about a third
-// of the time of the unpipelined form, which matters wherever the epilogue is not hidden behind a long main loop
-// (inner dimensions of one or two thousand, and the wide-tile kernel).
+// validCols = columns of the tile that exist in the matrix.  One tensor-memory load of 32 columns at a time: the
+// kernels that use it hide the epilogue behind the next tile's main loop, and there the short form measured better
+// inside a power-limited training step than the software-pipelined one below (fewer live registers, less switching).
 template <class RowPtrFn>
 __device__ __forceinline__ void DrainTile(uint32_t taddrLane, int bn, uint8_t* stg, int lane, int validCols, int nDst, RowPtrFn rowPtr)
+{
+    for (int c0 = 0; c0 < bn; c0 += 64) {
+        const int chunk = (bn - c0) < 64 ? (bn - c0) : 64;
+        for (int h = 0; h < chunk; h += 32) {
+            uint32_t v[32];
+            TmemLd32x32(taddrLane + (uint32_t)(c0 + h), v);
+            TmemLdWait();
+            uint4* d = reinterpret_cast<uint4*>(stg + lane * kStgRowBytes + h * 2);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
+                    w[j] = *reinterpret_cast<uint32_t*>(&b);
+                }
+                d[i] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+        __syncwarp();
+        const int piecesPerRow = chunk / 8;          // 16-byte pieces
+        for (int i = lane; i < 32 * piecesPerRow; i += 32) {
+            const int r = i / piecesPerRow, pc = i % piecesPerRow;
+            const int col = c0 + pc * 8;
+            if (col >= validCols) continue;
+            const uint4 val = *reinterpret_cast<const uint4*>(stg + r * kStgRowBytes + pc * 16);
+            for (int dd = 0; dd < nDst; ++dd) {
+                __nv_bfloat16* p = rowPtr(r, dd);
+                if (p != nullptr) *reinterpret_cast<uint4*>(p + col) = val;
+            }
+        }
+        __syncwarp();
+    }
+}
+
+// The same drain as a software pipeline over chunks of 64 columns: the two tensor-memory loads of chunk i + 1 are
+// issued BEFORE chunk i is copied from the staging area to its destination, so their latency is covered by that copy
+// (global / peer stores are posted); one wait per chunk instead of one per 32 columns.  For kernels whose epilogue is
+// NOT hidden behind a main loop (the wide-tile kernel, whose accumulator fills all of tensor memory).
+template <class RowPtrFn>
+__device__ __forceinline__ void DrainTilePipelined(uint32_t taddrLane, int bn, uint8_t* stg, int lane, int validCols, int nDst, RowPtrFn rowPtr)
 {
     uint32_t va[32], vb[32];
     auto issue = [&](int c0) {

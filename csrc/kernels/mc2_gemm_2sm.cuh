@@ -184,6 +184,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 int stage = 0;
                 uint32_t phase = 0;
                 bool ok = true;
+                MC2_TR(long long trReady = 0, trEmpty = 0; const long long trC0 = clock64(); uint64_t trFirst = 0; int trTiles = 0; if (g.trace) g.trace[(size_t)cta * kTraceWords + TR_START_NS] = TimerNs();)
                 const uint64_t polA = g.l2HintA == 1 ? L2PolicyEvictLast() : L2PolicyEvictFirst();
                 const uint64_t polB = g.l2HintB == 1 ? L2PolicyEvictLast() : L2PolicyEvictFirst();
                 for (int t = pair; t < nTiles && ok; t += nPairs) {
@@ -196,13 +197,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                     const int rowA = (own ? mt - ownFirst : mt) * kBM;
                     if (MODE == MODE_AG && !own) {
                         const int nWorkers = (int)gridDim.x - g.nGemmCtas;
+                        MC2_TR(const long long c0 = clock64();)
                         if (g.agPush) ok = SpinUntilGE64(g.agReady[g.rank] + mt, (uint64_t)g.K * 2 * kBM, abortWord);
                         else ok = SpinUntilGE(g.ctl + kCtlReady + mt, (uint32_t)nWorkers, abortWord);
+                        MC2_TR(trReady += clock64() - c0; if (trFirst == 0) trFirst = TimerNs();)
                         FenceProxyAsync();
                         if (!ok) break;
                     }
+                    MC2_TR(++trTiles;)
                     for (int kb = 0; kb < kBlocks; ++kb) {
+                        MC2_TR(const long long c1 = clock64();)
                         ok = MbarWait(&emptyBar[stage], phase ^ 1u, abortWord, kWaitLimitNs);
+                        MC2_TR(trEmpty += clock64() - c1;)
                         if (!ok) break;
                         uint8_t* sa = smem + stage * L::kStageBytes;
                         uint8_t* sb = sa + L::kABytes;
@@ -237,6 +243,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                     const uint64_t t0 = TimerNs();
                     while (TimerNs() - t0 < 200000) {}
                 }
+                MC2_TR(if (g.trace) {
+                    uint64_t* w = g.trace + (size_t)cta * kTraceWords;
+                    w[TR_PROD_READY_CLK] = (uint64_t)trReady; w[TR_PROD_FIRST_REMOTE_NS] = trFirst; w[TR_PROD_EMPTY_CLK] = (uint64_t)trEmpty;
+                    w[TR_PROD_END_NS] = TimerNs(); w[TR_TILES] = (uint64_t)trTiles; w[TR_EPI_PIECES] = (uint64_t)(clock64() - trC0);   // producer's cycles: the clock rate
+                })
             }
         } else if (warp == 1) {
             // ===== MMA issuer: leader CTA only
@@ -247,13 +258,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 int acc = 0;
                 uint32_t accPhase = 0;
                 bool ok = true;
+                MC2_TR(long long trFull = 0, trTmem = 0;)
                 for (int t = pair; t < nTiles && ok; t += nPairs) {
+                    MC2_TR(const long long c0 = clock64();)
                     ok = MbarWait(&tmemEmpty[acc], accPhase ^ 1u, abortWord, kWaitLimitNs);
+                    MC2_TR(trTmem += clock64() - c0;)
                     if (!ok) break;
                     TcFenceAfter();
                     const uint32_t tmemD = tmemBase + (uint32_t)(acc * kBN2);
                     for (int kb = 0; kb < kBlocks; ++kb) {
+                        MC2_TR(const long long c1 = clock64();)
                         ok = MbarWait(&fullBar[stage], phase, abortWord, kWaitLimitNs);
+                        MC2_TR(trFull += clock64() - c1;)
                         if (!ok) break;
                         TcFenceAfter();
                         const uint32_t sa = SmemAddr(smem + stage * L::kStageBytes);
@@ -273,6 +289,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                     UmmaCommit2Sm(&tmemFull[acc]);
                     if (++acc == 2) { acc = 0; accPhase ^= 1u; }
                 }
+                MC2_TR(if (g.trace) {
+                    uint64_t* w = g.trace + (size_t)cta * kTraceWords;
+                    w[TR_MMA_FULL_CLK] = (uint64_t)trFull; w[TR_MMA_TMEM_CLK] = (uint64_t)trTmem; w[TR_MMA_END_NS] = TimerNs();
+                })
             }
         } else {
             // ===== epilogue warps 2..5 of both CTAs: each CTA drains its own 128 accumulator rows
@@ -285,14 +305,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             bool pushLeft = MODE == MODE_AG && g.agPush == kAgPushCoop;
             bool reduceLeft = MODE == MODE_RS && (warp - 2) < g.rsCoop;      // g.rsCoop of the four epilogue warps reduce
             int reducePending = -1;
-            if (pushLeft && cta == 0 && warp == 2) CoopPushOpen(c, g, launchEpoch, lane);
+            MC2_TR(long long trPush = 0, trDrain = 0, trWait = 0, trTail = 0; const bool trMe = g.trace != nullptr && warp == 3 && lane == 0;)
+            if (pushLeft && cta == 0 && warp == 2) {
+                CoopPushOpen(c, g, launchEpoch, lane);
+                MC2_TR(if (g.trace && lane == 0) g.trace[TR_GO_NS] = TimerNs();)
+            }
             for (int t = pair; t < nTiles && ok; t += nPairs) {
                 int mt2, nt;
                 TileCoord2<MODE>(g, t, tilesM2, &mt2, &nt);
                 const int mt = mt2 * 2 + (int)crank;
+                MC2_TR(const long long c0 = clock64();)
                 if (MODE == MODE_AG && pushLeft) pushLeft = CoopPushWhileWaiting(g, launchEpoch, lane, &tmemFull[acc], accPhase);
                 if (MODE == MODE_RS && reduceLeft) reduceLeft = CoopReduceWhileWaiting(g, launchEpoch, lane, &reducePending, &tmemFull[acc], accPhase);
+                MC2_TR(const long long c1 = clock64(); trPush += c1 - c0;)
                 ok = MbarWait(&tmemFull[acc], accPhase, abortWord, kWaitLimitNs);
+                MC2_TR(const long long c2 = clock64(); trWait += c2 - c1;)
                 if (!ok) break;
                 TcFenceAfter();
                 const int row0 = mt * kBM + quarter * 32;
@@ -315,6 +342,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 }
                 TcFenceBefore();
                 __syncwarp();
+                MC2_TR(trDrain += clock64() - c2;)
                 if (lane == 0) MbarArriveCluster(SmemAddr(&tmemEmpty[acc]) & kPeerBitMask);     // the leader's barrier
                 if (++acc == 2) { acc = 0; accPhase ^= 1u; }
                 if (MODE == MODE_RS) {
@@ -329,8 +357,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                     }
                 }
             }
+            MC2_TR(const long long c3 = clock64();)
             if (MODE == MODE_AG && pushLeft) CoopPushDrain(g, launchEpoch, lane);
             if (MODE == MODE_RS && reduceLeft) CoopReduceDrain(g, launchEpoch, lane, &reducePending);
+            MC2_TR(trTail = clock64() - c3;
+                   if (trMe) {
+                       uint64_t* w = g.trace + (size_t)cta * kTraceWords;
+                       w[TR_EPI_PUSH_CLK] = (uint64_t)trPush; w[TR_EPI_DRAIN_CLK] = (uint64_t)trDrain; w[TR_EPI_FULL_CLK] = (uint64_t)trWait;
+                       w[TR_EPI_TAIL_PUSH_CLK] = (uint64_t)trTail; w[TR_EPI_END_NS] = TimerNs();
+                   })
         }
         // teardown: nobody leaves while its peer may still touch its shared memory, barriers or TMEM
         TcFenceBefore();

@@ -2,6 +2,8 @@
 #include "mc2_launch.h"
 #include <map>
 #include <mutex>
+#include <string>
+#include <vector>
 #include "../core/comm.h"
 #include "../core/cuda_driver.h"
 #include "../core/log.h"
@@ -279,6 +281,50 @@ void FillPeers(CommImpl* comm, GemmArgs* g)
 
 }  // namespace
 
+#ifdef HCCL_MC2_TRACE
+// Trace builds only: one timeline buffer per process, dumped as JSON lines (one per CTA) for the launches
+// HCCL_MC2_TRACE_FROM .. +2 of each kind into <HCCL_MC2_TRACE_FILE>.rank<r>.jsonl.
+namespace {
+uint64_t* TraceBuffer(int grid)
+{
+    static uint64_t* buf = nullptr;
+    static int cap = 0;
+    if (grid > cap) {
+        if (buf) cudaFree(buf);
+        if (cudaMalloc(&buf, (size_t)grid * mc2::kTraceWords * sizeof(uint64_t)) != cudaSuccess) { buf = nullptr; cap = 0; return nullptr; }
+        cap = grid;
+    }
+    cudaMemset(buf, 0, (size_t)grid * mc2::kTraceWords * sizeof(uint64_t));
+    return buf;
+}
+void TraceDump(const char* kind, int which, const GemmArgs& g, int grid, cudaStream_t stream)
+{
+    static int launches[4] = {0, 0, 0, 0};
+    static const int from = [] { const char* e = getenv("HCCL_MC2_TRACE_FROM"); return e ? atoi(e) : 8; }();
+    const char* prefix = getenv("HCCL_MC2_TRACE_FILE");
+    const int n = launches[which]++;
+    if (prefix == nullptr || g.trace == nullptr || n < from || n >= from + 3) return;
+    cudaStreamSynchronize(stream);
+    std::vector<uint64_t> h((size_t)grid * mc2::kTraceWords);
+    cudaMemcpy(h.data(), g.trace, h.size() * sizeof(uint64_t), cudaMemcpyDeviceToHost);
+    const std::string path = std::string(prefix) + ".rank" + std::to_string(g.rank) + ".jsonl";
+    FILE* f = fopen(path.c_str(), "a");
+    if (!f) return;
+    for (int c = 0; c < grid; ++c) {
+        fprintf(f, "{\"kind\": \"%s\", \"launch\": %d, \"rank\": %d, \"cta\": %d, \"M\": %d, \"N\": %d, \"K\": %d, \"bn\": %d, \"w\": [", kind, n, g.rank, c, g.M, g.N, g.K, g.bn);
+        for (int i = 0; i < mc2::kTraceWords; ++i) fprintf(f, "%s%llu", i ? ", " : "", (unsigned long long)h[(size_t)c * mc2::kTraceWords + i]);
+        fprintf(f, "]}\n");
+    }
+    fclose(f);
+}
+}  // namespace
+#define MC2_TRACE_ARM(g, grid) (g).trace = TraceBuffer(grid)
+#define MC2_TRACE_DUMP(kind, which, g, grid, stream) TraceDump(kind, which, g, grid, stream)
+#else
+#define MC2_TRACE_ARM(g, grid)
+#define MC2_TRACE_DUMP(kind, which, g, grid, stream)
+#endif
+
 HcclResult Mc2EnsureState(CommImpl* comm, uint64_t parityBytes)
 {
     if (comm->emulated() || comm->hostComm) return HCCL_E_NOT_SUPPORT;
@@ -468,7 +514,10 @@ HcclResult Mc2AllGatherMatmul(CommImpl* comm, const void* aShard, const void* b,
         g.bn = bestBn;
         g.tilesN = (int)((n + bestBn - 1) / bestBn);
         CHK_RET(MapB(&tb, b, n, k, bMn, bestBn / 2));
-        return DispatchLayout2Sm<MODE_AG>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream, &taOwn);
+        MC2_TRACE_ARM(g, grid);
+        const HcclResult r = DispatchLayout2Sm<MODE_AG>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream, &taOwn);
+        MC2_TRACE_DUMP("ag_matmul", 0, g, grid, stream);
+        return r;
     }
     return DispatchLayout<256, MODE_AG>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream, &taOwn);
 }
@@ -508,7 +557,11 @@ HcclResult Mc2MatmulReduceScatter(CommImpl* comm, const void* a, const void* b, 
     // block while they wait for accumulators.  HCCL_MC2_RS_WORKERS=<n> keeps n dedicated reduction CTAs instead.
     int workers = 0;
     static const int rsWarps = [] { const char* e = getenv("HCCL_MC2_RS_WARPS"); const int v = e ? atoi(e) : 4; return v < 1 ? 1 : (v > 4 ? 4 : v); }();
-    if (ForcedWorkers(false) == 0) g.rsCoop = rsWarps;
+    // At two ranks every rank reduces HALF of the product: most of the switch's reduction rate for the whole kernel,
+    // and epilogue warps busy reducing delay the accumulator drain (measured 0.59 ms against 0.49 ms with worker
+    // CTAs), so two ranks keep the workers; HCCL_MC2_RS_WARPS set explicitly forces the cooperative form.
+    static const bool warpsForced = getenv("HCCL_MC2_RS_WARPS") != nullptr;
+    if (ForcedWorkers(false) == 0 && (comm->nRanks >= 4 || warpsForced)) g.rsCoop = rsWarps;
     else workers = twoSm ? ReduceWorkerCtas((g.M / 256) * g.tilesN, 2, localTiles, g.K, g.nRanks, g.xchgMc != nullptr)
                          : ReduceWorkerCtas(g.tilesM * g.tilesN, 1, localTiles, g.K, g.nRanks, g.xchgMc != nullptr);
     const int grid = SmCount() & ~1;
@@ -516,7 +569,10 @@ HcclResult Mc2MatmulReduceScatter(CommImpl* comm, const void* a, const void* b, 
     if (twoSm) {
         g.bn = 256;
         CHK_RET(MapB(&tb, b, n, k, bMn, 128));
-        return DispatchLayout2Sm<MODE_RS>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream);
+        MC2_TRACE_ARM(g, grid);
+        const HcclResult r = DispatchLayout2Sm<MODE_RS>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream);
+        MC2_TRACE_DUMP("matmul_rs", 1, g, grid, stream);
+        return r;
     }
     return DispatchLayout<256, MODE_RS>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream);
 }

@@ -130,6 +130,10 @@ struct Exec {
     }
     uint64_t esOut() const { return p.castScale ? DataTypeSize(p.outType) : es; }
     uint64_t LoopBytes(uint64_t region, uint64_t multiple) const { return AlignDown(region / multiple, 128); }
+    // The push forms land data in the receivers' stage-in region, which holds two landing copies taken in turn; the
+    // second starts at the same offset for every operator, whatever its size, so that copies of different operators
+    // never overlap.
+    uint64_t LandingCopyBytes() const { return AlignDown(L.inBytes / 2, 128); }
 
     // ---- AllReduce / Reduce --------------------------------------------------
     HcclResult AllReduceLike() const
@@ -137,6 +141,28 @@ struct Exec {
         const uint64_t total = p.count * es;
         const bool isReduce = p.op == HCCL_CMD_REDUCE;
         const bool ll = dalg == DALG_AR_LL;
+        if (dalg == DALG_AR_PUSH_TWOSHOT) {
+            // slices pushed into their owners' landing copies (p slots of one slice each), reduced slices exchanged
+            // through the exchange region: the input is read once and never staged
+            const uint64_t landing = LandingCopyBytes();
+            if (landing < 256ull * (uint64_t)P) return HCCL_E_MEMORY;
+            const uint64_t limit = std::min(AlignDown(landing - 16ull * (uint64_t)P, 128), LoopBytes(L.xchBytes, 1));
+            if (limit == 0) return HCCL_E_MEMORY;
+            for (uint64_t off = 0; off < total; off += limit) {
+                const uint64_t n = std::min(limit, total - off);
+                CollArgs a;
+                memset(&a, 0, sizeof(a));
+                a.in = (const char*)p.send + off;
+                a.out = (char*)p.recv + off;
+                a.bytes = n;
+                a.op = (int)p.redOp;
+                a.chunk = landing;
+                FillStageIn(a);
+                FillXch(a);
+                CHK_RET(Launch(a, n / (uint64_t)P * 2 + 1));
+            }
+            return HCCL_SUCCESS;
+        }
         RegInfo in = Reg(c, p.send, total), out = Reg(c, p.recv, total);
         const bool inDirect = d.inRegistered && d.aligned16 && in.reg && Aligned16(p.send);
         const bool nvlsAlg = dalg == DALG_AR_NVLS;
@@ -200,6 +226,26 @@ struct Exec {
             dspB[q] = (v ? p.sdispls[(size_t)q] : p.count * (uint64_t)q) * es;
             maxCnt = std::max(maxCnt, cntB[q]);
             inSpan = std::max(inSpan, dspB[q] + cntB[q]);
+        }
+        if (dalg == DALG_RS_PUSH) {
+            // block q pushed into rank q's landing copy (p slots of one chunk each): the input is read once, never staged
+            const uint64_t landing = LandingCopyBytes();
+            const uint64_t limit = AlignDown(landing / (uint64_t)P, 128);
+            if (limit == 0) return HCCL_E_MEMORY;
+            const uint64_t block = p.count * es;
+            for (uint64_t off = 0; off < block; off += limit) {
+                CollArgs a;
+                memset(&a, 0, sizeof(a));
+                a.in = (const char*)p.send;
+                a.out = (char*)p.recv + off;
+                a.op = (int)p.redOp;
+                a.bytes = std::min(limit, block - off);
+                a.chunk = landing;
+                for (int q = 0; q < P; ++q) { a.cnt[q] = a.bytes; a.dsp2[q] = dspB[q] + off; }
+                FillStageIn(a);
+                CHK_RET(Launch(a, a.bytes + 1));
+            }
+            return HCCL_SUCCESS;
         }
         RegInfo in = Reg(c, p.send, inSpan);
         bool inDirect = d.inRegistered && d.aligned16 && in.reg && Aligned16(p.send);
@@ -452,13 +498,13 @@ struct Exec {
         if (dalg == DALG_A2A_PUSH) {
             // every pair's block lands in the receiver's stage-in region, two copies by parity
             const uint64_t pair = sendB[0], slot = AlignUp(pair, 16), copyBytes = slot * (uint64_t)P;
-            if (2 * copyBytes > L.inBytes) return HCCL_E_INTERNAL;
+            if (copyBytes > LandingCopyBytes()) return HCCL_E_INTERNAL;
             CollArgs a;
             memset(&a, 0, sizeof(a));
             a.in = (const char*)p.send;
             a.out = (char*)p.recv;
             a.bytes = pair;
-            a.chunk = copyBytes;
+            a.chunk = LandingCopyBytes();
             for (int q = 0; q < P; ++q) { a.dsp2[q] = sdspB[q]; a.dsp[q] = rdspB[q]; }
             FillStageIn(a);
             return Launch(a, pair * (uint64_t)P);
@@ -637,7 +683,8 @@ HcclResult ExecDescribed(CommImpl* c, OpParam& p, OpDesc d, const uint32_t* pres
 {
     const auto t0 = std::chrono::steady_clock::now();
     const uint32_t localFlags = d.Flags();
-    PlanKey key = {(uint32_t)p.op, (uint32_t)p.dtype, (uint32_t)p.redOp, p.root, d.bytes, localFlags, (uint32_t)c->generation};
+    // a plan is the outcome of selection: it dies with the communicator's generation and with a reload of the environment
+    PlanKey key = {(uint32_t)p.op, (uint32_t)p.dtype, (uint32_t)p.redOp, p.root, d.bytes, localFlags, (uint32_t)c->generation ^ (EnvConfigVersion() << 16)};
     Plan plan;
     const AlgEntry* alg = nullptr;
     // a plan made for other combined flags (emulated ranks: the combination is known before every call and depends on

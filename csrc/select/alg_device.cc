@@ -491,6 +491,46 @@ void RegisterAll()
         };
         R.Register(e);
     }
+    // ---------------- ReduceScatter and AllReduce on ordinary buffers without the stage-in pass: every rank writes block q
+    // of its input into rank q's landing copy (stage-in region, two copies taken in turn) and reduces what landed
+    {
+        auto ordinaryInput = [](const OpDesc& o, const TopoInfo& t, std::string* why) {
+            if (o.inRegistered) { *why = "op: the input is registered, the pull form reads it in place"; return false; }
+            if (t.nRanks < 2) { *why = "topo: a single rank"; return false; }
+            if (o.stageInBytes / 2 < 4096ull * t.nRanks) { *why = "op: the landing zone is too small"; return false; }
+            return true;
+        };
+        AlgEntry e = Base("P2pReduceScatterSoleMeshPush", HCCL_CMD_REDUCE_SCATTER, HCCL_ENGINE_P2P, "MeshPush", DALG_RS_PUSH, AlgoType::MESH);
+        e.attrs.dtypeMask = kReduceTypes;
+        e.attrs.needsAligned16 = true;
+        e.attrs.minBytes = 256ull << 10;
+        e.attrs.opCustomCheck = ordinaryInput;
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = (m.p - 1) / m.p * m.link();
+            c.ratio = 1.0 / m.p;
+            c.B = 0.25 * m.copy();          // the landed blocks are read once more, locally
+            c.C = m.lm.launchUs + m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+        AlgEntry f = Base("P2pAllReduceSoleMeshPushTwoShot", HCCL_CMD_ALLREDUCE, HCCL_ENGINE_P2P, "MeshPushTwoShot", DALG_AR_PUSH_TWOSHOT, AlgoType::TWOSHOT);
+        f.attrs.dtypeMask = kReduceTypes;
+        f.attrs.needsAligned16 = true;
+        f.attrs.minBytes = 256ull << 10;
+        f.attrs.opCustomCheck = ordinaryInput;
+        f.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = 2.0 * (m.p - 1) / m.p * m.link();
+            c.ratio = 1.0 / m.p;
+            c.B = 0.25 * m.copy() + m.copy() / m.p;
+            c.C = m.lm.launchUs + 3 * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(f);
+    }
     // ---------------- point to point and barrier
     for (HcclCMDType op : {HCCL_CMD_SEND, HCCL_CMD_RECEIVE, HCCL_CMD_BATCH_SEND_RECV}) {
         const char* name = op == HCCL_CMD_SEND ? "P2pSendSoleMesh" : (op == HCCL_CMD_RECEIVE ? "P2pRecvSoleMesh" : "P2pBatchSendRecvSoleMesh");

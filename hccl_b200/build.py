@@ -3,7 +3,7 @@
 Every ``.cu`` file is compiled by nvcc for sm_100a only
 (``-gencode arch=compute_100a,code=sm_100a -lineinfo``), every ``.cc`` file by
 g++; objects are cached under ``build/obj`` and rebuilt when the source or any
-header is newer.  Usage: ``python hccl_b200/build.py [--force] [--verbose] [--ptxas] [--asan]``.
+header is newer.  Usage: ``python hccl_b200/build.py [--force] [--verbose] [--ptxas] [--asan] [--trace]``.
 
 ``--asan`` builds a second library, ``build/lib/libhccl_b200_asan.so``, whose host code (every ``.cc`` file: API, selector,
 bootstrap, host engine, verifier) is compiled with AddressSanitizer; the CUDA objects are shared with the normal
@@ -134,6 +134,32 @@ def build_asan(verbose: bool = False) -> Path:
     return _build_variant(OBJ_ASAN, LIB_ASAN, ASAN_FLAGS, ["-Xcompiler", "-fsanitize=address"], verbose)
 
 
+OBJ_TRACE = ROOT / "build" / "obj_trace"
+LIB_TRACE = ROOT / "build" / "lib" / "libhccl_b200_trace.so"
+
+
+def build_trace(verbose: bool = False) -> Path:
+    """The timeline variant: the fused matmul kernels compiled with -DHCCL_MC2_TRACE (every role of every CTA writes
+    where its time went; `HCCL_MC2_TRACE_FILE=<prefix>` dumps launches `HCCL_MC2_TRACE_FROM`..+2 as JSON lines), all
+    other objects shared with the normal build.  Load it with `HCCL_B200_LIB=<path>`; a tool for performance work,
+    not for timing (the trace costs a few per cent)."""
+    build(verbose=verbose)
+    OBJ_TRACE.mkdir(parents=True, exist_ok=True)
+    LIB_TRACE.parent.mkdir(parents=True, exist_ok=True)
+    cu, cc = _sources()
+    objs = []
+    for src in cu + cc:
+        if src.name == "mc2_launch.cu":
+            objs.append(_compile(src, verbose, ("-DHCCL_MC2_TRACE",), OBJ_TRACE))
+        else:
+            objs.append(OBJ / (str(src.relative_to(CSRC)).replace("/", "__") + ".o"))
+    cmd = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB_TRACE), *map(str, objs), "-Xcompiler", "-pthread", "-ldl", "-lrt"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"linking {LIB_TRACE.name} failed:\n{r.stdout}\n{r.stderr}")
+    return LIB_TRACE
+
+
 OBJ_COV = ROOT / "build" / "obj_cov"
 LIB_COV = ROOT / "build" / "lib" / "libhccl_b200_cov.so"
 
@@ -169,6 +195,9 @@ def cov_report() -> str:
 if __name__ == "__main__":
     if "--asan" in sys.argv:
         print(build_asan(verbose="--verbose" in sys.argv))
+        sys.exit(0)
+    if "--trace" in sys.argv:
+        print(build_trace(verbose="--verbose" in sys.argv))
         sys.exit(0)
     if "--cov" in sys.argv:
         print(build_cov(verbose="--verbose" in sys.argv))

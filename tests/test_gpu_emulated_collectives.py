@@ -287,13 +287,13 @@ def test_selector_on_device_communicator_and_resource_query():
     small = cs[0].explain(Cmd.ALLREDUCE, 256, DataType.FP32)
     big = cs[0].explain(Cmd.ALLREDUCE, 64 << 20, DataType.FP32)
     assert small.startswith("selected P2pAllReduceSoleMeshLL"), small
-    assert big.startswith("selected P2pAllReduceSoleMeshTwoShot"), big
+    assert big.startswith("selected P2pAllReduceSoleMeshPushTwoShot"), big      # ordinary buffers: slices pushed, no stage-in pass
     assert "NvlsAllReduceSoleMesh" not in big.split("\n")[0]          # no multicast on emulated ranks
     assert "Host" not in big                                           # host algorithms never compete on a device communicator
     r = HcclOpResource()
     # 64 Mi floats = 256 MiB through a 16 MiB slab: several launches, scratch bounded by the slab
     assert lib.HcclCalcOpResource(cs[0].handle, int(Cmd.ALLREDUCE), 64 << 20, int(DataType.FP32), 0, 0, ctypes.byref(r)) == 0
-    assert r.algName.decode() == "P2pAllReduceSoleMeshTwoShot" and r.launches > 1 and r.streams == 1 and 0 < r.scratchBytes <= (16 << 20)
+    assert r.algName.decode() == "P2pAllReduceSoleMeshPushTwoShot" and r.launches > 1 and r.streams == 1 and 0 < r.scratchBytes <= (16 << 20)
     assert lib.HcclCalcOpResource(cs[0].handle, int(Cmd.ALLREDUCE), 64 << 20, int(DataType.FP32), 0, 1, ctypes.byref(r)) == 0
     assert r.scratchBytes == 0            # symmetric buffers need no staging
     for c in cs:

@@ -165,3 +165,78 @@ def test_all_to_all_through_the_slabs(comms, per):
             for q in range(p):
                 assert torch.equal(outs[r][q * per:(q + 1) * per], ins[q][r * per:(r + 1) * per])
     assert comms[0].async_error() == hb.Result.SUCCESS
+
+
+def _push_or_switch(name, push):
+    # with a switch that reduces, the staged switch form may still price below the push form; both are legal here
+    # ... and blocks that still fit the flag-in-data lines take those
+    return name == push or name.startswith("Nvls") or name.endswith("LL")
+
+
+@pytest.mark.parametrize("n", [70000, 300000, 1 << 20])
+def test_reduce_scatter_of_ordinary_buffers_without_staging(comms, n):
+    """Ordinary tensors, blocks pushed into the receivers' landing copies; blocks of 4 MiB need several launches with
+    this slab; out of place and in place (the output is this rank's block of the input)."""
+    p = len(comms)
+    for dtype in (torch.float32, torch.bfloat16):
+        for inplace in (False, True):
+            ins = [_rand(n * p, dtype, 300 + r) for r in range(p)]
+            ref = torch.stack([x.double() for x in ins]).sum(0)
+            outs = [x[r * n:(r + 1) * n] for r, x in enumerate(ins)] if inplace else [torch.empty(n, device="cuda", dtype=dtype) for _ in range(p)]
+            for c, x, y in zip(comms, ins, outs):
+                c.reduce_scatter(x, y)
+            torch.cuda.synchronize()
+            assert _push_or_switch(comms[0].last_algorithm(), "P2pReduceScatterSoleMeshPush"), comms[0].last_algorithm()
+            tol = 3e-2 if dtype == torch.bfloat16 else 1e-5
+            for r, y in enumerate(outs):
+                torch.testing.assert_close(y.double(), ref[r * n:(r + 1) * n], rtol=tol, atol=tol * p)
+    assert comms[0].async_error() == hb.Result.SUCCESS
+
+
+@pytest.mark.parametrize("n", [70001, 1 << 20, 3 * 1024 * 1024 + 8])
+def test_all_reduce_of_ordinary_buffers_without_staging(comms, n):
+    p = len(comms)
+    with _Algo("allreduce=level0:twoshot"):
+        for inplace in (False, True):
+            ins = [_rand(n, torch.float32, 340 + r) for r in range(p)]
+            ref = torch.stack([x.double() for x in ins]).sum(0)
+            outs = ins if inplace else [torch.empty_like(x) for x in ins]
+            for c, x, y in zip(comms, ins, outs):
+                c.all_reduce(x, y)
+            torch.cuda.synchronize()
+            assert comms[0].last_algorithm() == "P2pAllReduceSoleMeshPushTwoShot", comms[0].last_algorithm()
+            for y in outs:
+                torch.testing.assert_close(y.double(), ref, rtol=1e-5, atol=1e-5)
+            for y in outs[1:]:
+                assert torch.equal(y, outs[0])
+    assert comms[0].async_error() == hb.Result.SUCCESS
+
+
+def test_push_forms_of_different_shapes_back_to_back(comms):
+    """The landing copies are taken in turn by a count of push operators, not by block row: operators of different
+    sizes and grids follow one another without a barrier between them and never write a copy that is still read."""
+    p = len(comms)
+    shapes = [70000, 300000, 90000, 1 << 19, 66000, 300000]
+    cases = []
+    for i, n in enumerate(shapes):
+        rs_in = [_rand(n * p, torch.float32, 400 + 10 * i + r) for r in range(p)]
+        rs_out = [torch.empty(n, device="cuda") for _ in range(p)]
+        a2a_in = [_rand(n * p, torch.float32, 500 + 10 * i + r) for r in range(p)]
+        a2a_out = [torch.empty(n * p, device="cuda") for _ in range(p)]
+        cases.append((n, rs_in, rs_out, a2a_in, a2a_out))
+    for n, rs_in, rs_out, a2a_in, a2a_out in cases:          # all launches first, one synchronize at the end
+        for c, x, y in zip(comms, rs_in, rs_out):
+            c.reduce_scatter(x, y)
+        if n * 4 * p * 2 + 64 * p <= 7 << 20:
+            for c, x, y in zip(comms, a2a_in, a2a_out):
+                c.all_to_all(x, y)
+    torch.cuda.synchronize()
+    assert comms[0].async_error() == hb.Result.SUCCESS
+    for n, rs_in, rs_out, a2a_in, a2a_out in cases:
+        ref = torch.stack([x.double() for x in rs_in]).sum(0)
+        for r, y in enumerate(rs_out):
+            torch.testing.assert_close(y.double(), ref[r * n:(r + 1) * n], rtol=1e-5, atol=1e-5)
+        if n * 4 * p * 2 + 64 * p <= 7 << 20:
+            for r in range(p):
+                for q in range(p):
+                    assert torch.equal(a2a_out[r][q * n:(q + 1) * n], a2a_in[q][r * n:(r + 1) * n])
