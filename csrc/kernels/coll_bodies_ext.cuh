@@ -506,6 +506,73 @@ struct BcastScatterNvlsBody {
 };
 
 // ---------------------------------------------------------------------------------------------------------------
+// Broadcast of large messages as a pipelined scatter + AllGather over plain peer reads.  The message is cut into
+// p - 1 slices, one per non-root rank.  In step i a rank pulls piece i of ITS slice from the root and, in the same
+// pass, piece i - 1 of every other slice from the rank that pulled it one step earlier; one barrier closes a step.
+// Every byte leaves the root once and enters every other rank once, and both directions of every port are busy in
+// every step but the first and the last (the two-shot form runs the two phases one after the other, and a single
+// multicast sender saturates far below the port rate).  `chunk` = bytes of one piece, cnt2[0] = number of pieces
+// (the same on every rank); src[root] = the root's data where the peers can read it; the owners' pieces are read
+// from dst[q] (MODE_PUSH: the output buffers themselves are peer-visible) or from xch[q].  Sync points: pieces + 2.
+struct BcastPipeBody {
+    using Args = CollArgs;
+    static constexpr int kThreads = 512;
+    // piece i of the sub-range [off, off + len)
+    __device__ static void Piece(size_t len, size_t piece, int i, size_t* b0, size_t* b1)
+    {
+        const size_t lo = (size_t)i * piece, hi = lo + piece;
+        *b0 = lo < len ? lo : len;
+        *b1 = hi < len ? hi : len;
+    }
+    __device__ static void Run(const DevComm& c, const Args& a, int b, int nb)
+    {
+        OpHead(c, b);
+        const int p = c.nRanks, me = c.rank, root = a.root;
+        const uint64_t e = LoadEpoch(c, b);
+        const int slices = p - 1, pieces = (int)a.cnt2[0];
+        const bool direct = (a.mode & MODE_PUSH) != 0;
+        const int mine = (me - root - 1 + p) % p;                 // this rank's slice (meaningless on the root)
+        if (me == root && (a.mode & MODE_STAGE_IN)) {
+            for (int s = 0; s < slices; ++s) {
+                size_t off, len;
+                SliceSub(a.bytes, slices, s, nb, b, &off, &len);
+                BlockCopyBytes(const_cast<char*>(a.src[root]) + off, a.in + off, len);
+            }
+        }
+        RankBarrier(c, b, 0, e + 1, K_BCAST);
+        for (int i = 0; i <= pieces; ++i) {
+            if (me != root) {
+                CopySeg segs[kMaxDevRanks + 1];
+                int n = 0;
+                if (i < pieces) {
+                    size_t off, len, b0, b1;
+                    SliceSub(a.bytes, slices, mine, nb, b, &off, &len);
+                    Piece(len, (size_t)a.chunk, i, &b0, &b1);
+                    char* hold = direct ? a.out : a.xch[me];
+                    if (b1 > b0) segs[n++] = CopySeg{hold + off + b0, a.src[root] + off + b0, b1 - b0};
+                }
+                if (i >= 1) {
+                    for (int k = 0; k < p; ++k) {
+                        const int q = (me + k) % p;
+                        if (q == root || (q == me && direct)) continue;
+                        const int sq = (q - root - 1 + p) % p;
+                        size_t off, len, b0, b1;
+                        SliceSub(a.bytes, slices, sq, nb, b, &off, &len);
+                        Piece(len, (size_t)a.chunk, i - 1, &b0, &b1);
+                        const char* from = direct ? a.dst[q] : a.xch[q];       // q == me: the piece this rank pulled one step ago
+                        if (b1 > b0) segs[n++] = CopySeg{a.out + off + b0, from + off + b0, b1 - b0};
+                    }
+                }
+                BlockCopyMulti(segs, n);
+            }
+            RankBarrier(c, b, 0, e + 2 + (uint64_t)i, K_BCAST);
+        }
+        StoreEpoch(c, b, e + 2 + (uint64_t)pieces);
+        OpTail(c, b);
+    }
+};
+
+// ---------------------------------------------------------------------------------------------------------------
 // AlltoAll through the receivers' slabs.  The pull form pays a table exchange and two barriers around the
 // transfer; here a rank WRITES its block for q into q's stage-in region (posted stores, no round trip), one
 // barrier publishes everything, and every rank copies its received blocks out locally.  The landing zone holds two

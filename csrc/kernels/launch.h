@@ -45,6 +45,8 @@ enum DevAlg : int {
     DALG_AG_NVLS, DALG_BCAST_SCATTER_NVLS, DALG_A2A_PUSH,
     // ordinary buffers without the stage-in pass: blocks pushed into the receivers' slabs
     DALG_RS_PUSH, DALG_AR_PUSH_TWOSHOT,
+    // Broadcast of large messages: scatter from the root and AllGather among the others, pipelined piece by piece
+    DALG_BCAST_PIPE,
     DALG_COUNT
 };
 

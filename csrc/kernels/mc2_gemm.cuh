@@ -72,6 +72,7 @@ struct GemmArgs {
     __nv_bfloat16* xchg[kMaxDevRanks];
     // device-resident control block of the communicator's MC2 state (local memory):
     //   [0] launch epoch, [1] exit ticket, [2] abort, [16 ..) per-row-block ready counters (AG)
+    int pipeDrain;                  // fused modes of the two-SM kernel: software-pipelined accumulator drain (DrainTilePipelined)
     uint64_t* trace;                // timeline words per CTA (kTraceWords each), filled only by builds with HCCL_MC2_TRACE
     uint32_t* ctl;
     // tile-ready flags for RS / AR: tileFlag[q] = rank q's flag array mapped here, index [srcRank][tile]
@@ -443,14 +444,14 @@ __device__ __forceinline__ void GatherPushWorker(const DevComm& c, const GemmArg
 // AllGather, cooperative push form.  The epilogue warps of a GEMM CTA are idle for most of a tile's main loop (a
 // 256 x 256 x 8192 tile takes about 45 us, draining it a few), and a posted write needs no shared memory and almost no
 // issue slots.  So instead of giving 20-28 SMs to copy workers, every CTA computes and its four epilogue warps take
-// 32 KiB pieces of the local shard from a shared counter whenever no accumulator is waiting: destinations in the
+// 64 KiB pieces of the local shard from a shared counter whenever no accumulator is waiting: destinations in the
 // order rank-1, rank-2, ... (the order in which the consumers need this rank's rows), pieces in address order, the
 // copy into this rank's own gathered buffer last.  After a piece the warp fences once and adds the bytes it wrote to
 // the destination's arrival counter of every 128-row block the piece touches.  At the start of the kernel all
 // epilogue warps are idle, which front-loads the transfer: the first remote rows reach their consumer long before the
 // tiles of its own shard are done.  One warp of CTA 0 runs the start barrier (every rank is inside the kernel: nobody
 // still reads its gathered buffer from earlier work, and its arrival counters are clear) and then opens the counter.
-constexpr uint32_t kPushPieceBytes = 32 * 1024;
+constexpr uint32_t kPushPieceBytes = 64 * 1024;
 
 __device__ __forceinline__ bool MbarTestWait(uint64_t* bar, uint32_t parity)
 {
@@ -507,19 +508,36 @@ __device__ __forceinline__ int CoopPushStep(const GemmArgs& g, uint32_t launchEp
     const size_t nv = (s1 - s0) >> 4;                // the shard is a multiple of 16 bytes (K is a multiple of 8)
     const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(g.aPeer[g.rank]) + s0);
     uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(g.gatheredPeer[dstRank]) + (size_t)g.rank * shardBytes + s0);
+    // Two register buffers of 16 vectors per lane: the loads of round r + 1 are in flight while round r is stored, so
+    // a warp always has 8 KiB of local reads outstanding (under the GEMM's memory traffic a load takes microseconds)
+    // and never waits for a store (posted).
     constexpr int U = 16;
-    for (size_t i = lane; i < nv; i += U * 32) {
-        uint4 v[U];
+    const size_t rounds = (nv + U * 32 - 1) / (U * 32);
+    uint4 va[U], vb[U];
+    auto load = [&](uint4 (&v)[U], size_t r) {
+        const size_t i = r * (U * 32) + lane;
 #pragma unroll
         for (int k = 0; k < U; ++k)
             if (i + k * 32 < nv) v[k] = __ldg(src + i + k * 32);
+    };
+    auto store = [&](const uint4 (&v)[U], size_t r) {
+        const size_t i = r * (U * 32) + lane;
 #pragma unroll
         for (int k = 0; k < U; ++k)
             if (i + k * 32 < nv) dst[i + k * 32] = v[k];
+    };
+    if (rounds > 0) load(va, 0);
+    for (size_t r = 0; r < rounds; r += 2) {
+        if (r + 1 < rounds) load(vb, r + 1);
+        store(va, r);
+        if (r + 2 < rounds) load(va, r + 2);
+        if (r + 1 < rounds) store(vb, r + 1);
     }
     __syncwarp();
     if (lane == 0) {
-        __threadfence_system();
+        // One release per piece: the warp barrier above orders every lane's stores before this thread, and a release
+        // at system scope is cumulative over them; a separate system fence in front of it would wait for the same
+        // acknowledgements a second time (with megabytes of posted writes in flight that is about ten microseconds).
         for (size_t b = s0 / blockBytes; b * blockBytes < s1; ++b) {
             const size_t lo = b * blockBytes > s0 ? b * blockBytes : s0;
             const size_t hi = (b + 1) * blockBytes < s1 ? (b + 1) * blockBytes : s1;

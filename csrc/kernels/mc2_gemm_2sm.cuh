@@ -327,18 +327,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 uint8_t* stg = smem + L::kStagingOff + quarter * kStgWarpBytes;
                 const int validCols = g.N - nt * BN;
                 if (MODE == MODE_RS) {
-                    DrainTile(taddr, BN, stg, lane, validCols, 1, [&](int r, int) -> __nv_bfloat16* {
+                    auto rowPtr = [&](int r, int) -> __nv_bfloat16* {
                         const int row = row0 + r;
                         const int dst = row / g.mPerRank;
                         if (row >= g.M || dst >= g.nRanks) return nullptr;
                         if (g.xchgMc != nullptr) return g.xchg[g.rank] + parityOff + (size_t)row * g.N + (size_t)nt * BN;
                         return g.xchg[dst] + parityOff + (size_t)g.rank * g.mPerRank * g.N + (size_t)(row - dst * g.mPerRank) * g.N + (size_t)nt * BN;
-                    });
+                    };
+                    // the fused shapes have short main loops (an inner dimension of a few thousand) and epilogue warps
+                    // with a second job: the pipelined drain leaves them the time for it
+                    if (g.pipeDrain) DrainTilePipelined(taddr, BN, stg, lane, validCols, 1, rowPtr);
+                    else DrainTile(taddr, BN, stg, lane, validCols, 1, rowPtr);
                 } else {
                     __nv_bfloat16* base = g.out + (size_t)nt * BN;
-                    DrainTile(taddr, BN, stg, lane, validCols, 1, [&](int r, int) -> __nv_bfloat16* {
-                        return (row0 + r < g.M) ? base + (size_t)(row0 + r) * g.ldc : nullptr;
-                    });
+                    auto rowPtr = [&](int r, int) -> __nv_bfloat16* { return (row0 + r < g.M) ? base + (size_t)(row0 + r) * g.ldc : nullptr; };
+                    if (MODE == MODE_AG && g.pipeDrain) DrainTilePipelined(taddr, BN, stg, lane, validCols, 1, rowPtr);
+                    else DrainTile(taddr, BN, stg, lane, validCols, 1, rowPtr);
                 }
                 TcFenceBefore();
                 __syncwarp();

@@ -402,9 +402,11 @@ struct Exec {
         RegInfo in = Reg(c, p.send, total);
         const bool scatterNvls = dalg == DALG_BCAST_SCATTER_NVLS;      // reads the root like the pull forms, writes like the switch form
         const bool nvlsAlg = dalg == DALG_BCAST_NVLS;
+        const bool pipe = dalg == DALG_BCAST_PIPE;
         const bool inDirect = d.inRegistered && in.reg && !nvlsAlg;
         uint64_t limit = ~0ull;
         if (!inDirect && !nvlsAlg) limit = std::min(limit, LoopBytes(L.inBytes, 1));
+        if (pipe && !inDirect) limit = std::min(limit, LoopBytes(L.xchBytes, 1));      // the owners' pieces wait in the exchange region
         const bool nvlsDirect = (nvlsAlg || scatterNvls) && d.inRegistered && d.inMulticast && d.aligned16 && in.reg && in.mc != nullptr && Aligned16(p.send);
         if (dalg == DALG_BCAST_TWOSHOT || ((nvlsAlg || scatterNvls) && !nvlsDirect)) limit = std::min(limit, LoopBytes(L.xchBytes, 1));
         if (limit == 0) return HCCL_E_MEMORY;
@@ -431,6 +433,17 @@ struct Exec {
                 }
             }
             if (dalg == DALG_BCAST_ONESHOT) a.mode |= MODE_PUSH;
+            if (pipe) {
+                if (inDirect) { a.mode |= MODE_PUSH; for (int q = 0; q < P; ++q) a.dst[q] = const_cast<char*>(in.peer[q]) + off; }
+                // pieces of about 48 KiB per block row and slice, at most 12 steps; the largest sub-range (slice 0, row 0)
+                // sizes the piece, so pieces x piece bytes covers every sub-range
+                const uint64_t nbRows = (uint64_t)BlocksFor(c, n, dalg);
+                const uint64_t slice = (((n + 15) / 16 + (uint64_t)(P - 1) - 1) / (uint64_t)(P - 1)) * 16;
+                const uint64_t sub = (((slice + 15) / 16 + nbRows - 1) / nbRows) * 16;
+                const uint64_t pieces = std::max<uint64_t>(1, std::min<uint64_t>(12, (sub + (48u << 10) - 1) / (48u << 10)));
+                a.cnt2[0] = pieces;
+                a.chunk = (((sub + 15) / 16 + pieces - 1) / pieces) * 16;
+            }
             CHK_RET(Launch(a, n));
         }
         return HCCL_SUCCESS;

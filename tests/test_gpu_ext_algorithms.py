@@ -240,3 +240,29 @@ def test_push_forms_of_different_shapes_back_to_back(comms):
             for r in range(p):
                 for q in range(p):
                     assert torch.equal(a2a_out[r][q * n:(q + 1) * n], a2a_in[q][r * n:(r + 1) * n])
+
+
+@pytest.mark.parametrize("n", [(4 << 20) // 4 + 4, 5 * 1024 * 1024 + 12])
+def test_pipelined_broadcast(comms, n):
+    """Scatter from the root and AllGather among the others, piece by piece: ordinary buffers (pieces wait in the
+    exchange region, several launches with this slab) and symmetric buffers (peers read the buffers themselves)."""
+    p = len(comms)
+    if p < 3:
+        pytest.skip("one receiver pulls everything from the root")
+    with _Algo("broadcast=level0:pipeline"):
+        for sym in (False, True):
+            for root in (0, p - 1):
+                src = _rand(n, torch.float32, 600 + root)
+                bufs = [c.empty((n,), torch.float32) if sym else torch.empty(n, device="cuda") for c in comms]
+                for r, x in enumerate(bufs):
+                    x.copy_(src) if r == root else x.fill_(-1.0)
+                for c, x in zip(comms, bufs):
+                    c.broadcast(x, root)
+                torch.cuda.synchronize()
+                assert comms[0].last_algorithm() == "P2pBroadcastSoleMeshPipe", comms[0].last_algorithm()
+                for x in bufs:
+                    assert torch.equal(x, src)
+                if sym:
+                    for c, x in zip(comms, bufs):
+                        c.free(x)
+    assert comms[0].async_error() == hb.Result.SUCCESS
