@@ -72,7 +72,6 @@ struct GemmArgs {
     __nv_bfloat16* xchg[kMaxDevRanks];
     // device-resident control block of the communicator's MC2 state (local memory):
     //   [0] launch epoch, [1] exit ticket, [2] abort, [16 ..) per-row-block ready counters (AG)
-    int pipeDrain;                  // fused modes of the two-SM kernel: software-pipelined accumulator drain (DrainTilePipelined)
     uint64_t* trace;                // timeline words per CTA (kTraceWords each), filled only by builds with HCCL_MC2_TRACE
     uint32_t* ctl;
     // tile-ready flags for RS / AR: tileFlag[q] = rank q's flag array mapped here, index [srcRank][tile]
@@ -199,9 +198,8 @@ __device__ __forceinline__ void Store32Cols(__nv_bfloat16* dst, const uint32_t (
 
 // Drains this warp's 32 accumulator rows x `bn` columns from TMEM and stores them as bf16 through the staging area.
 // rowPtr(r, d) returns the address of column 0 of the tile in destination d for warp row r (nullptr = skip the row);
-// validCols = columns of the tile that exist in the matrix.  One tensor-memory load of 32 columns at a time: the
-// kernels that use it hide the epilogue behind the next tile's main loop, and there the short form measured better
-// inside a power-limited training step than the software-pipelined one below (fewer live registers, less switching).
+// validCols = columns of the tile that exist in the matrix.  The general form (any destination per row, several
+// destinations): Matmul->AllReduce uses it; outputs with a fixed row stride take DrainTileRows below.
 template <class RowPtrFn>
 __device__ __forceinline__ void DrainTile(uint32_t taddrLane, int bn, uint8_t* stg, int lane, int validCols, int nDst, RowPtrFn rowPtr)
 {
@@ -239,18 +237,22 @@ __device__ __forceinline__ void DrainTile(uint32_t taddrLane, int bn, uint8_t* s
     }
 }
 
-// The same drain as a software pipeline over chunks of 64 columns: the two tensor-memory loads of chunk i + 1 are
-// issued BEFORE chunk i is copied from the staging area to its destination, so their latency is covered by that copy
-// (global / peer stores are posted); one wait per chunk instead of one per 32 columns.  For kernels whose epilogue is
-// NOT hidden behind a main loop (the wide-tile kernel, whose accumulator fills all of tensor memory).
-template <class RowPtrFn>
-__device__ __forceinline__ void DrainTilePipelined(uint32_t taddrLane, int bn, uint8_t* stg, int lane, int validCols, int nDst, RowPtrFn rowPtr)
+// Drain for destinations whose rows lie `stride` elements apart (every plain, gathered and scattered output here): the
+// warp's 32 rows x `bn` columns go to base + r * stride.  Same staging as DrainTile, but the copy out of the staging
+// area has no per-piece index arithmetic (DrainTile divides twice per 16-byte piece and calls a row-pointer function,
+// about 150 instructions per piece: measured 12 us for a 128 x 256 tile, as long as half a main loop at an inner
+// dimension of 3584): lane l always copies 16-byte column l % 8 of rows l / 8, l / 8 + 4, ..., eight loads from
+// shared memory in flight, then eight stores.  The tensor-memory loads of the next 64 columns are issued before the
+// copy-out and land while it runs.  validRows / validCols clip the tile at the matrix edge (columns in units of 8).
+__device__ __forceinline__ void DrainTileRows(uint32_t taddrLane, int bn, uint8_t* stg, int lane, int validCols, int validRows, __nv_bfloat16* base,
+                                              size_t stride)
 {
+    if (bn <= 0) return;
     uint32_t va[32], vb[32];
+    const int pc = lane & 7, r0 = lane >> 3;
     auto issue = [&](int c0) {
-        const int chunk = (bn - c0) < 64 ? (bn - c0) : 64;
         TmemLd32x32(taddrLane + (uint32_t)c0, va);
-        if (chunk > 32) TmemLd32x32(taddrLane + (uint32_t)(c0 + 32), vb);
+        if (bn - c0 > 32) TmemLd32x32(taddrLane + (uint32_t)(c0 + 32), vb);
     };
     auto stage = [&](const uint32_t (&v)[32], int h) {
         uint4* d = reinterpret_cast<uint4*>(stg + lane * kStgRowBytes + h * 2);
@@ -265,7 +267,6 @@ __device__ __forceinline__ void DrainTilePipelined(uint32_t taddrLane, int bn, u
             d[i] = make_uint4(w[0], w[1], w[2], w[3]);
         }
     };
-    if (bn <= 0) return;
     issue(0);
     for (int c0 = 0; c0 < bn; c0 += 64) {
         const int chunk = (bn - c0) < 64 ? (bn - c0) : 64;
@@ -273,18 +274,16 @@ __device__ __forceinline__ void DrainTilePipelined(uint32_t taddrLane, int bn, u
         stage(va, 0);
         if (chunk > 32) stage(vb, 32);
         __syncwarp();
-        if (c0 + 64 < bn) issue(c0 + 64);          // in flight while this chunk leaves the staging area
-        const int piecesPerRow = chunk / 8;          // 16-byte pieces
-        for (int i = lane; i < 32 * piecesPerRow; i += 32) {
-            const int r = i / piecesPerRow, pc = i % piecesPerRow;
-            const int col = c0 + pc * 8;
-            if (col >= validCols) continue;
-            const uint4 val = *reinterpret_cast<const uint4*>(stg + r * kStgRowBytes + pc * 16);
-            for (int dd = 0; dd < nDst; ++dd) {
-                __nv_bfloat16* p = rowPtr(r, dd);
-                if (p != nullptr) *reinterpret_cast<uint4*>(p + col) = val;
-            }
-        }
+        if (c0 + 64 < bn) issue(c0 + 64);
+        const int col = c0 + pc * 8;
+        const bool colOk = pc * 8 < chunk && col < validCols;
+        uint4 v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = *reinterpret_cast<const uint4*>(stg + (r0 + 4 * k) * kStgRowBytes + pc * 16);
+        __nv_bfloat16* p = base + (size_t)r0 * stride + col;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (colOk && r0 + 4 * k < validRows) *reinterpret_cast<uint4*>(p + (size_t)(4 * k) * stride) = v[k];
         __syncwarp();
     }
 }
@@ -1012,21 +1011,19 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const uint32_t taddr = tmemBase + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
                 uint8_t* stg = smem + L::kStagingOff + quarter * kStgWarpBytes;
                 const int validCols = g.N - nt * BN;
+                // a warp's 32 rows lie in one rank's row block (blocks are multiples of 128 rows) and a fixed stride apart
                 if (MODE == MODE_PLAIN || MODE == MODE_AG) {
-                    __nv_bfloat16* base = g.out + (size_t)nt * BN;
-                    DrainTile(taddr, BN, stg, lane, validCols, 1, [&](int r, int) -> __nv_bfloat16* {
-                        return (row0 + r < g.M) ? base + (size_t)(row0 + r) * g.ldc : nullptr;
-                    });
+                    DrainTileRows(taddr, BN, stg, lane, validCols, g.M - row0, g.out + (size_t)row0 * g.ldc + (size_t)nt * BN, (size_t)g.ldc);
                 } else if (MODE == MODE_RS) {
-                    // partial of row block `dst` goes into the owner's slot [me]
-                    DrainTile(taddr, BN, stg, lane, validCols, 1, [&](int r, int) -> __nv_bfloat16* {
-                        const int row = row0 + r;
-                        const int dst = row / g.mPerRank;
-                        if (row >= g.M || dst >= g.nRanks) return nullptr;
-                        // switch-reduce form: the partial stays in this rank's own buffer, laid out like the product
-                        if (g.xchgMc != nullptr) return g.xchg[g.rank] + parityOff + (size_t)row * g.N + (size_t)nt * BN;
-                        return g.xchg[dst] + parityOff + (size_t)g.rank * g.mPerRank * g.N + (size_t)(row - dst * g.mPerRank) * g.N + (size_t)nt * BN;
-                    });
+                    // partial of row block `dst` goes into the owner's slot [me]; switch-reduce form: the partial stays in
+                    // this rank's own buffer, laid out like the product
+                    const int dst = row0 / g.mPerRank;
+                    __nv_bfloat16* base = nullptr;
+                    if (row0 < g.M && dst < g.nRanks) {
+                        if (g.xchgMc != nullptr) base = g.xchg[g.rank] + parityOff + (size_t)row0 * g.N + (size_t)nt * BN;
+                        else base = g.xchg[dst] + parityOff + (size_t)g.rank * g.mPerRank * g.N + (size_t)(row0 - dst * g.mPerRank) * g.N + (size_t)nt * BN;
+                    }
+                    DrainTileRows(taddr, BN, stg, lane, validCols, base != nullptr ? g.M - row0 : 0, base, (size_t)g.N);
                 } else {
                     // AllReduce: this rank's slot on every rank
                     DrainTile(taddr, BN, stg, lane, validCols, g.nRanks, [&](int r, int dd) -> __nv_bfloat16* {

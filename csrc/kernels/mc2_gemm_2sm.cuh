@@ -326,23 +326,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 const uint32_t taddr = tmemBase + (uint32_t)(acc * kBN2) + ((uint32_t)(quarter * 32) << 16);
                 uint8_t* stg = smem + L::kStagingOff + quarter * kStgWarpBytes;
                 const int validCols = g.N - nt * BN;
+                // a warp's 32 rows lie in one rank's row block (blocks are multiples of 128 rows) and `stride` apart
+                const int validRows = g.M - row0;
                 if (MODE == MODE_RS) {
-                    auto rowPtr = [&](int r, int) -> __nv_bfloat16* {
-                        const int row = row0 + r;
-                        const int dst = row / g.mPerRank;
-                        if (row >= g.M || dst >= g.nRanks) return nullptr;
-                        if (g.xchgMc != nullptr) return g.xchg[g.rank] + parityOff + (size_t)row * g.N + (size_t)nt * BN;
-                        return g.xchg[dst] + parityOff + (size_t)g.rank * g.mPerRank * g.N + (size_t)(row - dst * g.mPerRank) * g.N + (size_t)nt * BN;
-                    };
-                    // the fused shapes have short main loops (an inner dimension of a few thousand) and epilogue warps
-                    // with a second job: the pipelined drain leaves them the time for it
-                    if (g.pipeDrain) DrainTilePipelined(taddr, BN, stg, lane, validCols, 1, rowPtr);
-                    else DrainTile(taddr, BN, stg, lane, validCols, 1, rowPtr);
+                    const int dst = row0 / g.mPerRank;
+                    __nv_bfloat16* base = nullptr;
+                    if (row0 < g.M && dst < g.nRanks) {
+                        if (g.xchgMc != nullptr) base = g.xchg[g.rank] + parityOff + (size_t)row0 * g.N + (size_t)nt * BN;
+                        else base = g.xchg[dst] + parityOff + (size_t)g.rank * g.mPerRank * g.N + (size_t)(row0 - dst * g.mPerRank) * g.N + (size_t)nt * BN;
+                    }
+                    DrainTileRows(taddr, BN, stg, lane, validCols, base != nullptr ? validRows : 0, base, (size_t)g.N);
                 } else {
-                    __nv_bfloat16* base = g.out + (size_t)nt * BN;
-                    auto rowPtr = [&](int r, int) -> __nv_bfloat16* { return (row0 + r < g.M) ? base + (size_t)(row0 + r) * g.ldc : nullptr; };
-                    if (MODE == MODE_AG && g.pipeDrain) DrainTilePipelined(taddr, BN, stg, lane, validCols, 1, rowPtr);
-                    else DrainTile(taddr, BN, stg, lane, validCols, 1, rowPtr);
+                    __nv_bfloat16* base = g.out + (size_t)row0 * g.ldc + (size_t)nt * BN;
+                    DrainTileRows(taddr, BN, stg, lane, validCols, validRows, base, (size_t)g.ldc);
                 }
                 TcFenceBefore();
                 __syncwarp();

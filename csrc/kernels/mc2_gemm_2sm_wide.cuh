@@ -188,10 +188,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 if (nt >= g.tilesN) break;
                 const uint32_t taddr = tmemBase + (uint32_t)(h * kBN2) + ((uint32_t)(quarter * 32) << 16);
                 const int validCols = g.N - nt * BN;
-                __nv_bfloat16* base = g.out + (size_t)nt * BN;
-                DrainTilePipelined(taddr, BN, stg, lane, validCols, 1, [&](int r, int) -> __nv_bfloat16* {
-                    return (row0 + r < g.M) ? base + (size_t)(row0 + r) * g.ldc : nullptr;
-                });
+                DrainTileRows(taddr, BN, stg, lane, validCols, g.M - row0, g.out + (size_t)row0 * g.ldc + (size_t)nt * BN, (size_t)g.ldc);
             }
             TcFenceBefore();
             __syncwarp();

@@ -178,21 +178,6 @@ bool Use2Sm()
     return v == 1;
 }
 
-// Accumulator drain of the fused two-SM kernels: HCCL_MC2_PIPE_DRAIN=0 / 1 picks the plain or the software-pipelined form
-// for both, HCCL_MC2_PIPE_DRAIN_AG / _RS for one of them.
-int PipeDrain(bool gather)
-{
-    static int v[2] = {-1, -1};
-    int& f = v[gather ? 1 : 0];
-    if (f < 0) {
-        f = gather ? 1 : 1;
-        const char* e = getenv(gather ? "HCCL_MC2_PIPE_DRAIN_AG" : "HCCL_MC2_PIPE_DRAIN_RS");
-        if (e == nullptr) e = getenv("HCCL_MC2_PIPE_DRAIN");
-        if (e != nullptr) f = e[0] == '0' ? 0 : 1;
-    }
-    return f;
-}
-
 // CTAs of a fused launch that move data instead of computing, taken from the GEMM.  HCCL_MC2_AG_WORKERS /
 // HCCL_MC2_RS_WORKERS fix the counts (even, 2 .. 64); otherwise:
 int ForcedWorkers(bool gather)
@@ -529,7 +514,6 @@ HcclResult Mc2AllGatherMatmul(CommImpl* comm, const void* aShard, const void* b,
         g.bn = bestBn;
         g.tilesN = (int)((n + bestBn - 1) / bestBn);
         CHK_RET(MapB(&tb, b, n, k, bMn, bestBn / 2));
-        g.pipeDrain = PipeDrain(true);
         MC2_TRACE_ARM(g, grid);
         const HcclResult r = DispatchLayout2Sm<MODE_AG>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream, &taOwn);
         MC2_TRACE_DUMP("ag_matmul", 0, g, grid, stream);
@@ -588,7 +572,6 @@ HcclResult Mc2MatmulReduceScatter(CommImpl* comm, const void* a, const void* b, 
     if (twoSm) {
         g.bn = 256;
         CHK_RET(MapB(&tb, b, n, k, bMn, 128));
-        g.pipeDrain = PipeDrain(false);
         MC2_TRACE_ARM(g, grid);
         const HcclResult r = DispatchLayout2Sm<MODE_RS>(false, bMn, ta, tb, g, comm->dev(), grid, true, stream);
         MC2_TRACE_DUMP("matmul_rs", 1, g, grid, stream);
