@@ -132,6 +132,8 @@ struct SmemLayout {
     static constexpr int kTotal = kStagingOff + kEpilogueStagingBytes + 1024;   // + slack for the 1024-byte alignment
 };
 
+constexpr int kAgBandRows = 8;      // row tiles per band of the AllGather->Matmul tile order
+
 // Flat tile index -> (m tile, n tile) in the order that suits the mode.
 template <int MODE>
 __device__ __forceinline__ void TileCoord(const GemmArgs& g, int t, int* mt, int* nt)
@@ -139,11 +141,19 @@ __device__ __forceinline__ void TileCoord(const GemmArgs& g, int t, int* mt, int
     if (MODE == MODE_AG) {
         // rows grouped by source rank, own rank first, then rank+1, ... : the own shard needs no transfer and the
         // gather workers fetch the others in exactly this order
-        const int tilesPerRank = (g.mPerRank / kBM) * g.tilesN;
+        // Inside a shard: bands of up to kAgBandRows row tiles walked column by column, so that the tiles in flight
+        // share a few row tiles of A AND a few column tiles of B (walking a row tile's columns first streams all of B
+        // once per row tile: at a weight shard of 14336 x 8192 that alone is HBM-bound).
+        const int rowTiles = g.mPerRank / kBM;
+        const int tilesPerRank = rowTiles * g.tilesN;
         const int step = t / tilesPerRank, rem = t % tilesPerRank;
         const int src = (g.rank + step) % g.nRanks;
-        *mt = src * (g.mPerRank / kBM) + rem / g.tilesN;
-        *nt = rem % g.tilesN;
+        const int band = rowTiles < kAgBandRows ? rowTiles : kAgBandRows;
+        const int perBand = band * g.tilesN;
+        const int first = (rem / perBand) * band, r2 = rem % perBand;
+        const int rows = (rowTiles - first) < band ? (rowTiles - first) : band;
+        *mt = src * rowTiles + first + r2 % rows;
+        *nt = r2 / rows;
     } else if (MODE == MODE_RS) {
         // column tile major: after column tile n every rank has produced its partial of (every row block, n), so the
         // owner can reduce column tile n while the GEMM works on n + 1.  Inside a column tile the row blocks start at

@@ -99,12 +99,17 @@ template <int MODE>
 __device__ __forceinline__ void TileCoord2(const GemmArgs& g, int t, int tilesM2, int* mt2, int* nt)
 {
     if (MODE == MODE_AG) {
+        // shards in the order rank, rank + 1, ...; inside a shard bands of row tiles walked column by column (see TileCoord)
         const int rowTiles = g.mPerRank / 256;
         const int tilesPerRank = rowTiles * g.tilesN;
         const int step = t / tilesPerRank, rem = t % tilesPerRank;
         const int src = (g.rank + step) % g.nRanks;
-        *mt2 = src * rowTiles + rem / g.tilesN;
-        *nt = rem % g.tilesN;
+        const int band = rowTiles < kAgBandRows ? rowTiles : kAgBandRows;
+        const int perBand = band * g.tilesN;
+        const int first = (rem / perBand) * band, r2 = rem % perBand;
+        const int rows = (rowTiles - first) < band ? (rowTiles - first) : band;
+        *mt2 = src * rowTiles + first + r2 % rows;
+        *nt = r2 / rows;
     } else if (MODE == MODE_RS) {
         const int rowTiles = g.mPerRank / 256;
         const int n = t / tilesM2, rem = t % tilesM2;

@@ -560,11 +560,10 @@ HcclResult Mc2MatmulReduceScatter(CommImpl* comm, const void* a, const void* b, 
     // block while they wait for accumulators.  HCCL_MC2_RS_WORKERS=<n> keeps n dedicated reduction CTAs instead.
     int workers = 0;
     static const int rsWarps = [] { const char* e = getenv("HCCL_MC2_RS_WARPS"); const int v = e ? atoi(e) : 4; return v < 1 ? 1 : (v > 4 ? 4 : v); }();
-    // At two ranks every rank reduces HALF of the product: most of the switch's reduction rate for the whole kernel,
-    // and epilogue warps busy reducing delay the accumulator drain (measured 0.59 ms against 0.49 ms with worker
-    // CTAs), so two ranks keep the workers; HCCL_MC2_RS_WARPS set explicitly forces the cooperative form.
-    static const bool warpsForced = getenv("HCCL_MC2_RS_WARPS") != nullptr;
-    if (ForcedWorkers(false) == 0 && (comm->nRanks >= 4 || warpsForced)) g.rsCoop = rsWarps;
+    // Every rank count: with the division-free accumulator drain the epilogue warps have the time, and at inner
+    // dimensions of ten thousand and more (two-way tensor parallelism) worker CTAs only take SMs from the GEMM
+    // (measured at two ranks, 4096 x 8192 x 14336: 0.64 ms against 0.71 ms with workers).
+    if (ForcedWorkers(false) == 0) g.rsCoop = rsWarps;
     else workers = twoSm ? ReduceWorkerCtas((g.M / 256) * g.tilesN, 2, localTiles, g.K, g.nRanks, g.xchgMc != nullptr)
                          : ReduceWorkerCtas(g.tilesM * g.tilesN, 1, localTiles, g.K, g.nRanks, g.xchgMc != nullptr);
     const int grid = SmCount() & ~1;
