@@ -992,10 +992,14 @@ struct ScatterBody {
 // pair of the WHOLE matrix, which no rank knows on the host (counts are private
 // to each rank), so the kernel works it out: after the first barrier every
 // block row reads all P x P send sizes from the tables, takes the maximum and
-// loops ceil(max / chunk) times - the same number on every rank.  Pass k moves
-// bytes [k * chunk, (k + 1) * chunk) of every pair: stage, barrier, pull,
-// barrier (nobody restages while a peer still reads).  The reference paces the
-// same loop with per-peer credit flags (aiv_all_to_all_v_mesh_1D.h:184-214).
+// loops ceil(max / window) times - the same number on every rank - where the
+// window is `chunk` or, when the largest pair is smaller, that pair's size (so
+// that the block rows share the bytes that actually move, not an empty window).
+// Pass k moves bytes [k * window, (k + 1) * window) of every pair: stage,
+// barrier, pull, barrier (nobody restages while a peer still reads).  The
+// reference paces the same loop with per-peer credit flags
+// (aiv_all_to_all_v_mesh_1D.h:184-214).
+struct A2aSendOffsets { uint64_t v[kMaxDevRanks]; };
 struct A2aBody {
     using Args = CollArgs;
     static constexpr int kThreads = 512;
@@ -1006,18 +1010,9 @@ struct A2aBody {
         const uint64_t e = LoadEpoch(c, b);
         uint64_t* myMeta = reinterpret_cast<uint64_t*>(a.xch[me]) + (size_t)b * 2 * kMaxDevRanks;
         const bool windowed = (a.mode & MODE_STAGE_IN) && a.chunk != 0;
-        const size_t win = (a.chunk + 15) & ~(size_t)15;
-        // A block row owns the same byte range [wb, we) of every window in every pass (clipped to what the pass moves):
-        // block rows only synchronise with the same row of the peers, so a row must never restage bytes that another
-        // row's reader may still be pulling.
-        size_t wb = 0, we = 0;
-        if (windowed) Share(a.chunk, nb, b, 16, &wb, &we);
+        const size_t win = (a.chunk + 15) & ~(size_t)15;             // distance between the peers' windows in the slab
         if (windowed) {
-            for (int q = 0; q < p; ++q) {
-                const size_t n0 = a.cnt2[q] < a.chunk ? a.cnt2[q] : a.chunk;
-                const size_t sb = wb < n0 ? wb : n0, se = we < n0 ? we : n0;
-                BlockCopyBytes(const_cast<char*>(a.src[me]) + (size_t)q * win + sb, a.in + a.dsp2[q] + sb, se - sb);
-            }
+            // sizes first: the window split depends on the largest pair of the whole matrix
             if (threadIdx.x < p) {
                 myMeta[threadIdx.x] = (uint64_t)threadIdx.x * win;
                 myMeta[kMaxDevRanks + threadIdx.x] = a.cnt2[threadIdx.x];
@@ -1035,7 +1030,16 @@ struct A2aBody {
             myMeta[threadIdx.x] = a.dsp2[threadIdx.x];
         }
         RankBarrier(c, b, 0, e + 1, K_A2AV);
+        // where each peer keeps its data for this rank: one remote read per peer, all in flight together
+        HCCL_SHARED(A2aSendOffsets, s_sd);
+        if ((int)threadIdx.x < p && (int)threadIdx.x != me)
+            s_sd.v[threadIdx.x] = reinterpret_cast<const volatile uint64_t*>(a.xch[threadIdx.x])[(size_t)b * 2 * kMaxDevRanks + me];
         uint64_t passes = 1;
+        // A block row owns the same byte range [wb, we) of every window in every pass (clipped to what the pass moves):
+        // block rows only synchronise with the same row of the peers, so a row must never restage bytes that another
+        // row's reader may still be pulling.  The range is a share of the EFFECTIVE window: the configured one, or the
+        // largest pair when that is smaller, so that a small exchange still uses every block row.
+        size_t wb = 0, we = 0, eff = 0;
         if (windowed) {
             HCCL_SHARED(unsigned long long, s_max);
             if (threadIdx.x == 0) s_max = 0ull;
@@ -1046,18 +1050,24 @@ struct A2aBody {
                 atomicMax(&s_max, (unsigned long long)v);
             }
             __syncthreads();
-            passes = s_max == 0 ? 1 : (s_max + a.chunk - 1) / a.chunk;
+            const uint64_t mx = s_max;
+            eff = mx >= a.chunk ? (size_t)a.chunk : (size_t)((mx + 15) & ~(uint64_t)15);
+            if (eff == 0) eff = 16;
+            passes = mx == 0 ? 1 : (mx + eff - 1) / eff;
+            Share(eff, nb, b, 16, &wb, &we);
+        } else {
+            __syncthreads();
         }
         for (uint64_t k = 0; k < passes; ++k) {
-            const size_t base = windowed ? (size_t)k * a.chunk : 0;
-            if (k > 0) {
+            const size_t base = windowed ? (size_t)k * eff : 0;
+            if (windowed) {
                 for (int q = 0; q < p; ++q) {
                     const size_t left = a.cnt2[q] > base ? a.cnt2[q] - base : 0;
-                    const size_t n0 = left < a.chunk ? left : a.chunk;
+                    const size_t n0 = left < eff ? left : eff;
                     const size_t sb = wb < n0 ? wb : n0, se = we < n0 ? we : n0;
                     BlockCopyBytes(const_cast<char*>(a.src[me]) + (size_t)q * win + sb, a.in + a.dsp2[q] + base + sb, se - sb);
                 }
-                RankBarrier(c, b, 0, e + 1 + 2 * k, K_A2AV);
+                RankBarrier(c, b, 0, e + 2 + 2 * k, K_A2AV);
             }
             {
                 CopySeg segs[kMaxDevRanks];
@@ -1068,23 +1078,19 @@ struct A2aBody {
                     size_t len = a.cnt[q];
                     if (windowed) {
                         const size_t left = a.cnt[q] > base ? a.cnt[q] - base : 0;
-                        len = left < a.chunk ? left : a.chunk;
+                        len = left < eff ? left : eff;
                     }
                     size_t rb, re;
                     if (windowed) { rb = wb < len ? wb : len; re = we < len ? we : len; }
                     else Share(len, nb, b, 16, &rb, &re);
-                    if (q == me) {
-                        own = CopySeg{a.out + a.dsp[q] + base + rb, a.in + a.dsp2[me] + base + rb, re - rb};
-                    } else {
-                        const uint64_t sd = reinterpret_cast<const volatile uint64_t*>(a.xch[q])[(size_t)b * 2 * kMaxDevRanks + me];
-                        segs[n++] = CopySeg{a.out + a.dsp[q] + base + rb, a.src[q] + sd + rb, re - rb};
-                    }
+                    if (q == me) own = CopySeg{a.out + a.dsp[q] + base + rb, a.in + a.dsp2[me] + base + rb, re - rb};
+                    else segs[n++] = CopySeg{a.out + a.dsp[q] + base + rb, a.src[q] + s_sd.v[q] + rb, re - rb};
                 }
                 BlockCopyRemoteAndLocal(segs, n, own);
             }
-            RankBarrier(c, b, 0, e + 2 + 2 * k, K_A2AV);
+            RankBarrier(c, b, 0, windowed ? e + 3 + 2 * k : e + 2, K_A2AV);
         }
-        StoreEpoch(c, b, e + 2 * passes);
+        StoreEpoch(c, b, windowed ? e + 1 + 2 * passes : e + 2);
         OpTail(c, b);
     }
 };

@@ -164,8 +164,9 @@ void RegisterAll()
                 c.net = NetType::NVLS_SWITCH;
                 c.B = (m.stageIn || !o.inMulticast) ? m.copy() : 0;
                 c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
-                // the switch still has to pull (p-1)/p of the input out of every GPU
-                c.D = (m.p - 1) / m.p * m.nvls() * (double)o.bytes;
+                // the switch still has to pull (p-1)/p of the input out of every GPU, at the rate of a port (measured 623 GB/s
+                // of egress at 1 GiB on 8 GPUs), and a staged input is copied before any of that starts
+                c.D = ((m.p - 1) / m.p * m.link() + c.B) * (double)o.bytes;
                 return std::vector<CostCoeff>{c};
             };
             R.Register(e);
@@ -341,7 +342,7 @@ void RegisterAll()
             c.A = (m.p - 1) / m.p * m.link();
             c.ratio = 1.0 / m.p;
             c.B = (m.stageIn ? m.copy() : 0) + m.copy() / m.p;
-            c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
+            c.C = m.lm.launchUs + 3 * m.lm.barrierUs;          // two barriers and the read of the senders' offset tables
             return std::vector<CostCoeff>{c};
         };
         R.Register(e);
@@ -456,9 +457,16 @@ void RegisterAll()
         AlgEntry f = Base("NvlsBroadcastSoleMeshScatter", HCCL_CMD_BROADCAST, HCCL_ENGINE_NVLS, "MeshScatter", DALG_BCAST_SCATTER_NVLS, AlgoType::NVLS);
         f.attrs.needsNvls = true;
         f.attrs.minBytes = 1024 * 1024;
-        // above a few tens of MiB a receiver's port takes multicast stores at little more than half the rate of peer
-        // reads (measured at 8 GPUs: 485 GB/s of bus bandwidth at 1 GiB): the pipelined peer-read form takes over
-        f.attrs.maxBytes = 48ull << 20;
+        // a receiver's port takes multicast stores at about two thirds of the rate of peer reads (measured at 8 GPUs:
+        // 485 GB/s of bus bandwidth at 1 GiB against 538 GB/s for the pipelined peer-read form, which has more steps and
+        // only wins from 512 MiB up)
+        f.attrs.maxBytes = 384ull << 20;
+        // two ranks: the one receiver pulls half and is sent the other half through the switch, measured 0.72-0.86 of
+        // NCCL from 8 MiB up where the plain pull of everything runs at 1.12
+        f.attrs.opCustomCheck = [](const OpDesc&, const TopoInfo& t, std::string* why) {
+            if (t.nRanks < 3) { *why = "topo: fewer than three ranks"; return false; }
+            return true;
+        };
         f.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
             M m(t, o);
             CostCoeff c;
@@ -499,8 +507,11 @@ void RegisterAll()
         AlgEntry e = Base("P2pBroadcastSoleMeshPipe", HCCL_CMD_BROADCAST, HCCL_ENGINE_P2P, "MeshPipe", DALG_BCAST_PIPE, AlgoType::PIPELINE);
         e.attrs.needsAligned16 = true;
         e.attrs.minBytes = 4ull << 20;
-        e.attrs.opCustomCheck = [](const OpDesc&, const TopoInfo& t, std::string* why) {
+        e.attrs.opCustomCheck = [](const OpDesc& o, const TopoInfo& t, std::string* why) {
             if (t.nRanks < 3) { *why = "topo: fewer than three ranks (one receiver pulls everything from the root)"; return false; }
+            // with a switch the multicast forms are faster up to a few hundred MiB (measured at 8 GPUs: 16 MiB 65 against
+            // 86 us, 256 MiB 584 against 596 us, 1 GiB 2213 against 1996 us)
+            if (t.nvls && o.bytes < (384ull << 20)) { *why = "op: below 384 MiB the switch forms are faster"; return false; }
             return true;
         };
         e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
@@ -546,6 +557,9 @@ void RegisterAll()
         f.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
             M m(t, o);
             CostCoeff c;
+            // (push, reduce and pull run one after the other inside a launch and a large message takes several launches:
+            // measured 485 GB/s of bus bandwidth at 1 GiB on 8 GPUs, where the staged switch form stays ahead; the
+            // staged peer-to-peer two-shot form has the same phases plus the stage-in pass)
             c.A = 2.0 * (m.p - 1) / m.p * m.link();
             c.ratio = 1.0 / m.p;
             c.B = 0.25 * m.copy() + m.copy() / m.p;

@@ -447,7 +447,8 @@ def test_device_cost_model_on_a_synthetic_nvswitch_box():
     assert first(8, 1, Cmd.REDUCE_SCATTER, 1 * G) == "NvlsReduceScatterSoleMesh"
     assert first(8, 1, Cmd.BROADCAST, 1 * K) == "P2pBroadcastSoleMeshLL"
     assert first(8, 1, Cmd.BROADCAST, 32 * M) == "NvlsBroadcastSoleMeshScatter"   # scatter + switch all-gather: p senders instead of one
-    assert first(8, 1, Cmd.BROADCAST, 256 * M) == "P2pBroadcastSoleMeshPipe"      # large: pipelined scatter + all-gather over peer reads
+    assert first(8, 1, Cmd.BROADCAST, 1 * G) == "P2pBroadcastSoleMeshPipe"        # very large: pipelined scatter + all-gather over peer reads
+    assert first(8, 0, Cmd.BROADCAST, 64 * M) == "P2pBroadcastSoleMeshPipe"       # no switch: the pipelined form from a few MiB
     assert first(8, 1, Cmd.ALLTOALL, 1 * M) == "P2pAlltoAllSoleMeshLL"
     assert first(8, 1, Cmd.ALLTOALL, 1 * G) == "P2pAlltoAllSoleMesh"
     # the cost grows with the message and every viable row carries a cost
