@@ -53,14 +53,26 @@ def human(b):
     return f"{b} B"
 
 
-def write_markdown(rows, path, command):
+def write_markdown(rows, path, command, ladder=False):
     """One table per (op, dtype): time (busBW) of the symmetric-buffer and the ordinary-buffer path and of NCCL, the
-    slowest single iteration of this library's symmetric path, the algorithm that ran, and the ratios."""
+    slowest single iteration of this library's symmetric path, the algorithm that ran, and the ratios.  `ladder`
+    keeps every fourth size (8 B, 128 B, ... 4 GiB; for AlltoAllV the sizes nearest to those)."""
     import collections
 
     t = collections.OrderedDict()
     for r in rows:
         t.setdefault((r["op"], r["dtype"], r["bytes"]), {})[r["impl"]] = r
+    if ladder:
+        per_op = collections.OrderedDict()
+        for (op, dt, b) in t:
+            per_op.setdefault((op, dt), []).append(b)
+        keep = set()
+        for (op, dt), sizes in per_op.items():
+            sizes = sorted(sizes)
+            for i, b in enumerate(sizes):
+                if i % 4 == 0 or i == len(sizes) - 1:
+                    keep.add((op, dt, b))
+        t = collections.OrderedDict((k, v) for k, v in t.items() if k in keep)
     world = rows[0]["n_gpus"] if rows else 0
     with open(path, "w") as f:
         f.write(f"# Collective sweep against NCCL, {world} x B200\n\nCommand:\n\n    {command}\n\n"
@@ -96,7 +108,14 @@ def main():
     ap.add_argument("--repeats", type=int, default=3)
     ap.add_argument("--markdown", default="", help="also write the tables as markdown to this file")
     ap.add_argument("--check", action="store_true", help="verify results against NCCL at every size")
+    ap.add_argument("--from-jsonl", default="", help="render --markdown from the rows of an earlier run instead of measuring (no GPU needed)")
+    ap.add_argument("--ladder", action="store_true", help="--markdown keeps every fourth size")
+    ap.add_argument("--command", default="", help="with --from-jsonl: the command that produced the rows, quoted in the markdown")
     args = ap.parse_args()
+    if args.from_jsonl:
+        rows = [json.loads(line) for line in open(args.from_jsonl) if line.startswith("{")]
+        write_markdown(rows, args.markdown, args.command or "(see the jsonl)", ladder=args.ladder)
+        return
 
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -211,7 +230,8 @@ def main():
             for r in rows:
                 f.write(json.dumps(r) + "\n")
     if rank == 0 and args.markdown:
-        write_markdown(rows, args.markdown, f"python -m torch.distributed.run --nnodes=1 --nproc-per-node {world} --master-addr 127.0.0.1 " + " ".join(sys.argv))
+        write_markdown(rows, args.markdown, f"python -m torch.distributed.run --nnodes=1 --nproc-per-node {world} --master-addr 127.0.0.1 " + " ".join(sys.argv),
+                       ladder=args.ladder)
     comm.destroy()
     dist.destroy_process_group()
 

@@ -453,14 +453,17 @@ __device__ __forceinline__ void GatherPushWorker(const DevComm& c, const GemmArg
 // AllGather, cooperative push form.  The epilogue warps of a GEMM CTA are idle for most of a tile's main loop (a
 // 256 x 256 x 8192 tile takes about 45 us, draining it a few), and a posted write needs no shared memory and almost no
 // issue slots.  So instead of giving 20-28 SMs to copy workers, every CTA computes and its four epilogue warps take
-// 64 KiB pieces of the local shard from a shared counter whenever no accumulator is waiting: destinations in the
+// 16 KiB pieces of the local shard from a shared counter whenever no accumulator is waiting: destinations in the
 // order rank-1, rank-2, ... (the order in which the consumers need this rank's rows), pieces in address order, the
 // copy into this rank's own gathered buffer last.  After a piece the warp fences once and adds the bytes it wrote to
 // the destination's arrival counter of every 128-row block the piece touches.  At the start of the kernel all
 // epilogue warps are idle, which front-loads the transfer: the first remote rows reach their consumer long before the
-// tiles of its own shard are done.  One warp of CTA 0 runs the start barrier (every rank is inside the kernel: nobody
+// tiles of its own shard are done.  The piece size decides when the FIRST destination is complete: the ~590 epilogue
+// warps of a GPU take consecutive pieces, so one round of them covers 590 x piece bytes; with 64 KiB pieces that was
+// 4.6 destinations' shards at once (8 MiB each at 4096 x 8192 over 8 ranks) and the nearest consumer saw its first
+// remote rows after 80-90 us, with 16 KiB pieces one round is about one shard.  One warp of CTA 0 runs the start barrier (every rank is inside the kernel: nobody
 // still reads its gathered buffer from earlier work, and its arrival counters are clear) and then opens the counter.
-constexpr uint32_t kPushPieceBytes = 64 * 1024;
+constexpr uint32_t kPushPieceBytes = 16 * 1024;
 
 __device__ __forceinline__ bool MbarTestWait(uint64_t* bar, uint32_t parity)
 {

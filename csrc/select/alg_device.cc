@@ -496,7 +496,7 @@ void RegisterAll()
             CostCoeff c;
             c.A = (m.p - 1) / m.p * m.link();
             c.ratio = 1.0 / m.p;
-            c.B = 2.0 * m.copy();
+            c.B = 1.0 * m.copy();           // the landed blocks are copied out once, locally
             c.C = m.lm.launchUs + m.lm.barrierUs;
             return std::vector<CostCoeff>{c};
         };
