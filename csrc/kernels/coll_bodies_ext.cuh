@@ -613,6 +613,120 @@ struct A2aPushBody {
 };
 
 // ---------------------------------------------------------------------------------------------------------------
+// AlltoAllV with a leader row.  The counts of an AlltoAllV are private to each rank, so the host cannot size the grid
+// by the data: every rank launches the full grid, and in A2aBody every one of its (up to 128) block rows runs the
+// size exchange and two barriers with its peers - 65-78 us for any exchange below a few MiB at 8 ranks where NCCL
+// takes 46-50 us.  Here only block row 0 exchanges the sizes: it publishes this rank's send sizes and offsets, runs one
+// barrier, reads all p x p sizes, and tells the other rows of ITS OWN rank the largest pair through two local words
+// (a release store of the operator's tag after the size; the rows wait for the tag with a bounded acquire spin).
+// From the largest pair every rank derives the same number of rows that take part, R = one row per 32 KiB a rank
+// receives; rows >= R leave at once, without a barrier (their epochs do not move), rows < R share the data R ways and
+// run the barriers the transfer itself needs (staging / closing) with the same rows of the peers.  A row b > 0 may
+// read a peer's buffers without a barrier of its own: row 0 of its rank has passed the start barrier, so every peer
+// is inside this operator and its tables are published, and the tag's acquire makes that visible to the row.
+// Fields as in A2aBody; staged inputs always go through windows (chunk != 0).  Sync points: 2 + passes on the rows
+// that take part, none on the others.
+struct A2avLeaderBody {
+    using Args = CollArgs;
+    static constexpr int kThreads = 512;
+    static constexpr uint64_t kBytesPerRow = 32u << 10;
+    __device__ static void Run(const DevComm& c, const Args& a, int b, int nb)
+    {
+        OpHead(c, b);
+        const int p = c.nRanks, me = c.rank;
+        const uint64_t seq = LoadA2avSeq(c), tag = seq + 1;
+        uint64_t ev = LoadEpoch(c, b);
+        uint64_t* myMeta = reinterpret_cast<uint64_t*>(a.xch[me]);                 // row 0's table: the only one in use
+        const bool staged = (a.mode & MODE_STAGE_IN) != 0;
+        const size_t win = (a.chunk + 15) & ~(size_t)15;
+        uint64_t* tagWord = c.epochs + kA2avTagWord;
+        volatile uint64_t* maxWord = c.epochs + kA2avMaxWord;
+        HCCL_SHARED(unsigned long long, s_max);
+        if (b == 0) {
+            if ((int)threadIdx.x < p) {
+                myMeta[threadIdx.x] = staged ? (uint64_t)threadIdx.x * win : a.dsp2[threadIdx.x];
+                myMeta[kMaxDevRanks + threadIdx.x] = a.cnt2[threadIdx.x];
+            }
+            if (threadIdx.x == 0) s_max = 0ull;
+            RankBarrier(c, 0, 0, ++ev, K_A2AV);
+            if ((int)threadIdx.x < p * p) {
+                const int q = threadIdx.x / p, r = threadIdx.x % p;
+                const uint64_t v = reinterpret_cast<const volatile uint64_t*>(a.xch[q])[kMaxDevRanks + r];
+                atomicMax(&s_max, (unsigned long long)v);
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                *maxWord = (uint64_t)s_max;
+                StReleaseSys(tagWord, tag);          // after the size; a failed barrier has raised the abort word already
+            }
+        } else {
+            if (threadIdx.x == 0) {
+                WaitFlagGE(c, tagWord, tag, K_A2AV, b, 0, me);
+                s_max = (unsigned long long)*maxWord;
+            }
+            __syncthreads();
+        }
+        const uint64_t mx = s_max;
+        uint64_t rows = (mx * (uint64_t)(p - 1) + kBytesPerRow - 1) / kBytesPerRow;
+        if (rows < 1) rows = 1;
+        if (rows > (uint64_t)nb) rows = (uint64_t)nb;
+        const int R = (int)rows;
+        if (b >= R) {
+            FinishA2avSeq(c, seq, nb);
+            OpTail(c, b);
+            return;
+        }
+        // where each peer keeps its data for this rank: one remote read per peer, all in flight together
+        HCCL_SHARED(A2aSendOffsets, s_sd);
+        if ((int)threadIdx.x < p && (int)threadIdx.x != me) s_sd.v[threadIdx.x] = reinterpret_cast<const volatile uint64_t*>(a.xch[threadIdx.x])[me];
+        __syncthreads();
+        size_t eff = 0, wb = 0, we = 0;
+        uint64_t passes = 1;
+        if (staged) {
+            eff = mx >= a.chunk ? (size_t)a.chunk : (size_t)((mx + 15) & ~(uint64_t)15);
+            if (eff == 0) eff = 16;
+            passes = mx == 0 ? 1 : (mx + eff - 1) / eff;
+            Share(eff, R, b, 16, &wb, &we);
+        }
+        for (uint64_t k = 0; k < passes; ++k) {
+            const size_t base = staged ? (size_t)k * eff : 0;
+            if (staged) {
+                for (int q = 0; q < p; ++q) {
+                    const size_t left = a.cnt2[q] > base ? a.cnt2[q] - base : 0;
+                    const size_t n0 = left < eff ? left : eff;
+                    const size_t sb = wb < n0 ? wb : n0, se = we < n0 ? we : n0;
+                    BlockCopyBytes(const_cast<char*>(a.src[me]) + (size_t)q * win + sb, a.in + a.dsp2[q] + base + sb, se - sb);
+                }
+                RankBarrier(c, b, 0, ++ev, K_A2AV);
+            }
+            CopySeg segs[kMaxDevRanks];
+            CopySeg own{nullptr, nullptr, 0};
+            int n = 0;
+            for (int kk = 0; kk < p; ++kk) {
+                const int q = (me + kk) % p;
+                size_t len = a.cnt[q];
+                size_t rb, re;
+                if (staged) {
+                    const size_t left = a.cnt[q] > base ? a.cnt[q] - base : 0;
+                    len = left < eff ? left : eff;
+                    rb = wb < len ? wb : len;
+                    re = we < len ? we : len;
+                } else {
+                    Share(len, R, b, 16, &rb, &re);
+                }
+                if (q == me) own = CopySeg{a.out + a.dsp[q] + base + rb, a.in + a.dsp2[me] + base + rb, re - rb};
+                else segs[n++] = CopySeg{a.out + a.dsp[q] + base + rb, a.src[q] + s_sd.v[q] + rb, re - rb};
+            }
+            BlockCopyRemoteAndLocal(segs, n, own);
+            RankBarrier(c, b, 0, ++ev, K_A2AV);          // nobody restages, overwrites its buffer or leaves while a peer still reads
+        }
+        StoreEpoch(c, b, ev);
+        FinishA2avSeq(c, seq, nb);
+        OpTail(c, b);
+    }
+};
+
+// ---------------------------------------------------------------------------------------------------------------
 // ReduceScatter and AllReduce for ORDINARY (unregistered) buffers without the stage-in pass.  The pull forms first
 // copy the whole input into the slab so that the peers can read it: a full extra pass over the message.  Here a
 // rank writes block q of its input straight into rank q's slab (posted stores over NVLink, the input is read once,

@@ -53,6 +53,7 @@ HcclResult LaunchCollectiveExt(const LaunchTarget& t, DevAlg alg, HcclDataType d
         case DALG_RS_PUSH: HCCL_REDUCE_DISPATCH_EXT(RsPushBody) break;
         case DALG_AR_PUSH_TWOSHOT: HCCL_REDUCE_DISPATCH_EXT(ArPushTwoShotBody) break;
         case DALG_BCAST_PIPE: return LaunchBody<BcastPipeBody>(t, a, nb);
+        case DALG_A2AV_LEADER: return LaunchBody<A2avLeaderBody>(t, a, nb);
         case DALG_AG_RING: return LaunchBody<AgRingBody>(t, a, nb);
         case DALG_AG_NVLS: return LaunchBody<AgNvlsBody>(t, a, nb);
         case DALG_BCAST_SCATTER_NVLS: return LaunchBody<BcastScatterNvlsBody>(t, a, nb);

@@ -191,6 +191,27 @@ __device__ __forceinline__ void FinishPushSeq(const DevComm& c, uint64_t seq, in
     }
 }
 
+// AlltoAllV with a leader row (A2avLeaderBody) keeps four words per communicator: a count of such operators (read by
+// every block at entry, advanced by the last block to finish, like the flag-in-data counter), its ticket, and a
+// (tag, largest pair) pair through which block row 0 tells the other rows of ITS rank what the size exchange found.
+constexpr int kA2avSeqWord = kMaxBlocks + 4, kA2avTicketWord = kMaxBlocks + 5, kA2avTagWord = kMaxBlocks + 6, kA2avMaxWord = kMaxBlocks + 7;
+__device__ __forceinline__ uint64_t LoadA2avSeq(const DevComm& c)
+{
+    return *reinterpret_cast<volatile uint64_t*>(c.epochs + kA2avSeqWord);
+}
+__device__ __forceinline__ void FinishA2avSeq(const DevComm& c, uint64_t seq, int nBlocks)
+{
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long* ticket = reinterpret_cast<unsigned long long*>(c.epochs + kA2avTicketWord);
+        const unsigned long long t = atomicAdd(ticket, 1ull);
+        if (t == (unsigned long long)(nBlocks - 1)) {
+            *reinterpret_cast<volatile uint64_t*>(ticket) = 0;
+            *reinterpret_cast<volatile uint64_t*>(c.epochs + kA2avSeqWord) = seq + 1;
+        }
+    }
+}
+
 // Barrier among the blocks with index `block` of all ranks, on flag slot `slot`.
 // Everything the calling block wrote before the barrier (local or peer memory)
 // is visible to every participating block after it.  All threads of the block

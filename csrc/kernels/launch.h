@@ -47,6 +47,8 @@ enum DevAlg : int {
     DALG_RS_PUSH, DALG_AR_PUSH_TWOSHOT,
     // Broadcast of large messages: scatter from the root and AllGather among the others, pipelined piece by piece
     DALG_BCAST_PIPE,
+    // AlltoAllV whose size exchange and start barrier run on one block row per rank
+    DALG_A2AV_LEADER,
     DALG_COUNT
 };
 

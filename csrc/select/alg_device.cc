@@ -347,6 +347,21 @@ void RegisterAll()
         };
         R.Register(e);
     }
+    // ---------------- AlltoAllV whose size exchange and start barrier run on one block row per rank (the counts are
+    // private to each rank, so every rank launches the full grid; here only the rows the data needs run barriers)
+    {
+        AlgEntry e = Base("P2pAlltoAllVSoleMeshLeader", HCCL_CMD_ALLTOALLV, HCCL_ENGINE_P2P, "MeshLeader", DALG_A2AV_LEADER, AlgoType::MESH);
+        e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
+            M m(t, o);
+            CostCoeff c;
+            c.A = (m.p - 1) / m.p * m.link();
+            c.ratio = 1.0 / m.p;
+            c.B = (m.stageIn ? m.copy() : 0) + m.copy() / m.p;
+            c.C = m.lm.launchUs + 2 * m.lm.barrierUs;
+            return std::vector<CostCoeff>{c};
+        };
+        R.Register(e);
+    }
     // ---------------- reductions fused with a cast and a scale (only for calls that ask for one)
     {
         constexpr uint64_t kCastTypes = Bit(HCCL_DATA_TYPE_FP16) | Bit(HCCL_DATA_TYPE_BFP16) | Bit(HCCL_DATA_TYPE_FP32);
