@@ -543,3 +543,36 @@ def test_reductions_with_cast_and_scale_on_the_host_engine():
         comms[0].all_reduce_ex(np.zeros(4, dtype=np.int32), np.zeros(4, dtype=np.int32), scale=0.5)
     for c in comms:
         c.destroy()
+
+
+def test_forms_for_ordinary_buffers_private_counts_and_large_broadcasts():
+    """Selection of the forms added for ordinary (unregistered) buffers, for AlltoAllV and for large Broadcasts, on
+    synthetic topologies: who is offered, who is filtered and why."""
+    os.environ.pop("HCCL_ALGO", None)
+    os.environ.pop("HCCL_SELECTOR_MODE", None)
+    lib.HcclReloadEnvConfig()
+    M, G = 1 << 20, 1 << 30
+    first = lambda *a, **k: _explain_device(*a, **k).splitlines()[0].replace("selected ", "")  # noqa: E731
+    # AlltoAllV: the leader-row form whatever the size and the buffers; the all-rows form stays registered
+    for reg in (0, 1):
+        for nbytes in (1024, 1 * M, 1 * G):
+            assert first(8, 1, Cmd.ALLTOALLV, nbytes, registered=reg) == "P2pAlltoAllVSoleMeshLeader"
+    assert "P2pAlltoAllVSoleMesh:" in _explain_device(8, 1, Cmd.ALLTOALLV, 1 * M)
+    # ReduceScatter on ordinary buffers: blocks pushed into the receivers' slabs; registered buffers are read in place
+    assert first(4, 0, Cmd.REDUCE_SCATTER, 64 * M, registered=0) == "P2pReduceScatterSoleMeshPush"
+    assert first(4, 0, Cmd.REDUCE_SCATTER, 64 * M, registered=1) == "P2pReduceScatterSoleMesh"
+    assert "the input is registered" in _explain_device(4, 0, Cmd.REDUCE_SCATTER, 64 * M, registered=1)
+    assert first(8, 1, Cmd.REDUCE_SCATTER, 1 * G, registered=0) == "P2pReduceScatterSoleMeshPush"      # staging 1 GiB for the switch costs a pass
+    assert first(8, 1, Cmd.REDUCE_SCATTER, 1 * G, registered=1) == "NvlsReduceScatterSoleMesh"
+    # AllReduce on ordinary buffers without a switch: slices pushed, no stage-in pass; with one the staged switch form stays
+    assert first(8, 0, Cmd.ALLREDUCE, 64 * M, registered=0) == "P2pAllReduceSoleMeshPushTwoShot"
+    assert first(8, 1, Cmd.ALLREDUCE, 64 * M, registered=0) == "NvlsAllReduceSoleMesh"
+    # Broadcast: two ranks never take the scatter + switch form; with a switch the pipelined peer-read form waits for 384 MiB
+    assert first(2, 1, Cmd.BROADCAST, 64 * M) == "P2pBroadcastSoleMeshOneShot"
+    assert "fewer than three ranks" in _explain_device(2, 1, Cmd.BROADCAST, 64 * M)
+    assert "below 384 MiB" in _explain_device(8, 1, Cmd.BROADCAST, 64 * M)
+    assert first(8, 1, Cmd.BROADCAST, 512 * M) == "P2pBroadcastSoleMeshPipe"
+    # AlltoAll: the push form (posted writes, one barrier) up to a few MiB on symmetric buffers, further on ordinary ones
+    assert first(8, 1, Cmd.ALLTOALL, 4 * M, registered=1) == "P2pAlltoAllSoleMeshPush"
+    assert first(8, 1, Cmd.ALLTOALL, 32 * M, registered=0) == "P2pAlltoAllSoleMeshPush"
+    assert first(8, 1, Cmd.ALLTOALL, 256 * M, registered=1) == "P2pAlltoAllSoleMesh"
