@@ -7,10 +7,11 @@
 //       ins_v2_all_reduce_concurrent_executor.cc): the data is split by the
 //       bandwidth ratio, part A runs the mesh template on queue 0 while part B
 //       runs NHR on queue 1.
-//   Pipeline (the reference's OmniPipe / PipeLine 2D executors,
+//   Pipeline (the reference's OmniPipe / PipeLine 2D and 3D executors,
 //       ins_v2_all_reduce_omnipipe_executor.cc, coll_algo_intro/Pipeline.md):
 //       the data is cut in at most five steps; step i's inter-server stage runs
-//       beside step i + 1's intra-server stage, each stage on its own queue.
+//       beside step i + 1's intra-server stage, each stage on its own queue;
+//       AllReduce also on three levels (server, pod, pods) in five stages.
 //   Nonuniform Bruck (HCCL_ALGO "NB", scatter_nb.cc): AllGather, Broadcast and a
 //       binomial-tree Scatter in ceil(log2 p) steps for any p.
 //   Hierarchical AlltoAll(V/VC) (all_to_all_v/.../aicpu/hier/*): intra-server
@@ -376,6 +377,38 @@ HcclResult PipelineAllReduce(HostWorld& w, HostPrims& x, uint32_t rank, const Wo
     return HCCL_SUCCESS;
 }
 
+// AllReduce on three levels (the reference's 3-D OmniPipe, ins_v2_all_reduce_omnipipe_executor.cc with
+// TopoMatchThreeLevel, per-step slices of omnipipe_data_slice_calc.cc): five stages - mesh ReduceScatter inside the
+// server, NHR ReduceScatter across the servers of the pod, NHR AllReduce across the pods on the slice that is left,
+// NHR AllGather across the servers, mesh AllGather inside the server - each on its own queue, and step i's stage s
+// beside step i + 1's stage s - 1.  A topology with fewer levels runs the two-level pipeline.
+HcclResult Pipeline3AllReduce(HostWorld& w, HostPrims& x, uint32_t rank, const Work& wk)
+{
+    AlgHierarchy h;
+    CHK_RET(MatchTopo(w.Topo(rank), TopoMatchKind::THREE_LEVEL, &h));
+    if (h.levels() < 3) return PipelineAllReduce(w, x, rank, wk);
+    Group g0, g1, g2;
+    LevelGroup(h, 0, rank, &g0);
+    LevelGroup(h, 1, rank, &g1);
+    LevelGroup(h, 2, rank, &g2);
+    const uint64_t ranks = (uint64_t)g0.size() * g1.size() * g2.size();
+    const uint32_t steps = PipelineStepCount(wk.count, ranks * std::max<uint64_t>(1, 128 / wk.es), kMaxPipeSteps);
+    for (const PipeSlot& s : PipelineSchedule(5, steps)) {
+        const Work chunk = SubWork(wk, steps, s.step);
+        const Work inServer = SubWork(chunk, g0.size(), g0.me);          // what this rank holds after stage 0
+        const Work inPod = SubWork(inServer, g1.size(), g1.me);          // ... and after stage 1
+        Ctx c{w, x, s.stage, 0, w.scratchBytes()};
+        switch (s.stage) {
+            case 0: MeshReduceScatter(c, g0, chunk); break;
+            case 1: ReduceScatterBy(Fam::NHR, c, g1, inServer); break;
+            case 2: AllReduceBy(Fam::NHR, c, g2, inPod); break;
+            case 3: AllGatherBy(Fam::NHR, c, g1, inServer); break;
+            default: MeshAllGather(c, g0, chunk); break;
+        }
+    }
+    return HCCL_SUCCESS;
+}
+
 // AllGather: every block is cut in steps.  Stage 0 pulls a piece of the server-mates' inputs (mesh), stage 1 pulls the
 // same piece of every other server's blocks from the rank with my local index there, once that rank's stage 0 of the
 // step is done.  Ranks are numbered server by server.
@@ -607,11 +640,12 @@ HcclResult RunHostExecutorExt(HostWorld& w, uint32_t rank, int alg, const OpPara
     Ctx c{w, x, 0, 0, w.scratchBytes()};
     HcclResult r = HCCL_SUCCESS;
     switch (alg) {
-        case HALG_AR_CONCURRENT_MESH_NHR: case HALG_AR_PIPELINE_MESH_NHR: case HALG_AR_TREE: {
+        case HALG_AR_CONCURRENT_MESH_NHR: case HALG_AR_PIPELINE_MESH_NHR: case HALG_AR_PIPELINE3_MESH_NHR_NHR: case HALG_AR_TREE: {
             x.Copy(Out(rank), In(rank), Bytes(p));
             const Work wk{BufKind::OUTPUT, 0, p.count, es};
             if (alg == HALG_AR_CONCURRENT_MESH_NHR) ConcurrentAllReduce(w, x, all, wk);
             else if (alg == HALG_AR_PIPELINE_MESH_NHR) r = PipelineAllReduce(w, x, rank, wk);
+            else if (alg == HALG_AR_PIPELINE3_MESH_NHR_NHR) r = Pipeline3AllReduce(w, x, rank, wk);
             else r = TreeAllReduce(w, x, rank, wk);
             break;
         }

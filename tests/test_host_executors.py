@@ -173,6 +173,24 @@ def test_pipeline_executors(algo_env, topo, n):
     destroy(comms)
 
 
+@pytest.mark.parametrize("topo,n", [(TWO_PODS, 8), ("[[[0,1,2],[3,4,5]],[[6,7,8],[9,10,11]],[[12,13,14],[15,16,17]]]", 18)])
+def test_three_level_pipeline_all_reduce(algo_env, topo, n):
+    """Servers, pods and the level above them: five pipelined stages (mesh ReduceScatter, NHR ReduceScatter, NHR
+    AllReduce, NHR AllGather, mesh AllGather), checked against the fp64 sum and by the trace verifier."""
+    comms = make(n, topo=topo, algo="level0:NA;level1:omnipipe;level2:omnipipe")
+    for count in (1, 5, 977, 30011):
+        ins = [np.random.default_rng(100 + r).standard_normal(count).astype(np.float32) for r in range(n)]
+        outs = [np.zeros(count, np.float32) for _ in range(n)]
+        verified(comms, lambda r, c: c.all_reduce(ins[r], outs[r]))
+        assert comms[0].last_algorithm() == "HostAllReducePipelineMeshNHRNHR", comms[0].last_algorithm()
+        ref = np.sum(np.stack(ins).astype(np.float64), 0)
+        for o in outs:
+            np.testing.assert_allclose(o, ref, rtol=3e-6, atol=3e-5)
+        for o in outs[1:]:
+            assert np.array_equal(o, outs[0])
+    destroy(comms)
+
+
 @pytest.mark.parametrize("n", [2, 3, 6, 8, 11])
 def test_nonuniform_bruck(algo_env, n):
     comms = make(n, algo="level0:NA;level1:NB")
