@@ -13,6 +13,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <functional>
+#include <memory>
 #include <string>
 #include <thread>
 #include "kernels/coll_bodies.cuh"
@@ -118,6 +119,53 @@ void Launch(World& w, const std::vector<typename Body::Args>& args, int nb, int 
     }
     for (std::thread& t : pool) t.join();
     for (hostshim::BlockCtx* c : blocks) { pthread_barrier_destroy(&c->bar); delete c; }
+}
+
+// A stream of launches: every rank runs the operators one after the other, and only ITS OWN blocks wait for one
+// another between two operators (a kernel boundary on that rank's stream).  Nothing lines the ranks up, so a fast
+// rank is inside operator n + 1 while a slow one still finishes operator n - what real GPUs do between two
+// stream-ordered kernels, and what the forms without a closing barrier have to survive.
+struct StreamOp {
+    int nb;
+    std::function<void(int rank, int block)> run;
+};
+void LaunchStream(World& w, const std::vector<StreamOp>& ops, int threads)
+{
+    int maxNb = 1;
+    for (const StreamOp& o : ops) maxNb = std::max(maxNb, o.nb);
+    std::vector<hostshim::BlockCtx*> blocks;
+    std::vector<pthread_barrier_t*> boundaries;
+    std::vector<std::thread> pool;
+    for (int r = 0; r < w.p; ++r) {
+        pthread_barrier_t* boundary = new pthread_barrier_t;
+        pthread_barrier_init(boundary, nullptr, (unsigned)(maxNb * threads));
+        boundaries.push_back(boundary);
+        for (int b = 0; b < maxNb; ++b) {
+            hostshim::BlockCtx* ctx = new hostshim::BlockCtx();
+            memset(ctx->shared, 0, sizeof(ctx->shared));
+            pthread_barrier_init(&ctx->bar, nullptr, (unsigned)threads);
+            blocks.push_back(ctx);
+            for (int t = 0; t < threads; ++t) {
+                pool.emplace_back([&ops, ctx, boundary, r, b, t, threads] {
+                    hostshim::ThreadCtx& me = hostshim::Tls();
+                    me.tid.x = (unsigned)t;
+                    me.bdim.x = (unsigned)threads;
+                    me.block = ctx;
+                    for (const StreamOp& o : ops) {
+                        if (b < o.nb) {
+                            me.bid.x = (unsigned)(r * o.nb + b);
+                            me.gdim.x = (unsigned)o.nb;
+                            o.run(r, b);
+                        }
+                        pthread_barrier_wait(boundary);
+                    }
+                });
+            }
+        }
+    }
+    for (std::thread& t : pool) t.join();
+    for (hostshim::BlockCtx* c : blocks) { pthread_barrier_destroy(&c->bar); delete c; }
+    for (pthread_barrier_t* bq : boundaries) { pthread_barrier_destroy(bq); delete bq; }
 }
 
 std::vector<float> RandVec(size_t n, unsigned seed)
