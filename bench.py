@@ -219,16 +219,38 @@ def main():
     if args.impl == "hccl" and not args.no_extras:
         t0 = time.perf_counter()
         extras, check = {}, {}
+
+        def guarded(name, fn):
+            """Runs one block of the extras; a failure on any rank ends that block on every rank (they agree over NCCL)
+            and is reported in the output instead of taking the step measurement down with it."""
+            res, err = None, None
+            try:
+                res = fn()
+                torch.cuda.synchronize()
+            except Exception as ex:                      # noqa: BLE001
+                err = f"{type(ex).__name__}: {ex}"[:300]
+            if world > 1:
+                flag = torch.tensor([0 if err else 1], device="cuda", dtype=torch.int32)
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                if int(flag.item()) == 0 and err is None:
+                    err = "another rank failed in this block"
+            if err is not None:
+                extras.setdefault("errors", {})[name] = err
+                return None
+            return res
+
         if world > 1:
             sizes = tuple(s for s in headline.LADDER if s <= args.ladder_max_bytes)
-            extras["collectives_busbw_vs_nccl"] = headline.collective_ladder(comm, sizes=sizes)
-            extras["fused_matmul_collective_vs_nccl_cublas"] = headline.mc2_headline(comm) if not args.tiny else []
-            check["collectives_max_rel_err"] = headline.collective_check(comm)
-            check["fused_kernels_max_rel_err"] = {r["case"] + (f"_m{r['m']}" if r["case"] == "matmul_ar" else ""): r["max_rel_err"]
-                                                  for r in extras["fused_matmul_collective_vs_nccl_cublas"]}
+            fused = guarded("fused_matmul_collective_vs_nccl_cublas", lambda: headline.mc2_headline(comm) if not args.tiny else [])
+            extras["fused_matmul_collective_vs_nccl_cublas"] = fused
+            check["fused_kernels_max_rel_err"] = {r["case"] + (f"_m{r['m']}" if r["case"] == "matmul_ar" else ""): r["max_rel_err"] for r in (fused or [])}
+            ladder = []                                   # rows are kept as they come: a failure late in the ladder loses nothing before it
+            guarded("collectives_busbw_vs_nccl", lambda: headline.collective_ladder(comm, sizes=sizes, emit=ladder.append))
+            extras["collectives_busbw_vs_nccl"] = ladder
+            check["collectives_max_rel_err"] = guarded("collectives_max_rel_err", lambda: headline.collective_check(comm))
         else:
-            extras["matmul_vs_cublas"] = headline.gemm_headline()
-            check["matmul_max_rel_err_vs_cublas"] = {r["name"]: r["max_rel_err_vs_cublas"] for r in extras["matmul_vs_cublas"]}
+            extras["matmul_vs_cublas"] = guarded("matmul_vs_cublas", headline.gemm_headline)
+            check["matmul_max_rel_err_vs_cublas"] = {r["name"]: r["max_rel_err_vs_cublas"] for r in (extras["matmul_vs_cublas"] or [])}
         check["model_loss_library_vs_baseline"] = [main_arm["last_loss"], base_arm["last_loss"] if base_arm else None]
         extras["seconds"] = time.perf_counter() - t0
 
@@ -265,7 +287,10 @@ def main():
             out["check"] = check
         print(json.dumps(out))
     if comm is not None:
-        comm.destroy()
+        try:
+            comm.destroy()
+        except Exception:                                # noqa: BLE001  (a communicator that reported an error above)
+            pass
     if world > 1:
         dist.destroy_process_group()
     return 0
