@@ -362,6 +362,9 @@ void RegisterHostAlgorithms()
     Reg({"HostAllGatherPipelineMeshMesh", HCCL_CMD_ALLGATHER, HALG_AG_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, false, Four, rs, true});
     Reg({"HostReduceScatterPipelineMeshMesh", HCCL_CMD_REDUCE_SCATTER, HALG_RS_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, true, Four, rs, false});
     Reg({"HostBroadcastPipelineMeshMesh", HCCL_CMD_BROADCAST, HALG_BCAST_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, false, Four, ar, true});
+    Reg({"HostAllGatherSoleMeshZAxisDetour", HCCL_CMD_ALLGATHER, HALG_AG_MESH_DETOUR, "sole", {"MeshZAxisDetour"}, AlgoType::DETOUR, 1, false, Two, rs, true});
+    Reg({"HostReduceScatterSoleMeshZAxisDetour", HCCL_CMD_REDUCE_SCATTER, HALG_RS_MESH_DETOUR, "sole", {"MeshZAxisDetour"}, AlgoType::DETOUR, 1, true, Two, rs, false});
+    Reg({"HostScatterSoleMeshZAxisDetour", HCCL_CMD_SCATTER, HALG_SCATTER_MESH_DETOUR, "sole", {"MeshZAxisDetour"}, AlgoType::DETOUR, 1, false, Two, rs, true});
     Reg({"HostAllGatherSoleNB", HCCL_CMD_ALLGATHER, HALG_AG_NB, "sole", {"NB"}, AlgoType::NB, 1, false, L1, rs, true});
     Reg({"HostBroadcastSoleNB", HCCL_CMD_BROADCAST, HALG_BCAST_NB, "sole", {"NB"}, AlgoType::NB, 1, false, L1, ar, true});
     Reg({"HostScatterSoleNB", HCCL_CMD_SCATTER, HALG_SCATTER_NB, "sole", {"NB"}, AlgoType::NB, 1, false, L1, one, true});

@@ -17,6 +17,9 @@
 //   Hierarchical AlltoAll(V/VC) (all_to_all_v/.../aicpu/hier/*): intra-server
 //       stage into relays, meta table, inter-server stage.
 //   Sequence forms of Broadcast, Reduce, Scatter and Barrier on two levels.
+//   Mesh with a detour (the reference's Z-axis detour templates): AllGather,
+//       ReduceScatter and Scatter whose pair transfers are split over two
+//       channels by bandwidth.
 //   Tree executor (experimental/ops/op_common/recursive_executor/*, RFC 0003):
 //       one executor that interprets a tree of seq / par / rev nodes with
 //       template leaves, given in HCCL_ALGO_TREE.
@@ -164,6 +167,62 @@ void ConcurrentAllGather(HostWorld& w, HostPrims& x, const Group& all, uint32_t 
         NhrAllGather(cb, all, B);
         for (uint32_t j = 0; j < n; ++j) x.Copy(Out(rank, ((uint64_t)j * p.count + a) * es), B.At(rank, (uint64_t)j * b), b * es, 1);
     }
+    x.SyncGroup(all.ranks, N_DONE);
+}
+
+// ---------------------------------------------------------------- mesh with a detour (Z-axis detour)
+// The reference's mesh templates with a detour (ins_temp_all_gather_mesh_1D_Z_axis_detour.cc and the ReduceScatter /
+// Scatter twins) move every pair's slice over TWO channels of the same pair: the direct mesh link and a second channel
+// through the other link class, split by bandwidth - p - 1 mesh links against the port count of the second class,
+// 8 unless configured (CalcCostCoeff :33-65, CalcDataSplitByBandwidthZAxisDetour template_utils.h:796-805).  Here the
+// two parts of a slice run on two queues; HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO="a,b" overrides the shares.
+uint64_t DetourDirectPart(uint64_t count, uint32_t ranks, uint32_t es)
+{
+    const EnvConfig& env = GetEnvConfig();
+    double direct = ranks > 1 ? (double)(ranks - 1) : 1.0, detour = 8.0;
+    if (env.splitRatio.size() >= 2 && env.splitRatio[0] + env.splitRatio[1] > 0) { direct = env.splitRatio[0]; detour = env.splitRatio[1]; }
+    return BandwidthSplit(count, direct, detour, std::max<uint64_t>(1, 128 / es));
+}
+void DetourAllGather(HostWorld& w, HostPrims& x, const Group& all, uint32_t rank, const OpParam& p)
+{
+    (void)w;
+    const uint32_t n = all.size(), es = DataTypeSize(p.dtype);
+    const uint64_t a = DetourDirectPart(p.count, n, es), b = p.count - a;
+    x.SyncGroup(all.ranks, N_READY);
+    for (uint32_t k = 0; k < n; ++k) {
+        const uint32_t j = (rank + k) % n;
+        if (a) x.Copy(Out(rank, (uint64_t)j * p.count * es), In(j), a * es, 0);
+        if (b) x.Copy(Out(rank, ((uint64_t)j * p.count + a) * es), In(j, a * es), b * es, 1);
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+}
+// ReduceScatter: block `rank` of every peer's input is folded into the output in rank order, the direct part on queue 0
+// and the detour part on queue 1 (the two parts are disjoint element ranges).
+void DetourReduceScatter(HostWorld& w, HostPrims& x, const Group& all, uint32_t rank, const OpParam& p)
+{
+    (void)w;
+    const uint32_t n = all.size(), es = DataTypeSize(p.dtype);
+    const uint64_t a = DetourDirectPart(p.count, n, es), b = p.count - a;
+    const uint64_t mine = (uint64_t)rank * p.count * es;
+    x.SyncGroup(all.ranks, N_READY);
+    if (a) x.Copy(Out(rank), In(rank, mine), a * es, 0);
+    if (b) x.Copy(Out(rank, a * es), In(rank, mine + a * es), b * es, 1);
+    for (uint32_t k = 1; k < n; ++k) {
+        const uint32_t j = (rank + k) % n;
+        if (a) x.Reduce(Out(rank), In(j, mine), a * es, 0);
+        if (b) x.Reduce(Out(rank, a * es), In(j, mine + a * es), b * es, 1);
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+}
+void DetourScatter(HostWorld& w, HostPrims& x, const Group& all, uint32_t rank, const OpParam& p)
+{
+    (void)w;
+    const uint32_t es = DataTypeSize(p.dtype);
+    const uint64_t a = DetourDirectPart(p.count, all.size(), es), b = p.count - a;
+    const uint64_t mine = (uint64_t)rank * p.count * es;
+    x.SyncGroup(all.ranks, N_READY);
+    if (a) x.Copy(Out(rank), In(p.root, mine), a * es, 0);
+    if (b) x.Copy(Out(rank, a * es), In(p.root, mine + a * es), b * es, 1);
     x.SyncGroup(all.ranks, N_DONE);
 }
 
@@ -649,6 +708,9 @@ HcclResult RunHostExecutorExt(HostWorld& w, uint32_t rank, int alg, const OpPara
             else r = TreeAllReduce(w, x, rank, wk);
             break;
         }
+        case HALG_AG_MESH_DETOUR: DetourAllGather(w, x, all, rank, p); break;
+        case HALG_RS_MESH_DETOUR: DetourReduceScatter(w, x, all, rank, p); break;
+        case HALG_SCATTER_MESH_DETOUR: DetourScatter(w, x, all, rank, p); break;
         case HALG_RS_CONCURRENT_MESH_NHR: ConcurrentReduceScatter(w, x, all, rank, p); break;
         case HALG_AG_CONCURRENT_MESH_NHR: ConcurrentAllGather(w, x, all, rank, p); break;
         case HALG_AG_PIPELINE_MESH_MESH: r = PipelineAllGather(w, x, rank, p); break;

@@ -183,6 +183,7 @@ enum HostAlg : int {
     HALG_P2P_DIRECT, HALG_BARRIER_MESH, HALG_BARRIER_NHR, HALG_BARRIER_RHD,
     // executors of host_executors.cc
     HALG_AR_CONCURRENT_MESH_NHR, HALG_RS_CONCURRENT_MESH_NHR, HALG_AG_CONCURRENT_MESH_NHR,
+    HALG_AG_MESH_DETOUR, HALG_RS_MESH_DETOUR, HALG_SCATTER_MESH_DETOUR,
     HALG_AR_PIPELINE_MESH_NHR, HALG_AR_PIPELINE3_MESH_NHR_NHR, HALG_AG_PIPELINE_MESH_MESH, HALG_RS_PIPELINE_MESH_MESH, HALG_BCAST_PIPELINE_MESH_MESH,
     HALG_AG_NB, HALG_BCAST_NB, HALG_SCATTER_NB,
     HALG_A2A_HIER,

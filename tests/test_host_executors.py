@@ -191,6 +191,45 @@ def test_three_level_pipeline_all_reduce(algo_env, topo, n):
     destroy(comms)
 
 
+@pytest.mark.parametrize("n", [2, 5, 8])
+def test_mesh_with_a_detour(algo_env, n):
+    """AllGather, ReduceScatter and Scatter whose pair transfers are split over two channels (queues) by bandwidth:
+    p - 1 mesh links against 8 ports of the second link class unless the split-ratio variable says otherwise."""
+    comms = make(n, algo="allgather=level0:detour/reducescatter=level0:detour/scatter=level0:detour")
+    try:
+        for ratio in (None, "1,3", "1,0"):
+            if ratio:
+                os.environ["HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO"] = ratio
+            else:
+                os.environ.pop("HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO", None)
+            lib.HcclReloadEnvConfig()
+            for count in (1, 130, 4099):
+                ag_in = [np.random.default_rng(r).integers(-9, 9, count).astype(np.int32) for r in range(n)]
+                ag_out = [np.zeros(count * n, np.int32) for _ in range(n)]
+                verified(comms, lambda r, c: c.all_gather(ag_in[r], ag_out[r]))
+                assert comms[0].last_algorithm() == "HostAllGatherSoleMeshZAxisDetour", comms[0].last_algorithm()
+                for o in ag_out:
+                    assert np.array_equal(o, np.concatenate(ag_in))
+                rs_in = [np.random.default_rng(50 + r).standard_normal(count * n) for r in range(n)]
+                rs_out = [np.zeros(count, np.float64) for _ in range(n)]
+                verified(comms, lambda r, c: c.reduce_scatter(rs_in[r], rs_out[r]))
+                assert comms[0].last_algorithm() == "HostReduceScatterSoleMeshZAxisDetour", comms[0].last_algorithm()
+                ref = np.sum(np.stack(rs_in), 0)
+                for r in range(n):
+                    np.testing.assert_allclose(rs_out[r], ref[r * count:(r + 1) * count], rtol=1e-12, atol=1e-13)
+                for root in (0, n - 1):
+                    sc_in = [np.arange(count * n, dtype=np.int64) + 1000 * r for r in range(n)]
+                    sc_out = [np.zeros(count, np.int64) for _ in range(n)]
+                    verified(comms, lambda r, c: c.scatter(sc_in[r], sc_out[r], root))
+                    assert comms[0].last_algorithm() == "HostScatterSoleMeshZAxisDetour", comms[0].last_algorithm()
+                    for r in range(n):
+                        assert np.array_equal(sc_out[r], sc_in[root][r * count:(r + 1) * count])
+    finally:
+        os.environ.pop("HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO", None)
+        lib.HcclReloadEnvConfig()
+    destroy(comms)
+
+
 @pytest.mark.parametrize("n", [2, 3, 6, 8, 11])
 def test_nonuniform_bruck(algo_env, n):
     comms = make(n, algo="level0:NA;level1:NB")
