@@ -299,6 +299,10 @@ void RegisterHostAlgorithms()
     Reg({"HostAllReduceSequenceMeshRing", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_MESH_RING, "sequence", {"Mesh", "Ring"}, AlgoType::RING, 2, true, TwoP1, ar, false});
     Reg({"HostAllReduceSequenceMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_MESH_NHR, "sequence", {"Mesh", "NHR"}, AlgoType::NHR, 2, true, TwoL, ar, false});
     Reg({"HostAllReduceSequenceMeshRHD", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_MESH_RHD, "sequence", {"Mesh", "RHD"}, AlgoType::HD_R, 2, true, TwoL, ar, false});
+    // one physical level folded into a grid (squeeze 2-D match): flat topologies only; one step more than the plain
+    // two-shot so that automatic selection keeps that one
+    Reg({"HostAllReduceSequenceSqueeze2DMeshMesh", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_SQUEEZE2D_MESH_MESH, "sequence", {"Mesh", "Mesh"}, AlgoType::HIER, 1, true,
+         [](double) { return 4.0; }, ar, false});
     Reg({"HostAllReduceSequenceMeshNHRNHR", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ3_MESH_NHR_NHR, "sequence", {"Mesh", "NHR", "NHR"}, AlgoType::NHR, 3, true, TwoL, ar, false});
     Reg({"HostAllReduceParallelMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_PARALLEL_MESH_NHR, "parallel", {"Mesh", "NHR"}, AlgoType::PIPELINE, 2, true, TwoL, ar, false});
     // ReduceScatter (+V)
@@ -419,7 +423,7 @@ HcclResult HcclDebugTopo(const char* topoJson, uint32_t nRanks, uint32_t rank, i
     CHK_PTR_NULL(text);
     TopoMeta meta;
     std::string err;
-    if (nRanks == 0 || rank >= nRanks || matchKind < 0 || matchKind > 2) return HCCL_E_PARA;
+    if (nRanks == 0 || rank >= nRanks || matchKind < 0 || matchKind > 3) return HCCL_E_PARA;
     if (!ParseTopoMeta(topoJson, nRanks, &meta, &err)) { snprintf(text, capacity, "error: %s", err.c_str()); return HCCL_SUCCESS; }
     TopoInfo t;
     CHK_RET(BuildTopoFromMeta(meta, rank, &t));

@@ -404,6 +404,16 @@ HcclResult RunHostAlgorithm(HostWorld& w, uint32_t rank, int alg, const OpParam&
             SequenceAllReduce(c, h, rank, wk, fam);
             break;
         }
+        case HALG_AR_SEQ_SQUEEZE2D_MESH_MESH: {
+            // a flat group laid out as a grid: mesh ReduceScatter along the rows, mesh AllReduce along the columns on
+            // the slice that is left, mesh AllGather along the rows - 2 (sqrt p - 1)-ish partners per rank instead of p - 1
+            AlgHierarchy h;
+            CHK_RET(hierarchy(TopoMatchKind::SQUEEZE_2D, &h));
+            x.Copy(Out(rank), In(rank), Bytes(p));
+            Work wk{BufKind::OUTPUT, 0, p.count, es};
+            SequenceAllReduce(c, h, rank, wk, std::vector<Fam>(h.levels(), Fam::MESH));
+            break;
+        }
         case HALG_AR_PARALLEL_MESH_NHR: {
             // two halves take the levels in opposite order, each on its own queue; scratch is split between them
             AlgHierarchy h;

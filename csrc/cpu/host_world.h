@@ -173,7 +173,7 @@ public:
 // Algorithm identifiers of the host engine (what AlgEntry::hostAlg holds).
 enum HostAlg : int {
     HALG_AR_MESH_ONESHOT = 0, HALG_AR_MESH_TWOSHOT, HALG_AR_RING, HALG_AR_RHD, HALG_AR_NHR, HALG_AR_SEQ_MESH_RING, HALG_AR_SEQ_MESH_NHR,
-    HALG_AR_SEQ_MESH_RHD, HALG_AR_SEQ3_MESH_NHR_NHR, HALG_AR_PARALLEL_MESH_NHR, HALG_AR_ORDER_PRESERVED,
+    HALG_AR_SEQ_MESH_RHD, HALG_AR_SEQ3_MESH_NHR_NHR, HALG_AR_SEQ_SQUEEZE2D_MESH_MESH, HALG_AR_PARALLEL_MESH_NHR, HALG_AR_ORDER_PRESERVED,
     HALG_RS_MESH, HALG_RS_RING, HALG_RS_RHD, HALG_RS_NHR, HALG_RS_SEQ_MESH_NHR, HALG_RS_ORDER_PRESERVED,
     HALG_AG_MESH, HALG_AG_RING, HALG_AG_RHD, HALG_AG_NHR, HALG_AG_SEQ_MESH_NHR,
     HALG_BCAST_MESH_ONESHOT, HALG_BCAST_MESH_TWOSHOT, HALG_BCAST_NHR,

@@ -183,6 +183,20 @@ HcclResult MatchTopo(const TopoInfo& t, TopoMatchKind kind, AlgHierarchy* out)
 {
     out->infos.clear();
     auto all = [&] { std::vector<uint32_t> v(t.nRanks); std::iota(v.begin(), v.end(), 0u); return v; };
+    if (kind == TopoMatchKind::SQUEEZE_2D) {
+        // one physical level (the whole group when it is flat, else not applicable) as a grid
+        if (t.nServers > 1) { HCCL_WARNING("squeeze-2D match is for a single physical level"); return HCCL_E_NOT_SUPPORT; }
+        uint32_t cols = 1;
+        for (uint32_t d = 2; (uint64_t)d * d <= t.nRanks; ++d)
+            if (t.nRanks % d == 0) cols = d;
+        if (cols == 1) { out->infos.push_back({all()}); return HCCL_SUCCESS; }
+        const uint32_t rowLen = t.nRanks / cols;                 // the longer side: consecutive ranks share a row
+        std::vector<std::vector<uint32_t>> rows(cols), columns(rowLen);
+        for (uint32_t r = 0; r < t.nRanks; ++r) { rows[r / rowLen].push_back(r); columns[r % rowLen].push_back(r); }
+        out->infos.push_back(rows);
+        out->infos.push_back(columns);
+        return HCCL_SUCCESS;
+    }
     if (kind == TopoMatchKind::ONE_LEVEL || t.nServers <= 1) {
         out->infos.push_back({all()});
         return HCCL_SUCCESS;

@@ -62,10 +62,15 @@ struct AlgHierarchy {
     std::vector<std::vector<std::vector<uint32_t>>> infos;
     uint32_t levels() const { return (uint32_t)infos.size(); }
 };
-enum class TopoMatchKind : int { ONE_LEVEL = 0, TWO_LEVEL = 1, THREE_LEVEL = 2 };
+enum class TopoMatchKind : int { ONE_LEVEL = 0, TWO_LEVEL = 1, THREE_LEVEL = 2, SQUEEZE_2D = 3 };
 // ONE_LEVEL: all ranks in one group.  TWO_LEVEL: level 0 = ranks of my server,
 // level 1 = ranks with my local index across servers (requires symmetric
-// servers).  THREE_LEVEL adds the pod level.
+// servers).  THREE_LEVEL adds the pod level.  SQUEEZE_2D folds ONE physical level
+// into two algorithm levels (reference topo_match_squeeze_2d): the ranks of a
+// server - or of the whole flat group - are laid out as rows x cols with cols the
+// largest divisor of the count that is at most its square root; level 0 = the rows
+// (consecutive ranks), level 1 = the columns.  A count without such a divisor
+// (a prime) stays one level.
 HcclResult MatchTopo(const TopoInfo& topo, TopoMatchKind kind, AlgHierarchy* out);
 
 }  // namespace hccl

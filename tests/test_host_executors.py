@@ -191,6 +191,24 @@ def test_three_level_pipeline_all_reduce(algo_env, topo, n):
     destroy(comms)
 
 
+@pytest.mark.parametrize("n", [4, 6, 7, 8, 12])
+def test_all_reduce_on_a_squeezed_grid(algo_env, n):
+    """A flat group folded into rows x columns (squeeze 2-D match): mesh ReduceScatter along the rows, mesh AllReduce
+    along the columns, mesh AllGather along the rows; a prime count runs as one mesh."""
+    comms = make(n, algo="allreduce=level0:hier")
+    for count in (1, 77, 10007):
+        ins = [np.random.default_rng(200 + r).standard_normal(count).astype(np.float32) for r in range(n)]
+        outs = [np.zeros(count, np.float32) for _ in range(n)]
+        verified(comms, lambda r, c: c.all_reduce(ins[r], outs[r]))
+        assert comms[0].last_algorithm() == "HostAllReduceSequenceSqueeze2DMeshMesh", comms[0].last_algorithm()
+        ref = np.sum(np.stack(ins).astype(np.float64), 0)
+        for o in outs:
+            np.testing.assert_allclose(o, ref, rtol=3e-6, atol=3e-5)
+        for o in outs[1:]:
+            assert np.array_equal(o, outs[0])
+    destroy(comms)
+
+
 @pytest.mark.parametrize("n", [2, 5, 8])
 def test_mesh_with_a_detour(algo_env, n):
     """AllGather, ReduceScatter and Scatter whose pair transfers are split over two channels (queues) by bandwidth:

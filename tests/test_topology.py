@@ -54,3 +54,13 @@ def test_bad_literals_are_reported():
     assert topo("[[[0,1],[2]]", 3, 0, 0)[0].startswith("error:")
     assert topo("[[0,1,2]]", 3, 0, 0)[0].startswith("error:")
     assert topo("[[[0,1],[2,3]]]", 5, 0, 0)[0].startswith("error:")              # four devices listed, five ranks asked for
+
+
+def test_squeeze_2d_folds_one_level_into_a_grid():
+    """One physical level laid out as rows x columns: the largest divisor that is at most the square root gives the
+    number of rows; a prime count stays one group; more than one server is refused."""
+    assert topo(None, 8, 3, 3)[2:4] == ["level 0: [0,1,2,3] [4,5,6,7]", "level 1: [0,4] [1,5] [2,6] [3,7]"]
+    assert topo(None, 6, 0, 3)[2:4] == ["level 0: [0,1,2] [3,4,5]", "level 1: [0,3] [1,4] [2,5]"]
+    assert topo(None, 16, 0, 3)[2:4] == ["level 0: [0,1,2,3] [4,5,6,7] [8,9,10,11] [12,13,14,15]", "level 1: [0,4,8,12] [1,5,9,13] [2,6,10,14] [3,7,11,15]"]
+    assert topo(None, 7, 0, 3)[2] == "level 0: [0,1,2,3,4,5,6]"
+    assert topo("[[[0,1],[2,3]]]", 4, 0, 3)[2] == "match: HCCL_E_NOT_SUPPORT"
