@@ -288,6 +288,7 @@ EnvConfig ParseEnvConfig(const EnvGetter& get)
     if (val("HCCL_MAX_BLOCKS", &s)) { if (ParseU32(s, &u) && u >= 1 && u <= 128) c.maxBlocks = u; else c.errors.push_back("HCCL_MAX_BLOCKS: expected 1..128"); }
     if (val("HCCL_B200_EMULATE", &s)) { if (ParseBool(s, &b)) c.emulate = b; }
     if (val("HCCL_B200_FORCE_IPC", &s)) { if (ParseBool(s, &b)) c.forceIpc = b; }
+    if (val("HCCL_A2AV_LEADER", &s)) { if (ParseBool(s, &b)) c.a2avLeader = b; else c.errors.push_back("HCCL_A2AV_LEADER: expected 0 or 1"); }
     if (val("HCCL_CALL_SHAPE_AGREE", &s)) { if (ParseBool(s, &b)) c.callShapeAgree = b; else c.errors.push_back("HCCL_CALL_SHAPE_AGREE: expected 0 or 1"); }
     return c;
 }

@@ -73,6 +73,7 @@ struct EnvConfig {
     uint32_t maxBlocks = 0;                           // HCCL_MAX_BLOCKS, 0 = auto
     bool emulate = false;                             // HCCL_B200_EMULATE
     bool forceIpc = false;                            // HCCL_B200_FORCE_IPC: skip VMM, use cudaIpc
+    bool a2avLeader = true;                           // HCCL_A2AV_LEADER: AlltoAllV with the size exchange on one block row per rank (0: on every row)
     bool callShapeAgree = true;                       // HCCL_CALL_SHAPE_AGREE: ranks exchange their buffer facts the first time they meet a call signature
     std::vector<std::string> errors;                  // one line per rejected variable
 };

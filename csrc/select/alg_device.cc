@@ -6,6 +6,7 @@
 // the Sole/Mesh entries of the other operators listed with REGISTER_EXEC_V2).
 #include <algorithm>
 #include "selector.h"
+#include "../core/config.h"
 #include "../kernels/dev_types.h"
 #include "../kernels/launch.h"
 
@@ -351,6 +352,10 @@ void RegisterAll()
     // private to each rank, so every rank launches the full grid; here only the rows the data needs run barriers)
     {
         AlgEntry e = Base("P2pAlltoAllVSoleMeshLeader", HCCL_CMD_ALLTOALLV, HCCL_ENGINE_P2P, "MeshLeader", DALG_A2AV_LEADER, AlgoType::MESH);
+        e.attrs.opCustomCheck = [](const OpDesc&, const TopoInfo&, std::string* why) {
+            if (!GetEnvConfig().a2avLeader) { *why = "config: HCCL_A2AV_LEADER=0"; return false; }
+            return true;
+        };
         e.costCoeff = [](const TopoInfo& t, const OpDesc& o) {
             M m(t, o);
             CostCoeff c;

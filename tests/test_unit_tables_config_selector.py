@@ -558,6 +558,14 @@ def test_forms_for_ordinary_buffers_private_counts_and_large_broadcasts():
         for nbytes in (1024, 1 * M, 1 * G):
             assert first(8, 1, Cmd.ALLTOALLV, nbytes, registered=reg) == "P2pAlltoAllVSoleMeshLeader"
     assert "P2pAlltoAllVSoleMesh:" in _explain_device(8, 1, Cmd.ALLTOALLV, 1 * M)
+    os.environ["HCCL_A2AV_LEADER"] = "0"
+    lib.HcclReloadEnvConfig()
+    try:
+        assert first(8, 1, Cmd.ALLTOALLV, 1 * M) == "P2pAlltoAllVSoleMesh"
+        assert "HCCL_A2AV_LEADER=0" in _explain_device(8, 1, Cmd.ALLTOALLV, 1 * M)
+    finally:
+        os.environ.pop("HCCL_A2AV_LEADER")
+        lib.HcclReloadEnvConfig()
     # ReduceScatter on ordinary buffers: blocks pushed into the receivers' slabs; registered buffers are read in place
     assert first(4, 0, Cmd.REDUCE_SCATTER, 64 * M, registered=0) == "P2pReduceScatterSoleMeshPush"
     assert first(4, 0, Cmd.REDUCE_SCATTER, 64 * M, registered=1) == "P2pReduceScatterSoleMesh"
