@@ -34,3 +34,14 @@ def test_kernel_bodies_on_cpu_threads(sanitizer):
     r = subprocess.run([str(exe), "--quick"], capture_output=True, text=True, env=env, timeout=1500)
     assert "ThreadSanitizer" not in r.stderr and "AddressSanitizer" not in r.stderr, r.stderr[-6000:]
     assert r.returncode == 0 and "all checks passed" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
+
+
+@pytest.mark.skipif(shutil.which("g++") is None or not Path(CUDA_HOME, "include", "cuda_runtime.h").exists(), reason="needs g++ and the CUDA headers")
+def test_small_sizes_around_vector_and_slice_boundaries():
+    """1 ... 257 elements on 2, 3 and 5 ranks for the bodies whose slicing rounds to 16 bytes (short and empty slices,
+    block rows with nothing to do, tails shorter than a vector), under AddressSanitizer."""
+    exe = ROOT / "build" / "kernel_harness_address"
+    _build("-fsanitize=address", exe)
+    r = subprocess.run([str(exe), "--edges"], capture_output=True, text=True, env=dict(os.environ, ASAN_OPTIONS="detect_leaks=0"), timeout=1500)
+    assert "AddressSanitizer" not in r.stderr, r.stderr[-6000:]
+    assert r.returncode == 0 and "all checks passed" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
