@@ -38,8 +38,9 @@ def test_kernel_bodies_on_cpu_threads(sanitizer):
 
 @pytest.mark.skipif(shutil.which("g++") is None or not Path(CUDA_HOME, "include", "cuda_runtime.h").exists(), reason="needs g++ and the CUDA headers")
 def test_small_sizes_around_vector_and_slice_boundaries():
-    """1 ... 257 elements on 2, 3 and 5 ranks for the bodies whose slicing rounds to 16 bytes (short and empty slices,
-    block rows with nothing to do, tails shorter than a vector), under AddressSanitizer."""
+    """1 ... 257 elements on 2 and 3 ranks for the bodies whose slicing rounds to 16 bytes (short and empty slices, block
+    rows with nothing to do, tails shorter than a vector), under AddressSanitizer; `--edges-all` runs every size, also
+    on 5 ranks (several minutes)."""
     exe = ROOT / "build" / "kernel_harness_address"
     _build("-fsanitize=address", exe)
     r = subprocess.run([str(exe), "--edges"], capture_output=True, text=True, env=dict(os.environ, ASAN_OPTIONS="detect_leaks=0"), timeout=1500)
