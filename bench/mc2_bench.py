@@ -47,6 +47,26 @@ def timed(fn, warm=5, iters=20, flush=None):
     return t.item()
 
 
+def headline_rows(args):
+    from hccl_b200.utils import headline
+
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+    comm = hb.Communicator.from_torch_distributed(config=hb.make_config(buffer_mib=256))
+    rows = headline.mc2_headline(comm, m=args.m, hidden=args.hidden, ffn=args.ffn, tp_shape=args.tp_shape)
+    if rank == 0:
+        for r in rows:
+            print(json.dumps(r), flush=True)
+        if args.out:
+            with open(args.out, "w") as f:
+                for r in rows:
+                    f.write(json.dumps(r) + "\n")
+    comm.destroy()
+    dist.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default="")
@@ -54,7 +74,12 @@ def main():
     ap.add_argument("--hidden", type=int, default=8192)
     ap.add_argument("--ffn", type=int, default=28672)
     ap.add_argument("--tp-shape", type=int, default=8, help="the TP degree the shard shapes are cut for (8 in the named config)")
+    ap.add_argument("--headline", action="store_true",
+                    help="print the rows bench.py reports in its extras instead (hccl_b200.utils.headline.mc2_headline at --m / --tp-shape: every launch timed "
+                         "alone AND back to back, roofline fractions against the burst and the sustained GEMM peak, errors against fp32)")
     args = ap.parse_args()
+    if args.headline:
+        return headline_rows(args)
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     rows = []
