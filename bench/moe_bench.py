@@ -8,6 +8,8 @@ routing from router logits N(0, 1) seeded per rank (variable per-peer counts); d
 fp32 scale per 1x128 block; combine is the gate-softmax-weighted bf16 sum back to token order.  The NCCL arm does the
 same work with torch ops: sort pairs by expert, quantise, all_to_all_single of counts / fp8 rows / scales, then
 all_to_all_single of the bf16 expert outputs and an index_add of the weighted rows.  Device-timed, max over ranks.
+Before the timings the library's result is checked against an fp32 evaluation with a different factor per expert
+(`max_rel_err_vs_fp32`; fp8 e4m3 with one scale per 128 values allows about 0.07).
 """
 from __future__ import annotations
 
@@ -21,7 +23,7 @@ import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import hccl_b200 as hb  # noqa: E402
-from hccl_b200.ops.moe import MoeDispatcher  # noqa: E402
+from hccl_b200.ops.moe import MoeDispatcher, dequantize  # noqa: E402
 
 
 def timed(fn, warm=3, iters=10):
@@ -78,6 +80,32 @@ def main():
     def ours_combine():
         disp.combine(w, out=out)
 
+    # ---- values first: expert e multiplies its (dequantised) rows by 1 + (e % 7) / 4, a different factor per expert of a
+    # token, so the combined row is x * sum_k w_k f(e_k): off when a row reaches the wrong expert, is quantised wrongly or
+    # meets the wrong gate weight
+    max_rel_err, check_error = None, None
+    try:
+        res = disp.dispatch(x, idx)
+        torch.cuda.synchronize()
+        off = res.offsets.cpu().tolist()
+        n_rows = off[-1]
+        deq = dequantize(res.x_fp8[:n_rows], res.scales[:n_rows])
+        for le in range(per):
+            deq[off[le]:off[le + 1]] *= 1.0 + ((rank * per + le) % 7) / 4.0
+        disp.y[:n_rows] = deq.bfloat16()
+        torch.cuda.synchronize()
+        dist.barrier()                                   # every rank's expert outputs are in place before anybody pulls them
+        got = disp.combine(w)
+        torch.cuda.synchronize()
+        f = 1.0 + (idx.long() % 7).float() / 4.0
+        ref = x.float() * (w * f).sum(1, keepdim=True)
+        err = torch.tensor([((got.float() - ref).abs().max() / ref.abs().max()).item()], device="cuda", dtype=torch.float64)
+        dist.all_reduce(err, op=dist.ReduceOp.MAX)
+        max_rel_err = err.item()                         # e4m3 with one scale per 128 values: up to about 0.07
+        dist.barrier()
+    except Exception as ex:                              # noqa: BLE001  (the timings below do not depend on the check)
+        check_error = f"{type(ex).__name__}: {ex}"[:200]
+
     ours_dispatch()
     torch.cuda.synchronize()
     n_recv = int(disp.offsets[-1])
@@ -120,7 +148,9 @@ def main():
     comb_bytes = T * K * H * 2
     row = {"case": "moe_ep", "n_gpus": world, "tokens_per_rank": T, "hidden": H, "experts": E, "topk": K, "dispatch_ms": t_d, "combine_ms": t_c,
            "nccl_dispatch_ms": t_nd, "nccl_combine_ms": t_nc, "dispatch_GBs_per_rank": disp_bytes / t_d / 1e6, "combine_GBs_per_rank": comb_bytes / t_c / 1e6,
-           "speedup_total": (t_nd + t_nc) / (t_d + t_c), "recv_rows": n_recv}
+           "speedup_total": (t_nd + t_nc) / (t_d + t_c), "recv_rows": n_recv, "max_rel_err_vs_fp32": max_rel_err}
+    if check_error:
+        row["check_error"] = check_error
     if rank == 0:
         print(json.dumps(row), flush=True)
         if args.out:
