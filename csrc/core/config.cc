@@ -105,6 +105,7 @@ const char* AlgoTypeName(AlgoType t)
         case AlgoType::HIER: return "hier";
         case AlgoType::TREE: return "tree";
         case AlgoType::DETOUR: return "detour";
+        case AlgoType::SERIAL: return "serial";
     }
     return "?";
 }
@@ -119,7 +120,7 @@ bool ParseAlgoType(const std::string& s, AlgoType* out)
         {"pairwise", AlgoType::PAIRWISE}, {"fullmesh", AlgoType::MESH}, {"mesh", AlgoType::MESH},
         {"oneshot", AlgoType::ONESHOT}, {"twoshot", AlgoType::TWOSHOT}, {"nvls", AlgoType::NVLS},
         {"ll", AlgoType::LL}, {"concurrent", AlgoType::CONCURRENT}, {"omnipipe", AlgoType::OMNIPIPE},
-        {"hier", AlgoType::HIER}, {"tree", AlgoType::TREE}, {"detour", AlgoType::DETOUR},
+        {"hier", AlgoType::HIER}, {"tree", AlgoType::TREE}, {"detour", AlgoType::DETOUR}, {"serial", AlgoType::SERIAL},
     };
     auto it = k.find(l);
     if (it == k.end()) return false;

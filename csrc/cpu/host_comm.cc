@@ -351,6 +351,9 @@ void RegisterHostAlgorithms()
         Reg({keep.back().c_str(), op, HALG_A2A_MESH, "sole", {"Mesh"}, AlgoType::MESH, 1, false, Two, rs, true});
         keep.push_back(std::string(base) + "SolePairwise");
         Reg({keep.back().c_str(), op, HALG_A2A_PAIRWISE, "sole", {"Pairwise"}, AlgoType::PAIRWISE, 1, false, P1, rs, true});
+        // one peer at a time through the staging buffer (every byte is copied twice): never the automatic choice
+        keep.push_back(std::string(base) + "SerialSoleMesh");
+        Reg({keep.back().c_str(), op, HALG_A2A_SERIAL, "serial", {"Mesh"}, AlgoType::SERIAL, 1, false, TwoP1, ar, true});
     }
     // Concurrent, Pipeline, Nonuniform Bruck, hierarchical and tree executors (host_executors.cc).  Their step counts
     // carry one extra step for the second queue or stage, so that automatic selection keeps the plain forms on ties.

@@ -657,6 +657,43 @@ HcclResult RunHostAlgorithm(HostWorld& w, uint32_t rank, int alg, const OpParam&
             x.SyncGroup(all.ranks, N_DONE);
             break;
         }
+        case HALG_A2A_SERIAL: {
+            // One peer at a time, for links where a rank may hold only one connection's worth of staging memory
+            // (reference: the serial sole executor of AlltoAllV, ins_v2_all_to_all_v_serial_sole_executor.cc:113-171,
+            // which also pairs rank ^ step and caps a transfer at half the staging buffer).  Step s pairs a rank with
+            // rank ^ s, so both ends of a pair choose each other in the same step and no rank serves two peers at
+            // once.  A pair moves max(sent, received) bytes in windows of half the staging buffer: the sender copies
+            // window k into half k % 2 of ITS buffer and posts, the receiver copies it out and acknowledges, and the
+            // sender waits for the acknowledgement of window k - 2 before it fills that half again - staging window
+            // k + 1 overlaps the peer's copy of window k.  Nothing but the staging buffer is read by a peer, so the
+            // input may be overwritten as soon as the call returns and no closing rendezvous is needed.
+            const uint32_t res = DataTypeSize(p.recvType);
+            const uint64_t half = (w.scratchBytes() / 2) & ~(uint64_t)63;
+            if (half == 0) return HCCL_E_MEMORY;
+            x.Copy(Out(rank, p.rdispls[rank] * res), In(rank, p.sdispls[rank] * es), p.sendCounts[rank] * es);
+            uint32_t limit = 1;
+            while (limit < n) limit <<= 1;
+            for (uint32_t step = 1; step < limit; ++step) {
+                const uint32_t peer = rank ^ step;
+                if (peer >= n) continue;
+                const uint64_t sendB = p.sendCounts[peer] * es, recvB = p.recvCounts[peer] * res;
+                const uint64_t most = sendB > recvB ? sendB : recvB;          // the same number on both ends of the pair
+                const uint64_t windows = (most + half - 1) / half;
+                for (uint64_t k = 0; k < windows; ++k) {
+                    const uint64_t off = k * half, slot = (k & 1) * half;
+                    const uint64_t sn = sendB > off ? (sendB - off < half ? sendB - off : half) : 0;
+                    const uint64_t rn = recvB > off ? (recvB - off < half ? recvB - off : half) : 0;
+                    if (k >= 2) x.Wait(peer, N_ACK);
+                    if (sn) x.Copy(Scratch(rank, slot), In(rank, p.sdispls[peer] * es + off), sn);
+                    x.Post(peer, N_DATA);
+                    x.Wait(peer, N_DATA);
+                    if (rn) x.Copy(Out(rank, p.rdispls[peer] * res + off), Scratch(peer, slot), rn);
+                    x.Post(peer, N_ACK);
+                }
+                for (uint64_t k = 0; k < (windows < 2 ? windows : 2); ++k) x.Wait(peer, N_ACK);   // both halves free for the next peer
+            }
+            break;
+        }
         // ------------------------------------------------------------ point to point
         case HALG_P2P_DIRECT: {
             // sends publish (buffer, bytes) in a per-destination mailbox in scratch and wait for the receiver to copy

@@ -211,6 +211,50 @@ def test_rooted_and_alltoall_ops(algo_env):
         destroy(comms)
 
 
+def test_serial_windowed_all_to_all(algo_env):
+    """AlltoAll / AlltoAllV one peer at a time (rank ^ step) through the staging buffer in windows of half of it
+    (reference: ins_v2_all_to_all_v_serial_sole_executor.cc:113-171): with a 1 MiB buffer the larger pairs take up to
+    four windows, so both halves are reused; rank counts that are and are not powers of two; a pair that sends
+    nothing one way; the trace verifier sees no race on the staging halves and no deadlock."""
+    for n in (2, 5, 8):
+        comms = make(n, algo="alltoall=level0:NA;level1:serial", buffer_mib=1)
+        count = 70001                                            # x 8 bytes: 547 KiB per pair = two windows of 512 KiB
+        a2a_in = [np.arange(count * n, dtype=np.int64) + 10000000 * r for r in range(n)]
+        a2a_out = [np.zeros(count * n, np.int64) for _ in range(n)]
+        comms[0].trace_begin()
+        run_ranks(comms, lambda r, c: c.all_to_all(a2a_in[r], a2a_out[r]))
+        assert comms[0].trace_verify().startswith("OK"), comms[0].trace_verify()
+        assert "SerialSoleMesh" in comms[0].last_algorithm()
+        for r in range(n):
+            for q in range(n):
+                assert np.array_equal(a2a_out[r][q * count:(q + 1) * count], a2a_in[q][r * count:(r + 1) * count])
+        # uneven counts: up to ~1.9 MiB one way (four windows) and nothing the other way for some pairs
+        cnt = [[0 if (i + 2 * j) % 5 == 1 else ((i * 7 + j * 13) % 9) * 53003 + 17 for j in range(n)] for i in range(n)]
+        sends = [np.arange(sum(cnt[i]), dtype=np.float32) + 0.5 * i for i in range(n)]
+        recvs = [np.zeros(sum(cnt[j][i] for j in range(n)), np.float32) for i in range(n)]
+
+        def a2av(i, c):
+            sd = [sum(cnt[i][:j]) for j in range(n)]
+            rc = [cnt[j][i] for j in range(n)]
+            rd = [sum(rc[:j]) for j in range(n)]
+            c.all_to_all_v(sends[i], cnt[i], sd, recvs[i], rc, rd)
+
+        comms[0].trace_begin()
+        run_ranks(comms, a2av)
+        assert comms[0].trace_verify().startswith("OK"), comms[0].trace_verify()
+        assert "SerialSoleMesh" in comms[0].last_algorithm()
+        recvs2 = [np.zeros_like(x) for x in recvs]
+        run_ranks(comms, lambda i, c: c.all_to_all_vc(sends[i], cnt, recvs2[i]))
+        for i in range(n):
+            off = 0
+            for j in range(n):
+                sd = sum(cnt[j][:i])
+                assert np.array_equal(recvs[i][off:off + cnt[j][i]], sends[j][sd:sd + cnt[j][i]])
+                off += cnt[j][i]
+            assert np.array_equal(recvs[i], recvs2[i])
+        destroy(comms)
+
+
 def test_v_variants_host(algo_env):
     n = 5
     comms = make(n)
