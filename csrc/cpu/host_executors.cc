@@ -470,7 +470,8 @@ HcclResult Pipeline3AllReduce(HostWorld& w, HostPrims& x, uint32_t rank, const W
 
 // AllGather: every block is cut in steps.  Stage 0 pulls a piece of the server-mates' inputs (mesh), stage 1 pulls the
 // same piece of every other server's blocks from the rank with my local index there, once that rank's stage 0 of the
-// step is done.  Ranks are numbered server by server.
+// step is done.  Ranks are numbered server by server.  AllGatherV: block j has its own count and displacement, every
+// block is cut in the same number of steps (from the largest block, which all ranks know).
 HcclResult PipelineAllGather(HostWorld& w, HostPrims& x, uint32_t rank, const OpParam& p)
 {
     AlgHierarchy h;
@@ -481,21 +482,30 @@ HcclResult PipelineAllGather(HostWorld& w, HostPrims& x, uint32_t rank, const Op
     g1.me = 0;
     if (h.levels() >= 2) { LevelGroup(h, 0, rank, &g0); LevelGroup(h, 1, rank, &g1); }
     const uint32_t es = DataTypeSize(p.dtype);
-    const uint32_t steps = PipelineStepCount(p.count, std::max<uint64_t>(1, 128 / es), kMaxPipeSteps);
+    const bool v = p.op == HCCL_CMD_ALLGATHER_V;
+    auto cnt = [&](uint32_t j) { return v ? p.recvCounts[j] : p.count; };
+    auto dsp = [&](uint32_t j) { return v ? p.rdispls[j] : (uint64_t)j * p.count; };
+    uint64_t largest = 0;
+    for (uint32_t j = 0; j < w.nRanks(); ++j) largest = std::max<uint64_t>(largest, cnt(j));
+    const uint32_t steps = PipelineStepCount(largest, std::max<uint64_t>(1, 128 / es), kMaxPipeSteps);
     x.SyncGroup(all.ranks, N_READY);
     for (const PipeSlot& s : PipelineSchedule(2, steps)) {
-        uint64_t b, e;
-        SliceOf(p.count, steps, s.step, &b, &e);
         if (s.stage == 0) {
             for (uint32_t k = 0; k < g0.size(); ++k) {
                 const uint32_t j = g0.world((g0.me + k) % g0.size());
-                x.Copy(Out(rank, ((uint64_t)j * p.count + b) * es), In(j, b * es), (e - b) * es, 0);
+                uint64_t b, e;
+                SliceOf(cnt(j), steps, s.step, &b, &e);
+                if (e > b) x.Copy(Out(rank, (dsp(j) + b) * es), In(j, b * es), (e - b) * es, 0);
             }
         } else {
             x.SyncGroup(g1.ranks, N_DATA, 1);
             for (uint32_t k = 1; k < g1.size(); ++k) {
                 const uint32_t peer = g1.world((g1.me + k) % g1.size());
-                for (uint32_t j : *GroupOf(h, 0, peer)) x.Copy(Out(rank, ((uint64_t)j * p.count + b) * es), Out(peer, ((uint64_t)j * p.count + b) * es), (e - b) * es, 1);
+                for (uint32_t j : *GroupOf(h, 0, peer)) {
+                    uint64_t b, e;
+                    SliceOf(cnt(j), steps, s.step, &b, &e);
+                    if (e > b) x.Copy(Out(rank, (dsp(j) + b) * es), Out(peer, (dsp(j) + b) * es), (e - b) * es, 1);
+                }
             }
         }
     }
@@ -561,6 +571,79 @@ HcclResult PipelineBroadcast(HostWorld& w, HostPrims& x, uint32_t rank, const Op
         } else {
             x.SyncGroup(t.g0.ranks, N_DATA, 1);
             if (rank != t.relay) x.Copy(Out(rank, b * es), Out(t.relay, b * es), (e - b) * es, 1);
+        }
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+    return HCCL_SUCCESS;
+}
+
+// Reduce: the message, copied to the upper half of the staging buffer, is cut in steps; stage 0 = mesh ReduceScatter
+// of a step inside the server, stage 1 = NHR ReduceScatter across servers of the slice this rank is left with, and
+// when the last step is through the root collects steps x members x servers pieces from their holders.
+HcclResult PipelineReduce(HostWorld& w, HostPrims& x, uint32_t rank, const OpParam& p)
+{
+    TwoLevel t;
+    CHK_RET(MatchTwoLevel(w, rank, p.root, &t));
+    const uint32_t es = DataTypeSize(p.dtype);
+    const uint64_t wOff = w.scratchBytes() / 2;
+    x.Copy(Scratch(rank, wOff), In(rank), Bytes(p));
+    const Work wk{BufKind::SCRATCH, wOff, p.count, es};
+    const Group all = WholeGroup(w, rank);
+    const uint32_t servers = t.flat ? 1 : t.g1.size();
+    const uint32_t steps = PipelineStepCount(p.count, (uint64_t)t.g0.size() * servers * std::max<uint64_t>(1, 128 / es), kMaxPipeSteps);
+    for (const PipeSlot& s : PipelineSchedule(2, steps)) {
+        const Work chunk = SubWork(wk, steps, s.step);
+        Ctx c{w, x, s.stage, 0, w.scratchBytes() / 2};
+        if (s.stage == 0) MeshReduceScatter(c, t.g0, chunk);
+        else if (!t.flat) NhrReduceScatter(c, t.g1, SubWork(chunk, t.g0.size(), t.g0.me));
+    }
+    x.SyncGroup(all.ranks, N_DATA);
+    if (rank == p.root) {
+        for (uint32_t step = 0; step < steps; ++step) {
+            const Work chunk = SubWork(wk, steps, step);
+            for (uint32_t l = 0; l < t.g0.size(); ++l) {
+                const Work sl = SubWork(chunk, t.g0.size(), l);
+                const std::vector<uint32_t>* col = t.flat ? nullptr : GroupOf(t.h, 1, t.g0.world(l));
+                for (uint32_t s = 0; s < servers; ++s) {
+                    const Work piece = SubWork(sl, servers, s);
+                    const uint32_t holder = t.flat ? t.g0.world(l) : (*col)[s];
+                    x.Copy(Out(rank, piece.base - wOff), Scratch(holder, piece.base), piece.count * es);
+                }
+            }
+        }
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+    return HCCL_SUCCESS;
+}
+
+// Scatter: every block is cut in steps.  Stage 0 moves a step of the blocks of one server from the root to the member
+// of that server that shares the root's local index (into its staging buffer, one slot per member), stage 1 hands the
+// step on inside the server; the root's own server reads the root's input directly.
+HcclResult PipelineScatter(HostWorld& w, HostPrims& x, uint32_t rank, const OpParam& p)
+{
+    TwoLevel t;
+    CHK_RET(MatchTwoLevel(w, rank, p.root, &t));
+    const uint32_t es = DataTypeSize(p.dtype);
+    const uint64_t blk = Bytes(p);
+    if ((uint64_t)t.g0.size() * blk > w.scratchBytes()) {
+        HCCL_ERROR("host engine: pipelined Scatter stages %llu bytes per server, the scratch buffer has %llu", (unsigned long long)(t.g0.size() * blk),
+                   (unsigned long long)w.scratchBytes());
+        return HCCL_E_MEMORY;
+    }
+    const uint32_t steps = PipelineStepCount(p.count, std::max<uint64_t>(1, 128 / es), kMaxPipeSteps);
+    const Group all = WholeGroup(w, rank);
+    x.SyncGroup(all.ranks, N_READY);
+    for (const PipeSlot& s : PipelineSchedule(2, steps)) {
+        uint64_t b, e;
+        SliceOf(p.count, steps, s.step, &b, &e);
+        const uint64_t off = b * es, len = (e - b) * es;
+        if (s.stage == 0) {
+            if (rank == t.relay && rank != p.root)
+                for (uint32_t l = 0; l < t.g0.size(); ++l) x.Copy(Scratch(rank, (uint64_t)l * blk + off), In(p.root, (uint64_t)t.g0.world(l) * blk + off), len, 0);
+        } else {
+            x.SyncGroup(t.g0.ranks, N_DATA, 1);
+            if (t.relay == p.root) x.Copy(Out(rank, off), In(p.root, (uint64_t)rank * blk + off), len, 1);
+            else x.Copy(Out(rank, off), Scratch(t.relay, (uint64_t)t.g0.me * blk + off), len, 1);
         }
     }
     x.SyncGroup(all.ranks, N_DONE);
@@ -716,6 +799,8 @@ HcclResult RunHostExecutorExt(HostWorld& w, uint32_t rank, int alg, const OpPara
         case HALG_AG_PIPELINE_MESH_MESH: r = PipelineAllGather(w, x, rank, p); break;
         case HALG_RS_PIPELINE_MESH_MESH: r = PipelineReduceScatter(w, x, rank, p); break;
         case HALG_BCAST_PIPELINE_MESH_MESH: r = PipelineBroadcast(w, x, rank, p); break;
+        case HALG_REDUCE_PIPELINE_MESH_NHR: r = PipelineReduce(w, x, rank, p); break;
+        case HALG_SCATTER_PIPELINE_MESH_MESH: r = PipelineScatter(w, x, rank, p); break;
         case HALG_AG_NB: {
             x.Copy(Out(rank, (uint64_t)rank * p.count * es), In(rank), p.count * es);
             NbAllGather(c, all, Work{BufKind::OUTPUT, 0, p.count * n, es});

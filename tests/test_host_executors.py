@@ -170,6 +170,27 @@ def test_pipeline_executors(algo_env, topo, n):
             verified(comms, lambda r, c: c.broadcast(bufs[r], root))
             assert "Pipeline" in comms[0].last_algorithm()
             assert all(np.all(b == 100 + root) for b in bufs)
+            counts = [(count * (r + 1)) // n + (r % 2) for r in range(n)]          # AllGatherV: uneven blocks with gaps
+            displs = [sum(counts[:r]) + 3 * r for r in range(n)]
+            agv_in = [np.random.default_rng(50 + r).integers(-99, 99, counts[r]).astype(np.int16) for r in range(n)]
+            agv_out = [np.full(displs[-1] + counts[-1], -777, np.int16) for _ in range(n)]
+            verified(comms, lambda r, c: c.all_gather_v(agv_in[r], agv_out[r], counts, displs))
+            assert comms[0].last_algorithm() == "HostAllGatherVPipelineMeshMesh", comms[0].last_algorithm()
+            for o in agv_out:
+                for r in range(n):
+                    assert np.array_equal(o[displs[r]:displs[r] + counts[r]], agv_in[r])
+                    assert np.all(o[displs[r] + counts[r]:displs[r] + counts[r] + 3][:3 if r < n - 1 else 0] == -777)
+            red_in = [np.random.default_rng(70 + r).standard_normal(count) for r in range(n)]
+            red_out = np.zeros(count, np.float64)
+            verified(comms, lambda r, c: c.reduce(red_in[r], red_out if r == root else None, root))
+            assert comms[0].last_algorithm() == "HostReducePipelineMeshNHR", comms[0].last_algorithm()
+            np.testing.assert_allclose(red_out, np.sum(np.stack(red_in), 0), rtol=1e-12, atol=1e-13)
+            sc_in = np.random.default_rng(90 + root).integers(-1000, 1000, count * n).astype(np.int32)
+            sc_out = [np.zeros(count, np.int32) for _ in range(n)]
+            verified(comms, lambda r, c: c.scatter(sc_in if r == root else None, sc_out[r], root))
+            assert comms[0].last_algorithm() == "HostScatterPipelineMeshMesh", comms[0].last_algorithm()
+            for r in range(n):
+                assert np.array_equal(sc_out[r], sc_in[r * count:(r + 1) * count])
     destroy(comms)
 
 
