@@ -650,6 +650,111 @@ HcclResult PipelineScatter(HostWorld& w, HostPrims& x, uint32_t rank, const OpPa
     return HCCL_SUCCESS;
 }
 
+// ---------------------------------------------------------------- Parallel (AllGather, ReduceScatter)
+// The reference's Parallel executors cut the data in two parts by the bandwidth of the two levels; part A takes the
+// levels bottom-up while part B takes them top-down at the same time, so that both link classes are busy from the
+// first step (CalcParallelDataSplitRatio, template_utils.h:809-826; ins_v2_all_gather_parallel_executor.cc and its
+// ReduceScatter twin).  Here part A runs on queue 0 with (first, second) = (my server, my column) and part B on queue 1
+// with (my column, my server); a column = the ranks that share my local index, one per server.  Both parts of a block
+// are element ranges [lo, hi) of it.
+
+// AllGather of the range [lo, hi) of every block: pull it from the members of `first`, wait for the members of
+// `second`, pull from each of them what it gathered from ITS `first` group.
+void TwoStageAllGather(HostPrims& x, const AlgHierarchy& h, uint32_t firstLevel, const Group& first, const Group& second, uint32_t rank, const OpParam& p,
+                       uint64_t lo, uint64_t hi, uint32_t queue, uint32_t notify)
+{
+    const uint32_t es = DataTypeSize(p.dtype);
+    if (hi <= lo) return;
+    const uint64_t len = (hi - lo) * es;
+    for (uint32_t k = 0; k < first.size(); ++k) {
+        const uint32_t j = first.world((first.me + k) % first.size());
+        x.Copy(Out(rank, ((uint64_t)j * p.count + lo) * es), In(j, lo * es), len, queue);
+    }
+    x.SyncGroup(second.ranks, notify, queue);
+    for (uint32_t k = 1; k < second.size(); ++k) {
+        const uint32_t peer = second.world((second.me + k) % second.size());
+        for (uint32_t j : *GroupOf(h, firstLevel, peer)) x.Copy(Out(rank, ((uint64_t)j * p.count + lo) * es), Out(peer, ((uint64_t)j * p.count + lo) * es), len, queue);
+    }
+}
+
+HcclResult ParallelAllGather(HostWorld& w, HostPrims& x, uint32_t rank, const OpParam& p)
+{
+    AlgHierarchy h;
+    CHK_RET(MatchTopo(w.Topo(rank), TopoMatchKind::TWO_LEVEL, &h));
+    const Group all = WholeGroup(w, rank);
+    x.SyncGroup(all.ranks, N_READY);
+    if (h.levels() < 2) {
+        Group self;
+        self.ranks = {rank};
+        self.me = 0;
+        AlgHierarchy flat;
+        flat.infos = {{all.ranks}};
+        TwoStageAllGather(x, flat, 0, all, self, rank, p, 0, p.count, 0, N_DATA);
+    } else {
+        Group g0, g1;
+        LevelGroup(h, 0, rank, &g0);
+        LevelGroup(h, 1, rank, &g1);
+        double sa, sb;
+        SplitShares(&sa, &sb);
+        const uint64_t a = BandwidthSplit(p.count, sa, sb, std::max<uint64_t>(1, 128 / DataTypeSize(p.dtype)));
+        TwoStageAllGather(x, h, 0, g0, g1, rank, p, 0, a, 0, N_DATA);
+        TwoStageAllGather(x, h, 1, g1, g0, rank, p, a, p.count, 1, N_AUX);
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+    return HCCL_SUCCESS;
+}
+
+// ReduceScatter of the range [lo, hi) of every block: for every member t of `second`, fold the range of ITS block
+// over the members of `first` into slot t of my staging region (at scratchOff); wait for the members of `second`; fold
+// my slot of theirs into the output.
+void TwoStageReduceScatter(HostPrims& x, const Group& first, const Group& second, uint32_t rank, const OpParam& p, uint64_t lo, uint64_t hi,
+                           uint64_t scratchOff, uint32_t queue, uint32_t notify)
+{
+    const uint32_t es = DataTypeSize(p.dtype);
+    if (hi <= lo) return;
+    const uint64_t len = (hi - lo) * es, blk = p.count * es;
+    for (uint32_t t = 0; t < second.size(); ++t) {
+        const uint32_t owner = second.world(t);
+        const Mem slot = Scratch(rank, scratchOff + (uint64_t)t * len);
+        x.Copy(slot, In(rank, (uint64_t)owner * blk + lo * es), len, queue);
+        for (uint32_t k = 1; k < first.size(); ++k) x.Reduce(slot, In(first.world((first.me + k) % first.size()), (uint64_t)owner * blk + lo * es), len, queue);
+    }
+    x.SyncGroup(second.ranks, notify, queue);
+    x.Copy(Out(rank, lo * es), Scratch(rank, scratchOff + (uint64_t)second.me * len), len, queue);
+    for (uint32_t k = 1; k < second.size(); ++k)
+        x.Reduce(Out(rank, lo * es), Scratch(second.world((second.me + k) % second.size()), scratchOff + (uint64_t)second.me * len), len, queue);
+}
+
+HcclResult ParallelReduceScatter(HostWorld& w, HostPrims& x, uint32_t rank, const OpParam& p)
+{
+    AlgHierarchy h;
+    CHK_RET(MatchTopo(w.Topo(rank), TopoMatchKind::TWO_LEVEL, &h));
+    const Group all = WholeGroup(w, rank);
+    const uint32_t es = DataTypeSize(p.dtype);
+    Group g0 = all, g1;
+    g1.ranks = {rank};
+    g1.me = 0;
+    uint64_t a = p.count;
+    if (h.levels() >= 2) {
+        LevelGroup(h, 0, rank, &g0);
+        LevelGroup(h, 1, rank, &g1);
+        double sa, sb;
+        SplitShares(&sa, &sb);
+        a = BandwidthSplit(p.count, sa, sb, std::max<uint64_t>(1, 128 / es));
+    }
+    const uint64_t needA = (uint64_t)g1.size() * a * es, needB = (uint64_t)g0.size() * (p.count - a) * es;
+    if (needA + needB > w.scratchBytes()) {
+        HCCL_ERROR("host engine: parallel ReduceScatter stages %llu bytes, the scratch buffer has %llu", (unsigned long long)(needA + needB),
+                   (unsigned long long)w.scratchBytes());
+        return HCCL_E_MEMORY;
+    }
+    x.SyncGroup(all.ranks, N_READY);
+    TwoStageReduceScatter(x, g0, g1, rank, p, 0, a, 0, 0, N_DATA);
+    if (h.levels() >= 2) TwoStageReduceScatter(x, g1, g0, rank, p, a, p.count, needA, 1, N_AUX);
+    x.SyncGroup(all.ranks, N_DONE);
+    return HCCL_SUCCESS;
+}
+
 // ---------------------------------------------------------------- tree executor (AllReduce)
 struct TreeRun {
     HostWorld& w;
@@ -800,6 +905,8 @@ HcclResult RunHostExecutorExt(HostWorld& w, uint32_t rank, int alg, const OpPara
         case HALG_RS_PIPELINE_MESH_MESH: r = PipelineReduceScatter(w, x, rank, p); break;
         case HALG_BCAST_PIPELINE_MESH_MESH: r = PipelineBroadcast(w, x, rank, p); break;
         case HALG_REDUCE_PIPELINE_MESH_NHR: r = PipelineReduce(w, x, rank, p); break;
+        case HALG_AG_PARALLEL_MESH_MESH: r = ParallelAllGather(w, x, rank, p); break;
+        case HALG_RS_PARALLEL_MESH_MESH: r = ParallelReduceScatter(w, x, rank, p); break;
         case HALG_SCATTER_PIPELINE_MESH_MESH: r = PipelineScatter(w, x, rank, p); break;
         case HALG_AG_NB: {
             x.Copy(Out(rank, (uint64_t)rank * p.count * es), In(rank), p.count * es);

@@ -298,8 +298,7 @@ def test_hierarchical_executors(algo_env, topo, n, algo):
     comms[0].trace_begin()
     run_ranks(comms, lambda r, c: c.reduce_scatter(rs_in[r], rs_out[r]))
     assert comms[0].trace_verify().startswith("OK")
-    if "pipeline" not in algo:
-        assert "Sequence" in comms[0].last_algorithm(), comms[0].last_algorithm()
+    assert ("Parallel" if "pipeline" in algo else "Sequence") in comms[0].last_algorithm(), comms[0].last_algorithm()
     ref = np.sum(np.stack(rs_in).astype(np.float64), 0)
     for r in range(n):
         np.testing.assert_allclose(rs_out[r], ref[r * 64:(r + 1) * 64], rtol=2e-6, atol=2e-5)
@@ -307,8 +306,7 @@ def test_hierarchical_executors(algo_env, topo, n, algo):
     comms[0].trace_begin()
     run_ranks(comms, lambda r, c: c.all_gather(rs_out[r], ag_out[r]))
     assert comms[0].trace_verify().startswith("OK")
-    if "pipeline" not in algo:
-        assert "Sequence" in comms[0].last_algorithm(), comms[0].last_algorithm()
+    assert ("Parallel" if "pipeline" in algo else "Sequence") in comms[0].last_algorithm(), comms[0].last_algorithm()
     for o in ag_out:
         np.testing.assert_allclose(o, ref, rtol=2e-6, atol=2e-5)
     destroy(comms)

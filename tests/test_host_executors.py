@@ -194,6 +194,37 @@ def test_pipeline_executors(algo_env, topo, n):
     destroy(comms)
 
 
+@pytest.mark.parametrize("ratio", [None, "1,0", "0,1", "3,1"])
+def test_parallel_all_gather_and_reduce_scatter(algo_env, ratio):
+    """Parallel executors: part A of every block goes server first, then column; part B column first, then server, on
+    a second queue (reference: CalcParallelDataSplitRatio, template_utils.h:809-826).  Every split ratio, parts that are
+    empty included, gives the same values; the trace verifier sees no race between the two parts."""
+    if ratio:
+        os.environ["HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO"] = ratio
+    try:
+        for topo, n in ((TWO_BY_FOUR, 8), (THREE_BY_TWO, 6)):
+            comms = make(n, topo=topo, algo="level0:NA;level1:pipeline")
+            for count in (1, 64, 20011):
+                ag_in = [np.random.default_rng(r).integers(-9, 9, count).astype(np.int32) for r in range(n)]
+                ag_out = [np.zeros(count * n, np.int32) for _ in range(n)]
+                verified(comms, lambda r, c: c.all_gather(ag_in[r], ag_out[r]))
+                assert comms[0].last_algorithm() == "HostAllGatherParallelMeshMesh", comms[0].last_algorithm()
+                for o in ag_out:
+                    assert np.array_equal(o, np.concatenate(ag_in))
+                rs_in = [np.random.default_rng(40 + r).standard_normal(count * n) for r in range(n)]
+                rs_out = [np.zeros(count, np.float64) for _ in range(n)]
+                verified(comms, lambda r, c: c.reduce_scatter(rs_in[r], rs_out[r]))
+                assert comms[0].last_algorithm() == "HostReduceScatterParallelMeshMesh", comms[0].last_algorithm()
+                ref = np.sum(np.stack(rs_in), 0)
+                for r in range(n):
+                    np.testing.assert_allclose(rs_out[r], ref[r * count:(r + 1) * count], rtol=1e-12, atol=1e-13)
+                assert all(np.array_equal(rs_in[r], np.random.default_rng(40 + r).standard_normal(count * n)) for r in range(n))   # inputs intact
+            destroy(comms)
+    finally:
+        os.environ.pop("HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO", None)
+        lib.HcclReloadEnvConfig()
+
+
 @pytest.mark.parametrize("topo,n", [(TWO_PODS, 8), ("[[[0,1,2],[3,4,5]],[[6,7,8],[9,10,11]],[[12,13,14],[15,16,17]]]", 18)])
 def test_three_level_pipeline_all_reduce(algo_env, topo, n):
     """Servers, pods and the level above them: five pipelined stages (mesh ReduceScatter, NHR ReduceScatter, NHR
