@@ -170,6 +170,54 @@ void ConcurrentAllGather(HostWorld& w, HostPrims& x, const Group& all, uint32_t 
     x.SyncGroup(all.ranks, N_DONE);
 }
 
+// Broadcast: both parts are scattered from the root (member i takes slice i of a part), then part A is gathered over
+// the mesh while part B is gathered by NHR on the second queue.
+void ConcurrentBroadcast(HostWorld& w, HostPrims& x, const Group& all, uint32_t rank, const OpParam& p)
+{
+    const uint32_t n = all.size(), es = DataTypeSize(p.dtype);
+    double sa, sb;
+    SplitShares(&sa, &sb);
+    const uint64_t a = BandwidthSplit(p.count, sa, sb, std::max<uint64_t>(1, 128 / es));
+    const Work part[2] = {Work{BufKind::OUTPUT, 0, a, es}, Work{BufKind::OUTPUT, a * es, p.count - a, es}};
+    x.SyncGroup(all.ranks, N_READY);
+    for (uint32_t q = 0; q < 2 && rank != p.root; ++q) {
+        uint64_t b, e;
+        Slice(part[q], n, rank, &b, &e);
+        if (e > b) x.Copy(Out(rank, part[q].base + b * es), Out(p.root, part[q].base + b * es), (e - b) * es, q);
+    }
+    x.SyncGroup(all.ranks, N_DATA);
+    Ctx ca{w, x, 0, 0, 0};
+    Ctx cb{w, x, 1, 0, w.scratchBytes()};
+    if (part[0].count) AllGatherBy(Fam::MESH, ca, all, part[0]);
+    if (part[1].count) AllGatherBy(Fam::NHR, cb, all, part[1]);
+}
+
+// Reduce: ReduceScatter of part A over the mesh and of part B by NHR on a copy in the upper half of the staging
+// buffer, then the root collects the slices of both parts from their holders.
+void ConcurrentReduce(HostWorld& w, HostPrims& x, const Group& all, uint32_t rank, const OpParam& p)
+{
+    const uint32_t n = all.size(), es = DataTypeSize(p.dtype);
+    double sa, sb;
+    SplitShares(&sa, &sb);
+    const uint64_t a = BandwidthSplit(p.count, sa, sb, std::max<uint64_t>(1, 128 / es));
+    const uint64_t wOff = w.scratchBytes() / 2;
+    x.Copy(Scratch(rank, wOff), In(rank), Bytes(p));
+    const Work part[2] = {Work{BufKind::SCRATCH, wOff, a, es}, Work{BufKind::SCRATCH, wOff + a * es, p.count - a, es}};
+    Ctx ca{w, x, 0, 0, 0};
+    Ctx cb{w, x, 1, 0, w.scratchBytes() / 2};
+    if (part[0].count) MeshReduceScatter(ca, all, part[0]);
+    if (part[1].count) NhrReduceScatter(cb, all, part[1]);
+    x.SyncGroup(all.ranks, N_LEVEL);
+    for (uint32_t q = 0; q < 2 && rank == p.root; ++q) {
+        for (uint32_t j = 0; j < n; ++j) {
+            uint64_t b, e;
+            Slice(part[q], n, j, &b, &e);
+            if (e > b) x.Copy(Out(rank, part[q].base - wOff + b * es), Scratch(j, part[q].base + b * es), (e - b) * es, q);
+        }
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+}
+
 // ---------------------------------------------------------------- mesh with a detour (Z-axis detour)
 // The reference's mesh templates with a detour (ins_temp_all_gather_mesh_1D_Z_axis_detour.cc and the ReduceScatter /
 // Scatter twins) move every pair's slice over TWO channels of the same pair: the direct mesh link and a second channel
@@ -901,6 +949,8 @@ HcclResult RunHostExecutorExt(HostWorld& w, uint32_t rank, int alg, const OpPara
         case HALG_SCATTER_MESH_DETOUR: DetourScatter(w, x, all, rank, p); break;
         case HALG_RS_CONCURRENT_MESH_NHR: ConcurrentReduceScatter(w, x, all, rank, p); break;
         case HALG_AG_CONCURRENT_MESH_NHR: ConcurrentAllGather(w, x, all, rank, p); break;
+        case HALG_BCAST_CONCURRENT_MESH_NHR: ConcurrentBroadcast(w, x, all, rank, p); break;
+        case HALG_REDUCE_CONCURRENT_MESH_NHR: ConcurrentReduce(w, x, all, rank, p); break;
         case HALG_AG_PIPELINE_MESH_MESH: r = PipelineAllGather(w, x, rank, p); break;
         case HALG_RS_PIPELINE_MESH_MESH: r = PipelineReduceScatter(w, x, rank, p); break;
         case HALG_BCAST_PIPELINE_MESH_MESH: r = PipelineBroadcast(w, x, rank, p); break;

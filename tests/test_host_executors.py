@@ -123,6 +123,16 @@ def test_concurrent_executors(algo_env, n):
         assert "Concurrent" in comms[0].last_algorithm()
         for o in ag_out:
             assert np.array_equal(o, np.concatenate(ag_in))
+        for root in (0, n - 1):
+            bufs = [np.full(count, 100 + r, np.int16) for r in range(n)]
+            verified(comms, lambda r, c: c.broadcast(bufs[r], root))
+            assert comms[0].last_algorithm() == "HostBroadcastConcurrentMeshNHR", comms[0].last_algorithm()
+            assert all(np.all(b == 100 + root) for b in bufs)
+            red_in = [np.random.default_rng(70 + r).standard_normal(count) for r in range(n)]
+            red_out = np.zeros(count, np.float64)
+            verified(comms, lambda r, c: c.reduce(red_in[r], red_out if r == root else None, root))
+            assert comms[0].last_algorithm() == "HostReduceConcurrentMeshNHR", comms[0].last_algorithm()
+            np.testing.assert_allclose(red_out, np.sum(np.stack(red_in), 0), rtol=1e-12, atol=1e-13)
     destroy(comms)
 
 
