@@ -270,6 +270,7 @@ HcclResult CommImpl::Resume()
     if (bs) CHK_RET(bs->Barrier());
     ++generation;
     if (plans) plans->Clear();
+    shapeSeen.clear();
     ctx.Clear();
     if (selector) selector.reset(new SelectorState());
     status_.store(HCCL_COMM_STATUS_READY);

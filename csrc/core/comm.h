@@ -104,6 +104,7 @@ public:
     std::unique_ptr<PlanCache> plans;
     std::unique_ptr<TopoInfo> topo;
     bool firstOpChecked[HCCL_CMD_MAX] = {false};
+    std::map<uint64_t, uint32_t> shapeSeen;   // call signature -> the local buffer facts it was last agreed with
     std::shared_ptr<MoeState> moe;  // scratch of the MoE dispatch / combine kernels, created on first use
     std::shared_ptr<Mc2State> mc2;  // resources of the fused matmul kernels, created on first use
     HostRank* hostComm = nullptr;  // non-null: a host-engine communicator (ranks are host threads)

@@ -673,7 +673,24 @@ HcclResult AgreeOnCallShape(CommImpl* c, const OpParam& p, uint64_t signature, u
     if (!c->bs || !IsCollective(p.op) || !GetEnvConfig().callShapeAgree) return HCCL_SUCCESS;
     ShapeRecord mine = {signature, localFlags, 0};
     std::vector<ShapeRecord> all((size_t)c->nRanks);
-    CHK_RET(c->bs->AllGather(&mine, all.data(), sizeof(mine)));
+    // A signature met again with other local facts: the peers take part in this exchange only if their facts changed
+    // too (ranks that still have the plan reuse it silently).  Say so before waiting, and again if the wait fails.
+    const auto seen = c->shapeSeen.find(signature);
+    const bool again = seen != c->shapeSeen.end() && seen->second != localFlags;
+    if (again)
+        HCCL_WARNING("comm %s rank %d: %s met again with other buffer facts (flags %#x, were %#x); the exchange completes only if every rank's "
+                     "registration / alignment / aliasing changed with this call", c->name.c_str(), c->rank, CmdName(p.op), localFlags, seen->second);
+    const HcclResult xr = c->bs->AllGather(&mine, all.data(), sizeof(mine));
+    if (xr != HCCL_SUCCESS) {
+        if (again)
+            HCCL_ERROR("comm %s rank %d: the buffer facts of %s changed on this rank only (flags %#x, were %#x): its peers reused their plan and did "
+                       "not join the exchange.  Change registration, alignment and in-place use on all ranks together, or set "
+                       "HCCL_CALL_SHAPE_AGREE=0 when every rank is known to pass equivalent buffers", c->name.c_str(), c->rank, CmdName(p.op), localFlags,
+                       seen->second);
+        return xr;
+    }
+    if (c->shapeSeen.size() >= 16384) c->shapeSeen.clear();      // only feeds the diagnosis above
+    c->shapeSeen[signature] = localFlags;
     for (int r = 0; r < c->nRanks; ++r) {
         if (all[(size_t)r].signature != signature) {
             HCCL_ERROR("comm %s: rank %d and rank %d are not in the same operation (%s here): operator, data type, reduce op, root or count differ",
