@@ -106,6 +106,8 @@ const char* AlgoTypeName(AlgoType t)
         case AlgoType::TREE: return "tree";
         case AlgoType::DETOUR: return "detour";
         case AlgoType::SERIAL: return "serial";
+        case AlgoType::TWO_DIE: return "2die";
+        case AlgoType::MESH_CONCUR: return "meshconcur";
     }
     return "?";
 }
@@ -120,7 +122,7 @@ bool ParseAlgoType(const std::string& s, AlgoType* out)
         {"pairwise", AlgoType::PAIRWISE}, {"fullmesh", AlgoType::MESH}, {"mesh", AlgoType::MESH},
         {"oneshot", AlgoType::ONESHOT}, {"twoshot", AlgoType::TWOSHOT}, {"nvls", AlgoType::NVLS},
         {"ll", AlgoType::LL}, {"concurrent", AlgoType::CONCURRENT}, {"omnipipe", AlgoType::OMNIPIPE},
-        {"hier", AlgoType::HIER}, {"tree", AlgoType::TREE}, {"detour", AlgoType::DETOUR}, {"serial", AlgoType::SERIAL},
+        {"hier", AlgoType::HIER}, {"tree", AlgoType::TREE}, {"detour", AlgoType::DETOUR}, {"serial", AlgoType::SERIAL}, {"2die", AlgoType::TWO_DIE}, {"meshconcur", AlgoType::MESH_CONCUR},
     };
     auto it = k.find(l);
     if (it == k.end()) return false;

@@ -18,7 +18,7 @@ namespace hccl {
 // Algorithm family names accepted by HCCL_ALGO (reference grammar:
 // docs/en/user_guide/hccl_env/HCCL_ALGO.md; parser alg_parse.cc).
 enum class AlgoType : int { DEFAULT = 0, NA, RING, HD_R, NHR, NHR_V1, NB, AHC, PIPELINE, PAIRWISE, MESH, ONESHOT, TWOSHOT, NVLS, LL,
-                            CONCURRENT, OMNIPIPE, HIER, TREE, DETOUR, SERIAL };   // executor families beyond the reference's HCCL_ALGO names
+                            CONCURRENT, OMNIPIPE, HIER, TREE, DETOUR, SERIAL, TWO_DIE, MESH_CONCUR };   // executor families beyond the reference's HCCL_ALGO names
 const char* AlgoTypeName(AlgoType t);
 bool ParseAlgoType(const std::string& s, AlgoType* out);
 

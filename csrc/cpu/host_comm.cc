@@ -362,6 +362,8 @@ void RegisterHostAlgorithms()
     auto Four = [](double) { return 4.0; };
     Reg({"HostAllReduceConcurrentMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, true, TwoL, ar, false});
     Reg({"HostReduceScatterConcurrentMeshNHR", HCCL_CMD_REDUCE_SCATTER, HALG_RS_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, true, L, rs, false});
+    Reg({"HostAllReduceSequence2DieMeshMesh", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_2DIE_MESH_MESH, "sequence2die", {"Mesh2Die", "Mesh2Die"}, AlgoType::TWO_DIE, 1, true, Four, ar, false});
+    Reg({"HostAllReduceSoleMeshConcur", HCCL_CMD_ALLREDUCE, HALG_AR_SOLE_MESH_CONCUR, "twoshotsole", {"MeshConcur", "MeshConcur"}, AlgoType::MESH_CONCUR, 1, true, Four, ar, false});
     Reg({"HostBroadcastConcurrentMeshNHR", HCCL_CMD_BROADCAST, HALG_BCAST_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, false, L1, ar, true});
     Reg({"HostReduceConcurrentMeshNHR", HCCL_CMD_REDUCE, HALG_REDUCE_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, true, L1, ar, false});
     Reg({"HostAllGatherConcurrentMeshNHR", HCCL_CMD_ALLGATHER, HALG_AG_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, false, L, rs, true});

@@ -170,6 +170,62 @@ void ConcurrentAllGather(HostWorld& w, HostPrims& x, const Group& all, uint32_t 
     x.SyncGroup(all.ranks, N_DONE);
 }
 
+// AllReduce as ReduceScatter then AllGather over a mesh whose peers sit behind two sets of links (the reference's
+// two-die sequence, ins_v2_allreduce_sequence2die_executor.cc:146-343 with the 2-die mesh templates: a package of two
+// dies reaches half of its peers through each die's ports).  The peers in my half of the group are served on queue
+// 0, those in the other half on queue 1, so both link sets carry data in both phases.  The second queue folds into an
+// accumulator of its own in the staging buffer (two queues must not fold into one destination), which joins my slice
+// at the end of the phase; the fold order is fixed.  Slices are the flat two-shot slices over all ranks.
+HcclResult TwoDieAllReduce(HostWorld& w, HostPrims& x, const Group& all, const Work& wk)
+{
+    const uint32_t n = all.size();
+    if (n == 1) return HCCL_SUCCESS;
+    const uint32_t half = (n + 1) / 2;
+    auto queueOf = [&](uint32_t j) { return (j < half) == (all.me < half) ? 0u : 1u; };
+    uint64_t b, e;
+    Slice(wk, n, all.me, &b, &e);
+    const uint64_t len = (e - b) * wk.es;
+    if (len > w.scratchBytes()) return HCCL_E_MEMORY;
+    const uint32_t me = all.world(all.me);
+    x.SyncGroup(all.ranks, N_READY);
+    bool first = true;
+    for (uint32_t k = 1; k < n; ++k) {
+        const uint32_t j = (all.me + k) % n;
+        if (queueOf(j) == 0) { x.Reduce(wk.At(me, b), wk.At(all.world(j), b), len, 0); continue; }
+        if (first) x.Copy(Scratch(me, 0), wk.At(all.world(j), b), len, 1);
+        else x.Reduce(Scratch(me, 0), wk.At(all.world(j), b), len, 1);
+        first = false;
+    }
+    if (!first) x.Reduce(wk.At(me, b), Scratch(me, 0), len, 0);
+    x.SyncGroup(all.ranks, N_DATA);
+    for (uint32_t k = 1; k < n; ++k) {
+        const uint32_t j = (all.me + k) % n;
+        uint64_t jb, je;
+        Slice(wk, n, j, &jb, &je);
+        x.Copy(wk.At(me, jb), wk.At(all.world(j), jb), (je - jb) * wk.es, queueOf(j));
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+    return HCCL_SUCCESS;
+}
+
+// AllReduce, two-shot over two link sets at once (the reference's AicpuAllReduceSoleMeshConcur,
+// ins_v2_all_reduce_two_shot_sole_executor.cc:305-393: ReduceScatter, then AllGather, each with a mesh template
+// that spans both link sets): the data is split by the bandwidth of the two sets and each part runs the mesh
+// two-shot on its own queue.
+void MeshConcurAllReduce(HostWorld& w, HostPrims& x, const Group& all, const Work& wk)
+{
+    double sa, sb;
+    SplitShares(&sa, &sb);
+    const uint64_t a = BandwidthSplit(wk.count, sa, sb, std::max<uint64_t>(1, 128 / wk.es));
+    const Work A{wk.buf, wk.base, a, wk.es}, B{wk.buf, wk.base + a * wk.es, wk.count - a, wk.es};
+    Ctx ca{w, x, 0, 0, 0};
+    Ctx cb{w, x, 1, 0, 0};
+    if (A.count) MeshReduceScatter(ca, all, A);
+    if (B.count) MeshReduceScatter(cb, all, B);
+    if (A.count) MeshAllGather(ca, all, A);
+    if (B.count) MeshAllGather(cb, all, B);
+}
+
 // Broadcast: both parts are scattered from the root (member i takes slice i of a part), then part A is gathered over
 // the mesh while part B is gathered by NHR on the second queue.
 void ConcurrentBroadcast(HostWorld& w, HostPrims& x, const Group& all, uint32_t rank, const OpParam& p)
@@ -935,12 +991,15 @@ HcclResult RunHostExecutorExt(HostWorld& w, uint32_t rank, int alg, const OpPara
     Ctx c{w, x, 0, 0, w.scratchBytes()};
     HcclResult r = HCCL_SUCCESS;
     switch (alg) {
-        case HALG_AR_CONCURRENT_MESH_NHR: case HALG_AR_PIPELINE_MESH_NHR: case HALG_AR_PIPELINE3_MESH_NHR_NHR: case HALG_AR_TREE: {
+        case HALG_AR_CONCURRENT_MESH_NHR: case HALG_AR_PIPELINE_MESH_NHR: case HALG_AR_PIPELINE3_MESH_NHR_NHR: case HALG_AR_TREE:
+        case HALG_AR_SEQ_2DIE_MESH_MESH: case HALG_AR_SOLE_MESH_CONCUR: {
             x.Copy(Out(rank), In(rank), Bytes(p));
             const Work wk{BufKind::OUTPUT, 0, p.count, es};
             if (alg == HALG_AR_CONCURRENT_MESH_NHR) ConcurrentAllReduce(w, x, all, wk);
             else if (alg == HALG_AR_PIPELINE_MESH_NHR) r = PipelineAllReduce(w, x, rank, wk);
             else if (alg == HALG_AR_PIPELINE3_MESH_NHR_NHR) r = Pipeline3AllReduce(w, x, rank, wk);
+            else if (alg == HALG_AR_SEQ_2DIE_MESH_MESH) r = TwoDieAllReduce(w, x, all, wk);
+            else if (alg == HALG_AR_SOLE_MESH_CONCUR) MeshConcurAllReduce(w, x, all, wk);
             else r = TreeAllReduce(w, x, rank, wk);
             break;
         }

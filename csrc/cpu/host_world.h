@@ -193,6 +193,7 @@ enum HostAlg : int {
     HALG_RS_SEQ_MESH_RING, HALG_RS_SEQ_MESH_RHD, HALG_AG_SEQ_MESH_RING, HALG_AG_SEQ_MESH_RHD,
     HALG_A2A_SERIAL, HALG_REDUCE_PIPELINE_MESH_NHR, HALG_SCATTER_PIPELINE_MESH_MESH,
     HALG_AG_PARALLEL_MESH_MESH, HALG_RS_PARALLEL_MESH_MESH, HALG_BCAST_CONCURRENT_MESH_NHR, HALG_REDUCE_CONCURRENT_MESH_NHR,
+    HALG_AR_SEQ_2DIE_MESH_MESH, HALG_AR_SOLE_MESH_CONCUR,
     HALG_COUNT
 };
 // Runs host algorithm `alg` for this rank; the world is already inside Enter().

@@ -136,6 +136,25 @@ def test_concurrent_executors(algo_env, n):
     destroy(comms)
 
 
+@pytest.mark.parametrize("n", [2, 3, 5, 8])
+@pytest.mark.parametrize("algo,name", [("allreduce=level0:2die", "HostAllReduceSequence2DieMeshMesh"), ("allreduce=level0:meshconcur", "HostAllReduceSoleMeshConcur")])
+def test_all_reduce_over_two_link_sets(algo_env, n, algo, name):
+    """Two-shot AllReduce whose peers (two-die sequence) or whose data (mesh over both link sets at once) are divided
+    between two queues; odd rank counts leave the halves unequal; the verifier sees no two queues fold into one place."""
+    comms = make(n, algo=algo)
+    for count in (1, 7, 4099, 100003):
+        ins = [np.random.default_rng(r).standard_normal(count).astype(np.float32) for r in range(n)]
+        outs = [np.zeros(count, np.float32) for _ in range(n)]
+        verified(comms, lambda r, c: c.all_reduce(ins[r], outs[r]))
+        assert comms[0].last_algorithm() == name, comms[0].last_algorithm()
+        ref = np.sum(np.stack(ins).astype(np.float64), 0)
+        for o in outs:
+            np.testing.assert_allclose(o, ref, rtol=2e-6, atol=2e-5)
+        for o in outs[1:]:
+            assert np.array_equal(o, outs[0])
+    destroy(comms)
+
+
 def test_concurrent_split_follows_the_ratio_variable(algo_env):
     os.environ["HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO"] = "1,0"
     try:
