@@ -27,12 +27,13 @@ def restore_algo_preference():
 
 
 PREFS = [None, "level0:NA;level1:ring", "level0:NA;level1:NHR", "level0:NA;level1:H-D_R", "level0:NA;level1:fullmesh", "level0:NA;level1:NB",
-         "level0:NA;level1:concurrent", "level0:NA;level1:oneshot"]
+         "level0:NA;level1:concurrent", "level0:NA;level1:oneshot", "level0:NA;level1:serial", "level0:NA;level1:2die",
+         "level0:NA;level1:meshconcur", "level0:NA;level1:detour"]
 DTYPES = [np.int32, np.int64, np.float64]
 FOLD = {ReduceOp.SUM: np.add, ReduceOp.MAX: np.maximum, ReduceOp.MIN: np.minimum}
 
 
-@settings(max_examples=30, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@settings(max_examples=80, deadline=None, suppress_health_check=[HealthCheck.too_slow])
 @given(n=st.integers(2, 7), count=st.integers(1, 1500), pref=st.sampled_from(PREFS), dtype=st.sampled_from(DTYPES),
        op=st.sampled_from(list(FOLD)), seed=st.integers(0, 1000))
 def test_allreduce_any_shape(n, count, pref, dtype, op, seed):
@@ -52,7 +53,7 @@ def test_allreduce_any_shape(n, count, pref, dtype, op, seed):
         assert np.array_equal(o, want)
 
 
-@settings(max_examples=30, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@settings(max_examples=80, deadline=None, suppress_health_check=[HealthCheck.too_slow])
 @given(n=st.integers(2, 7), count=st.integers(1, 700), pref=st.sampled_from(PREFS), kind=st.sampled_from(["ag", "rs", "bc", "sc", "a2a", "red"]),
        root=st.integers(0, 6), seed=st.integers(0, 1000))
 def test_other_operators_any_shape(n, count, pref, kind, root, seed):
