@@ -375,6 +375,9 @@ void RegisterHostAlgorithms()
     Reg({"HostBroadcastPipelineMeshMesh", HCCL_CMD_BROADCAST, HALG_BCAST_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, false, Four, ar, true});
     Reg({"HostAllGatherParallelMeshMesh", HCCL_CMD_ALLGATHER, HALG_AG_PARALLEL_MESH_MESH, "parallel", {"Mesh", "Mesh"}, AlgoType::PIPELINE, 2, false, Four, rs, true});
     Reg({"HostReduceScatterParallelMeshMesh", HCCL_CMD_REDUCE_SCATTER, HALG_RS_PARALLEL_MESH_MESH, "parallel", {"Mesh", "Mesh"}, AlgoType::PIPELINE, 2, true, Four, rs, false});
+    Reg({"HostBroadcastParallelMeshMesh", HCCL_CMD_BROADCAST, HALG_BCAST_PARALLEL_MESH_MESH, "parallel", {"Mesh", "Mesh"}, AlgoType::PIPELINE, 2, false, Four, ar, true});
+    Reg({"HostScatterParallelMeshMesh", HCCL_CMD_SCATTER, HALG_SCATTER_PARALLEL_MESH_MESH, "parallel", {"Mesh", "Mesh"}, AlgoType::PIPELINE, 2, false, Four, rs, true});
+    Reg({"HostReduceParallelMeshNHR", HCCL_CMD_REDUCE, HALG_REDUCE_PARALLEL_MESH_NHR, "parallel", {"Mesh", "NHR"}, AlgoType::PIPELINE, 2, true, TwoL1, ar, false});
     Reg({"HostAllGatherVPipelineMeshMesh", HCCL_CMD_ALLGATHER_V, HALG_AG_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, false, Four, rs, true});
     Reg({"HostReducePipelineMeshNHR", HCCL_CMD_REDUCE, HALG_REDUCE_PIPELINE_MESH_NHR, "pipeline", {"Mesh", "NHR"}, AlgoType::OMNIPIPE, 2, true, TwoL1, ar, false});
     Reg({"HostScatterPipelineMeshMesh", HCCL_CMD_SCATTER, HALG_SCATTER_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, false, Four, rs, true});

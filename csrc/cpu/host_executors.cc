@@ -859,6 +859,123 @@ HcclResult ParallelReduceScatter(HostWorld& w, HostPrims& x, uint32_t rank, cons
     return HCCL_SUCCESS;
 }
 
+// Parallel forms of the rooted operators (reference: ins_v2_broadcast_parallel_executor.cc, ins_v2_reduce_parallel_
+// executor.cc, ins_v2_scatter_parallel_executor.cc): part A crosses the servers first and spreads inside them second,
+// part B the other way round, on the second queue.  "Column" = the ranks that share a local index, one per server;
+// the column head is its member in the root's server.
+uint64_t ParallelSplit(const TwoLevel& t, uint64_t count, uint32_t es)
+{
+    if (t.flat) return count;
+    double sa, sb;
+    SplitShares(&sa, &sb);
+    return BandwidthSplit(count, sa, sb, std::max<uint64_t>(1, 128 / es));
+}
+
+HcclResult ParallelBroadcast(HostWorld& w, HostPrims& x, uint32_t rank, const OpParam& p)
+{
+    TwoLevel t;
+    CHK_RET(MatchTwoLevel(w, rank, p.root, &t));
+    const uint32_t es = DataTypeSize(p.dtype);
+    const uint64_t a = ParallelSplit(t, p.count, es), lenA = a * es, lenB = (p.count - a) * es;
+    const Group all = WholeGroup(w, rank);
+    x.SyncGroup(all.ranks, N_READY);
+    if (lenA) {
+        // root -> the member of every server with the root's local index -> its server
+        if (!t.flat && rank == t.relay && rank != p.root) x.Copy(Out(rank), Out(p.root), lenA, 0);
+        x.SyncGroup(t.g0.ranks, N_DATA, 0);
+        if (rank != t.relay) x.Copy(Out(rank), Out(t.relay), lenA, 0);
+    }
+    if (lenB) {
+        // root -> its own server -> every member's column
+        const bool rootServer = t.g1.me == t.rootServer;
+        const uint32_t head = t.g1.world(t.rootServer);
+        if (rootServer && rank != p.root) x.Copy(Out(rank, lenA), Out(p.root, lenA), lenB, 1);
+        x.SyncGroup(t.g1.ranks, N_AUX, 1);
+        if (!rootServer) x.Copy(Out(rank, lenA), Out(head, lenA), lenB, 1);
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+    return HCCL_SUCCESS;
+}
+
+HcclResult ParallelScatter(HostWorld& w, HostPrims& x, uint32_t rank, const OpParam& p)
+{
+    TwoLevel t;
+    CHK_RET(MatchTwoLevel(w, rank, p.root, &t));
+    const uint32_t es = DataTypeSize(p.dtype);
+    const uint64_t blk = Bytes(p);
+    const uint64_t a = ParallelSplit(t, p.count, es), lenA = a * es, lenB = (p.count - a) * es;
+    const uint64_t offB = (uint64_t)t.g0.size() * lenA;                 // part B's staging slots follow part A's
+    if (offB + (uint64_t)t.g1.size() * lenB > w.scratchBytes()) {
+        HCCL_ERROR("host engine: parallel Scatter stages %llu bytes, the scratch buffer has %llu", (unsigned long long)(offB + t.g1.size() * lenB),
+                   (unsigned long long)w.scratchBytes());
+        return HCCL_E_MEMORY;
+    }
+    const Group all = WholeGroup(w, rank);
+    x.SyncGroup(all.ranks, N_READY);
+    if (lenA) {
+        // the blocks of a server go to its member with the root's local index, which hands them on
+        if (rank == t.relay && rank != p.root)
+            for (uint32_t l = 0; l < t.g0.size(); ++l) x.Copy(Scratch(rank, (uint64_t)l * lenA), In(p.root, (uint64_t)t.g0.world(l) * blk), lenA, 0);
+        x.SyncGroup(t.g0.ranks, N_DATA, 0);
+        if (t.relay == p.root) x.Copy(Out(rank), In(p.root, (uint64_t)rank * blk), lenA, 0);
+        else x.Copy(Out(rank), Scratch(t.relay, (uint64_t)t.g0.me * lenA), lenA, 0);
+    }
+    if (lenB) {
+        // the blocks of a column go to its head in the root's server, which hands them on
+        const bool rootServer = t.g1.me == t.rootServer;
+        const uint32_t head = t.g1.world(t.rootServer);
+        if (rootServer && rank != p.root)
+            for (uint32_t s = 0; s < t.g1.size(); ++s) x.Copy(Scratch(rank, offB + (uint64_t)s * lenB), In(p.root, (uint64_t)t.g1.world(s) * blk + lenA), lenB, 1);
+        x.SyncGroup(t.g1.ranks, N_AUX, 1);
+        if (head == p.root) x.Copy(Out(rank, lenA), In(p.root, (uint64_t)rank * blk + lenA), lenB, 1);
+        else x.Copy(Out(rank, lenA), Scratch(head, offB + (uint64_t)t.g1.me * lenB), lenB, 1);
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+    return HCCL_SUCCESS;
+}
+
+// Reduce on a copy in the upper half of the staging buffer: part A = mesh ReduceScatter in the server, NHR
+// ReduceScatter along the column; part B = NHR along the column first, mesh in the server second; the root collects
+// the pieces of both parts from their holders.  One loop handles at most a quarter of the staging buffer (the two
+// parts' templates stage side by side in the lower half).
+HcclResult ParallelReduce(HostWorld& w, HostPrims& x, uint32_t rank, const OpParam& p)
+{
+    TwoLevel t;
+    CHK_RET(MatchTwoLevel(w, rank, p.root, &t));
+    const uint32_t es = DataTypeSize(p.dtype);
+    const uint64_t wOff = w.scratchBytes() / 2, quarter = (w.scratchBytes() / 4) & ~(uint64_t)127;
+    if (Bytes(p) > quarter) return HCCL_E_MEMORY;
+    x.Copy(Scratch(rank, wOff), In(rank), Bytes(p));
+    const uint64_t a = ParallelSplit(t, p.count, es);
+    const Work A{BufKind::SCRATCH, wOff, a, es}, B{BufKind::SCRATCH, wOff + a * es, p.count - a, es};
+    const uint32_t L = t.g0.size(), S = t.flat ? 1 : t.g1.size();
+    Ctx ca{w, x, 0, 0, quarter};
+    Ctx cb{w, x, 1, quarter, quarter};
+    if (A.count) {
+        MeshReduceScatter(ca, t.g0, A);
+        if (!t.flat) NhrReduceScatter(ca, t.g1, SubWork(A, L, t.g0.me));
+    }
+    if (B.count) {
+        NhrReduceScatter(cb, t.g1, B);
+        MeshReduceScatter(cb, t.g0, SubWork(B, S, t.g1.me));
+    }
+    const Group all = WholeGroup(w, rank);
+    x.SyncGroup(all.ranks, N_DATA);
+    if (rank == p.root) {
+        for (uint32_t l = 0; l < L; ++l) {
+            const std::vector<uint32_t>* col = t.flat ? nullptr : GroupOf(t.h, 1, t.g0.world(l));
+            for (uint32_t s = 0; s < S; ++s) {
+                const uint32_t holder = t.flat ? t.g0.world(l) : (*col)[s];
+                const Work pa = SubWork(SubWork(A, L, l), S, s), pb = SubWork(SubWork(B, S, s), L, l);
+                if (pa.count) x.Copy(Out(rank, pa.base - wOff), Scratch(holder, pa.base), pa.count * es, 0);
+                if (pb.count) x.Copy(Out(rank, pb.base - wOff), Scratch(holder, pb.base), pb.count * es, 1);
+            }
+        }
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+    return HCCL_SUCCESS;
+}
+
 // ---------------------------------------------------------------- tree executor (AllReduce)
 struct TreeRun {
     HostWorld& w;
@@ -1015,6 +1132,9 @@ HcclResult RunHostExecutorExt(HostWorld& w, uint32_t rank, int alg, const OpPara
         case HALG_BCAST_PIPELINE_MESH_MESH: r = PipelineBroadcast(w, x, rank, p); break;
         case HALG_REDUCE_PIPELINE_MESH_NHR: r = PipelineReduce(w, x, rank, p); break;
         case HALG_AG_PARALLEL_MESH_MESH: r = ParallelAllGather(w, x, rank, p); break;
+        case HALG_BCAST_PARALLEL_MESH_MESH: r = ParallelBroadcast(w, x, rank, p); break;
+        case HALG_SCATTER_PARALLEL_MESH_MESH: r = ParallelScatter(w, x, rank, p); break;
+        case HALG_REDUCE_PARALLEL_MESH_NHR: r = ParallelReduce(w, x, rank, p); break;
         case HALG_RS_PARALLEL_MESH_MESH: r = ParallelReduceScatter(w, x, rank, p); break;
         case HALG_SCATTER_PIPELINE_MESH_MESH: r = PipelineScatter(w, x, rank, p); break;
         case HALG_AG_NB: {

@@ -370,6 +370,7 @@ uint64_t HostScratchMultiple(int alg, uint32_t n)
     switch (alg) {
         case HALG_AR_MESH_ONESHOT: case HALG_AR_ORDER_PRESERVED: case HALG_RS_ORDER_PRESERVED: return n;
         case HALG_AR_TREE: return 3;      // one staging region per level of the tree
+        case HALG_REDUCE_PARALLEL_MESH_NHR: return 2;      // two parts' templates stage side by side
         default: return 1;
     }
 }

@@ -248,6 +248,22 @@ def test_parallel_all_gather_and_reduce_scatter(algo_env, ratio):
                 for r in range(n):
                     np.testing.assert_allclose(rs_out[r], ref[r * count:(r + 1) * count], rtol=1e-12, atol=1e-13)
                 assert all(np.array_equal(rs_in[r], np.random.default_rng(40 + r).standard_normal(count * n)) for r in range(n))   # inputs intact
+                for root in (0, n // 2, n - 1):                  # the rooted operators: the root in the first, a middle and the last server
+                    bufs = [np.full(count, 100 + r, np.int16) for r in range(n)]
+                    verified(comms, lambda r, c: c.broadcast(bufs[r], root))
+                    assert comms[0].last_algorithm() == "HostBroadcastParallelMeshMesh", comms[0].last_algorithm()
+                    assert all(np.all(b == 100 + root) for b in bufs)
+                    red_in = [np.random.default_rng(70 + r).standard_normal(count) for r in range(n)]
+                    red_out = np.zeros(count, np.float64)
+                    verified(comms, lambda r, c: c.reduce(red_in[r], red_out if r == root else None, root))
+                    assert comms[0].last_algorithm() == "HostReduceParallelMeshNHR", comms[0].last_algorithm()
+                    np.testing.assert_allclose(red_out, np.sum(np.stack(red_in), 0), rtol=1e-12, atol=1e-13)
+                    sc_in = np.random.default_rng(90 + root).integers(-1000, 1000, count * n).astype(np.int32)
+                    sc_out = [np.zeros(count, np.int32) for _ in range(n)]
+                    verified(comms, lambda r, c: c.scatter(sc_in if r == root else None, sc_out[r], root))
+                    assert comms[0].last_algorithm() == "HostScatterParallelMeshMesh", comms[0].last_algorithm()
+                    for r in range(n):
+                        assert np.array_equal(sc_out[r], sc_in[r * count:(r + 1) * count])
             destroy(comms)
     finally:
         os.environ.pop("HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO", None)
