@@ -364,6 +364,11 @@ void RegisterHostAlgorithms()
     Reg({"HostReduceScatterConcurrentMeshNHR", HCCL_CMD_REDUCE_SCATTER, HALG_RS_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, true, L, rs, false});
     Reg({"HostAllReduceSequence2DieMeshMesh", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_2DIE_MESH_MESH, "sequence2die", {"Mesh2Die", "Mesh2Die"}, AlgoType::TWO_DIE, 1, true, Four, ar, false});
     Reg({"HostAllReduceSoleMeshConcur", HCCL_CMD_ALLREDUCE, HALG_AR_SOLE_MESH_CONCUR, "twoshotsole", {"MeshConcur", "MeshConcur"}, AlgoType::MESH_CONCUR, 1, true, Four, ar, false});
+    for (HcclCMDType op : {HCCL_CMD_ALLTOALL, HCCL_CMD_ALLTOALLV, HCCL_CMD_ALLTOALLVC}) {
+        static std::vector<std::string> keepConcur;
+        keepConcur.push_back(std::string(op == HCCL_CMD_ALLTOALL ? "HostAlltoAll" : op == HCCL_CMD_ALLTOALLV ? "HostAlltoAllV" : "HostAlltoAllVC") + "ConcurrentMeshMesh");
+        Reg({keepConcur.back().c_str(), op, HALG_A2A_CONCURRENT_MESH_MESH, "concurrent", {"Mesh", "Mesh"}, AlgoType::CONCURRENT, 1, false, Three, rs, true});
+    }
     Reg({"HostBroadcastConcurrentMeshNHR", HCCL_CMD_BROADCAST, HALG_BCAST_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, false, L1, ar, true});
     Reg({"HostReduceConcurrentMeshNHR", HCCL_CMD_REDUCE, HALG_REDUCE_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, true, L1, ar, false});
     Reg({"HostAllGatherConcurrentMeshNHR", HCCL_CMD_ALLGATHER, HALG_AG_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, false, L, rs, true});

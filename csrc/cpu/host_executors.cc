@@ -226,6 +226,31 @@ void MeshConcurAllReduce(HostWorld& w, HostPrims& x, const Group& all, const Wor
     if (B.count) MeshAllGather(cb, all, B);
 }
 
+// AlltoAll family: every pair's block is split by the bandwidth of the two link sets; the receiver pulls the first
+// parts from its peers in mesh order on queue 0 and the second parts in the opposite order on queue 1 (reference: the
+// Concurrent executors of AlltoAll / AlltoAllV, ins_v2_all_to_all_v_concurrent_executor.cc, two mesh templates on two
+// link sets).  The senders' displacements are published at the start of their staging buffers.
+void ConcurrentAlltoAll(HostWorld& w, HostPrims& x, const Group& all, uint32_t rank, const OpParam& p)
+{
+    const uint32_t n = all.size(), es = DataTypeSize(p.dtype), res = DataTypeSize(p.recvType);
+    double sa, sb;
+    SplitShares(&sa, &sb);
+    uint64_t* table = reinterpret_cast<uint64_t*>(w.Resolve(Scratch(rank, 0)));
+    for (uint32_t j = 0; j < n; ++j) table[j] = p.sdispls[j] * es;
+    x.SyncGroup(all.ranks, N_READY);
+    x.Copy(Out(rank, p.rdispls[rank] * res), In(rank, p.sdispls[rank] * es), p.sendCounts[rank] * es);
+    for (uint32_t q = 0; q < 2; ++q) {
+        for (uint32_t k = 1; k < n; ++k) {
+            const uint32_t from = q == 0 ? (rank + k) % n : (rank + n - k) % n;
+            const uint64_t sd = reinterpret_cast<const uint64_t*>(w.Resolve(Scratch(from, 0)))[rank];
+            const uint64_t a = BandwidthSplit(p.recvCounts[from], sa, sb, 1);
+            const uint64_t off = q == 0 ? 0 : a, cnt = q == 0 ? a : p.recvCounts[from] - a;
+            if (cnt) x.Copy(Out(rank, (p.rdispls[from] + off) * res), Mem{from, BufKind::INPUT, sd + off * res}, cnt * res, q);
+        }
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+}
+
 // Broadcast: both parts are scattered from the root (member i takes slice i of a part), then part A is gathered over
 // the mesh while part B is gathered by NHR on the second queue.
 void ConcurrentBroadcast(HostWorld& w, HostPrims& x, const Group& all, uint32_t rank, const OpParam& p)
@@ -1126,6 +1151,7 @@ HcclResult RunHostExecutorExt(HostWorld& w, uint32_t rank, int alg, const OpPara
         case HALG_RS_CONCURRENT_MESH_NHR: ConcurrentReduceScatter(w, x, all, rank, p); break;
         case HALG_AG_CONCURRENT_MESH_NHR: ConcurrentAllGather(w, x, all, rank, p); break;
         case HALG_BCAST_CONCURRENT_MESH_NHR: ConcurrentBroadcast(w, x, all, rank, p); break;
+        case HALG_A2A_CONCURRENT_MESH_MESH: ConcurrentAlltoAll(w, x, all, rank, p); break;
         case HALG_REDUCE_CONCURRENT_MESH_NHR: ConcurrentReduce(w, x, all, rank, p); break;
         case HALG_AG_PIPELINE_MESH_MESH: r = PipelineAllGather(w, x, rank, p); break;
         case HALG_RS_PIPELINE_MESH_MESH: r = PipelineReduceScatter(w, x, rank, p); break;

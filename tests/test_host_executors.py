@@ -123,6 +123,34 @@ def test_concurrent_executors(algo_env, n):
         assert "Concurrent" in comms[0].last_algorithm()
         for o in ag_out:
             assert np.array_equal(o, np.concatenate(ag_in))
+        a2a_in = [np.arange(count * n, dtype=np.int64) + 1000000 * r for r in range(n)]
+        a2a_out = [np.zeros(count * n, np.int64) for _ in range(n)]
+        verified(comms, lambda r, c: c.all_to_all(a2a_in[r], a2a_out[r]))
+        assert comms[0].last_algorithm() == "HostAlltoAllConcurrentMeshMesh", comms[0].last_algorithm()
+        for r in range(n):
+            for q in range(n):
+                assert np.array_equal(a2a_out[r][q * count:(q + 1) * count], a2a_in[q][r * count:(r + 1) * count])
+        cnt = [[(i * 3 + j * 5 + count) % 7 for j in range(n)] for i in range(n)]          # zeros included
+        sends = [np.arange(sum(cnt[i]), dtype=np.float32) + 100 * i for i in range(n)]
+        recvs = [np.zeros(sum(cnt[j][i] for j in range(n)), np.float32) for i in range(n)]
+
+        def a2av(i, c):
+            sd = [sum(cnt[i][:j]) for j in range(n)]
+            rc = [cnt[j][i] for j in range(n)]
+            rd = [sum(rc[:j]) for j in range(n)]
+            c.all_to_all_v(sends[i], cnt[i], sd, recvs[i], rc, rd)
+
+        verified(comms, a2av)
+        assert comms[0].last_algorithm() == "HostAlltoAllVConcurrentMeshMesh", comms[0].last_algorithm()
+        recvs2 = [np.zeros_like(v) for v in recvs]
+        verified(comms, lambda i, c: c.all_to_all_vc(sends[i], cnt, recvs2[i]))
+        for i in range(n):
+            off = 0
+            for j in range(n):
+                sd = sum(cnt[j][:i])
+                assert np.array_equal(recvs[i][off:off + cnt[j][i]], sends[j][sd:sd + cnt[j][i]])
+                off += cnt[j][i]
+            assert np.array_equal(recvs[i], recvs2[i])
         for root in (0, n - 1):
             bufs = [np.full(count, 100 + r, np.int16) for r in range(n)]
             verified(comms, lambda r, c: c.broadcast(bufs[r], root))
