@@ -168,6 +168,15 @@ void RegisterAll()
                 // the switch still has to pull (p-1)/p of the input out of every GPU, at the rate of a port (measured 623 GB/s
                 // of egress at 1 GiB on 8 GPUs), and a staged input is copied before any of that starts
                 c.D = ((m.p - 1) / m.p * m.link() + c.B) * (double)o.bytes;
+                // An ordinary input has to be copied into the slab before the switch can read it.  Measured at 8 GPUs next to
+                // the push form, which lands the blocks without that pass: 38 / 55 / 137 / 521 / 1953 us against 37 / 46 /
+                // 114 / 441 / 1705 us at 4 / 16 / 64 / 256 / 1024 MiB.  So this form is never priced below 1.05 x the push
+                // form's own estimate for such an input.
+                if (!o.inRegistered && o.aligned16) {
+                    const double util = LinkUtilisation(NetType::MESH_P2P, (double)o.bytes / m.p, HCCL_ENGINE_P2P, (int)t.nRanks);
+                    const double push = ((m.p - 1) / m.p * m.link() / util + 0.25 * m.copy()) * (double)o.bytes + m.lm.launchUs + m.lm.barrierUs;
+                    c.D = std::max(c.D, 1.05 * push);
+                }
                 return std::vector<CostCoeff>{c};
             };
             R.Register(e);

@@ -572,6 +572,9 @@ def test_forms_for_ordinary_buffers_private_counts_and_large_broadcasts():
     assert "the input is registered" in _explain_device(4, 0, Cmd.REDUCE_SCATTER, 64 * M, registered=1)
     assert first(8, 1, Cmd.REDUCE_SCATTER, 1 * G, registered=0) == "P2pReduceScatterSoleMeshPush"      # staging 1 GiB for the switch costs a pass
     assert first(8, 1, Cmd.REDUCE_SCATTER, 1 * G, registered=1) == "NvlsReduceScatterSoleMesh"
+    for nbytes in (4 * M, 16 * M, 64 * M, 256 * M):     # measured at 8 GPUs: the push form ahead of the staged switch form from 4 MiB up
+        assert first(8, 1, Cmd.REDUCE_SCATTER, nbytes, registered=0) == "P2pReduceScatterSoleMeshPush"
+        assert first(8, 1, Cmd.REDUCE_SCATTER, nbytes, registered=1) == "NvlsReduceScatterSoleMesh"
     # AllReduce on ordinary buffers without a switch: slices pushed, no stage-in pass; with one the staged switch form stays
     assert first(8, 0, Cmd.ALLREDUCE, 64 * M, registered=0) == "P2pAllReduceSoleMeshPushTwoShot"
     assert first(8, 1, Cmd.ALLREDUCE, 64 * M, registered=0) == "NvlsAllReduceSoleMesh"
