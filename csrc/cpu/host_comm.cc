@@ -375,6 +375,8 @@ void RegisterHostAlgorithms()
     // three levels first: on a topology with pods it wins the tie with the two-level form, elsewhere it is filtered
     Reg({"HostAllReducePipelineMeshNHRNHR", HCCL_CMD_ALLREDUCE, HALG_AR_PIPELINE3_MESH_NHR_NHR, "pipeline", {"Mesh", "NHR", "NHR"}, AlgoType::OMNIPIPE, 3, true, TwoL1, ar, false});
     Reg({"HostAllReducePipelineMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_PIPELINE_MESH_NHR, "pipeline", {"Mesh", "NHR"}, AlgoType::OMNIPIPE, 2, true, TwoL1, ar, false});
+    Reg({"HostAllGatherPipelineMeshMeshMesh", HCCL_CMD_ALLGATHER, HALG_AG_PIPELINE3_MESH_MESH_MESH, "pipeline", {"Mesh", "Mesh", "Mesh"}, AlgoType::OMNIPIPE, 3, false, Four, rs, true});
+    Reg({"HostReduceScatterPipelineMeshMeshMesh", HCCL_CMD_REDUCE_SCATTER, HALG_RS_PIPELINE3_MESH_MESH_MESH, "pipeline", {"Mesh", "Mesh", "Mesh"}, AlgoType::OMNIPIPE, 3, true, Four, rs, false});
     Reg({"HostAllGatherPipelineMeshMesh", HCCL_CMD_ALLGATHER, HALG_AG_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, false, Four, rs, true});
     Reg({"HostReduceScatterPipelineMeshMesh", HCCL_CMD_REDUCE_SCATTER, HALG_RS_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, true, Four, rs, false});
     Reg({"HostBroadcastPipelineMeshMesh", HCCL_CMD_BROADCAST, HALG_BCAST_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, false, Four, ar, true});

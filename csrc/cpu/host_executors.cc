@@ -682,6 +682,106 @@ HcclResult PipelineReduceScatter(HostWorld& w, HostPrims& x, uint32_t rank, cons
     return HCCL_SUCCESS;
 }
 
+// AllGather on three levels (server, pod, pods): three pipelined stages, one queue each.  Stage 0 pulls a step of the
+// server-mates' inputs, stage 1 pulls the same step of the blocks of every other server of the pod from the rank with
+// my local index there, stage 2 the blocks of every other pod from the rank at my (server, local) position there -
+// each peer hands over exactly what its earlier stages of that step collected.
+HcclResult Pipeline3AllGather(HostWorld& w, HostPrims& x, uint32_t rank, const OpParam& p)
+{
+    AlgHierarchy h;
+    CHK_RET(MatchTopo(w.Topo(rank), TopoMatchKind::THREE_LEVEL, &h));
+    if (h.levels() < 3) return PipelineAllGather(w, x, rank, p);
+    const Group all = WholeGroup(w, rank);
+    Group g[3];
+    for (uint32_t k = 0; k < 3; ++k) LevelGroup(h, k, rank, &g[k]);
+    const uint32_t es = DataTypeSize(p.dtype);
+    // the ranks whose blocks `peer` holds when its stages below `level` are done
+    std::function<void(uint32_t, uint32_t, std::vector<uint32_t>*)> reach = [&](uint32_t peer, uint32_t level, std::vector<uint32_t>* out) {
+        if (level == 0) { out->push_back(peer); return; }
+        for (uint32_t m : *GroupOf(h, level - 1, peer)) reach(m, level - 1, out);
+    };
+    const uint32_t steps = PipelineStepCount(p.count, std::max<uint64_t>(1, 128 / es), kMaxPipeSteps);
+    x.SyncGroup(all.ranks, N_READY);
+    for (const PipeSlot& s : PipelineSchedule(3, steps)) {
+        uint64_t b, e;
+        SliceOf(p.count, steps, s.step, &b, &e);
+        if (s.stage == 0) {
+            for (uint32_t k = 0; k < g[0].size(); ++k) {
+                const uint32_t j = g[0].world((g[0].me + k) % g[0].size());
+                x.Copy(Out(rank, ((uint64_t)j * p.count + b) * es), In(j, b * es), (e - b) * es, 0);
+            }
+            continue;
+        }
+        const Group& gs = g[s.stage];
+        x.SyncGroup(gs.ranks, s.stage == 1 ? N_DATA : N_AUX, s.stage);
+        for (uint32_t k = 1; k < gs.size(); ++k) {
+            const uint32_t peer = gs.world((gs.me + k) % gs.size());
+            std::vector<uint32_t> blocks;
+            reach(peer, s.stage, &blocks);
+            for (uint32_t j : blocks) x.Copy(Out(rank, ((uint64_t)j * p.count + b) * es), Out(peer, ((uint64_t)j * p.count + b) * es), (e - b) * es, s.stage);
+        }
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+    return HCCL_SUCCESS;
+}
+
+// ReduceScatter on three levels, rank (pod, server, local): stage 0 folds, for every rank q with my local index, a step
+// of block q over the members of my server into staging slot (server of q, pod of q); stage 1 folds, for every pod,
+// the slot (my server, that pod) of the ranks with my local index in my pod into a second row of slots; stage 2 folds
+// my pod's slot of the ranks at my position in the other pods into the output.
+HcclResult Pipeline3ReduceScatter(HostWorld& w, HostPrims& x, uint32_t rank, const OpParam& p)
+{
+    AlgHierarchy h;
+    CHK_RET(MatchTopo(w.Topo(rank), TopoMatchKind::THREE_LEVEL, &h));
+    if (h.levels() < 3) return PipelineReduceScatter(w, x, rank, p);
+    const Group all = WholeGroup(w, rank);
+    Group g0, g1, g2;
+    LevelGroup(h, 0, rank, &g0);
+    LevelGroup(h, 1, rank, &g1);
+    LevelGroup(h, 2, rank, &g2);
+    const uint32_t es = DataTypeSize(p.dtype), S = g1.size(), P = g2.size();
+    const uint64_t blk = p.count * es;
+    const uint64_t row1 = (uint64_t)S * P * blk;                    // the second row of slots starts here
+    if (row1 + (uint64_t)P * blk > w.scratchBytes()) {
+        HCCL_ERROR("host engine: three-level pipelined ReduceScatter stages %llu bytes, the scratch buffer has %llu", (unsigned long long)(row1 + P * blk),
+                   (unsigned long long)w.scratchBytes());
+        return HCCL_E_MEMORY;
+    }
+    const uint32_t steps = PipelineStepCount(p.count, std::max<uint64_t>(1, 128 / es), kMaxPipeSteps);
+    x.SyncGroup(all.ranks, N_READY);
+    for (const PipeSlot& s : PipelineSchedule(3, steps)) {
+        uint64_t b, e;
+        SliceOf(p.count, steps, s.step, &b, &e);
+        const uint64_t off = b * es, len = (e - b) * es;
+        if (s.stage == 0) {
+            for (uint32_t i1 = 0; i1 < S; ++i1) {
+                const std::vector<uint32_t>* across = GroupOf(h, 2, g1.world(i1));      // the ranks at position (server i1, my local) in every pod
+                for (uint32_t i2 = 0; i2 < P; ++i2) {
+                    const uint32_t owner = (*across)[i2];
+                    const Mem slot = Scratch(rank, ((uint64_t)i1 * P + i2) * blk + off);
+                    x.Copy(slot, In(rank, (uint64_t)owner * blk + off), len, 0);
+                    for (uint32_t k = 1; k < g0.size(); ++k) x.Reduce(slot, In(g0.world((g0.me + k) % g0.size()), (uint64_t)owner * blk + off), len, 0);
+                }
+            }
+        } else if (s.stage == 1) {
+            x.SyncGroup(g1.ranks, N_DATA, 1);
+            for (uint32_t i2 = 0; i2 < P; ++i2) {
+                const Mem slot = Scratch(rank, row1 + (uint64_t)i2 * blk + off);
+                const uint64_t from = ((uint64_t)g1.me * P + i2) * blk + off;
+                x.Copy(slot, Scratch(rank, from), len, 1);
+                for (uint32_t k = 1; k < S; ++k) x.Reduce(slot, Scratch(g1.world((g1.me + k) % S), from), len, 1);
+            }
+        } else {
+            x.SyncGroup(g2.ranks, N_AUX, 2);
+            const uint64_t from = row1 + (uint64_t)g2.me * blk + off;
+            x.Copy(Out(rank, off), Scratch(rank, from), len, 2);
+            for (uint32_t k = 1; k < P; ++k) x.Reduce(Out(rank, off), Scratch(g2.world((g2.me + k) % P), from), len, 2);
+        }
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+    return HCCL_SUCCESS;
+}
+
 // Broadcast: stage 0 moves a step from the root to the member of every server that shares its local index, stage 1
 // spreads the step inside every server.
 HcclResult PipelineBroadcast(HostWorld& w, HostPrims& x, uint32_t rank, const OpParam& p)
@@ -1157,6 +1257,8 @@ HcclResult RunHostExecutorExt(HostWorld& w, uint32_t rank, int alg, const OpPara
         case HALG_RS_PIPELINE_MESH_MESH: r = PipelineReduceScatter(w, x, rank, p); break;
         case HALG_BCAST_PIPELINE_MESH_MESH: r = PipelineBroadcast(w, x, rank, p); break;
         case HALG_REDUCE_PIPELINE_MESH_NHR: r = PipelineReduce(w, x, rank, p); break;
+        case HALG_AG_PIPELINE3_MESH_MESH_MESH: r = Pipeline3AllGather(w, x, rank, p); break;
+        case HALG_RS_PIPELINE3_MESH_MESH_MESH: r = Pipeline3ReduceScatter(w, x, rank, p); break;
         case HALG_AG_PARALLEL_MESH_MESH: r = ParallelAllGather(w, x, rank, p); break;
         case HALG_BCAST_PARALLEL_MESH_MESH: r = ParallelBroadcast(w, x, rank, p); break;
         case HALG_SCATTER_PARALLEL_MESH_MESH: r = ParallelScatter(w, x, rank, p); break;

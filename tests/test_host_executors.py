@@ -313,6 +313,19 @@ def test_three_level_pipeline_all_reduce(algo_env, topo, n):
             np.testing.assert_allclose(o, ref, rtol=3e-6, atol=3e-5)
         for o in outs[1:]:
             assert np.array_equal(o, outs[0])
+        ag_in = [np.random.default_rng(r).integers(-9, 9, count).astype(np.int64) for r in range(n)]
+        ag_out = [np.zeros(count * n, np.int64) for _ in range(n)]
+        verified(comms, lambda r, c: c.all_gather(ag_in[r], ag_out[r]))
+        assert comms[0].last_algorithm() == "HostAllGatherPipelineMeshMeshMesh", comms[0].last_algorithm()
+        for o in ag_out:
+            assert np.array_equal(o, np.concatenate(ag_in))
+        rs_in = [np.random.default_rng(40 + r).standard_normal(count * n) for r in range(n)]
+        rs_out = [np.zeros(count, np.float64) for _ in range(n)]
+        verified(comms, lambda r, c: c.reduce_scatter(rs_in[r], rs_out[r]))
+        assert comms[0].last_algorithm() == "HostReduceScatterPipelineMeshMeshMesh", comms[0].last_algorithm()
+        ref = np.sum(np.stack(rs_in), 0)
+        for r in range(n):
+            np.testing.assert_allclose(rs_out[r], ref[r * count:(r + 1) * count], rtol=1e-12, atol=1e-13)
     destroy(comms)
 
 
