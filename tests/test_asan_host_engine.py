@@ -30,7 +30,9 @@ def test_host_engine_slice_is_clean_under_asan():
     select = "test_allreduce_algorithms_and_rank_counts and (3-ring or 5-rhd or 7-nhr or 8-mesh or 4-oneshot) or test_rooted_and_alltoall_ops or test_v_variants_host"
     r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-p", "no:cacheprovider", "tests/test_host_engine.py", "tests/test_host_executors.py",
                         "tests/test_verifier_selftests.py", "tests/test_host_retry.py", "-k",
-                        select + " or test_tree_executor or test_hierarchical_alltoall or test_pipeline_executors or test_semantic_defects or test_dropped_notify"],
+                        select + " or test_tree_executor or test_hierarchical_alltoall or test_pipeline_executors or test_semantic_defects or test_dropped_notify"
+                        " or test_serial_windowed_all_to_all or (test_three_level_pipeline_all_reduce and 8)"
+                        " or (test_concurrent_executors and 5) or (test_all_reduce_over_two_link_sets and 5)"],
                        capture_output=True, text=True, cwd=ROOT, env=env, timeout=900)
     tail = (r.stdout + r.stderr)[-3000:]
     assert "AddressSanitizer" not in r.stdout + r.stderr, tail
