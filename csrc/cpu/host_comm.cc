@@ -311,6 +311,8 @@ void RegisterHostAlgorithms()
     Reg({"HostReduceScatterSoleRHD", HCCL_CMD_REDUCE_SCATTER, HALG_RS_RHD, "sole", {"RHD"}, AlgoType::HD_R, 1, true, L, rs, false});
     Reg({"HostReduceScatterSoleNHR", HCCL_CMD_REDUCE_SCATTER, HALG_RS_NHR, "sole", {"NHR"}, AlgoType::NHR, 1, true, L, rs, false});
     Reg({"HostReduceScatterStrictOrderedMesh", HCCL_CMD_REDUCE_SCATTER, HALG_RS_ORDER_PRESERVED, "orderpreserved", {"OrderPreservedGroup"}, AlgoType::AHC, 1, true, Three, full, true});
+    // three levels first: on a topology with pods it wins the tie with the two-level form, elsewhere it is filtered
+    Reg({"HostReduceScatterSequenceMeshNHRNHR", HCCL_CMD_REDUCE_SCATTER, HALG_RS_SEQ3_MESH_NHR_NHR, "sequence", {"NHR", "NHR", "Mesh"}, AlgoType::NHR, 3, true, L, rs, false});
     Reg({"HostReduceScatterSequenceMeshNHR", HCCL_CMD_REDUCE_SCATTER, HALG_RS_SEQ_MESH_NHR, "sequence", {"NHR", "Mesh"}, AlgoType::NHR, 2, true, L, rs, false});
     Reg({"HostReduceScatterSequenceMeshRing", HCCL_CMD_REDUCE_SCATTER, HALG_RS_SEQ_MESH_RING, "sequence", {"Ring", "Mesh"}, AlgoType::RING, 2, true, P1, rs, false});
     Reg({"HostReduceScatterSequenceMeshRHD", HCCL_CMD_REDUCE_SCATTER, HALG_RS_SEQ_MESH_RHD, "sequence", {"RHD", "Mesh"}, AlgoType::HD_R, 2, true, L, rs, false});
@@ -323,6 +325,7 @@ void RegisterHostAlgorithms()
     Reg({"HostAllGatherSoleRing", HCCL_CMD_ALLGATHER, HALG_AG_RING, "sole", {"Ring"}, AlgoType::RING, 1, false, P1, rs, true});
     Reg({"HostAllGatherSoleRHD", HCCL_CMD_ALLGATHER, HALG_AG_RHD, "sole", {"RHD"}, AlgoType::HD_R, 1, false, L, rs, true});
     Reg({"HostAllGatherSoleNHR", HCCL_CMD_ALLGATHER, HALG_AG_NHR, "sole", {"NHR"}, AlgoType::NHR, 1, false, L, rs, true});
+    Reg({"HostAllGatherSequenceMeshNHRNHR", HCCL_CMD_ALLGATHER, HALG_AG_SEQ3_MESH_NHR_NHR, "sequence", {"Mesh", "NHR", "NHR"}, AlgoType::NHR, 3, false, L, rs, true});
     Reg({"HostAllGatherSequenceMeshNHR", HCCL_CMD_ALLGATHER, HALG_AG_SEQ_MESH_NHR, "sequence", {"Mesh", "NHR"}, AlgoType::NHR, 2, false, L, rs, true});
     Reg({"HostAllGatherSequenceMeshRing", HCCL_CMD_ALLGATHER, HALG_AG_SEQ_MESH_RING, "sequence", {"Mesh", "Ring"}, AlgoType::RING, 2, false, P1, rs, true});
     Reg({"HostAllGatherSequenceMeshRHD", HCCL_CMD_ALLGATHER, HALG_AG_SEQ_MESH_RHD, "sequence", {"Mesh", "RHD"}, AlgoType::HD_R, 2, false, L, rs, true});

@@ -437,7 +437,7 @@ HcclResult RunHostAlgorithm(HostWorld& w, uint32_t rank, int alg, const OpParam&
         }
         // ------------------------------------------------------------ ReduceScatter (+V through the slice of `me`)
         case HALG_RS_MESH: case HALG_RS_RING: case HALG_RS_RHD: case HALG_RS_NHR: case HALG_RS_ORDER_PRESERVED: case HALG_RS_SEQ_MESH_NHR:
-        case HALG_RS_SEQ_MESH_RING: case HALG_RS_SEQ_MESH_RHD: {
+        case HALG_RS_SEQ_MESH_RING: case HALG_RS_SEQ_MESH_RHD: case HALG_RS_SEQ3_MESH_NHR_NHR: {
             // work on a scratch copy of the whole input so that the user's send buffer stays intact; layout of W:
             // rank i's block at i * blockElems (V: at its displacement)
             const bool v = p.op == HCCL_CMD_REDUCE_SCATTER_V;
@@ -483,12 +483,22 @@ HcclResult RunHostAlgorithm(HostWorld& w, uint32_t rank, int alg, const OpParam&
                 x.SyncGroup(all.ranks, N_DONE);
                 break;
             }
-            if (alg == HALG_RS_SEQ_MESH_NHR || alg == HALG_RS_SEQ_MESH_RING || alg == HALG_RS_SEQ_MESH_RHD) {
-                // level 1 first on whole server-sized blocks, then level 0 inside the server
+            if (alg == HALG_RS_SEQ_MESH_NHR || alg == HALG_RS_SEQ_MESH_RING || alg == HALG_RS_SEQ_MESH_RHD || alg == HALG_RS_SEQ3_MESH_NHR_NHR) {
+                // the top level first on whole pod- or server-sized blocks, then down to level 0 inside the server
                 const Fam upper = alg == HALG_RS_SEQ_MESH_RING ? Fam::RING : alg == HALG_RS_SEQ_MESH_RHD ? Fam::RHD : Fam::NHR;
                 AlgHierarchy h;
-                CHK_RET(hierarchy(TopoMatchKind::TWO_LEVEL, &h));
-                if (h.levels() == 2) {
+                CHK_RET(hierarchy(alg == HALG_RS_SEQ3_MESH_NHR_NHR ? TopoMatchKind::THREE_LEVEL : TopoMatchKind::TWO_LEVEL, &h));
+                if (h.levels() == 3) {
+                    Group g0, g1, g2;
+                    LevelGroup(h, 0, rank, &g0);
+                    LevelGroup(h, 1, rank, &g1);
+                    LevelGroup(h, 2, rank, &g2);
+                    // ranks are numbered pod by pod and server by server inside a pod
+                    ReduceScatterBy(upper, cc, g2, wk);
+                    const Work pod = SubWork(wk, g2.size(), g2.me);
+                    ReduceScatterBy(upper, cc, g1, pod);
+                    MeshReduceScatter(cc, g0, SubWork(pod, g1.size(), g1.me));
+                } else if (h.levels() == 2) {
                     Group g0, g1;
                     LevelGroup(h, 0, rank, &g0);
                     LevelGroup(h, 1, rank, &g1);
@@ -508,7 +518,7 @@ HcclResult RunHostAlgorithm(HostWorld& w, uint32_t rank, int alg, const OpParam&
         }
         // ------------------------------------------------------------ AllGather (+V)
         case HALG_AG_MESH: case HALG_AG_RING: case HALG_AG_RHD: case HALG_AG_NHR: case HALG_AG_SEQ_MESH_NHR:
-        case HALG_AG_SEQ_MESH_RING: case HALG_AG_SEQ_MESH_RHD: {
+        case HALG_AG_SEQ_MESH_RING: case HALG_AG_SEQ_MESH_RHD: case HALG_AG_SEQ3_MESH_NHR_NHR: {
             const bool v = p.op == HCCL_CMD_ALLGATHER_V;
             if (v && alg != HALG_AG_MESH) {
                 // variable blocks through ring / RHD / NHR, in place in the output at the callers' displacements
@@ -533,11 +543,21 @@ HcclResult RunHostAlgorithm(HostWorld& w, uint32_t rank, int alg, const OpParam&
             }
             x.Copy(Out(rank, (uint64_t)rank * p.count * es), In(rank), p.count * es);
             Work wk{BufKind::OUTPUT, 0, p.count * n, es};
-            if (alg == HALG_AG_SEQ_MESH_NHR || alg == HALG_AG_SEQ_MESH_RING || alg == HALG_AG_SEQ_MESH_RHD) {
+            if (alg == HALG_AG_SEQ_MESH_NHR || alg == HALG_AG_SEQ_MESH_RING || alg == HALG_AG_SEQ_MESH_RHD || alg == HALG_AG_SEQ3_MESH_NHR_NHR) {
                 const Fam upper = alg == HALG_AG_SEQ_MESH_RING ? Fam::RING : alg == HALG_AG_SEQ_MESH_RHD ? Fam::RHD : Fam::NHR;
                 AlgHierarchy h;
-                CHK_RET(hierarchy(TopoMatchKind::TWO_LEVEL, &h));
-                if (h.levels() == 2) {
+                CHK_RET(hierarchy(alg == HALG_AG_SEQ3_MESH_NHR_NHR ? TopoMatchKind::THREE_LEVEL : TopoMatchKind::TWO_LEVEL, &h));
+                if (h.levels() == 3) {
+                    // bottom-up: the server's blocks, then the pod's, then everything
+                    Group g0, g1, g2;
+                    LevelGroup(h, 0, rank, &g0);
+                    LevelGroup(h, 1, rank, &g1);
+                    LevelGroup(h, 2, rank, &g2);
+                    const Work pod = SubWork(wk, g2.size(), g2.me);
+                    MeshAllGather(c, g0, SubWork(pod, g1.size(), g1.me));
+                    AllGatherBy(upper, c, g1, pod);
+                    AllGatherBy(upper, c, g2, wk);
+                } else if (h.levels() == 2) {
                     Group g0, g1;
                     LevelGroup(h, 0, rank, &g0);
                     LevelGroup(h, 1, rank, &g1);

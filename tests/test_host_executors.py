@@ -329,6 +329,28 @@ def test_three_level_pipeline_all_reduce(algo_env, topo, n):
     destroy(comms)
 
 
+@pytest.mark.parametrize("topo,n", [(TWO_PODS, 8), ("[[[0,1,2],[3,4,5]],[[6,7,8],[9,10,11]],[[12,13,14],[15,16,17]]]", 18)])
+def test_three_level_sequence_all_gather_and_reduce_scatter(algo_env, topo, n):
+    """Sequence executors over server, pod and pods: ReduceScatter from the top level down (NHR across pods, NHR across
+    the servers of a pod, mesh in the server), AllGather from the bottom up."""
+    comms = make(n, topo=topo, algo="level0:NA;level1:NHR;level2:NHR")
+    for count in (1, 5, 977, 30011):
+        ag_in = [np.random.default_rng(r).integers(-9, 9, count).astype(np.int32) for r in range(n)]
+        ag_out = [np.zeros(count * n, np.int32) for _ in range(n)]
+        verified(comms, lambda r, c: c.all_gather(ag_in[r], ag_out[r]))
+        assert comms[0].last_algorithm() == "HostAllGatherSequenceMeshNHRNHR", comms[0].last_algorithm()
+        for o in ag_out:
+            assert np.array_equal(o, np.concatenate(ag_in))
+        rs_in = [np.random.default_rng(40 + r).standard_normal(count * n) for r in range(n)]
+        rs_out = [np.zeros(count, np.float64) for _ in range(n)]
+        verified(comms, lambda r, c: c.reduce_scatter(rs_in[r], rs_out[r]))
+        assert comms[0].last_algorithm() == "HostReduceScatterSequenceMeshNHRNHR", comms[0].last_algorithm()
+        ref = np.sum(np.stack(rs_in), 0)
+        for r in range(n):
+            np.testing.assert_allclose(rs_out[r], ref[r * count:(r + 1) * count], rtol=1e-12, atol=1e-13)
+    destroy(comms)
+
+
 @pytest.mark.parametrize("n", [4, 6, 7, 8, 12])
 def test_all_reduce_on_a_squeezed_grid(algo_env, n):
     """A flat group folded into rows x columns (squeeze 2-D match): mesh ReduceScatter along the rows, mesh AllReduce
