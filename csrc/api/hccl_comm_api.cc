@@ -25,6 +25,7 @@ extern "C" {
 
 const char* HcclGetVersion(void) { return "hccl_b200 0.1.0"; }
 HcclResult HcclReloadEnvConfig(void) { ReloadEnvConfig(); AlgoPluginReload(); return HCCL_SUCCESS; }
+HcclResult HcclAlgoPluginQueryAlgs(const char* opName, char* buf, uint32_t bufLen, uint32_t* count) { return AlgoPluginQueryAlgs(opName, buf, bufLen, count); }
 const char* HcclGetErrorString(HcclResult code) { return ResultString(code); }
 
 HcclResult HcclGetRootInfo(HcclRootInfo* rootInfo)

@@ -1,5 +1,6 @@
 #include "algo_plugin.h"
 #include <dlfcn.h>
+#include <cstddef>
 #include <cstring>
 #include <mutex>
 #include "../ops/op_common.h"
@@ -27,7 +28,7 @@ const HcclAlgoPluginTable* Table()
     using GetFn = const HcclAlgoPluginTable* (*)();
     GetFn get = (GetFn)dlsym(g_handle, "GetHcclAlgoPlugin");
     const HcclAlgoPluginTable* t = get ? get() : nullptr;
-    if (!t || t->magic != HCCL_ALGO_PLUGIN_TABLE_MAGIC || t->apiVersion != HCCL_PLUGIN_API_VERSION || t->structSize < sizeof(HcclAlgoPluginTable) ||
+    if (!t || t->magic != HCCL_ALGO_PLUGIN_TABLE_MAGIC || t->apiVersion != HCCL_PLUGIN_API_VERSION || t->structSize < offsetof(HcclAlgoPluginTable, QueryAlgs) ||
         !t->SelectAlg || !t->ExecuteAlg) {
         HCCL_WARNING("algorithm plugin '%s': missing GetHcclAlgoPlugin, wrong version or incomplete table: ignored", path.c_str());
         dlclose(g_handle);
@@ -82,6 +83,20 @@ bool AlgoPluginTryExecute(CommImpl* comm, const OpParam& p, HcclResult* result, 
     *result = t->ExecuteAlg(name, &q);
     if (*result != HCCL_SUCCESS) HCCL_ERROR("algorithm plugin: %s failed in %s: %s", name, q.opName, ResultString(*result));
     return true;
+}
+
+HcclResult AlgoPluginQueryAlgs(const char* opName, char* buf, uint32_t bufLen, uint32_t* count)
+{
+    if (!buf || !count || bufLen == 0) return HCCL_E_PTR;
+    *count = 0;
+    buf[0] = 0;
+    const HcclAlgoPluginTable* t = Table();
+    if (!t) return HCCL_E_NOT_FOUND;
+    if (t->structSize < sizeof(HcclAlgoPluginTable) || !t->QueryAlgs) return HCCL_E_NOT_SUPPORT;
+    const int n = t->QueryAlgs(opName ? opName : "", buf, bufLen);
+    if (n < 0) return HCCL_E_MEMORY;
+    *count = (uint32_t)n;
+    return HCCL_SUCCESS;
 }
 
 }  // namespace hccl

@@ -11,6 +11,7 @@
 #define HCCL_B200_ALGO_PLUGIN_H_
 
 #include <stdbool.h>
+#include <stddef.h>
 #include <stdint.h>
 #include <string.h>
 #include "hccl_types.h"
@@ -56,9 +57,29 @@ typedef struct {
     /* HCCL_SUCCESS + algName: the plugin will run this call.  Anything else: the built-in path runs. */
     HcclResult (*SelectAlg)(const HcclAlgoPluginParam* param, char algName[HCCL_ALGO_PLUGIN_ALG_NAME_LEN]);
     HcclResult (*ExecuteAlg)(const char* algName, const HcclAlgoPluginParam* param);
+    /* Optional (a table whose structSize ends before it has none): the names of the algorithms the plugin offers for
+       an operator ("AllReduce", ...; NULL or "" = all), written to buf as a sequence of '\0'-terminated names closed
+       by an empty one.  Returns the number of names, or a negative value when bufLen is too small.  (HCCL's broker
+       table has the same query, hccl_algo_plugin_broker_api.h:52-54.) */
+    int (*QueryAlgs)(const char* opName, char* buf, size_t bufLen);
 } HcclAlgoPluginTable;
 
 const HcclAlgoPluginTable* GetHcclAlgoPlugin(void);   /* exported by the plugin */
+
+/* Fills the common fields of a parameter block (what the library does before it calls SelectAlg; for plugin tests). */
+static inline void HcclAlgoPluginParamInit(HcclAlgoPluginParam* param)
+{
+    if (param == NULL) return;
+    memset(param, 0, sizeof(*param));
+    param->version = HCCL_PLUGIN_API_VERSION;
+    param->magic = HCCL_ALGO_PLUGIN_PARAM_MAGIC;
+    param->structSize = (uint32_t)sizeof(HcclAlgoPluginParam);
+}
+
+/* Library side: the algorithm names of the loaded plugin (HCCL_ALGO_PLUGIN_PATH) for an operator, in the format of
+   QueryAlgs.  HCCL_E_NOT_FOUND without a plugin, HCCL_E_NOT_SUPPORT when the plugin has no query, HCCL_E_MEMORY when
+   buf is too small; *count receives the number of names. */
+HcclResult HcclAlgoPluginQueryAlgs(const char* opName, char* buf, uint32_t bufLen, uint32_t* count);
 
 #ifdef __cplusplus
 }

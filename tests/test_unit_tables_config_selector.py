@@ -271,7 +271,13 @@ static HcclResult Execute(const char* name, const HcclAlgoPluginParam* p) {
     float* out = (float*)p->recvBuf;
     for (uint64_t i = 0; i < p->count; ++i) out[i] = 1000.0f + (float)p->rankNum;   // host buffers in this test
     return HCCL_SUCCESS; }
-static HcclAlgoPluginTable g_table = {HCCL_PLUGIN_API_VERSION, HCCL_ALGO_PLUGIN_TABLE_MAGIC, sizeof(HcclAlgoPluginTable), Ready, Select, Execute};
+static int Query(const char* op, char* buf, size_t len) {
+    static const char names[] = "PluginBroadcastFill\0";             // one name, then the empty name that closes the list
+    if (op && op[0] && strcmp(op, "Broadcast") != 0) { if (len < 1) return -1; buf[0] = 0; return 0; }
+    if (len < sizeof(names)) return -1;
+    memcpy(buf, names, sizeof(names));
+    return 1; }
+static HcclAlgoPluginTable g_table = {HCCL_PLUGIN_API_VERSION, HCCL_ALGO_PLUGIN_TABLE_MAGIC, sizeof(HcclAlgoPluginTable), Ready, Select, Execute, Query};
 extern "C" const HcclAlgoPluginTable* GetHcclAlgoPlugin(void) { return &g_table; }
 """
 
@@ -305,9 +311,19 @@ def test_algo_plugin_takes_over_claimed_operator(tmp_path):
         assert comms[0].last_algorithm().startswith("HostAllReduce")
         for c in comms:
             c.destroy()
+        # the plugin's own list of algorithms, per operator
+        lib.HcclAlgoPluginQueryAlgs.restype = ctypes.c_int
+        lib.HcclAlgoPluginQueryAlgs.argtypes = [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_uint32, ctypes.POINTER(ctypes.c_uint32)]
+        buf, n = ctypes.create_string_buffer(256), ctypes.c_uint32(99)
+        assert lib.HcclAlgoPluginQueryAlgs(b"Broadcast", buf, 256, ctypes.byref(n)) == 0 and n.value == 1
+        assert buf.raw.split(b"\0")[0] == b"PluginBroadcastFill"
+        assert lib.HcclAlgoPluginQueryAlgs(b"AllReduce", buf, 256, ctypes.byref(n)) == 0 and n.value == 0
+        assert lib.HcclAlgoPluginQueryAlgs(None, buf, 256, ctypes.byref(n)) == 0 and n.value == 1
+        assert lib.HcclAlgoPluginQueryAlgs(b"Broadcast", buf, 4, ctypes.byref(n)) != 0          # too small: an error, not a truncated list
     finally:
         os.environ.pop("HCCL_ALGO_PLUGIN_PATH", None)
         lib.HcclReloadEnvConfig()
+    assert lib.HcclAlgoPluginQueryAlgs(b"Broadcast", buf, 256, ctypes.byref(n)) != 0            # no plugin loaded
 
 
 def _threshold(op, nbytes, ranks=8, levels=1, host=0, nvls=0, strict=0):
