@@ -508,6 +508,14 @@ HcclResult HcclCalcOpResGraphMode(const char* group, HcclCMDType op, uint64_t co
     return HcclCalcOpResource(c, op, count, dataType, reduceOp, 0, res);
 }
 
+HcclResult HcclCalcOpResOnlineGraphMode(const char* group, HcclCMDType op, uint64_t count, HcclDataType dataType, HcclReduceOp reduceOp, int registered,
+                                        HcclOpResource* res)
+{
+    CommImpl* c = nullptr;
+    CHK_RET(ResolveGroup(group, &c));
+    return HcclCalcOpResource(c, op, count, dataType, reduceOp, registered, res);
+}
+
 #define GRAPH_NODE() GraphNode node; CHK_RET(node.Begin(group, tag, res))
 HcclResult HcclAllReduceGraphMode(void* sendBuf, void* recvBuf, uint64_t count, HcclDataType dataType, HcclReduceOp op, const char* group,
                                   const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream)
@@ -550,6 +558,31 @@ HcclResult HcclAlltoAllGraphMode(const void* sendBuf, uint64_t sendCount, HcclDa
 {
     GRAPH_NODE();
     return HcclAlltoAll(sendBuf, sendCount, sendType, recvBuf, recvCount, recvType, node.comm, stream);
+}
+HcclResult HcclAllGatherVGraphMode(void* sendBuf, void* recvBuf, uint64_t sendCount, const void* recvCounts, const void* recvDispls, HcclDataType dataType,
+                                   const char* group, const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream)
+{
+    GRAPH_NODE();
+    return HcclAllGatherV(sendBuf, sendCount, recvBuf, recvCounts, recvDispls, dataType, node.comm, stream);
+}
+HcclResult HcclReduceScatterVGraphMode(void* sendBuf, const void* sendCounts, const void* sendDispls, void* recvBuf, uint64_t recvCount, HcclDataType dataType,
+                                       HcclReduceOp op, const char* group, const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream)
+{
+    GRAPH_NODE();
+    return HcclReduceScatterV(sendBuf, sendCounts, sendDispls, recvBuf, recvCount, dataType, op, node.comm, stream);
+}
+HcclResult HcclAlltoAllVGraphMode(const void* sendBuf, const void* sendCounts, const void* sdispls, HcclDataType sendType, const void* recvBuf,
+                                  const void* recvCounts, const void* rdispls, HcclDataType recvType, const char* group, const char* tag,
+                                  const HcclResPackGraphMode* res, hcclStream_t stream)
+{
+    GRAPH_NODE();
+    return HcclAlltoAllV(sendBuf, sendCounts, sdispls, sendType, recvBuf, recvCounts, rdispls, recvType, node.comm, stream);
+}
+HcclResult HcclAlltoAllVCGraphMode(const void* sendBuf, const void* sendCountMatrix, HcclDataType sendType, const void* recvBuf, HcclDataType recvType,
+                                   const char* group, const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream)
+{
+    GRAPH_NODE();
+    return HcclAlltoAllVC(sendBuf, sendCountMatrix, sendType, recvBuf, recvType, node.comm, stream);
 }
 HcclResult HcclSendGraphMode(void* sendBuf, uint64_t count, HcclDataType dataType, uint32_t destRank, const char* group, const char* tag,
                              const HcclResPackGraphMode* res, hcclStream_t stream)

@@ -223,30 +223,46 @@ HcclResult HcclSelectorExplain(HcclComm comm, HcclCMDType op, uint64_t count, Hc
     return r;
 }
 
-HcclResult HcclCalcOpResource(HcclComm comm, HcclCMDType op, uint64_t count, HcclDataType dt, HcclReduceOp rop, int registered, HcclOpResource* res)
+}  // extern "C"
+
+namespace {
+// What a communicator is to the resource query: everything the answer depends on.  Filled from a live communicator
+// (online) or from a description of the box (offline: no device, no communicator).
+struct ResQueryCtx {
+    const TopoInfo* topo;
+    SelectorState* selector;
+    StageLayout layout;
+    uint64_t bufferBytes;
+    int nRanks, maxBlocks;
+    HcclCommEngine engine;
+    Deterministic det;
+    bool nvls, host;
+    std::string name;
+    HcclComm comm;
+};
+
+HcclResult CalcOpRes(const ResQueryCtx& q, HcclCMDType op, uint64_t count, HcclDataType dt, HcclReduceOp rop, int registered, HcclOpResource* res)
 {
-    CHK_PTR_NULL(comm); CHK_PTR_NULL(res);
-    CommImpl* c = static_cast<CommImpl*>(comm);
     memset(res, 0, sizeof(*res));
     res->streams = 1;
     OpDesc d;
-    d.op = op; d.dtype = dt; d.redOp = rop; d.nRanks = (uint32_t)c->nRanks; d.det = c->cfg.deterministic;
-    d.engine = c->hostComm ? HCCL_ENGINE_HOSTCPU : c->cfg.engine;
+    d.op = op; d.dtype = dt; d.redOp = rop; d.nRanks = (uint32_t)q.nRanks; d.det = q.det;
+    d.engine = q.host ? HCCL_ENGINE_HOSTCPU : q.engine;
     const uint64_t es = DataTypeSize(dt);
     if (es == 0) return HCCL_E_PARA;
-    const uint64_t P = (uint64_t)c->nRanks;
+    const uint64_t P = (uint64_t)q.nRanks;
     const bool perRank = op == HCCL_CMD_ALLGATHER || op == HCCL_CMD_REDUCE_SCATTER || op == HCCL_CMD_SCATTER || op == HCCL_CMD_ALLTOALL;
     d.bytes = count * es * (perRank ? P : 1);
     d.inRegistered = d.outRegistered = registered != 0;
-    d.stageInBytes = c->layout().inBytes;
-    d.inMulticast = d.outMulticast = registered != 0 && c->nvls();      // "registered" here means HcclMemAlloc memory
+    d.stageInBytes = q.layout.inBytes;
+    d.inMulticast = d.outMulticast = registered != 0 && q.nvls;      // "registered" here means HcclMemAlloc memory
     Selection sel;
-    CHK_RET(SelectAlgorithm(*c->selector, *c->topo, GetEnvConfig(), d, c->name, comm, c->cfg.bufferBytes, &sel));
+    CHK_RET(SelectAlgorithm(*q.selector, *q.topo, GetEnvConfig(), d, q.name, q.comm, q.bufferBytes, &sel));
     snprintf(res->algName, sizeof(res->algName), "%s", sel.alg->name.c_str());
     res->engine = (uint32_t)sel.alg->engine;
-    if (c->hostComm || c->nRanks == 1) { res->blocks = 0; res->launches = c->nRanks == 1 ? 0 : 1; return HCCL_SUCCESS; }
+    if (q.host || q.nRanks == 1) { res->blocks = 0; res->launches = q.nRanks == 1 ? 0 : 1; return HCCL_SUCCESS; }
     // mirror of the sole executor's loop bound: staged inputs go through the stage-in region, two-shot results through the exchange region
-    const StageLayout& L = c->layout();
+    const StageLayout& L = q.layout;
     const bool ll = sel.alg->devAlg == DALG_AR_LL || sel.alg->devAlg == DALG_AG_LL;
     uint64_t staged = (registered || ll) ? 0 : d.bytes;
     if (op == HCCL_CMD_ALLGATHER && !registered) staged = d.bytes / P;
@@ -263,8 +279,41 @@ HcclResult HcclCalcOpResource(HcclComm comm, HcclCMDType op, uint64_t count, Hcc
     if (sel.alg->devAlg == DALG_AR_TWOSHOT || sel.alg->devAlg == DALG_AR_NVLS || sel.alg->devAlg == DALG_AR_PUSH_TWOSHOT) traffic = perLaunch / P * 2 + 1;
     if (sel.alg->devAlg == DALG_RS_PUSH) traffic = perLaunch / P + 1;
     uint64_t nb = ll ? std::min<uint64_t>((perLaunch / (op == HCCL_CMD_ALLGATHER ? P : 1) + 8191) / 8192, 8) : (traffic + (128u << 10) - 1) / (128u << 10);
-    res->blocks = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(nb, (uint64_t)c->MaxBlocks()));
+    res->blocks = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(nb, (uint64_t)q.maxBlocks));
     return HCCL_SUCCESS;
+}
+}  // namespace
+
+extern "C" {
+
+HcclResult HcclCalcOpResource(HcclComm comm, HcclCMDType op, uint64_t count, HcclDataType dt, HcclReduceOp rop, int registered, HcclOpResource* res)
+{
+    CHK_PTR_NULL(comm); CHK_PTR_NULL(res);
+    CommImpl* c = static_cast<CommImpl*>(comm);
+    const ResQueryCtx q{c->topo.get(), c->selector.get(), c->layout(), c->cfg.bufferBytes, c->nRanks, c->MaxBlocks(), c->cfg.engine, c->cfg.deterministic,
+                        c->nvls(), c->hostComm != nullptr, c->name, comm};
+    return CalcOpRes(q, op, count, dt, rop, registered, res);
+}
+
+// The same answer without a communicator or a device: one NVSwitch box of nRanks GPUs, a staging slab of bufferBytes
+// (0 = the default), the environment's engine and determinism settings.  (The reference sizes a graph node's resources
+// before any communicator exists: HcclCalcOpResOfflineGraphMode, interface_graph_mode/calc_resource_graph_mode.cc.)
+HcclResult HcclCalcOpResOfflineGraphMode(uint32_t nRanks, int nvls, uint64_t bufferBytes, HcclCMDType op, uint64_t count, HcclDataType dt,
+                                         HcclReduceOp rop, int registered, HcclOpResource* res)
+{
+    CHK_PTR_NULL(res);
+    if (nRanks < 1 || nRanks > (uint32_t)kMaxDevRanks) return HCCL_E_PARA;
+    EnsureAlgorithmsRegistered();
+    EffectiveConfig eff;
+    CHK_RET(MergeConfig(GetEnvConfig(), nullptr, &eff));
+    if (bufferBytes) eff.bufferBytes = bufferBytes;
+    const TopoInfo topo = SyntheticNvswitchBox(nRanks, nvls != 0, GlobalLinkModel().p2pGBs);
+    SelectorState st;
+    int maxBlocks = eff.maxBlocks ? (int)eff.maxBlocks : 128;
+    if (maxBlocks > kMaxBlocks) maxBlocks = kMaxBlocks;
+    const ResQueryCtx q{&topo, &st, MakeStageLayout(eff.bufferBytes, (int)nRanks), eff.bufferBytes, (int)nRanks, maxBlocks, eff.engine, eff.deterministic,
+                        nvls != 0, false, "offline", nullptr};
+    return CalcOpRes(q, op, count, dt, rop, registered, res);
 }
 
 uint32_t HcclAlgRegistryCount(void)

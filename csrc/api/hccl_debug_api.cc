@@ -138,21 +138,7 @@ HcclResult HcclDebugExplainDevice(uint32_t nRanks, int nvls, HcclCMDType op, uin
 {
     CHK_PTR_NULL(text);
     if (nRanks < 2 || nRanks > 8) return HCCL_E_PARA;
-    TopoInfo topo;
-    topo.nRanks = nRanks;
-    topo.rank = 0;
-    topo.serverOf.assign(nRanks, 0);
-    topo.podOf.assign(nRanks, 0);
-    topo.localOf.resize(nRanks);
-    for (uint32_t i = 0; i < nRanks; ++i) topo.localOf[i] = i;
-    topo.serverSizes = {nRanks};
-    topo.level0 = Level0Shape::MESH_1D;
-    topo.level0Link = LinkKind::NVLINK_SWITCH;
-    topo.nvls = nvls != 0;
-    topo.p2pAll = true;
-    topo.nvlinkCount = 18;
-    topo.linkGBs = GlobalLinkModel().p2pGBs;
-    topo.deviceName = "NVIDIA B200 (synthetic)";
+    const TopoInfo topo = SyntheticNvswitchBox(nRanks, nvls != 0, GlobalLinkModel().p2pGBs);
     OpDesc d;
     d.op = op; d.dtype = dt; d.redOp = rop; d.nRanks = nRanks; d.bytes = bytes;
     d.det = deterministic == 2 ? Deterministic::STRICT : deterministic == 1 ? Deterministic::ON : Deterministic::OFF;

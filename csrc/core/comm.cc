@@ -50,7 +50,7 @@ CommImpl::~CommImpl()
     delete dev_;
 }
 
-static StageLayout MakeLayout(uint64_t dataBytes, int nRanks)
+StageLayout MakeStageLayout(uint64_t dataBytes, int nRanks)
 {
     StageLayout l{};
     l.dataBytes = dataBytes;
@@ -90,7 +90,7 @@ HcclResult CommImpl::SetupDeviceState()
     dev_->status = dStatus_;
     dev_->timeoutNs = cfg.execTimeoutNs;
     dev_->stageBytes = slab_.size - kSlabDataOff;
-    layout_ = MakeLayout(dev_->stageBytes, nRanks);
+    layout_ = MakeStageLayout(dev_->stageBytes, nRanks);
     CHK_CUDA(cudaDeviceSynchronize());
     selector.reset(new SelectorState());
     plans.reset(new PlanCache());

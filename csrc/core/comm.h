@@ -54,6 +54,9 @@ struct StageLayout {
     uint64_t mailboxOff, mailboxHalf;  // p2p mailboxes: [from][2][half]
 };
 
+// How a staging slab of dataBytes is divided among stage-in region, exchange region and p2p mailboxes for nRanks ranks.
+StageLayout MakeStageLayout(uint64_t dataBytes, int nRanks);
+
 class CommImpl {
 public:
     CommImpl();

@@ -42,6 +42,15 @@ HcclResult HcclGroupUnbindThread(const char* group);
 HcclResult HcclCalcOpResGraphMode(const char* group, HcclCMDType op, uint64_t count, HcclDataType dataType, HcclReduceOp reduceOp,
                                   HcclOpResource* res);
 
+// The same for a group that exists (online; `registered` != 0: the node's buffers come from HcclMemAlloc), and for a
+// box that is only described (offline: no communicator, no device; nRanks GPUs behind one NVSwitch, nvls != 0 when the
+// switch reduces, bufferBytes = the staging slab, 0 for the configured default).  Reference: HcclCalcOpResOnline /
+// OfflineGraphMode (interface_graph_mode/calc_resource_graph_mode.cc).
+HcclResult HcclCalcOpResOnlineGraphMode(const char* group, HcclCMDType op, uint64_t count, HcclDataType dataType, HcclReduceOp reduceOp, int registered,
+                                        HcclOpResource* res);
+HcclResult HcclCalcOpResOfflineGraphMode(uint32_t nRanks, int nvls, uint64_t bufferBytes, HcclCMDType op, uint64_t count, HcclDataType dataType,
+                                         HcclReduceOp reduceOp, int registered, HcclOpResource* res);
+
 HcclResult HcclAllReduceGraphMode(void* sendBuf, void* recvBuf, uint64_t count, HcclDataType dataType, HcclReduceOp op, const char* group,
                                   const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream);
 HcclResult HcclBroadcastGraphMode(void* buf, uint64_t count, HcclDataType dataType, uint32_t root, const char* group, const char* tag,
@@ -57,6 +66,18 @@ HcclResult HcclScatterGraphMode(void* sendBuf, void* recvBuf, uint64_t recvCount
 HcclResult HcclAlltoAllGraphMode(const void* sendBuf, uint64_t sendCount, HcclDataType sendType, const void* recvBuf, uint64_t recvCount,
                                  HcclDataType recvType, const char* group, const char* tag, const HcclResPackGraphMode* res,
                                  hcclStream_t stream);
+// Counts and displacements: host arrays of uint64_t, as in the operators themselves.
+HcclResult HcclAllGatherVGraphMode(void* sendBuf, void* recvBuf, uint64_t sendCount, const void* recvCounts, const void* recvDispls,
+                                   HcclDataType dataType, const char* group, const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream);
+HcclResult HcclReduceScatterVGraphMode(void* sendBuf, const void* sendCounts, const void* sendDispls, void* recvBuf, uint64_t recvCount,
+                                       HcclDataType dataType, HcclReduceOp op, const char* group, const char* tag, const HcclResPackGraphMode* res,
+                                       hcclStream_t stream);
+HcclResult HcclAlltoAllVGraphMode(const void* sendBuf, const void* sendCounts, const void* sdispls, HcclDataType sendType, const void* recvBuf,
+                                  const void* recvCounts, const void* rdispls, HcclDataType recvType, const char* group, const char* tag,
+                                  const HcclResPackGraphMode* res, hcclStream_t stream);
+HcclResult HcclAlltoAllVCGraphMode(const void* sendBuf, const void* sendCountMatrix, HcclDataType sendType, const void* recvBuf,
+                                   HcclDataType recvType, const char* group, const char* tag, const HcclResPackGraphMode* res,
+                                   hcclStream_t stream);
 HcclResult HcclSendGraphMode(void* sendBuf, uint64_t count, HcclDataType dataType, uint32_t destRank, const char* group, const char* tag,
                              const HcclResPackGraphMode* res, hcclStream_t stream);
 HcclResult HcclRecvGraphMode(void* recvBuf, uint64_t count, HcclDataType dataType, uint32_t srcRank, const char* group, const char* tag,

@@ -236,4 +236,24 @@ HcclResult MatchTopo(const TopoInfo& t, TopoMatchKind kind, AlgHierarchy* out)
     return HCCL_SUCCESS;
 }
 
+TopoInfo SyntheticNvswitchBox(uint32_t nRanks, bool nvls, double linkGBs)
+{
+    TopoInfo topo;
+    topo.nRanks = nRanks;
+    topo.rank = 0;
+    topo.serverOf.assign(nRanks, 0);
+    topo.podOf.assign(nRanks, 0);
+    topo.localOf.resize(nRanks);
+    for (uint32_t i = 0; i < nRanks; ++i) topo.localOf[i] = i;
+    topo.serverSizes = {nRanks};
+    topo.level0 = Level0Shape::MESH_1D;
+    topo.level0Link = LinkKind::NVLINK_SWITCH;
+    topo.nvls = nvls;
+    topo.p2pAll = true;
+    topo.nvlinkCount = 18;
+    topo.linkGBs = linkGBs;
+    topo.deviceName = "NVIDIA B200 (synthetic)";
+    return topo;
+}
+
 }  // namespace hccl

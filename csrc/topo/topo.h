@@ -62,6 +62,10 @@ struct AlgHierarchy {
     std::vector<std::vector<std::vector<uint32_t>>> infos;
     uint32_t levels() const { return (uint32_t)infos.size(); }
 };
+// One NVSwitch box of nRanks B200s as the probe would describe it, without a device (offline resource queries, tests
+// of the cost model).
+TopoInfo SyntheticNvswitchBox(uint32_t nRanks, bool nvls, double linkGBs);
+
 enum class TopoMatchKind : int { ONE_LEVEL = 0, TWO_LEVEL = 1, THREE_LEVEL = 2, SQUEEZE_2D = 3 };
 // ONE_LEVEL: all ranks in one group.  TWO_LEVEL: level 0 = ranks of my server,
 // level 1 = ranks with my local index across servers (requires symmetric

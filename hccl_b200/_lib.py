@@ -213,3 +213,9 @@ _sig("HcclAlltoAllGraphMode", R, c_void_p, c_uint64, c_int, c_void_p, c_uint64, 
 _sig("HcclSendGraphMode", R, c_void_p, c_uint64, c_int, c_uint32, c_char_p, c_char_p, _RP, c_void_p)
 _sig("HcclRecvGraphMode", R, c_void_p, c_uint64, c_int, c_uint32, c_char_p, c_char_p, _RP, c_void_p)
 _sig("HcclBarrierGraphMode", R, c_char_p, c_char_p, _RP, c_void_p)
+_sig("HcclAllGatherVGraphMode", R, c_void_p, c_void_p, c_uint64, c_void_p, c_void_p, c_int, c_char_p, c_char_p, _RP, c_void_p)
+_sig("HcclReduceScatterVGraphMode", R, c_void_p, c_void_p, c_void_p, c_void_p, c_uint64, c_int, c_int, c_char_p, c_char_p, _RP, c_void_p)
+_sig("HcclAlltoAllVGraphMode", R, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_char_p, c_char_p, _RP, c_void_p)
+_sig("HcclAlltoAllVCGraphMode", R, c_void_p, c_void_p, c_int, c_void_p, c_int, c_char_p, c_char_p, _RP, c_void_p)
+_sig("HcclCalcOpResOnlineGraphMode", R, c_char_p, c_int, c_uint64, c_int, c_int, c_int, POINTER(HcclOpResource))
+_sig("HcclCalcOpResOfflineGraphMode", R, c_uint32, c_int, c_uint64, c_int, c_uint64, c_int, c_int, c_int, POINTER(HcclOpResource))

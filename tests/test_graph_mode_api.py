@@ -35,6 +35,19 @@ def test_named_group_runs_every_twin():
     a2a_in = [np.arange(count * n, dtype=np.int64) + 10 ** 6 * r for r in range(n)]
     a2a_out = [np.zeros(count * n, np.int64) for _ in range(n)]
     got = [np.zeros(5, np.int32) for _ in range(n)]
+    v_counts = [3 + 2 * r for r in range(n)]
+    v_cnt = np.array(v_counts, np.uint64)
+    v_dsp = np.array([sum(v_counts[:r]) + r for r in range(n)], np.uint64)            # a gap of one element between blocks
+    v_total = int(v_dsp[-1]) + v_counts[-1]
+    agv_in = [np.full(v_counts[r], 10 + r, np.int32) for r in range(n)]
+    agv_out = [np.full(v_total, -1, np.int32) for _ in range(n)]
+    rsv_in = [np.random.default_rng(50 + r).standard_normal(v_total).astype(np.float32) for r in range(n)]
+    rsv_out = [np.zeros(v_counts[r], np.float32) for r in range(n)]
+    m_cnt = [[(i * 3 + j) % 4 + 1 for j in range(n)] for i in range(n)]
+    m_flat = np.array(m_cnt, np.uint64).reshape(-1)
+    a2av_in = [np.arange(sum(m_cnt[i]), dtype=np.float32) + 100 * i for i in range(n)]
+    a2av_out = [np.zeros(sum(m_cnt[j][i] for j in range(n)), np.float32) for i in range(n)]
+    a2avc_out = [np.zeros_like(x) for x in a2av_out]
 
     def body(r, c):
         ok = lambda code: code == 0 or (_ for _ in ()).throw(AssertionError(Result(code)))  # noqa: E731
@@ -55,6 +68,14 @@ def test_named_group_runs_every_twin():
         else:
             ok(lib.HcclRecvGraphMode(ptr(got[r]), 5, DataType.INT32, r - 1, group, b"node_p2p", None, None))
         ok(lib.HcclBarrierGraphMode(group, b"node_bar", None, None))
+        # the variable-count twins: counts and displacements are host arrays of uint64
+        ok(lib.HcclAllGatherVGraphMode(ptr(agv_in[r]), ptr(agv_out[r]), v_counts[r], ptr(v_cnt), ptr(v_dsp), DataType.INT32, group, b"node_agv", None, None))
+        ok(lib.HcclReduceScatterVGraphMode(ptr(rsv_in[r]), ptr(v_cnt), ptr(v_dsp), ptr(rsv_out[r]), v_counts[r], DataType.FP32, ReduceOp.SUM, group, b"node_rsv", None, None))
+        sc, sd = np.array(m_cnt[r], np.uint64), np.array([sum(m_cnt[r][:j]) for j in range(n)], np.uint64)
+        rc = np.array([m_cnt[j][r] for j in range(n)], np.uint64)
+        rd = np.array([sum(rc[:j]) for j in range(n)], np.uint64)
+        ok(lib.HcclAlltoAllVGraphMode(ptr(a2av_in[r]), ptr(sc), ptr(sd), DataType.FP32, ptr(a2av_out[r]), ptr(rc), ptr(rd), DataType.FP32, group, b"node_a2av", None, None))
+        ok(lib.HcclAlltoAllVCGraphMode(ptr(a2av_in[r]), ptr(m_flat), DataType.FP32, ptr(a2avc_out[r]), DataType.FP32, group, b"node_a2avc", None, None))
         ok(lib.HcclGroupUnbindThread(group))
 
     run_ranks(comms, body)
@@ -70,6 +91,16 @@ def test_named_group_runs_every_twin():
             assert np.array_equal(a2a_out[r][q * count:(q + 1) * count], a2a_in[q][r * count:(r + 1) * count])
         if r % 2:
             assert np.all(got[r] == r - 1)
+        for q in range(n):
+            assert np.all(agv_out[r][int(v_dsp[q]):int(v_dsp[q]) + v_counts[q]] == 10 + q)
+        rsv_ref = np.sum(np.stack(rsv_in).astype(np.float64), 0)
+        np.testing.assert_allclose(rsv_out[r], rsv_ref[int(v_dsp[r]):int(v_dsp[r]) + v_counts[r]], rtol=2e-6, atol=2e-5)
+        off = 0
+        for j in range(n):
+            sdj = sum(m_cnt[j][:r])
+            assert np.array_equal(a2av_out[r][off:off + m_cnt[j][r]], a2av_in[j][sdj:sdj + m_cnt[j][r]])
+            off += m_cnt[j][r]
+        assert np.array_equal(a2av_out[r], a2avc_out[r])
     for c in comms:
         c.destroy()
 
@@ -85,6 +116,19 @@ def test_lookup_errors_resource_query_and_bad_pack():
     res = HcclOpResource()
     assert lib.HcclCalcOpResGraphMode(b"pair", Cmd.ALLREDUCE, 1 << 20, DataType.FP32, ReduceOp.SUM, ctypes.byref(res)) == 0
     assert res.streams == 1 and res.algName.decode().startswith("HostAllReduce")
+    assert lib.HcclCalcOpResOnlineGraphMode(b"pair", Cmd.ALLREDUCE, 1 << 20, DataType.FP32, ReduceOp.SUM, 0, ctypes.byref(res)) == 0
+    assert res.algName.decode().startswith("HostAllReduce")
+    # offline: eight GPUs behind a switch that reduces, default slab, nobody initialised - the device selector's answer
+    off = HcclOpResource()
+    assert lib.HcclCalcOpResOfflineGraphMode(8, 1, 0, Cmd.ALLREDUCE, 16 << 20, DataType.BFP16, ReduceOp.SUM, 1, ctypes.byref(off)) == 0
+    assert off.algName.decode() == "NvlsAllReduceSoleMesh" and off.launches == 1 and off.scratchBytes == 0 and 1 <= off.blocks <= 128
+    assert lib.HcclCalcOpResOfflineGraphMode(8, 1, 0, Cmd.ALLREDUCE, 1 << 30, DataType.BFP16, ReduceOp.SUM, 0, ctypes.byref(off)) == 0
+    assert off.launches > 1 and off.scratchBytes > 0                      # ordinary buffers of 2 GiB go through the slab in several launches
+    assert lib.HcclCalcOpResOfflineGraphMode(8, 1, 64 << 20, Cmd.ALLREDUCE, 1 << 30, DataType.BFP16, ReduceOp.SUM, 0, ctypes.byref(res)) == 0
+    assert res.launches > off.launches                                    # a smaller slab, more launches
+    assert lib.HcclCalcOpResOfflineGraphMode(8, 0, 0, Cmd.REDUCE_SCATTER, 1 << 20, DataType.FP32, ReduceOp.SUM, 1, ctypes.byref(off)) == 0
+    assert off.algName.decode() == "P2pReduceScatterSoleMesh"
+    assert lib.HcclCalcOpResOfflineGraphMode(9, 1, 0, Cmd.ALLREDUCE, 4, DataType.FP32, ReduceOp.SUM, 0, ctypes.byref(off)) == Result.E_PARA
     bad = HcclResPackGraphMode(4, None, 0, None, 0)
     x = np.zeros(4, np.float32)
     assert lib.HcclAllReduceGraphMode(ptr(x), ptr(x), 4, DataType.FP32, ReduceOp.SUM, b"pair", b"t", ctypes.byref(bad), None) == Result.E_PARA
