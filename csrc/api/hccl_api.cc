@@ -13,7 +13,12 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <mutex>
+#include <new>
+#include <string>
 #include "../core/log.h"
+#include "../core/plan_cache.h"
+#include "../kernels/dev_types.h"
 #include "../ops/op_common.h"
 #include "../ops/param_check.h"
 #include "hccl/hccl.h"
@@ -514,6 +519,110 @@ HcclResult HcclCalcOpResOnlineGraphMode(const char* group, HcclCMDType op, uint6
     CommImpl* c = nullptr;
     CHK_RET(ResolveGroup(group, &c));
     return HcclCalcOpResource(c, op, count, dataType, reduceOp, registered, res);
+}
+
+struct HcclOpParamGraphMode {
+    HcclCMDType op = HCCL_CMD_ALLREDUCE;
+    uint64_t count = 0, bufferBytes = 0;
+    uint32_t rankSize = 8, blockLimit = 0;
+    HcclDataType dataType = HCCL_DATA_TYPE_FP32;
+    HcclReduceOp reduceOp = HCCL_REDUCE_SUM;
+    int registered = 0, switchReduces = 1;
+};
+HcclResult HcclCreateOpParamGraphMode(HcclOpParamGraphMode** opParam)
+{
+    CHK_PTR_NULL(opParam);
+    *opParam = new (std::nothrow) HcclOpParamGraphMode();
+    return *opParam ? HCCL_SUCCESS : HCCL_E_MEMORY;
+}
+HcclResult HcclDestroyOpParamGraphMode(HcclOpParamGraphMode* opParam)
+{
+    CHK_PTR_NULL(opParam);
+    delete opParam;
+    return HCCL_SUCCESS;
+}
+HcclResult HcclSetOpParamGraphModeOpType(HcclOpParamGraphMode* opParam, const char* opType)
+{
+    CHK_PTR_NULL(opParam); CHK_PTR_NULL(opType);
+    std::string s;
+    for (const char* p = opType; *p; ++p)
+        if (*p != '_') s.push_back((char)tolower((unsigned char)*p));
+    if (s.compare(0, 4, "hcom") == 0) s.erase(0, 4);
+    else if (s.compare(0, 4, "hccl") == 0) s.erase(0, 4);
+    for (int op = 0; op < (int)HCCL_CMD_MAX; ++op) {
+        std::string n;
+        for (const char* p = CmdName((HcclCMDType)op); p && *p; ++p) n.push_back((char)tolower((unsigned char)*p));
+        if (!n.empty() && n == s) { opParam->op = (HcclCMDType)op; return HCCL_SUCCESS; }
+    }
+    HCCL_ERROR("HcclSetOpParamGraphModeOpType: unknown operator '%s'", opType);
+    return HCCL_E_PARA;
+}
+HcclResult HcclSetOpParamGraphModeDataCount(HcclOpParamGraphMode* opParam, uint64_t dataCount) { CHK_PTR_NULL(opParam); opParam->count = dataCount; return HCCL_SUCCESS; }
+HcclResult HcclSetOpParamGraphModeRankSize(HcclOpParamGraphMode* opParam, uint32_t rankSize)
+{
+    CHK_PTR_NULL(opParam);
+    if (rankSize < 1 || rankSize > (uint32_t)kMaxDevRanks) return HCCL_E_PARA;
+    opParam->rankSize = rankSize;
+    return HCCL_SUCCESS;
+}
+HcclResult HcclSetOpParamGraphModeHCCLBufferSize(HcclOpParamGraphMode* opParam, uint64_t bufferBytes) { CHK_PTR_NULL(opParam); opParam->bufferBytes = bufferBytes; return HCCL_SUCCESS; }
+HcclResult HcclSetOpParamGraphModeDataType(HcclOpParamGraphMode* opParam, HcclDataType dataType)
+{
+    CHK_PTR_NULL(opParam);
+    if (DataTypeSize(dataType) == 0) return HCCL_E_PARA;
+    opParam->dataType = dataType;
+    return HCCL_SUCCESS;
+}
+HcclResult HcclSetOpParamGraphModeReduceType(HcclOpParamGraphMode* opParam, HcclReduceOp reduceOp) { CHK_PTR_NULL(opParam); opParam->reduceOp = reduceOp; return HCCL_SUCCESS; }
+HcclResult HcclSetOpParamGraphModeRegistered(HcclOpParamGraphMode* opParam, int registered, int switchReduces)
+{
+    CHK_PTR_NULL(opParam);
+    opParam->registered = registered != 0;
+    opParam->switchReduces = switchReduces != 0;
+    return HCCL_SUCCESS;
+}
+HcclResult HcclSetOpParamGraphModeBlockLimit(HcclOpParamGraphMode* opParam, uint32_t blockLimit)
+{
+    CHK_PTR_NULL(opParam);
+    if (blockLimit > (uint32_t)kMaxBlocks) return HCCL_E_PARA;
+    opParam->blockLimit = blockLimit;
+    return HCCL_SUCCESS;
+}
+HcclResult HcclCalcOpResOpParamGraphMode(const HcclOpParamGraphMode* opParam, uint64_t* opMemSize, uint32_t* streamNum, uint32_t* taskNum, uint32_t* blockNum,
+                                         char algName[128])
+{
+    CHK_PTR_NULL(opParam);
+    HcclOpResource r;
+    CHK_RET(HcclCalcOpResOfflineGraphMode(opParam->rankSize, opParam->switchReduces, opParam->bufferBytes, opParam->op, opParam->count, opParam->dataType,
+                                          opParam->reduceOp, opParam->registered, &r));
+    if (opMemSize) *opMemSize = r.scratchBytes;
+    if (streamNum) *streamNum = r.streams;
+    if (taskNum) *taskNum = r.launches;
+    if (blockNum) *blockNum = opParam->blockLimit && r.blocks > opParam->blockLimit ? opParam->blockLimit : r.blocks;
+    if (algName) snprintf(algName, 128, "%s", r.algName);
+    return HCCL_SUCCESS;
+}
+HcclResult HcclSelectAlgGraphMode(const char* group, uint64_t count, HcclDataType dataType, HcclReduceOp op, HcclCMDType opType, uint32_t blockLimit,
+                                  bool* onDevice, char algName[128])
+{
+    CommImpl* c = nullptr;
+    CHK_RET(ResolveGroup(group, &c));
+    (void)blockLimit;                       // the grid does not change which algorithm runs
+    HcclOpResource r;
+    CHK_RET(HcclCalcOpResource(c, opType, count, dataType, op, 0, &r));
+    if (onDevice) *onDevice = r.engine != (uint32_t)HCCL_ENGINE_HOSTCPU;
+    if (algName) snprintf(algName, 128, "%s", r.algName);
+    return HCCL_SUCCESS;
+}
+HcclResult HcclSetBlockLimitGraphMode(const char* group, uint32_t blockLimit)
+{
+    CommImpl* c = nullptr;
+    CHK_RET(ResolveGroup(group, &c));
+    if (blockLimit > (uint32_t)kMaxBlocks) return HCCL_E_PARA;
+    std::lock_guard<std::mutex> lk(c->opMu);
+    c->cfg.maxBlocks = blockLimit;
+    if (c->plans) c->plans->Clear();        // launch shapes were planned for the old grid
+    return HCCL_SUCCESS;
 }
 
 #define GRAPH_NODE() GraphNode node; CHK_RET(node.Begin(group, tag, res))

@@ -18,6 +18,7 @@
 #ifndef HCCL_B200_GRAPH_MODE_H
 #define HCCL_B200_GRAPH_MODE_H
 #include "hccl.h"
+#include <stdbool.h>
 #include "hccl_ext.h"
 
 #ifdef __cplusplus
@@ -50,6 +51,33 @@ HcclResult HcclCalcOpResOnlineGraphMode(const char* group, HcclCMDType op, uint6
                                         HcclOpResource* res);
 HcclResult HcclCalcOpResOfflineGraphMode(uint32_t nRanks, int nvls, uint64_t bufferBytes, HcclCMDType op, uint64_t count, HcclDataType dataType,
                                          HcclReduceOp reduceOp, int registered, HcclOpResource* res);
+
+// A node described field by field, for graph builders that assemble an operator before any group exists (reference:
+// HcclCreateOpParamGraphMode / HcclSetOpParamGraphMode<Field> / HcclCalcOpResOnlineGraphMode(opParam, ...) /
+// HcclSetAivSelectOpParamGraphMode, calc_resource_graph_mode.h).  Defaults: 8 ranks, switch reduction available, the
+// configured slab, fp32, sum, ordinary buffers, no block limit.  The operator is named as the graph names it:
+// "AllReduce", "HcomAllReduce", "allreduce", ... (prefix and case are ignored).  The vector cores of the reference
+// correspond to thread blocks here: a block limit caps the grid of the node's kernels.
+typedef struct HcclOpParamGraphMode HcclOpParamGraphMode;
+HcclResult HcclCreateOpParamGraphMode(HcclOpParamGraphMode** opParam);
+HcclResult HcclDestroyOpParamGraphMode(HcclOpParamGraphMode* opParam);
+HcclResult HcclSetOpParamGraphModeOpType(HcclOpParamGraphMode* opParam, const char* opType);
+HcclResult HcclSetOpParamGraphModeDataCount(HcclOpParamGraphMode* opParam, uint64_t dataCount);
+HcclResult HcclSetOpParamGraphModeRankSize(HcclOpParamGraphMode* opParam, uint32_t rankSize);
+HcclResult HcclSetOpParamGraphModeHCCLBufferSize(HcclOpParamGraphMode* opParam, uint64_t bufferBytes);
+HcclResult HcclSetOpParamGraphModeDataType(HcclOpParamGraphMode* opParam, HcclDataType dataType);
+HcclResult HcclSetOpParamGraphModeReduceType(HcclOpParamGraphMode* opParam, HcclReduceOp reduceOp);
+HcclResult HcclSetOpParamGraphModeRegistered(HcclOpParamGraphMode* opParam, int registered, int switchReduces);
+HcclResult HcclSetOpParamGraphModeBlockLimit(HcclOpParamGraphMode* opParam, uint32_t blockLimit);
+// opMemSize: staging bytes of the slab one launch uses; streamNum: 1; taskNum: kernel launches; blockNum: grid size.
+HcclResult HcclCalcOpResOpParamGraphMode(const HcclOpParamGraphMode* opParam, uint64_t* opMemSize, uint32_t* streamNum, uint32_t* taskNum,
+                                         uint32_t* blockNum, char algName[128]);
+// Which algorithm a node of an existing group will run and whether it runs on the device engines (the reference's
+// HcclSelectAlgGraphMode with its AIV flag); blockLimit 0 = the group's own.
+HcclResult HcclSelectAlgGraphMode(const char* group, uint64_t count, HcclDataType dataType, HcclReduceOp op, HcclCMDType opType, uint32_t blockLimit,
+                                  bool* onDevice, char algName[128]);
+// Caps the grids of every later operator of the group (1..128; 0 lifts the cap).  Reference: HcclSetAivCoreLimitGraphMode.
+HcclResult HcclSetBlockLimitGraphMode(const char* group, uint32_t blockLimit);
 
 HcclResult HcclAllReduceGraphMode(void* sendBuf, void* recvBuf, uint64_t count, HcclDataType dataType, HcclReduceOp op, const char* group,
                                   const char* tag, const HcclResPackGraphMode* res, hcclStream_t stream);

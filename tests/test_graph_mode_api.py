@@ -129,6 +129,38 @@ def test_lookup_errors_resource_query_and_bad_pack():
     assert lib.HcclCalcOpResOfflineGraphMode(8, 0, 0, Cmd.REDUCE_SCATTER, 1 << 20, DataType.FP32, ReduceOp.SUM, 1, ctypes.byref(off)) == 0
     assert off.algName.decode() == "P2pReduceScatterSoleMesh"
     assert lib.HcclCalcOpResOfflineGraphMode(9, 1, 0, Cmd.ALLREDUCE, 4, DataType.FP32, ReduceOp.SUM, 0, ctypes.byref(off)) == Result.E_PARA
+    # a node assembled field by field, before any group exists
+    for name in ("HcclCreateOpParamGraphMode", "HcclDestroyOpParamGraphMode", "HcclSetOpParamGraphModeOpType", "HcclSetOpParamGraphModeDataCount",
+                 "HcclSetOpParamGraphModeRankSize", "HcclSetOpParamGraphModeHCCLBufferSize", "HcclSetOpParamGraphModeDataType",
+                 "HcclSetOpParamGraphModeReduceType", "HcclSetOpParamGraphModeRegistered", "HcclSetOpParamGraphModeBlockLimit",
+                 "HcclCalcOpResOpParamGraphMode", "HcclSelectAlgGraphMode", "HcclSetBlockLimitGraphMode"):
+        getattr(lib, name).restype = ctypes.c_int
+    node = ctypes.c_void_p()
+    assert lib.HcclCreateOpParamGraphMode(ctypes.byref(node)) == 0 and node.value
+    assert lib.HcclSetOpParamGraphModeOpType(node, b"HcomReduceScatter") == 0
+    assert lib.HcclSetOpParamGraphModeOpType(node, b"butterfly") == Result.E_PARA
+    assert lib.HcclSetOpParamGraphModeOpType(node, b"all_reduce") == 0
+    assert lib.HcclSetOpParamGraphModeDataCount(node, ctypes.c_uint64(8 << 20)) == 0
+    assert lib.HcclSetOpParamGraphModeRankSize(node, 8) == 0 and lib.HcclSetOpParamGraphModeRankSize(node, 9) == Result.E_PARA
+    assert lib.HcclSetOpParamGraphModeDataType(node, int(DataType.BFP16)) == 0
+    assert lib.HcclSetOpParamGraphModeReduceType(node, int(ReduceOp.SUM)) == 0
+    assert lib.HcclSetOpParamGraphModeRegistered(node, 1, 1) == 0
+    mem, streams, tasks, blocks = ctypes.c_uint64(7), ctypes.c_uint32(), ctypes.c_uint32(), ctypes.c_uint32()
+    alg = ctypes.create_string_buffer(128)
+    assert lib.HcclCalcOpResOpParamGraphMode(node, ctypes.byref(mem), ctypes.byref(streams), ctypes.byref(tasks), ctypes.byref(blocks), alg) == 0
+    assert alg.value == b"NvlsAllReduceSoleMesh" and mem.value == 0 and streams.value == 1 and tasks.value == 1 and blocks.value > 4
+    assert lib.HcclSetOpParamGraphModeBlockLimit(node, 4) == 0 and lib.HcclSetOpParamGraphModeBlockLimit(node, 129) == Result.E_PARA
+    assert lib.HcclCalcOpResOpParamGraphMode(node, None, None, None, ctypes.byref(blocks), None) == 0 and blocks.value == 4
+    assert lib.HcclSetOpParamGraphModeRegistered(node, 0, 0) == 0 and lib.HcclSetOpParamGraphModeHCCLBufferSize(node, ctypes.c_uint64(32 << 20)) == 0
+    assert lib.HcclCalcOpResOpParamGraphMode(node, ctypes.byref(mem), None, ctypes.byref(tasks), None, alg) == 0
+    assert mem.value > 0 and tasks.value > 1 and alg.value.startswith(b"P2pAllReduce")      # 16 MiB through a 32 MiB slab, no switch
+    assert lib.HcclDestroyOpParamGraphMode(node) == 0
+    # selection for a node of a live group, and the group's block limit
+    on_device = ctypes.c_bool(True)
+    assert lib.HcclSelectAlgGraphMode(b"pair", ctypes.c_uint64(1 << 20), int(DataType.FP32), int(ReduceOp.SUM), int(Cmd.ALLREDUCE), 0, ctypes.byref(on_device), alg) == 0
+    assert alg.value.startswith(b"HostAllReduce") and on_device.value is False
+    assert lib.HcclSetBlockLimitGraphMode(b"pair", 16) == 0 and lib.HcclSetBlockLimitGraphMode(b"pair", 1000) == Result.E_PARA
+    assert lib.HcclSetBlockLimitGraphMode(b"nobody", 16) == Result.E_NOT_FOUND
     bad = HcclResPackGraphMode(4, None, 0, None, 0)
     x = np.zeros(4, np.float32)
     assert lib.HcclAllReduceGraphMode(ptr(x), ptr(x), 4, DataType.FP32, ReduceOp.SUM, b"pair", b"t", ctypes.byref(bad), None) == Result.E_PARA
