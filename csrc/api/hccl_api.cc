@@ -23,6 +23,7 @@
 #include "../ops/param_check.h"
 #include "hccl/hccl.h"
 #include "hccl/hccl_graph_mode.h"
+#include "hccl/hccl_mc2.h"
 
 using namespace hccl;
 
@@ -612,6 +613,36 @@ HcclResult HcclSelectAlgGraphMode(const char* group, uint64_t count, HcclDataTyp
     CHK_RET(HcclCalcOpResource(c, opType, count, dataType, op, 0, &r));
     if (onDevice) *onDevice = r.engine != (uint32_t)HCCL_ENGINE_HOSTCPU;
     if (algName) snprintf(algName, 128, "%s", r.algName);
+    return HCCL_SUCCESS;
+}
+HcclResult HcclCalcBlockNumGraphMode(const char* group, uint64_t count, HcclDataType dataType, HcclReduceOp op, HcclCMDType opType, uint32_t blockLimit,
+                                     uint32_t* numBlocks)
+{
+    CHK_PTR_NULL(numBlocks);
+    CommImpl* c = nullptr;
+    CHK_RET(ResolveGroup(group, &c));
+    HcclOpResource r;
+    CHK_RET(HcclCalcOpResource(c, opType, count, dataType, op, 0, &r));
+    *numBlocks = blockLimit && r.blocks > blockLimit ? blockLimit : r.blocks;
+    return HCCL_SUCCESS;
+}
+HcclResult HcclGetAlgExecParamGraphMode(const char* tag, const char* group, uint64_t count, HcclCMDType opType, HcclDataType dataType, HcclReduceOp op,
+                                        void** commContext, uint64_t* len)
+{
+    CHK_PTR_NULL(commContext); CHK_PTR_NULL(len);
+    CommImpl* c = nullptr;
+    CHK_RET(ResolveGroup(group, &c));
+    void* args = nullptr;
+    CHK_RET(HcclKfcAllocOpArgs(&args));
+    HcclKfcOpArgsSetSrcDataType(args, (uint8_t)dataType);
+    HcclKfcOpArgsSetDstDataType(args, (uint8_t)dataType);
+    HcclKfcOpArgsSetReduceType(args, (uint32_t)op);
+    HcclKfcOpArgsSetCount(args, count);
+    const HcclResult r = HcclCreateOpResCtx(c, (uint8_t)opType, args, commContext);
+    HcclKfcFreeOpArgs(args);
+    if (r != HCCL_SUCCESS) return r;
+    *len = sizeof(HcclMc2ResCtx);
+    HCCL_INFO("graph node %s: communicator context of group %s for %s", tag ? tag : "(untagged)", group, CmdName(opType));
     return HCCL_SUCCESS;
 }
 HcclResult HcclSetBlockLimitGraphMode(const char* group, uint32_t blockLimit)

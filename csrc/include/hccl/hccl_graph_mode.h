@@ -76,6 +76,15 @@ HcclResult HcclCalcOpResOpParamGraphMode(const HcclOpParamGraphMode* opParam, ui
 // HcclSelectAlgGraphMode with its AIV flag); blockLimit 0 = the group's own.
 HcclResult HcclSelectAlgGraphMode(const char* group, uint64_t count, HcclDataType dataType, HcclReduceOp op, HcclCMDType opType, uint32_t blockLimit,
                                   bool* onDevice, char algName[128]);
+// The grid a node of an existing group will launch (the reference's HcclCalcAivCoreNumGraphMode).
+HcclResult HcclCalcBlockNumGraphMode(const char* group, uint64_t count, HcclDataType dataType, HcclReduceOp op, HcclCMDType opType, uint32_t blockLimit,
+                                     uint32_t* numBlocks);
+// What a fused kernel of the graph needs to talk to the group without going through an operator call: *commContext
+// receives a DEVICE pointer to the group's HcclMc2ResCtx for opType (peer tables, flag rows, multicast alias;
+// hccl_mc2.h), *len its size.  The reference hands a graph's fused node its communicator context the same way
+// (HcclGetAlgExecParamGraphMode); the tag names the node in the logs.  Device communicators only.
+HcclResult HcclGetAlgExecParamGraphMode(const char* tag, const char* group, uint64_t count, HcclCMDType opType, HcclDataType dataType, HcclReduceOp op,
+                                        void** commContext, uint64_t* len);
 // Caps the grids of every later operator of the group (1..128; 0 lifts the cap).  Reference: HcclSetAivCoreLimitGraphMode.
 HcclResult HcclSetBlockLimitGraphMode(const char* group, uint32_t blockLimit);
 

@@ -161,6 +161,13 @@ def test_lookup_errors_resource_query_and_bad_pack():
     assert alg.value.startswith(b"HostAllReduce") and on_device.value is False
     assert lib.HcclSetBlockLimitGraphMode(b"pair", 16) == 0 and lib.HcclSetBlockLimitGraphMode(b"pair", 1000) == Result.E_PARA
     assert lib.HcclSetBlockLimitGraphMode(b"nobody", 16) == Result.E_NOT_FOUND
+    lib.HcclCalcBlockNumGraphMode.restype = lib.HcclGetAlgExecParamGraphMode.restype = ctypes.c_int
+    assert lib.HcclCalcBlockNumGraphMode(b"pair", ctypes.c_uint64(1 << 20), int(DataType.FP32), int(ReduceOp.SUM), int(Cmd.ALLREDUCE), 0, ctypes.byref(blocks)) == 0
+    assert blocks.value == 0                                  # a host-engine group launches no grid
+    ctx, length = ctypes.c_void_p(), ctypes.c_uint64()
+    args = (b"node_mm_rs", b"pair", ctypes.c_uint64(1 << 20), int(Cmd.REDUCE_SCATTER), int(DataType.BFP16), int(ReduceOp.SUM), ctypes.byref(ctx), ctypes.byref(length))
+    assert lib.HcclGetAlgExecParamGraphMode(*args) == Result.E_NOT_SUPPORT         # a communicator context exists on device groups only
+    assert lib.HcclGetAlgExecParamGraphMode(b"t", b"nobody", *args[2:]) == Result.E_NOT_FOUND
     bad = HcclResPackGraphMode(4, None, 0, None, 0)
     x = np.zeros(4, np.float32)
     assert lib.HcclAllReduceGraphMode(ptr(x), ptr(x), 4, DataType.FP32, ReduceOp.SUM, b"pair", b"t", ctypes.byref(bad), None) == Result.E_PARA
