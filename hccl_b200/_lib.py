@@ -217,5 +217,21 @@ _sig("HcclAllGatherVGraphMode", R, c_void_p, c_void_p, c_uint64, c_void_p, c_voi
 _sig("HcclReduceScatterVGraphMode", R, c_void_p, c_void_p, c_void_p, c_void_p, c_uint64, c_int, c_int, c_char_p, c_char_p, _RP, c_void_p)
 _sig("HcclAlltoAllVGraphMode", R, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_char_p, c_char_p, _RP, c_void_p)
 _sig("HcclAlltoAllVCGraphMode", R, c_void_p, c_void_p, c_int, c_void_p, c_int, c_char_p, c_char_p, _RP, c_void_p)
+_sig("HcclCreateOpParamGraphMode", R, POINTER(c_void_p))
+_sig("HcclDestroyOpParamGraphMode", R, c_void_p)
+_sig("HcclSetOpParamGraphModeOpType", R, c_void_p, c_char_p)
+_sig("HcclSetOpParamGraphModeDataCount", R, c_void_p, c_uint64)
+_sig("HcclSetOpParamGraphModeRankSize", R, c_void_p, c_uint32)
+_sig("HcclSetOpParamGraphModeHCCLBufferSize", R, c_void_p, c_uint64)
+_sig("HcclSetOpParamGraphModeDataType", R, c_void_p, c_int)
+_sig("HcclSetOpParamGraphModeReduceType", R, c_void_p, c_int)
+_sig("HcclSetOpParamGraphModeRegistered", R, c_void_p, c_int, c_int)
+_sig("HcclSetOpParamGraphModeBlockLimit", R, c_void_p, c_uint32)
+_sig("HcclCalcOpResOpParamGraphMode", R, c_void_p, POINTER(c_uint64), POINTER(c_uint32), POINTER(c_uint32), POINTER(c_uint32), c_char_p)
+_sig("HcclSelectAlgGraphMode", R, c_char_p, c_uint64, c_int, c_int, c_int, c_uint32, POINTER(ctypes.c_bool), c_char_p)
+_sig("HcclCalcBlockNumGraphMode", R, c_char_p, c_uint64, c_int, c_int, c_int, c_uint32, POINTER(c_uint32))
+_sig("HcclGetAlgExecParamGraphMode", R, c_char_p, c_char_p, c_uint64, c_int, c_int, c_int, POINTER(c_void_p), POINTER(c_uint64))
+_sig("HcclSetBlockLimitGraphMode", R, c_char_p, c_uint32)
+_sig("HcclAlgoPluginQueryAlgs", R, c_char_p, c_char_p, c_uint32, POINTER(c_uint32))
 _sig("HcclCalcOpResOnlineGraphMode", R, c_char_p, c_int, c_uint64, c_int, c_int, c_int, POINTER(HcclOpResource))
 _sig("HcclCalcOpResOfflineGraphMode", R, c_uint32, c_int, c_uint64, c_int, c_uint64, c_int, c_int, c_int, POINTER(HcclOpResource))
