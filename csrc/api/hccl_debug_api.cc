@@ -65,6 +65,15 @@ HcclResult HcclDebugStepTable(const char* kind, uint32_t p, uint32_t rank, const
     } else if (k == "pipeline") {
         // p = stages, rank = steps
         for (const PipeSlot& s : PipelineSchedule(p, rank)) os << "t " << s.time << " stage " << s.stage << " step " << s.step << "\n";
+    } else if (k == "ifname") {
+        // arg = "rule|name,name,...": which interface a rule of HCCL_SOCKET_IFNAME selects
+        const std::string a = arg ? arg : "";
+        const size_t bar = a.find('|');
+        std::vector<std::string> names;
+        std::stringstream ns(bar == std::string::npos ? std::string() : a.substr(bar + 1));
+        for (std::string n; std::getline(ns, n, ',');) names.push_back(n);
+        const int i = MatchInterfaceRule(a.substr(0, bar), names);
+        os << (i < 0 ? std::string("none") : names[(size_t)i]) << "\n";
     } else if (k == "parse_tree") {
         std::unique_ptr<AlgoTreeNode> tree;
         std::string err;
@@ -233,6 +242,10 @@ HcclResult HcclDebugParseEnv(const char* settings, char* text, uint32_t cap)
        << " algoSpecified=" << c.algo.global.specified << " perOp=" << c.algo.perOp.size() << "\n";
     os << "effective bufferBytes=" << eff.bufferBytes << " execTimeoutNs=" << eff.execTimeoutNs << " waitNs=" << tc.waitNs << " fullNs=" << tc.fullNs << " kernelNs="
        << tc.kernelNs << " hostNotifyNs=" << tc.hostNotifyNs << "\n";
+    os << "bootstrap ifname=" << c.socketIfname << " ipv6=" << c.socketIpv6 << " whitelistDisable=" << c.whitelistDisable << " whitelistFile=" << c.whitelistFile
+       << " portAuto=" << c.hostPortAuto << " ports=";
+    for (auto& r : c.hostPortRanges) os << r.first << "-" << r.second << ";";
+    os << " notApplicable=" << c.notApplicable.size() << "\n";
     for (auto& e : c.errors) os << "rejected: " << e << "\n";
     snprintf(text, cap, "%s", os.str().c_str());
     return HCCL_SUCCESS;

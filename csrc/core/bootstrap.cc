@@ -3,7 +3,13 @@
 #include <cerrno>
 #include <chrono>
 #include <cstring>
+#include <algorithm>
 #include <fcntl.h>
+#include <fstream>
+#include <ifaddrs.h>
+#include <net/if.h>
+#include <set>
+#include <sstream>
 #include <netinet/in.h>
 #include <netinet/tcp.h>
 #include <poll.h>
@@ -13,6 +19,7 @@
 #include <thread>
 #include <unistd.h>
 #include "config.h"
+#include "json.h"
 #include "log.h"
 
 namespace hccl {
@@ -51,7 +58,7 @@ bool ReadAll(int fd, void* buf, size_t n, int timeoutMs)
 
 // Relay: accepts nRanks connections, then for every round gathers one request of
 // equal size from each rank and answers with the concatenation.
-void RelayThread(int listenFd, uint64_t uniqueId)
+void RelayThread(int listenFd, uint64_t uniqueId, std::shared_ptr<std::set<uint32_t>> allowed)
 {
     std::vector<int> fds;
     uint32_t nRanks = 0;
@@ -61,8 +68,18 @@ void RelayThread(int listenFd, uint64_t uniqueId)
         struct pollfd pf = {listenFd, POLLIN, 0};
         int pr = ::poll(&pf, 1, 7200 * 1000);
         if (pr <= 0) { if (pr < 0 && errno == EINTR) continue; break; }
-        int fd = ::accept(listenFd, nullptr, nullptr);
+        struct sockaddr_in from;
+        socklen_t fromLen = sizeof(from);
+        int fd = ::accept(listenFd, (struct sockaddr*)&from, &fromLen);
         if (fd < 0) continue;
+        if (allowed && !allowed->count(from.sin_addr.s_addr)) {
+            // trust list (HCCL_WHITELIST_DISABLE=0): an address that is not listed never gets as far as the hello
+            char text[INET_ADDRSTRLEN] = {0};
+            inet_ntop(AF_INET, &from.sin_addr, text, sizeof(text));
+            HCCL_WARNING("rendezvous: connection from %s refused, the address is not in HCCL_WHITELIST_FILE", text);
+            ::close(fd);
+            continue;
+        }
         int one = 1;
         setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
         Hello h;
@@ -122,24 +139,119 @@ socklen_t FillUds(struct sockaddr_un* a, const std::string& name)
     return (socklen_t)(offsetof(struct sockaddr_un, sun_path) + 1 + name.size());
 }
 
+// The trust list of HCCL_WHITELIST_FILE: {"host_ip": ["a.b.c.d", ...]} (a "device_ip" array is accepted and unused).
+HcclResult LoadWhitelist(const std::string& path, std::set<uint32_t>* out)
+{
+    std::ifstream in(path);
+    if (!in) { HCCL_ERROR("HCCL_WHITELIST_DISABLE=0 but HCCL_WHITELIST_FILE '%s' cannot be read", path.c_str()); return HCCL_E_PARA; }
+    std::stringstream ss;
+    ss << in.rdbuf();
+    JsonValue root;
+    std::string err;
+    const std::string text = ss.str();
+    if (!JsonParser(text).Parse(&root, &err) || root.kind != JsonValue::OBJ) { HCCL_ERROR("HCCL_WHITELIST_FILE '%s': %s", path.c_str(), err.empty() ? "not an object" : err.c_str()); return HCCL_E_PARA; }
+    const JsonValue* hosts = root.Get("host_ip");
+    if (!hosts || hosts->kind != JsonValue::ARR) { HCCL_ERROR("HCCL_WHITELIST_FILE '%s': no \"host_ip\" array", path.c_str()); return HCCL_E_PARA; }
+    for (const JsonValue& v : hosts->arr) {
+        struct in_addr a;
+        if (v.kind != JsonValue::STR || inet_pton(AF_INET, v.str.c_str(), &a) != 1) { HCCL_ERROR("HCCL_WHITELIST_FILE '%s': '%s' is not a dotted IPv4 address", path.c_str(), v.str.c_str()); return HCCL_E_PARA; }
+        out->insert(a.s_addr);
+    }
+    return HCCL_SUCCESS;
+}
+
+}  // namespace
+
+// Which of the interfaces (name order as given) a rule of HCCL_SOCKET_IFNAME selects: -1 when none.  "eth,enp":
+// names with one of the prefixes; "=eth0,enp0": exactly these; a leading '^' turns either into an exclusion.
+int MatchInterfaceRule(const std::string& rule, const std::vector<std::string>& names)
+{
+    std::string body = rule;
+    bool exclude = false, exact = false;
+    if (!body.empty() && body[0] == '^') { exclude = true; body.erase(0, 1); }
+    if (!body.empty() && body[0] == '=') { exact = true; body.erase(0, 1); }
+    std::vector<std::string> keys;
+    std::stringstream ss(body);
+    for (std::string k; std::getline(ss, k, ',');)
+        if (!k.empty()) keys.push_back(k);
+    auto listed = [&](const std::string& n) {
+        for (const std::string& k : keys)
+            if (exact ? n == k : n.compare(0, k.size(), k) == 0) return true;
+        return false;
+    };
+    if (!exclude) {
+        // the first key that matches an interface wins (keys are a preference order)
+        for (const std::string& k : keys)
+            for (size_t i = 0; i < names.size(); ++i)
+                if (exact ? names[i] == k : names[i].compare(0, k.size(), k) == 0) return (int)i;
+        return -1;
+    }
+    for (size_t i = 0; i < names.size(); ++i)
+        if (!listed(names[i])) return (int)i;
+    return -1;
+}
+
+namespace {
+// IPv4 address of the interface HCCL_SOCKET_IFNAME selects.  Candidates in the order the reference documents for its
+// own default: interfaces other than docker* / lo by name, then docker*, then lo.
+HcclResult InterfaceAddress(const std::string& rule, std::string* ip)
+{
+    struct ifaddrs* list = nullptr;
+    if (getifaddrs(&list) != 0) return HCCL_E_SYSCALL;
+    std::vector<std::pair<std::string, std::string>> found;
+    for (struct ifaddrs* it = list; it; it = it->ifa_next) {
+        if (!it->ifa_addr || it->ifa_addr->sa_family != AF_INET || !(it->ifa_flags & IFF_UP)) continue;
+        char text[INET_ADDRSTRLEN] = {0};
+        inet_ntop(AF_INET, &((struct sockaddr_in*)it->ifa_addr)->sin_addr, text, sizeof(text));
+        found.emplace_back(it->ifa_name, text);
+    }
+    freeifaddrs(list);
+    auto klass = [](const std::string& n) { return n == "lo" ? 2 : n.compare(0, 6, "docker") == 0 ? 1 : 0; };
+    std::sort(found.begin(), found.end(), [&](const auto& a, const auto& b) { return klass(a.first) != klass(b.first) ? klass(a.first) < klass(b.first) : a.first < b.first; });
+    std::vector<std::string> names;
+    for (auto& f : found) names.push_back(f.first);
+    const int i = MatchInterfaceRule(rule, names);
+    if (i < 0) { HCCL_ERROR("HCCL_SOCKET_IFNAME=%s selects none of the %zu interfaces with an IPv4 address", rule.c_str(), names.size()); return HCCL_E_NOT_FOUND; }
+    *ip = found[(size_t)i].second;
+    HCCL_INFO("rendezvous address %s from interface %s (HCCL_SOCKET_IFNAME=%s)", ip->c_str(), found[(size_t)i].first.c_str(), rule.c_str());
+    return HCCL_SUCCESS;
+}
 }  // namespace
 
 HcclResult BootstrapCreateRootAt(const std::string& ipIn, uint32_t port, uint64_t uniqueId, HcclRootInfo* out)
 {
     CHK_PTR_NULL(out);
+    const EnvConfig& env = GetEnvConfig();
+    if (env.socketIpv6) { HCCL_ERROR("HCCL_SOCKET_FAMILY=AF_INET6: the rendezvous of this library speaks IPv4 only"); return HCCL_E_NOT_SUPPORT; }
+    std::shared_ptr<std::set<uint32_t>> allowed;
+    if (!env.whitelistDisable) {
+        allowed.reset(new std::set<uint32_t>());
+        CHK_RET(LoadWhitelist(env.whitelistFile, allowed.get()));
+    }
     std::string ip = ipIn.empty() ? "127.0.0.1" : ipIn;
-    int fd = ::socket(AF_INET, SOCK_STREAM, 0);
-    if (fd < 0) return HCCL_E_SYSCALL;
-    int one = 1;
-    setsockopt(fd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
     struct sockaddr_in addr;
     memset(&addr, 0, sizeof(addr));
     addr.sin_family = AF_INET;
-    addr.sin_port = htons((uint16_t)port);
-    if (inet_pton(AF_INET, ip.c_str(), &addr.sin_addr) != 1) { ::close(fd); HCCL_ERROR("bad rendezvous address '%s'", ip.c_str()); return HCCL_E_PARA; }
-    if (::bind(fd, (struct sockaddr*)&addr, sizeof(addr)) != 0 || ::listen(fd, 256) != 0) {
-        HCCL_ERROR("cannot listen on %s:%u: %s", ip.c_str(), port, strerror(errno));
+    if (inet_pton(AF_INET, ip.c_str(), &addr.sin_addr) != 1) { HCCL_ERROR("bad rendezvous address '%s'", ip.c_str()); return HCCL_E_PARA; }
+    // the ports to try: the caller's (a rank table names one), else HCCL_HOST_SOCKET_PORT_RANGE, else whatever is free
+    std::vector<uint32_t> ports;
+    if (port == 0 && !env.hostPortAuto)
+        for (auto& r : env.hostPortRanges)
+            for (uint32_t q = r.first; q <= r.second && ports.size() < 4096; ++q) ports.push_back(q);
+    if (ports.empty()) ports.push_back(port);
+    int fd = -1;
+    for (uint32_t q : ports) {
+        fd = ::socket(AF_INET, SOCK_STREAM, 0);
+        if (fd < 0) return HCCL_E_SYSCALL;
+        int reuse = 1;
+        setsockopt(fd, SOL_SOCKET, SO_REUSEADDR, &reuse, sizeof(reuse));
+        addr.sin_port = htons((uint16_t)q);
+        if (::bind(fd, (struct sockaddr*)&addr, sizeof(addr)) == 0 && ::listen(fd, 256) == 0) break;
         ::close(fd);
+        fd = -1;
+    }
+    if (fd < 0) {
+        HCCL_ERROR("cannot listen on %s, ports %u..%u: %s", ip.c_str(), ports.front(), ports.back(), strerror(errno));
         return HCCL_E_TCP_CONNECT;
     }
     socklen_t len = sizeof(addr);
@@ -151,7 +263,7 @@ HcclResult BootstrapCreateRootAt(const std::string& ipIn, uint32_t port, uint64_
     snprintf(p->ip, sizeof(p->ip), "%s", ip.c_str());
     p->port = ntohs(addr.sin_port);
     p->uniqueId = uniqueId;
-    std::thread(RelayThread, fd, uniqueId).detach();
+    std::thread(RelayThread, fd, uniqueId, allowed).detach();
     HCCL_INFO("rendezvous endpoint %s:%u id %016llx", p->ip, p->port, (unsigned long long)uniqueId);
     return HCCL_SUCCESS;
 }
@@ -162,7 +274,12 @@ HcclResult BootstrapCreateRoot(HcclRootInfo* out)
     std::random_device rd;
     uint64_t id = ((uint64_t)rd() << 32) ^ rd() ^ ((uint64_t)getpid() << 16) ^
                   (uint64_t)std::chrono::steady_clock::now().time_since_epoch().count();
-    return BootstrapCreateRootAt(env.ifIp, env.ifBasePort, id, out);
+    // the address: HCCL_IF_IP, else the interface HCCL_SOCKET_IFNAME selects, else the loopback (one box);
+    // the port: HCCL_HOST_SOCKET_PORT_RANGE when set (it takes precedence), else HCCL_IF_BASE_PORT, else any
+    std::string ip = env.ifIp;
+    if (ip.empty() && !env.socketIfname.empty()) CHK_RET(InterfaceAddress(env.socketIfname, &ip));
+    const bool ranged = env.hostPortAuto || !env.hostPortRanges.empty();
+    return BootstrapCreateRootAt(ip, ranged ? 0 : env.ifBasePort, id, out);
 }
 
 Bootstrap::~Bootstrap() { Close(); }

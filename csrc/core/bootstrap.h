@@ -31,6 +31,8 @@ constexpr uint32_t kRootInfoMagic = 0x48434c42u;  // "HCLB"
 
 // Creates the listening endpoint + relay thread and fills `out`.
 HcclResult BootstrapCreateRoot(HcclRootInfo* out);
+// Index of the interface a rule of HCCL_SOCKET_IFNAME selects among `names` (in that order), -1 for none.
+int MatchInterfaceRule(const std::string& rule, const std::vector<std::string>& names);
 // Same, with an explicit address (rank-table initialisation); port 0 = ephemeral.
 HcclResult BootstrapCreateRootAt(const std::string& ip, uint32_t port, uint64_t uniqueId, HcclRootInfo* out);
 

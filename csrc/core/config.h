@@ -8,6 +8,7 @@
 #pragma once
 #include <cstdint>
 #include <functional>
+#include <utility>
 #include <map>
 #include <string>
 #include <vector>
@@ -63,6 +64,13 @@ struct EnvConfig {
     std::string ifIp;                                 // HCCL_IF_IP
     uint32_t ifBasePort = 0;                          // HCCL_IF_BASE_PORT
     uint32_t connectTimeoutS = 120;                   // HCCL_CONNECT_TIMEOUT
+    std::string socketIfname;                         // HCCL_SOCKET_IFNAME: [^][=]name[,name...] - which NIC gives the rendezvous address
+    bool socketIpv6 = false;                          // HCCL_SOCKET_FAMILY=AF_INET6 (the rendezvous speaks IPv4: rejected with a message)
+    bool whitelistDisable = true;                     // HCCL_WHITELIST_DISABLE: 0 = only addresses of HCCL_WHITELIST_FILE may join
+    std::string whitelistFile;                        // HCCL_WHITELIST_FILE: {"host_ip": ["a.b.c.d", ...]}
+    bool hostPortAuto = false;                        // HCCL_HOST_SOCKET_PORT_RANGE=auto
+    std::vector<std::pair<uint32_t, uint32_t>> hostPortRanges;   // ... or ports / ranges, first..last inclusive; beats HCCL_IF_BASE_PORT
+    std::vector<std::string> notApplicable;           // variables of fabrics this library does not drive (RDMA, PCIe, UB): set, checked, without effect
     std::string tunerPlugin;                          // HCCL_ALG_TUNER_PLUGIN
     std::string algoPlugin;                           // HCCL_ALGO_PLUGIN_PATH
     std::vector<double> splitRatio;                   // HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO
