@@ -40,6 +40,25 @@ def test_example_plugin_builds_and_exports_its_entry(src, tmp_path):
     assert "GetHcclAlgoPlugin" in syms or "HcclTunerPluginOpsGet" in syms, syms[-500:]
 
 
+@pytest.mark.skipif(not Path(NVCC).exists(), reason="nvcc not found")
+def test_graph_node_resource_example_runs_without_a_gpu(tmp_path):
+    """The graph-mode sizing example needs no device: built, run, and its table checked."""
+    src = ROOT / "examples" / "04_graph_mode" / "node_resources.cc"
+    out = tmp_path / "node_resources"
+    subprocess.run([NVCC, "-std=c++17", f"-I{INC}", str(src), f"-L{LIBDIR}", "-lhccl_b200", "-Xlinker", f"-rpath={LIBDIR}", "-o", str(out)], check=True,
+                   capture_output=True)
+    r = subprocess.run([str(out), "8", "256"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("Hcom")]
+    assert len(lines) == 6
+    assert "NvlsAllReduceSoleMesh" in r.stdout or "P2pAllReduce" in r.stdout
+    big = next(ln for ln in lines if "536870912" in ln)
+    assert int(big.split()[-2]) > 1                      # a 1 GiB ordinary bucket goes through the slab in several launches
+    small = r.stdout.splitlines()
+    r4 = subprocess.run([str(out), "4", "64"], capture_output=True, text=True, timeout=120)
+    assert r4.returncode == 0 and "4 GPUs" in r4.stdout and small != r4.stdout.splitlines()
+
+
 def test_python_examples_and_benchmarks_compile():
     import py_compile
 
