@@ -363,6 +363,8 @@ void RegisterHostAlgorithms()
     auto TwoL1 = [](double p) { return 2 * Log2Ceil(p) + 1; };
     auto L1 = [](double p) { return Log2Ceil(p) + 1; };
     auto Four = [](double) { return 4.0; };
+    auto Five = [](double) { return 5.0; };
+    auto TwoL2 = [](double p) { return 2 * Log2Ceil(p) + 2; };
     Reg({"HostAllReduceConcurrentMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, true, TwoL, ar, false});
     Reg({"HostReduceScatterConcurrentMeshNHR", HCCL_CMD_REDUCE_SCATTER, HALG_RS_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, true, L, rs, false});
     Reg({"HostAllReduceSequence2DieMeshMesh", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_2DIE_MESH_MESH, "sequence2die", {"Mesh2Die", "Mesh2Die"}, AlgoType::TWO_DIE, 1, true, Four, ar, false});
@@ -386,11 +388,11 @@ void RegisterHostAlgorithms()
     Reg({"HostAllGatherParallelMeshMesh", HCCL_CMD_ALLGATHER, HALG_AG_PARALLEL_MESH_MESH, "parallel", {"Mesh", "Mesh"}, AlgoType::PIPELINE, 2, false, Four, rs, true});
     Reg({"HostReduceScatterParallelMeshMesh", HCCL_CMD_REDUCE_SCATTER, HALG_RS_PARALLEL_MESH_MESH, "parallel", {"Mesh", "Mesh"}, AlgoType::PIPELINE, 2, true, Four, rs, false});
     Reg({"HostBroadcastParallelMeshMesh", HCCL_CMD_BROADCAST, HALG_BCAST_PARALLEL_MESH_MESH, "parallel", {"Mesh", "Mesh"}, AlgoType::PIPELINE, 2, false, Four, ar, true});
-    Reg({"HostScatterParallelMeshMesh", HCCL_CMD_SCATTER, HALG_SCATTER_PARALLEL_MESH_MESH, "parallel", {"Mesh", "Mesh"}, AlgoType::PIPELINE, 2, false, Four, rs, true});
-    Reg({"HostReduceParallelMeshNHR", HCCL_CMD_REDUCE, HALG_REDUCE_PARALLEL_MESH_NHR, "parallel", {"Mesh", "NHR"}, AlgoType::PIPELINE, 2, true, TwoL1, ar, false});
+    Reg({"HostScatterParallelMeshMesh", HCCL_CMD_SCATTER, HALG_SCATTER_PARALLEL_MESH_MESH, "parallel", {"Mesh", "Mesh"}, AlgoType::PIPELINE, 2, false, Five, rs, true});
+    Reg({"HostReduceParallelMeshNHR", HCCL_CMD_REDUCE, HALG_REDUCE_PARALLEL_MESH_NHR, "parallel", {"Mesh", "NHR"}, AlgoType::PIPELINE, 2, true, TwoL2, ar, false});
     Reg({"HostAllGatherVPipelineMeshMesh", HCCL_CMD_ALLGATHER_V, HALG_AG_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, false, Four, rs, true});
-    Reg({"HostReducePipelineMeshNHR", HCCL_CMD_REDUCE, HALG_REDUCE_PIPELINE_MESH_NHR, "pipeline", {"Mesh", "NHR"}, AlgoType::OMNIPIPE, 2, true, TwoL1, ar, false});
-    Reg({"HostScatterPipelineMeshMesh", HCCL_CMD_SCATTER, HALG_SCATTER_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, false, Four, rs, true});
+    Reg({"HostReducePipelineMeshNHR", HCCL_CMD_REDUCE, HALG_REDUCE_PIPELINE_MESH_NHR, "pipeline", {"Mesh", "NHR"}, AlgoType::OMNIPIPE, 2, true, TwoL2, ar, false});
+    Reg({"HostScatterPipelineMeshMesh", HCCL_CMD_SCATTER, HALG_SCATTER_PIPELINE_MESH_MESH, "pipeline", {"Mesh", "Mesh"}, AlgoType::OMNIPIPE, 2, false, Five, rs, true});
     Reg({"HostAllGatherSoleMeshZAxisDetour", HCCL_CMD_ALLGATHER, HALG_AG_MESH_DETOUR, "sole", {"MeshZAxisDetour"}, AlgoType::DETOUR, 1, false, Two, rs, true});
     Reg({"HostReduceScatterSoleMeshZAxisDetour", HCCL_CMD_REDUCE_SCATTER, HALG_RS_MESH_DETOUR, "sole", {"MeshZAxisDetour"}, AlgoType::DETOUR, 1, true, Two, rs, false});
     Reg({"HostScatterSoleMeshZAxisDetour", HCCL_CMD_SCATTER, HALG_SCATTER_MESH_DETOUR, "sole", {"MeshZAxisDetour"}, AlgoType::DETOUR, 1, false, Two, rs, true});
