@@ -296,6 +296,8 @@ void RegisterHostAlgorithms()
     Reg({"HostAllReduceSoleRHD", HCCL_CMD_ALLREDUCE, HALG_AR_RHD, "sole", {"RHD"}, AlgoType::HD_R, 1, true, TwoL, ar, false});
     Reg({"HostAllReduceSoleNHR", HCCL_CMD_ALLREDUCE, HALG_AR_NHR, "sole", {"NHR"}, AlgoType::NHR, 1, true, TwoL, ar, false});
     Reg({"HostAllReduceStrictOrderedMesh", HCCL_CMD_ALLREDUCE, HALG_AR_ORDER_PRESERVED, "orderpreserved", {"OrderPreservedGroup"}, AlgoType::AHC, 1, true, Three, full, true});
+    // three levels first: on a topology with pods it wins the tie with the two-level forms, elsewhere it is filtered
+    Reg({"HostAllReduceSequenceMeshNHRNHR", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ3_MESH_NHR_NHR, "sequence", {"Mesh", "NHR", "NHR"}, AlgoType::NHR, 3, true, TwoL, ar, false});
     Reg({"HostAllReduceSequenceMeshRing", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_MESH_RING, "sequence", {"Mesh", "Ring"}, AlgoType::RING, 2, true, TwoP1, ar, false});
     Reg({"HostAllReduceSequenceMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_MESH_NHR, "sequence", {"Mesh", "NHR"}, AlgoType::NHR, 2, true, TwoL, ar, false});
     Reg({"HostAllReduceSequenceMeshRHD", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_MESH_RHD, "sequence", {"Mesh", "RHD"}, AlgoType::HD_R, 2, true, TwoL, ar, false});
@@ -303,7 +305,6 @@ void RegisterHostAlgorithms()
     // two-shot so that automatic selection keeps that one
     Reg({"HostAllReduceSequenceSqueeze2DMeshMesh", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ_SQUEEZE2D_MESH_MESH, "sequence", {"Mesh", "Mesh"}, AlgoType::HIER, 1, true,
          [](double) { return 4.0; }, ar, false});
-    Reg({"HostAllReduceSequenceMeshNHRNHR", HCCL_CMD_ALLREDUCE, HALG_AR_SEQ3_MESH_NHR_NHR, "sequence", {"Mesh", "NHR", "NHR"}, AlgoType::NHR, 3, true, TwoL, ar, false});
     Reg({"HostAllReduceParallelMeshNHR", HCCL_CMD_ALLREDUCE, HALG_AR_PARALLEL_MESH_NHR, "parallel", {"Mesh", "NHR"}, AlgoType::PIPELINE, 2, true, TwoL, ar, false});
     // ReduceScatter (+V)
     Reg({"HostReduceScatterSoleMesh", HCCL_CMD_REDUCE_SCATTER, HALG_RS_MESH, "sole", {"Mesh"}, AlgoType::MESH, 1, true, Two, rs, false});
