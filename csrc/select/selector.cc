@@ -523,7 +523,7 @@ HcclResult SelectAlgorithm(SelectorState& st, const TopoInfo& topo, const EnvCon
             }
         }
     }
-    // Phase 4: best engine tier, min cost, ties -> first registered
+    // Phase 4: best engine tier, min cost, ties -> deeper form, then first registered
     const std::vector<HcclCommEngine> tiers = EngineTiers(op.engine);
     for (HcclCommEngine tier : tiers) {
         int best = -1;
@@ -536,7 +536,13 @@ HcclResult SelectAlgorithm(SelectorState& st, const TopoInfo& topo, const EnvCon
             if (!inTier) continue;
             if (anyPref && !r.preferred) continue;
             if (best < 0 || r.cost < out->table[(size_t)best].cost) { best = (int)i; tie = false; }
-            else if (r.cost == out->table[(size_t)best].cost) tie = true;
+            else if (r.cost == out->table[(size_t)best].cost) {
+                // equal cost: the form written for more topology levels is the more specific one and wins quietly;
+                // between forms of the same depth the first registered one stays (and the tie is reported)
+                const uint32_t depth = a.attrs.minLevels, bestDepth = all[(size_t)out->table[(size_t)best].algIndex].attrs.minLevels;
+                if (depth > bestDepth) { best = (int)i; tie = false; }
+                else if (depth == bestDepth) tie = true;
+            }
         }
         if (best >= 0) {
             if (tie && !st.tieWarned[op.op]) {
