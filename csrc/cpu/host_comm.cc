@@ -375,6 +375,7 @@ void RegisterHostAlgorithms()
         keepConcur.push_back(std::string(op == HCCL_CMD_ALLTOALL ? "HostAlltoAll" : op == HCCL_CMD_ALLTOALLV ? "HostAlltoAllV" : "HostAlltoAllVC") + "ConcurrentMeshMesh");
         Reg({keepConcur.back().c_str(), op, HALG_A2A_CONCURRENT_MESH_MESH, "concurrent", {"Mesh", "Mesh"}, AlgoType::CONCURRENT, 1, false, Three, rs, true});
     }
+    Reg({"HostScatterConcurrentMeshMesh", HCCL_CMD_SCATTER, HALG_SCATTER_CONCURRENT_MESH_MESH, "concurrent", {"Mesh", "Mesh"}, AlgoType::CONCURRENT, 1, false, Three, rs, true});
     Reg({"HostBroadcastConcurrentMeshNHR", HCCL_CMD_BROADCAST, HALG_BCAST_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, false, L1, ar, true});
     Reg({"HostReduceConcurrentMeshNHR", HCCL_CMD_REDUCE, HALG_REDUCE_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, true, L1, ar, false});
     Reg({"HostAllGatherConcurrentMeshNHR", HCCL_CMD_ALLGATHER, HALG_AG_CONCURRENT_MESH_NHR, "concurrent", {"Mesh", "NHR"}, AlgoType::CONCURRENT, 1, false, L, rs, true});

@@ -251,6 +251,31 @@ void ConcurrentAlltoAll(HostWorld& w, HostPrims& x, const Group& all, uint32_t r
     x.SyncGroup(all.ranks, N_DONE);
 }
 
+// Scatter: the first part of a rank's block is pulled from the root (reads over the mesh links), the second part is
+// pushed by the root into the rank's staging buffer on the second queue (writes over the other link set) and copied
+// out locally; a part that does not fit the staging buffer is pulled as well.
+void ConcurrentScatter(HostWorld& w, HostPrims& x, const Group& all, uint32_t rank, const OpParam& p)
+{
+    const uint32_t es = DataTypeSize(p.dtype);
+    double sa, sb;
+    SplitShares(&sa, &sb);
+    uint64_t a = BandwidthSplit(p.count, sa, sb, std::max<uint64_t>(1, 128 / es));
+    if ((p.count - a) * es > w.scratchBytes()) a = p.count;
+    const uint64_t b = p.count - a, blk = p.count * es;
+    x.SyncGroup(all.ranks, N_READY);
+    if (a) x.Copy(Out(rank), In(p.root, (uint64_t)rank * blk), a * es, 0);
+    if (b) {
+        if (rank == p.root)
+            for (uint32_t k = 0; k < all.size(); ++k) {
+                const uint32_t j = all.world((all.me + k) % all.size());
+                x.Copy(j == rank ? Out(rank, a * es) : Scratch(j, 0), In(rank, (uint64_t)j * blk + a * es), b * es, 1);
+            }
+        x.SyncGroup(all.ranks, N_DATA, 1);
+        if (rank != p.root) x.Copy(Out(rank, a * es), Scratch(rank, 0), b * es, 1);
+    }
+    x.SyncGroup(all.ranks, N_DONE);
+}
+
 // Broadcast: both parts are scattered from the root (member i takes slice i of a part), then part A is gathered over
 // the mesh while part B is gathered by NHR on the second queue.
 void ConcurrentBroadcast(HostWorld& w, HostPrims& x, const Group& all, uint32_t rank, const OpParam& p)
@@ -1252,6 +1277,7 @@ HcclResult RunHostExecutorExt(HostWorld& w, uint32_t rank, int alg, const OpPara
         case HALG_AG_CONCURRENT_MESH_NHR: ConcurrentAllGather(w, x, all, rank, p); break;
         case HALG_BCAST_CONCURRENT_MESH_NHR: ConcurrentBroadcast(w, x, all, rank, p); break;
         case HALG_A2A_CONCURRENT_MESH_MESH: ConcurrentAlltoAll(w, x, all, rank, p); break;
+        case HALG_SCATTER_CONCURRENT_MESH_MESH: ConcurrentScatter(w, x, all, rank, p); break;
         case HALG_REDUCE_CONCURRENT_MESH_NHR: ConcurrentReduce(w, x, all, rank, p); break;
         case HALG_AG_PIPELINE_MESH_MESH: r = PipelineAllGather(w, x, rank, p); break;
         case HALG_RS_PIPELINE_MESH_MESH: r = PipelineReduceScatter(w, x, rank, p); break;

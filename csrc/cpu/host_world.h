@@ -195,7 +195,7 @@ enum HostAlg : int {
     HALG_AG_PARALLEL_MESH_MESH, HALG_RS_PARALLEL_MESH_MESH, HALG_BCAST_CONCURRENT_MESH_NHR, HALG_REDUCE_CONCURRENT_MESH_NHR,
     HALG_AR_SEQ_2DIE_MESH_MESH, HALG_AR_SOLE_MESH_CONCUR,
     HALG_BCAST_PARALLEL_MESH_MESH, HALG_SCATTER_PARALLEL_MESH_MESH, HALG_REDUCE_PARALLEL_MESH_NHR, HALG_A2A_CONCURRENT_MESH_MESH,
-    HALG_AG_PIPELINE3_MESH_MESH_MESH, HALG_RS_PIPELINE3_MESH_MESH_MESH, HALG_AG_SEQ3_MESH_NHR_NHR, HALG_RS_SEQ3_MESH_NHR_NHR,
+    HALG_AG_PIPELINE3_MESH_MESH_MESH, HALG_RS_PIPELINE3_MESH_MESH_MESH, HALG_AG_SEQ3_MESH_NHR_NHR, HALG_RS_SEQ3_MESH_NHR_NHR, HALG_SCATTER_CONCURRENT_MESH_MESH,
     HALG_COUNT
 };
 // Runs host algorithm `alg` for this rank; the world is already inside Enter().

@@ -156,6 +156,12 @@ def test_concurrent_executors(algo_env, n):
             verified(comms, lambda r, c: c.broadcast(bufs[r], root))
             assert comms[0].last_algorithm() == "HostBroadcastConcurrentMeshNHR", comms[0].last_algorithm()
             assert all(np.all(b == 100 + root) for b in bufs)
+            sc_in = np.random.default_rng(90 + root).integers(-1000, 1000, count * n).astype(np.int32)
+            sc_out = [np.zeros(count, np.int32) for _ in range(n)]
+            verified(comms, lambda r, c: c.scatter(sc_in if r == root else None, sc_out[r], root))
+            assert comms[0].last_algorithm() == "HostScatterConcurrentMeshMesh", comms[0].last_algorithm()
+            for r in range(n):
+                assert np.array_equal(sc_out[r], sc_in[r * count:(r + 1) * count])
             red_in = [np.random.default_rng(70 + r).standard_normal(count) for r in range(n)]
             red_out = np.zeros(count, np.float64)
             verified(comms, lambda r, c: c.reduce(red_in[r], red_out if r == root else None, root))
