@@ -1,5 +1,6 @@
 #include "selector.h"
 #include "auto_selector.h"
+#include <atomic>
 #include <algorithm>
 #include <chrono>
 #include <cmath>
@@ -545,8 +546,9 @@ HcclResult SelectAlgorithm(SelectorState& st, const TopoInfo& topo, const EnvCon
             }
         }
         if (best >= 0) {
-            if (tie && !st.tieWarned[op.op]) {
-                st.tieWarned[op.op] = true;
+            // once per operator and communicator, and at most a handful per process: threads-as-ranks share the finding
+            static std::atomic<uint32_t> processWide[HCCL_CMD_MAX];
+            if (tie && !st.tieWarned[op.op] && (st.tieWarned[op.op] = true) && processWide[op.op].fetch_add(1) < 2) {
                 HCCL_WARNING("cost tie for op %d at %llu bytes: first registered algorithm wins (said once per operator)", (int)op.op, (unsigned long long)op.bytes);
             }
             out->algIndex = out->table[(size_t)best].algIndex;
